@@ -1,0 +1,589 @@
+// bf16 GEMM  C[M,N] = A[M,K] * W[N,K]^T  (+bias[N]) (+residual[M,N]) on tcgen05 / TMEM.
+//
+// Two kernels:
+//   gemm_bf16_tn_kernel   persistent, 128 x BN output tiles (BN = 128 | 256), TMA-fed
+//                         smem ring, accumulators double-buffered in TMEM so the epilogue
+//                         of tile i overlaps the main loop of tile i+1. For M > 256.
+//   gemm_bf16_swap_kernel small-M ("decode") form: the weight tile is the 128-row MMA
+//                         operand and the activations are the N operand (UMMA N = M padded
+//                         to 16), so the weight stream is read exactly once; split-K over
+//                         blockIdx.y with fp32 partials reduced in fixed order.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2..5 = epilogue (each owns the TMEM lane quarter warp_id % 4).
+//
+// Replaces the library GEMM calls of the reference (src/vt/cuda/cuda_matmul.cu:284-355
+// "MatmulBT" and :219-274), which hand every projection to cuBLASLt.
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "sm100.cuh"
+
+namespace b200 {
+
+static constexpr int kBM = 128;
+static constexpr int kBK = 64;
+static constexpr int kGemmThreads = 192;
+static constexpr int kMaxStages = 12;
+
+struct GemmParams {
+  int M, N, K;
+  void* out;
+  int ldo;
+  int out_f32;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int ldr;
+  int* status;
+  int tiles_m, tiles_n;
+  int stages;
+  // swap-AB only
+  int mp;            // padded M = UMMA N
+  int splits;
+  int kb_per_split;
+  float* workspace;  // [splits, M, N] fp32 partials
+};
+
+struct alignas(8) GemmBarriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Grouped ordering: 16 consecutive M tiles share each N tile while it is L2-hot.
+  constexpr int G = 16;
+  int per_group = G * tiles_n;
+  int g = t / per_group;
+  int first_m = g * G;
+  int gsz = min(G, tiles_m - first_m);
+  int r = t - g * per_group;
+  tm = first_m + (r % gsz);
+  tn = r / gsz;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA,
+                        const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kABytes = kBM * kBK * 2;
+  constexpr int kBBytes = BN * kBK * 2;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  const int stages = p.stages;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + (size_t)stages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 4);
+    }
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 2 * BN >= 32 ? 2 * BN : 32);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % stages;
+          uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { ok = false; break; }
+          uint8_t* a_dst = smem + (size_t)s * kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          mbar_expect_tx(&bars->full[s], kStageBytes);
+          tma_load_2d(a_dst, &tmA, &bars->full[s], kb * kBK, tm * kBM);
+          tma_load_2d(b_dst, &tmB, &bars->full[s], kb * kBK, tn * BN);
+        }
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+        int buf = tc & 1;
+        uint32_t aph = (tc >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[buf], aph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          int s = it % stages;
+          uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->full[s], ph, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes);
+          uint32_t b_addr = a_addr + kABytes;
+          uint64_t adesc = umma_desc_k_sw128(a_addr, 1024);
+          uint64_t bdesc = umma_desc_k_sw128(b_addr, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // +32 bytes per 16-element K step inside the 128-byte swizzle row.
+            umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          }
+          umma_commit(&bars->empty[s]);
+        }
+        if (ok) umma_commit(&bars->acc_full[buf]);
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else {
+    // ---------------- Epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;
+    uint32_t tc = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      int buf = tc & 1;
+      uint32_t aph = (tc >> 1) & 1;
+      ok = mbar_wait(&bars->acc_full[buf], aph, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tm * kBM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.bias) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < p.N) {
+                uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + i);
+                float2 f;
+                f = unpack_bf16x2(b.x); v[i + 0] += f.x; v[i + 1] += f.y;
+                f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+                f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+                f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+              }
+            }
+          }
+          if (p.residual) {
+            const __nv_bfloat16* rr = p.residual + (size_t)row * p.ldr + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < p.N) {
+                uint4 b = *reinterpret_cast<const uint4*>(rr + i);
+                float2 f;
+                f = unpack_bf16x2(b.x); v[i + 0] += f.x; v[i + 1] += f.y;
+                f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+                f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+                f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+              }
+            }
+          }
+          if (p.out_f32) {
+            float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col0 + i < p.N)
+                *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldo + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < p.N) {
+                uint4 w;
+                w.x = pack_bf16x2(v[i + 0], v[i + 1]);
+                w.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                w.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                w.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(o + i) = w;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN >= 32 ? 2 * BN : 32);
+}
+
+// ---------------------------------------------------------------------------------------
+// Small-M swap-AB split-K kernel.
+// TMEM accumulator: lane = weight row (output column n), column = token m.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_bf16_swap_kernel(const __grid_constant__ CUtensorMap tmW,
+                          const __grid_constant__ CUtensorMap tmA, GemmParams p,
+                          uint32_t tmem_cols) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kWBytes = kBM * kBK * 2;
+  const int a_bytes = p.mp * kBK * 2;
+  // Keep every tile 1024-byte aligned (mp is a multiple of 16 -> a_bytes multiple of 2048).
+  const int stage_bytes = kWBytes + a_bytes;
+  const int stages = p.stages;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + (size_t)stages * stage_bytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tn = blockIdx.x;
+  const int split = blockIdx.y;
+  const int kblocks_total = (p.K + kBK - 1) / kBK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(kblocks_total, kb0 + p.kb_per_split);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->acc_full[0], 1);
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      tma_prefetch_desc(&tmA);
+      for (int i = 0; i < nkb; ++i) {
+        int s = i % stages;
+        uint32_t ph = (i / stages) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { bars->failed = 1; break; }
+        uint8_t* w_dst = smem + (size_t)s * stage_bytes;
+        uint8_t* a_dst = w_dst + kWBytes;
+        mbar_expect_tx(&bars->full[s], stage_bytes);
+        tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, tn * kBM);
+        tma_load_2d(a_dst, &tmA, &bars->full[s], (kb0 + i) * kBK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(kBM, p.mp);
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        int s = i % stages;
+        uint32_t ph = (i / stages) & 1;
+        if (!mbar_wait(&bars->full[s], ph, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t w_addr = smem_u32(smem + (size_t)s * stage_bytes);
+        uint32_t a_addr = w_addr + kWBytes;
+        uint64_t wdesc = umma_desc_k_sw128(w_addr, 1024);
+        uint64_t adesc = umma_desc_k_sw128(a_addr, 1024);
+#pragma unroll
+        for (int k = 0; k < kBK / 16; ++k)
+          umma_bf16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (i | k) != 0);
+        umma_commit(&bars->empty[s]);
+      }
+      if (ok) umma_commit(&bars->acc_full[0]);
+      else bars->failed = 1;
+    }
+  } else {
+    const int quarter = warp & 3;
+    bool ok = true;
+    if (nkb > 0) ok = mbar_wait(&bars->acc_full[0], 0, p.status);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    const int n = tn * kBM + quarter * 32 + lane;
+    const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    if (ok) {
+      float bias_v = 0.f;
+      if (p.bias && p.splits == 1 && n < p.N) bias_v = __bfloat162float(p.bias[n]);
+      for (int c = 0; c < p.mp / 16; ++c) {
+        uint32_t r[16];
+        if (nkb > 0) {
+          tmem_ld_32x32b_x16(t_addr + c * 16, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = 0;
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            int m = c * 16 + i;
+            if (m < p.M) {
+              float v = __uint_as_float(r[i]);
+              if (p.splits > 1) {
+                p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
+              } else {
+                v += bias_v;
+                if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.ldr + n]);
+                if (p.out_f32)
+                  reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] =
+                      __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// out[m,n] = sum_s ws[s,m,n] (+bias) (+residual), splits summed in ascending order.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N,
+                                     void* out, int ldo, int out_f32,
+                                     const __nv_bfloat16* __restrict__ bias,
+                                     const __nv_bfloat16* __restrict__ residual, int ldr) {
+  const int n4 = N >> 2;
+  const size_t total = (size_t)M * n4;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    int m = (int)(idx / n4);
+    int n = (int)(idx % n4) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(ws + (size_t)m * N + n);
+    for (int s = 1; s < splits; ++s) {
+      float4 v = *reinterpret_cast<const float4*>(ws + ((size_t)s * M + m) * N + n);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias) {
+      uint2 b = *reinterpret_cast<const uint2*>(bias + n);
+      float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y);
+      acc.x += f0.x; acc.y += f0.y; acc.z += f1.x; acc.w += f1.y;
+    }
+    if (residual) {
+      uint2 b = *reinterpret_cast<const uint2*>(residual + (size_t)m * ldr + n);
+      float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y);
+      acc.x += f0.x; acc.y += f0.y; acc.z += f1.x; acc.w += f1.y;
+    }
+    if (out_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)m * ldo + n) = acc;
+    } else {
+      uint2 w;
+      w.x = pack_bf16x2(acc.x, acc.y);
+      w.y = pack_bf16x2(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n) = w;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host launcher
+// ---------------------------------------------------------------------------------------
+struct TmapKey {
+  const void* p;
+  uint64_t rows, cols, ld;
+  uint32_t br, bc;
+  bool operator==(const TmapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && br == o.br && bc == o.bc;
+  }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.p);
+    h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    h ^= k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
+    h ^= k.ld * 0x165667b19e3779f9ull + (h << 6) + (h >> 2);
+    h ^= ((uint64_t)k.br << 32 | k.bc) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+static bool get_tmap_bf16(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols,
+                          uint64_t ld, uint32_t br, uint32_t bc) {
+  static std::mutex mu;
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  TmapKey key{p, rows, cols, ld, br, bc};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return true;
+    }
+  }
+  CUtensorMap m;
+  if (!encode_tmap_2d(&m, p, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols, ld, br, bc,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 65536) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return true;
+}
+
+static constexpr int kSmemBudget = 220 * 1024;
+
+template <int BN>
+static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
+                     cudaStream_t stream) {
+  constexpr int stage_bytes = kBM * kBK * 2 + BN * kBK * 2;
+  int stages = (kSmemBudget - 2048) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  int kblocks = (p.K + kBK - 1) / kBK;
+  if (stages > kblocks + 1) stages = kblocks + 1;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         kSmemBudget + 4096);
+    attr_set = true;
+  }
+  int tiles = p.tiles_m * p.tiles_n;
+  int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
+  gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                              int out_f32, const void* bias, const void* residual, int ldr, int M,
+                              int N, int K, void* workspace, size_t ws_bytes, int force_path,
+                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.status = device_status_word();
+  const int sms = b200_num_sms();
+  const int kblocks = (K + kBK - 1) / kBK;
+
+  bool use_swap = (M <= 256);
+  if (force_path == 1) use_swap = false;
+  if (force_path == 2 && M <= 256) use_swap = true;
+
+  if (use_swap) {
+    int mp = (M + 15) & ~15;
+    p.mp = mp;
+    p.tiles_n = (N + kBM - 1) / kBM;
+    int splits = 1;
+    if (p.tiles_n < sms) {
+      splits = (sms + p.tiles_n - 1) / p.tiles_n;
+      int max_by_k = kblocks / 4;
+      if (max_by_k < 1) max_by_k = 1;
+      if (splits > max_by_k) splits = max_by_k;
+      if (splits > 16) splits = 16;
+    }
+    if (splits > 1) {
+      size_t need = (size_t)splits * M * N * sizeof(float);
+      while (splits > 1 && (workspace == nullptr || need > ws_bytes)) {
+        --splits;
+        need = (size_t)splits * M * N * sizeof(float);
+      }
+    }
+    int kb_per = (kblocks + splits - 1) / splits;
+    splits = (kblocks + kb_per - 1) / kb_per;
+    p.splits = splits;
+    p.kb_per_split = kb_per;
+    p.workspace = reinterpret_cast<float*>(workspace);
+    int stage_bytes = kBM * kBK * 2 + mp * kBK * 2;
+    int stages = (kSmemBudget - 2048) / stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages > kb_per) stages = kb_per;
+    if (stages < 2) stages = 2;
+    p.stages = stages;
+    uint32_t tmem_cols = 32;
+    while ((int)tmem_cols < mp) tmem_cols <<= 1;
+    CUtensorMap tmW, tmA;
+    if (!get_tmap_bf16(&tmW, W, N, K, ldw, kBM, kBK)) return -3;
+    if (!get_tmap_bf16(&tmA, A, M, K, lda, mp, kBK)) return -3;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kSmemBudget + 4096);
+      attr_set = true;
+    }
+    size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+    dim3 grid(p.tiles_n, splits);
+    gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, p, tmem_cols);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+    if (splits > 1) {
+      size_t total = (size_t)M * (N / 4);
+      int blocks = (int)((total + 255) / 256);
+      if (blocks > sms * 8) blocks = sms * 8;
+      splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, out, ldo,
+                                                       out_f32, p.bias, p.residual, ldr);
+      if (cudaGetLastError() != cudaSuccess) return -2;
+    }
+    return 0;
+  }
+
+  p.tiles_m = (M + kBM - 1) / kBM;
+  int tn256 = (N + 255) / 256, tn128 = (N + 127) / 128;
+  long waves256 = ((long)p.tiles_m * tn256 + sms - 1) / sms;
+  long waves128 = ((long)p.tiles_m * tn128 + sms - 1) / sms;
+  bool use256 = (waves256 * 2 * 100 <= waves128 * 108);
+  if (force_path == 3) use256 = false;
+  if (force_path == 4) use256 = true;
+  CUtensorMap tmA, tmB;
+  if (!get_tmap_bf16(&tmA, A, M, K, lda, kBM, kBK)) return -3;
+  if (use256) {
+    p.tiles_n = tn256;
+    if (!get_tmap_bf16(&tmB, W, N, K, ldw, 256, kBK)) return -3;
+    return launch_tn<256>(tmA, tmB, p, stream);
+  }
+  p.tiles_n = tn128;
+  if (!get_tmap_bf16(&tmB, W, N, K, ldw, 128, kBK)) return -3;
+  return launch_tn<128>(tmA, tmB, p, stream);
+}

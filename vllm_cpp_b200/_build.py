@@ -1,0 +1,115 @@
+"""In-tree native build: CUDA kernels (sm_100a) -> ``_kernels.so``; host engine -> ``_engine*.so``.
+
+Everything is compiled with explicit ``nvcc`` / ``g++`` command lines (no JIT cache), so the
+shared objects sit inside the package directory and travel with the source tree.
+Objects are rebuilt only when a source or header is newer than the object.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+BUILD = ROOT / "build"
+
+NVCC = os.environ.get("NVCC", shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc")
+CXX = os.environ.get("CXX", "g++")
+CUDA_HOME = Path(NVCC).resolve().parent.parent
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+    "-I", str(CSRC / "kernels"), "-I", str(ROOT / "include"),
+]
+CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread",
+             "-I", str(ROOT / "include"), "-I", str(CSRC)]
+
+
+def _newer(src: Path, deps: list[Path], obj: Path) -> bool:
+    if not obj.exists():
+        return True
+    t = obj.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in [src, *deps] if d.exists())
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError(f"native build failed: {cmd[0]} {cmd[-1]}")
+
+
+def build_kernels(verbose: bool = False) -> Path:
+    """Compile every ``csrc/kernels/*.cu`` for sm_100a and link ``_kernels.so``."""
+    out = PKG / "_kernels.so"
+    srcs = sorted((CSRC / "kernels").glob("*.cu"))
+    hdrs = sorted((CSRC / "kernels").glob("*.h")) + sorted((CSRC / "kernels").glob("*.cuh"))
+    objdir = BUILD / "kernels"
+    objdir.mkdir(parents=True, exist_ok=True)
+    jobs = []
+    for s in srcs:
+        o = objdir / (s.stem + ".o")
+        if _newer(s, hdrs, o):
+            jobs.append([NVCC, *NVCC_FLAGS, "-c", str(s), "-o", str(o)])
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            list(ex.map(_run, jobs))
+    objs = [objdir / (s.stem + ".o") for s in srcs]
+    if jobs or not out.exists():
+        _run([NVCC, "-shared", "-o", str(out), *map(str, objs), "-cudart", "shared",
+              "-Xlinker", f"-rpath={CUDA_HOME}/lib64"])
+    if verbose:
+        print(f"built {out} from {len(srcs)} CUDA sources ({len(jobs)} recompiled)")
+    return out
+
+
+def build_engine(verbose: bool = False) -> Path:
+    """Compile the host engine (scheduler, KV manager, tokenizer, C ABI ...) and its Python
+    binding into ``_engine.so`` (pybind11 module) plus ``libvllm_b200.so`` (C ABI only)."""
+    import pybind11
+
+    out = PKG / ("_engine" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+    srcs = sorted((CSRC / "engine").rglob("*.cpp"))
+    hdrs = sorted((CSRC / "engine").rglob("*.h")) + sorted((ROOT / "include").rglob("*.h"))
+    objdir = BUILD / "engine"
+    objdir.mkdir(parents=True, exist_ok=True)
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+    jobs = []
+    objs = []
+    for s in srcs:
+        o = objdir / (str(s.relative_to(CSRC / "engine")).replace("/", "__")[:-4] + ".o")
+        objs.append(o)
+        if _newer(s, hdrs, o):
+            jobs.append([CXX, *CXX_FLAGS, *inc, "-c", str(s), "-o", str(o)])
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            list(ex.map(_run, jobs))
+    if jobs or not out.exists():
+        _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
+    capi = PKG / "libvllm_b200.so"
+    capi_objs = [o for o in objs if not o.name.startswith("bindings")]
+    if capi_objs and (jobs or not capi.exists()):
+        _run([CXX, "-shared", "-o", str(capi), *map(str, capi_objs), "-pthread", "-ldl",
+              f"-Wl,--version-script={CSRC / 'engine' / 'capi' / 'export.map'}"]
+             if (CSRC / "engine" / "capi" / "export.map").exists() else
+             [CXX, "-shared", "-o", str(capi), *map(str, capi_objs), "-pthread", "-ldl"])
+    if verbose:
+        print(f"built {out} from {len(srcs)} C++ sources ({len(jobs)} recompiled)")
+    return out
+
+
+def build_all(verbose: bool = False) -> None:
+    build_kernels(verbose)
+    if (CSRC / "engine").exists():
+        build_engine(verbose)
+
+
+if __name__ == "__main__":
+    build_all(verbose=True)

@@ -1,0 +1,129 @@
+"""Loader for the in-tree sm_100a kernel library (``_kernels.so``).
+
+The library is plain C (raw pointers + stream), so the same entry points serve the Python
+wrappers here and the C++ runtime. Loading fails loudly: on a machine with a GPU a missing
+library is an error, never a silent fallback to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch  # noqa: F401  (loads libcudart before the kernel library resolves against it)
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB_PATH = _PKG / "_kernels.so"
+_lib = None
+
+
+class KernelLibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            if os.environ.get("VLLM_B200_AUTOBUILD", "1") == "1":
+                from .. import _build
+                _build.build_kernels()
+            if not _LIB_PATH.exists():
+                raise KernelLibraryMissing(
+                    f"{_LIB_PATH} not found: run `python -m vllm_cpp_b200._build`")
+        _lib = ctypes.CDLL(str(_LIB_PATH))
+        _declare(_lib)
+    return _lib
+
+
+def available() -> bool:
+    try:
+        lib()
+        return True
+    except (KernelLibraryMissing, OSError):
+        return False
+
+
+P = ctypes.c_void_p
+I = ctypes.c_int
+L = ctypes.c_int64
+F = ctypes.c_float
+Z = ctypes.c_size_t
+
+_SIGS = {
+    "b200_num_sms": ([], I),
+    "b200_read_status": ([], I),
+    "b200_status_ptr": ([], P),
+    "b200_gemm_bf16": ([P, I, P, I, P, I, I, P, P, I, I, I, I, P, Z, I, P], I),
+    "b200_rmsnorm": ([P, I, P, P, P, I, I, I, F, I, P], I),
+    "b200_layernorm": ([P, P, P, P, I, I, F, P], I),
+    "b200_act_and_mul": ([P, I, P, I, I, I, P], I),
+    "b200_eltwise": ([P, P, P, Z, I, F, P], I),
+    "b200_cast_bf16_f32": ([P, P, Z, P], I),
+    "b200_cast_f32_bf16": ([P, P, Z, P], I),
+    "b200_embedding": ([P, P, P, I, I, L, L, L, F, P], I),
+    "b200_gather_rows": ([P, P, P, I, I, I, P], I),
+    "b200_rope_kv": ([P, I, I, I, I, I, I, I, I, I, P, P, P, P, F, I, I, P, P, I, P, I, P], I),
+    "b200_reshape_and_cache": ([P, I, P, I, P, P, I, I, I, I, P], I),
+    "b200_concat_and_cache_mla": ([P, I, P, I, P, P, I, I, I, P], I),
+    "b200_rope_table": ([P, P, I, I, F, P], I),
+    "b200_attn_prefill": ([P, I, P, I, P, P, L, I, I, I, I, P, I, P, P, P, P, I, I, F, F, I, I, P], I),
+    "b200_attn_decode_splits": ([I, I, I, I, I], I),
+    "b200_attn_decode": ([P, I, P, I, P, I, I, I, I, P, I, P, I, F, F, I, I, P, P, P], I),
+    "b200_merge_attn_states": ([P, P, P, P, P, P, I, I, I, P], I),
+    "b200_argmax": ([P, I, I, I, P, P, P, P], I),
+    "b200_apply_temperature": ([P, I, I, I, P, P], I),
+    "b200_apply_penalties": ([P, I, I, P, P, P, I, P, P, P, P], I),
+    "b200_sparse_edit": ([P, I, I, P, P, P, I, I, P], I),
+    "b200_apply_bitmask": ([P, I, I, P, I, P, P], I),
+    "b200_apply_min_p": ([P, I, I, I, P, P], I),
+    "b200_apply_top_k_top_p": ([P, I, I, I, P, P, P], I),
+    "b200_softmax": ([P, I, P, I, I, I, I, P], I),
+    "b200_random_sample": ([P, I, I, I, P, P, P, P], I),
+    "b200_merge_greedy_random": ([P, P, P, P, I, P], I),
+    "b200_token_rank": ([P, I, I, I, P, P, P, P], I),
+    "b200_greedy_reject": ([P, P, P, I, I, P, P], I),
+    "b200_splice_sampled": ([P, P, P, P, I, P], I),
+    "b200_scatter_sampled": ([P, P, P, I, P], I),
+    "b200_splitmix64": ([ctypes.c_uint64], ctypes.c_uint64),
+}
+
+
+def _declare(l: ctypes.CDLL) -> None:
+    for name, (args, res) in _SIGS.items():
+        try:
+            fn = getattr(l, name)
+        except AttributeError:
+            continue
+        fn.argtypes = args
+        fn.restype = res
+
+
+def declare(name: str, args, res=I) -> None:
+    """Register the signature of an entry point added by a later kernel file."""
+    _SIGS[name] = (args, res)
+    if _lib is not None and hasattr(_lib, name):
+        fn = getattr(_lib, name)
+        fn.argtypes = args
+        fn.restype = res
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_CODES = {-1: "rejected shape/alignment", -2: "launch failure", -3: "tensor-map encode failure",
+          -4: "size beyond the stated maximum"}
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what}: {_CODES.get(rc, 'error')} (code {rc})")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()

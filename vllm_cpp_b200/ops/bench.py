@@ -1,0 +1,113 @@
+"""Kernel micro-benchmarks: ``python -m vllm_cpp_b200.ops.bench [--json out.json]``.
+
+Each case is timed with CUDA events on the launching stream after warm-up, with an L2 flush
+(a write larger than L2) between timed iterations, and reported as achieved TFLOP/s or GB/s
+next to the same shape run through ``torch.matmul`` (cuBLAS) where that is meaningful.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import reference as ref
+from .. import ops
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+
+    def gemm_case(M, N, K, tag):
+        a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        t_ours = _time(lambda: ops.gemm(a, w, out=out), flush=flush)
+        t_lib = _time(lambda: torch.matmul(a, w.t(), out=out), flush=flush)
+        fl = 2.0 * M * N * K
+        by = 2.0 * (M * K + N * K + M * N)
+        rows.append(dict(kind="gemm_bf16", tag=tag, M=M, N=N, K=K, ms=t_ours, cublas_ms=t_lib,
+                         tflops=fl / t_ours / 1e9, cublas_tflops=fl / t_lib / 1e9,
+                         gbs=by / t_ours / 1e6, cublas_gbs=by / t_lib / 1e6))
+        print(f"gemm {tag:>10} M={M:5d} N={N:6d} K={K:5d}: ours {t_ours:8.4f} ms "
+              f"({fl / t_ours / 1e9:7.1f} TF, {by / t_ours / 1e6:6.0f} GB/s) | cuBLAS {t_lib:8.4f} ms "
+              f"({fl / t_lib / 1e9:7.1f} TF)", flush=True)
+
+    # Llama-3.1-8B projections: prefill (M=8192) and decode (M=1..256)
+    shapes = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096),
+              ("down", 4096, 14336)]
+    for tag, N, K in shapes:
+        for M in ([8192, 64] if args.quick else [8192, 2048, 256, 64, 8, 1]):
+            gemm_case(M, N, K, tag)
+    if not args.quick:
+        gemm_case(256, 128256, 4096, "lm_head")
+        gemm_case(8192, 8192, 8192, "square")
+
+    # attention
+    Hq, Hkv, D, bs = 32, 8, 128, 16
+    for B, ctx in ([(64, 1024)] if args.quick else [(256, 1152), (64, 1024), (8, 4096), (1, 8192)]):
+        nb = (ctx + bs - 1) // bs
+        cache = torch.randn(B * nb + 1, 2, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        q = torch.randn(B, Hq * D, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        t = _time(lambda: ops.attn_decode(q, cache, block_table=bt, seq_lens=sl, num_q_heads=Hq,
+                                          num_kv_heads=Hkv, head_dim=D, block_size=bs,
+                                          scale=D ** -0.5, out=out), flush=flush)
+        by = 2.0 * B * ctx * 2 * Hkv * D
+        rows.append(dict(kind="attn_decode", B=B, ctx=ctx, ms=t, gbs=by / t / 1e6))
+        print(f"attn_decode B={B:4d} ctx={ctx:5d}: {t:8.4f} ms ({by / t / 1e6:6.0f} GB/s)", flush=True)
+        del cache
+    for B, ql in ([(4, 1024)] if args.quick else [(8, 1024), (2, 4096), (1, 8192)]):
+        nb = (ql + bs - 1) // bs
+        cache = torch.randn(B * nb + 1, 2, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ql, dtype=torch.int32, device=dev)
+        qs = torch.arange(B + 1, device=dev, dtype=torch.int32) * ql
+        treq, tq0 = ref.build_prefill_tiles([ql] * B)
+        treq = torch.tensor(treq, dtype=torch.int32, device=dev)
+        tq0 = torch.tensor(tq0, dtype=torch.int32, device=dev)
+        q = torch.randn(B * ql, Hq * D, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        t = _time(lambda: ops.attn_prefill(q, cache, block_table=bt, seq_lens=sl, q_start=qs,
+                                           tile_req=treq, tile_q0=tq0, num_q_heads=Hq,
+                                           num_kv_heads=Hkv, head_dim=D, block_size=bs,
+                                           scale=D ** -0.5, out=out), flush=flush)
+        fl = 4.0 * B * Hq * D * ql * ql / 2
+        rows.append(dict(kind="attn_prefill", B=B, q_len=ql, ms=t, tflops=fl / t / 1e9))
+        print(f"attn_prefill B={B} q_len={ql}: {t:8.4f} ms ({fl / t / 1e9:7.1f} TF causal)", flush=True)
+        del cache
+    st = ops.read_status()
+    print("status word:", st)
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump(dict(rows=rows, status=st), f, indent=1)
+
+
+if __name__ == "__main__":
+    main()
