@@ -184,7 +184,8 @@ def top_k_top_p(logits, top_k, top_p):
             sp, si = torch.sort(probs, descending=True)
             cs = torch.cumsum(sp, dim=-1)
             # first index where cumulative mass >= p
-            cut = int(torch.searchsorted(cs, torch.tensor(p * float(cs[-1]), dtype=cs.dtype)))
+            cut = int(torch.searchsorted(cs, torch.tensor(p * float(cs[-1]), dtype=cs.dtype,
+                                                          device=cs.device)))
             cut = min(cut, V - 1)
             thr = row[si[cut]]
             row[row < thr] = -math.inf
