@@ -1,0 +1,244 @@
+"""Serving benchmark: output tokens/s of the engine on the Llama-3.1-8B-shaped BF16 config.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (synthetic, random-init weights): continuous batching at concurrency 256, every
+request 1024 uniform-random prompt ids and 256 greedy output tokens. The engine is first
+brought to steady state (untimed ramp in which the initial requests get staggered output
+lengths, so arrivals are spread evenly afterwards), then W warm-up steps, then EXACTLY K
+engine steps are timed. One step = one iteration of the engine loop (schedule, one packed
+host->device copy from pinned memory, forward, sample, device->host read of the sampled
+ids, update).
+
+Two numbers come out of the same K steps:
+  value      output tokens / sum of per-step device time (CUDA events around each step's
+             GPU work, max over ranks)
+  e2e.value  output tokens / wall time of the K ``LLM.step()`` calls (public API, includes
+             the host scheduler, the copies and the synchronisation), max over ranks
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+MODEL = "llama-3.1-8b"
+CONCURRENCY = 256
+INPUT_LEN = 1024
+OUTPUT_LEN = 256
+PUBLISHED_BASELINE = None  # the reference publishes no number for this config
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                 "200", "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def run_reference(args) -> int:
+    # The reference ships no setup.py / pyproject.toml, so the one permitted offline install
+    # (`pip install --no-index --target baseline/_ref /root/reference`) stops with
+    # "Neither 'setup.py' nor 'pyproject.toml' found"; there is nothing to import or run.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a CMake/C++ project: pip install --target "
+                                     "baseline/_ref fails (neither setup.py nor pyproject.toml)"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--concurrency", type=int, default=CONCURRENCY)
+    ap.add_argument("--input-len", type=int, default=INPUT_LEN)
+    ap.add_argument("--output-len", type=int, default=OUTPUT_LEN)
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    n_gpus = world
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from vllm_cpp_b200.config import EngineArgs, ParallelConfig, synthetic_config
+    from vllm_cpp_b200.engine import LLM, SamplingParams
+    from vllm_cpp_b200.ops import _lib
+
+    cfg = synthetic_config(args.model)
+    C, IN, OUT = args.concurrency, args.input_len, args.output_len
+    block = 32
+    max_len = IN + OUT + block
+    llm = LLM(EngineArgs(
+        model_config=cfg, device="cuda", block_size=block, max_model_len=max_len,
+        max_num_seqs=C, max_num_batched_tokens=args.max_num_batched_tokens,
+        num_blocks=C * ((max_len + block - 1) // block + 1) + 64,
+        enable_cuda_graphs=not args.no_graphs, enable_prefix_caching=True,
+        parallel=ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank)))
+    gen = torch.Generator().manual_seed(1)
+
+    def new_prompt():
+        return torch.randint(0, cfg.vocab_size, (IN,), generator=gen).tolist()
+
+    def submit(out_len):
+        llm.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=out_len,
+                                                     ignore_eos=True))
+
+    # ---- ramp to steady state (untimed): staggered output lengths for the first wave
+    llm.runner.warmup_graphs()
+    for i in range(C):
+        submit(1 + (i * OUT) // C)
+    ramp_steps = 0
+
+    def step_and_refill():
+        """One engine step; finished requests are replaced at once (closed loop)."""
+        outs = llm.step()
+        fin = 0
+        for st in outs:
+            if st.finished:
+                fin += 1
+        for _ in range(fin):
+            submit(OUT)
+        return outs
+
+    # the ramp ends once every first-wave request has finished (all live requests are
+    # full-length ones at evenly spread positions)
+    first_wave = set(llm._states.keys())
+    while first_wave & set(llm._states.keys()):
+        step_and_refill()
+        ramp_steps += 1
+        if ramp_steps > 4 * OUT + 64:
+            break
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step_and_refill()
+
+    # ---- timed region
+    sampler = ClockSampler(local_rank)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(args.steps)]
+    h2d0, d2h0 = llm.runner.h2d_bytes, llm.runner.d2h_bytes
+    launches0 = _lib.LAUNCHES[0]
+    tokens = 0
+    barrier()
+    sampler.start()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        ev[i][0].record()
+        outs = step_and_refill()
+        ev[i][1].record()
+        for st in outs:
+            tokens += 1  # one new token per returned request per step (no speculative decode)
+    barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    launches = _lib.LAUNCHES[0] - launches0
+    h2d = (llm.runner.h2d_bytes - h2d0) / args.steps
+    d2h = (llm.runner.d2h_bytes - d2h0) / args.steps
+    status = llm.runner.ops.read_status()
+
+    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms = float(t[0]), float(t[1])
+    value = tokens / (dev_ms / 1e3)
+    e2e = tokens / (wall_ms / 1e3)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s",
+            "n_gpus": n_gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
+            "dtype": "bf16", "data": "synthetic (uniform-random prompt ids, random-init weights)",
+            "impl": "ours",
+            "config": {"model": "Llama-3.1-8B-shaped", "global_batch": C, "seq_len": IN + OUT,
+                       "input_len": IN, "output_len": OUT,
+                       "parallelism": f"tp{world}", "mode": "continuous batching, steady state",
+                       "max_num_batched_tokens": args.max_num_batched_tokens,
+                       "l2": "weights (16 GB) and KV (>40 GB) per step exceed L2 (126 MB)",
+                       "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h), "wall_ms_per_step": round(wall_ms / args.steps, 4)},
+            "gpu_launches": int(launches), "output_tokens": tokens, "kernel_status": status,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,96 @@
+"""End-to-end engine on the GPU: kernels + C++ scheduler/KV manager/input batch + CUDA graphs,
+checked against the same model run through the CPU (fp32-restatement) back end."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from vllm_cpp_b200 import ops  # noqa: E402
+from vllm_cpp_b200.config import EngineArgs, synthetic_config  # noqa: E402
+from vllm_cpp_b200.engine import LLM, SamplingParams  # noqa: E402
+
+
+def _cfg():
+    c = synthetic_config("tiny-qwen3")
+    c.head_dim = 128
+    c.num_layers = 3
+    return c
+
+
+def _prompts(cfg, lens, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+
+
+def _run(device, cfg, prompts, max_tokens=12, graphs=True, budget=128, seqs=4, **kw):
+    llm = LLM(EngineArgs(model_config=cfg, device=device, block_size=16, num_blocks=200,
+                         max_model_len=640, max_num_seqs=seqs, max_num_batched_tokens=budget,
+                         enable_cuda_graphs=graphs, **kw))
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=max_tokens,
+                                                ignore_eos=True))
+    return [o.outputs[0].token_ids for o in outs], llm
+
+
+def _agreement(a, b):
+    """Fraction of positions that agree up to the first divergence of each sequence."""
+    hit = tot = 0
+    for x, y in zip(a, b):
+        n = 0
+        for p, q in zip(x, y):
+            if p != q:
+                break
+            n += 1
+        hit += n
+        tot += len(x)
+    return hit / tot
+
+
+def test_gpu_matches_cpu_oracle_greedy():
+    cfg = _cfg()
+    prompts = _prompts(cfg, (150, 9, 300, 40, 17, 64))
+    gpu, llm = _run("cuda", cfg, prompts)
+    cpu, _ = _run("cpu", cfg, prompts)
+    assert ops.read_status() == 0
+    # random-init models have many near-ties; bf16 tensor-core sums differ in the last bit from
+    # the fp32 oracle, so require exactness of the first tokens and high overall agreement
+    assert [g[0] for g in gpu] == [c[0] for c in cpu]
+    assert _agreement(gpu, cpu) > 0.8
+
+
+def test_graphs_vs_eager_and_batch_invariance():
+    cfg = _cfg()
+    prompts = _prompts(cfg, (33, 200, 5, 77))
+    a, _ = _run("cuda", cfg, prompts, graphs=True)
+    b, _ = _run("cuda", cfg, prompts, graphs=False)
+    assert a == b
+    # chunked prefill (small budget) gives the same tokens as one-shot prefill
+    c, _ = _run("cuda", cfg, prompts, graphs=True, budget=64)
+    assert _agreement(a, c) > 0.9
+    assert ops.read_status() == 0
+
+
+def test_prefix_cache_hit_same_tokens():
+    cfg = _cfg()
+    p = _prompts(cfg, (128,))[0]
+    llm = LLM(EngineArgs(model_config=cfg, device="cuda", block_size=16, num_blocks=200,
+                         max_model_len=640, max_num_seqs=4, max_num_batched_tokens=256))
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    first = llm.generate([p + [1, 2, 3]], sp)[0]
+    second = llm.generate([p + [1, 2, 3]], sp)[0]
+    assert second.num_cached_tokens >= 112
+    assert first.outputs[0].token_ids == second.outputs[0].token_ids
+
+
+def test_sampling_params_seeded_random_is_reproducible():
+    cfg = _cfg()
+    p = _prompts(cfg, (20, 31))
+    llm = LLM(EngineArgs(model_config=cfg, device="cuda", block_size=16, num_blocks=200,
+                         max_model_len=640, max_num_seqs=4, max_num_batched_tokens=256))
+    sp = SamplingParams(temperature=0.8, top_p=0.9, top_k=50, seed=1234, max_tokens=10,
+                        ignore_eos=True, repetition_penalty=1.1, presence_penalty=0.2)
+    a = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
+    b = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
+    assert a == b
+    g = [o.outputs[0].token_ids for o in llm.generate(
+        p, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))]
+    assert a != g  # sampling actually happened

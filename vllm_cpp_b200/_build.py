@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "-I", str(CSRC / "kernels"), "-I", str(ROOT / "include"),
 ]
 CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread",
-             "-I", str(ROOT / "include"), "-I", str(CSRC)]
+             "-I", str(ROOT / "include"), "-I", str(CSRC), "-I", str(CSRC / "engine")]
 
 
 def _newer(src: Path, deps: list[Path], obj: Path) -> bool:

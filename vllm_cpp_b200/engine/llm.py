@@ -1,0 +1,196 @@
+"""The public Python API: ``LLM`` (offline, synchronous step loop) on top of the C++ engine
+core, a model from the registry and a ``ModelRunner``.
+
+Assembly order follows the reference's ``LoadedEngine`` (``src/vllm/entrypoints/
+model_loader.cpp:273-366``): config -> model/weights -> KV sizing -> runner -> scheduler
+config (token budget per family, prefix caching unless hybrid, async when the runner
+supports it) -> engine core. ``LLMEngine``-style calls: ``add_request / step / generate /
+abort_request`` (``src/vllm/v1/engine/llm_engine.cpp:22-83``).
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Iterable, Optional, Sequence
+
+import torch
+
+from .. import _engine as E
+from ..config import EngineArgs, ModelConfig, ParallelConfig, load_model_config
+from ..models import registry
+from ..worker.runner import ModelRunner
+
+SamplingParams = E.SamplingParams
+
+
+@dataclass
+class CompletionOutput:
+    index: int = 0
+    text: str = ""
+    token_ids: list = field(default_factory=list)
+    logprobs: Optional[list] = None
+    finish_reason: Optional[str] = None
+    stop_reason: Optional[object] = None
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    prompt_token_ids: list
+    outputs: list
+    finished: bool = False
+    num_cached_tokens: int = 0
+    prompt: Optional[str] = None
+    metrics: dict = field(default_factory=dict)
+
+
+class LLM:
+    def __init__(self, args: EngineArgs | None = None, **kw):
+        if args is None:
+            args = EngineArgs(**kw)
+        self.args = args
+        cfg = args.model_config
+        self.tokenizer = None
+        tensors = None
+        if cfg is None:
+            if args.model is None:
+                raise ValueError("either model or model_config is required")
+            from ..loader import load_model_dir
+            cfg, tensors, self.tokenizer = load_model_dir(args.model, args.tokenizer)
+        self.cfg = cfg
+        par = args.parallel
+        self.comm = self._make_comm(par)
+        device = torch.device(args.device)
+        if device.type == "cuda":
+            torch.cuda.set_device(par.local_rank)
+            device = torch.device("cuda", par.local_rank)
+        self.device = device
+        max_len = args.max_model_len or cfg.max_position_embeddings
+        self.max_model_len = max_len
+        _, cls = registry.resolve(cfg.architecture)
+        self.model = cls(cfg, device=device, parallel=par, comm=self.comm, max_position=max_len)
+        if tensors is not None:
+            self.model.load_weights(tensors)
+        else:
+            self.model.init_random(args.seed)
+        budget = args.resolve_max_num_batched_tokens(cfg)
+        num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
+        use_async = args.async_scheduling if args.async_scheduling is not None else False
+        self.runner = ModelRunner(self.model, block_size=args.block_size, num_blocks=num_blocks,
+                                  max_num_seqs=args.max_num_seqs, max_num_batched_tokens=budget,
+                                  max_model_len=max_len, enable_cuda_graphs=args.enable_cuda_graphs,
+                                  async_mode=use_async)
+        sc = E.SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=args.max_num_seqs,
+                               max_model_len=max_len, policy=args.scheduling_policy,
+                               async_scheduling=use_async,
+                               enable_prefix_caching=args.resolve_prefix_caching(cfg))
+        self.scheduler_config = sc
+        self.core = E.EngineCore(sc, self.runner.kv_cache_config(), self.runner,
+                                 2 if use_async else 1)
+        self.use_async = use_async
+        self._counter = itertools.count()
+        self._states: dict[str, RequestOutput] = {}
+        self.eos_token_id = cfg.eos_token_id
+        self.step_times: list = []
+
+    # ------------------------------------------------------------------ set-up helpers
+    @staticmethod
+    def _make_comm(par: ParallelConfig):
+        from ..parallel.comm import SingleComm, TorchComm
+        if par.tensor_parallel_size <= 1:
+            return SingleComm()
+        return TorchComm()
+
+    def _size_kv_cache(self, args: EngineArgs, budget: int, max_len: int) -> int:
+        per_block = self.model.kv_bytes_per_block(args.block_size)
+        if self.device.type != "cuda":
+            want = args.max_num_seqs * ((max_len + args.block_size - 1) // args.block_size) + 1
+            return max(16, min(want, 4096))
+        torch.cuda.synchronize()
+        free, total = torch.cuda.mem_get_info(self.device)
+        # leave room for activations of a full-budget step
+        c = self.cfg
+        act = budget * (4 * c.hidden_size + 3 * max(c.intermediate_size, 1)) * 2 * 2
+        usable = free - (1.0 - args.gpu_memory_utilization) * total - act - (2 << 30)
+        n = int(usable // per_block)
+        cap = args.max_num_seqs * ((max_len + args.block_size - 1) // args.block_size) + 16
+        return max(16, min(n, cap))
+
+    # ------------------------------------------------------------------ LLMEngine surface
+    def add_request(self, prompt_token_ids: Sequence[int], params: "E.SamplingParams",
+                    request_id: Optional[str] = None, priority: int = 0,
+                    prompt: Optional[str] = None) -> str:
+        rid = request_id or f"req-{next(self._counter)}"
+        toks = list(prompt_token_ids)
+        if len(toks) >= self.max_model_len:
+            raise ValueError(f"prompt ({len(toks)} tokens) is longer than max_model_len "
+                             f"({self.max_model_len})")
+        req = E.EngineCoreRequest(rid, toks, params, self.eos_token_id, time.monotonic(), priority)
+        self.runner.set_eos(rid, self.eos_token_id)
+        self.core.add_request(req)
+        self._states[rid] = RequestOutput(rid, toks, [CompletionOutput()], prompt=prompt)
+        return rid
+
+    def abort_request(self, request_id: str) -> None:
+        self.core.abort_requests([request_id])
+        self._states.pop(request_id, None)
+
+    def has_unfinished_requests(self) -> bool:
+        return self.core.has_work()
+
+    def step(self) -> list[RequestOutput]:
+        """One engine step; returns the requests that produced tokens (finished ones are
+        flagged and dropped from the live table)."""
+        outs, _ = self.core.step_with_batch_queue() if self.use_async else self.core.step()
+        done = []
+        for o in outs.outputs:
+            st = self._states.get(o.request_id)
+            if st is None:
+                continue
+            c = st.outputs[0]
+            c.token_ids.extend(o.new_token_ids)
+            st.num_cached_tokens = o.num_cached_tokens
+            if o.new_logprobs:
+                c.logprobs = (c.logprobs or []) + list(o.new_logprobs)
+            if o.finished():
+                c.finish_reason = E.finish_reason_str(o.finish_reason)
+                if o.stop_reason is not None:
+                    c.stop_reason = o.stop_reason.token if o.stop_reason.is_token else o.stop_reason.text
+                st.finished = True
+                self._states.pop(o.request_id, None)
+            done.append(st)
+        return done
+
+    def generate(self, prompts: Iterable, sampling_params=None, use_tqdm: bool = False):
+        """Runs a batch to completion. ``prompts``: token-id lists, strings (needs a tokenizer)
+        or dicts with ``prompt_token_ids``. Returns RequestOutputs in input order."""
+        prompts = list(prompts)
+        if sampling_params is None:
+            sampling_params = E.SamplingParams()
+        if not isinstance(sampling_params, (list, tuple)):
+            sampling_params = [sampling_params] * len(prompts)
+        order = []
+        for p, sp in zip(prompts, sampling_params):
+            text = None
+            if isinstance(p, str):
+                if self.tokenizer is None:
+                    raise ValueError("string prompts need a tokenizer")
+                text, p = p, self.tokenizer.encode(p)
+            elif isinstance(p, dict):
+                p = p["prompt_token_ids"]
+            order.append(self.add_request(p, sp, prompt=text))
+        results: dict[str, RequestOutput] = {}
+        while self.has_unfinished_requests():
+            for st in self.step():
+                if st.finished:
+                    results[st.request_id] = st
+        outs = [results[r] for r in order if r in results]
+        if self.tokenizer is not None:
+            for o in outs:
+                for c in o.outputs:
+                    c.text = self.tokenizer.decode(c.token_ids)
+        return outs
+
+    def stats(self):
+        return self.core.scheduler().make_stats()

@@ -1,0 +1,174 @@
+"""Op back ends the model code is written against.
+
+``GpuBackend`` launches the sm_100a kernels (no eager fallback). ``CpuBackend`` evaluates the
+same ops with the fp32 PyTorch restatements; it is the oracle the GPU path is compared with
+(token-exact greedy gates) and the execution path of the CPU benchmark configuration.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import reference as ref
+
+
+class CpuBackend:
+    name = "cpu"
+
+    def __init__(self, device="cpu"):
+        self.device = torch.device(device)
+
+    def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        y = ref.gemm(a, w, bias, residual, out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def rmsnorm(self, x, w, eps, residual=None, out=None, gemma=False):
+        y, newr = ref.rmsnorm(x, w, eps, residual, gemma)
+        if residual is not None:
+            residual.copy_(newr)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def layernorm(self, x, w, b, eps):
+        return ref.layernorm(x, w, b, eps)
+
+    def act_and_mul(self, x, kind=0, out=None):
+        return ref.act_and_mul(x, kind)
+
+    def embedding(self, ids, table, out=None, vocab_start=0, vocab_total=None, scale=1.0):
+        local = ids - vocab_start
+        ok = (local >= 0) & (local < table.shape[0])
+        y = table[local.clamp(0, table.shape[0] - 1)]
+        y = torch.where(ok[:, None], y, torch.zeros_like(y))
+        if scale != 1.0:
+            y = (y.float() * scale).to(table.dtype)
+        return y
+
+    def gather_rows(self, x, idx, out=None):
+        return x[idx.long()]
+
+    def rope_table(self, inv_freq, max_pos, mscale=1.0):
+        return ref.rope_table(inv_freq.to(self.device), max_pos, mscale)
+
+    def rope_kv(self, qkv, positions, table, *, num_q_heads, num_kv_heads, head_dim, rot_dim,
+                neox, q_norm, k_norm, eps, gemma, slot_mapping, kv_cache, block_size,
+                q_head_stride=None, offsets=None):
+        q, k, v = ref.rope_kv(qkv, positions, table, num_q_heads, num_kv_heads, head_dim, rot_dim,
+                              neox, q_norm, k_norm, eps, gemma)
+        T = qkv.shape[0]
+        qkv[:, : num_q_heads * head_dim] = q.reshape(T, -1)
+        if kv_cache is not None:
+            ref.write_kv_cache(kv_cache, k, v, slot_mapping, block_size)
+
+    def attention(self, q, kv_cache, ctx, group, *, num_q_heads, num_kv_heads, head_dim,
+                  block_size, scale, out=None, softcap=0.0, window=0):
+        y = ref.paged_attention(q, kv_cache, ctx.block_table[group], ctx.seq_lens,
+                                ctx.query_start, num_q_heads, num_kv_heads, head_dim, block_size,
+                                scale, softcap, window)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def add(self, a, b):
+        return (a.float() + b.float()).to(a.dtype)
+
+    def mul_scalar(self, a, s):
+        return (a.float() * s).to(a.dtype)
+
+    def softcap(self, a, cap):
+        return (cap * torch.tanh(a.float() / cap)).to(a.dtype)
+
+    def sigmoid_mul(self, a, g):
+        return (a.float() * torch.sigmoid(g.float())).to(a.dtype)
+
+    def argmax(self, logits):
+        return logits.argmax(-1)
+
+
+class GpuBackend:
+    name = "cuda"
+
+    def __init__(self, device="cuda"):
+        from .. import ops
+        self.ops = ops
+        self.device = torch.device(device)
+        ops.lib()  # fail loudly here if the kernel library is missing
+
+    def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        return self.ops.gemm(a, w, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
+
+    def rmsnorm(self, x, w, eps, residual=None, out=None, gemma=False):
+        return self.ops.rmsnorm(x, w, eps, residual=residual, out=out, gemma=gemma)
+
+    def layernorm(self, x, w, b, eps):
+        return self.ops.layernorm(x, w, b, eps)
+
+    def act_and_mul(self, x, kind=0, out=None):
+        return self.ops.act_and_mul(x, kind, out)
+
+    def embedding(self, ids, table, out=None, vocab_start=0, vocab_total=None, scale=1.0):
+        return self.ops.embedding(ids, table, out=out, vocab_start=vocab_start,
+                                  vocab_total=vocab_total, scale=scale)
+
+    def gather_rows(self, x, idx, out=None):
+        return self.ops.gather_rows(x, idx, out)
+
+    def rope_table(self, inv_freq, max_pos, mscale=1.0):
+        return self.ops.rope_table(inv_freq.to(self.device), max_pos, mscale)
+
+    def rope_kv(self, qkv, positions, table, *, num_q_heads, num_kv_heads, head_dim, rot_dim,
+                neox, q_norm, k_norm, eps, gemma, slot_mapping, kv_cache, block_size,
+                q_head_stride=None, offsets=None):
+        self.ops.rope_kv(qkv, positions, table, num_q_heads=num_q_heads,
+                         num_kv_heads=num_kv_heads, head_dim=head_dim, rot_dim=rot_dim, neox=neox,
+                         q_norm=q_norm, k_norm=k_norm, eps=eps, gemma=gemma,
+                         slot_mapping=slot_mapping, kv_cache=kv_cache, block_size=block_size,
+                         q_head_stride=q_head_stride, offsets=offsets)
+
+    def attention(self, q, kv_cache, ctx, group, *, num_q_heads, num_kv_heads, head_dim,
+                  block_size, scale, out=None, softcap=0.0, window=0):
+        """Decode rows first (one token per request), then the prefill rows."""
+        T = q.shape[0]
+        if out is None:
+            out = torch.empty((T, num_q_heads * head_dim), dtype=q.dtype, device=q.device)
+        nd = ctx.num_decodes
+        bt = ctx.block_table[group]
+        if nd > 0:
+            self.ops.attn_decode(q[:nd], kv_cache, block_table=bt[:nd], seq_lens=ctx.seq_lens[:nd],
+                                 num_q_heads=num_q_heads, num_kv_heads=num_kv_heads,
+                                 head_dim=head_dim, block_size=block_size, scale=scale,
+                                 out=out[:nd], splits=ctx.decode_splits, softcap=softcap,
+                                 window=window, tmp=ctx.extra.get("decode_tmp"))
+        if ctx.num_prefills > 0:
+            self.ops.attn_prefill(q[nd:], kv_cache, block_table=bt[nd:], seq_lens=ctx.seq_lens[nd:],
+                                  q_start=ctx.prefill_q_start, tile_req=ctx.tile_req[:ctx.num_tiles],
+                                  tile_q0=ctx.tile_q0[:ctx.num_tiles], num_q_heads=num_q_heads,
+                                  num_kv_heads=num_kv_heads, head_dim=head_dim,
+                                  block_size=block_size, scale=scale, out=out[nd:],
+                                  softcap=softcap, window=window)
+        return out
+
+    def add(self, a, b):
+        return self.ops.add(a, b)
+
+    def mul_scalar(self, a, s):
+        return self.ops.mul_scalar(a, s)
+
+    def softcap(self, a, cap):
+        return self.ops.softcap(a, cap)
+
+    def sigmoid_mul(self, a, g):
+        return self.ops.sigmoid_mul(a, g)
+
+    def argmax(self, logits):
+        return self.ops.argmax(logits)
+
+
+def make_backend(device) -> "CpuBackend | GpuBackend":
+    device = torch.device(device)
+    return GpuBackend(device) if device.type == "cuda" else CpuBackend(device)

@@ -1,0 +1,341 @@
+"""Dense decoder family: Llama / Mistral / Qwen3 / Gemma(2,3) / GLM-4 / OLMo-2,3 / Phi-3 /
+Granite, all expressed as one block with switches (per-head qk-norm, biases, sandwich or
+post norms, GeGLU, soft-caps, scalar multipliers, sliding-window layers, tied embeddings).
+
+Per layer:  (add+)RMSNorm -> merged QKV GEMM -> fused qk-norm + RoPE + KV write -> paged
+attention -> o_proj GEMM [TP: reduce] -> add+RMSNorm -> merged gate_up GEMM -> act*mul ->
+down GEMM [TP: reduce]. Only the rows that sample a token go through the lm_head.
+
+Reference forward: ``src/vllm/model_executor/models/qwen3.cpp:135-244``,
+``include/vllm/model_executor/models/dense_attn_block.h:311-512``; the other families are
+``gemma*.cpp``, ``glm4.cpp``, ``olmo2.cpp``, ``phi3.cpp``, ``granite.cpp``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig, ParallelConfig
+from .backend import make_backend
+from .base import BufferPool, StepContext, normal_, shard_cols, shard_rows
+from .rope import rope_parameters, softmax_scale
+
+ACT_KIND = {"silu": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "gelu": 2}
+
+
+class DenseModel:
+    def __init__(self, cfg: ModelConfig, device="cuda", parallel: ParallelConfig | None = None,
+                 comm=None, max_position: int | None = None):
+        from ..parallel.comm import SingleComm
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.par = parallel or ParallelConfig()
+        self.comm = comm or SingleComm()
+        self.tp = self.par.tensor_parallel_size
+        self.rank = self.par.rank
+        self.be = make_backend(self.device)
+        self.dtype = torch.bfloat16
+        c = cfg
+        assert c.num_heads % self.tp == 0
+        self.hq = c.num_heads // self.tp
+        # kv heads are replicated when there are more ranks than kv heads
+        self.hkv = max(1, c.num_kv_heads // self.tp)
+        self.kv_rep = max(1, self.tp // c.num_kv_heads)
+        self.D = c.head_dim
+        self.inter = c.intermediate_size // self.tp
+        self.vocab_shard = (c.vocab_size + self.tp - 1) // self.tp
+        self.vocab_start = self.rank * self.vocab_shard
+        self.max_position = max_position or c.max_position_embeddings
+        inv, msc, tlen = rope_parameters(c.rope, c.head_dim, self.max_position)
+        self.rot = c.rope.rotary_dim or c.head_dim
+        self.rope_table = self.be.rope_table(inv, min(tlen, self.max_position), msc)
+        self.scale = c.attention_multiplier if c.attention_multiplier is not None else \
+            softmax_scale(c.rope, c.head_dim)
+        self.bufs = BufferPool(self.device)
+        self.w: dict[str, torch.Tensor] = {}
+        self.layers: list[dict[str, torch.Tensor]] = []
+
+    # ------------------------------------------------------------------ weights
+    def init_random(self, seed: int = 0, std: float = 0.02) -> None:
+        """Random N(0, std) weights of the configured shape; every rank draws the full tensor
+        from the same generator and keeps its shard, so any TP degree sees the same model."""
+        c = self.cfg
+        H, D = c.hidden_size, c.head_dim
+        # Small models draw on the CPU generator (bit-identical on any device, used by the
+        # CPU-vs-GPU gates); big ones draw on the device to keep start-up short.
+        n_params = c.num_layers * (2 * c.num_heads * D * H + 3 * c.intermediate_size * H)
+        gdev = self.device if (self.device.type == "cuda" and n_params > 5e8) else torch.device("cpu")
+        g = torch.Generator(device=gdev).manual_seed(seed)
+
+        def full(shape):
+            w = torch.empty(shape, dtype=torch.float32, device=gdev)
+            w.normal_(0.0, std, generator=g)
+            return w.to(self.dtype)
+
+        emb = full((c.vocab_size, H))
+        tensors = {"model.embed_tokens.weight": emb}
+        for l in range(c.num_layers):
+            p = f"model.layers.{l}."
+            tensors[p + "self_attn.q_proj.weight"] = full((c.num_heads * D, H))
+            tensors[p + "self_attn.k_proj.weight"] = full((c.num_kv_heads * D, H))
+            tensors[p + "self_attn.v_proj.weight"] = full((c.num_kv_heads * D, H))
+            tensors[p + "self_attn.o_proj.weight"] = full((H, c.num_heads * D))
+            tensors[p + "mlp.gate_proj.weight"] = full((c.intermediate_size, H))
+            tensors[p + "mlp.up_proj.weight"] = full((c.intermediate_size, H))
+            tensors[p + "mlp.down_proj.weight"] = full((H, c.intermediate_size))
+            ones = torch.ones(H, dtype=self.dtype) if not c.gemma_norm else torch.zeros(H, dtype=self.dtype)
+            tensors[p + "input_layernorm.weight"] = ones.clone()
+            tensors[p + "post_attention_layernorm.weight"] = ones.clone()
+            if c.sandwich_norm:
+                tensors[p + "pre_feedforward_layernorm.weight"] = ones.clone()
+                tensors[p + "post_feedforward_layernorm.weight"] = ones.clone()
+            if c.qk_norm:
+                hd1 = torch.ones(D, dtype=self.dtype) if not c.gemma_norm else torch.zeros(D, dtype=self.dtype)
+                tensors[p + "self_attn.q_norm.weight"] = hd1.clone()
+                tensors[p + "self_attn.k_norm.weight"] = hd1.clone()
+            if c.attention_bias:
+                tensors[p + "self_attn.q_proj.bias"] = full((c.num_heads * D,))
+                tensors[p + "self_attn.k_proj.bias"] = full((c.num_kv_heads * D,))
+                tensors[p + "self_attn.v_proj.bias"] = full((c.num_kv_heads * D,))
+        tensors["model.norm.weight"] = (torch.ones(H, dtype=self.dtype) if not c.gemma_norm
+                                        else torch.zeros(H, dtype=self.dtype))
+        if not c.tie_word_embeddings:
+            tensors["lm_head.weight"] = full((c.vocab_size, H))
+        self.load_weights(tensors.items())
+
+    def load_weights(self, named_tensors) -> None:
+        """Accepts HF-named full (unsharded) tensors; merges q|k|v and gate|up and keeps this
+        rank's shard. Pre-fused ``qkv_proj`` / ``gate_up_proj`` (Phi-3) are split first."""
+        c, D = self.cfg, self.cfg.head_dim
+        tp, r = self.tp, self.rank
+        staged: dict[str, torch.Tensor] = {}
+        for name, t in named_tensors:
+            if name.endswith("qkv_proj.weight"):
+                base = name[: -len("qkv_proj.weight")]
+                nq, nk = c.num_heads * D, c.num_kv_heads * D
+                staged[base + "q_proj.weight"] = t[:nq]
+                staged[base + "k_proj.weight"] = t[nq:nq + nk]
+                staged[base + "v_proj.weight"] = t[nq + nk:]
+            elif name.endswith("gate_up_proj.weight"):
+                base = name[: -len("gate_up_proj.weight")]
+                staged[base + "gate_proj.weight"] = t[: c.intermediate_size]
+                staged[base + "up_proj.weight"] = t[c.intermediate_size:]
+            else:
+                staged[name] = t
+        dev, dt = self.device, self.dtype
+
+        def put(t):
+            return t.to(dt).contiguous().to(dev)
+
+        def kv_shard(w):  # rows = kv heads * D
+            if self.kv_rep > 1:
+                h = r // self.kv_rep
+                return w[h * D:(h + 1) * D]
+            return shard_rows(w, r, tp)
+
+        emb = staged["model.embed_tokens.weight"]
+        pad = self.vocab_shard * tp - c.vocab_size
+        if pad:
+            emb = torch.cat([emb, torch.zeros(pad, emb.shape[1], dtype=emb.dtype,
+                                              device=emb.device)], 0)
+        self.w["embed"] = put(emb[self.vocab_start:self.vocab_start + self.vocab_shard])
+        if c.tie_word_embeddings or "lm_head.weight" not in staged:
+            self.w["lm_head"] = self.w["embed"]
+        else:
+            lm = staged["lm_head.weight"]
+            if pad:
+                lm = torch.cat([lm, torch.zeros(pad, lm.shape[1], dtype=lm.dtype,
+                                                device=lm.device)], 0)
+            self.w["lm_head"] = put(lm[self.vocab_start:self.vocab_start + self.vocab_shard])
+        self.w["final_norm"] = put(staged["model.norm.weight"])
+        self.layers = []
+        for l in range(c.num_layers):
+            p = f"model.layers.{l}."
+            L: dict[str, torch.Tensor] = {}
+            q = shard_rows(staged[p + "self_attn.q_proj.weight"], r, tp)
+            k = kv_shard(staged[p + "self_attn.k_proj.weight"])
+            v = kv_shard(staged[p + "self_attn.v_proj.weight"])
+            L["qkv"] = put(torch.cat([q, k, v], 0))
+            if c.attention_bias and (p + "self_attn.q_proj.bias") in staged:
+                L["qkv_bias"] = put(torch.cat([
+                    shard_rows(staged[p + "self_attn.q_proj.bias"][:, None], r, tp)[:, 0],
+                    kv_shard(staged[p + "self_attn.k_proj.bias"][:, None])[:, 0],
+                    kv_shard(staged[p + "self_attn.v_proj.bias"][:, None])[:, 0]], 0))
+            L["o"] = put(shard_cols(staged[p + "self_attn.o_proj.weight"], r, tp))
+            g = shard_rows(staged[p + "mlp.gate_proj.weight"], r, tp)
+            u = shard_rows(staged[p + "mlp.up_proj.weight"], r, tp)
+            L["gate_up"] = put(torch.cat([g, u], 0))
+            L["down"] = put(shard_cols(staged[p + "mlp.down_proj.weight"], r, tp))
+            L["ln1"] = put(staged[p + "input_layernorm.weight"])
+            L["ln2"] = put(staged[p + "post_attention_layernorm.weight"])
+            if c.sandwich_norm:
+                L["ln_pre_ff"] = put(staged[p + "pre_feedforward_layernorm.weight"])
+                L["ln_post_ff"] = put(staged[p + "post_feedforward_layernorm.weight"])
+            if c.qk_norm and (p + "self_attn.q_norm.weight") in staged:
+                L["q_norm"] = put(staged[p + "self_attn.q_norm.weight"])
+                L["k_norm"] = put(staged[p + "self_attn.k_norm.weight"])
+            self.layers.append(L)
+
+    # ------------------------------------------------------------------ KV cache
+    def kv_cache_groups(self, block_size: int):
+        """[(layer indices, spec dict)] -- one group for full attention; sliding-window
+        layers form a second group when the model mixes both."""
+        c = self.cfg
+        full, sliding = [], []
+        for l in range(c.num_layers):
+            lt = c.layer_types[l] if c.layer_types else "full_attention"
+            (sliding if lt == "sliding_attention" and c.sliding_window else full).append(l)
+        groups = []
+        spec = dict(kind="full", block_size=block_size, num_kv_heads=self.hkv, head_size=self.D,
+                    dtype_bytes=2)
+        if full:
+            groups.append((full, dict(spec)))
+        if sliding:
+            s = dict(spec)
+            s.update(kind="sliding", sliding_window=c.sliding_window)
+            groups.append((sliding, s))
+        return groups
+
+    def alloc_kv_cache(self, num_blocks: int, block_size: int):
+        self.block_size = block_size
+        self.kv_caches = [torch.zeros((num_blocks, 2, block_size, self.hkv, self.D),
+                                      dtype=self.dtype, device=self.device)
+                          for _ in range(self.cfg.num_layers)]
+        self.layer_group = [0] * self.cfg.num_layers
+        for gi, (layers, _) in enumerate(self.kv_cache_groups(block_size)):
+            for l in layers:
+                self.layer_group[l] = gi
+        return self.kv_caches
+
+    def kv_bytes_per_block(self, block_size: int) -> int:
+        return self.cfg.num_layers * 2 * block_size * self.hkv * self.D * 2
+
+    def weight_bytes(self) -> int:
+        seen, n = set(), 0
+        for t in list(self.w.values()) + [t for L in self.layers for t in L.values()]:
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+        return n
+
+    def reserve_buffers(self, max_tokens: int, max_reqs: int) -> None:
+        c = self.cfg
+        qkv_w = (self.hq + 2 * self.hkv) * self.D
+        for name, cols in (("hidden", c.hidden_size), ("resid", c.hidden_size),
+                           ("normed", c.hidden_size), ("qkv", qkv_w), ("attn", self.hq * self.D),
+                           ("gate_up", 2 * self.inter), ("act", self.inter)):
+            self.bufs.reserve(name, max_tokens, cols)
+        self.bufs.reserve("last", max_reqs, c.hidden_size)
+        self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """Returns fp32 logits ``[num_logits, vocab]`` for the rows in ``ctx.logits_indices``."""
+        c, be, T = self.cfg, self.be, ctx.num_tokens
+        H = c.hidden_size
+        eps = c.rms_norm_eps
+        act_kind = ACT_KIND.get(c.hidden_act, 0)
+        hidden = self.bufs.get("hidden", T, H)
+        resid = self.bufs.get("resid", T, H)
+        normed = self.bufs.get("normed", T, H)
+        qkv = self.bufs.get("qkv", T, (self.hq + 2 * self.hkv) * self.D)
+        attn = self.bufs.get("attn", T, self.hq * self.D)
+        gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
+        act = self.bufs.get("act", T, self.inter)
+
+        be_emb = be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden,
+                              vocab_start=self.vocab_start, vocab_total=c.vocab_size,
+                              scale=c.embed_scale)
+        if be_emb is not hidden:
+            hidden.copy_(be_emb)
+        if self.tp > 1:
+            self.comm.all_reduce(hidden)
+        pos = ctx.positions[:T]
+        first = True
+        for l, L in enumerate(self.layers):
+            grp = self.layer_group[l]
+            window = c.sliding_window if (c.sliding_window and (
+                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            # ---- attention block
+            if c.post_norm:
+                if first:
+                    resid.copy_(hidden)
+                x_in = resid
+            elif first:
+                resid.copy_(hidden)
+                x_in = be.rmsnorm(hidden, L["ln1"], eps, out=normed, gemma=c.gemma_norm)
+            else:
+                x_in = be.rmsnorm(hidden, L["ln1"], eps, residual=resid, out=normed,
+                                  gemma=c.gemma_norm)
+            first = False
+            be.gemm(x_in, L["qkv"], bias=L.get("qkv_bias"), out=qkv)
+            be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                       head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
+                       q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=eps,
+                       gemma=c.gemma_norm, slot_mapping=ctx.slot_mapping[grp][:T],
+                       kv_cache=self.kv_caches[l], block_size=self.block_size)
+            be.attention(qkv[:, : self.hq * self.D], self.kv_caches[l], ctx, grp,
+                         num_q_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.D,
+                         block_size=self.block_size, scale=self.scale, out=attn,
+                         softcap=c.attn_logit_softcap, window=window)
+            be.gemm(attn, L["o"], out=hidden)
+            if self.tp > 1:
+                self.comm.all_reduce(hidden)
+            if c.post_norm:
+                # OLMo-2: stream = stream + norm(attn(stream)); the stream lives in `resid`
+                t = be.rmsnorm(hidden, L["ln2"], eps, out=normed)
+                x_mlp = self._add_into(resid, t)
+            else:
+                if c.sandwich_norm:
+                    hidden = be.rmsnorm(hidden, L["ln2"], eps, out=hidden, gemma=c.gemma_norm)
+                    x_mlp = be.rmsnorm(hidden, L["ln_pre_ff"], eps, residual=resid, out=normed,
+                                       gemma=c.gemma_norm)
+                else:
+                    if c.residual_multiplier != 1.0:
+                        hidden = be.mul_scalar(hidden, c.residual_multiplier)
+                    x_mlp = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed,
+                                       gemma=c.gemma_norm)
+            # ---- MLP block
+            be.gemm(x_mlp, L["gate_up"], out=gate_up)
+            a = be.act_and_mul(gate_up, act_kind, out=act)
+            hidden = self.bufs.get("hidden", T, H)
+            be.gemm(a, L["down"], out=hidden)
+            if self.tp > 1:
+                self.comm.all_reduce(hidden)
+            if c.post_norm:
+                t = be.rmsnorm(hidden, L["ln_post_ff"] if "ln_post_ff" in L else L["ln1"], eps,
+                               out=normed)
+                self._add_into(resid, t)
+            elif c.sandwich_norm:
+                hidden = be.rmsnorm(hidden, L["ln_post_ff"], eps, out=hidden, gemma=c.gemma_norm)
+            elif c.residual_multiplier != 1.0:
+                hidden = be.mul_scalar(hidden, c.residual_multiplier)
+        # ---- final norm on the rows that sample, lm_head
+        if c.post_norm:
+            final_in, res = resid, None
+        else:
+            final_in, res = hidden, resid
+        if ctx.decode_only_full_logits:
+            n = T
+            last = be.rmsnorm(final_in, self.w["final_norm"], eps, residual=res, out=normed,
+                              gemma=c.gemma_norm)
+        else:
+            n = ctx.num_logits
+            full = be.rmsnorm(final_in, self.w["final_norm"], eps, residual=res, out=normed,
+                              gemma=c.gemma_norm)
+            last = be.gather_rows(full, ctx.logits_indices[:n], out=self.bufs.get("last", n, H))
+        logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
+        be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
+        if self.tp > 1:
+            logits = self.comm.all_gather(logits, dim=-1)
+        if logits.shape[1] != c.vocab_size:
+            logits = logits[:, : c.vocab_size]
+        if c.logits_scaling != 1.0:
+            logits = logits / c.logits_scaling
+        if c.final_logit_softcap > 0:
+            logits = c.final_logit_softcap * torch.tanh(logits / c.final_logit_softcap)
+        return logits
+
+    def _add_into(self, resid, t):
+        """Post-norm residual: resid += t; returns the stream."""
+        resid.copy_(self.be.add(resid, t))
+        return resid

@@ -116,7 +116,11 @@ _CODES = {-1: "rejected shape/alignment", -2: "launch failure", -3: "tensor-map 
           -4: "size beyond the stated maximum"}
 
 
+LAUNCHES = [0]  # launcher calls made by this process (each launches >= 1 kernel)
+
+
 def check(rc: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if rc != 0:
         raise KernelError(f"{what}: {_CODES.get(rc, 'error')} (code {rc})")
 

@@ -33,11 +33,58 @@ def _time(fn, iters=10, warmup=3, flush=None):
     return times[len(times) // 2]
 
 
+def small_case(name: str):
+    """One kernel on a small input (a few hundred MB at most), three launches."""
+    dev = torch.device("cuda")
+    Hq, Hkv, D, bs = 32, 8, 128, 16
+    if name == "gemm_small":
+        a = torch.randn(4096, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(6144, 4096, device=dev, dtype=torch.bfloat16) * 0.05
+        fn = lambda: ops.gemm(a, w)
+    elif name == "gemm_decode_small":
+        a = torch.randn(64, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(28672, 4096, device=dev, dtype=torch.bfloat16) * 0.05
+        fn = lambda: ops.gemm(a, w)
+    elif name == "prefill_small":
+        B, ql = 4, 1024
+        nb = ql // bs
+        cache = torch.randn(B * nb + 1, 2, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ql, dtype=torch.int32, device=dev)
+        qs = torch.arange(B + 1, device=dev, dtype=torch.int32) * ql
+        treq, tq0 = ref.build_prefill_tiles([ql] * B)
+        treq = torch.tensor(treq, dtype=torch.int32, device=dev)
+        tq0 = torch.tensor(tq0, dtype=torch.int32, device=dev)
+        q = torch.randn(B * ql, Hq * D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.attn_prefill(q, cache, block_table=bt, seq_lens=sl, q_start=qs,
+                                      tile_req=treq, tile_q0=tq0, num_q_heads=Hq,
+                                      num_kv_heads=Hkv, head_dim=D, block_size=bs,
+                                      scale=D ** -0.5)
+    elif name == "decode_small":
+        B, ctx = 128, 1024
+        nb = ctx // bs
+        cache = torch.randn(B * nb + 1, 2, bs, Hkv, D, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        q = torch.randn(B, Hq * D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.attn_decode(q, cache, block_table=bt, seq_lens=sl, num_q_heads=Hq,
+                                     num_kv_heads=Hkv, head_dim=D, block_size=bs, scale=D ** -0.5)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    ms = _time(fn, iters=3, warmup=1)
+    print(f"{name}: {ms:.4f} ms  status={ops.read_status()}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--case", default=None,
+                    help="run one small case only (for profiler captures): "
+                         "gemm_small | gemm_decode_small | prefill_small | decode_small")
     args = ap.parse_args()
+    if args.case:
+        return small_case(args.case)
     dev = torch.device("cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []

@@ -1,0 +1,424 @@
+"""Model runner: turns a SchedulerOutput into one packed host->device copy, a forward pass
+(CUDA graph replay for decode-only batches) and sampled token ids.
+
+The step loop, the scheduler and the input preparation (``InputBatch.prepare``) are C++;
+this class owns the device side: KV-cache tensors, the packed step buffer (pinned host +
+device copy), CUDA graphs keyed by padded decode batch size, and the sampler pipeline.
+
+Reference: ``src/vllm/v1/worker/gpu/runner.cpp:373`` (initialize_kv_cache), ``:669-880``
+(execute_model), ``:1051`` (sample_tokens), ``:1164`` (sample_tokens_async), decode graphs
+``qwen3_5.cpp:5898-5960`` and ``include/vllm/model_executor/models/decode_graph_sizes.h``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _engine as E
+from ..models.base import StepContext
+
+_DT = {"input_ids": (torch.int64, 8), "positions": (torch.int64, 8), "slot_mapping": (torch.int64, 8),
+       "query_start": (torch.int32, 4), "seq_lens": (torch.int32, 4), "block_table": (torch.int32, 4),
+       "logits_indices": (torch.int32, 4), "tile_req": (torch.int32, 4), "tile_q0": (torch.int32, 4),
+       "prefill_q_start": (torch.int32, 4), "state_slots": (torch.int32, 4),
+       "temperature": (torch.float32, 4), "top_p": (torch.float32, 4), "min_p": (torch.float32, 4),
+       "top_k": (torch.int32, 4), "seeds": (torch.int64, 8), "steps": (torch.int64, 8),
+       "rep_pen": (torch.float32, 4), "freq_pen": (torch.float32, 4), "pres_pen": (torch.float32, 4),
+       "splice_dst": (torch.int32, 4), "splice_src": (torch.int32, 4)}
+
+
+def decode_graph_sizes(max_num_seqs: int) -> list[int]:
+    """Padded decode batch sizes that get a captured graph: 1,2,4,8,16,24,...,max."""
+    sizes = [s for s in (1, 2, 4, 8) if s <= max_num_seqs]
+    s = 16
+    while s < max_num_seqs:
+        sizes.append(s)
+        s += 8 if s < 64 else (16 if s < 256 else 32)
+    if max_num_seqs not in sizes:
+        sizes.append(max_num_seqs)
+    return sorted(set(sizes))
+
+
+class ModelRunner(E.ModelRunnerBase):
+    def __init__(self, model, *, block_size: int, num_blocks: int, max_num_seqs: int,
+                 max_num_batched_tokens: int, max_model_len: int, enable_cuda_graphs: bool = True,
+                 async_mode: bool = False):
+        super().__init__()
+        self.model = model
+        self.device = model.device
+        self.is_cuda = self.device.type == "cuda"
+        self.block_size = block_size
+        self.num_blocks = num_blocks
+        self.max_num_seqs = max_num_seqs
+        self.max_tokens = max(max_num_batched_tokens, max_num_seqs)
+        self.max_model_len = max_model_len
+        self.async_mode = async_mode
+        self.groups = model.kv_cache_groups(block_size)
+        self.num_groups = len(self.groups)
+        self.max_blocks = (max_model_len + block_size - 1) // block_size + 1
+        self.layout = E.StepLayout.make(self.max_tokens, max_num_seqs, self.max_blocks,
+                                        self.num_groups)
+        self.off = self.layout.offsets()
+        nbytes = self.layout.total_bytes
+        self.host_buf = torch.zeros(nbytes, dtype=torch.uint8, pin_memory=self.is_cuda)
+        self.dev_buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        self.batch = E.InputBatch(max_num_seqs, max_model_len, self.max_tokens,
+                                  [g[1]["block_size"] for g in self.groups])
+        model.alloc_kv_cache(num_blocks, block_size)
+        model.reserve_buffers(self.max_tokens, max_num_seqs)
+        self.views = self._make_views(self.dev_buf)
+        self.host_views = self._make_views(self.host_buf)
+        self.sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
+        self.sampled_host = torch.zeros(max_num_seqs, dtype=torch.int64,
+                                        pin_memory=self.is_cuda)
+        self.last_sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
+        self.graphs: dict[int, tuple] = {}
+        self.enable_graphs = enable_cuda_graphs and self.is_cuda
+        self.graph_sizes = decode_graph_sizes(max_num_seqs) if self.enable_graphs else []
+        self._info = None
+        self._logits = None
+        self._eos: dict[str, int] = {}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.num_kernel_steps = 0
+        self.launches = 0
+        if self.is_cuda:
+            from .. import ops
+            self.ops = ops
+            self.copy_stream = torch.cuda.Stream(device=self.device)
+            Hq, Hkv, D = model.hq, model.hkv, model.D
+            self._decode_tmp: dict[int, tuple] = {}
+            self._Hq, self._Hkv, self._D = Hq, Hkv, D
+
+    # ------------------------------------------------------------------ helpers
+    def _make_views(self, buf: torch.Tensor) -> dict:
+        L, o = self.layout, self.off
+        v = {}
+
+        def view(name, count):
+            dt, sz = _DT[name]
+            return buf[o[name]: o[name] + count * sz].view(dt)
+
+        T, R, B, G = L.max_tokens, L.max_reqs, L.max_blocks, L.num_groups
+        v["input_ids"] = view("input_ids", T)
+        v["positions"] = view("positions", T)
+        sm = view("slot_mapping", T * G).view(G, T)
+        v["slot_mapping"] = [sm[g] for g in range(G)]
+        v["query_start"] = view("query_start", R + 1)
+        v["seq_lens"] = view("seq_lens", R)
+        bt = view("block_table", G * R * B).view(G, R, B)
+        v["block_table"] = [bt[g] for g in range(G)]
+        v["logits_indices"] = view("logits_indices", R)
+        v["tile_req"] = view("tile_req", L.max_tiles)
+        v["tile_q0"] = view("tile_q0", L.max_tiles)
+        v["prefill_q_start"] = view("prefill_q_start", R + 1)
+        v["state_slots"] = view("state_slots", R)
+        for k in ("temperature", "top_p", "min_p", "top_k", "seeds", "steps", "rep_pen", "freq_pen",
+                  "pres_pen", "splice_dst", "splice_src"):
+            v[k] = view(k, R)
+        return v
+
+    def kv_cache_config(self) -> "E.KVCacheConfig":
+        groups = []
+        for layers, spec in self.groups:
+            kind = {"full": E.KVSpecKind.FULL_ATTENTION, "sliding": E.KVSpecKind.SLIDING_WINDOW,
+                    "mla": E.KVSpecKind.MLA, "mamba": E.KVSpecKind.MAMBA,
+                    "chunked": E.KVSpecKind.CHUNKED_LOCAL}[spec["kind"]]
+            kw = {k: v for k, v in spec.items() if k != "kind"}
+            groups.append(E.KVCacheGroupSpec([f"layers.{l}" for l in layers],
+                                             E.KVCacheSpec(kind=kind, **kw)))
+        return E.KVCacheConfig(self.num_blocks, groups)
+
+    def set_eos(self, req_id: str, eos: Optional[int]) -> None:
+        self._eos[req_id] = -1 if eos is None else int(eos)
+
+    def supports_async(self) -> bool:
+        return self.is_cuda
+
+    def _decode_splits(self, batch: int) -> tuple[int, tuple | None]:
+        if not self.is_cuda:
+            return 1, None
+        key = batch
+        if key not in self._decode_tmp:
+            s = self.ops.attn_decode_splits(batch, self._Hkv, self._Hq // self._Hkv, self._D,
+                                            self.max_model_len)
+            tmp = None
+            if s > 1:
+                tmp = (torch.empty((batch, self._Hq, s, self._D), dtype=torch.float32,
+                                   device=self.device),
+                       torch.empty((batch, self._Hq, s), dtype=torch.float32, device=self.device))
+            self._decode_tmp[key] = (s, tmp)
+        return self._decode_tmp[key]
+
+    def _context(self, info, padded: int | None = None) -> StepContext:
+        v = self.views
+        T = padded if padded is not None else info.num_tokens
+        nd = padded if padded is not None else info.num_decodes
+        splits, tmp = self._decode_splits(nd) if nd > 0 else (1, None)
+        ctx = StepContext(
+            num_tokens=T, num_reqs=padded if padded is not None else info.num_reqs,
+            num_decodes=nd, num_prefills=0 if padded is not None else info.num_prefills,
+            num_prefill_tokens=0 if padded is not None else info.num_prefill_tokens,
+            num_tiles=0 if padded is not None else info.num_tiles,
+            num_logits=T if padded is not None else info.num_logits,
+            input_ids=v["input_ids"], positions=v["positions"], slot_mapping=v["slot_mapping"],
+            query_start=v["query_start"], seq_lens=v["seq_lens"], block_table=v["block_table"],
+            logits_indices=v["logits_indices"], tile_req=v["tile_req"], tile_q0=v["tile_q0"],
+            prefill_q_start=v["prefill_q_start"], state_slots=v["state_slots"],
+            decode_splits=splits, max_seq_len=info.max_seq_len if info else 0,
+            max_query_len=info.max_query_len if info else 1,
+            decode_only_full_logits=padded is not None)
+        ctx.extra["decode_tmp"] = tmp
+        if not self.is_cuda:
+            # CPU oracle path wants exact-length views
+            R = ctx.num_reqs
+            ctx.query_start = v["query_start"][: R + 1]
+            ctx.seq_lens = v["seq_lens"][:R]
+            ctx.block_table = [b[:R] for b in v["block_table"]]
+        return ctx
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def _pad_size(self, n: int) -> int | None:
+        for s in self.graph_sizes:
+            if s >= n:
+                return s
+        return None
+
+    def _capture(self, size: int):
+        """Capture forward + greedy argmax for a decode-only batch padded to ``size`` rows."""
+        info_stub = type("S", (), {"max_seq_len": 0, "max_query_len": 1})()
+        ctx = self._context(info_stub, padded=size)
+        # warm-up run on a side stream (allocations, tensor maps, lazy module state)
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                logits = self.model.forward(ctx)
+                self.ops.argmax(logits, out=self.sampled[:size])
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        from ..ops import _lib
+        g = torch.cuda.CUDAGraph()
+        n0 = _lib.LAUNCHES[0]
+        with torch.cuda.graph(g):
+            logits = self.model.forward(ctx)
+            self.ops.argmax(logits, out=self.sampled[:size])
+        self.graphs[size] = (g, logits, _lib.LAUNCHES[0] - n0)
+        return self.graphs[size]
+
+    def warmup_graphs(self, sizes: list[int] | None = None) -> None:
+        """Capture the decode graphs up front (pad rows: slot -1, seq_len 0, token 0)."""
+        if not self.enable_graphs:
+            return
+        hv = self.host_views
+        for k in ("input_ids", "positions", "seq_lens"):
+            hv[k].zero_()
+        for g in range(self.num_groups):
+            hv["slot_mapping"][g].fill_(-1)
+            hv["block_table"][g].zero_()
+        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+        for s in (sizes or self.graph_sizes):
+            if s not in self.graphs:
+                self._capture(s)
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ step
+    def execute_model(self, so) -> None:
+        self.batch.update_states(so)
+        for n in so.scheduled_new_reqs:
+            pass
+        info = self.batch.prepare(so, self.layout, self.host_buf.data_ptr(), self.async_mode)
+        self._info = info
+        R, T = info.num_reqs, info.num_tokens
+        decode_only = info.num_prefills == 0 and info.num_decodes == R
+        pad = self._pad_size(R) if (decode_only and self.enable_graphs and info.all_greedy
+                                    and not info.any_penalties and not info.any_logprobs) else None
+        if pad is not None and pad > R:
+            hv = self.host_views
+            hv["input_ids"][R:pad].zero_()
+            hv["positions"][R:pad].zero_()
+            hv["seq_lens"][R:pad].zero_()
+            for g in range(self.num_groups):
+                hv["slot_mapping"][g][R:pad].fill_(-1)
+        # one packed host->device copy per step
+        nbytes = self.layout.total_bytes
+        if self.is_cuda:
+            self.dev_buf.copy_(self.host_buf, non_blocking=True)
+        else:
+            self.dev_buf.copy_(self.host_buf)
+        self.h2d_bytes += nbytes
+        if info.num_splice and self.is_cuda:
+            v = self.views
+            from ..ops import _lib
+            _lib.check(_lib.lib().b200_splice_sampled(
+                v["input_ids"].data_ptr(), v["splice_dst"].data_ptr(), v["splice_src"].data_ptr(),
+                self.last_sampled.data_ptr(), info.num_splice, _lib.stream_ptr()), "splice")
+        if pad is not None:
+            g = self.graphs.get(pad) or self._capture(pad)
+            g[0].replay()
+            from ..ops import _lib as _l
+            _l.LAUNCHES[0] += g[2]  # launcher calls folded into the replayed graph
+            self._logits = g[1][:R]
+            self._graph_sampled = True
+        else:
+            ctx = self._context(info)
+            self._logits = self.model.forward(ctx)
+            self._graph_sampled = False
+        self.num_kernel_steps += 1
+
+    def _sample_device(self, info, grammar) -> torch.Tensor:
+        """Runs the sampler pipeline on the logits of this step; returns int64 ids [num_logits]."""
+        n = info.num_logits
+        logits = self._logits
+        v = self.views
+        if self._graph_sampled:
+            return self.sampled[:n]
+        if not self.is_cuda:
+            return self._sample_cpu(info, grammar)
+        ops = self.ops
+        # row-compacted per-request scalars (rows that sample are a subset of the batch)
+        rows = [i for i, p in enumerate(info.produces_token) if p]
+        idx = None
+        if len(rows) != info.num_reqs:
+            idx = torch.tensor(rows, dtype=torch.int64, device=self.device)
+
+        def per_row(name):
+            t = v[name][: info.num_reqs]
+            return t if idx is None else t[idx].contiguous()
+
+        dev = self.device
+        if grammar is not None and grammar.structured_output_request_ids:
+            rid = {r: i for i, r in enumerate([info.req_ids[j] for j in rows])}
+            row_ids = torch.tensor([rid.get(r, -1) for r in grammar.structured_output_request_ids],
+                                   dtype=torch.int32, device=dev)
+            mask = torch.tensor(grammar.bitmask, dtype=torch.int32, device=dev).view(
+                len(grammar.structured_output_request_ids), grammar.words_per_row)
+            ops.apply_bitmask(logits, mask, row_ids)
+        br, btk, bv, nr, nt = self.batch.logit_edits(info, self._eos)
+        if br:
+            ops.apply_logit_bias(logits, torch.tensor(br, dtype=torch.int32, device=dev),
+                                 torch.tensor(btk, dtype=torch.int32, device=dev),
+                                 torch.tensor(bv, dtype=torch.float32, device=dev))
+        if nr:
+            ops.apply_token_mask(logits, torch.tensor(nr, dtype=torch.int32, device=dev),
+                                 torch.tensor(nt, dtype=torch.int32, device=dev))
+        if info.any_penalties:
+            pr, pt, pc = self.batch.penalty_entries(info)
+            if pr:
+                ops.apply_penalties(logits, torch.tensor(pr, dtype=torch.int32, device=dev),
+                                    torch.tensor(pt, dtype=torch.int32, device=dev),
+                                    torch.tensor(pc, dtype=torch.int32, device=dev),
+                                    per_row("rep_pen"), per_row("freq_pen"), per_row("pres_pen"))
+        greedy = ops.argmax(logits, out=self.sampled[:n])
+        if info.all_greedy:
+            return greedy
+        temp = per_row("temperature")
+        ops.apply_temperature(logits, temp)
+        if info.any_min_p:
+            ops.apply_min_p(logits, per_row("min_p"))
+        if info.any_top_k_top_p:
+            ops.apply_top_k_top_p(logits, per_row("top_k"), per_row("top_p"))
+        probs = ops.softmax(logits)
+        rnd = ops.random_sample(probs, per_row("seeds"), per_row("steps"))
+        out = ops.merge_greedy_random(greedy.clone(), rnd, temp, out=self.sampled[:n])
+        return out
+
+    def _sample_cpu(self, info, grammar) -> torch.Tensor:
+        from ..sample import cpu_sampler
+        return cpu_sampler.sample(self, info, self._logits, grammar)
+
+    def _logprobs_rows(self, info, ids: torch.Tensor):
+        if not info.any_logprobs:
+            return None
+        lp = torch.log_softmax(self._raw_logits.float(), -1) if hasattr(self, "_raw_logits") else \
+            torch.log_softmax(self._logits.float(), -1)
+        out = []
+        row = 0
+        for r, p in enumerate(info.produces_token):
+            if not p:
+                out.append([])
+                continue
+            k = info.max_logprobs[r]
+            if k < 0:
+                out.append([])
+            else:
+                tok = int(ids[row])
+                lr = E.LogprobsRow()
+                vals, idxs = torch.topk(lp[row], k) if k > 0 else (torch.empty(0), torch.empty(0))
+                lr.token_ids = [tok] + [int(i) for i in idxs]
+                lr.logprobs = [float(lp[row, tok])] + [float(x) for x in vals]
+                rank = int((lp[row] > lp[row, tok]).sum()) + 1
+                lr.ranks = [rank] + list(range(1, k + 1))
+                out.append([lr])
+            row += 1
+        return out
+
+    def _build_output(self, info, ids_host) -> "E.ModelRunnerOutput":
+        out = E.ModelRunnerOutput()
+        out.req_ids = list(info.req_ids)
+        toks = []
+        row = 0
+        for r, p in enumerate(info.produces_token):
+            if p:
+                t = int(ids_host[row])
+                toks.append([t])
+                self.batch.append_sampled(info.req_ids[r], [t])
+                row += 1
+            else:
+                toks.append([])
+        out.sampled_token_ids = toks
+        return out
+
+    def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
+        info = self._info
+        n = info.num_logits
+        if n == 0:
+            return self._build_output(info, [])
+        if info.any_logprobs:
+            self._raw_logits = self._logits.clone()
+        ids = self._sample_device(info, grammar)
+        if self.is_cuda:
+            self.sampled_host[:n].copy_(ids[:n], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            host = self.sampled_host[:n].tolist()
+        else:
+            host = ids[:n].tolist()
+        self.d2h_bytes += n * 8
+        out = self._build_output(info, host)
+        lps = self._logprobs_rows(info, host)
+        if lps is not None:
+            out.logprobs = lps
+        return out
+
+    def sample_tokens_async(self, grammar):
+        """Sampled ids stay on the device for the next step's input splice; the returned
+        handle blocks only on the copy-stream event of the device->host copy."""
+        info = self._info
+        n = info.num_logits
+        if n == 0 or not self.is_cuda:
+            out = self.sample_tokens(grammar)
+            return lambda: out
+        ids = self._sample_device(info, grammar).clone()  # the next step reuses the buffer
+        rows = [i for i, p in enumerate(info.produces_token) if p]
+        # scatter into the per-batch-row table read by the next step's splice kernel
+        row_of = torch.tensor(rows, dtype=torch.int32, device=self.device)
+        from ..ops import _lib
+        _lib.check(_lib.lib().b200_scatter_sampled(self.last_sampled.data_ptr(), row_of.data_ptr(),
+                                                   ids.data_ptr(), n, _lib.stream_ptr()), "scatter")
+        ev = torch.cuda.Event()
+        host = torch.empty(n, dtype=torch.int64, pin_memory=True)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(ready)
+            host.copy_(ids[:n], non_blocking=True)
+            ev.record(self.copy_stream)
+        self.d2h_bytes += n * 8
+
+        def get():
+            ev.synchronize()
+            return self._build_output(info, host.tolist())
+
+        return get
