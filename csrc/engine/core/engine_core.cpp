@@ -40,8 +40,10 @@ std::pair<EngineCoreOutputs, bool> EngineCore::step() {
   double t1 = now_ms();
   bool executed = so.total_num_scheduled_tokens > 0;
   ModelRunnerOutput mro;
+  // The runner sees every scheduler output, also an empty one: that is how it learns about
+  // finished and preempted requests and releases their state.
+  executor_->execute_model(so);
   if (executed) {
-    executor_->execute_model(so);
     GrammarOutput g = scheduler_->get_grammar_bitmask(so);
     mro = executor_->sample_tokens(g.structured_output_request_ids.empty() ? nullptr : &g);
     ++num_executed_steps;
@@ -64,8 +66,8 @@ std::pair<EngineCoreOutputs, bool> EngineCore::step_with_batch_queue() {
     double t0 = now_ms();
     SchedulerOutput so = scheduler_->schedule();
     last_schedule_ms = now_ms() - t0;
+    executor_->execute_model(so);  // also for an empty schedule (state release)
     if (so.total_num_scheduled_tokens > 0) {
-      executor_->execute_model(so);
       // Structured requests need the tokens of the previous step to advance their grammar
       // before a mask can be built, so their sampling cannot be deferred behind the queue.
       bool has_structured = !so.structured_output_request_ids.empty();

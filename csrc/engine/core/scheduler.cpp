@@ -440,7 +440,7 @@ void Scheduler::update_draft_token_ids(const DraftTokenIds& drafts) {
     auto r = get_request(drafts.req_ids[i]);
     if (!r || r->finished()) continue;
     // A request that is still prefilling (chunked) cannot verify drafts yet.
-    if (r->num_computed_tokens < r->num_tokens()) { r->spec_token_ids.clear(); continue; }
+    if (r->num_computed_tokens < r->num_tokens() - 1) { r->spec_token_ids.clear(); continue; }
     r->spec_token_ids = drafts.draft_token_ids[i];
   }
 }

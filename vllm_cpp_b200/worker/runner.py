@@ -227,8 +227,9 @@ class ModelRunner(E.ModelRunnerBase):
     # ------------------------------------------------------------------ step
     def execute_model(self, so) -> None:
         self.batch.update_states(so)
-        for n in so.scheduled_new_reqs:
-            pass
+        if so.total_num_scheduled_tokens == 0:
+            self._info = None
+            return
         info = self.batch.prepare(so, self.layout, self.host_buf.data_ptr(), self.async_mode)
         self._info = info
         R, T = info.num_reqs, info.num_tokens
