@@ -316,6 +316,14 @@ int b200_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kv_
   return 0;
 }
 
+int b200_attn_decode_merge(const void* tmp_o, const void* tmp_lse, void* out, int ldo, int B,
+                           int Hq, int D, int splits, cudaStream_t stream) {
+  dim3 grid(B, Hq);
+  attn_decode_merge_kernel<<<grid, 128, 0, stream>>>((const float*)tmp_o, (const float*)tmp_lse,
+                                                     (__nv_bfloat16*)out, ldo, Hq, D, splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 int b200_merge_attn_states(const void* a, const void* lse_a, const void* b, const void* lse_b,
                            void* out, void* lse_out, int T, int H, int D, cudaStream_t stream) {
   if (T <= 0) return 0;

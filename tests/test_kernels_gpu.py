@@ -242,6 +242,38 @@ def test_attn_decode(D, Hq, Hkv, bs, splits):
     assert _rel_err(out2, exp2) < 1e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv,bs,splits", [(32, 8, 16, 0), (4, 1, 32, 1), (32, 4, 16, 3),
+                                              (16, 16, 64, 2), (8, 1, 128, 4), (16, 1, 16, 2)])
+def test_attn_decode_tcgen05(Hq, Hkv, bs, splits):
+    """tcgen05 swapped-operand decode kernel vs the fp32 oracle and vs the CUDA-core kernel."""
+    torch.manual_seed(21)
+    D = 128
+    seq_lens = [1, 127, 128, 129, 700, 1234, 0, 31]
+    lens_for_cache = [max(s, 1) for s in seq_lens]
+    cache, bt = _make_paged(lens_for_cache, Hkv, D, bs)
+    B = len(seq_lens)
+    q = _rand(B, Hq * D)
+    # strided q like the model passes it (a column slice of the merged qkv buffer)
+    wide = _rand(B, (Hq + 2 * Hkv) * D)
+    wide[:, : Hq * D] = q
+    qv = wide[:, : Hq * D]
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    qs = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    kw = dict(block_table=bt, seq_lens=sl, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+              block_size=bs, scale=D ** -0.5, splits=splits)
+    out = ops.attn_decode(qv, cache, **kw)
+    assert ops.read_status() == 0
+    exp = ref.paged_attention(q, cache, bt, sl, qs, Hq, Hkv, D, bs, D ** -0.5)
+    assert _rel_err(out, exp) < 1e-2
+    old = ops.attn_decode(qv, cache, force_cuda_core=True, **kw)
+    assert _rel_err(out, old) < 1e-2
+    out2 = ops.attn_decode(qv, cache, window=100, softcap=30.0, **kw)
+    exp2 = ref.paged_attention(q, cache, bt, sl, qs, Hq, Hkv, D, bs, D ** -0.5, window=100,
+                               softcap=30.0)
+    assert _rel_err(out2, exp2) < 1e-2
+    assert ops.read_status() == 0
+
+
 def test_merge_attn_states():
     torch.manual_seed(12)
     T, H, D = 9, 4, 128

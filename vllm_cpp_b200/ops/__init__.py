@@ -229,21 +229,39 @@ def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, *, block_table: torch.
     return out
 
 
-def attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len) -> int:
+def _decode_uses_tc(head_dim: int, group: int, block_size: int) -> bool:
+    """The tcgen05 swapped-operand decode kernel covers head_dim 128, GQA groups up to 16 and
+    page sizes that tile 128 tokens; everything else takes the CUDA-core kernel."""
+    if head_dim != 128 or group > 16 or block_size < 8 or block_size % 8:
+        return False
+    return (128 % block_size == 0) if block_size <= 128 else (block_size % 128 == 0)
+
+
+def attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len,
+                       block_size: int = 16) -> int:
+    if _decode_uses_tc(head_dim, group, block_size):
+        ctas = max(1, batch * num_kv_heads)
+        want = -(-2 * num_sms() // ctas)
+        tiles = max(1, -(-max_seq_len // 128))
+        return max(1, min(want, max(1, tiles // 2), 32))
     return lib().b200_attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len)
 
 
 def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, *, block_table: torch.Tensor,
                 seq_lens: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int,
                 block_size: int, scale: float, out: torch.Tensor | None = None, splits: int = 0,
-                softcap: float = 0.0, window: int = 0, tmp: tuple | None = None):
+                softcap: float = 0.0, window: int = 0, tmp: tuple | None = None,
+                force_cuda_core: bool = False):
     """Paged decode attention, one query row per sequence."""
     B = q.shape[0]
     if out is None:
         out = torch.empty((B, num_q_heads * head_dim), dtype=q.dtype, device=q.device)
+    use_tc = (not force_cuda_core) and _decode_uses_tc(head_dim, num_q_heads // num_kv_heads,
+                                                       block_size)
     if splits <= 0:
         splits = attn_decode_splits(B, num_kv_heads, num_q_heads // num_kv_heads, head_dim,
-                                    block_table.shape[1] * block_size)
+                                    block_table.shape[1] * block_size,
+                                    block_size if use_tc else 0)
     tmp_o = tmp_lse = None
     if splits > 1:
         if tmp is None:
@@ -252,6 +270,13 @@ def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, *, block_table: torch.T
             tmp_lse = torch.empty((B, num_q_heads, splits), dtype=torch.float32, device=q.device)
         else:
             tmp_o, tmp_lse = tmp
+    if use_tc:
+        check(lib().b200_attn_decode_tc(
+            ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(kv_cache), kv_cache.shape[0],
+            block_size, num_q_heads, num_kv_heads, head_dim, ptr(block_table),
+            block_table.stride(0), ptr(seq_lens), B, scale, softcap, window, splits, ptr(tmp_o),
+            ptr(tmp_lse), stream_ptr()), "attn_decode_tc")
+        return out
     check(lib().b200_attn_decode(
         ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(kv_cache), block_size, num_q_heads,
         num_kv_heads, head_dim, ptr(block_table), block_table.stride(0), ptr(seq_lens), B, scale,

@@ -70,6 +70,7 @@ _SIGS = {
     "b200_attn_prefill": ([P, I, P, I, P, P, L, I, I, I, I, P, I, P, P, P, P, I, I, F, F, I, I, P], I),
     "b200_attn_decode_splits": ([I, I, I, I, I], I),
     "b200_attn_decode": ([P, I, P, I, P, I, I, I, I, P, I, P, I, F, F, I, I, P, P, P], I),
+    "b200_attn_decode_tc": ([P, I, P, I, P, L, I, I, I, I, P, I, P, I, F, F, I, I, P, P, P], I),
     "b200_merge_attn_states": ([P, P, P, P, P, P, I, I, I, P], I),
     "b200_argmax": ([P, I, I, I, P, P, P, P], I),
     "b200_apply_temperature": ([P, I, I, I, P, P], I),

@@ -143,7 +143,7 @@ class ModelRunner(E.ModelRunnerBase):
         key = batch
         if key not in self._decode_tmp:
             s = self.ops.attn_decode_splits(batch, self._Hkv, self._Hq // self._Hkv, self._D,
-                                            self.max_model_len)
+                                            self.max_model_len, self.block_size)
             tmp = None
             if s > 1:
                 tmp = (torch.empty((batch, self._Hq, s, self._D), dtype=torch.float32,
