@@ -1,17 +1,18 @@
 // Paged flash-attention prefill on tcgen05 / TMEM (varlen, causal with bottom-right
 // alignment, GQA, sliding window, soft-cap), head_dim 64 or 128.
 //
-// One CTA = one 128-row query tile of one request and one query head. Per 128-token KV
-// tile:  S = Q K^T  (tcgen05, A = Q smem, B = K smem, both K-major SW128, fp32 S in TMEM),
-// softmax with one thread per query row (TMEM lane == row, so no cross-thread reductions),
-// P written to smem as bf16 in the UMMA K-major swizzled layout, then  PV = P V  with V as
-// an MN-major operand (the pages land in smem exactly as they sit in the cache, d
-// contiguous). QK^T of tile j+1 and PV of tile j-1 run on the tensor pipe while the softmax
-// warps work on tile j; S is double-buffered in TMEM; O lives in registers and is
-// rescaled when the running max moves.
+// One CTA = one 128-row query tile of one request and one query head; two CTAs share an SM.
+// Per 64-token KV tile:  S = Q K^T  (tcgen05, A = Q smem, B = K smem, both K-major SW128,
+// fp32 S in TMEM), softmax with one thread per query row (TMEM lane == row, so no
+// cross-thread reductions), P written to smem as bf16 in the UMMA K-major swizzled layout,
+// then  PV = P V  with V as an MN-major operand (the pages land in smem exactly as they sit
+// in the cache, d contiguous). QK^T of tile j+1 and PV of tile j-1 run on the tensor pipe
+// while the softmax warps work on tile j; S is double-buffered in TMEM; O lives in registers
+// and is rescaled when the running max moves.
 //
-// K/V pages are fetched with 3-D TMA boxes (64 dims x 1 head x min(block_size,128) tokens)
-// straight from the paged cache [num_blocks, 2, block_size, Hkv, D].
+// K and V tiles share one ring of three TMA slots; pages are fetched with 3-D TMA boxes
+// (64 dims x 1 head x min(block_size, 64) tokens) straight from the paged cache
+// [num_blocks, 2, block_size, Hkv, D].
 //
 // Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner,
 // warps 2..5 softmax + output.
@@ -28,7 +29,8 @@
 namespace b200 {
 
 static constexpr int kQT = 128;   // query rows per CTA
-static constexpr int kKT = 128;   // kv tokens per tile
+static constexpr int kKT = 64;    // kv tokens per tile
+static constexpr int kRing = 3;   // K/V slots
 
 struct PrefillParams {
   __nv_bfloat16* out;   // [T, Hq*D]
@@ -42,7 +44,7 @@ struct PrefillParams {
   const int32_t* tile_q0;      // [num_tiles] first query row of the tile inside its request
   int Hq, Hkv, block_size;
   float scale_log2;            // softmax scale * log2(e)
-  float softcap;               // 0 = off
+  float softcap2;              // soft-cap in the log2 domain, 0 = off
   int window;                  // sliding window (tokens to the left incl. self), 0 = off
   int causal;
   int* status;
@@ -50,28 +52,34 @@ struct PrefillParams {
 
 struct alignas(8) PrefillBars {
   uint64_t q_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t kv_full[kRing], kv_empty[kRing];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, p_empty, o_full, o_empty;
   uint32_t tmem_base;
 };
 
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
     attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                         const __grid_constant__ CUtensorMap tmKV, PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  constexpr int kDH = D / 64;                  // 64-wide halves of the head dim
-  constexpr int kHalfBytes = 128 * 128;        // 128 rows x 128 B
-  constexpr int kQBytes = kDH * kHalfBytes;
-  constexpr int kKVBytes = kDH * kHalfBytes;   // one K or V stage
-  constexpr int kPBytes = 2 * kHalfBytes;      // 128 x 128 bf16
+  constexpr int kDH = D / 64;                     // 64-wide halves of the head dim
+  constexpr int kQHalf = kQT * 128;               // 16 KB: 128 rows x 128 B
+  constexpr int kKVHalf = kKT * 128;              // 8 KB: 64 tokens x 128 B
+  constexpr int kQBytes = kDH * kQHalf;
+  constexpr int kSlotBytes = kDH * kKVHalf;       // one K or V tile
+  constexpr int kPBytes = kQT * kKT * 2;          // 16 KB: one K-major half-tile
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kQBytes;                  // 2 stages
-  uint8_t* sV = sK + 2 * kKVBytes;             // 2 stages
-  uint8_t* sP = sV + 2 * kKVBytes;
+  uint8_t* sKV = sQ + kQBytes;
+  uint8_t* sP = sKV + kRing * kSlotBytes;
   PrefillBars* bars = reinterpret_cast<PrefillBars*>(sP + kPBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -94,11 +102,11 @@ __global__ void __launch_bounds__(192, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(&bars->kv_full[i], 1);
+      mbar_init(&bars->kv_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->k_full[i], 1);
-      mbar_init(&bars->k_empty[i], 1);
-      mbar_init(&bars->v_full[i], 1);
-      mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->s_empty[i], 4);
     }
@@ -109,17 +117,14 @@ __global__ void __launch_bounds__(192, 1)
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, 512);
+    tmem_alloc(&bars->tmem_base, 256);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;
-
-  const int rows_per_load = min(p.block_size, kKT);
-  const int loads_per_tile = kKT / rows_per_load;
+  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 128;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -127,30 +132,32 @@ __global__ void __launch_bounds__(192, 1)
       tma_prefetch_desc(&tmKV);
       mbar_expect_tx(&bars->q_full, kQBytes);
       for (int dh = 0; dh < kDH; ++dh)
-        tma_load_2d(sQ + dh * kHalfBytes, &tmQ, &bars->q_full, h * D + dh * 64, q_begin + q0);
+        tma_load_2d(sQ + dh * kQHalf, &tmQ, &bars->q_full, h * D + dh * 64, q_begin + q0);
       const int32_t* bt = p.block_table + (size_t)req * p.max_blocks;
       const int nblk_valid = (seq_len + p.block_size - 1) / p.block_size;
+      const int rows_per_load = min(p.block_size, kKT);
+      const int loads = kKT / rows_per_load;
       bool ok = true;
       for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
         const int tok0 = (kt0 + j) * kKT;
-        // K then V for this tile
+        int blk[8];
+        for (int l = 0; l < loads; ++l) {
+          const int bi = (tok0 + l * rows_per_load) / p.block_size;
+          int b = (bi < nblk_valid) ? bt[bi] : bt[0];
+          blk[l] = b < 0 ? 0 : b;
+        }
         for (int kv = 0; kv < 2 && ok; ++kv) {
-          uint64_t* full = kv ? &bars->v_full[st] : &bars->k_full[st];
-          uint64_t* empty = kv ? &bars->v_empty[st] : &bars->k_empty[st];
-          if (!mbar_wait(empty, ph ^ 1, p.status)) { ok = false; break; }
-          uint8_t* dst = (kv ? sV : sK) + st * kKVBytes;
-          mbar_expect_tx(full, kKVBytes);
-          for (int l = 0; l < loads_per_tile; ++l) {
-            const int tok = tok0 + l * rows_per_load;
-            int bi = tok / p.block_size;
-            const int off = tok % p.block_size;
-            int blk = (bi < nblk_valid) ? bt[bi] : bt[0];
-            const int row = (blk * 2 + kv) * p.block_size + off;
+          const int it = 2 * j + kv, sl = it % kRing;
+          const uint32_t ph = (it / kRing) & 1;
+          if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
+          uint8_t* dst = sKV + sl * kSlotBytes;
+          mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
+          for (int l = 0; l < loads; ++l) {
+            const int off = (tok0 + l * rows_per_load) % p.block_size;
+            const int row = (blk[l] * 2 + kv) * p.block_size + off;
             for (int dh = 0; dh < kDH; ++dh)
-              tma_load_3d(dst + dh * kHalfBytes + l * rows_per_load * 128, &tmKV, full, dh * 64,
-                          hkv, row);
+              tma_load_3d(dst + dh * kKVHalf + l * rows_per_load * 128, &tmKV,
+                          &bars->kv_full[sl], dh * 64, hkv, row);
           }
         }
       }
@@ -160,42 +167,40 @@ __global__ void __launch_bounds__(192, 1)
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kQT, kKT, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kQT, D, 0, 1);  // B (V) is MN-major
       bool ok = mbar_wait(&bars->q_full, 0, p.status);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       for (int j = 0; j <= ntiles && ok; ++j) {
         if (j < ntiles) {
-          const int st = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
-          if (!mbar_wait(&bars->k_full[st], ph, p.status)) { ok = false; break; }
-          if (!mbar_wait(&bars->s_empty[st], ph ^ 1, p.status)) { ok = false; break; }
+          const int it = 2 * j, sl = it % kRing, sb = j & 1;
+          if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
+          if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + st * kKVBytes);
+          const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t off = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-            umma_bf16_ss(tmem_s0 + st * 128, umma_desc_k_sw128(q_addr + off, 1024),
-                         umma_desc_k_sw128(k_addr + off, 1024), idesc_qk, kk != 0);
+            umma_bf16_ss(tmem_s0 + sb * kKT,
+                         umma_desc_k_sw128(q_addr + (kk / 4) * kQHalf + (kk % 4) * 32, 1024),
+                         umma_desc_k_sw128(k_addr + (kk / 4) * kKVHalf + (kk % 4) * 32, 1024),
+                         idesc_qk, kk != 0);
           }
-          umma_commit(&bars->k_empty[st]);
-          umma_commit(&bars->s_full[st]);
+          umma_commit(&bars->kv_empty[sl]);
+          umma_commit(&bars->s_full[sb]);
         }
         if (j >= 1) {
           const int i = j - 1;
-          const int st = i & 1;
-          const uint32_t ph = (i >> 1) & 1;
-          if (!mbar_wait(&bars->v_full[st], ph, p.status)) { ok = false; break; }
+          const int it = 2 * i + 1, sl = it % kRing;
+          if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
           if (!mbar_wait(&bars->p_full, i & 1, p.status)) { ok = false; break; }
           if (!mbar_wait(&bars->o_empty, (i & 1) ^ 1, p.status)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t p_addr = smem_u32(sP), v_addr = smem_u32(sV + st * kKVBytes);
+          const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
           for (int kk = 0; kk < kKT / 16; ++kk) {
-            const uint32_t poff = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-            // V: MN-major; 64-dim blocks are kHalfBytes apart, 8-token groups 1024 B apart,
+            // V: MN-major; 64-dim blocks are kKVHalf apart, 8-token groups 1024 B apart,
             // 16 tokens per instruction = 2048 B.
-            umma_bf16_ss(tmem_o, umma_desc_k_sw128(p_addr + poff, 1024),
-                         umma_desc_mn_sw128(v_addr + kk * 2048, kHalfBytes, 1024), idesc_pv,
-                         kk != 0);
+            umma_bf16_ss(tmem_o, umma_desc_k_sw128(p_addr + kk * 32, 1024),
+                         umma_desc_mn_sw128(v_addr + kk * 2048, kKVHalf, 1024), idesc_pv, kk != 0);
           }
-          umma_commit(&bars->v_empty[st]);
+          umma_commit(&bars->kv_empty[sl]);
           umma_commit(&bars->p_empty);
           umma_commit(&bars->o_full);
         }
@@ -208,90 +213,85 @@ __global__ void __launch_bounds__(192, 1)
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int q_pos = ctx_off + q0 + r;             // absolute position of this query row
     const int lo = (p.window > 0) ? (q_pos - p.window + 1) : 0;
-    const int hi = p.causal ? q_pos : (seq_len - 1);
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+    const int hi = min(p.causal ? q_pos : (seq_len - 1), seq_len - 1);
+    const float sc = p.scale_log2;
+    const bool cap = p.softcap2 > 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;   // m in the scaled log2 domain
     float o[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.f;
     bool ok = true;
+    uint8_t* prow = sP + r * 128;
     for (int j = 0; j < ntiles && ok; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[st], ph, p.status));
+      const int sb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (j >> 1) & 1, p.status));
       if (!ok) break;
       tc_fence_after_sync();
       const int kbase = (kt0 + j) * kKT;
-      const uint32_t s_addr = tmem_s0 + st * 128 + lane_off;
-      const bool need_mask = (kbase + kKT - 1 > hi) || (kbase < lo) || (kbase + kKT > seq_len);
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kKT / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, rr);
-        tmem_ld_wait();
+      const uint32_t s_addr = tmem_s0 + sb * kKT + lane_off;
+      const bool need_mask = (kbase + kKT - 1 > hi) || (kbase < lo);
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32b_x32(s_addr, s0);
+      tmem_ld_32x32b_x32(s_addr + 32, s1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[sb]);   // S is in registers now
+      // scaled scores (log2 domain), soft-cap, mask
+      if (cap || need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(rr[i]);
-          if (p.softcap > 0.f) s = p.softcap * tanhf(s * (p.scale_log2 * 0.6931471805599453f) / p.softcap) / (p.scale_log2 * 0.6931471805599453f);
-          const int kp = kbase + c * 32 + i;
-          if (need_mask && (kp > hi || kp < lo || kp >= seq_len)) s = -INFINITY;
-          mx = fmaxf(mx, s);
+          float a = __uint_as_float(s0[i]) * sc, b = __uint_as_float(s1[i]) * sc;
+          if (cap) {
+            a = p.softcap2 * tanhf(a / p.softcap2);
+            b = p.softcap2 * tanhf(b / p.softcap2);
+          }
+          const int ka = kbase + i, kb = kbase + 32 + i;
+          if (ka > hi || ka < lo) a = -INFINITY;
+          if (kb > hi || kb < lo) b = -INFINITY;
+          s0[i] = __float_as_uint(a);
+          s1[i] = __float_as_uint(b);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          s0[i] = __float_as_uint(__uint_as_float(s0[i]) * sc);
+          s1[i] = __float_as_uint(__uint_as_float(s1[i]) * sc);
         }
       }
-      const float m_new = fmaxf(m, mx);
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
+      }
+      const float m_new = fmaxf(m, fmaxf(mx0, mx1));
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_new == -INFINITY) ? 1.f : exp2f((m - m_new) * p.scale_log2);
+      const float alpha = (m_new == -INFINITY) ? 1.f : ex2_fast(m - m_new);
       // P buffer must be free (PV of tile j-1 finished reading it)
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty, (j & 1) ^ 1, p.status));
       if (!ok) break;
-      // pass 2: p = exp2((s - m) * scale), row sum, write bf16 P into the swizzled tile
-      float rs = 0.f;
-      const float moff = m_use * p.scale_log2;
-#pragma unroll 1
-      for (int c = 0; c < kKT / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32b_x32(s_addr + c * 32, rr);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(rr[i]), s1 = __uint_as_float(rr[i + 1]);
-          if (p.softcap > 0.f) {
-            const float sc = p.scale_log2 * 0.6931471805599453f;
-            s0 = p.softcap * tanhf(s0 * sc / p.softcap) / sc;
-            s1 = p.softcap * tanhf(s1 * sc / p.softcap) / sc;
-          }
-          const int kp = kbase + c * 32 + i;
-          float p0 = exp2f(s0 * p.scale_log2 - moff), p1 = exp2f(s1 * p.scale_log2 - moff);
-          if (need_mask) {
-            if (kp > hi || kp < lo || kp >= seq_len) p0 = 0.f;
-            if (kp + 1 > hi || kp + 1 < lo || kp + 1 >= seq_len) p1 = 0.f;
-          }
-          // Sum what the tensor core will see (bf16-rounded) so rows renormalise exactly.
-          const uint32_t pp = pack_bf16x2(p0, p1);
-          const float2 pr = unpack_bf16x2(pp);
-          rs += pr.x + pr.y;
-          pk[i >> 1] = pp;
-        }
-        // 32 columns = 4 chunks of 16 B in half-tile (c / 2), chunk ids (c & 1) * 4 + 0..3
-        uint8_t* half = sP + (c >> 1) * kHalfBytes + r * 128;
+      for (int c = 0; c < 8; ++c) {     // 8 chunks of 8 columns = 16 bytes each
+        uint32_t pk[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-          *reinterpret_cast<uint4*>(half + chunk * 16) =
-              make_uint4(pk[q * 4 + 0], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+        for (int e = 0; e < 4; ++e) {
+          const int i = (c & 3) * 8 + e * 2;
+          const float x0 = __uint_as_float(c < 4 ? s0[i] : s1[i]);
+          const float x1 = __uint_as_float(c < 4 ? s0[i + 1] : s1[i + 1]);
+          const float p0 = ex2_fast(x0 - m_use), p1 = ex2_fast(x1 - m_use);
+          rs0 += p0;
+          rs1 += p1;
+          pk[e] = pack_bf16x2(p0, p1);
         }
+        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l = l * alpha + rs;
+      l = l * alpha + (rs0 + rs1);
       m = m_new;
       fence_proxy_async_smem();
-      tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars->p_full);
-        mbar_arrive(&bars->s_empty[st]);
-      }
+      if (lane == 0) mbar_arrive(&bars->p_full);
       // deferred accumulate of PV_{j-1}
       if (j >= 1) {
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (j - 1) & 1, p.status));
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(192, 1)
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(rr[i]);
+            o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(rr[i]));
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(192, 1)
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(rr[i]);
+            o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(rr[i]));
         }
       }
     }
@@ -341,15 +341,14 @@ __global__ void __launch_bounds__(192, 1)
       }
       if (p.lse) {
         const float ln2 = 0.6931471805599453f;
-        p.lse[(size_t)(q_begin + q0 + r) * p.Hq + h] =
-            l > 0.f ? (m * p.scale_log2 + log2f(l)) * ln2 : -INFINITY;
+        p.lse[(size_t)(q_begin + q0 + r) * p.Hq + h] = l > 0.f ? (m + log2f(l)) * ln2 : -INFINITY;
       }
     }
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
 struct KvMapKey {
@@ -366,6 +365,22 @@ struct KvMapKeyHash {
            ((size_t)k.hkv << 40) ^ ((size_t)k.d << 20) ^ (size_t)k.box_rows;
   }
 };
+
+template <int D>
+static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const PrefillParams& p,
+                          dim3 grid, cudaStream_t stream) {
+  constexpr int kDH = D / 64;
+  constexpr size_t smem = (size_t)kDH * 16384 + (size_t)kRing * kDH * 8192 + 16384 + 1024 +
+                          sizeof(PrefillBars);
+  static bool set = false;
+  if (!set) {
+    cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+    set = true;
+  }
+  attn_prefill_kernel<D><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 }  // namespace b200
 
@@ -412,27 +427,10 @@ extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, voi
   p.tile_req = (const int32_t*)tile_req; p.tile_q0 = (const int32_t*)tile_q0;
   p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.softcap = softcap; p.window = window; p.causal = causal;
+  p.softcap2 = softcap * 1.4426950408889634f;
+  p.window = window; p.causal = causal;
   p.status = device_status_word();
   dim3 grid(num_tiles, Hq);
-  if (D == 128) {
-    constexpr size_t smem = (size_t)(2 + 4 * 2 + 2) * 16384 + 1024 + sizeof(PrefillBars);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem);
-      set = true;
-    }
-    attn_prefill_kernel<128><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  } else {
-    constexpr size_t smem = (size_t)(1 + 4 * 1 + 2) * 16384 + 1024 + sizeof(PrefillBars);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem);
-      set = true;
-    }
-    attn_prefill_kernel<64><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  }
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return D == 128 ? launch_prefill<128>(tmQ, tmKV, p, grid, stream)
+                  : launch_prefill<64>(tmQ, tmKV, p, grid, stream);
 }
