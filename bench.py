@@ -109,6 +109,8 @@ def main() -> int:
     ap.add_argument("--output-len", type=int, default=OUTPUT_LEN)
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--sync-scheduling", action="store_true",
+                    help="schedule step N+1 only after step N's tokens are on the host")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -140,6 +142,7 @@ def main() -> int:
         max_num_seqs=C, max_num_batched_tokens=args.max_num_batched_tokens,
         num_blocks=C * ((max_len + block - 1) // block + 1) + 64,
         enable_cuda_graphs=not args.no_graphs, enable_prefix_caching=True,
+        async_scheduling=not args.sync_scheduling,
         parallel=ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank)))
     gen = torch.Generator().manual_seed(1)
 
@@ -186,24 +189,23 @@ def main() -> int:
 
     # ---- timed region
     sampler = ClockSampler(local_rank)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-          for _ in range(args.steps)]
     h2d0, d2h0 = llm.runner.h2d_bytes, llm.runner.d2h_bytes
     launches0 = _lib.LAUNCHES[0]
     tokens = 0
     barrier()
+    llm.runner.step_events = []
+    llm.runner.time_steps = True
     sampler.start()
     t0 = time.perf_counter()
     for i in range(args.steps):
-        ev[i][0].record()
         outs = step_and_refill()
-        ev[i][1].record()
         for st in outs:
             tokens += 1  # one new token per returned request per step (no speculative decode)
     barrier()
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
-    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    dev_ms = llm.runner.device_step_ms()
+    llm.runner.time_steps = False
     launches = _lib.LAUNCHES[0] - launches0
     h2d = (llm.runner.h2d_bytes - h2d0) / args.steps
     d2h = (llm.runner.d2h_bytes - d2h0) / args.steps
@@ -229,7 +231,8 @@ def main() -> int:
                        "parallelism": f"tp{world}", "mode": "continuous batching, steady state",
                        "max_num_batched_tokens": args.max_num_batched_tokens,
                        "l2": "weights (16 GB) and KV (>40 GB) per step exceed L2 (126 MB)",
-                       "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs},
+                       "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs,
+                       "async_scheduling": not args.sync_scheduling},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "wall_ms_per_step": round(wall_ms / args.steps, 4)},

@@ -32,7 +32,11 @@ class PyModelRunner : public ModelRunnerBase {
     py::function f = py::get_override(static_cast<const ModelRunnerBase*>(this), "sample_tokens_async");
     if (!f) return ModelRunnerBase::sample_tokens_async(g);
     py::object handle = f(g);
-    auto holder = std::make_shared<py::object>(std::move(handle));
+    // The handle may be dropped on the engine thread: take the GIL for the decref.
+    std::shared_ptr<py::object> holder(new py::object(std::move(handle)), [](py::object* o) {
+      py::gil_scoped_acquire g;
+      delete o;
+    });
     return [holder]() {
       py::gil_scoped_acquire gil2;
       ModelRunnerOutput out = (*holder)().cast<ModelRunnerOutput>();

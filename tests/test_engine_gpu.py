@@ -94,3 +94,13 @@ def test_sampling_params_seeded_random_is_reproducible():
     g = [o.outputs[0].token_ids for o in llm.generate(
         p, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))]
     assert a != g  # sampling actually happened
+
+
+def test_async_scheduling_same_tokens_as_sync():
+    cfg = _cfg()
+    prompts = _prompts(cfg, (33, 200, 5, 77, 130, 18), seed=5)
+    a, _ = _run("cuda", cfg, prompts, max_tokens=20, seqs=4)
+    b, llm = _run("cuda", cfg, prompts, max_tokens=20, seqs=4, async_scheduling=True)
+    assert llm.use_async
+    assert a == b
+    assert ops.read_status() == 0

@@ -84,6 +84,8 @@ class ModelRunner(E.ModelRunnerBase):
         self.d2h_bytes = 0
         self.num_kernel_steps = 0
         self.launches = 0
+        self.time_steps = False          # record CUDA events around each step's GPU work
+        self.step_events: list = []
         if self.is_cuda:
             from .. import ops
             self.ops = ops
@@ -244,6 +246,10 @@ class ModelRunner(E.ModelRunnerBase):
             for g in range(self.num_groups):
                 hv["slot_mapping"][g][R:pad].fill_(-1)
         # one packed host->device copy per step
+        if self.time_steps and self.is_cuda:
+            e0 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.step_events.append([e0, None])
         nbytes = self.layout.total_bytes
         if self.is_cuda:
             self.dev_buf.copy_(self.host_buf, non_blocking=True)
@@ -356,6 +362,19 @@ class ModelRunner(E.ModelRunnerBase):
             row += 1
         return out
 
+    def _mark_step_end(self) -> None:
+        if self.time_steps and self.is_cuda and self.step_events and self.step_events[-1][1] is None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            self.step_events[-1][1] = e1
+
+    def device_step_ms(self) -> float:
+        """Sum of per-step device time (first copy to last sampling kernel) since the last call."""
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in self.step_events if b is not None)
+        self.step_events = []
+        return ms
+
     def _build_output(self, info, ids_host) -> "E.ModelRunnerOutput":
         out = E.ModelRunnerOutput()
         out.req_ids = list(info.req_ids)
@@ -380,6 +399,7 @@ class ModelRunner(E.ModelRunnerBase):
         if info.any_logprobs:
             self._raw_logits = self._logits.clone()
         ids = self._sample_device(info, grammar)
+        self._mark_step_end()
         if self.is_cuda:
             self.sampled_host[:n].copy_(ids[:n], non_blocking=True)
             torch.cuda.current_stream().synchronize()
@@ -402,6 +422,7 @@ class ModelRunner(E.ModelRunnerBase):
             out = self.sample_tokens(grammar)
             return lambda: out
         ids = self._sample_device(info, grammar).clone()  # the next step reuses the buffer
+        self._mark_step_end()
         rows = [i for i, p in enumerate(info.produces_token) if p]
         # scatter into the per-batch-row table read by the next step's splice kernel
         row_of = torch.tensor(rows, dtype=torch.int32, device=self.device)
