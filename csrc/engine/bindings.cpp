@@ -492,7 +492,7 @@ PYBIND11_MODULE(_engine, m) {
         d["temperature"] = l.temperature; d["top_p"] = l.top_p; d["min_p"] = l.min_p;
         d["top_k"] = l.top_k; d["seeds"] = l.seeds; d["steps"] = l.steps; d["rep_pen"] = l.rep_pen;
         d["freq_pen"] = l.freq_pen; d["pres_pen"] = l.pres_pen; d["splice_dst"] = l.splice_dst;
-        d["splice_src"] = l.splice_src;
+        d["splice_src"] = l.splice_src; d["sample_rows"] = l.sample_rows;
         return d;
       });
   py::class_<StepInfo>(m, "StepInfo")

@@ -43,6 +43,7 @@ StepLayout StepLayout::make(int max_tokens, int max_reqs, int max_blocks, int nu
   l.pres_pen = take(4ull * max_reqs);
   l.splice_dst = take(4ull * max_reqs);
   l.splice_src = take(4ull * max_reqs);
+  l.sample_rows = take(4ull * max_reqs);
   l.total_bytes = off;
   return l;
 }
@@ -152,6 +153,7 @@ StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uin
   auto* pres = reinterpret_cast<float*>(buf + L.pres_pen);
   auto* sp_dst = reinterpret_cast<int32_t*>(buf + L.splice_dst);
   auto* sp_src = reinterpret_cast<int32_t*>(buf + L.splice_src);
+  auto* sample_rows = reinterpret_cast<int32_t*>(buf + L.sample_rows);
 
   const int G = L.num_groups;
   int tok = 0;
@@ -227,6 +229,7 @@ StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uin
     const bool produces = lo + n >= (int)s.token_ids.size();
     info.produces_token.push_back(produces ? 1 : 0);
     if (produces) {
+      sample_rows[info.num_logits] = (int32_t)r;
       logits_idx[info.num_logits++] = tok - 1;
       s.sample_step += 1;
       if (sp.temperature >= kSamplingEps) {

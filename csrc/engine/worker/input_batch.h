@@ -56,6 +56,7 @@ struct StepLayout {
   size_t rep_pen = 0, freq_pen = 0, pres_pen = 0;  // f32 [max_reqs]
   size_t splice_dst = 0;      // int32 [max_reqs] async: position in input_ids to overwrite
   size_t splice_src = 0;      // int32 [max_reqs] async: row of the previous batch's sampled ids
+  size_t sample_rows = 0;     // int32 [max_reqs] batch row of each logits row (rows that sample)
   size_t total_bytes = 0;
   static StepLayout make(int max_tokens, int max_reqs, int max_blocks, int num_groups);
 };

@@ -22,6 +22,25 @@ int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* out, in
                    int out_f32, const void* bias, const void* residual, int ldr, int M, int N,
                    int K, void* workspace, size_t ws_bytes, int force_path, cudaStream_t stream);
 
+// Tensor-parallel prologue / epilogue of a GEMM (see gemm_bf16.cu and tp_fused.cu).
+typedef struct B200TpGemm {
+  int world, rank, rows_per_rank;
+  int scatter;                 // 1: epilogue scatters bf16 partial rows to their owner rank
+  int gather;                  // 1: producer waits for gathered rows before loading A
+  void* peer_recv[8];          // receive buffers [2][world][rows_per_rank][N], one per rank
+  void* peer_rs_flags[8];      // arrival counters [2][rows_per_rank / 32], one per rank
+  long long recv_parity_stride;
+  int rs_flag_parity_stride;
+  const void* a_alt;           // gather: the parity-1 copy of A (A itself is the parity-0 copy)
+  const void* ag_flags;        // local gather counters [2][groups]
+  int ag_flag_parity_stride;
+  const void* op_counter;      // local device word, bumped by b200_tp_reduce_norm_gather
+  int out_f32;                 // gather mode: fp32 output (lm_head)
+} B200TpGemm;
+
+int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
+                      int N, int K, const B200TpGemm* tp, int* expected_rs, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,7 +43,43 @@ struct GemmParams {
   int splits;
   int kb_per_split;
   float* workspace;  // [splits, M, N] fp32 partials
+  // ---- fused tensor-parallel modes (all zero when unused) -------------------------------
+  // scatter epilogue (GEMM + reduce-scatter): row m of the bf16 partial goes to the rank that
+  // owns it (m / rows_per_rank), into that rank's receive buffer slot [parity][tp_rank], and
+  // the owner's arrival counter of the 32-row group is bumped with a system-scope release.
+  int tp_world, tp_rank, rows_per_rank;
+  __nv_bfloat16* peer_recv[8];
+  uint32_t* peer_rs_flags[8];
+  long long recv_parity_stride;   // elements between the two parities of a receive buffer
+  int rs_flag_parity_stride;
+  // gather prologue (all-gather + GEMM): A is this rank's copy of the gathered activations,
+  // filled by peer stores; the producer waits until every row of a 32-row group has landed.
+  const uint32_t* ag_flags;
+  int ag_flag_parity_stride;
+  const uint32_t* op_counter;     // device-side op counter; its low bit selects the parity
 };
+
+// Bounded system-scope acquire wait on a counter another GPU increments.
+__device__ __forceinline__ bool wait_counter_ge(const uint32_t* ctr, uint32_t target, int* status) {
+  long long t0 = clock64();
+  uint32_t it = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= target) return true;
+    if (((++it) & 0xff) == 0 && clock64() - t0 > kPeerWaitCycles) {
+      if (status) atomicExch(status, (int)kErrFlagTimeout);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void signal_counter(uint32_t* ctr) {
+  asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+}
+// Peer stores (generic proxy) must be visible to this SM's TMA reads (async proxy).
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
 
 struct alignas(8) GemmBarriers {
   uint64_t full[kMaxStages];
@@ -69,6 +105,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmA,
+                        const __grid_constant__ CUtensorMap tmA_alt,
                         const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -108,13 +145,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmA);
+      // gather mode: A has one copy per parity of the op counter, pick the one just written
+      const CUtensorMap* ta = (p.ag_flags && ((*p.op_counter - 1) & 1)) ? &tmA_alt : &tmA;
+      tma_prefetch_desc(ta);
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        if (p.ag_flags) {
+          const uint32_t par = (*p.op_counter - 1) & 1;
+          for (int g = tm * 4; g < tm * 4 + 4 && ok; ++g) {
+            const int need = min(32, p.M - g * 32);
+            if (need > 0)
+              ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g, need, p.status);
+          }
+          if (!ok) break;
+          fence_proxy_async_global();
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
@@ -122,7 +171,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint8_t* a_dst = smem + (size_t)s * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
           mbar_expect_tx(&bars->full[s], kStageBytes);
-          tma_load_2d(a_dst, &tmA, &bars->full[s], kb * kBK, tm * kBM);
+          tma_load_2d(a_dst, ta, &bars->full[s], kb * kBK, tm * kBM);
           tma_load_2d(b_dst, &tmB, &bars->full[s], kb * kBK, tn * BN);
         }
       }
@@ -213,7 +262,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               }
             }
           }
-          if (p.out_f32) {
+          if (p.tp_world > 1 && p.peer_recv[0]) {
+            const int owner = row / p.rows_per_rank;
+            const uint32_t par = *p.op_counter & 1;
+            __nv_bfloat16* o = p.peer_recv[owner] + par * p.recv_parity_stride +
+                               ((size_t)p.tp_rank * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.N + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < p.N) {
+                uint4 w;
+                w.x = pack_bf16x2(v[i + 0], v[i + 1]);
+                w.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                w.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                w.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(o + i) = w;
+              }
+            }
+          } else if (p.out_f32) {
             float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
@@ -236,6 +301,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
+      if (p.tp_world > 1 && p.peer_recv[0]) {
+        // this warp's 32 rows x BN columns have been stored to their owner: publish
+        __threadfence_system();
+        __syncwarp();
+        const int row0 = tm * kBM + quarter * 32;
+        if (lane == 0 && row0 < p.M) {
+          const int owner = row0 / p.rows_per_rank;
+          const uint32_t par = *p.op_counter & 1;
+          signal_counter(p.peer_rs_flags[owner] + par * p.rs_flag_parity_stride +
+                         (row0 - owner * p.rows_per_rank) / 32);
+        }
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
@@ -254,7 +331,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_swap_kernel(const __grid_constant__ CUtensorMap tmW,
-                          const __grid_constant__ CUtensorMap tmA, GemmParams p,
+                          const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmA_alt, GemmParams p,
                           uint32_t tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -295,9 +373,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   if (warp == 0) {
     if (lane == 0) {
+      const CUtensorMap* ta = (p.ag_flags && ((*p.op_counter - 1) & 1)) ? &tmA_alt : &tmA;
       tma_prefetch_desc(&tmW);
-      tma_prefetch_desc(&tmA);
-      for (int i = 0; i < nkb; ++i) {
+      tma_prefetch_desc(ta);
+      bool ag_ok = true;
+      if (p.ag_flags) {
+        const uint32_t par = (*p.op_counter - 1) & 1;
+        for (int g = 0; g * 32 < p.M && ag_ok; ++g)
+          ag_ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g,
+                                  min(32, p.M - g * 32), p.status);
+        fence_proxy_async_global();
+      }
+      for (int i = 0; i < nkb && ag_ok; ++i) {
         int s = i % stages;
         uint32_t ph = (i / stages) & 1;
         if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { bars->failed = 1; break; }
@@ -305,7 +392,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint8_t* a_dst = w_dst + kWBytes;
         mbar_expect_tx(&bars->full[s], stage_bytes);
         tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, tn * kBM);
-        tma_load_2d(a_dst, &tmA, &bars->full[s], (kb0 + i) * kBK, 0);
+        tma_load_2d(a_dst, ta, &bars->full[s], (kb0 + i) * kBK, 0);
       }
     }
   } else if (warp == 1) {
@@ -357,6 +444,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               float v = __uint_as_float(r[i]);
               if (p.splits > 1) {
                 p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
+              } else if (p.tp_world > 1 && p.peer_recv[0]) {
+                const int owner = m / p.rows_per_rank;
+                const uint32_t par = *p.op_counter & 1;
+                p.peer_recv[owner][par * p.recv_parity_stride +
+                                   ((size_t)p.tp_rank * p.rows_per_rank + (m - owner * p.rows_per_rank)) * p.N + n] =
+                    __float2bfloat16(v);
               } else {
                 v += bias_v;
                 if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.ldr + n]);
@@ -367,6 +460,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                       __float2bfloat16(v);
               }
             }
+          }
+        }
+      }
+      if (p.tp_world > 1 && p.peer_recv[0] && p.splits == 1) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t par = *p.op_counter & 1;
+          for (int g = 0; g * 32 < p.M; ++g) {
+            const int row0 = g * 32, owner = row0 / p.rows_per_rank;
+            signal_counter(p.peer_rs_flags[owner] + par * p.rs_flag_parity_stride +
+                           (row0 - owner * p.rows_per_rank) / 32);
           }
         }
       }
@@ -464,8 +569,8 @@ static bool get_tmap_bf16(CUtensorMap* out, const void* p, uint64_t rows, uint64
 static constexpr int kSmemBudget = 220 * 1024;
 
 template <int BN>
-static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
-                     cudaStream_t stream) {
+static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
+                     GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = kBM * kBK * 2 + BN * kBK * 2;
   int stages = (kSmemBudget - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -482,7 +587,7 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams&
   }
   int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
-  gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmB, p);
+  gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmA2, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -490,15 +595,52 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams&
 
 using namespace b200;
 
+static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                          int out_f32, const void* bias, const void* residual, int ldr, int M,
+                          int N, int K, void* workspace, size_t ws_bytes, int force_path,
+                          const B200TpGemm* tp, cudaStream_t stream);
+
 extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                               int out_f32, const void* bias, const void* residual, int ldr, int M,
                               int N, int K, void* workspace, size_t ws_bytes, int force_path,
                               cudaStream_t stream) {
+  return gemm_bf16_impl(A, lda, W, ldw, out, ldo, out_f32, bias, residual, ldr, M, N, K, workspace,
+                        ws_bytes, force_path, nullptr, stream);
+}
+
+// Same GEMM with the tensor-parallel prologue / epilogue described by `tp`.
+// Returns in *expected_rs the arrival count the owner of a 32-row group must wait for.
+extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw, void* out,
+                                 int ldo, int M, int N, int K, const B200TpGemm* tp,
+                                 int* expected_rs, cudaStream_t stream) {
+  if (!tp || tp->world < 1 || tp->world > 8) return -1;
+  if (tp->scatter && (tp->rows_per_rank <= 0 || (tp->rows_per_rank & 31))) return -1;
+  const int tiles_n = (N + 127) / 128;
+  const bool swap = (M <= 256);
+  if (expected_rs) {
+    if (swap) *expected_rs = tp->world * tiles_n * 4;
+    else {
+      // the tiled path picks BN below; mirror the choice
+      const int sms = b200_num_sms();
+      int tm = (M + 127) / 128, tn256 = (N + 255) / 256, tn128 = (N + 127) / 128;
+      long w256 = ((long)tm * tn256 + sms - 1) / sms, w128 = ((long)tm * tn128 + sms - 1) / sms;
+      *expected_rs = tp->world * ((w256 * 2 * 100 <= w128 * 108) ? tn256 : tn128);
+    }
+  }
+  return gemm_bf16_impl(A, lda, W, ldw, out, ldo, tp->scatter ? 0 : tp->out_f32, nullptr, nullptr,
+                        0, M, N, K, nullptr, 0, swap ? 2 : 1, tp, stream);
+}
+
+static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                          int out_f32, const void* bias, const void* residual, int ldr, int M,
+                          int N, int K, void* workspace, size_t ws_bytes, int force_path,
+                          const B200TpGemm* tp, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
        reinterpret_cast<uintptr_t>(out)) & 15)
     return -1;
+  if (tp && tp->scatter && !out) out = const_cast<void*>(A);  // unused by the scatter epilogue
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
@@ -506,6 +648,24 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
   p.status = device_status_word();
+  if (tp) {
+    p.tp_world = tp->world;
+    p.tp_rank = tp->rank;
+    p.rows_per_rank = tp->rows_per_rank;
+    p.op_counter = reinterpret_cast<const uint32_t*>(tp->op_counter);
+    if (tp->scatter) {
+      for (int i = 0; i < tp->world; ++i) {
+        p.peer_recv[i] = reinterpret_cast<__nv_bfloat16*>(tp->peer_recv[i]);
+        p.peer_rs_flags[i] = reinterpret_cast<uint32_t*>(tp->peer_rs_flags[i]);
+      }
+      p.recv_parity_stride = tp->recv_parity_stride;
+      p.rs_flag_parity_stride = tp->rs_flag_parity_stride;
+    }
+    if (tp->gather) {
+      p.ag_flags = reinterpret_cast<const uint32_t*>(tp->ag_flags);
+      p.ag_flag_parity_stride = tp->ag_flag_parity_stride;
+    }
+  }
   const int sms = b200_num_sms();
   const int kblocks = (K + kBK - 1) / kBK;
 
@@ -518,7 +678,7 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     p.mp = mp;
     p.tiles_n = (N + kBM - 1) / kBM;
     int splits = 1;
-    if (p.tiles_n < sms) {
+    if (p.tiles_n < sms && !(tp && tp->scatter)) {
       splits = (sms + p.tiles_n - 1) / p.tiles_n;
       int max_by_k = kblocks / 4;
       if (max_by_k < 1) max_by_k = 1;
@@ -545,9 +705,11 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     p.stages = stages;
     uint32_t tmem_cols = 32;
     while ((int)tmem_cols < mp) tmem_cols <<= 1;
-    CUtensorMap tmW, tmA;
+    CUtensorMap tmW, tmA, tmA2;
     if (!get_tmap_bf16(&tmW, W, N, K, ldw, kBM, kBK)) return -3;
     if (!get_tmap_bf16(&tmA, A, M, K, lda, mp, kBK)) return -3;
+    tmA2 = tmA;
+    if (tp && tp->gather && tp->a_alt && !get_tmap_bf16(&tmA2, tp->a_alt, M, K, lda, mp, kBK)) return -3;
     static bool attr_set = false;
     if (!attr_set) {
       cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -556,7 +718,7 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
     }
     size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
     dim3 grid(p.tiles_n, splits);
-    gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, p, tmem_cols);
+    gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, tmA2, p, tmem_cols);
     if (cudaGetLastError() != cudaSuccess) return -2;
     if (splits > 1) {
       size_t total = (size_t)M * (N / 4);
@@ -576,14 +738,16 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
   bool use256 = (waves256 * 2 * 100 <= waves128 * 108);
   if (force_path == 3) use256 = false;
   if (force_path == 4) use256 = true;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmA2, tmB;
   if (!get_tmap_bf16(&tmA, A, M, K, lda, kBM, kBK)) return -3;
+  tmA2 = tmA;
+  if (tp && tp->gather && tp->a_alt && !get_tmap_bf16(&tmA2, tp->a_alt, M, K, lda, kBM, kBK)) return -3;
   if (use256) {
     p.tiles_n = tn256;
     if (!get_tmap_bf16(&tmB, W, N, K, ldw, 256, kBK)) return -3;
-    return launch_tn<256>(tmA, tmB, p, stream);
+    return launch_tn<256>(tmA, tmA2, tmB, p, stream);
   }
   p.tiles_n = tn128;
   if (!get_tmap_bf16(&tmB, W, N, K, ldw, 128, kBK)) return -3;
-  return launch_tn<128>(tmA, tmB, p, stream);
+  return launch_tn<128>(tmA, tmA2, tmB, p, stream);
 }

@@ -29,6 +29,8 @@ enum KernelError : int {
 
 // 2^31 cycles is about 1.1 s at 1.9 GHz.
 static constexpr long long kSpinLimitCycles = 1ll << 31;
+// Waits on another GPU's progress allow for host-side jitter between ranks (about 9 s).
+static constexpr long long kPeerWaitCycles = 1ll << 34;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

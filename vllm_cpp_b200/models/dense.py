@@ -228,8 +228,78 @@ class DenseModel:
         self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
 
     # ------------------------------------------------------------------ forward
+    # ------------------------------------------------------------------ fused TP forward
+    def fused_tp_supported(self) -> bool:
+        c = self.cfg
+        return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+                and not c.sandwich_norm and not c.post_norm and not c.attention_bias
+                and c.residual_multiplier == 1.0 and c.hidden_size % 8 == 0)
+
+    def enable_fused_tp(self, max_tokens: int) -> None:
+        from ..parallel.tp_fused import TpFusedContext
+        self.tpf = TpFusedContext(self.comm, self.device, self.cfg.hidden_size, max_tokens)
+
+    def _forward_tp_fused(self, ctx: StepContext) -> torch.Tensor:
+        """Sequence-parallel forward: every o_proj / down_proj is GEMM + reduce-scatter (scatter
+        epilogue), followed by reduce + residual + RMSNorm + all-gather on the row shard, and
+        every qkv / gate_up GEMM waits for its gathered rows tile by tile."""
+        c, be, T, tpf = self.cfg, self.be, ctx.num_tokens, self.tpf
+        H, eps = c.hidden_size, c.rms_norm_eps
+        act_kind = ACT_KIND.get(c.hidden_act, 0)
+        hidden = self.bufs.get("hidden", T, H)
+        qkv = self.bufs.get("qkv", T, (self.hq + 2 * self.hkv) * self.D)
+        attn = self.bufs.get("attn", T, self.hq * self.D)
+        gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
+        act = self.bufs.get("act", T, self.inter)
+        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                     vocab_total=c.vocab_size, scale=c.embed_scale)
+        self.comm.all_reduce(hidden)
+        tpf.first_norm(hidden, self.layers[0]["ln1"], eps, c.gemma_norm)
+        pos = ctx.positions[:T]
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            grp = self.layer_group[l]
+            window = c.sliding_window if (c.sliding_window and (
+                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            tpf.gemm_gather(T, L["qkv"], qkv)
+            be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                       head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
+                       q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=eps,
+                       gemma=c.gemma_norm, slot_mapping=ctx.slot_mapping[grp][:T],
+                       kv_cache=self.kv_caches[l], block_size=self.block_size)
+            be.attention(qkv[:, : self.hq * self.D], self.kv_caches[l], ctx, grp,
+                         num_q_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.D,
+                         block_size=self.block_size, scale=self.scale, out=attn,
+                         softcap=c.attn_logit_softcap, window=window)
+            exp = tpf.gemm_scatter(attn, L["o"])
+            tpf.reduce_norm_gather(T, exp, L["ln2"], eps, c.gemma_norm)
+            tpf.gemm_gather(T, L["gate_up"], gate_up)
+            be.act_and_mul(gate_up, act_kind, out=act)
+            exp = tpf.gemm_scatter(act, L["down"])
+            nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
+            tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)
+        if ctx.decode_only_full_logits:
+            n = T
+            logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
+            tpf.gemm_gather(T, self.w["lm_head"], logits)
+        else:
+            n = ctx.num_logits
+            last = tpf.gather_rows(T, ctx.logits_indices[:n], self.bufs.get("last", n, H))
+            logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
+            be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
+        logits = self.comm.all_gather(logits, dim=-1)
+        if logits.shape[1] != c.vocab_size:
+            logits = logits[:, : c.vocab_size]
+        if c.logits_scaling != 1.0:
+            logits = logits / c.logits_scaling
+        if c.final_logit_softcap > 0:
+            logits = c.final_logit_softcap * torch.tanh(logits / c.final_logit_softcap)
+        return logits
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Returns fp32 logits ``[num_logits, vocab]`` for the rows in ``ctx.logits_indices``."""
+        if getattr(self, "tpf", None) is not None:
+            return self._forward_tp_fused(ctx)
         c, be, T = self.cfg, self.be, ctx.num_tokens
         H = c.hidden_size
         eps = c.rms_norm_eps

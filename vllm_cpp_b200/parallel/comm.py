@@ -36,6 +36,9 @@ class SingleComm:
     def broadcast_object(self, obj, src: int = 0):
         return obj
 
+    def all_gather_object(self, obj) -> list:
+        return [obj]
+
     def barrier(self) -> None:
         pass
 
@@ -76,6 +79,11 @@ class TorchComm:
         box = [obj]
         self.dist.broadcast_object_list(box, src=src, group=self.group)
         return box[0]
+
+    def all_gather_object(self, obj) -> list:
+        outs = [None] * self.world
+        self.dist.all_gather_object(outs, obj, group=self.group)
+        return outs
 
     def barrier(self):
         self.dist.barrier(group=self.group)
@@ -140,6 +148,9 @@ class FakeComm:
     def broadcast_object(self, obj, src=0):
         vals = self._exchange(obj)
         return vals[src]
+
+    def all_gather_object(self, obj) -> list:
+        return self._exchange(obj)
 
     def barrier(self):
         self._sync()

@@ -1,0 +1,211 @@
+"""Multi-GPU self-test of the tensor-parallel paths, one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29533 -m vllm_cpp_b200.parallel.selftest [--bench]
+
+Checks, against plain fp32 PyTorch + NCCL on the same data:
+  1. fused primitives: GEMM + reduce-scatter (scatter epilogue), reduce + residual + RMSNorm +
+     all-gather, all-gather + GEMM (gather prologue), for decode-sized and prefill-sized T;
+  2. the engine end to end: greedy tokens of TP=N fused vs TP=N NCCL mode vs TP=1.
+With ``--bench`` it also times one fused block against the GEMM + NCCL baseline (CUDA events,
+max over ranks). Rank 0 prints one JSON line; a non-zero exit code means a check failed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def check_primitives(comm, device, results):
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.ops import reference as ref
+    from vllm_cpp_b200.parallel.tp_fused import TpFusedContext
+    W, r = comm.world, comm.rank
+    H, Kfull, N2 = 1024, 2048, 1536
+    tpf = TpFusedContext(comm, device, H, 1024)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    worst = 0.0
+    for T in (8, 200, 700):
+        a_full = (torch.randn(T, Kfull, generator=g) * 0.5).to(torch.bfloat16).to(device)
+        w_full = (torch.randn(H, Kfull, generator=g) * 0.05).to(torch.bfloat16).to(device)
+        w2 = (torch.randn(N2, H, generator=g) * 0.05).to(torch.bfloat16).to(device)
+        hidden = (torch.randn(T, H, generator=g)).to(torch.bfloat16).to(device)
+        nw0 = (torch.rand(H, generator=g) + 0.5).to(torch.bfloat16).to(device)
+        nw1 = (torch.rand(H, generator=g) + 0.5).to(torch.bfloat16).to(device)
+        ks = Kfull // W
+        a = a_full[:, r * ks:(r + 1) * ks].contiguous()
+        w = w_full[:, r * ks:(r + 1) * ks].contiguous()
+        for rep in range(3):   # repeated use exercises the parity double-buffering
+            tpf.first_norm(hidden, nw0, 1e-6, False)
+            out0 = torch.empty(T, N2, dtype=torch.bfloat16, device=device)
+            tpf.gemm_gather(T, w2, out0)
+            exp0 = ref.gemm(ref.rmsnorm(hidden, nw0, 1e-6)[0], w2)
+            e0 = _rel(out0, exp0)
+            exp_rs = tpf.gemm_scatter(a, w)
+            tpf.reduce_norm_gather(T, exp_rs, nw1, 1e-6, False)
+            out1 = torch.empty(T, N2, dtype=torch.bfloat16, device=device)
+            tpf.gemm_gather(T, w2, out1)
+            # reference: full-K product (what the sum of the partials equals), + residual
+            full = ref.gemm(a_full, w_full, out_dtype=torch.float32)
+            res = (full + hidden.float()).to(torch.bfloat16)
+            exp1 = ref.gemm(ref.rmsnorm(res, nw1, 1e-6)[0], w2)
+            e1 = _rel(out1, exp1)
+            worst = max(worst, e0, e1)
+        torch.cuda.synchronize()
+    status = ops.read_status()
+    results["primitives_max_rel_err"] = worst
+    results["primitives_status"] = status
+    ok = worst < 2e-2 and status == 0
+    tpf.close()
+    return ok
+
+
+def check_engine(comm, device, results, local_rank):
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.config import EngineArgs, ParallelConfig, synthetic_config
+    from vllm_cpp_b200.engine import LLM, SamplingParams
+    cfg = synthetic_config("tiny-qwen3")
+    cfg.head_dim = 128
+    cfg.num_heads, cfg.num_kv_heads = 8, 8
+    cfg.hidden_size, cfg.intermediate_size, cfg.num_layers = 512, 1024, 3
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 9, 300, 40)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+
+    def run(tp, fused):
+        par = ParallelConfig(tensor_parallel_size=tp, rank=comm.rank if tp > 1 else 0,
+                             local_rank=local_rank, fused_collectives=fused)
+        llm = LLM(EngineArgs(model_config=cfg, device="cuda", block_size=16, num_blocks=200,
+                             max_model_len=640, max_num_seqs=4, max_num_batched_tokens=256,
+                             parallel=par))
+        toks = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        if getattr(llm.model, "tpf", None) is not None:
+            torch.cuda.synchronize()
+            comm.barrier()
+            llm.model.tpf.close()
+        return toks
+
+    base = run(1, False)
+    nccl = run(comm.world, False)
+    fused = run(comm.world, True)
+
+    def agree(a, b):
+        hit = tot = 0
+        for x, y in zip(a, b):
+            n = 0
+            for p, q in zip(x, y):
+                if p != q:
+                    break
+                n += 1
+            hit += n
+            tot += len(x)
+        return hit / tot
+
+    results["engine_first_tokens_equal"] = [x[0] for x in fused] == [x[0] for x in base]
+    results["engine_agree_fused_vs_tp1"] = agree(fused, base)
+    results["engine_agree_nccl_vs_tp1"] = agree(nccl, base)
+    results["engine_agree_fused_vs_nccl"] = agree(fused, nccl)
+    results["engine_status"] = ops.read_status()
+    # every rank must hold the same tokens
+    same = comm.all_gather_object(fused)
+    results["engine_ranks_identical"] = all(s == same[0] for s in same)
+    return (results["engine_first_tokens_equal"] and results["engine_agree_fused_vs_tp1"] > 0.7
+            and results["engine_ranks_identical"] and results["engine_status"] == 0)
+
+
+def bench_block(comm, device, results):
+    """One transformer block's communication-bound half at Llama-8B width, fused vs NCCL."""
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.parallel.tp_fused import TpFusedContext
+    W, r = comm.world, comm.rank
+    H, I = 4096, 14336
+    rows = []
+    for T in (256, 2048, 8192):
+        tpf = TpFusedContext(comm, device, H, T)
+        a = torch.randn(T, I // W, device=device, dtype=torch.bfloat16)
+        w_down = torch.randn(H, I // W, device=device, dtype=torch.bfloat16) * 0.02
+        w_gu = torch.randn(2 * I // W, H, device=device, dtype=torch.bfloat16) * 0.02
+        nw = torch.ones(H, device=device, dtype=torch.bfloat16)
+        hidden = torch.randn(T, H, device=device, dtype=torch.bfloat16)
+        out = torch.empty(T, 2 * I // W, device=device, dtype=torch.bfloat16)
+        resid = torch.zeros(T, H, device=device, dtype=torch.bfloat16)
+        tmp = torch.empty(T, H, device=device, dtype=torch.bfloat16)
+        tpf.first_norm(hidden, nw, 1e-6, False)
+
+        def fused():
+            e = tpf.gemm_scatter(a, w_down)
+            tpf.reduce_norm_gather(T, e, nw, 1e-6, False)
+            tpf.gemm_gather(T, w_gu, out)
+
+        def nccl():
+            ops.gemm(a, w_down, out=tmp)
+            dist.all_reduce(tmp)
+            x = ops.rmsnorm(tmp, nw, 1e-6, residual=resid)
+            ops.gemm(x, w_gu, out=out)
+
+        def timeit(fn):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(10):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([s.elapsed_time(e) / 10], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+
+        tf, tn = timeit(fused), timeit(nccl)
+        flops = 2.0 * T * (I // W) * H + 2.0 * T * H * (2 * I // W)
+        nv_bytes = 2.0 * T * H * 2 * (W - 1) / W          # scatter out + gather in, per rank
+        roof_ms = max(flops / 1393e12, nv_bytes / 770e9) * 1e3
+        rows.append(dict(T=T, fused_ms=tf, nccl_ms=tn, speedup=tn / tf, roofline_ms=roof_ms,
+                         frac_of_roofline=roof_ms / tf))
+        torch.cuda.synchronize()
+        comm.barrier()
+        tpf.close()
+    results["block_bench"] = rows
+    results["block_bench_status"] = ops.read_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--skip-engine", action="store_true")
+    args = ap.parse_args()
+    rank, local_rank = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+    from vllm_cpp_b200.parallel.comm import TorchComm
+    comm = TorchComm()
+    results = {"world": comm.world}
+    ok = check_primitives(comm, device, results)
+    if not args.skip_engine:
+        ok = check_engine(comm, device, results, local_rank) and ok
+    if args.bench:
+        bench_block(comm, device, results)
+    flag = torch.tensor([1 if ok else 0], device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    results["ok"] = bool(flag.item())
+    if rank == 0:
+        print(json.dumps(results))
+    dist.destroy_process_group()
+    return 0 if results["ok"] else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

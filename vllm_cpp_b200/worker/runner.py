@@ -26,7 +26,8 @@ _DT = {"input_ids": (torch.int64, 8), "positions": (torch.int64, 8), "slot_mappi
        "temperature": (torch.float32, 4), "top_p": (torch.float32, 4), "min_p": (torch.float32, 4),
        "top_k": (torch.int32, 4), "seeds": (torch.int64, 8), "steps": (torch.int64, 8),
        "rep_pen": (torch.float32, 4), "freq_pen": (torch.float32, 4), "pres_pen": (torch.float32, 4),
-       "splice_dst": (torch.int32, 4), "splice_src": (torch.int32, 4)}
+       "splice_dst": (torch.int32, 4), "splice_src": (torch.int32, 4),
+       "sample_rows": (torch.int32, 4)}
 
 
 def decode_graph_sizes(max_num_seqs: int) -> list[int]:
@@ -62,14 +63,22 @@ class ModelRunner(E.ModelRunnerBase):
                                         self.num_groups)
         self.off = self.layout.offsets()
         nbytes = self.layout.total_bytes
-        self.host_buf = torch.zeros(nbytes, dtype=torch.uint8, pin_memory=self.is_cuda)
+        # two pinned staging buffers: with a step in flight its copy may not have run yet when
+        # the next step is prepared
+        self.host_bufs = [torch.zeros(nbytes, dtype=torch.uint8, pin_memory=self.is_cuda)
+                          for _ in range(2 if async_mode else 1)]
+        self.host_buf = self.host_bufs[0]
+        self._step_no = 0
         self.dev_buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         self.batch = E.InputBatch(max_num_seqs, max_model_len, self.max_tokens,
                                   [g[1]["block_size"] for g in self.groups])
         model.alloc_kv_cache(num_blocks, block_size)
         model.reserve_buffers(self.max_tokens, max_num_seqs)
+        if getattr(model, "fused_tp_supported", None) and model.fused_tp_supported():
+            model.enable_fused_tp(self.max_tokens)
         self.views = self._make_views(self.dev_buf)
-        self.host_views = self._make_views(self.host_buf)
+        self.host_views_all = [self._make_views(b) for b in self.host_bufs]
+        self.host_views = self.host_views_all[0]
         self.sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
         self.sampled_host = torch.zeros(max_num_seqs, dtype=torch.int64,
                                         pin_memory=self.is_cuda)
@@ -118,7 +127,7 @@ class ModelRunner(E.ModelRunnerBase):
         v["prefill_q_start"] = view("prefill_q_start", R + 1)
         v["state_slots"] = view("state_slots", R)
         for k in ("temperature", "top_p", "min_p", "top_k", "seeds", "steps", "rep_pen", "freq_pen",
-                  "pres_pen", "splice_dst", "splice_src"):
+                  "pres_pen", "splice_dst", "splice_src", "sample_rows"):
             v[k] = view(k, R)
         return v
 
@@ -232,6 +241,9 @@ class ModelRunner(E.ModelRunnerBase):
         if so.total_num_scheduled_tokens == 0:
             self._info = None
             return
+        self._step_no += 1
+        k = self._step_no % len(self.host_bufs)
+        self.host_buf, self.host_views = self.host_bufs[k], self.host_views_all[k]
         info = self.batch.prepare(so, self.layout, self.host_buf.data_ptr(), self.async_mode)
         self._info = info
         R, T = info.num_reqs, info.num_tokens
@@ -423,9 +435,8 @@ class ModelRunner(E.ModelRunnerBase):
             return lambda: out
         ids = self._sample_device(info, grammar).clone()  # the next step reuses the buffer
         self._mark_step_end()
-        rows = [i for i, p in enumerate(info.produces_token) if p]
         # scatter into the per-batch-row table read by the next step's splice kernel
-        row_of = torch.tensor(rows, dtype=torch.int32, device=self.device)
+        row_of = self.views["sample_rows"]
         from ..ops import _lib
         _lib.check(_lib.lib().b200_scatter_sampled(self.last_sampled.data_ptr(), row_of.data_ptr(),
                                                    ids.data_ptr(), n, _lib.stream_ptr()), "scatter")
