@@ -236,6 +236,12 @@ class TpFusedContext:
               "tp_gather_rows")
         return out
 
+    def gather_all(self, T: int, out: torch.Tensor) -> torch.Tensor:
+        """Local copy of all ``T`` gathered rows (waits for every group to arrive)."""
+        if not hasattr(self, "_arange") or self._arange.numel() < T:
+            self._arange = torch.arange(self.max_tokens, dtype=torch.int32, device=self.device)
+        return self.gather_rows(T, self._arange[:T], out)
+
     def close(self):
         for b in (self.recv, self.x_full, self.flags):
             b.close()
