@@ -94,7 +94,7 @@ def build_engine(verbose: bool = False) -> Path:
     if jobs or not out.exists():
         _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
     capi = PKG / "libvllm_b200.so"
-    capi_objs = [o for o in objs if not o.name.startswith("bindings")]
+    capi_objs = [o for o in objs if "bindings" not in o.name]
     if capi_objs and (jobs or not capi.exists()):
         _run([CXX, "-shared", "-o", str(capi), *map(str, capi_objs), "-pthread", "-ldl",
               f"-Wl,--version-script={CSRC / 'engine' / 'capi' / 'export.map'}"]
