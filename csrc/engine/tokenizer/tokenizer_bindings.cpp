@@ -22,6 +22,7 @@ void bind_tokenizer(py::module_& m) {
     return out;
   });
   m.def("family_from_pattern", &family_from_pattern);
+  m.def("byte_to_codepoint", [](int b) { return byte_to_codepoint((uint8_t)b); });
 
   py::class_<Tokenizer, std::shared_ptr<Tokenizer>>(m, "Tokenizer")
       .def_static("from_hf_json", [](const std::string& tj, const std::string& cj) {
