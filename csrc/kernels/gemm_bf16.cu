@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const int owner = row / p.rows_per_rank;
             const uint32_t par = *p.op_counter & 1;
             __nv_bfloat16* o = p.peer_recv[owner] + par * p.recv_parity_stride +
-                               ((size_t)p.tp_rank * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.N + col0;
+                               ((size_t)p.tp_rank * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.N + col0;  // one slot per rank
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               if (col0 + i < p.N) {
@@ -442,14 +442,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             int m = c * 16 + i;
             if (m < p.M) {
               float v = __uint_as_float(r[i]);
-              if (p.splits > 1) {
-                p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
-              } else if (p.tp_world > 1 && p.peer_recv[0]) {
+              if (p.tp_world > 1 && p.peer_recv[0]) {
+                // (rank, k-split) is one virtual source slot of the owner's receive buffer
                 const int owner = m / p.rows_per_rank;
                 const uint32_t par = *p.op_counter & 1;
                 p.peer_recv[owner][par * p.recv_parity_stride +
-                                   ((size_t)p.tp_rank * p.rows_per_rank + (m - owner * p.rows_per_rank)) * p.N + n] =
-                    __float2bfloat16(v);
+                                   ((size_t)(p.tp_rank * p.splits + split) * p.rows_per_rank +
+                                    (m - owner * p.rows_per_rank)) * p.N + n] = __float2bfloat16(v);
+              } else if (p.splits > 1) {
+                p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
               } else {
                 v += bias_v;
                 if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.ldr + n]);
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       }
-      if (p.tp_world > 1 && p.peer_recv[0] && p.splits == 1) {
+      if (p.tp_world > 1 && p.peer_recv[0]) {
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
@@ -618,7 +619,13 @@ extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw,
   const int tiles_n = (N + 127) / 128;
   const bool swap = (M <= 256);
   if (expected_rs) {
-    if (swap) *expected_rs = tp->world * tiles_n * 4;
+    if (swap) {
+      const int kblocks = (K + kBK - 1) / kBK;
+      int s = tp->scatter_splits > 0 ? tp->scatter_splits : 1;
+      const int kb_per = (kblocks + s - 1) / s;
+      s = (kblocks + kb_per - 1) / kb_per;      // the launcher's effective split count
+      *expected_rs = tp->world * tiles_n * 4 * s;
+    }
     else {
       // the tiled path picks BN below; mirror the choice
       const int sms = b200_num_sms();
@@ -685,7 +692,8 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
       if (splits > max_by_k) splits = max_by_k;
       if (splits > 16) splits = 16;
     }
-    if (splits > 1) {
+    if (tp && tp->scatter) splits = tp->scatter_splits > 0 ? tp->scatter_splits : 1;
+    if (splits > 1 && !(tp && tp->scatter)) {
       size_t need = (size_t)splits * M * N * sizeof(float);
       while (splits > 1 && (workspace == nullptr || need > ws_bytes)) {
         --splits;
@@ -720,7 +728,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     dim3 grid(p.tiles_n, splits);
     gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, tmA2, p, tmem_cols);
     if (cudaGetLastError() != cudaSuccess) return -2;
-    if (splits > 1) {
+    if (splits > 1 && !(tp && tp->scatter)) {
       size_t total = (size_t)M * (N / 4);
       int blocks = (int)((total + 255) / 256);
       if (blocks > sms * 8) blocks = sms * 8;

@@ -32,6 +32,7 @@ struct ReduceNormParams {
   uint32_t* rs_flags;                 // local [2][rows_per_rank / 32]
   int rs_flag_parity_stride;
   int expected_rs;
+  int nsrc;                           // source slots to sum (world x k-splits of the scatter GEMM)
   __nv_bfloat16* residual;            // local shard [rows_per_rank][H], updated in place (may be null)
   const __nv_bfloat16* norm_w;        // [H]
   float eps;
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(ReduceNormPa
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int s = 0; s < p.world; ++s) {   // fixed rank order => same bits on every run
+      for (int s = 0; s < p.nsrc; ++s) {    // fixed slot order => same bits on every run
         const uint4 v = *reinterpret_cast<const uint4*>(base + s * src_stride + i * 8);
         float2 f;
         f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
@@ -267,6 +268,7 @@ typedef struct B200TpReduce {
   void* rs_flags;
   int rs_flag_parity_stride;
   int expected_rs;
+  int nsrc;
   void* residual;
   const void* norm_w;
   float eps;
@@ -288,6 +290,7 @@ int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream) {
   p.recv = (const __nv_bfloat16*)a->recv; p.recv_parity_stride = a->recv_parity_stride;
   p.rs_flags = (uint32_t*)a->rs_flags; p.rs_flag_parity_stride = a->rs_flag_parity_stride;
   p.expected_rs = a->expected_rs;
+  p.nsrc = a->nsrc > 0 ? a->nsrc : a->world;
   p.residual = (__nv_bfloat16*)a->residual; p.norm_w = (const __nv_bfloat16*)a->norm_w;
   p.eps = a->eps; p.gemma = a->gemma;
   for (int i = 0; i < a->world; ++i) {

@@ -306,7 +306,7 @@ class MoeModel(DenseModel):
             self._moe_block(normed, L, T, scatter=sc)
             nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
             # every source rank delivers 32 arrivals per 32-row group (see moe_combine_kernel)
-            tpf.reduce_norm_gather(T, tpf.world * 32, nw, eps, False)
+            tpf.reduce_norm_gather(T, tpf.world * 32, nw, eps, False, nsrc=tpf.world)
         if ctx.decode_only_full_logits:
             n = T
             logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)

@@ -35,6 +35,7 @@ def check_primitives(comm, device, results):
     tpf = TpFusedContext(comm, device, H, 1024)
     g = torch.Generator(device="cpu").manual_seed(7)
     worst = 0.0
+    sync_token = torch.zeros(1, device=device)
     for T in (8, 200, 700):
         a_full = (torch.randn(T, Kfull, generator=g) * 0.5).to(torch.bfloat16).to(device)
         w_full = (torch.randn(H, Kfull, generator=g) * 0.05).to(torch.bfloat16).to(device)
@@ -46,6 +47,9 @@ def check_primitives(comm, device, results):
         a = a_full[:, r * ks:(r + 1) * ks].contiguous()
         w = w_full[:, r * ks:(r + 1) * ks].contiguous()
         for rep in range(3):   # repeated use exercises the parity double-buffering
+            # first_norm is local: like the model (embedding all-reduce) it must follow a
+            # collective so that no rank starts a new pass while a peer still reads the last one
+            dist.all_reduce(sync_token)
             tpf.first_norm(hidden, nw0, 1e-6, False)
             out0 = torch.empty(T, N2, dtype=torch.bfloat16, device=device)
             tpf.gemm_gather(T, w2, out0)

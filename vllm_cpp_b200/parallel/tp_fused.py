@@ -32,7 +32,8 @@ class B200TpGemm(ctypes.Structure):
                 ("recv_parity_stride", ctypes.c_longlong), ("rs_flag_parity_stride", ctypes.c_int),
                 ("a_alt", ctypes.c_void_p),
                 ("ag_flags", ctypes.c_void_p), ("ag_flag_parity_stride", ctypes.c_int),
-                ("op_counter", ctypes.c_void_p), ("out_f32", ctypes.c_int)]
+                ("op_counter", ctypes.c_void_p), ("out_f32", ctypes.c_int),
+                ("scatter_splits", ctypes.c_int)]
 
 
 class B200TpReduce(ctypes.Structure):
@@ -40,6 +41,7 @@ class B200TpReduce(ctypes.Structure):
                 ("M", ctypes.c_int), ("H", ctypes.c_int), ("recv", ctypes.c_void_p),
                 ("recv_parity_stride", ctypes.c_longlong), ("rs_flags", ctypes.c_void_p),
                 ("rs_flag_parity_stride", ctypes.c_int), ("expected_rs", ctypes.c_int),
+                ("nsrc", ctypes.c_int),
                 ("residual", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
                 ("eps", ctypes.c_float), ("gemma", ctypes.c_int),
                 ("peer_x", ctypes.c_void_p * 8), ("x_parity_stride", ctypes.c_longlong),
@@ -183,6 +185,18 @@ class TpFusedContext:
         d.recv_parity_stride = self.recv_parity
         d.rs_flag_parity_stride = self.rs_groups
         d.op_counter = self._op_counter()
+        # small batches: split K so that more than N/128 CTAs stream the weight shard; every
+        # (rank, split) pair owns a source slot in the receive buffer
+        splits = 1
+        if T <= 256:
+            tiles_n = -(-N // 128)
+            kblocks = -(-K // 64)
+            splits = max(1, min(-(-_lib.lib().b200_num_sms() // tiles_n), kblocks // 4,
+                                self.rpr_max // d.rows_per_rank, 8))
+            kb_per = -(-kblocks // splits)
+            splits = -(-kblocks // kb_per)
+        d.scatter_splits = splits
+        self._last_nsrc = self.world * splits
         exp = ctypes.c_int(0)
         check(lib().b200_gemm_bf16_tp(ptr(a), a.stride(0), ptr(w), w.stride(0), None, N, T, N, K,
                                       ctypes.byref(d), ctypes.byref(exp), stream_ptr()),
@@ -190,7 +204,7 @@ class TpFusedContext:
         return exp.value
 
     def reduce_norm_gather(self, T: int, expected_rs: int, weight: torch.Tensor, eps: float,
-                           gemma: bool, use_residual: bool = True):
+                           gemma: bool, use_residual: bool = True, nsrc: int = 0):
         a = B200TpReduce()
         a.world, a.rank, a.rows_per_rank, a.M, a.H = (self.world, self.rank, self.rows_per_rank(T),
                                                       T, self.H)
@@ -199,6 +213,7 @@ class TpFusedContext:
         a.rs_flags = self._rs_flags(self.rank)
         a.rs_flag_parity_stride = self.rs_groups
         a.expected_rs = expected_rs
+        a.nsrc = nsrc if nsrc else getattr(self, "_last_nsrc", self.world)
         a.residual = ptr(self.residual) if use_residual else None
         a.norm_w = ptr(weight)
         a.eps, a.gemma = eps, int(gemma)
