@@ -42,6 +42,27 @@ typedef struct B200TpGemm {
 int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
                       int N, int K, const B200TpGemm* tp, int* expected_rs, cudaStream_t stream);
 
+// ---- small-M GEMM that allocates nothing ------------------------------------------------
+// This entry point has no counterpart in the reference project. It exists for callers that
+// need a decode-sized GEMM (M <= 256) but may not allocate at that point: a plug-in inside
+// another runtime's callback, a thread kept away from the framework's caching allocator, a
+// plain C host without torch. out[M,N] (bf16, row stride ldo) = A[M,K] * W[N,K]^T, the same
+// split-K kernels as b200_gemm_bf16, with the fp32 partial sums kept in an array that is part
+// of the module image (B200_GEMM_STATIC_SCRATCH_BYTES per device) instead of a workspace.
+//   * All calls on a device share that array: calls that can overlap in time race. Serialise.
+//   * Nothing in the array needs clearing between calls.
+//   * The first call on a device resolves the array's address (cudaGetSymbolAddress) and sets
+//     a kernel attribute; make it before any stream capture on that device.
+//   * Refused with -4 when M > 256 or 2*M*N*4 bytes exceed the array; -1 for misaligned
+//     arguments; b200_gemm_bf16_smallm_static_error() names the reason (thread-local).
+//   * b200_gemm_bf16_smallm_static_status() copies out this path's own sticky error word
+//     (non-zero after a bounded wait inside the kernel ran out); it synchronises the device.
+#define B200_GEMM_STATIC_SCRATCH_BYTES (8u << 20)
+int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* W, int ldw, void* out,
+                                 int ldo, int M, int N, int K, cudaStream_t stream);
+const char* b200_gemm_bf16_smallm_static_error(void);
+int b200_gemm_bf16_smallm_static_status(int* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -759,3 +759,148 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   if (!get_tmap_bf16(&tmB, W, N, K, ldw, 128, kBK)) return -3;
   return launch_tn<128>(tmA, tmA2, tmB, p, stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// b200_gemm_bf16_smallm_static: the small-M split-K GEMM for callers that cannot allocate.
+//
+// Some hosts of this library own no allocator they may call at the point where they need a
+// GEMM: a plug-in running inside another runtime's callback, a thread that must not touch the
+// framework's caching allocator, a C program that links the kernels without torch. The regular
+// entry point asks such a caller for a workspace pointer; this one brings its own. The split-K
+// partial sums live in a fixed array that is part of the loaded module image, and the sticky
+// error word that the kernels' bounded waits report into is a second such symbol. No device or
+// host memory is requested here or in anything this function calls: tensor maps are encoded
+// on the stack and nothing is cached.
+//
+// Consequences a caller has to know:
+//   * The array is one per device and every call on that device uses it, on whatever stream.
+//     Two calls whose execution can overlap (different streams, or different host threads
+//     feeding different streams) race on the partial sums. Serialise them.
+//   * Nothing in the array has to start at zero: each split overwrites its whole M x N slab
+//     before the reduction reads it. The error word starts at zero when the module loads and
+//     is never cleared by a call, so one timeout stays visible.
+//   * The first call on a device looks up the two symbol addresses and raises the kernel's
+//     shared-memory limit. That may make the CUDA runtime load the module. Make that first
+//     call ahead of any stream capture on the device.
+//   * Shapes whose two-way split does not fit the array are refused (-4), never shrunk to a
+//     slower unsplit run behind the caller's back.
+// ---------------------------------------------------------------------------------------
+namespace b200 {
+static __device__ __align__(256) float g_static_splitk_scratch[B200_GEMM_STATIC_SCRATCH_BYTES / 4];
+static __device__ int g_static_status_word;
+
+struct StaticGemmDevice {
+  float* scratch = nullptr;
+  int* status = nullptr;
+  bool ready = false;
+};
+static StaticGemmDevice g_static_dev[64];
+static std::mutex g_static_mu;
+static thread_local const char* g_static_err = "";
+}  // namespace b200
+
+extern "C" const char* b200_gemm_bf16_smallm_static_error(void) { return b200::g_static_err; }
+
+extern "C" int b200_gemm_bf16_smallm_static_status(int* out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !out) return -1;
+  if (!g_static_dev[dev].ready) { *out = 0; return 0; }
+  return cudaMemcpy(out, g_static_dev[dev].status, sizeof(int), cudaMemcpyDeviceToHost) ==
+                 cudaSuccess ? 0 : -2;
+}
+
+extern "C" int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* W, int ldw,
+                                            void* out, int ldo, int M, int N, int K,
+                                            cudaStream_t stream) {
+  g_static_err = "";
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 256) { g_static_err = "M > 256: use b200_gemm_bf16 with a caller-owned workspace"; return -4; }
+  if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) ||
+      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
+        reinterpret_cast<uintptr_t>(out)) & 15)) {
+    g_static_err = "K, N and the leading dimensions must be multiples of 8; pointers 16-byte aligned";
+    return -1;
+  }
+  const size_t slab = (size_t)M * N * sizeof(float);
+  if (2 * slab > (size_t)B200_GEMM_STATIC_SCRATCH_BYTES) {
+    g_static_err = "2 * M * N * 4 bytes exceeds B200_GEMM_STATIC_SCRATCH_BYTES";
+    return -4;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { g_static_err = "no current device"; return -2; }
+  StaticGemmDevice sd;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticGemmDevice& d = g_static_dev[dev];
+    if (!d.ready) {
+      void* ps = nullptr;
+      void* pw = nullptr;
+      if (cudaGetSymbolAddress(&ps, g_static_splitk_scratch) != cudaSuccess ||
+          cudaGetSymbolAddress(&pw, g_static_status_word) != cudaSuccess || !ps || !pw) {
+        g_static_err = "cudaGetSymbolAddress failed for the static scratch";
+        return -2;
+      }
+      if (cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSmemBudget + 4096) != cudaSuccess) {
+        g_static_err = "cannot raise the kernel's shared-memory limit";
+        return -2;
+      }
+      d.scratch = reinterpret_cast<float*>(ps);
+      d.status = reinterpret_cast<int*>(pw);
+      d.ready = true;
+    }
+    sd = d;
+  }
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_f32 = 0;
+  p.status = sd.status;
+  const int sms = b200_num_sms();
+  const int kblocks = (K + kBK - 1) / kBK;
+  const int mp = (M + 15) & ~15;
+  p.mp = mp;
+  p.tiles_n = (N + kBM - 1) / kBM;
+  int splits = 1;
+  if (p.tiles_n < sms) {
+    splits = (sms + p.tiles_n - 1) / p.tiles_n;
+    int max_by_k = kblocks / 4;
+    if (max_by_k < 1) max_by_k = 1;
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+  }
+  while (splits > 1 && (size_t)splits * slab > (size_t)B200_GEMM_STATIC_SCRATCH_BYTES) --splits;
+  const int kb_per = (kblocks + splits - 1) / splits;
+  splits = (kblocks + kb_per - 1) / kb_per;
+  p.splits = splits;
+  p.kb_per_split = kb_per;
+  p.workspace = sd.scratch;
+  const int stage_bytes = kBM * kBK * 2 + mp * kBK * 2;
+  int stages = (kSmemBudget - 2048) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > kb_per) stages = kb_per;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < mp) tmem_cols <<= 1;
+  CUtensorMap tmW, tmA;
+  if (!encode_tmap_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldw, kBM, kBK,
+                      CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, mp, kBK,
+                      CU_TENSOR_MAP_SWIZZLE_128B)) {
+    g_static_err = "tensor map encoding failed";
+    return -3;
+  }
+  const size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+  dim3 grid(p.tiles_n, splits);
+  gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, tmA, p, tmem_cols);
+  if (cudaGetLastError() != cudaSuccess) { g_static_err = "kernel launch failed"; return -2; }
+  if (splits > 1) {
+    const size_t total = (size_t)M * (N / 4);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > sms * 8) blocks = sms * 8;
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(sd.scratch, splits, M, N, out, ldo, 0,
+                                                     nullptr, nullptr, 0);
+    if (cudaGetLastError() != cudaSuccess) { g_static_err = "reduce launch failed"; return -2; }
+  }
+  return 0;
+}
