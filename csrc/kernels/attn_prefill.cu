@@ -1,5 +1,5 @@
 // Paged flash-attention prefill on tcgen05 / TMEM (varlen, causal with bottom-right
-// alignment, GQA, sliding window, soft-cap), head_dim 64 or 128.
+// alignment, GQA, sliding window, soft-cap), head_dim 64, 128 or 256.
 //
 // One CTA = one 128-row query tile of one request and one query head; two CTAs share an SM.
 // Per 64-token KV tile:  S = Q K^T  (tcgen05, A = Q smem, B = K smem, both K-major SW128,
@@ -64,14 +64,19 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
+// D = 256 keeps two softmax threads per query row (warps w and w + 4 share a TMEM lane
+// quarter): both reduce the full score row, each writes half of P and owns half of O.
 template <int D>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ,
                         const __grid_constant__ CUtensorMap tmKV, PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   constexpr int kDH = D / 64;                     // 64-wide halves of the head dim
+  constexpr int kSplit = D > 128 ? 2 : 1;         // softmax threads per query row
+  constexpr int kDO = D / kSplit;                 // output dims owned by one thread
+  constexpr uint32_t kTmemCols = D > 128 ? 512 : 256;
   constexpr int kQHalf = kQT * 128;               // 16 KB: 128 rows x 128 B
   constexpr int kKVHalf = kKT * 128;              // 8 KB: 64 tokens x 128 B
   constexpr int kQBytes = kDH * kQHalf;
@@ -108,16 +113,16 @@ __global__ void __launch_bounds__(192, 2)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 4);
+      mbar_init(&bars->s_empty[i], 4 * kSplit);
     }
-    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->p_full, 4 * kSplit);
     mbar_init(&bars->p_empty, 1);
     mbar_init(&bars->o_full, 1);
-    mbar_init(&bars->o_empty, 4);
+    mbar_init(&bars->o_empty, 4 * kSplit);
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, 256);
+    tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -209,6 +214,7 @@ __global__ void __launch_bounds__(192, 2)
   } else {
     // ---------------- softmax + output: one thread per query row ----------------
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;               // which half of P / O this thread owns
     const int r = quarter * 32 + lane;              // row inside the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int q_pos = ctx_off + q0 + r;             // absolute position of this query row
@@ -217,9 +223,9 @@ __global__ void __launch_bounds__(192, 2)
     const float sc = p.scale_log2;
     const bool cap = p.softcap2 > 0.f;
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;   // m in the scaled log2 domain
-    float o[D];
+    float o[kDO];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < kDO; ++i) o[i] = 0.f;
     bool ok = true;
     uint8_t* prow = sP + r * 128;
     for (int j = 0; j < ntiles && ok; ++j) {
@@ -285,7 +291,8 @@ __global__ void __launch_bounds__(192, 2)
           rs1 += p1;
           pk[e] = pack_bf16x2(p0, p1);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        if (kSplit == 1 || (c >> 2) == part)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l = l * alpha + (rs0 + rs1);
       m = m_new;
@@ -298,9 +305,9 @@ __global__ void __launch_bounds__(192, 2)
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < kDO / 32; ++c) {
           uint32_t rr[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, rr);
+          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -317,9 +324,9 @@ __global__ void __launch_bounds__(192, 2)
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < kDO / 32; ++c) {
           uint32_t rr[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_off + c * 32, rr);
+          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -329,9 +336,9 @@ __global__ void __launch_bounds__(192, 2)
     }
     if (ok && r < rows) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(q_begin + q0 + r) * p.ldo + h * D;
+      __nv_bfloat16* dst = p.out + (size_t)(q_begin + q0 + r) * p.ldo + h * D + part * kDO;
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
+      for (int i = 0; i < kDO; i += 8) {
         uint4 w;
         w.x = pack_bf16x2(o[i + 0] * inv, o[i + 1] * inv);
         w.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
@@ -339,7 +346,7 @@ __global__ void __launch_bounds__(192, 2)
         w.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
         *reinterpret_cast<uint4*>(dst + i) = w;
       }
-      if (p.lse) {
+      if (p.lse && part == 0) {
         const float ln2 = 0.6931471805599453f;
         p.lse[(size_t)(q_begin + q0 + r) * p.Hq + h] = l > 0.f ? (m + log2f(l)) * ln2 : -INFINITY;
       }
@@ -348,7 +355,7 @@ __global__ void __launch_bounds__(192, 2)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 struct KvMapKey {
@@ -378,7 +385,7 @@ static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const
                          (int)smem);
     set = true;
   }
-  attn_prefill_kernel<D><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  attn_prefill_kernel<D><<<grid, 64 + 128 * (D > 128 ? 2 : 1), smem, stream>>>(tmQ, tmKV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -393,7 +400,7 @@ extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, voi
                                  const void* tile_q0, int num_tiles, int total_q, float scale,
                                  float softcap, int window, int causal, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
-  if (D != 64 && D != 128) return -1;
+  if (D != 64 && D != 128 && D != 256) return -1;
   if (block_size < 8 || (block_size & 7) || (block_size < kKT && kKT % block_size) ||
       (block_size > kKT && block_size % kKT))
     return -1;
@@ -431,6 +438,7 @@ extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, voi
   p.window = window; p.causal = causal;
   p.status = device_status_word();
   dim3 grid(num_tiles, Hq);
+  if (D == 256) return launch_prefill<256>(tmQ, tmKV, p, grid, stream);
   return D == 128 ? launch_prefill<128>(tmQ, tmKV, p, grid, stream)
                   : launch_prefill<64>(tmQ, tmKV, p, grid, stream);
 }

@@ -245,17 +245,22 @@ __global__ void __launch_bounds__(128)
 }
 
 // ------------------------------------------------------------------------------------
-// gated RMSNorm over rows of D (<= 1024, multiple of 4): one warp per row.
+// gated RMSNorm over rows of D (<= 1024, multiple of 4): one warp per row. Row r is head
+// r % heads of token r / heads; ldx / ldz / ldo are token strides, heads sit D apart.
 // gate_kind 0: silu(z), 1: sigmoid(z).
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
     rmsnorm_gated_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict__ z, long ldz,
                          const bf16* __restrict__ w, bf16* __restrict__ out, long ldo, long R, int D,
-                         float eps, int gate_kind) {
+                         float eps, int gate_kind, int heads) {
   const long r = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (r >= R) return;
-  const bf16* xr = x + r * ldx;
+  const long tok = r / heads;
+  const long hoff = (r % heads) * (long)D;
+  const bf16* xr = x + tok * ldx + hoff;
+  const bf16* zr = z + tok * ldz + hoff;
+  bf16* orow = out + tok * ldo + hoff;
   float ss = 0.f;
   for (int i = lane * 4; i < D; i += 128) {
     const uint2 v = *reinterpret_cast<const uint2*>(xr + i);
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(128)
   const float inv = rsqrtf(ss / (float)D + eps);
   for (int i = lane * 4; i < D; i += 128) {
     const uint2 v = *reinterpret_cast<const uint2*>(xr + i);
-    const uint2 zv = *reinterpret_cast<const uint2*>(z + r * ldz + i);
+    const uint2 zv = *reinterpret_cast<const uint2*>(zr + i);
     const uint2 wv = *reinterpret_cast<const uint2*>(w + i);
     const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y);
     const float2 z0 = unpack_bf16x2(zv.x), z1 = unpack_bf16x2(zv.y);
@@ -276,7 +281,7 @@ __global__ void __launch_bounds__(128)
     uint2 o;
     o.x = pack_bf16x2(f0.x * inv * w0.x * gate(z0.x), f0.y * inv * w0.y * gate(z0.y));
     o.y = pack_bf16x2(f1.x * inv * w1.x * gate(z1.x), f1.y * inv * w1.y * gate(z1.y));
-    *reinterpret_cast<uint2*>(out + r * ldo + i) = o;
+    *reinterpret_cast<uint2*>(orow + i) = o;
   }
 }
 
@@ -338,11 +343,13 @@ int b200_gdn_packed_decode(const void* xc, long ld, const void* a, const void* b
 }
 
 int b200_rmsnorm_gated(const void* x, long ldx, const void* z, long ldz, const void* w, void* out,
-                       long ldo, long R, int D, float eps, int gate_kind, cudaStream_t stream) {
+                       long ldo, long R, int D, float eps, int gate_kind, int heads,
+                       cudaStream_t stream) {
   if (R <= 0) return 0;
+  if (heads < 1) heads = 1;
   if ((D & 3) || (ldx & 3) || (ldz & 3) || (ldo & 3)) return -1;
   rmsnorm_gated_kernel<<<(unsigned)((R + 3) / 4), 128, 0, stream>>>(
-      (const bf16*)x, ldx, (const bf16*)z, ldz, (const bf16*)w, (bf16*)out, ldo, R, D, eps, gate_kind);
+      (const bf16*)x, ldx, (const bf16*)z, ldz, (const bf16*)w, (bf16*)out, ldo, R, D, eps, gate_kind, heads);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

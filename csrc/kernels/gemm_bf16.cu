@@ -686,7 +686,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     p.tiles_n = (N + kBM - 1) / kBM;
     int splits = 1;
     if (p.tiles_n < sms && !(tp && tp->scatter)) {
-      splits = (sms + p.tiles_n - 1) / p.tiles_n;
+      splits = sms / p.tiles_n;       // whole CTAs per SM: one wave, never a ragged second one
       int max_by_k = kblocks / 4;
       if (max_by_k < 1) max_by_k = 1;
       if (splits > max_by_k) splits = max_by_k;
@@ -862,7 +862,7 @@ extern "C" int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* 
   p.tiles_n = (N + kBM - 1) / kBM;
   int splits = 1;
   if (p.tiles_n < sms) {
-    splits = (sms + p.tiles_n - 1) / p.tiles_n;
+    splits = sms / p.tiles_n;
     int max_by_k = kblocks / 4;
     if (max_by_k < 1) max_by_k = 1;
     if (splits > max_by_k) splits = max_by_k;

@@ -131,12 +131,12 @@ def test_packed_decode_matches_recurrence():
 
 def test_rmsnorm_gated():
     torch.manual_seed(2)
-    R, D = 50, 128
-    x = torch.randn(R, D, device=DEV).to(torch.bfloat16)
-    zfull = torch.randn(R, 3 * D, device=DEV).to(torch.bfloat16)
-    z = zfull[:, D:2 * D]
+    R, D, heads = 50, 128, 3
+    x = torch.randn(R, heads * D, device=DEV).to(torch.bfloat16)
+    zfull = torch.randn(R, 5 * D, device=DEV).to(torch.bfloat16)
+    z = zfull[:, D:(1 + heads) * D]
     w = (torch.rand(D, device=DEV) + 0.5).to(torch.bfloat16)
     out = torch.empty_like(x)
     for gate in ("silu", "sigmoid"):
-        G.rmsnorm_gated(x, z, w, out, gate=gate)
-        assert _rel(out, G.ref_rmsnorm_gated(x, z, w, gate=gate)) < 1e-2
+        G.rmsnorm_gated(x, z, w, out, gate=gate, heads=heads)
+        assert _rel(out, G.ref_rmsnorm_gated(x, z, w, gate=gate, heads=heads)) < 1e-2

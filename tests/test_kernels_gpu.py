@@ -172,7 +172,7 @@ def _make_paged(seq_lens, Hkv, D, bs, extra_blocks=3):
 
 
 @pytest.mark.parametrize("D,Hq,Hkv,bs", [(128, 8, 2, 16), (128, 4, 4, 32), (64, 4, 1, 16),
-                                         (128, 4, 1, 128)])
+                                         (128, 4, 1, 128), (256, 6, 1, 16), (256, 2, 2, 64)])
 def test_attn_prefill(D, Hq, Hkv, bs):
     torch.manual_seed(9)
     q_lens = [200, 17, 128, 333]

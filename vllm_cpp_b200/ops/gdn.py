@@ -22,7 +22,7 @@ def _declare():
     _lib.declare("b200_gdn_conv1d_update", [P, L, P, P, P, P, L, I, I, P], I)
     _lib.declare("b200_gdn_post_conv", [P, L, I, I, I, I, P, P, L, P, P, P, P, P, P, F, P], I)
     _lib.declare("b200_gdn_packed_decode", [P, L, P, P, L, P, P, P, P, P, I, I, I, I, I, F, P], I)
-    _lib.declare("b200_rmsnorm_gated", [P, L, P, L, P, P, L, L, I, F, I, P], I)
+    _lib.declare("b200_rmsnorm_gated", [P, L, P, L, P, P, L, L, I, F, I, I, P], I)
     _lib.declare("b200_gdn_chunk_scan", [P, P, P, L, I, P, P, I, I, I, P, P, I, P, P, P, I, P, P, P, P,
                                          P, P, P, P], I)
     lib()
@@ -70,13 +70,16 @@ def packed_decode(xc, a, b, A_log, dt_bias, state, slots, out, Hk, Hv, eps=1e-6)
     return out
 
 
-def rmsnorm_gated(x, z, w, out, eps=1e-6, gate="silu"):
-    """x, z, out: bf16 [R, D] row-strided; out = rmsnorm(x) * w * gate(z)."""
+def rmsnorm_gated(x, z, w, out, eps=1e-6, gate="silu", heads=1):
+    """out = rmsnorm(x) * w * gate(z) over groups of D = w.numel() columns. x, z, out: bf16
+    [T, heads * D] row-strided (each head normalised on its own)."""
     _declare()
-    R, D = x.shape
+    T = x.shape[0]
+    D = w.numel()
+    assert x.shape[1] == heads * D
     check(lib().b200_rmsnorm_gated(ptr(x), x.stride(0), ptr(z), z.stride(0), ptr(w), ptr(out),
-                                   out.stride(0), R, D, eps, 0 if gate == "silu" else 1, stream_ptr()),
-          "rmsnorm_gated")
+                                   out.stride(0), T * heads, D, eps, 0 if gate == "silu" else 1,
+                                   heads, stream_ptr()), "rmsnorm_gated")
     return out
 
 
@@ -191,9 +194,10 @@ def ref_recurrent(q, k, v, g, beta, state0):
     return o, S
 
 
-def ref_rmsnorm_gated(x, z, w, eps=1e-6, gate="silu"):
-    xf = x.float()
+def ref_rmsnorm_gated(x, z, w, eps=1e-6, gate="silu", heads=1):
+    T = x.shape[0]
+    xf = x.float().reshape(T, heads, -1)
     y = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * w.float()
-    zz = z.float()
+    zz = z.float().reshape(T, heads, -1)
     y = y * (torch.nn.functional.silu(zz) if gate == "silu" else torch.sigmoid(zz))
-    return y.to(torch.bfloat16)
+    return y.reshape(T, -1).to(torch.bfloat16)

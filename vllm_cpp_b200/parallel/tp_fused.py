@@ -191,7 +191,7 @@ class TpFusedContext:
         if T <= 256:
             tiles_n = -(-N // 128)
             kblocks = -(-K // 64)
-            splits = max(1, min(-(-_lib.lib().b200_num_sms() // tiles_n), kblocks // 4,
+            splits = max(1, min(_lib.lib().b200_num_sms() // tiles_n, kblocks // 4,
                                 self.rpr_max // d.rows_per_rank, 8))
             kb_per = -(-kblocks // splits)
             splits = -(-kblocks // kb_per)

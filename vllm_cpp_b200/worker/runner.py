@@ -182,6 +182,8 @@ class ModelRunner(E.ModelRunnerBase):
             max_query_len=info.max_query_len if info else 1,
             decode_only_full_logits=padded is not None)
         ctx.extra["decode_tmp"] = tmp
+        if padded is None:
+            ctx.extra["host"] = self.host_views   # this step's pinned host copies
         if not self.is_cuda:
             # CPU oracle path wants exact-length views
             R = ctx.num_reqs
