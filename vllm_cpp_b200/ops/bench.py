@@ -69,6 +69,46 @@ def small_case(name: str):
         q = torch.randn(B, Hq * D, device=dev, dtype=torch.bfloat16)
         fn = lambda: ops.attn_decode(q, cache, block_table=bt, seq_lens=sl, num_q_heads=Hq,
                                      num_kv_heads=Hkv, head_dim=D, block_size=bs, scale=D ** -0.5)
+    elif name == "gdn_scan_small":
+        from . import gdn as G
+        T, Hk, Hv = 16384, 2, 6          # one 16k-token prompt at the TP=8 head counts of Qwen3.6-27B
+        xc = torch.randn(T, 2 * Hk * 128 + Hv * 128, device=dev).to(torch.bfloat16)
+        q = torch.nn.functional.normalize(torch.randn(T, Hk, 128, device=dev), dim=-1).to(torch.bfloat16)
+        k = torch.nn.functional.normalize(torch.randn(T, Hk, 128, device=dev), dim=-1).to(torch.bfloat16)
+        g = -torch.rand(T, Hv, device=dev) * 0.1
+        beta = torch.rand(T, Hv, device=dev)
+        lens = [2048] * 8
+        qsl = [0]
+        for n in lens:
+            qsl.append(qsl[-1] + n)
+        state = torch.zeros(len(lens), Hv, 128, 128, device=dev)
+        slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+        hi = torch.zeros(len(lens), dtype=torch.int32, device=dev)
+        out = torch.empty(T, Hv, 128, device=dev, dtype=torch.bfloat16)
+        ws = G.GdnWorkspace(dev, T, len(lens), Hv)
+        fn = lambda: G.chunk_scan(q, k, xc, g, beta, state, qsl, slots, hi, out, ws, v_col0=2 * Hk * 128)
+    elif name == "gdn_decode_small":
+        from . import gdn as G
+        B, Hk, Hv = 256, 2, 6
+        xc = torch.randn(B, 2 * Hk * 128 + Hv * 128, device=dev).to(torch.bfloat16)
+        a = torch.randn(B, Hv, device=dev).to(torch.bfloat16)
+        b = torch.randn(B, Hv, device=dev).to(torch.bfloat16)
+        A_log = torch.zeros(Hv, device=dev)
+        dtb = torch.zeros(Hv, device=dev)
+        state = torch.zeros(B, Hv, 128, 128, device=dev)     # 100 MB read + written per launch
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        out = torch.empty(B, Hv, 128, device=dev, dtype=torch.bfloat16)
+        fn = lambda: G.packed_decode(xc, a, b, A_log, dtb, state, slots, out, Hk, Hv)
+    elif name == "moe_small":
+        from . import moe as M
+        T, E, k, H, I = 2048, 128, 8, 2048, 768
+        x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+        wgu = (torch.randn(E, 2 * I, H, device=dev) * 0.05).to(torch.bfloat16)
+        ids, w = M.router_topk(torch.randn(T, E, device=dev), k)
+        ws = M.MoeWorkspace(dev, T, k, E, H, I)
+        M.moe_sort(ids, 0, E, ws)
+        M.moe_gather(x, ws, E, T * k)
+        fn = lambda: M.grouped_gemm(ws.xs, wgu, ws.gu, ws, T * k)
     else:
         raise SystemExit(f"unknown case {name}")
     ms = _time(fn, iters=3, warmup=1)
@@ -81,7 +121,8 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--case", default=None,
                     help="run one small case only (for profiler captures): "
-                         "gemm_small | gemm_decode_small | prefill_small | decode_small")
+                         "gemm_small | gemm_decode_small | prefill_small | decode_small | gdn_scan_small | "
+                         "gdn_decode_small | moe_small")
     args = ap.parse_args()
     if args.case:
         return small_case(args.case)
