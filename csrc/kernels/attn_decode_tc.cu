@@ -285,7 +285,9 @@ __global__ void __launch_bounds__(192, 2)
         const int pb = j & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty[pb], ((j >> 1) & 1) ^ 1, p.status));
         if (!ok) break;
+        bool pv_waited = false;
         if (rescale && j > 0) {
+          pv_waited = true;
           // all PV products issued so far must have landed before O^T is rescaled in place
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
           if (!ok) break;
@@ -311,6 +313,13 @@ __global__ void __launch_bounds__(192, 2)
             *reinterpret_cast<__nv_bfloat16*>(pbuf + g * 128 + (((c >> 3) ^ (g & 7)) << 4) +
                                               (c & 7) * 2) = pb16;
           }
+        }
+        // Observe every completion of pv_done in order (one per tile): a parity wait that
+        // skipped phases could be satisfied by an older one. PV(j) cannot start before
+        // PV(j-1) has finished anyway, so this costs nothing.
+        if (j > 0 && !pv_waited) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
+          if (!ok) break;
         }
         fence_proxy_async_smem();
         tc_fence_before_sync();

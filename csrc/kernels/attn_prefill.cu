@@ -418,6 +418,7 @@ extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, voi
     std::lock_guard<std::mutex> lock(mu);
     auto it = kv_cache_maps.find(key);
     if (it == kv_cache_maps.end()) {
+      if (kv_cache_maps.size() > 4096) kv_cache_maps.clear();   // scratch caches come and go
       CUtensorMap m;
       if (!encode_tmap_3d(&m, kv_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)D,
                           (uint64_t)Hkv, rows, (uint64_t)D * 2, (uint64_t)Hkv * D * 2, 64, 1,

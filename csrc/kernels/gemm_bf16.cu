@@ -43,6 +43,10 @@ struct GemmParams {
   int splits;
   int kb_per_split;
   float* workspace;  // [splits, M, N] fp32 partials
+  // batched mode (blockIdx.z = batch): W is [batch * N, K], batch b reads the A columns from
+  // b * batch_a_cols and writes out + b * batch_out_stride. No split-K.
+  int batch_a_cols;
+  long long batch_out_stride;
   // ---- fused tensor-parallel modes (all zero when unused) -------------------------------
   // scatter epilogue (GEMM + reduce-scatter): row m of the bf16 partial goes to the rank that
   // owns it (m / rows_per_rank), into that rank's receive buffer slot [parity][tp_rank], and
@@ -348,6 +352,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int lane = threadIdx.x & 31;
   const int tn = blockIdx.x;
   const int split = blockIdx.y;
+  const int bz = blockIdx.z;
   const int kblocks_total = (p.K + kBK - 1) / kBK;
   const int kb0 = split * p.kb_per_split;
   const int kb1 = min(kblocks_total, kb0 + p.kb_per_split);
@@ -391,8 +396,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         uint8_t* w_dst = smem + (size_t)s * stage_bytes;
         uint8_t* a_dst = w_dst + kWBytes;
         mbar_expect_tx(&bars->full[s], stage_bytes);
-        tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, tn * kBM);
-        tma_load_2d(a_dst, ta, &bars->full[s], (kb0 + i) * kBK, 0);
+        tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, bz * p.N + tn * kBM);
+        tma_load_2d(a_dst, ta, &bars->full[s], bz * p.batch_a_cols + (kb0 + i) * kBK, 0);
       }
     }
   } else if (warp == 1) {
@@ -454,11 +459,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
               } else {
                 v += bias_v;
                 if (p.residual) v += __bfloat162float(p.residual[(size_t)m * p.ldr + n]);
+                const size_t o = (size_t)bz * p.batch_out_stride + (size_t)m * p.ldo + n;
                 if (p.out_f32)
-                  reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+                  reinterpret_cast<float*>(p.out)[o] = v;
                 else
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] =
-                      __float2bfloat16(v);
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16(v);
               }
             }
           }
@@ -758,6 +763,50 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   p.tiles_n = tn128;
   if (!get_tmap_bf16(&tmB, W, N, K, ldw, 128, kBK)) return -3;
   return launch_tn<128>(tmA, tmA2, tmB, p, stream);
+}
+
+// Batched small-M GEMM (M <= 256, K a multiple of 64): for b in [0, batch)
+//   out[b * out_batch_stride + m * ldo + n] = sum_k A[m * lda + b * a_batch_cols + k] * W[(b * N + n) * ldw + k]
+// One launch, grid (N / 128, 1, batch). Used for the per-head W_UK / W_UV products of MLA
+// (reference: BatchedMatmulKernelCuda in src/vt/cuda/cuda_matmul.cu).
+extern "C" int b200_gemm_bf16_batched(const void* A, int lda, int a_batch_cols, const void* W, int ldw,
+                                      void* out, int ldo, long long out_batch_stride, int M, int N,
+                                      int K, int batch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if (M > 256 || (K & 63) || (lda & 7) || (ldw & 7) || (a_batch_cols & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_f32 = 0;
+  p.status = device_status_word();
+  p.batch_a_cols = a_batch_cols;
+  p.batch_out_stride = out_batch_stride;
+  const int mp = (M + 15) & ~15;
+  p.mp = mp;
+  p.tiles_n = (N + kBM - 1) / kBM;
+  p.splits = 1;
+  const int kblocks = K / kBK;
+  p.kb_per_split = kblocks;
+  const int stage_bytes = kBM * kBK * 2 + mp * kBK * 2;
+  int stages = (kSmemBudget - 2048) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > kblocks) stages = kblocks;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < mp) tmem_cols <<= 1;
+  CUtensorMap tmW, tmA;
+  if (!get_tmap_bf16(&tmW, W, (uint64_t)batch * N, K, ldw, kBM, kBK)) return -3;
+  if (!get_tmap_bf16(&tmA, A, M, (uint64_t)lda, lda, mp, kBK)) return -3;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         kSmemBudget + 4096);
+    attr_set = true;
+  }
+  const size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+  gemm_bf16_swap_kernel<<<dim3(p.tiles_n, 1, batch), kGemmThreads, smem, stream>>>(tmW, tmA, tmA, p, tmem_cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -314,6 +314,13 @@ def synthetic_config(name: str) -> ModelConfig:
         if n == "tiny-qwen3":
             return ModelConfig(architecture="Qwen3ForCausalLM", qk_norm=True,
                                tie_word_embeddings=True, **base)
+        if n == "tiny-mla":
+            base.update(head_dim=192, num_heads=4, num_kv_heads=4)
+            return ModelConfig(architecture="DeepseekV2ForCausalLM", num_experts=8, num_experts_per_tok=2,
+                               moe_intermediate_size=128, num_shared_experts=1, first_k_dense_replace=1,
+                               norm_topk_prob=False, kv_lora_rank=512, qk_nope_head_dim=128,
+                               qk_rope_head_dim=64, v_head_dim=128,
+                               **{**base, "rope": RopeConfig(theta=1e4, neox=False, rotary_dim=64)})
         if n == "tiny-gdn":
             base.update(num_layers=4, head_dim=256, num_heads=2, num_kv_heads=1)
             return ModelConfig(architecture="Qwen3_5ForConditionalGeneration", qk_norm=True,
