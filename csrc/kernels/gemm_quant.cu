@@ -1,0 +1,587 @@
+// Quantised GEMMs and the kernels that produce their operands.
+//
+//   fp8 (e4m3) x fp8 -> bf16, per-tensor (optionally per-output-channel) scales: persistent
+//   128 x 128 tcgen05 kind::f8f6f4 tiles, TMA ring of 128-byte K blocks (128 elements),
+//   accumulators double-buffered in TMEM.     reference: MatmulFp8CublasLt / MatmulFp8Cutlass
+//
+//   NVFP4 weights (E2M1 pairs packed in bytes, one UE4M3 scale per 16 values, fp32 per-tensor
+//   scale) x bf16 activations:
+//     small M (<= 256): swap-AB kernel whose four otherwise idle epilogue warps expand each
+//       packed 128 x 64 weight block (4 KB + 512 B of scales instead of 16 KB) into the
+//       swizzled bf16 tile the MMA reads, so HBM only ever sees 4.5 bits per weight;
+//     large M: one pass that expands the matrix to a bf16 scratch, then the bf16 GEMM.
+//                                             reference: MatmulNvfp4* W4A16 path, Marlin dense
+//
+//   producers: bf16 -> fp8 with a static scale (plain, RMSNorm-fused), bf16 -> NVFP4 with
+//   per-16 block scales (plain, SiLU-mul-fused), row-major or 128x4-swizzled scale output.
+//                                             reference: QuantFp8StaticKernel,
+//                                             RmsNormQuantFp8RowKernel, ScaledFp4Quant*,
+//                                             SiluAndMulFp4Quant*, SwizzleBlockscaleKernel
+#include <cuda_fp8.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "api.h"
+#include "sm100.cuh"
+
+namespace b200 {
+
+typedef __nv_bfloat16 bf16;
+
+static constexpr int kQM = 128, kQN = 128, kQKB = 128;   // tile, K bytes per block
+static constexpr int kQThreads = 192;
+static constexpr int kQMaxStages = 8;
+
+struct QBars {
+  uint64_t full[kQMaxStages], empty[kQMaxStages];
+  uint64_t raw_full[kQMaxStages];     // W4A16: packed weights landed
+  uint64_t acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int failed;
+};
+
+struct Fp8Params {
+  int M, N, K;
+  bf16* out;
+  int ldo;
+  const float* a_scale;      // per-tensor
+  const float* w_scale;      // per-tensor or per-channel [N]
+  int w_scale_per_channel;
+  const bf16* bias;
+  int tiles_m, tiles_n, stages;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kQThreads, 1)
+    gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    Fp8Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kABytes = kQM * kQKB, kBBytes = kQN * kQKB, kStage = kABytes + kBBytes;
+  const int stages = p.stages;
+  QBars* bars = reinterpret_cast<QBars*>(smem + (size_t)stages * kStage);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + kQKB - 1) / kQKB;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bars->acc_full[b], 1); mbar_init(&bars->acc_empty[b], 4); }
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, 2 * kQN); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % stages;
+          if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, p.status)) { ok = false; break; }
+          uint8_t* a_dst = smem + (size_t)s * kStage;
+          mbar_expect_tx(&bars->full[s], kStage);
+          tma_load_2d(a_dst, &tmA, &bars->full[s], kb * kQKB, tm * kQM);
+          tma_load_2d(a_dst + kABytes, &tmB, &bars->full[s], kb * kQKB, tn * kQN);
+        }
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_e4m3(kQM, kQN);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+        const int buf = tc & 1;
+        if (!mbar_wait(&bars->acc_empty[buf], ((tc >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * kQN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % stages;
+          if (!mbar_wait(&bars->full[s], (it / stages) & 1, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * kStage);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr, 1024);
+          const uint64_t bdesc = umma_desc_k_sw128(a_addr + kABytes, 1024);
+#pragma unroll
+          for (int k = 0; k < kQKB / 32; ++k)   // 32 fp8 values = 32 bytes per instruction
+            umma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&bars->empty[s]);
+        }
+        if (ok) umma_commit(&bars->acc_full[buf]);
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else {
+    const int quarter = warp & 3;
+    uint32_t tc = 0;
+    bool ok = true;
+    const float sa = *p.a_scale;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int buf = tc & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[buf], (tc >> 1) & 1, p.status));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tm * kQM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + buf * kQN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kQN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = tn * kQN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          bf16* o = p.out + (size_t)row * p.ldo + col0;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (col0 + i < p.N) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float sw = p.w_scale_per_channel ? p.w_scale[col0 + i + e] : p.w_scale[0];
+                v[e] = __uint_as_float(r[i + e]) * sa * sw;
+                if (p.bias) v[e] += __bfloat162float(p.bias[col0 + i + e]);
+              }
+              uint4 w;
+              w.x = pack_bf16x2(v[0], v[1]); w.y = pack_bf16x2(v[2], v[3]);
+              w.z = pack_bf16x2(v[4], v[5]); w.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(o + i) = w;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * kQN);
+}
+
+// ---------------------------------------------------------------------------------------
+// NVFP4
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+  // sign | 2-bit exponent | 1-bit mantissa: 0, .5, 1, 1.5, 2, 3, 4, 6
+  const uint32_t mag = code & 7u;
+  const float v = mag < 2 ? 0.5f * (float)mag : (float)(2 + (mag & 1)) * (float)(1 << ((mag >> 1) - 1)) * 0.5f;
+  return (code & 8u) ? -v : v;
+}
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  __nv_fp8_e4m3 t;
+  t.__x = b;
+  return (float)t;
+}
+
+// Whole-matrix expansion: packed [N, K/2] + scales [N, K/16] -> bf16 [N, K].
+__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf,
+                                     const float* __restrict__ gscale, bf16* __restrict__ out, long N,
+                                     int K) {
+  const long groups = N * (long)(K / 16);
+  const float g = *gscale;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < groups; i += (long)gridDim.x * blockDim.x) {
+    const float s = e4m3_to_float(sf[i]) * g;
+    const uint2 raw = reinterpret_cast<const uint2*>(packed)[i];   // 8 bytes = 16 values
+    uint32_t w[8];
+    const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t byte = (words[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+      w[j] = pack_bf16x2(e2m1_value(byte & 15u) * s, e2m1_value(byte >> 4) * s);
+    }
+    uint4* o = reinterpret_cast<uint4*>(out + i * 16);
+    o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+struct W4Params {
+  int M, N, K;
+  bf16* out;
+  int ldo;
+  const uint8_t* wq;      // [N, K/2]
+  const uint8_t* sf;      // [N, K/16] e4m3
+  const float* gscale;
+  const bf16* bias;
+  int mp, stages, splits, kb_per_split;
+  float* workspace;
+  int* status;
+};
+
+// Swap-AB: weights are the 128-row operand. Warp 0 streams activations (TMA) and packed
+// weights (plain 16-byte loads into shared memory via cp.async-free vector copies done by
+// the converter warps themselves), warps 2-5 expand, warp 1 issues the MMAs.
+__global__ void __launch_bounds__(kQThreads, 1)
+    gemm_w4a16_swap_kernel(const __grid_constant__ CUtensorMap tmA, W4Params p, uint32_t tmem_cols) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kWBytes = 128 * 64 * 2;            // expanded bf16 weight block
+  const int a_bytes = p.mp * 64 * 2;
+  const int stage_bytes = kWBytes + a_bytes;
+  const int stages = p.stages;
+  QBars* bars = reinterpret_cast<QBars*>(smem + (size_t)stages * stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tn = blockIdx.x, split = blockIdx.y;
+  const int kblocks_total = p.K / 64;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(kblocks_total, kb0 + p.kb_per_split) - kb0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);        // activations (TMA)
+      mbar_init(&bars->raw_full[s], 4);    // expanded weights (4 converter warps)
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->acc_full[0], 1);
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % stages;
+        if (!mbar_wait(&bars->empty[s], ((i / stages) & 1) ^ 1, p.status)) { bars->failed = 1; break; }
+        mbar_expect_tx(&bars->full[s], a_bytes);
+        tma_load_2d(smem + (size_t)s * stage_bytes + kWBytes, &tmA, &bars->full[s], (kb0 + i) * 64, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, p.mp);
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % stages;
+        const uint32_t ph = (i / stages) & 1;
+        if (!mbar_wait(&bars->full[s], ph, p.status) || !mbar_wait(&bars->raw_full[s], ph, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t w_addr = smem_u32(smem + (size_t)s * stage_bytes);
+        const uint64_t wdesc = umma_desc_k_sw128(w_addr, 1024);
+        const uint64_t adesc = umma_desc_k_sw128(w_addr + kWBytes, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_bf16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (i | k) != 0);
+        umma_commit(&bars->empty[s]);
+      }
+      if (ok) umma_commit(&bars->acc_full[0]);
+      else bars->failed = 1;
+    }
+  } else {
+    // ---- converters: thread t owns weight row t of the tile ----
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const long n = (long)tn * 128 + r;
+    const bool row_ok = n < p.N;
+    const float g = *p.gscale;
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % stages;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ((i / stages) & 1) ^ 1, p.status));
+      if (!ok) break;
+      uint8_t* w_dst = smem + (size_t)s * stage_bytes + (size_t)r * 128;
+      const int kb = kb0 + i;
+      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = raw0;
+      uint32_t sfw = 0;
+      if (row_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.wq + n * (p.K / 2) + (size_t)kb * 32);
+        raw0 = src[0];
+        raw1 = src[1];
+        sfw = *reinterpret_cast<const uint32_t*>(p.sf + n * (p.K / 16) + (size_t)kb * 4);
+      }
+      const uint32_t words[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {           // 8 columns (16 bytes of bf16) per chunk
+        const float sc = e4m3_to_float((uint8_t)(sfw >> ((c >> 1) * 8))) * g;
+        const uint32_t wd = words[c];
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t byte = (wd >> (e * 8)) & 0xffu;
+          o[e] = pack_bf16x2(e2m1_value(byte & 15u) * sc, e2m1_value(byte >> 4) * sc);
+        }
+        *reinterpret_cast<uint4*>(w_dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->raw_full[s]);
+    }
+    // ---- epilogue ----
+    if (ok && nkb > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[0], 0, p.status));
+    if (ok) {
+      tc_fence_after_sync();
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const float bias_v = (p.bias && p.splits == 1 && row_ok) ? __bfloat162float(p.bias[n]) : 0.f;
+      for (int c = 0; c < p.mp / 16; ++c) {
+        uint32_t rr[16];
+        if (nkb > 0) { tmem_ld_32x32b_x16(t_addr + c * 16, rr); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) rr[e] = 0;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int m = c * 16 + e;
+            if (m < p.M) {
+              const float v = __uint_as_float(rr[e]);
+              if (p.splits > 1) p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
+              else p.out[(size_t)m * p.ldo + n] = __float2bfloat16(v + bias_v);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+__global__ void w4_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, bf16* out,
+                                        int ldo, const bf16* __restrict__ bias) {
+  const size_t total = (size_t)M * N;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / N), n = (int)(i % N);
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + i];
+    if (bias) acc += __bfloat162float(bias[n]);
+    out[(size_t)m * ldo + n] = __float2bfloat16(acc);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Producers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint32_t float_to_e2m1(float v) {
+  // round to nearest representable magnitude (ties to even code), saturate at 6
+  const float a = fabsf(v);
+  uint32_t code;
+  if (a <= 0.25f) code = 0;
+  else if (a < 0.75f) code = 1;
+  else if (a <= 1.25f) code = 2;
+  else if (a < 1.75f) code = 3;
+  else if (a <= 2.5f) code = 4;
+  else if (a < 3.5f) code = 5;
+  else if (a <= 5.0f) code = 6;
+  else code = 7;
+  return code | (v < 0.f ? 8u : 0u);
+}
+
+// out = fp8(x / scale) (optionally after RMSNorm with weight w; gemma adds 1 to w).
+__global__ void __launch_bounds__(256)
+    quant_fp8_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict__ w, float eps, int gemma,
+                     const float* __restrict__ scale, uint8_t* __restrict__ out, long ldo, int H) {
+  __shared__ float red[32];
+  const long t = blockIdx.x;
+  const bf16* xr = x + t * ldx;
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = __bfloat162float(xr[i]);
+      ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+    inv = rsqrtf(tot / (float)H + eps);
+  }
+  const float is = 1.f / *scale;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = __bfloat162float(xr[i]);
+    if (w) v = __bfloat162float(__float2bfloat16(v * inv * (__bfloat162float(w[i]) + (gemma ? 1.f : 0.f))));
+    out[t * ldo + i] = float_to_e4m3(v * is);
+  }
+}
+
+// NVFP4 activation quant: per 16 values, scale = e4m3(amax / 6 * gs) where gs is the global
+// scale (448 * 6 / tensor amax); values = e2m1(x * gs / scale). mode 0: x; mode 1: silu(gate) * up
+// with x = [gate | up] rows of width 2K. Scales row-major [T, K/16] or in the 128x4-swizzled
+// layout of block-scaled MMAs (swizzle = 1).
+__global__ void __launch_bounds__(128)
+    quant_nvfp4_kernel(const bf16* __restrict__ x, long ldx, const float* __restrict__ gscale,
+                       uint8_t* __restrict__ out, uint8_t* __restrict__ sf, long T, int K, int mode,
+                       int swizzle) {
+  const long groups = T * (long)(K / 16);
+  const float gs = *gscale;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < groups; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / (K / 16);
+    const int gidx = (int)(i % (K / 16));
+    const bf16* src = x + t * ldx + (long)gidx * 16;
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      float a = __bfloat162float(src[e]);
+      if (mode == 1) {
+        const float u = __bfloat162float(src[K + e]);
+        a = __bfloat162float(__float2bfloat16(a / (1.f + __expf(-a)) * u));
+      }
+      v[e] = a;
+      amax = fmaxf(amax, fabsf(a));
+    }
+    const uint8_t sb = float_to_e4m3(amax * gs / 6.f);
+    const float sdec = e4m3_to_float(sb);
+    const float mul = sdec > 0.f ? gs / sdec : 0.f;
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      w0 |= float_to_e2m1(v[e] * mul) << (e * 4);
+      w1 |= float_to_e2m1(v[8 + e] * mul) << (e * 4);
+    }
+    reinterpret_cast<uint2*>(out)[i] = make_uint2(w0, w1);
+    size_t so;
+    if (swizzle) {
+      // [T/128][K/64][32 rows][4 row-groups][4 k] bytes
+      const long rb = t / 128, r = t % 128;
+      const int kb = gidx / 4, kk = gidx % 4;
+      so = ((size_t)rb * (K / 64) + kb) * 512 + (size_t)(r % 32) * 16 + (size_t)(r / 32) * 4 + kk;
+    } else {
+      so = (size_t)i;
+    }
+    sf[so] = sb;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int ldo, const float* a_scale,
+                  const float* w_scale, int w_scale_per_channel, const void* bias, int M, int N, int K,
+                  cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 15) || (lda & 15) || (ldw & 15) || (N & 7) || (ldo & 7)) return -1;
+  CUtensorMap tmA, tmB;
+  if (!encode_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, kQM, kQKB, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldw, kQN, kQKB, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  Fp8Params p{};
+  p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
+  p.a_scale = a_scale; p.w_scale = w_scale; p.w_scale_per_channel = w_scale_per_channel;
+  p.bias = (const bf16*)bias;
+  p.tiles_m = (M + kQM - 1) / kQM; p.tiles_n = (N + kQN - 1) / kQN;
+  const int kblocks = (K + kQKB - 1) / kQKB;
+  p.stages = kblocks + 1 < 6 ? (kblocks + 1 < 2 ? 2 : kblocks + 1) : 6;
+  p.status = device_status_word();
+  const size_t smem = (size_t)p.stages * (kQM * kQKB + kQN * kQKB) + 1024 + sizeof(QBars);
+  static bool set = false;
+  if (!set) {
+    cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 6 * 32768 + 2048 + (int)sizeof(QBars));
+    set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
+  gemm_fp8_kernel<<<grid, kQThreads, smem, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, void* out, long N, int K,
+                       cudaStream_t stream) {
+  if (N <= 0 || K <= 0) return 0;
+  if (K & 15) return -1;
+  const long groups = N * (long)(K / 16);
+  long blocks = (groups + 255) / 256;
+  if (blocks > (long)b200_num_sms() * 16) blocks = (long)b200_num_sms() * 16;
+  nvfp4_dequant_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const uint8_t*)packed, (const uint8_t*)sf, gscale,
+                                                             (bf16*)out, N, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Small-M fused path (M <= 256, K a multiple of 64). workspace: fp32 [splits, M, N] for split-K.
+int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out,
+                    int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes,
+                    cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 256 || (K & 63) || (lda & 7) || (ldo & 7)) return -1;
+  W4Params p{};
+  p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
+  p.wq = (const uint8_t*)wq; p.sf = (const uint8_t*)sf; p.gscale = gscale; p.bias = (const bf16*)bias;
+  p.mp = (M + 15) & ~15;
+  p.status = device_status_word();
+  const int sms = b200_num_sms();
+  const int tiles_n = (N + 127) / 128, kblocks = K / 64;
+  int splits = 1;
+  if (tiles_n < sms) {
+    splits = sms / tiles_n;
+    if (splits > kblocks / 4) splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
+    if (splits > 16) splits = 16;
+    while (splits > 1 && (!workspace || (size_t)splits * M * N * 4 > ws_bytes)) --splits;
+  }
+  const int kb_per = (kblocks + splits - 1) / splits;
+  splits = (kblocks + kb_per - 1) / kb_per;
+  p.splits = splits; p.kb_per_split = kb_per; p.workspace = (float*)workspace;
+  const int stage_bytes = 16384 + p.mp * 128;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > kQMaxStages) stages = kQMaxStages;
+  if (stages > kb_per) stages = kb_per;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < p.mp) tmem_cols <<= 1;
+  CUtensorMap tmA;
+  if (!encode_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, p.mp, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  static bool set = false;
+  if (!set) {
+    cudaFuncSetAttribute(gemm_w4a16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    set = true;
+  }
+  const size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(QBars);
+  gemm_w4a16_swap_kernel<<<dim3(tiles_n, splits), kQThreads, smem, stream>>>(tmA, p, tmem_cols);
+  if (cudaGetLastError() != cudaSuccess) return -2;
+  if (splits > 1) {
+    const size_t total = (size_t)M * N;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > sms * 8) blocks = sms * 8;
+    w4_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, p.out, ldo, p.bias);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+  }
+  return 0;
+}
+
+int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int gemma, const float* scale,
+                   void* out, long ldo, long T, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  quant_fp8_kernel<<<(unsigned)T, 256, 0, stream>>>((const bf16*)x, ldx, (const bf16*)norm_w, eps, gemma, scale,
+                                                    (uint8_t*)out, ldo, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int b200_quant_nvfp4(const void* x, long ldx, const float* gscale, void* out, void* sf, long T, int K, int mode,
+                     int swizzle, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((K & 15) || (swizzle && (K & 63))) return -1;
+  const long groups = T * (long)(K / 16);
+  long blocks = (groups + 127) / 128;
+  if (blocks > (long)b200_num_sms() * 32) blocks = (long)b200_num_sms() * 32;
+  quant_nvfp4_kernel<<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)x, ldx, gscale, (uint8_t*)out, (uint8_t*)sf,
+                                                           T, K, mode, swizzle);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // extern "C"

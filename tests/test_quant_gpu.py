@@ -1,0 +1,88 @@
+"""fp8 tcgen05 GEMM, NVFP4 weight expansion + fused W4A16 GEMM, quantisation producers."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from vllm_cpp_b200 import ops  # noqa: E402
+from vllm_cpp_b200.ops import quant as Q  # noqa: E402
+
+DEV = "cuda"
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K,per_channel", [(128, 256, 256, False), (300, 520, 384, True), (7, 4096, 4096, False),
+                                               (1000, 1024, 2048, True)])
+def test_gemm_fp8(M, N, K, per_channel):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV) * 0.1
+    sa = (a.abs().max() / 448).reshape(1)
+    sw = (w.abs().amax(1) / 448) if per_channel else (w.abs().max() / 448).reshape(1)
+    a8 = (a / sa).to(torch.float8_e4m3fn)
+    w8 = (w / (sw[:, None] if per_channel else sw)).to(torch.float8_e4m3fn)
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    out = Q.gemm_fp8(a8, w8, sa.float(), sw.float().contiguous(), bias=bias)
+    exp = (a8.float() @ w8.float().t()) * sa * (sw[None, :] if per_channel else sw) + bias.float()
+    assert ops.read_status() == 0
+    assert _rel(out, exp) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (64, 4096, 4096), (256, 1024, 14336), (33, 520, 512),
+                                   (700, 1024, 1024)])
+def test_nvfp4_weights(M, N, K):
+    torch.manual_seed(1)
+    w = torch.randn(N, K, device=DEV) * 0.05
+    packed, sf, g = Q.ref_quant_nvfp4_weights(w)
+    wd = Q.ref_dequant_nvfp4(packed, sf, g)
+    assert _rel(wd, w) < 0.15                       # the format itself: 4-bit values
+    got = Q.nvfp4_dequant(packed, sf, g)
+    assert torch.equal(got.float(), wd.to(torch.bfloat16).float())
+    a = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    out = Q.gemm_w4a16(a, packed, sf, g, bias=bias)
+    exp = a.float() @ wd.to(torch.bfloat16).float().t() + bias.float()
+    assert ops.read_status() == 0
+    assert _rel(out, exp) < 1e-2
+
+
+def test_quant_fp8_static_and_rmsnorm():
+    torch.manual_seed(2)
+    x = (torch.randn(37, 512, device=DEV) * 3).to(torch.bfloat16)
+    scale = torch.tensor([0.05], device=DEV)
+    got = Q.quant_fp8(x, scale)
+    exp = (x.float() / 0.05).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (got.float() - exp.float()).abs().max() <= exp.float().abs().max() * 0.07
+    assert (got.view(torch.uint8) == exp.view(torch.uint8)).float().mean() > 0.98
+    w = (torch.rand(512, device=DEV) + 0.5).to(torch.bfloat16)
+    got = Q.quant_fp8(x, scale, norm_weight=w, eps=1e-6)
+    xf = x.float()
+    n = (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-6) * w.float()).to(torch.bfloat16).float()
+    exp = (n / 0.05).to(torch.float8_e4m3fn)
+    assert _rel(got.float(), exp.float()) < 2e-2
+
+
+def test_quant_nvfp4_activations():
+    torch.manual_seed(3)
+    T, K = 200, 256
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    gs = (448.0 * 6.0 / x.float().abs().max()).reshape(1).float()
+    packed, sf = Q.quant_nvfp4(x, gs)
+    deq = Q.ref_dequant_nvfp4(packed, sf, (1.0 / gs))
+    assert _rel(deq, x) < 0.12
+    # fused silu(gate) * up
+    gu = torch.randn(T, 2 * K, device=DEV).to(torch.bfloat16)
+    y = (torch.nn.functional.silu(gu[:, :K].float()) * gu[:, K:].float()).to(torch.bfloat16)
+    gs2 = (448.0 * 6.0 / y.float().abs().max()).reshape(1).float()
+    p2, s2 = Q.quant_nvfp4(gu, gs2, silu_mul=True)
+    assert _rel(Q.ref_dequant_nvfp4(p2, s2, 1.0 / gs2), y) < 0.12
+    # swizzled scale layout holds the same bytes
+    p3, s3 = Q.quant_nvfp4(x, gs, swizzle=True)
+    assert torch.equal(p3, packed)
+    t, gidx = 77, 5
+    off = ((t // 128) * (K // 64) + gidx // 4) * 512 + (t % 32) * 16 + ((t % 128) // 32) * 4 + gidx % 4
+    assert s3[off].item() == sf[t, gidx].item()

@@ -1,0 +1,123 @@
+"""Quantised GEMM wrappers (fp8 e4m3, NVFP4 weights x bf16 activations) and the activation /
+weight quantisation producers, with fp32 PyTorch restatements of the formats."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, workspace
+from ._lib import check, lib, ptr, stream_ptr
+
+_declared = False
+FP4_VALUES = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    P, I, L, F, Z = _lib.P, _lib.I, _lib.L, _lib.F, _lib.Z
+    _lib.declare("b200_gemm_fp8", [P, I, P, I, P, I, P, P, I, P, I, I, I, P], I)
+    _lib.declare("b200_nvfp4_dequant", [P, P, P, P, L, I, P], I)
+    _lib.declare("b200_gemm_w4a16", [P, I, P, P, P, P, I, P, I, I, I, P, Z, P], I)
+    _lib.declare("b200_quant_fp8", [P, L, P, F, I, P, P, L, L, I, P], I)
+    _lib.declare("b200_quant_nvfp4", [P, L, P, P, P, L, I, I, I, P], I)
+    lib()
+    _declared = True
+
+
+def gemm_fp8(a8, w8, a_scale, w_scale, out=None, bias=None):
+    """a8 [M, K], w8 [N, K] float8_e4m3fn; a_scale fp32 [1]; w_scale fp32 [1] or [N]."""
+    _declare()
+    M, K = a8.shape
+    N = w8.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+    check(lib().b200_gemm_fp8(ptr(a8), a8.stride(0), ptr(w8), w8.stride(0), ptr(out), out.stride(0),
+                              ptr(a_scale), ptr(w_scale), int(w_scale.numel() > 1), ptr(bias), M, N, K,
+                              stream_ptr()), "gemm_fp8")
+    return out
+
+
+def nvfp4_dequant(packed, sf, gscale, out=None):
+    _declare()
+    N, kh = packed.shape
+    if out is None:
+        out = torch.empty((N, kh * 2), dtype=torch.bfloat16, device=packed.device)
+    check(lib().b200_nvfp4_dequant(ptr(packed), ptr(sf), ptr(gscale), ptr(out), N, kh * 2, stream_ptr()),
+          "nvfp4_dequant")
+    return out
+
+
+def gemm_w4a16(a, packed, sf, gscale, out=None, bias=None, scratch=None):
+    """a bf16 [M, K]; packed uint8 [N, K/2]; sf e4m3 bytes [N, K/16]; gscale fp32 [1] (multiplier).
+    M <= 256 runs the fused expand-in-shared-memory kernel; larger M expands the matrix into
+    ``scratch`` (bf16 [N, K]) once and runs the bf16 GEMM."""
+    _declare()
+    from . import gemm
+    M, K = a.shape
+    N = packed.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    if M <= 256:
+        ws = workspace(a.device, 16 << 20, "w4")
+        check(lib().b200_gemm_w4a16(ptr(a), a.stride(0), ptr(packed), ptr(sf), ptr(gscale), ptr(out),
+                                    out.stride(0), ptr(bias), M, N, K, ptr(ws), ws.numel(), stream_ptr()),
+              "gemm_w4a16")
+        return out
+    if scratch is None:
+        scratch = torch.empty((N, K), dtype=torch.bfloat16, device=a.device)
+    nvfp4_dequant(packed, sf, gscale, scratch)
+    return gemm(a, scratch[:N], bias=bias, out=out)
+
+
+def quant_fp8(x, scale, out=None, norm_weight=None, eps=1e-6, gemma=False):
+    """fp8(x / scale), optionally after RMSNorm. Returns a float8_e4m3fn tensor."""
+    _declare()
+    T, H = x.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    check(lib().b200_quant_fp8(ptr(x), x.stride(0), ptr(norm_weight), eps, int(gemma), ptr(scale), ptr(out),
+                               out.stride(0), T, H, stream_ptr()), "quant_fp8")
+    return out
+
+
+def quant_nvfp4(x, gscale, K=None, silu_mul=False, swizzle=False):
+    """Returns (packed uint8 [T, K/2], block scales uint8). gscale fp32 [1]."""
+    _declare()
+    T = x.shape[0]
+    K = K or (x.shape[1] // 2 if silu_mul else x.shape[1])
+    packed = torch.empty((T, K // 2), dtype=torch.uint8, device=x.device)
+    n_sf = ((T + 127) // 128) * 128 * (K // 16) if swizzle else T * (K // 16)
+    sf = torch.zeros(n_sf, dtype=torch.uint8, device=x.device)
+    check(lib().b200_quant_nvfp4(ptr(x), x.stride(0), ptr(gscale), ptr(packed), ptr(sf), T, K,
+                                 int(silu_mul), int(swizzle), stream_ptr()), "quant_nvfp4")
+    return packed, (sf if swizzle else sf.view(T, K // 16))
+
+
+# ------------------------------------------------------------------------------ references
+def ref_quant_nvfp4_weights(w: torch.Tensor):
+    """Quantise an fp32/bf16 [N, K] matrix to NVFP4: (packed, e4m3 scale bytes, global scale
+    multiplier fp32 [1]) such that w ~= e2m1 * e4m3_scale * global."""
+    wf = w.float()
+    N, K = wf.shape
+    amax = wf.abs().max().clamp_min(1e-12)
+    g = (amax / (448.0 * 6.0)).reshape(1)                   # multiplier
+    blocks = wf.reshape(N, K // 16, 16)
+    bmax = blocks.abs().amax(-1)
+    s8 = (bmax / 6.0 / g).to(torch.float8_e4m3fn)
+    sdec = s8.float() * g
+    q = blocks / sdec.clamp_min(1e-30).unsqueeze(-1)
+    vals = torch.tensor(FP4_VALUES, device=w.device)
+    idx = (q.abs().unsqueeze(-1) - vals).abs().argmin(-1)
+    code = (idx | ((q < 0).long() << 3)).reshape(N, K).to(torch.uint8)
+    packed = (code[:, 0::2] | (code[:, 1::2] << 4)).contiguous()
+    return packed, s8.view(torch.uint8).contiguous(), g.to(torch.float32)
+
+
+def ref_dequant_nvfp4(packed, sf_bytes, g):
+    N, kh = packed.shape
+    vals = torch.tensor(FP4_VALUES + [-v for v in FP4_VALUES], device=packed.device)
+    p = packed.long()
+    v = torch.stack([vals[p & 15], vals[p >> 4]], -1).reshape(N, kh * 2)
+    s = sf_bytes.view(torch.float8_e4m3fn).float() * g.float()
+    return (v.reshape(N, -1, 16) * s.reshape(N, -1, 1)).reshape(N, kh * 2)
