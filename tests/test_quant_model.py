@@ -1,0 +1,48 @@
+"""NVFP4-weight models through the engine: the quantised CPU oracle differs from bf16 (the
+rounding is real) and the GPU W4A16 path reproduces the quantised oracle."""
+import pytest
+import torch
+
+from vllm_cpp_b200.config import EngineArgs, synthetic_config
+from vllm_cpp_b200.engine import LLM, SamplingParams
+
+
+def _run(dev, cfg, prompts, budget=256, n=8):
+    llm = LLM(EngineArgs(model_config=cfg, device=dev, block_size=16, num_blocks=128, max_model_len=512,
+                         max_num_seqs=4, max_num_batched_tokens=budget))
+    sp = SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True)
+    return llm, [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+
+
+def _prompts(cfg):
+    g = torch.Generator().manual_seed(9)
+    return [torch.randint(0, cfg.vocab_size, (k,), generator=g).tolist() for k in (40, 7, 300)]
+
+
+def test_quantised_cpu_model_runs_and_is_quantised():
+    from vllm_cpp_b200.models.backend import QuantWeight
+    cfg = synthetic_config("tiny-dense")
+    cfg.quant = "nvfp4"
+    llm, toks = _run("cpu", cfg, _prompts(cfg))
+    assert isinstance(llm.model.layers[0]["qkv"], QuantWeight)
+    assert all(len(t) == 8 for t in toks)
+    w = llm.model.layers[0]["qkv"]
+    # 4.5 bits per weight
+    assert w.numel() * 8 / (w.shape[0] * w.shape[1]) == 4.5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["tiny-dense", "tiny-gdn"])
+def test_quantised_gpu_matches_quantised_cpu(name):
+    from vllm_cpp_b200 import ops
+    cfg = synthetic_config(name)
+    cfg.quant = "nvfp4"
+    if name == "tiny-dense":
+        cfg.head_dim = 128
+    prompts = _prompts(cfg)
+    _, cpu = _run("cpu", cfg, prompts)
+    _, gpu = _run("cuda", cfg, prompts)
+    assert ops.read_status() == 0
+    assert [a[0] for a in gpu] == [a[0] for a in cpu]
+    hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(gpu, cpu))
+    assert hit / sum(len(a) for a in gpu) > 0.7

@@ -74,6 +74,9 @@ class LLM:
             self.model.load_weights(tensors)
         else:
             self.model.init_random(args.seed)
+        if getattr(cfg, "quant", None) == "nvfp4" and getattr(args, "quantize", True) \
+                and hasattr(self.model, "quantize_weights"):
+            self.model.quantize_weights("nvfp4")
         budget = args.resolve_max_num_batched_tokens(cfg)
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
         use_async = args.async_scheduling if args.async_scheduling is not None else False
@@ -86,8 +89,14 @@ class LLM:
                                async_scheduling=use_async,
                                enable_prefix_caching=args.resolve_prefix_caching(cfg))
         self.scheduler_config = sc
+        self.structured = None
+        if self.tokenizer is not None and hasattr(E, "StructuredOutputManager"):
+            tk = self.tokenizer
+            tb = [b"" if tk.is_special(i) else tk.token_bytes(i) for i in range(tk.vocab_size)]
+            eos = [e for e in {cfg.eos_token_id, tk.eos_id} if e is not None and e >= 0]
+            self.structured = E.StructuredOutputManager(tb, cfg.vocab_size, eos)
         self.core = E.EngineCore(sc, self.runner.kv_cache_config(), self.runner,
-                                 2 if use_async else 1)
+                                 2 if use_async else 1, self.structured)
         self.use_async = use_async
         self._counter = itertools.count()
         self._states: dict[str, RequestOutput] = {}

@@ -11,6 +11,39 @@ import torch
 from ..ops import reference as ref
 
 
+class QuantWeight:
+    """NVFP4 weight of a linear layer: E2M1 pairs, one E4M3 scale per 16 values, fp32 tensor
+    scale (multiplier). ``shape`` mimics the dense [N, K] weight it replaces."""
+
+    def __init__(self, packed, sf, gscale):
+        self.packed, self.sf, self.gscale = packed, sf, gscale
+        self.shape = (packed.shape[0], packed.shape[1] * 2)
+        self.device = packed.device
+        self._scratch = None
+
+    def numel(self):
+        return self.packed.numel() + self.sf.numel()
+
+    def element_size(self):
+        return 1
+
+    def data_ptr(self):
+        return self.packed.data_ptr()
+
+    def dequant(self):
+        from ..ops.quant import ref_dequant_nvfp4
+        return ref_dequant_nvfp4(self.packed, self.sf, self.gscale).to(torch.bfloat16)
+
+    @staticmethod
+    def from_dense(w: torch.Tensor) -> "QuantWeight":
+        from ..ops.quant import ref_quant_nvfp4_weights
+        packed, sf, g = ref_quant_nvfp4_weights(w)
+        return QuantWeight(packed, sf, g)
+
+
+_SHARED_SCRATCH: dict = {}
+
+
 class CpuBackend:
     name = "cpu"
 
@@ -18,6 +51,8 @@ class CpuBackend:
         self.device = torch.device(device)
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        if isinstance(w, QuantWeight):
+            w = w.dequant()
         y = ref.gemm(a, w, bias, residual, out_dtype)
         if out is not None:
             out.copy_(y)
@@ -100,6 +135,21 @@ class GpuBackend:
         ops.lib()  # fail loudly here if the kernel library is missing
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        if isinstance(w, QuantWeight):
+            from ..ops import quant as Q
+            N, K = w.shape
+            scratch = None
+            if a.shape[0] > 256:
+                # one expansion buffer per device, shared by every layer (stream ordered)
+                key = (a.device, N * K)
+                scratch = _SHARED_SCRATCH.get(key)
+                if scratch is None:
+                    scratch = torch.empty((N, K), dtype=torch.bfloat16, device=a.device)
+                    _SHARED_SCRATCH[key] = scratch
+            y = Q.gemm_w4a16(a, w.packed, w.sf, w.gscale, out=out, bias=bias, scratch=scratch)
+            if residual is not None:
+                y = self.ops.add(y, residual) if out is None else out.copy_(self.ops.add(y, residual))
+            return y
         return self.ops.gemm(a, w, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
 
     def rmsnorm(self, x, w, eps, residual=None, out=None, gemma=False):

@@ -175,6 +175,22 @@ class DenseModel:
                 L["k_norm"] = put(staged[p + "self_attn.k_norm.weight"])
             self.layers.append(L)
 
+    QUANT_KEYS = ("qkv", "o", "gate_up", "down", "in_proj", "out")
+
+    def quantize_weights(self, method: str = "nvfp4") -> None:
+        """Replaces the linear-layer weights by NVFP4 ``QuantWeight``s (values are rounded
+        once here, on whatever device holds them, so CPU oracle and GPU see the same
+        numbers)."""
+        if method != "nvfp4":
+            raise ValueError(f"unsupported weight quantisation {method!r}")
+        from .backend import QuantWeight
+        for L in self.layers:
+            for k in self.QUANT_KEYS:
+                w = L.get(k)
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 64 == 0:
+                    L[k] = QuantWeight.from_dense(w)
+        self.quantized = method
+
     # ------------------------------------------------------------------ KV cache
     def kv_cache_groups(self, block_size: int):
         """[(layer indices, spec dict)] -- one group for full attention; sliding-window
@@ -230,6 +246,8 @@ class DenseModel:
     # ------------------------------------------------------------------ forward
     # ------------------------------------------------------------------ fused TP forward
     def fused_tp_supported(self) -> bool:
+        if getattr(self, "quantized", None):
+            return False
         c = self.cfg
         return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
                 and not c.sandwich_norm and not c.post_norm and not c.attention_bias
