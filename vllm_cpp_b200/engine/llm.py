@@ -43,6 +43,9 @@ class RequestOutput:
     num_cached_tokens: int = 0
     prompt: Optional[str] = None
     metrics: dict = field(default_factory=dict)
+    detok: object = None          # incremental detokenizer (stop strings, UTF-8 hold-back)
+    delta: bool = False
+    delta_text: Optional[str] = None
 
 
 class LLM:
@@ -137,8 +140,17 @@ class LLM:
                              f"({self.max_model_len})")
         req = E.EngineCoreRequest(rid, toks, params, self.eos_token_id, time.monotonic(), priority)
         self.runner.set_eos(rid, self.eos_token_id)
+        if self.structured is not None and params.structured_outputs is not None \
+                and params.structured_outputs.any():
+            self.structured.validate(params.structured_outputs)    # raises on a bad constraint
         self.core.add_request(req)
-        self._states[rid] = RequestOutput(rid, toks, [CompletionOutput()], prompt=prompt)
+        st = RequestOutput(rid, toks, [CompletionOutput()], prompt=prompt)
+        if self.tokenizer is not None and params.detokenize:
+            st.detok = E.IncrementalDetokenizer(self.tokenizer, toks, params.skip_special_tokens,
+                                                list(params.stop), params.include_stop_str_in_output,
+                                                params.min_tokens)
+        st.delta = params.output_kind == E.OutputKind.DELTA
+        self._states[rid] = st
         return rid
 
     def abort_request(self, request_id: str) -> None:
@@ -160,6 +172,25 @@ class LLM:
             c = st.outputs[0]
             c.token_ids.extend(o.new_token_ids)
             st.num_cached_tokens = o.num_cached_tokens
+            stop_hit = None
+            if st.detok is not None and o.new_token_ids:
+                # the last token of a request that stopped on EOS / a stop token is not text
+                stop_terminated = (o.finished() and E.finish_reason_str(o.finish_reason) == "stop"
+                                   and (o.stop_reason is None or o.stop_reason.is_token))
+                stop_hit = st.detok.update(list(o.new_token_ids), bool(stop_terminated))
+                if stop_hit is not None and not o.finished():
+                    # a stop string ends the request here: drop it from the engine
+                    self.core.abort_requests([o.request_id])
+                    c.finish_reason, c.stop_reason = "stop", stop_hit
+                    st.finished = True
+                    self._states.pop(o.request_id, None)
+                finished_now = st.finished or o.finished()
+                piece = st.detok.get_next_output_text(finished_now, st.delta)
+                c.text = piece if st.delta else piece
+                st.delta_text = piece if st.delta else None
+            if st.finished:
+                done.append(st)
+                continue
             if o.new_logprobs:
                 c.logprobs = (c.logprobs or []) + list(o.new_logprobs)
             if o.finished():
@@ -198,7 +229,8 @@ class LLM:
         if self.tokenizer is not None:
             for o in outs:
                 for c in o.outputs:
-                    c.text = self.tokenizer.decode(c.token_ids)
+                    if o.detok is None:
+                        c.text = self.tokenizer.decode(c.token_ids)
         return outs
 
     def stats(self):
