@@ -1,0 +1,220 @@
+"""The C interface (include/vllm.h): exported symbols, header validity as C, and the whole
+surface driven through ctypes and from a plain C program that dlopens the library."""
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import sysconfig
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB = os.path.join(ROOT, "vllm_cpp_b200", "libvllm_b200.so")
+
+SYMBOLS = """vllm_model_params_default vllm_sampling_params_default vllm_engine_load vllm_engine_free
+vllm_complete vllm_complete_stream vllm_request_submit vllm_request_cancel vllm_request_wait vllm_request_done
+vllm_request_error vllm_request_free vllm_chat vllm_chat_stream vllm_string_free vllm_completion_free
+vllm_last_error vllm_version vllm_abi_version""".split()
+
+
+class ModelParams(ctypes.Structure):
+    _fields_ = [("model_path", ctypes.c_char_p), ("tokenizer_config_path", ctypes.c_char_p),
+                ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32), ("max_model_len", ctypes.c_int32),
+                ("max_num_seqs", ctypes.c_int32), ("tool_parser", ctypes.c_char_p),
+                ("reasoning_parser", ctypes.c_char_p), ("tensor_parallel_size", ctypes.c_int32),
+                ("enable_expert_parallel", ctypes.c_int32), ("device", ctypes.c_char_p)]
+
+
+class SamplingParams(ctypes.Structure):
+    _fields_ = [("temperature", ctypes.c_float), ("top_p", ctypes.c_float), ("top_k", ctypes.c_int32),
+                ("min_p", ctypes.c_float), ("max_tokens", ctypes.c_int32), ("seed", ctypes.c_uint64),
+                ("has_seed", ctypes.c_bool), ("presence_penalty", ctypes.c_float),
+                ("frequency_penalty", ctypes.c_float), ("repetition_penalty", ctypes.c_float),
+                ("min_tokens", ctypes.c_int32), ("ignore_eos", ctypes.c_bool),
+                ("stop", ctypes.POINTER(ctypes.c_char_p)), ("n_stop", ctypes.c_size_t),
+                ("structured_json", ctypes.c_char_p), ("structured_regex", ctypes.c_char_p),
+                ("structured_choice", ctypes.POINTER(ctypes.c_char_p)), ("n_structured_choice", ctypes.c_size_t),
+                ("structured_grammar", ctypes.c_char_p), ("structured_json_object", ctypes.c_bool)]
+
+
+class Completion(ctypes.Structure):
+    _fields_ = [("text", ctypes.c_void_p), ("finish_reason", ctypes.c_char_p),
+                ("prompt_tokens", ctypes.c_int32), ("completion_tokens", ctypes.c_int32)]
+
+
+CB = ctypes.CFUNCTYPE(ctypes.c_bool, ctypes.c_char_p, ctypes.c_bool, ctypes.c_void_p)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    assert os.path.exists(LIB), "C library not built"
+    l = ctypes.CDLL(LIB)
+    l.vllm_model_params_default.restype = ModelParams
+    l.vllm_sampling_params_default.restype = SamplingParams
+    l.vllm_last_error.restype = ctypes.c_char_p
+    l.vllm_version.restype = ctypes.c_char_p
+    l.vllm_request_error.restype = ctypes.c_char_p
+    l.vllm_request_done.restype = ctypes.c_bool
+    for f in ("vllm_engine_free", "vllm_request_cancel", "vllm_request_free", "vllm_string_free",
+              "vllm_completion_free"):
+        getattr(l, f).restype = None
+    l.vllm_engine_free.argtypes = [ctypes.c_void_p]
+    l.vllm_string_free.argtypes = [ctypes.c_void_p]
+    for f in ("vllm_request_cancel", "vllm_request_free", "vllm_request_wait", "vllm_request_done",
+              "vllm_request_error"):
+        getattr(l, f).argtypes = [ctypes.c_void_p]
+    l.vllm_engine_load.argtypes = [ctypes.POINTER(ModelParams), ctypes.POINTER(ctypes.c_void_p)]
+    l.vllm_complete.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), ctypes.POINTER(Completion)]
+    l.vllm_complete_stream.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), CB, ctypes.c_void_p]
+    l.vllm_request_submit.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), CB,
+                                      ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+    l.vllm_chat.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]
+    l.vllm_chat_stream.argtypes = [ctypes.c_void_p, ctypes.c_char_p, CB, ctypes.c_void_p]
+    return l
+
+
+@pytest.fixture(scope="module")
+def ckpt(tmp_path_factory):
+    from vllm_cpp_b200 import loader
+    from vllm_cpp_b200.config import synthetic_config
+    return loader.write_synthetic_checkpoint(str(tmp_path_factory.mktemp("c") / "ck"), synthetic_config("tiny-qwen3"), seed=5)
+
+
+def test_exported_symbols_and_header():
+    out = subprocess.run(["nm", "-D", "--defined-only", LIB], capture_output=True, text=True).stdout
+    exported = sorted(l.split()[-1] for l in out.splitlines() if " T " in l)
+    assert exported == sorted(SYMBOLS)           # exactly the 19 entry points, nothing else
+    hdr = os.path.join(ROOT, "include", "vllm.h")
+    r = subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", hdr],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
+def test_defaults_and_errors(lib):
+    assert lib.vllm_abi_version() == 6 and lib.vllm_version()
+    mp, sp = lib.vllm_model_params_default(), lib.vllm_sampling_params_default()
+    assert (mp.block_size, mp.num_blocks, mp.max_num_seqs, mp.tensor_parallel_size) == (32, 256, 8, 1)
+    assert sp.repetition_penalty == 1.0 and sp.temperature == 1.0 and sp.top_p == 1.0
+    eng = ctypes.c_void_p()
+    assert lib.vllm_engine_load(None, ctypes.byref(eng)) == 1 and b"required" in lib.vllm_last_error()
+    mp.model_path = b"/nonexistent/model"
+    mp.device = b"cpu"
+    assert lib.vllm_engine_load(ctypes.byref(mp), ctypes.byref(eng)) in (2, 3) and not eng.value
+    assert lib.vllm_last_error()
+    lib.vllm_engine_free(None)                   # no-op
+    assert lib.vllm_request_done(None)
+
+
+def test_full_surface_through_ctypes(lib, ckpt):
+    mp = lib.vllm_model_params_default()
+    mp.model_path, mp.device, mp.max_model_len, mp.block_size = ckpt.encode(), b"cpu", 256, 16
+    eng = ctypes.c_void_p()
+    assert lib.vllm_engine_load(ctypes.byref(mp), ctypes.byref(eng)) == 0, lib.vllm_last_error()
+    sp = lib.vllm_sampling_params_default()
+    sp.temperature, sp.max_tokens = 0.0, 6
+    out = Completion()
+    assert lib.vllm_complete(eng, b"The quick brown fox", ctypes.byref(sp), ctypes.byref(out)) == 0
+    text = ctypes.string_at(out.text).decode()
+    assert out.prompt_tokens > 0 and 0 < out.completion_tokens <= 6 and out.finish_reason in (b"length", b"stop")
+    lib.vllm_completion_free(ctypes.byref(out))
+    assert not out.text
+    # streaming gives the same text; zeroed params are refused
+    pieces = []
+    cb = CB(lambda d, fin, u: pieces.append((d.decode(), fin)) or True)
+    assert lib.vllm_complete_stream(eng, b"The quick brown fox", ctypes.byref(sp), cb, None) == 0
+    assert "".join(p for p, _ in pieces) == text and pieces[-1][1] is True
+    zero = SamplingParams()
+    assert lib.vllm_complete(eng, b"x", ctypes.byref(zero), ctypes.byref(out)) == 1
+    assert b"repetition_penalty" in lib.vllm_last_error()
+    # returning false stops early and is still OK
+    seen = []
+    stop_cb = CB(lambda d, fin, u: (seen.append(d), False)[1])
+    sp.max_tokens = 64
+    assert lib.vllm_complete_stream(eng, b"abc", ctypes.byref(sp), stop_cb, None) == 0 and len(seen) <= 3
+    # structured output through the POD fields
+    choices = (ctypes.c_char_p * 2)(b"yes", b"no")
+    sp2 = lib.vllm_sampling_params_default()
+    sp2.max_tokens, sp2.structured_choice, sp2.n_structured_choice = 8, choices, 2
+    assert lib.vllm_complete(eng, b"Answer:", ctypes.byref(sp2), ctypes.byref(out)) == 0
+    assert ctypes.string_at(out.text) in (b"yes", b"no")
+    lib.vllm_completion_free(ctypes.byref(out))
+    # non-blocking request
+    got = []
+    cb2 = CB(lambda d, fin, u: got.append((d, fin)) or True)
+    sp.max_tokens = 5
+    req = ctypes.c_void_p()
+    assert lib.vllm_request_submit(eng, b"hello", ctypes.byref(sp), cb2, None, ctypes.byref(req)) == 0
+    assert lib.vllm_request_wait(req) == 0 and lib.vllm_request_done(req) and lib.vllm_request_error(req) is None
+    assert got and got[-1][1] is True
+    lib.vllm_request_cancel(req)                 # idempotent after completion
+    lib.vllm_request_free(req)
+    # chat: JSON in, JSON out, and chunks
+    body = json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0}).encode()
+    js = ctypes.c_void_p()
+    assert lib.vllm_chat(eng, body, ctypes.byref(js)) == 0, lib.vllm_last_error()
+    resp = json.loads(ctypes.string_at(js).decode())
+    lib.vllm_string_free(js)
+    assert resp["object"] == "chat.completion" and resp["choices"][0]["message"]["role"] == "assistant"
+    chunks = []
+    cb3 = CB(lambda d, fin, u: chunks.append((d.decode(), fin)) or True)
+    assert lib.vllm_chat_stream(eng, body, cb3, None) == 0
+    assert chunks[-1] == ("", True) and json.loads(chunks[0][0])["object"] == "chat.completion.chunk"
+    streamed = "".join(json.loads(c)["choices"][0]["delta"].get("content", "") for c, f in chunks[:-1]
+                       if json.loads(c)["choices"])
+    assert streamed == (resp["choices"][0]["message"]["content"] or "")
+    assert lib.vllm_chat(eng, b"{not json", ctypes.byref(js)) != 0
+    lib.vllm_engine_free(eng)
+
+
+C_PROGRAM = r"""
+#include <dlfcn.h>
+#include <stdio.h>
+#include <string.h>
+#include "vllm.h"
+typedef vllm_model_params (*mpd_t)(void);
+typedef vllm_sampling_params (*spd_t)(void);
+typedef vllm_status (*load_t)(const vllm_model_params*, vllm_engine**);
+typedef vllm_status (*complete_t)(vllm_engine*, const char*, const vllm_sampling_params*, vllm_completion*);
+typedef void (*cfree_t)(vllm_completion*);
+typedef void (*efree_t)(vllm_engine*);
+typedef const char* (*err_t)(void);
+int main(int argc, char** argv) {
+  void* h = dlopen(argv[1], RTLD_NOW | RTLD_GLOBAL);
+  if (!h) { fprintf(stderr, "dlopen: %s\n", dlerror()); return 2; }
+  mpd_t mpd = (mpd_t)dlsym(h, "vllm_model_params_default");
+  spd_t spd = (spd_t)dlsym(h, "vllm_sampling_params_default");
+  load_t load = (load_t)dlsym(h, "vllm_engine_load");
+  complete_t complete = (complete_t)dlsym(h, "vllm_complete");
+  cfree_t cfree = (cfree_t)dlsym(h, "vllm_completion_free");
+  efree_t efree = (efree_t)dlsym(h, "vllm_engine_free");
+  err_t err = (err_t)dlsym(h, "vllm_last_error");
+  vllm_model_params mp = mpd();
+  mp.model_path = argv[2]; mp.device = "cpu"; mp.max_model_len = 128; mp.block_size = 16;
+  vllm_engine* e = NULL;
+  if (load(&mp, &e) != VLLM_OK) { fprintf(stderr, "load: %s\n", err()); return 3; }
+  vllm_sampling_params sp = spd();
+  sp.temperature = 0.0f; sp.max_tokens = 4;
+  vllm_completion c;
+  if (complete(e, "The quick", &sp, &c) != VLLM_OK) { fprintf(stderr, "complete: %s\n", err()); return 4; }
+  printf("OK %d %d %s\n", c.prompt_tokens, c.completion_tokens, c.finish_reason);
+  cfree(&c);
+  efree(e);
+  return 0;
+}
+"""
+
+
+def test_plain_c_program_with_dlopen(tmp_path, ckpt):
+    src = tmp_path / "drv.c"
+    src.write_text(C_PROGRAM)
+    exe = tmp_path / "drv"
+    r = subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-ldl"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    env = dict(os.environ)
+    site = sysconfig.get_paths()["purelib"]
+    env["PYTHONPATH"] = os.pathsep.join([ROOT, site, env.get("PYTHONPATH", "")])
+    r = subprocess.run([str(exe), LIB, ckpt], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.startswith("OK ") and r.stdout.split()[2] in ("1", "2", "3", "4")

@@ -93,16 +93,29 @@ def build_engine(verbose: bool = False) -> Path:
             list(ex.map(_run, jobs))
     if jobs or not out.exists():
         _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
-    capi = PKG / "libvllm_b200.so"
-    capi_objs = [o for o in objs if "bindings" not in o.name]
-    if capi_objs and (jobs or not capi.exists()):
-        _run([CXX, "-shared", "-o", str(capi), *map(str, capi_objs), "-pthread", "-ldl",
-              f"-Wl,--version-script={CSRC / 'engine' / 'capi' / 'export.map'}"]
-             if (CSRC / "engine" / "capi" / "export.map").exists() else
-             [CXX, "-shared", "-o", str(capi), *map(str, capi_objs), "-pthread", "-ldl"])
+    build_capi(verbose)
     if verbose:
         print(f"built {out} from {len(srcs)} C++ sources ({len(jobs)} recompiled)")
     return out
+
+
+def build_capi(verbose: bool = False) -> Path:
+    """``libvllm_b200.so``: the C interface of ``include/vllm.h``. It embeds the interpreter, so
+    it links against libpython; only the ``vllm_*`` symbols are exported."""
+    capi = PKG / "libvllm_b200.so"
+    srcs = sorted((CSRC / "capi").glob("*.cpp"))
+    if not srcs:
+        return capi
+    hdrs = [ROOT / "include" / "vllm.h"]
+    if any(_newer(s, hdrs, capi) for s in srcs):
+        libdir = sysconfig.get_config_var("LIBDIR") or "/usr/lib"
+        ver = sysconfig.get_config_var("LDVERSION") or "3.12"
+        _run([CXX, *CXX_FLAGS, "-I", sysconfig.get_paths()["include"], "-shared", "-o", str(capi),
+              *map(str, srcs), "-pthread", "-ldl", f"-L{libdir}", f"-lpython{ver}",
+              f"-Wl,--version-script={CSRC / 'capi' / 'export.map'}", f"-Wl,-rpath,{libdir}"])
+        if verbose:
+            print(f"built {capi}")
+    return capi
 
 
 def build_all(verbose: bool = False) -> None:
