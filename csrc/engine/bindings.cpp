@@ -56,6 +56,7 @@ struct EngineCoreHolder {
   std::unique_ptr<InprocClient> client;
   py::object runner_ref;  // keeps the Python runner alive
   py::object so_ref;      // keeps the structured-output manager alive
+  py::object kv_ref;      // keeps the KV connector alive
 };
 
 }  // namespace
@@ -416,22 +417,25 @@ PYBIND11_MODULE(_engine, m) {
 
   py::class_<EngineCoreHolder>(m, "EngineCore")
       .def(py::init([](const SchedulerConfig& c, const KVCacheConfig& k, py::object runner,
-                       int max_concurrent_batches, py::object structured) {
+                       int max_concurrent_batches, py::object structured, py::object connector) {
              auto h = std::make_unique<EngineCoreHolder>();
              h->runner_ref = runner;
              h->so_ref = structured;
+             h->kv_ref = connector;
+             KVConnectorHook* kv_hook = connector.is_none() ? nullptr : connector.cast<KVConnectorHook*>();
              StructuredOutputHook* so_hook =
                  structured.is_none() ? nullptr : structured.cast<StructuredOutputHook*>();
              ModelRunnerBase* rb = runner.cast<ModelRunnerBase*>();
              h->executor = std::make_unique<Executor>(rb, max_concurrent_batches);
              std::unique_ptr<Scheduler> s;
-             if (c.async_scheduling) s = std::make_unique<AsyncScheduler>(c, k, so_hook);
-             else s = std::make_unique<Scheduler>(c, k, so_hook);
+             if (c.async_scheduling) s = std::make_unique<AsyncScheduler>(c, k, so_hook, kv_hook);
+             else s = std::make_unique<Scheduler>(c, k, so_hook, kv_hook);
              h->core = std::make_unique<EngineCore>(std::move(s), h->executor.get());
              return h;
            }),
            py::arg("scheduler_config"), py::arg("kv_cache_config"), py::arg("runner"),
-           py::arg("max_concurrent_batches") = 1, py::arg("structured_output_manager") = py::none())
+           py::arg("max_concurrent_batches") = 1, py::arg("structured_output_manager") = py::none(),
+           py::arg("kv_connector") = py::none())
       .def("add_request", [](EngineCoreHolder& h, const EngineCoreRequest& r) { h.core->add_request(r); })
       .def("abort_requests", [](EngineCoreHolder& h, std::vector<std::string> ids) { h.core->abort_requests(ids); })
       .def("step", [](EngineCoreHolder& h) { return h.core->step(); })

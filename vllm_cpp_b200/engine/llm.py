@@ -98,8 +98,17 @@ class LLM:
             tb = [b"" if tk.is_special(i) else tk.token_bytes(i) for i in range(tk.vocab_size)]
             eos = [e for e in {cfg.eos_token_id, tk.eos_id} if e is not None and e >= 0]
             self.structured = E.StructuredOutputManager(tb, cfg.vocab_size, eos)
+        self.offload = None
+        if args.kv_transfer_config:
+            from ..worker.offload import KVOffloadWorker
+            caches = self.model.kv_caches
+            caches = list(caches.values()) if isinstance(caches, dict) else list(caches)
+            self.offload = KVOffloadWorker(caches, args.block_size, args.kv_transfer_config,
+                                           model_id=f"{cfg.architecture}:{cfg.hidden_size}x{cfg.num_layers}")
+            self.runner.offload = self.offload
         self.core = E.EngineCore(sc, self.runner.kv_cache_config(), self.runner,
-                                 2 if use_async else 1, self.structured)
+                                 2 if use_async else 1, self.structured,
+                                 self.offload.connector if self.offload else None)
         self.use_async = use_async
         self._counter = itertools.count()
         self._states: dict[str, RequestOutput] = {}

@@ -238,8 +238,12 @@ class ModelRunner(E.ModelRunnerBase):
         torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ step
+    offload = None   # KVOffloadWorker when KV offloading is configured
+
     def execute_model(self, so) -> None:
         self.batch.update_states(so)
+        if self.offload is not None:
+            self.offload.run_step_plan()
         if so.total_num_scheduled_tokens == 0:
             self._info = None
             return
