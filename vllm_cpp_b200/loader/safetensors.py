@@ -90,7 +90,10 @@ class SafetensorsFile:
         if en == b:
             return torch.empty(shape, dtype=tdt)
         buf = memoryview(self._mm)[self.data_start + b: self.data_start + en]
-        t = torch.frombuffer(buf, dtype=torch.uint8).view(tdt)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)   # read-only mmap: tensors are never written
+            t = torch.frombuffer(buf, dtype=torch.uint8).view(tdt)
         return t.reshape(shape)
 
     def release(self, name: str) -> None:
