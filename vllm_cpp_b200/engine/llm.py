@@ -49,7 +49,9 @@ class RequestOutput:
 
 
 class LLM:
-    def __init__(self, args: EngineArgs | None = None, **kw):
+    def __init__(self, args: EngineArgs | None = None, comm=None, **kw):
+        """``comm``: a communicator to use instead of the one built from ``args.parallel``
+        (host-mock ranks in tests)."""
         if args is None:
             args = EngineArgs(**kw)
         self.args = args
@@ -63,7 +65,7 @@ class LLM:
             cfg, tensors, self.tokenizer = load_model_dir(args.model, args.tokenizer)
         self.cfg = cfg
         par = args.parallel
-        self.comm = self._make_comm(par)
+        self.comm = comm if comm is not None else self._make_comm(par)
         device = torch.device(args.device)
         if device.type == "cuda":
             torch.cuda.set_device(par.local_rank)
