@@ -104,3 +104,23 @@ def test_async_scheduling_same_tokens_as_sync():
     assert llm.use_async
     assert a == b
     assert ops.read_status() == 0
+
+
+@pytest.mark.gpu
+def test_opt_model_gpu_vs_cpu():
+    from vllm_cpp_b200.config import EngineArgs, synthetic_config
+    from vllm_cpp_b200.engine import LLM, SamplingParams
+    cfg = synthetic_config("tiny-opt")
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (60, 9, 130)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+
+    def run(dev):
+        llm = LLM(EngineArgs(model_config=cfg, device=dev, block_size=16, num_blocks=128, max_model_len=512,
+                             max_num_seqs=4, max_num_batched_tokens=64))
+        return [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+
+    gpu, cpu = run("cuda"), run("cpu")
+    assert [a[0] for a in gpu] == [a[0] for a in cpu]
+    hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(gpu, cpu))
+    assert hit / sum(len(a) for a in gpu) > 0.7

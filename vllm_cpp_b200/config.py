@@ -314,6 +314,9 @@ def synthetic_config(name: str) -> ModelConfig:
         if n == "tiny-qwen3":
             return ModelConfig(architecture="Qwen3ForCausalLM", qk_norm=True,
                                tie_word_embeddings=True, **base)
+        if n == "tiny-opt":
+            return ModelConfig(architecture="OPTForCausalLM", hidden_act="relu", tie_word_embeddings=True,
+                               **{**base, "num_kv_heads": 4})
         if n == "tiny-mla":
             base.update(head_dim=192, num_heads=4, num_kv_heads=4)
             return ModelConfig(architecture="DeepseekV2ForCausalLM", num_experts=8, num_experts_per_tok=2,

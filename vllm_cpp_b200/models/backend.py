@@ -95,7 +95,7 @@ class CpuBackend:
         q, k, v = ref.rope_kv(qkv, positions, table, num_q_heads, num_kv_heads, head_dim, rot_dim,
                               neox, q_norm, k_norm, eps, gemma)
         T = qkv.shape[0]
-        qkv[:, : num_q_heads * head_dim] = q.reshape(T, -1)
+        qkv[:, : num_q_heads * head_dim] = q.reshape(T, -1).clone()
         if kv_cache is not None:
             ref.write_kv_cache(kv_cache, k, v, slot_mapping, block_size)
 
