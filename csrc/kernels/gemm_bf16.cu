@@ -61,6 +61,14 @@ struct GemmParams {
   const uint32_t* ag_flags;
   int ag_flag_parity_stride;
   const uint32_t* op_counter;     // device-side op counter; its low bit selects the parity
+  // ---- stream-K (tn kernel only) ---------------------------------------------------------
+  // The (tile, k-block) units are cut into gridDim.x equal contiguous ranges. A CTA whose range
+  // starts inside a tile writes that fp32 partial to sk_partials[cta] and raises
+  // sk_flags[cta * 4 + warp quarter]; the CTA that holds the tile's first k-block adds the
+  // partials of the CTAs after it and runs the epilogue, then clears the flags it consumed.
+  int sk;                         // number of leading tiles in the stream-K region (0 = none)
+  float* sk_partials;
+  uint32_t* sk_flags;
 };
 
 // Bounded system-scope acquire wait on a counter another GPU increments.
@@ -104,6 +112,60 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   int r = t - g * per_group;
   tm = first_m + (r % gsz);
   tn = r / gsz;
+}
+
+// Work iterator shared by the three warp roles. Plain mode: whole tiles strided over the workers
+// (a worker is a CTA, or a CTA pair in the pair kernel). Stream-K mode: the first p.sk tiles are
+// cut into (tile, k-block) units and dealt out as equal contiguous ranges, one per worker; the
+// remaining tiles follow as whole tiles. Workers that run whole tiles side by side step through
+// K together and share their operand tiles in L2; the stream-K region, where they do not, is
+// kept to the ragged part of the problem and runs first so that its fix-up hides under the rest.
+struct SegState {
+  int sk_tiles, t, stride, u, u1;
+};
+__device__ __forceinline__ int sk_range_start_w(int w, int units, int nworkers) {
+  const int q = units / nworkers, r = units % nworkers;
+  return w * q + min(w, r);
+}
+__device__ __forceinline__ SegState seg_init_w(const GemmParams& p, int kblocks, int worker,
+                                               int nworkers) {
+  SegState s;
+  s.sk_tiles = p.sk;
+  s.t = p.sk + worker;
+  s.stride = nworkers;
+  s.u = sk_range_start_w(worker, p.sk * kblocks, nworkers);
+  s.u1 = sk_range_start_w(worker + 1, p.sk * kblocks, nworkers);
+  return s;
+}
+__device__ __forceinline__ bool seg_next(SegState& s, int num_tiles, int kblocks, int& t, int& kb0,
+                                         int& kb1) {
+  if (s.u < s.u1) {
+    t = s.u / kblocks;
+    kb0 = s.u - t * kblocks;
+    kb1 = min(kblocks, kb0 + (s.u1 - s.u));
+    s.u += kb1 - kb0;
+    return true;
+  }
+  if (s.t >= num_tiles) return false;
+  t = s.t;
+  kb0 = 0;
+  kb1 = kblocks;
+  s.t += s.stride;
+  return true;
+}
+// Bounded device-scope acquire wait for a stream-K partial flag.
+__device__ __forceinline__ bool wait_flag_set(const uint32_t* f, int* status) {
+  long long t0 = clock64();
+  uint32_t it = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v != 0) return true;
+    if (((++it) & 0xff) == 0 && clock64() - t0 > kPeerWaitCycles) {
+      if (status) atomicExch(status, (int)kErrFlagTimeout);
+      return false;
+    }
+  }
 }
 
 template <int BN>
@@ -155,7 +217,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      SegState seg = seg_init_w(p, kblocks, blockIdx.x, gridDim.x);
+      int t, kb0, kb1;
+      while (ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         if (p.ag_flags) {
@@ -168,7 +232,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!ok) break;
           fence_proxy_async_global();
         }
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { ok = false; break; }
@@ -187,13 +251,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+      SegState seg = seg_init_w(p, kblocks, blockIdx.x, gridDim.x);
+      int t, kb0, kb1;
+      for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
         int buf = tc & 1;
         uint32_t aph = (tc >> 1) & 1;
         if (!mbar_wait(&bars->acc_empty[buf], aph ^ 1, p.status)) { ok = false; break; }
         tc_fence_after_sync();
         uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
           if (!mbar_wait(&bars->full[s], ph, p.status)) { ok = false; break; }
@@ -205,7 +271,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
             // +32 bytes per 16-element K step inside the 128-byte swizzle row.
-            umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
           }
           umma_commit(&bars->empty[s]);
         }
@@ -218,7 +284,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int quarter = warp & 3;
     uint32_t tc = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+    SegState seg = seg_init_w(p, kblocks, blockIdx.x, gridDim.x);
+    int t, kb0, kb1;
+    for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       int buf = tc & 1;
@@ -229,6 +297,44 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_after_sync();
       const int row = tm * kBM + quarter * 32 + lane;
       const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      if (kb0 > 0) {
+        // stream-K partial: raw fp32 accumulators to this CTA's slot, then the flag
+        // column-major inside the slot: the 32 lanes of a warp write 32 consecutive floats
+        float* dst = p.sk_partials + (size_t)blockIdx.x * kBM * BN + quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)(c * 32 + i) * kBM, __uint_as_float(r[i]));
+        }
+        __threadfence();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t one = 1;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + blockIdx.x * 4 + quarter),
+                       "r"(one)
+                       : "memory");
+          mbar_arrive(&bars->acc_empty[buf]);
+        }
+        continue;
+      }
+      // stream-K owner: the CTAs after this one hold the rest of the tile's k-blocks
+      int sk_first = 0, sk_last = -1;
+      if (kb1 < kblocks) {
+        const int tile_end = (t + 1) * kblocks;
+        sk_first = blockIdx.x + 1;
+        sk_last = blockIdx.x;
+        while (sk_last + 1 < (int)gridDim.x &&
+               sk_range_start_w(sk_last + 1, p.sk * kblocks, (int)gridDim.x) < tile_end)
+          ++sk_last;
+        for (int x = sk_first; x <= sk_last && ok; ++x)
+          ok = wait_flag_set(p.sk_flags + x * 4 + quarter, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -239,6 +345,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          for (int x = sk_first; x <= sk_last; ++x) {
+            const float* src = p.sk_partials + (size_t)x * kBM * BN + (size_t)c * 32 * kBM + quarter * 32 + lane;
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __ldcg(src + (size_t)i * kBM);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += f[i];
+          }
           if (p.bias) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
@@ -319,7 +433,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->acc_empty[buf]);
+      if (lane == 0) {
+        for (int x = sk_first; x <= sk_last; ++x) p.sk_flags[x * 4 + quarter] = 0;
+        mbar_arrive(&bars->acc_empty[buf]);
+      }
     }
   }
 
@@ -327,6 +444,261 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN >= 32 ? 2 * BN : 32);
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair kernel: a cluster of two CTAs computes a 256 x BN tile with cta_group::2 MMAs.
+// Per 64-wide k-block each CTA stages its 128 rows of A and its BN/2 rows of W (32 KB for
+// BN = 256, against 48 KB per CTA for the same 128 x 256 outputs in the 1-CTA kernel), so the
+// L2 -> shared-memory traffic per FLOP drops by a third. The even CTA issues every MMA; each
+// CTA's TMEM holds its 128 rows of the accumulator and its own epilogue warps store them.
+// Barriers: full[s] lives in the leader and counts the bytes of both CTAs' loads; empty[s],
+// acc_full[b] are signalled in both CTAs by the leader's commits; acc_empty[b] lives in the
+// leader and collects the eight epilogue warps of the pair.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, float (&v)[32], int row,
+                                                     int col0) {
+  if (p.bias) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      if (col0 + i < p.N) {
+        uint4 b = *reinterpret_cast<const uint4*>(p.bias + col0 + i);
+        float2 f;
+        f = unpack_bf16x2(b.x); v[i + 0] += f.x; v[i + 1] += f.y;
+        f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+        f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+        f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+      }
+    }
+  }
+  if (p.residual) {
+    const __nv_bfloat16* rr = p.residual + (size_t)row * p.ldr + col0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      if (col0 + i < p.N) {
+        uint4 b = *reinterpret_cast<const uint4*>(rr + i);
+        float2 f;
+        f = unpack_bf16x2(b.x); v[i + 0] += f.x; v[i + 1] += f.y;
+        f = unpack_bf16x2(b.y); v[i + 2] += f.x; v[i + 3] += f.y;
+        f = unpack_bf16x2(b.z); v[i + 4] += f.x; v[i + 5] += f.y;
+        f = unpack_bf16x2(b.w); v[i + 6] += f.x; v[i + 7] += f.y;
+      }
+    }
+  }
+  if (p.out_f32) {
+    float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldo + col0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      if (col0 + i < p.N)
+        *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldo + col0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      if (col0 + i < p.N) {
+        uint4 w;
+        w.x = pack_bf16x2(v[i + 0], v[i + 1]);
+        w.y = pack_bf16x2(v[i + 2], v[i + 3]);
+        w.z = pack_bf16x2(v[i + 4], v[i + 5]);
+        w.w = pack_bf16x2(v[i + 6], v[i + 7]);
+        *reinterpret_cast<uint4*>(o + i) = w;
+      }
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  constexpr int kABytes = kBM * kBK * 2;
+  constexpr int kBBytes = (BN / 2) * kBK * 2;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  const int stages = p.stages;
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + (size_t)stages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const int num_tiles = p.tiles_m * p.tiles_n;      // tiles_m counts 256-row tiles here
+  const int kblocks = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->acc_full[b], 1);
+      mbar_init(&bars->acc_empty[b], 8);
+    }
+    bars->failed = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();            // the peer's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      SegState seg = seg_init_w(p, kblocks, pair, npairs);
+      int t, kb0, kb1;
+      while (ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1)) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          int s = it % stages;
+          uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { ok = false; break; }
+          uint8_t* a_dst = smem + (size_t)s * kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
+          const uint32_t leader_bar = mapa_u32(smem_u32(&bars->full[s]), 0);
+          tma_load_2d_pair(a_dst, &tmA, leader_bar, kb * kBK, tm * 2 * kBM + (int)rank * kBM);
+          tma_load_2d_pair(b_dst, &tmB, leader_bar, kb * kBK, tn * BN + (int)rank * (BN / 2));
+        }
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * kBM, BN);
+      uint32_t it = 0, tc = 0;
+      bool ok = true;
+      SegState seg = seg_init_w(p, kblocks, pair, npairs);
+      int t, kb0, kb1;
+      for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
+        int buf = tc & 1;
+        uint32_t aph = (tc >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[buf], aph ^ 1, p.status)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          int s = it % stages;
+          uint32_t ph = (it / stages) & 1;
+          if (!mbar_wait(&bars->full[s], ph, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes);
+          uint32_t b_addr = a_addr + kABytes;
+          uint64_t adesc = umma_desc_k_sw128(a_addr, 1024);
+          uint64_t bdesc = umma_desc_k_sw128(b_addr, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_bf16_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
+          umma_commit_pair(&bars->empty[s], 3);
+        }
+        if (ok) umma_commit_pair(&bars->acc_full[buf], 3);
+      }
+      if (!ok) bars->failed = 1;
+    }
+  } else {
+    // ---------------- Epilogue (warps 2..5 of both CTAs) ----------------
+    const int quarter = warp & 3;
+    const int me = blockIdx.x;                        // partial slot / flag owner
+    uint32_t tc = 0;
+    bool ok = true;
+    SegState seg = seg_init_w(p, kblocks, pair, npairs);
+    int t, kb0, kb1;
+    for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      int buf = tc & 1;
+      uint32_t aph = (tc >> 1) & 1;
+      ok = mbar_wait(&bars->acc_full[buf], aph, p.status);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tm * 2 * kBM + (int)rank * kBM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t leader_acc_empty = mapa_u32(smem_u32(&bars->acc_empty[buf]), 0);
+      if (kb0 > 0) {
+        float* dst = p.sk_partials + (size_t)me * kBM * BN + quarter * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)(c * 32 + i) * kBM, __uint_as_float(r[i]));
+        }
+        __threadfence();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t one = 1;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.sk_flags + me * 4 + quarter), "r"(one)
+                       : "memory");
+          mbar_arrive_cluster(leader_acc_empty);
+        }
+        continue;
+      }
+      int sk_first = 0, sk_last = -1;                 // contributing pairs
+      if (kb1 < kblocks) {
+        const int tile_end = (t + 1) * kblocks;
+        sk_first = pair + 1;
+        sk_last = pair;
+        while (sk_last + 1 < npairs && sk_range_start_w(sk_last + 1, p.sk * kblocks, npairs) < tile_end)
+          ++sk_last;
+        for (int x = sk_first; x <= sk_last && ok; ++x)
+          ok = wait_flag_set(p.sk_flags + (x * 2 + (int)rank) * 4 + quarter, p.status);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = tn * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          for (int x = sk_first; x <= sk_last; ++x) {
+            const float* src = p.sk_partials + (size_t)(x * 2 + (int)rank) * kBM * BN +
+                               (size_t)c * 32 * kBM + quarter * 32 + lane;
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __ldcg(src + (size_t)i * kBM);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += f[i];
+          }
+          epilogue_store_chunk(p, v, row, col0);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        for (int x = sk_first; x <= sk_last; ++x) p.sk_flags[(x * 2 + (int)rank) * 4 + quarter] = 0;
+        mbar_arrive_cluster(leader_acc_empty);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();            // neither CTA frees while the other still reads its accumulators
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -574,6 +946,61 @@ static bool get_tmap_bf16(CUtensorMap* out, const void* p, uint64_t rows, uint64
 
 static constexpr int kSmemBudget = 220 * 1024;
 
+// Stream-K scratch of the current device: one 128 x 256 fp32 partial per CTA plus four flags per
+// CTA. Allocated on first use outside stream capture; GEMMs that share it must be ordered on one
+// stream (two streams running stream-K GEMMs at once would mix their partials).
+static bool streamk_scratch(cudaStream_t stream, float** partials, uint32_t** flags) {
+  static std::mutex mu;
+  static float* g_part[64] = {};
+  static uint32_t* g_flags[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!g_part[dev]) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone)
+      return false;
+    const size_t n = (size_t)b200_num_sms() * kBM * 256 * sizeof(float);
+    float* pp = nullptr;
+    uint32_t* ff = nullptr;
+    if (cudaMalloc(&pp, n) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaMalloc(&ff, (size_t)b200_num_sms() * 4 * sizeof(uint32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(pp);
+      return false;
+    }
+    cudaMemset(ff, 0, (size_t)b200_num_sms() * 4 * sizeof(uint32_t));
+    g_part[dev] = pp;
+    g_flags[dev] = ff;
+  }
+  *partials = g_part[dev];
+  *flags = g_flags[dev];
+  return true;
+}
+
+// Stream-K plan for `tiles` tiles of `kblocks` k-blocks on at most `max_workers` workers.
+// Fewer tiles than workers: every tile is cut into the same number of parts (workers that share
+// an operand stay in step). Otherwise only the tiles of the ragged last wave are cut.
+static void plan_streamk(long tiles, int kblocks, int max_workers, int* nworkers, int* sk_tiles) {
+  *nworkers = tiles < max_workers ? (int)tiles : max_workers;
+  *sk_tiles = 0;
+  if (kblocks < 16 || tiles <= 0) return;
+  if (tiles < max_workers) {
+    int parts = max_workers / (int)tiles;
+    while (parts >= 2 && kblocks / parts < 8) --parts;
+    if (parts >= 2) {
+      *nworkers = (int)tiles * parts;
+      *sk_tiles = (int)tiles;
+    }
+    return;
+  }
+  const int r = (int)(tiles % max_workers);
+  if (r == 0 || r * 100 >= max_workers * 85) return;
+  // a sliver of a wave would be cut too finely (one owner summing dozens of partials): take a
+  // whole wave into the region with it
+  *sk_tiles = ((long)r * kblocks < 8l * max_workers) ? r + max_workers : r;
+}
+
 template <int BN>
 static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
                      GemmParams& p, cudaStream_t stream) {
@@ -593,8 +1020,77 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
   }
   int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
+  if (p.sk) {   // on entry: stream-K wanted; from here on: tiles in the stream-K region
+    int sk_tiles = 0;
+    plan_streamk(tiles, kblocks, b200_num_sms(), &grid, &sk_tiles);
+    if (sk_tiles && !streamk_scratch(stream, &p.sk_partials, &p.sk_flags)) {
+      sk_tiles = 0;
+      grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
+    }
+    p.sk = sk_tiles;
+  }
   gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmA2, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// CTA-pair launch: clusters of two, as many as can be resident at once (at most one per SM pair).
+template <int BN>
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
+                       cudaStream_t stream) {
+  constexpr int stage_bytes = kBM * kBK * 2 + (BN / 2) * kBK * 2;
+  int stages = (kSmemBudget - 2048) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  int kblocks = (p.K + kBK - 1) / kBK;
+  if (stages > kblocks + 1) stages = kblocks + 1;
+  if (stages < 2) stages = 2;
+  p.stages = stages;
+  size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+  static int max_clusters[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -2;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kSmemBudget + 4096;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!max_clusters[dev]) {
+    cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         kSmemBudget + 4096);
+    cfg.gridDim = dim3(b200_num_sms() & ~1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel<BN>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      return -2;
+    }
+    max_clusters[dev] = n;
+  }
+  const long tiles = (long)p.tiles_m * p.tiles_n;
+  int max_pairs = max_clusters[dev];
+  if (max_pairs > b200_num_sms() / 2) max_pairs = b200_num_sms() / 2;
+  int pairs = tiles < max_pairs ? (int)tiles : max_pairs;
+  if (p.sk) {
+    int sk_tiles = 0;
+    plan_streamk(tiles, kblocks, max_pairs, &pairs, &sk_tiles);
+    if (sk_tiles && !streamk_scratch(stream, &p.sk_partials, &p.sk_flags)) {
+      sk_tiles = 0;
+      pairs = tiles < max_pairs ? (int)tiles : max_pairs;
+    }
+    p.sk = sk_tiles;
+  }
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.dynamicSmemBytes = smem;
+  if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN>, tmA, tmB, p) != cudaSuccess) {
+    cudaGetLastError();
+    return -2;
+  }
+  return 0;
 }
 
 }  // namespace b200
@@ -751,6 +1247,28 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   bool use256 = (waves256 * 2 * 100 <= waves128 * 108);
   if (force_path == 3) use256 = false;
   if (force_path == 4) use256 = true;
+  // force_path: 0 auto | 1 tiled 1-CTA | 3 / 4 1-CTA with BN 128 / 256 | 5 / 6 1-CTA BN 256 / 128
+  // with stream-K | 7 / 8 CTA pairs with 256 x 256 / 256 x 128 tiles | 9 / 10 pairs with stream-K.
+  // Plain GEMMs above the small-M range run on CTA pairs; the tensor-parallel prologue and
+  // epilogue live in the 1-CTA kernel.
+  if (force_path == 5) { use256 = true; p.sk = !tp; }
+  if (force_path == 6) { use256 = false; p.sk = !tp; }
+  const bool pair_path = !tp && (force_path == 0 || (force_path >= 7 && force_path <= 10));
+  if (pair_path) {
+    const bool bn256 = force_path == 0 ? (N > 128) : (force_path == 7 || force_path == 9);
+    p.sk = (force_path == 0 || force_path >= 9) ? 1 : 0;
+    p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+    CUtensorMap tA, tB;
+    if (!get_tmap_bf16(&tA, A, M, K, lda, kBM, kBK)) return -3;
+    if (bn256) {
+      p.tiles_n = tn256;
+      if (!get_tmap_bf16(&tB, W, N, K, ldw, 128, kBK)) return -3;
+      return launch_pair<256>(tA, tB, p, stream);
+    }
+    p.tiles_n = tn128;
+    if (!get_tmap_bf16(&tB, W, N, K, ldw, 64, kBK)) return -3;
+    return launch_pair<128>(tA, tB, p, stream);
+  }
   CUtensorMap tmA, tmA2, tmB;
   if (!get_tmap_bf16(&tmA, A, M, K, lda, kBM, kBK)) return -3;
   tmA2 = tmA;

@@ -20,8 +20,9 @@ def _run(dev, cfg, prompts, budget, max_tokens=6):
     return [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
 
 
-def test_hybrid_cpu_chunked_prefill_matches_unchunked():
-    cfg = synthetic_config("tiny-gdn")
+@pytest.mark.parametrize("shape", ["tiny-gdn", "tiny-gdn-moe"])
+def test_hybrid_cpu_chunked_prefill_matches_unchunked(shape):
+    cfg = synthetic_config(shape)
     prompts = _prompts(cfg, (70, 5, 33))
     whole = _run("cpu", cfg, prompts, 256)
     chunked = _run("cpu", cfg, prompts, 32)      # prompts split over several steps
@@ -31,9 +32,10 @@ def test_hybrid_cpu_chunked_prefill_matches_unchunked():
 
 
 @pytest.mark.gpu
-def test_hybrid_gpu_vs_cpu():
+@pytest.mark.parametrize("shape", ["tiny-gdn", "tiny-gdn-moe"])
+def test_hybrid_gpu_vs_cpu(shape):
     from vllm_cpp_b200 import ops
-    cfg = synthetic_config("tiny-gdn")
+    cfg = synthetic_config(shape)
     prompts = _prompts(cfg, (150, 9, 70))
     cpu = _run("cpu", cfg, prompts, 256, 8)
     for budget in (256, 64):

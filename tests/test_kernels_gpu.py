@@ -38,6 +38,25 @@ def test_gemm_tiled(M, N, K, path):
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1280, 4096, 4096), (1280, 4096, 14336), (384, 4096, 4096),
+                                   (1000, 6144, 4096), (130, 512, 8192), (520, 4104, 1024),
+                                   (128, 256, 64)])
+@pytest.mark.parametrize("path", [0, 5, 6])
+def test_gemm_stream_k(M, N, K, path):
+    """Stream-K: tiles are cut along K across CTAs and fixed up through fp32 partials. Run twice:
+    the second launch only works if the first one cleared every flag it consumed."""
+    torch.manual_seed(2)
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    r = _rand(M, N)
+    exp = ref.gemm(a, w)
+    for _ in range(2):
+        out = ops.gemm(a, w, force_path=path)
+        assert _rel_err(out, exp) < 6e-3
+    out = ops.gemm(a, w, residual=r, force_path=path, out_dtype=torch.float32)
+    assert _rel_err(out, exp + r.float()) < 6e-3
+    assert ops.read_status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (16, 128, 64), (33, 4096, 14336),
                                    (64, 28672, 4096), (200, 1024, 1024), (256, 4096, 4096),
                                    (5, 128256, 1024)])

@@ -334,6 +334,19 @@ def synthetic_config(name: str) -> ModelConfig:
                                linear_key_head_dim=128, linear_value_head_dim=128,
                                linear_conv_kernel_dim=4, tie_word_embeddings=True,
                                **{**base, "rope": RopeConfig(theta=1e4, rotary_dim=64)})
+        if n == "tiny-gdn-moe":
+            base.update(num_layers=4, head_dim=256, num_heads=2, num_kv_heads=1)
+            return ModelConfig(architecture="Qwen3_5MoeForConditionalGeneration", qk_norm=True,
+                               gemma_norm=True, attn_output_gate=True,
+                               layer_types=["full_attention" if (i + 1) % 4 == 0 else "linear_attention"
+                                            for i in range(4)],
+                               linear_num_key_heads=2, linear_num_value_heads=4,
+                               linear_key_head_dim=128, linear_value_head_dim=128,
+                               linear_conv_kernel_dim=4, tie_word_embeddings=True,
+                               num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128,
+                               shared_expert_intermediate_size=256, num_shared_experts=1,
+                               shared_expert_gate=True, norm_topk_prob=True,
+                               **{**base, "rope": RopeConfig(theta=1e4, rotary_dim=64)})
         if n == "tiny-moe":
             return ModelConfig(architecture="Qwen3MoeForCausalLM", qk_norm=True, num_experts=8,
                                num_experts_per_tok=2, moe_intermediate_size=128, **base)

@@ -19,6 +19,7 @@ import torch
 from ..config import ModelConfig, ParallelConfig
 from .base import StepContext, shard_cols, shard_rows
 from .dense import ACT_KIND, DenseModel
+from .moe import MoeModel
 
 
 def _round_up(a, b):
@@ -45,6 +46,16 @@ class Qwen35Model(DenseModel):
         self.attn_layers = [l for l in range(c.num_layers) if not self.is_gdn[l]]
         self.gdn_layers = [l for l in range(c.num_layers) if self.is_gdn[l]]
         self.has_moe = bool(c.num_experts)
+        if self.has_moe:
+            # expert block of the MoE hybrids (35B-A3B, Qwen3-Next): routed experts sharded whole
+            # per rank, one shared expert sharded like a dense MLP, scaled by a sigmoid gate
+            self.E, self.k, self.moe_inter = c.num_experts, c.num_experts_per_tok, c.moe_intermediate_size
+            self.ep = self.tp
+            assert self.E % self.ep == 0
+            self.e_local = self.E // self.ep
+            self.e0 = self.rank * self.e_local if self.ep > 1 else 0
+            self.shared_inter = c.shared_expert_intermediate_size // self.tp
+            self.moe_ws = None
         self.gdn_ws = None
         self.conv_state: dict[int, torch.Tensor] = {}
         self.ssm_state: dict[int, torch.Tensor] = {}
@@ -90,6 +101,17 @@ class Qwen35Model(DenseModel):
                     yield q + "o_proj.weight", full((H, c.num_heads * D))
                     yield q + "q_norm.weight", torch.zeros(D, dtype=self.dtype)
                     yield q + "k_norm.weight", torch.zeros(D, dtype=self.dtype)
+                if self.has_moe:
+                    I, S = c.moe_intermediate_size, c.shared_expert_intermediate_size
+                    yield p + "mlp.gate.weight", full((c.num_experts, H), 0.5)
+                    yield p + "mlp.experts.gate_up_proj", full((c.num_experts, 2 * I, H))
+                    yield p + "mlp.experts.down_proj", full((c.num_experts, H, I))
+                    if S:
+                        yield p + "mlp.shared_expert.gate_proj.weight", full((S, H))
+                        yield p + "mlp.shared_expert.up_proj.weight", full((S, H))
+                        yield p + "mlp.shared_expert.down_proj.weight", full((H, S))
+                        yield p + "mlp.shared_expert_gate.weight", full((1, H), 0.2)
+                    continue
                 yield p + "mlp.gate_proj.weight", full((c.intermediate_size, H))
                 yield p + "mlp.up_proj.weight", full((c.intermediate_size, H))
                 yield p + "mlp.down_proj.weight", full((H, c.intermediate_size))
@@ -215,8 +237,49 @@ class Qwen35Model(DenseModel):
                     del P["gate_proj"], P["up_proj"]
             elif rest == "mlp.down_proj.weight":
                 L["down"] = put(shard_cols(t, r, tp))
+            elif self.has_moe and rest.startswith("mlp."):
+                self._load_moe_tensor(L, P, parts, rest, t, put)
+        if self.has_moe:
+            e0, el = self.e0, self.e_local
+            for l, P in pend.items():
+                pe = P.get("pe")
+                if not pe:
+                    continue
+                L = self.layers[l]
+                L["w_gate_up"] = put(torch.stack([torch.cat([pe[(e, "gate_proj")], pe[(e, "up_proj")]], 0)
+                                                  for e in range(e0, e0 + el)], 0))
+                L["w_down"] = put(torch.stack([pe[(e, "down_proj")] for e in range(e0, e0 + el)], 0))
         if c.tie_word_embeddings or "lm_head" not in self.w:
             self.w["lm_head"] = self.w["embed"]
+
+    def _load_moe_tensor(self, L, P, parts, rest, t, put) -> None:
+        """Expert-block tensors: fused ``experts.gate_up_proj`` [E, 2I, H] / ``experts.down_proj``
+        [E, H, I] or one tensor per expert, the shared expert and its scalar gate."""
+        tp, r = self.tp, self.rank
+        e0, el = self.e0, self.e_local
+        if rest == "mlp.gate.weight":
+            L["router"] = put(t)
+        elif rest in ("mlp.experts.gate_up_proj", "mlp.experts.gate_up_proj.weight"):
+            L["w_gate_up"] = put(t[e0:e0 + el])
+        elif rest in ("mlp.experts.down_proj", "mlp.experts.down_proj.weight"):
+            L["w_down"] = put(t[e0:e0 + el])
+        elif len(parts) >= 8 and parts[4] == "experts" and parts[5].isdigit():
+            e = int(parts[5])
+            if e0 <= e < e0 + el:
+                P.setdefault("pe", {})[(e, parts[6])] = t
+        elif rest in ("mlp.shared_expert.gate_proj.weight", "mlp.shared_expert.up_proj.weight"):
+            P["s_" + parts[5]] = t
+            if "s_gate_proj" in P and "s_up_proj" in P:
+                L["s_gate_up"] = put(torch.cat([shard_rows(P["s_gate_proj"], r, tp),
+                                                shard_rows(P["s_up_proj"], r, tp)], 0))
+                del P["s_gate_proj"], P["s_up_proj"]
+        elif rest == "mlp.shared_expert.down_proj.weight":
+            L["s_down"] = put(shard_cols(t, r, tp))
+        elif rest == "mlp.shared_expert_gate.weight":
+            # [1, H] padded to 8 rows so that it runs through the GEMM path
+            g = torch.zeros(8, t.shape[-1], dtype=t.dtype, device=t.device)
+            g[0] = t.reshape(-1)
+            L["s_gate"] = put(g)
 
     # ------------------------------------------------------------------ caches
     def kv_cache_groups(self, block_size: int):
@@ -257,9 +320,43 @@ class Qwen35Model(DenseModel):
         if self.device.type == "cuda":
             from ..ops.gdn import GdnWorkspace
             self.gdn_ws = GdnWorkspace(self.device, max_tokens, max_reqs, self.gv)
+        if self.has_moe:
+            self.bufs.reserve("router", max_tokens, self.E, torch.float32)
+            self.bufs.reserve("moe_out", max_tokens, c.hidden_size)
+            self.bufs.reserve("s_gate_up", max_tokens, max(2 * self.shared_inter, 8))
+            self.bufs.reserve("s_act", max_tokens, max(self.shared_inter, 8))
+            self.bufs.reserve("s_out", max_tokens, c.hidden_size)
+            self.bufs.reserve("s_gate", max_tokens, 8, torch.float32)
+            if self.device.type == "cuda":
+                from ..ops.moe import MoeWorkspace
+                self.moe_ws = MoeWorkspace(self.device, max_tokens, self.k, self.e_local,
+                                           c.hidden_size, self.moe_inter)
 
     def fused_tp_supported(self) -> bool:
         return False
+
+    # ------------------------------------------------------------------ expert block
+    _moe_block = MoeModel._moe_block
+    _moe_block_cpu = MoeModel._moe_block_cpu
+
+    def _expert_block(self, x: torch.Tensor, L: dict, T: int, act_kind: int) -> torch.Tensor:
+        """routed(x) + sigmoid(x . w_g) * shared(x); each rank returns its partial sum (its
+        experts, its slice of the shared expert), the caller all-reduces."""
+        c, be = self.cfg, self.be
+        H = c.hidden_size
+        routed = self._moe_block(x, L, T)
+        hidden = self.bufs.get("hidden", T, H)
+        if "s_gate_up" not in L:
+            hidden.copy_(routed)
+            return hidden
+        gu = self.bufs.get("s_gate_up", T, 2 * self.shared_inter)
+        be.gemm(x, L["s_gate_up"], out=gu)
+        a_ = be.act_and_mul(gu, act_kind, out=self.bufs.get("s_act", T, self.shared_inter))
+        so = be.gemm(a_, L["s_down"], out=self.bufs.get("s_out", T, H))
+        g = be.gemm(x, L["s_gate"], out=self.bufs.get("s_gate", T, 8, torch.float32),
+                    out_dtype=torch.float32)
+        hidden.copy_(torch.addcmul(routed.float(), torch.sigmoid(g[:, :1]), so.float()))
+        return hidden
 
     # ------------------------------------------------------------------ GDN layer
     def _gdn_layer(self, l: int, L: dict, x: torch.Tensor, ctx: StepContext, T: int, meta: dict):
@@ -410,9 +507,12 @@ class Qwen35Model(DenseModel):
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
             x = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed, gemma=True)
-            be.gemm(x, L["gate_up"], out=gate_up)
-            a_ = be.act_and_mul(gate_up, act_kind, out=act)
-            be.gemm(a_, L["down"], out=hidden)
+            if self.has_moe:
+                hidden = self._expert_block(x, L, T, act_kind)
+            else:
+                be.gemm(x, L["gate_up"], out=gate_up)
+                a_ = be.act_and_mul(gate_up, act_kind, out=act)
+                be.gemm(a_, L["down"], out=hidden)
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
         full = be.rmsnorm(hidden, self.w["final_norm"], eps, residual=resid, out=normed, gemma=True)
