@@ -25,6 +25,7 @@ enum KernelError : int {
   kErrMbarTimeout = 1,   // an mbarrier wait inside a pipeline gave up
   kErrFlagTimeout = 2,   // a peer flag wait (fused collective) gave up
   kErrBadArg = 3,
+  kErrBadAlign = 4,      // dynamic shared memory base not 1024-byte aligned
 };
 
 // 2^31 cycles is about 1.1 s at 1.9 GHz.
@@ -68,6 +69,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Pure poll (never suspends the thread), for issuers that watch several barriers at once.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)

@@ -261,6 +261,31 @@ def test_attn_decode(D, Hq, Hkv, bs, splits):
     assert _rel_err(out2, exp2) < 1e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv,bs,splits", [(32, 8, 32, 1), (16, 4, 16, 3)])
+def test_attn_decode_tcgen05_persistent(Hq, Hkv, bs, splits):
+    """More (sequence, kv head, split) items than resident CTAs: every CTA walks several items
+    (some of them empty) and the rings run across the item boundaries."""
+    torch.manual_seed(22)
+    D = 128
+    B = 100 if Hkv == 8 else 60
+    gen = torch.Generator().manual_seed(5)
+    seq_lens = torch.randint(0, 600, (B,), generator=gen).tolist()
+    seq_lens[3] = 0
+    seq_lens[7] = 128
+    seq_lens[11] = 1
+    cache, bt = _make_paged([max(s, 1) for s in seq_lens], Hkv, D, bs)
+    q = _rand(B, Hq * D)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    qs = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    kw = dict(block_table=bt, seq_lens=sl, num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+              block_size=bs, scale=D ** -0.5, splits=splits)
+    exp = ref.paged_attention(q, cache, bt, sl, qs, Hq, Hkv, D, bs, D ** -0.5)
+    for _ in range(2):
+        out = ops.attn_decode(q, cache, **kw)
+        assert ops.read_status() == 0
+        assert _rel_err(out, exp) < 1e-2
+
+
 @pytest.mark.parametrize("Hq,Hkv,bs,splits", [(32, 8, 16, 0), (4, 1, 32, 1), (32, 4, 16, 3),
                                               (16, 16, 64, 2), (8, 1, 128, 4), (16, 1, 16, 2)])
 def test_attn_decode_tcgen05(Hq, Hkv, bs, splits):
