@@ -108,6 +108,12 @@ def main() -> int:
     ap.add_argument("--input-len", type=int, default=INPUT_LEN)
     ap.add_argument("--output-len", type=int, default=OUTPUT_LEN)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="diagnostic: override the number of layers (the JSON line then carries "
+                         "layers_override and is not a benchmark result)")
+    ap.add_argument("--verbose", action="store_true", help="phase timestamps on stderr")
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds after which every rank dumps its Python stacks and exits")
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
     ap.add_argument("--sync-scheduling", action="store_true",
                     help="schedule step N+1 only after step N's tokens are on the host")
@@ -117,8 +123,19 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
 
+    import faulthandler
+    if args.watchdog > 0:
+        # a rank stuck in a collective or a kernel wait must not hold the GPUs: dump and leave
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     import torch
     import torch.distributed as dist
+
+    t_start = time.perf_counter()
+
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {os.environ.get('RANK', '0')} +{time.perf_counter() - t_start:7.1f}s] {msg}",
+                  file=sys.stderr, flush=True)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -134,6 +151,10 @@ def main() -> int:
     from vllm_cpp_b200.ops import _lib
 
     cfg = synthetic_config(args.model)
+    if args.layers > 0:
+        cfg.num_layers = args.layers
+        if cfg.layer_types:
+            cfg.layer_types = cfg.layer_types[: args.layers]
     C, IN, OUT = args.concurrency, args.input_len, args.output_len
     block = 32
     max_len = IN + OUT + block
@@ -144,6 +165,7 @@ def main() -> int:
         enable_cuda_graphs=not args.no_graphs, enable_prefix_caching=True,
         async_scheduling=not args.sync_scheduling,
         parallel=ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank)))
+    note("engine built")
     gen = torch.Generator().manual_seed(1)
 
     def new_prompt():
@@ -155,6 +177,7 @@ def main() -> int:
 
     # ---- ramp to steady state (untimed): staggered output lengths for the first wave
     llm.runner.warmup_graphs()
+    note("graphs captured")
     for i in range(C):
         submit(1 + (i * OUT) // C)
     ramp_steps = 0
@@ -176,8 +199,11 @@ def main() -> int:
     while first_wave & set(llm._states.keys()):
         step_and_refill()
         ramp_steps += 1
+        if args.verbose and ramp_steps % 32 == 1:
+            note(f"ramp step {ramp_steps}")
         if ramp_steps > 4 * OUT + 64:
             break
+    note(f"ramp done after {ramp_steps} steps")
 
     def barrier():
         if world > 1:
@@ -232,14 +258,41 @@ def main() -> int:
                        "max_num_batched_tokens": args.max_num_batched_tokens,
                        "l2": "weights (16 GB) and KV (>40 GB) per step exceed L2 (126 MB)",
                        "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs,
-                       "async_scheduling": not args.sync_scheduling},
+                       "async_scheduling": not args.sync_scheduling,
+                       **({"layers_override": args.layers} if args.layers > 0 else {})},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "wall_ms_per_step": round(wall_ms / args.steps, 4)},
             "gpu_launches": int(launches), "output_tokens": tokens, "kernel_status": status,
         }))
     if world > 1:
-        dist.destroy_process_group()
+        # Orderly teardown: nothing in flight on any rank, drop what holds the communicator (the
+        # captured decode graphs contain NCCL kernels, the fused-TP context maps peer memory),
+        # then destroy the process group. Destruction has been seen to block with live graphs,
+        # so it runs beside a timer; the process leaves with code 0 either way.
+        sys.stdout.flush()
+        dist.barrier()
+        torch.cuda.synchronize()
+        llm.runner.graphs.clear()
+        if getattr(llm.model, "tpf", None) is not None:
+            llm.model.tpf = None
+        import gc
+        import threading
+        gc.collect()
+        torch.cuda.synchronize()
+        done = threading.Event()
+
+        def destroy():
+            try:
+                dist.destroy_process_group()
+            finally:
+                done.set()
+
+        threading.Thread(target=destroy, daemon=True).start()
+        done.wait(timeout=30)
+        note("process group destroyed" if done.is_set() else "process group destruction timed out")
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

@@ -484,7 +484,9 @@ PYBIND11_MODULE(_engine, m) {
 
   // ---- worker-side input preparation
   py::class_<StepLayout>(m, "StepLayout")
-      .def_static("make", &StepLayout::make)
+      .def_static("make", &StepLayout::make, py::arg("max_tokens"), py::arg("max_reqs"),
+                  py::arg("max_blocks"), py::arg("num_groups"), py::arg("max_spec") = 0)
+      .def_readonly("max_logits", &StepLayout::max_logits)
       .def_readonly("max_tokens", &StepLayout::max_tokens)
       .def_readonly("max_reqs", &StepLayout::max_reqs)
       .def_readonly("max_blocks", &StepLayout::max_blocks)
@@ -523,6 +525,8 @@ PYBIND11_MODULE(_engine, m) {
       .def_readonly("req_ids", &StepInfo::req_ids)
       .def_readonly("num_scheduled", &StepInfo::num_scheduled)
       .def_readonly("produces_token", &StepInfo::produces_token)
+      .def_readonly("num_draft", &StepInfo::num_draft)
+      .def_readonly("logits_row0", &StepInfo::logits_row0)
       .def_readonly("max_logprobs", &StepInfo::max_logprobs);
   py::class_<InputBatch>(m, "InputBatch")
       .def(py::init<int, int, int, std::vector<int>>())
@@ -532,6 +536,12 @@ PYBIND11_MODULE(_engine, m) {
         return b.prepare(so, l, reinterpret_cast<uint8_t*>(buf), async_mode);
       }, py::arg("scheduler_output"), py::arg("layout"), py::arg("buffer_ptr"),
            py::arg("async_mode") = false)
+      .def("propose_ngram", &InputBatch::propose_ngram)
+      .def("num_tokens", [](const InputBatch& b, const std::string& id) {
+        const CachedRequestState* s = b.get(id);
+        return s ? (int)s->token_ids.size() : -1;
+      })
+      .def("plain_greedy", &InputBatch::plain_greedy)
       .def("append_sampled", &InputBatch::append_sampled)
       .def("num_requests", &InputBatch::num_requests)
       .def("token_ids", [](InputBatch& b, const std::string& id) {

@@ -8,8 +8,10 @@ namespace b200 {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-StepLayout StepLayout::make(int max_tokens, int max_reqs, int max_blocks, int num_groups) {
+StepLayout StepLayout::make(int max_tokens, int max_reqs, int max_blocks, int num_groups,
+                            int max_spec) {
   StepLayout l;
+  l.max_logits = max_reqs * (1 + (max_spec > 0 ? max_spec : 0));
   l.max_tokens = max_tokens;
   l.max_reqs = max_reqs;
   l.max_blocks = max_blocks;
@@ -27,7 +29,7 @@ StepLayout StepLayout::make(int max_tokens, int max_reqs, int max_blocks, int nu
   l.query_start = take(4ull * (max_reqs + 1));
   l.seq_lens = take(4ull * max_reqs);
   l.block_table = take(4ull * num_groups * max_reqs * max_blocks);
-  l.logits_indices = take(4ull * max_reqs);
+  l.logits_indices = take(4ull * l.max_logits);
   l.tile_req = take(4ull * l.max_tiles);
   l.tile_q0 = take(4ull * l.max_tiles);
   l.prefill_q_start = take(4ull * (max_reqs + 1));
@@ -43,7 +45,7 @@ StepLayout StepLayout::make(int max_tokens, int max_reqs, int max_blocks, int nu
   l.pres_pen = take(4ull * max_reqs);
   l.splice_dst = take(4ull * max_reqs);
   l.splice_src = take(4ull * max_reqs);
-  l.sample_rows = take(4ull * max_reqs);
+  l.sample_rows = take(4ull * l.max_logits);
   l.total_bytes = off;
   return l;
 }
@@ -65,6 +67,37 @@ int InputBatch::alloc_state_slot() {
 const CachedRequestState* InputBatch::get(const std::string& id) const {
   auto it = reqs_.find(id);
   return it == reqs_.end() ? nullptr : &it->second;
+}
+
+std::vector<int32_t> InputBatch::propose_ngram(const std::string& id, int min_n, int max_n,
+                                                int k) const {
+  std::vector<int32_t> out;
+  auto it = reqs_.find(id);
+  if (it == reqs_.end() || k <= 0) return out;
+  const std::vector<int32_t>& t = it->second.token_ids;
+  const int n_tok = (int)t.size();
+  for (int n = std::min(max_n, n_tok - 1); n >= std::max(1, min_n); --n) {
+    const int32_t* tail = t.data() + n_tok - n;
+    for (int start = n_tok - n - 1; start >= 0; --start) {
+      if (!std::equal(tail, tail + n, t.data() + start)) continue;
+      const int f0 = start + n, f1 = std::min(n_tok, f0 + k);
+      if (f1 > f0) {
+        out.assign(t.begin() + f0, t.begin() + f1);
+        return out;
+      }
+    }
+  }
+  return out;
+}
+
+bool InputBatch::plain_greedy(const std::string& id) const {
+  auto it = reqs_.find(id);
+  if (it == reqs_.end()) return false;
+  const SamplingParams& sp = it->second.sampling_params;
+  const int n_out = (int)it->second.token_ids.size() - it->second.num_prompt_tokens;
+  return sp.temperature < kSamplingEps && !sp.has_penalties() && sp.logit_bias.empty() &&
+         sp.allowed_token_ids.empty() && sp.bad_words_token_ids.empty() && !sp.logprobs &&
+         n_out >= sp.min_tokens;
 }
 
 void InputBatch::update_states(const SchedulerOutput& so) {
@@ -119,13 +152,15 @@ void InputBatch::append_sampled(const std::string& req_id, const std::vector<int
 StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uint8_t* buf,
                              bool async_mode) {
   StepInfo info;
-  struct Item { CachedRequestState* s; int n; };
+  struct Item { CachedRequestState* s; int n; const std::vector<int32_t>* spec; };
   std::vector<Item> items;
   items.reserve(so.num_scheduled_tokens.size());
   for (auto& p : so.num_scheduled_tokens) {
     auto it = reqs_.find(p.first);
     if (it == reqs_.end()) throw std::runtime_error("scheduled request unknown to the worker: " + p.first);
-    items.push_back({&it->second, p.second});
+    auto sp = so.scheduled_spec_decode_tokens.find(p.first);
+    items.push_back({&it->second, p.second,
+                     sp == so.scheduled_spec_decode_tokens.end() || sp->second.empty() ? nullptr : &sp->second});
   }
   // decode-first, stable
   std::stable_partition(items.begin(), items.end(), [](const Item& a) { return a.n == 1; });
@@ -173,6 +208,8 @@ StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uin
       int64_t id = 0;
       if (p < (int)s.token_ids.size()) {
         id = s.token_ids[p];
+      } else if (items[r].spec && p - (int)s.token_ids.size() < (int)items[r].spec->size()) {
+        id = (*items[r].spec)[p - (int)s.token_ids.size()];   // a draft token to verify
       } else if (async_mode) {
         auto lr = last_rows_.find(s.req_id);
         if (lr == last_rows_.end()) throw std::runtime_error("no in-flight token for " + s.req_id);
@@ -228,9 +265,19 @@ StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uin
     pres[r] = (float)sp.presence_penalty;
     const bool produces = lo + n >= (int)s.token_ids.size();
     info.produces_token.push_back(produces ? 1 : 0);
+    // drafts verified this step: the scheduled positions beyond the known tokens
+    // (positions beyond the known tokens without a draft are in-flight tokens of async scheduling)
+    const int k = (produces && items[r].spec)
+                      ? std::min((int)items[r].spec->size(), std::max(0, lo + n - (int)s.token_ids.size()))
+                      : 0;
+    info.num_draft.push_back(k);
+    info.logits_row0.push_back(produces ? info.num_logits : -1);
     if (produces) {
-      sample_rows[info.num_logits] = (int32_t)r;
-      logits_idx[info.num_logits++] = tok - 1;
+      if (info.num_logits + k + 1 > L.max_logits) throw std::runtime_error("batch exceeds the logits rows of the layout");
+      for (int i = 0; i <= k; ++i) {   // one row per draft position plus the bonus position
+        sample_rows[info.num_logits] = (int32_t)r;
+        logits_idx[info.num_logits++] = tok - 1 - k + i;
+      }
       s.sample_step += 1;
       if (sp.temperature >= kSamplingEps) {
         info.all_greedy = false;
@@ -256,10 +303,9 @@ void InputBatch::build_penalty_entries(const StepInfo& info, std::vector<int32_t
                                        std::vector<int32_t>& toks,
                                        std::vector<int32_t>& out_cnt) const {
   rows.clear(); toks.clear(); out_cnt.clear();
-  int logit_row = 0;
   for (size_t r = 0; r < info.req_ids.size(); ++r) {
     if (!info.produces_token[r]) continue;
-    const int row = logit_row++;
+    const int row = info.logits_row0[r];
     auto it = reqs_.find(info.req_ids[r]);
     if (it == reqs_.end()) continue;
     const CachedRequestState& s = it->second;
@@ -282,10 +328,9 @@ void InputBatch::build_logit_edits(const StepInfo& info, std::vector<int32_t>& b
                                    std::vector<int32_t>& ban_rows, std::vector<int32_t>& ban_toks,
                                    const std::map<std::string, int32_t>& eos_of) const {
   bias_rows.clear(); bias_toks.clear(); bias_vals.clear(); ban_rows.clear(); ban_toks.clear();
-  int logit_row = 0;
   for (size_t r = 0; r < info.req_ids.size(); ++r) {
     if (!info.produces_token[r]) continue;
-    const int row = logit_row++;
+    const int row = info.logits_row0[r];
     auto it = reqs_.find(info.req_ids[r]);
     if (it == reqs_.end()) continue;
     const CachedRequestState& s = it->second;

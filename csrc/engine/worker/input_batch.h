@@ -36,13 +36,14 @@ struct CachedRequestState {
 // Byte offsets of each array inside the packed step buffer.
 struct StepLayout {
   int max_tokens = 0, max_reqs = 0, max_blocks = 0, num_groups = 1, max_tiles = 0;
+  int max_logits = 0;         // max_reqs * (1 + max draft tokens per request)
   size_t input_ids = 0;       // int64 [max_tokens]
   size_t positions = 0;       // int64 [max_tokens]
   size_t slot_mapping = 0;    // int64 [num_groups][max_tokens]
   size_t query_start = 0;     // int32 [max_reqs + 1]
   size_t seq_lens = 0;        // int32 [max_reqs]
   size_t block_table = 0;     // int32 [num_groups][max_reqs][max_blocks]
-  size_t logits_indices = 0;  // int32 [max_reqs]
+  size_t logits_indices = 0;  // int32 [max_logits]
   size_t tile_req = 0;        // int32 [max_tiles]   (request index relative to first prefill)
   size_t tile_q0 = 0;         // int32 [max_tiles]
   size_t prefill_q_start = 0; // int32 [max_reqs + 1] (token offsets relative to first prefill token)
@@ -58,7 +59,9 @@ struct StepLayout {
   size_t splice_src = 0;      // int32 [max_reqs] async: row of the previous batch's sampled ids
   size_t sample_rows = 0;     // int32 [max_reqs] batch row of each logits row (rows that sample)
   size_t total_bytes = 0;
-  static StepLayout make(int max_tokens, int max_reqs, int max_blocks, int num_groups);
+  // max_spec: draft tokens a request may verify per step (each adds a logits row).
+  static StepLayout make(int max_tokens, int max_reqs, int max_blocks, int num_groups,
+                         int max_spec = 0);
 };
 
 struct StepInfo {
@@ -75,6 +78,8 @@ struct StepInfo {
   std::vector<int> num_scheduled;          // per request
   std::vector<uint8_t> produces_token;     // request finishes its known tokens this step
   std::vector<int> max_logprobs;           // per request (-1 = none)
+  std::vector<int> num_draft;              // per request: draft tokens verified this step
+  std::vector<int> logits_row0;            // per request: its first logits row (-1 = none)
 };
 
 class InputBatch {
@@ -90,6 +95,13 @@ class InputBatch {
   // Sync mode: record sampled tokens (the scheduler also sends them back as new_token_ids).
   void append_sampled(const std::string& req_id, const std::vector<int32_t>& toks);
   const CachedRequestState* get(const std::string& id) const;
+  // Prompt-lookup drafting (reference: include/vllm/v1/spec_decode/ngram_proposer.h): the longest
+  // suffix of between min_n and max_n tokens that occurred earlier in the request (latest
+  // occurrence first); returns up to k tokens that followed it. Empty if none.
+  std::vector<int32_t> propose_ngram(const std::string& id, int min_n, int max_n, int k) const;
+  // True if the request samples greedily with nothing that edits its logits (the case drafts are
+  // verified by plain argmax comparison).
+  bool plain_greedy(const std::string& id) const;
   size_t num_requests() const { return reqs_.size(); }
   int max_num_reqs() const { return max_num_reqs_; }
   // Penalty triples (row, token, output count) for the rows of the last prepared batch.

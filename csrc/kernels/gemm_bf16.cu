@@ -66,6 +66,10 @@ struct GemmParams {
   // starts inside a tile writes that fp32 partial to sk_partials[cta] and raises
   // sk_flags[cta * 4 + warp quarter]; the CTA that holds the tile's first k-block adds the
   // partials of the CTAs after it and runs the epilogue, then clears the flags it consumed.
+  // fused gated activation (pair kernel, BN = 256): W rows come in blocks of [128 gate | 128 up],
+  // so a tile holds both halves of 128 outputs; out[M, N / 2] = act(gate) * up. 0 = off,
+  // otherwise activation kind + 1 (1 SiLU, 2 GELU-tanh, 3 GELU-erf).
+  int act_fuse;
   int sk;                         // number of leading tiles in the stream-K region (0 = none)
   float* sk_partials;
   uint32_t* sk_flags;
@@ -508,6 +512,41 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, float 
   }
 }
 
+__device__ __forceinline__ float gated_act(float g, int kind) {
+  if (kind == 0) return g / (1.f + __expf(-g));
+  if (kind == 1) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    return 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g)));
+  }
+  return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
+}
+// act(gate) * up on 32 columns; both inputs are rounded to bf16 first so that the result equals
+// a bf16 GEMM followed by the separate activation kernel bit for bit.
+__device__ __forceinline__ void epilogue_store_gated(const GemmParams& p, const float (&g)[32],
+                                                     const float (&u)[32], int row, int col0) {
+  const int kind = p.act_fuse - 1;
+  const int n_out = p.N >> 1;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldo + col0;
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    if (col0 + i < n_out) {
+      float r[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gg = __bfloat162float(__float2bfloat16(g[i + j]));
+        const float uu = __bfloat162float(__float2bfloat16(u[i + j]));
+        r[j] = gated_act(gg, kind) * uu;
+      }
+      uint4 w;
+      w.x = pack_bf16x2(r[0], r[1]);
+      w.y = pack_bf16x2(r[2], r[3]);
+      w.z = pack_bf16x2(r[4], r[5]);
+      w.w = pack_bf16x2(r[6], r[7]);
+      *reinterpret_cast<uint4*>(o + i) = w;
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -663,26 +702,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      // accumulator columns [c * 32, c * 32 + 32) of this thread's row, stream-K partials added
+      auto load_chunk = [&](int c, float (&v)[32]) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
-        const int col0 = tn * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        for (int x = sk_first; x <= sk_last; ++x) {
+          const float* src = p.sk_partials + (size_t)(x * 2 + (int)rank) * kBM * BN +
+                             (size_t)c * 32 * kBM + quarter * 32 + lane;
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __ldcg(src + (size_t)i * kBM);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += f[i];
+        }
+      };
+      if (BN == 256 && p.act_fuse) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float g[32], u[32];
+          load_chunk(c, g);
+          load_chunk(c + 4, u);
+          const int col0 = tn * 128 + c * 32;
+          if (row < p.M && col0 < (p.N >> 1)) epilogue_store_gated(p, g, u, row, col0);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
           float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          for (int x = sk_first; x <= sk_last; ++x) {
-            const float* src = p.sk_partials + (size_t)(x * 2 + (int)rank) * kBM * BN +
-                               (size_t)c * 32 * kBM + quarter * 32 + lane;
-            float f[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __ldcg(src + (size_t)i * kBM);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] += f[i];
-          }
-          epilogue_store_chunk(p, v, row, col0);
+          load_chunk(c, v);
+          const int col0 = tn * BN + c * 32;
+          if (row < p.M && col0 < p.N) epilogue_store_chunk(p, v, row, col0);
         }
       }
       tc_fence_before_sync();
@@ -1100,7 +1152,7 @@ using namespace b200;
 static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                           int out_f32, const void* bias, const void* residual, int ldr, int M,
                           int N, int K, void* workspace, size_t ws_bytes, int force_path,
-                          const B200TpGemm* tp, cudaStream_t stream);
+                          const B200TpGemm* tp, cudaStream_t stream, int act_fuse = 0);
 
 extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                               int out_f32, const void* bias, const void* residual, int ldr, int M,
@@ -1108,6 +1160,20 @@ extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, vo
                               cudaStream_t stream) {
   return gemm_bf16_impl(A, lda, W, ldw, out, ldo, out_f32, bias, residual, ldr, M, N, K, workspace,
                         ws_bytes, force_path, nullptr, stream);
+}
+
+// Gated-MLP first half in one kernel: out[M, N / 2] = act(A W_gate^T) * (A W_up^T), where W holds
+// the gate and up rows interleaved in blocks of 128 ([128 gate | 128 up] per 256 rows) so that
+// every 256-column accumulator tile contains both halves of 128 outputs. M > 256 (the CTA-pair
+// kernel); smaller batches run the plain GEMM and the interleave-aware activation kernel.
+// kind: 0 SiLU, 1 GELU-tanh, 2 GELU-erf. Replaces MatmulBT + SiluAndMul / GeluAndMul of the
+// reference (src/vt/cuda/cuda_matmul.cu, cuda_ops.cu) on the prefill-sized path.
+extern "C" int b200_gemm_bf16_gated(const void* A, int lda, const void* W, int ldw, void* out,
+                                    int ldo, int M, int N, int K, int kind, int force_path,
+                                    cudaStream_t stream) {
+  if (kind < 0 || kind > 2) return -1;
+  return gemm_bf16_impl(A, lda, W, ldw, out, ldo, 0, nullptr, nullptr, 0, M, N, K, nullptr, 0,
+                        force_path, nullptr, stream, kind + 1);
 }
 
 // Same GEMM with the tensor-parallel prologue / epilogue described by `tp`.
@@ -1132,7 +1198,7 @@ extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw,
       const int sms = b200_num_sms();
       int tm = (M + 127) / 128, tn256 = (N + 255) / 256, tn128 = (N + 127) / 128;
       long w256 = ((long)tm * tn256 + sms - 1) / sms, w128 = ((long)tm * tn128 + sms - 1) / sms;
-      *expected_rs = tp->world * ((w256 * 2 * 100 <= w128 * 108) ? tn256 : tn128);
+      *expected_rs = tp->world * ((N >= 256 && w256 * 2 * 100 <= w128 * 135) ? tn256 : tn128);
     }
   }
   return gemm_bf16_impl(A, lda, W, ldw, out, ldo, tp->scatter ? 0 : tp->out_f32, nullptr, nullptr,
@@ -1142,8 +1208,9 @@ extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw,
 static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                           int out_f32, const void* bias, const void* residual, int ldr, int M,
                           int N, int K, void* workspace, size_t ws_bytes, int force_path,
-                          const B200TpGemm* tp, cudaStream_t stream) {
+                          const B200TpGemm* tp, cudaStream_t stream, int act_fuse) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (act_fuse && (tp || M <= 256 || (N & 255) || bias || residual || out_f32)) return -1;
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
        reinterpret_cast<uintptr_t>(out)) & 15)
@@ -1244,7 +1311,9 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   int tn256 = (N + 255) / 256, tn128 = (N + 127) / 128;
   long waves256 = ((long)p.tiles_m * tn256 + sms - 1) / sms;
   long waves128 = ((long)p.tiles_m * tn128 + sms - 1) / sms;
-  bool use256 = (waves256 * 2 * 100 <= waves128 * 108);
+  // a 128 x 256 tile runs at about 1.6x the per-tile rate of two 128 x 128 tiles (operand traffic per
+  // FLOP), so the wide tile wins unless it needs a third more waves
+  bool use256 = (N >= 256 && waves256 * 2 * 100 <= waves128 * 135);
   if (force_path == 3) use256 = false;
   if (force_path == 4) use256 = true;
   // force_path: 0 auto | 1 tiled 1-CTA | 3 / 4 1-CTA with BN 128 / 256 | 5 / 6 1-CTA BN 256 / 128
@@ -1254,8 +1323,10 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   if (force_path == 5) { use256 = true; p.sk = !tp; }
   if (force_path == 6) { use256 = false; p.sk = !tp; }
   const bool pair_path = !tp && (force_path == 0 || (force_path >= 7 && force_path <= 10));
+  if (act_fuse && !pair_path) return -1;
+  p.act_fuse = act_fuse;
   if (pair_path) {
-    const bool bn256 = force_path == 0 ? (N > 128) : (force_path == 7 || force_path == 9);
+    const bool bn256 = act_fuse || (force_path == 0 ? (N > 128) : (force_path == 7 || force_path == 9));
     p.sk = (force_path == 0 || force_path >= 9) ? 1 : 0;
     p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
     CUtensorMap tA, tB;

@@ -112,17 +112,23 @@ __device__ __forceinline__ float act_fn(float g, int kind) {
   return 0.5f * g * (1.f + erff(g * 0.7071067811865476f));
 }
 
-// x: [T, 2*I] = [gate | up]; out: [T, I] = act(gate) * up.
+// x: [T, 2*I] = [gate | up] (or, with kind | 0x100, blocks of [128 gate | 128 up]);
+// out: [T, I] = act(gate) * up.
 __global__ void __launch_bounds__(256)
     act_and_mul_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* out, int I,
-                       int T, int kind) {
+                       int T, int kind_flags) {
+  const int kind = kind_flags & 0xff;
+  const bool il = (kind_flags & 0x100) != 0;
   const int nv = I >> 3;
   const size_t total = (size_t)T * nv;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     int t = (int)(idx / nv), i = (int)(idx % nv);
-    const uint4 g = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + i * 8);
-    const uint4 u = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + I + i * 8);
+    // interleaved input: blocks of [128 gate | 128 up] instead of [all gate | all up]
+    const int goff = il ? ((i * 8) >> 7) * 256 + ((i * 8) & 127) : i * 8;
+    const int uoff = il ? goff + 128 : I + i * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + goff);
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + uoff);
     uint4 o;
     float2 a, b;
     a = unpack_bf16x2(g.x); b = unpack_bf16x2(u.x); o.x = pack_bf16x2(act_fn(a.x, kind) * b.x, act_fn(a.y, kind) * b.y);
@@ -262,6 +268,7 @@ int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind,
                      cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((I & 7) || (ldx & 7)) return -1;
+  if ((kind & 0x100) && (I & 127)) return -1;      // interleaved layout needs whole blocks
   act_and_mul_kernel<<<ew_grid((size_t)T * (I / 8)), 256, 0, stream>>>((const bf16*)x, ldx,
                                                                       (bf16*)out, I, T, kind);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -447,3 +447,26 @@ def test_greedy_rejection():
     target = torch.tensor([5, 6, 9, 11, 1, 2, 13], device=DEV)
     out = ops.greedy_reject(target, draft, cu, 3)
     assert out.tolist() == [[5, 6, 9, -1], [1, 2, 13, -1]]
+
+
+@pytest.mark.parametrize("M,I,K,kind", [(1280, 1024, 512, 0), (300, 384, 256, 1), (64, 256, 128, 0),
+                                        (700, 14336, 4096, 0), (2048, 128, 64, 2)])
+def test_gemm_gated_activation(M, I, K, kind):
+    """act(gate) * up in the GEMM epilogue (interleaved gate / up rows). With the same tiling and
+    no stream-K split it equals the bf16 GEMM followed by the activation kernel bit for bit;
+    otherwise (fp32 partial sums added in another order) within bf16 rounding."""
+    torch.manual_seed(3)
+    a = _rand(M, K)
+    wg, wu = _rand(I, K, scale=0.05), _rand(I, K, scale=0.05)
+    w_il = ops.interleave_gate_up(wg, wu)
+    merged_w = torch.cat([wg, wu], 0)
+    exp = ref.act_and_mul(ref.gemm(a, merged_w), kind)
+    out = ops.gemm_gated(a, w_il, kind)
+    assert ops.read_status() == 0
+    assert _rel_err(out, exp) < 2e-2
+    if M > 256:
+        two_step = ops.act_and_mul(ops.gemm(a, merged_w, force_path=7), kind)
+        assert torch.equal(ops.gemm_gated(a, w_il, kind, force_path=7), two_step)
+        assert _rel_err(ops.gemm_gated(a, w_il, kind, force_path=9), exp) < 2e-2
+    else:
+        assert torch.equal(out, ops.act_and_mul(ops.gemm(a, merged_w), kind))

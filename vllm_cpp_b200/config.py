@@ -379,6 +379,9 @@ class EngineArgs:
     enable_prefix_caching: Optional[bool] = None  # None => on unless hybrid
     scheduling_policy: str = "fcfs"
     async_scheduling: Optional[bool] = None
+    # spec_decode.SpeculativeConfig; method "ngram" is wired through the engine (prompt-lookup
+    # drafts, argmax verification), the other methods have their building blocks only
+    speculative_config: Optional[object] = None
     enable_cuda_graphs: bool = True
     seed: int = 0
     device: str = "cuda"

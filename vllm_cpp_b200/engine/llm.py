@@ -85,14 +85,19 @@ class LLM:
         budget = args.resolve_max_num_batched_tokens(cfg)
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
         use_async = args.async_scheduling if args.async_scheduling is not None else False
+        spec = args.speculative_config
+        if spec is not None and spec.method == "ngram":
+            use_async = False       # drafts are verified on the host between steps
         self.runner = ModelRunner(self.model, block_size=args.block_size, num_blocks=num_blocks,
                                   max_num_seqs=args.max_num_seqs, max_num_batched_tokens=budget,
                                   max_model_len=max_len, enable_cuda_graphs=args.enable_cuda_graphs,
-                                  async_mode=use_async)
+                                  async_mode=use_async, speculative_config=spec)
         sc = E.SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=args.max_num_seqs,
                                max_model_len=max_len, policy=args.scheduling_policy,
                                async_scheduling=use_async,
                                enable_prefix_caching=args.resolve_prefix_caching(cfg))
+        if self.runner.max_spec:
+            sc.num_lookahead_tokens = self.runner.max_spec
         self.scheduler_config = sc
         self.structured = None
         if self.tokenizer is not None and hasattr(E, "StructuredOutputManager"):

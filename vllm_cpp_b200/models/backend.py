@@ -71,7 +71,8 @@ class CpuBackend:
     def layernorm(self, x, w, b, eps):
         return ref.layernorm(x, w, b, eps)
 
-    def act_and_mul(self, x, kind=0, out=None):
+    def act_and_mul(self, x, kind=0, out=None, interleaved=False):
+        assert not interleaved, "the interleaved gate / up layout is GPU-only"
         return ref.act_and_mul(x, kind)
 
     def embedding(self, ids, table, out=None, vocab_start=0, vocab_total=None, scale=1.0):
@@ -158,8 +159,15 @@ class GpuBackend:
     def layernorm(self, x, w, b, eps):
         return self.ops.layernorm(x, w, b, eps)
 
-    def act_and_mul(self, x, kind=0, out=None):
-        return self.ops.act_and_mul(x, kind, out)
+    def act_and_mul(self, x, kind=0, out=None, interleaved=False):
+        return self.ops.act_and_mul(x, kind, out, interleaved=interleaved)
+
+    def gemm_gated(self, a, w, kind=0, out=None, scratch=None):
+        """act(a W_gate^T) * (a W_up^T) for an interleaved gate / up weight."""
+        if isinstance(w, QuantWeight):
+            y = self.gemm(a, w, out=scratch)
+            return self.ops.act_and_mul(y, kind, out, interleaved=True)
+        return self.ops.gemm_gated(a, w, kind, out=out, scratch=scratch)
 
     def embedding(self, ids, table, out=None, vocab_start=0, vocab_total=None, scale=1.0):
         return self.ops.embedding(ids, table, out=out, vocab_start=vocab_start,

@@ -51,6 +51,7 @@ class DenseModel:
         self.scale = c.attention_multiplier if c.attention_multiplier is not None else \
             softmax_scale(c.rope, c.head_dim)
         self.bufs = BufferPool(self.device)
+        self.gate_up_il = False      # set by load_weights when it stores gate / up interleaved
         self.w: dict[str, torch.Tensor] = {}
         self.layers: list[dict[str, torch.Tensor]] = []
 
@@ -148,6 +149,10 @@ class DenseModel:
             self.w["lm_head"] = put(lm[self.vocab_start:self.vocab_start + self.vocab_shard])
         self.w["final_norm"] = put(staged["model.norm.weight"])
         self.layers = []
+        # On the GPU the merged gate / up projection is stored in blocks of [128 gate | 128 up]
+        # rows, so that the GEMM epilogue can apply the gated activation (see ops.gemm_gated).
+        self.gate_up_il = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and
+                           self.inter % 128 == 0 and not self.cfg.mlp_bias)
         for l in range(c.num_layers):
             p = f"model.layers.{l}."
             L: dict[str, torch.Tensor] = {}
@@ -163,7 +168,11 @@ class DenseModel:
             L["o"] = put(shard_cols(staged[p + "self_attn.o_proj.weight"], r, tp))
             g = shard_rows(staged[p + "mlp.gate_proj.weight"], r, tp)
             u = shard_rows(staged[p + "mlp.up_proj.weight"], r, tp)
-            L["gate_up"] = put(torch.cat([g, u], 0))
+            if self.gate_up_il:
+                from ..ops import interleave_gate_up
+                L["gate_up"] = put(interleave_gate_up(g, u))
+            else:
+                L["gate_up"] = put(torch.cat([g, u], 0))
             L["down"] = put(shard_cols(staged[p + "mlp.down_proj.weight"], r, tp))
             L["ln1"] = put(staged[p + "input_layernorm.weight"])
             L["ln2"] = put(staged[p + "post_attention_layernorm.weight"])
@@ -292,7 +301,7 @@ class DenseModel:
             exp = tpf.gemm_scatter(attn, L["o"])
             tpf.reduce_norm_gather(T, exp, L["ln2"], eps, c.gemma_norm)
             tpf.gemm_gather(T, L["gate_up"], gate_up)
-            be.act_and_mul(gate_up, act_kind, out=act)
+            be.act_and_mul(gate_up, act_kind, out=act, interleaved=self.gate_up_il)
             exp = tpf.gemm_scatter(act, L["down"])
             nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
             tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)
@@ -383,8 +392,11 @@ class DenseModel:
                     x_mlp = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed,
                                        gemma=c.gemma_norm)
             # ---- MLP block
-            be.gemm(x_mlp, L["gate_up"], out=gate_up)
-            a = be.act_and_mul(gate_up, act_kind, out=act)
+            if self.gate_up_il:
+                a = be.gemm_gated(x_mlp, L["gate_up"], act_kind, out=act, scratch=gate_up)
+            else:
+                be.gemm(x_mlp, L["gate_up"], out=gate_up)
+                a = be.act_and_mul(gate_up, act_kind, out=act)
             hidden = self.bufs.get("hidden", T, H)
             be.gemm(a, L["down"], out=hidden)
             if self.tp > 1:

@@ -78,15 +78,50 @@ def layernorm(x, weight, bias, eps, out=None):
     return out
 
 
-def act_and_mul(x: torch.Tensor, kind: int = ACT_SILU, out: torch.Tensor | None = None):
-    """``x = [gate | up]`` along the last dim -> ``act(gate) * up``."""
+def act_and_mul(x: torch.Tensor, kind: int = ACT_SILU, out: torch.Tensor | None = None,
+                interleaved: bool = False):
+    """``x = [gate | up]`` along the last dim -> ``act(gate) * up``. ``interleaved``: the columns
+    come in blocks of ``[128 gate | 128 up]`` (see :func:`interleave_gate_up`)."""
     T, two_i = x.shape
     inter = two_i // 2
     if out is None:
         out = torch.empty((T, inter), dtype=x.dtype, device=x.device)
-    check(lib().b200_act_and_mul(ptr(x), x.stride(0), ptr(out), T, inter, kind, stream_ptr()),
+    flags = kind | (0x100 if interleaved else 0)
+    check(lib().b200_act_and_mul(ptr(x), x.stride(0), ptr(out), T, inter, flags, stream_ptr()),
           "act_and_mul")
     return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Weight rows in blocks of ``[128 gate | 128 up]``: every 256-column tile of the merged
+    projection then holds both halves of 128 outputs, which lets the GEMM epilogue apply the
+    gated activation. Needs the intermediate size to be a multiple of 128."""
+    I, H = gate.shape
+    assert up.shape == gate.shape and I % 128 == 0
+    return torch.stack([gate.reshape(I // 128, 128, H), up.reshape(I // 128, 128, H)], 1).reshape(2 * I, H)
+
+
+def gemm_gated(a: torch.Tensor, w_il: torch.Tensor, kind: int = ACT_SILU, *,
+               out: torch.Tensor | None = None, scratch: torch.Tensor | None = None,
+               force_path: int = 0) -> torch.Tensor:
+    """``act(a @ w_gate^T) * (a @ w_up^T)`` with ``w_il`` from :func:`interleave_gate_up`.
+    Above 256 rows the activation runs in the GEMM epilogue (one kernel, the merged
+    projection never reaches memory); below, the small-M GEMM writes the interleaved
+    projection to ``scratch`` and the activation kernel reads it."""
+    M, K = a.shape
+    N = w_il.shape[0]
+    assert a.dtype == torch.bfloat16 and w_il.dtype == torch.bfloat16 and N % 256 == 0
+    if out is None:
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+    if M > 256:
+        check(lib().b200_gemm_bf16_gated(ptr(a), a.stride(0), ptr(w_il), w_il.stride(0), ptr(out),
+                                         out.stride(0), M, N, K, kind, force_path, stream_ptr()),
+              f"gemm_gated M={M} N={N} K={K}")
+        return out
+    if scratch is None:
+        scratch = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    gemm(a, w_il, out=scratch)
+    return act_and_mul(scratch, kind, out, interleaved=True)
 
 
 def silu_and_mul(x, out=None):

@@ -58,6 +58,7 @@ _SIGS = {
     "b200_rmsnorm": ([P, I, P, P, P, I, I, I, F, I, P], I),
     "b200_layernorm": ([P, P, P, P, I, I, F, P], I),
     "b200_act_and_mul": ([P, I, P, I, I, I, P], I),
+    "b200_gemm_bf16_gated": ([P, I, P, I, P, I, I, I, I, I, I, P], I),
     "b200_eltwise": ([P, P, P, Z, I, F, P], I),
     "b200_cast_bf16_f32": ([P, P, Z, P], I),
     "b200_cast_f32_bf16": ([P, P, Z, P], I),

@@ -23,11 +23,14 @@ def sample(runner, info, logits: torch.Tensor, grammar) -> torch.Tensor:
     rows = [i for i, p in enumerate(info.produces_token) if p]
     v = runner.views
 
+    # logits row -> batch row (a request that verifies drafts owns several rows)
+    row_req = v["sample_rows"][: info.num_logits].long()
+
     def per_row(name):
-        return v[name][: info.num_reqs][rows]
+        return v[name][: info.num_reqs][row_req]
 
     if grammar is not None and grammar.structured_output_request_ids:
-        rid = {info.req_ids[j]: i for i, j in enumerate(rows)}
+        rid = {info.req_ids[j]: info.logits_row0[j] for j in rows}
         words = grammar.words_per_row
         mask = torch.tensor(grammar.bitmask, dtype=torch.int32).view(-1, words)
         V = logits.shape[1]

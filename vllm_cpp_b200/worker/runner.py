@@ -45,8 +45,17 @@ def decode_graph_sizes(max_num_seqs: int) -> list[int]:
 class ModelRunner(E.ModelRunnerBase):
     def __init__(self, model, *, block_size: int, num_blocks: int, max_num_seqs: int,
                  max_num_batched_tokens: int, max_model_len: int, enable_cuda_graphs: bool = True,
-                 async_mode: bool = False):
+                 async_mode: bool = False, speculative_config=None):
         super().__init__()
+        # Speculative decoding, n-gram (prompt lookup) drafts verified by argmax comparison:
+        # a request scheduled with k drafts runs k + 1 query tokens, gets k + 1 logits rows and
+        # keeps the longest prefix of drafts that the target agrees with plus one more token.
+        self.spec = speculative_config if (speculative_config is not None and
+                                           speculative_config.method == "ngram") else None
+        self.max_spec = self.spec.num_speculative_tokens if self.spec else 0
+        self._drafts: dict[str, list[int]] = {}
+        self._scheduled_spec: dict[str, list[int]] = {}
+        self.spec_stats = {"drafted": 0, "accepted": 0}
         self.model = model
         self.device = model.device
         self.is_cuda = self.device.type == "cuda"
@@ -60,7 +69,7 @@ class ModelRunner(E.ModelRunnerBase):
         self.num_groups = len(self.groups)
         self.max_blocks = (max_model_len + block_size - 1) // block_size + 1
         self.layout = E.StepLayout.make(self.max_tokens, max_num_seqs, self.max_blocks,
-                                        self.num_groups)
+                                        self.num_groups, self.max_spec)
         self.off = self.layout.offsets()
         nbytes = self.layout.total_bytes
         # two pinned staging buffers: with a step in flight its copy may not have run yet when
@@ -79,8 +88,9 @@ class ModelRunner(E.ModelRunnerBase):
         self.views = self._make_views(self.dev_buf)
         self.host_views_all = [self._make_views(b) for b in self.host_bufs]
         self.host_views = self.host_views_all[0]
-        self.sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
-        self.sampled_host = torch.zeros(max_num_seqs, dtype=torch.int64,
+        max_logits = self.layout.max_logits
+        self.sampled = torch.zeros(max_logits, dtype=torch.int64, device=self.device)
+        self.sampled_host = torch.zeros(max_logits, dtype=torch.int64,
                                         pin_memory=self.is_cuda)
         self.last_sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
         self.graphs: dict[int, tuple] = {}
@@ -121,14 +131,15 @@ class ModelRunner(E.ModelRunnerBase):
         v["seq_lens"] = view("seq_lens", R)
         bt = view("block_table", G * R * B).view(G, R, B)
         v["block_table"] = [bt[g] for g in range(G)]
-        v["logits_indices"] = view("logits_indices", R)
+        v["logits_indices"] = view("logits_indices", L.max_logits)
         v["tile_req"] = view("tile_req", L.max_tiles)
         v["tile_q0"] = view("tile_q0", L.max_tiles)
         v["prefill_q_start"] = view("prefill_q_start", R + 1)
         v["state_slots"] = view("state_slots", R)
         for k in ("temperature", "top_p", "min_p", "top_k", "seeds", "steps", "rep_pen", "freq_pen",
-                  "pres_pen", "splice_dst", "splice_src", "sample_rows"):
+                  "pres_pen", "splice_dst", "splice_src"):
             v[k] = view(k, R)
+        v["sample_rows"] = view("sample_rows", L.max_logits)
         return v
 
     def kv_cache_config(self) -> "E.KVCacheConfig":
@@ -145,7 +156,19 @@ class ModelRunner(E.ModelRunnerBase):
     def set_eos(self, req_id: str, eos: Optional[int]) -> None:
         self._eos[req_id] = -1 if eos is None else int(eos)
 
+    def take_draft_token_ids(self):
+        """Drafts proposed after the last sampling step (consumed by the scheduler)."""
+        if not self._drafts:
+            return None
+        d = E.DraftTokenIds()
+        d.req_ids = list(self._drafts.keys())
+        d.draft_token_ids = [self._drafts[r] for r in d.req_ids]
+        self._drafts = {}
+        return d
+
     def supports_async(self) -> bool:
+        if self.spec is not None:
+            return False        # draft verification reads the sampled ids on the host every step
         return self.is_cuda
 
     def _decode_splits(self, batch: int) -> tuple[int, tuple | None]:
@@ -252,6 +275,7 @@ class ModelRunner(E.ModelRunnerBase):
         self.host_buf, self.host_views = self.host_bufs[k], self.host_views_all[k]
         info = self.batch.prepare(so, self.layout, self.host_buf.data_ptr(), self.async_mode)
         self._info = info
+        self._scheduled_spec = dict(so.scheduled_spec_decode_tokens) if self.spec else {}
         R, T = info.num_reqs, info.num_tokens
         decode_only = info.num_prefills == 0 and info.num_decodes == R
         pad = self._pad_size(R) if (decode_only and self.enable_graphs and info.all_greedy
@@ -306,8 +330,9 @@ class ModelRunner(E.ModelRunnerBase):
         # row-compacted per-request scalars (rows that sample are a subset of the batch)
         rows = [i for i, p in enumerate(info.produces_token) if p]
         idx = None
-        if len(rows) != info.num_reqs:
-            idx = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        if n != info.num_reqs or len(rows) != info.num_reqs:
+            # logits row -> batch row (a request verifying drafts owns several rows)
+            idx = v["sample_rows"][:n].to(torch.int64)
 
         def per_row(name):
             t = v[name][: info.num_reqs]
@@ -315,7 +340,7 @@ class ModelRunner(E.ModelRunnerBase):
 
         dev = self.device
         if grammar is not None and grammar.structured_output_request_ids:
-            rid = {r: i for i, r in enumerate([info.req_ids[j] for j in rows])}
+            rid = {info.req_ids[j]: info.logits_row0[j] for j in rows}
             row_ids = torch.tensor([rid.get(r, -1) for r in grammar.structured_output_request_ids],
                                    dtype=torch.int32, device=dev)
             mask = torch.tensor(grammar.bitmask, dtype=torch.int32, device=dev).view(
@@ -377,7 +402,7 @@ class ModelRunner(E.ModelRunnerBase):
                 rank = int((lp[row] > lp[row, tok]).sum()) + 1
                 lr.ranks = [rank] + list(range(1, k + 1))
                 out.append([lr])
-            row += 1
+            row += 1 + info.num_draft[r]
         return out
 
     def _mark_step_end(self) -> None:
@@ -400,13 +425,33 @@ class ModelRunner(E.ModelRunnerBase):
         row = 0
         for r, p in enumerate(info.produces_token):
             if p:
-                t = int(ids_host[row])
-                toks.append([t])
-                self.batch.append_sampled(info.req_ids[r], [t])
-                row += 1
+                k = info.num_draft[r]
+                rid = info.req_ids[r]
+                if k:
+                    # rows row .. row + k hold the target's choice after each draft prefix
+                    drafts = self._scheduled_spec.get(rid, [])[:k]
+                    acc = 0
+                    while acc < k and acc < len(drafts) and int(ids_host[row + acc]) == drafts[acc]:
+                        acc += 1
+                    new = [int(ids_host[row + i]) for i in range(acc + 1)]
+                    self.spec_stats["drafted"] += k
+                    self.spec_stats["accepted"] += acc
+                else:
+                    new = [int(ids_host[row])]
+                toks.append(new)
+                self.batch.append_sampled(rid, new)
+                row += k + 1
             else:
                 toks.append([])
         out.sampled_token_ids = toks
+        if self.spec is not None:
+            for r, p in enumerate(info.produces_token):
+                rid = info.req_ids[r]
+                if p:
+                    # an entry for every request that sampled (empty = no drafts next step)
+                    self._drafts[rid] = self.batch.propose_ngram(
+                        rid, self.spec.prompt_lookup_min, self.spec.prompt_lookup_max,
+                        self.max_spec) if self.batch.plain_greedy(rid) else []
         return out
 
     def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
