@@ -107,6 +107,11 @@ def main() -> int:
     ap.add_argument("--concurrency", type=int, default=CONCURRENCY)
     ap.add_argument("--input-len", type=int, default=INPUT_LEN)
     ap.add_argument("--output-len", type=int, default=OUTPUT_LEN)
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="N > 1: dp = one engine replica per GPU, the concurrent requests are split "
+                         "between them (the model fits on one GPU; this is the faster deployment); "
+                         "tp = one tensor-parallel engine over all GPUs with the fused "
+                         "GEMM + collective kernels")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--layers", type=int, default=0,
                     help="diagnostic: override the number of layers (the JSON line then carries "
@@ -150,12 +155,15 @@ def main() -> int:
     from vllm_cpp_b200.engine import LLM, SamplingParams
     from vllm_cpp_b200.ops import _lib
 
+    dp = world > 1 and args.parallelism == "dp"
     cfg = synthetic_config(args.model)
     if args.layers > 0:
         cfg.num_layers = args.layers
         if cfg.layer_types:
             cfg.layer_types = cfg.layer_types[: args.layers]
-    C, IN, OUT = args.concurrency, args.input_len, args.output_len
+    C_total, IN, OUT = args.concurrency, args.input_len, args.output_len
+    # data parallel: this replica serves its share of the concurrent requests
+    C = (C_total // world + (1 if rank < C_total % world else 0)) if dp else C_total
     block = 32
     max_len = IN + OUT + block
     llm = LLM(EngineArgs(
@@ -164,9 +172,10 @@ def main() -> int:
         num_blocks=C * ((max_len + block - 1) // block + 1) + 64,
         enable_cuda_graphs=not args.no_graphs, enable_prefix_caching=True,
         async_scheduling=not args.sync_scheduling,
-        parallel=ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank)))
+        parallel=(ParallelConfig(local_rank=local_rank) if dp else
+                  ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank))))
     note("engine built")
-    gen = torch.Generator().manual_seed(1)
+    gen = torch.Generator().manual_seed(1 + (rank if dp else 0))
 
     def new_prompt():
         return torch.randint(0, cfg.vocab_size, (IN,), generator=gen).tolist()
@@ -240,6 +249,12 @@ def main() -> int:
     t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if dp:
+            # replicas: tokens, launches and copies add up; the time is the slowest replica's
+            sums = torch.tensor([tokens, launches, h2d, d2h, status], dtype=torch.float64, device="cuda")
+            dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+            tokens, launches, h2d, d2h, status = (int(sums[0]), int(sums[1]), float(sums[2]),
+                                                  float(sums[3]), int(sums[4]))
     dev_ms, wall_ms = float(t[0]), float(t[1])
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / (wall_ms / 1e3)
@@ -252,9 +267,10 @@ def main() -> int:
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
             "dtype": "bf16", "data": "synthetic (uniform-random prompt ids, random-init weights)",
             "impl": "ours",
-            "config": {"model": "Llama-3.1-8B-shaped", "global_batch": C, "seq_len": IN + OUT,
+            "config": {"model": "Llama-3.1-8B-shaped", "global_batch": C_total, "seq_len": IN + OUT,
                        "input_len": IN, "output_len": OUT,
-                       "parallelism": f"tp{world}", "mode": "continuous batching, steady state",
+                       "parallelism": (f"dp{world}" if dp else f"tp{world}"),
+                       "mode": "continuous batching, steady state",
                        "max_num_batched_tokens": args.max_num_batched_tokens,
                        "l2": "weights (16 GB) and KV (>40 GB) per step exceed L2 (126 MB)",
                        "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs,
