@@ -205,166 +205,6 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const u
   }
 }
 
-struct W4Params {
-  int M, N, K;
-  bf16* out;
-  int ldo;
-  const uint8_t* wq;      // [N, K/2]
-  const uint8_t* sf;      // [N, K/16] e4m3
-  const float* gscale;
-  const bf16* bias;
-  int mp, stages, splits, kb_per_split;
-  float* workspace;
-  int* status;
-};
-
-// Swap-AB: weights are the 128-row operand. Warp 0 streams activations (TMA) and packed
-// weights (plain 16-byte loads into shared memory via cp.async-free vector copies done by
-// the converter warps themselves), warps 2-5 expand, warp 1 issues the MMAs.
-__global__ void __launch_bounds__(kQThreads, 1)
-    gemm_w4a16_swap_kernel(const __grid_constant__ CUtensorMap tmA, W4Params p, uint32_t tmem_cols) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int kWBytes = 128 * 64 * 2;            // expanded bf16 weight block
-  const int a_bytes = p.mp * 64 * 2;
-  const int stage_bytes = kWBytes + a_bytes;
-  const int stages = p.stages;
-  QBars* bars = reinterpret_cast<QBars*>(smem + (size_t)stages * stage_bytes);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tn = blockIdx.x, split = blockIdx.y;
-  const int kblocks_total = p.K / 64;
-  const int kb0 = split * p.kb_per_split;
-  const int nkb = min(kblocks_total, kb0 + p.kb_per_split) - kb0;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(&bars->full[s], 1);        // activations (TMA)
-      mbar_init(&bars->raw_full[s], 4);    // expanded weights (4 converter warps)
-      mbar_init(&bars->empty[s], 1);
-    }
-    mbar_init(&bars->acc_full[0], 1);
-    bars->failed = 0;
-    mbar_fence_init();
-  }
-  if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % stages;
-        if (!mbar_wait(&bars->empty[s], ((i / stages) & 1) ^ 1, p.status)) { bars->failed = 1; break; }
-        mbar_expect_tx(&bars->full[s], a_bytes);
-        tma_load_2d(smem + (size_t)s * stage_bytes + kWBytes, &tmA, &bars->full[s], (kb0 + i) * 64, 0);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(128, p.mp);
-      bool ok = true;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % stages;
-        const uint32_t ph = (i / stages) & 1;
-        if (!mbar_wait(&bars->full[s], ph, p.status) || !mbar_wait(&bars->raw_full[s], ph, p.status)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after_sync();
-        const uint32_t w_addr = smem_u32(smem + (size_t)s * stage_bytes);
-        const uint64_t wdesc = umma_desc_k_sw128(w_addr, 1024);
-        const uint64_t adesc = umma_desc_k_sw128(w_addr + kWBytes, 1024);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) umma_bf16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (i | k) != 0);
-        umma_commit(&bars->empty[s]);
-      }
-      if (ok) umma_commit(&bars->acc_full[0]);
-      else bars->failed = 1;
-    }
-  } else {
-    // ---- converters: thread t owns weight row t of the tile ----
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
-    const long n = (long)tn * 128 + r;
-    const bool row_ok = n < p.N;
-    const float g = *p.gscale;
-    bool ok = true;
-    for (int i = 0; i < nkb && ok; ++i) {
-      const int s = i % stages;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->empty[s], ((i / stages) & 1) ^ 1, p.status));
-      if (!ok) break;
-      uint8_t* w_dst = smem + (size_t)s * stage_bytes + (size_t)r * 128;
-      const int kb = kb0 + i;
-      uint4 raw0 = make_uint4(0, 0, 0, 0), raw1 = raw0;
-      uint32_t sfw = 0;
-      if (row_ok) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.wq + n * (p.K / 2) + (size_t)kb * 32);
-        raw0 = src[0];
-        raw1 = src[1];
-        sfw = *reinterpret_cast<const uint32_t*>(p.sf + n * (p.K / 16) + (size_t)kb * 4);
-      }
-      const uint32_t words[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {           // 8 columns (16 bytes of bf16) per chunk
-        const float sc = e4m3_to_float((uint8_t)(sfw >> ((c >> 1) * 8))) * g;
-        const uint32_t wd = words[c];
-        uint32_t o[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t byte = (wd >> (e * 8)) & 0xffu;
-          o[e] = pack_bf16x2(e2m1_value(byte & 15u) * sc, e2m1_value(byte >> 4) * sc);
-        }
-        *reinterpret_cast<uint4*>(w_dst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->raw_full[s]);
-    }
-    // ---- epilogue ----
-    if (ok && nkb > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[0], 0, p.status));
-    if (ok) {
-      tc_fence_after_sync();
-      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      const float bias_v = (p.bias && p.splits == 1 && row_ok) ? __bfloat162float(p.bias[n]) : 0.f;
-      for (int c = 0; c < p.mp / 16; ++c) {
-        uint32_t rr[16];
-        if (nkb > 0) { tmem_ld_32x32b_x16(t_addr + c * 16, rr); tmem_ld_wait(); }
-        else {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) rr[e] = 0;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int m = c * 16 + e;
-            if (m < p.M) {
-              const float v = __uint_as_float(rr[e]);
-              if (p.splits > 1) p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
-              else p.out[(size_t)m * p.ldo + n] = __float2bfloat16(v + bias_v);
-            }
-          }
-        }
-      }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
-}
-
-__global__ void w4_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, bf16* out,
-                                        int ldo, const bf16* __restrict__ bias) {
-  const size_t total = (size_t)M * N;
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int m = (int)(i / N), n = (int)(i % N);
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + i];
-    if (bias) acc += __bfloat162float(bias[n]);
-    out[(size_t)m * ldo + n] = __float2bfloat16(acc);
-  }
-}
-
 // ---------------------------------------------------------------------------------------
 // Producers
 // ---------------------------------------------------------------------------------------
@@ -510,58 +350,6 @@ int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, 
   nvfp4_dequant_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const uint8_t*)packed, (const uint8_t*)sf, gscale,
                                                              (bf16*)out, N, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
-}
-
-// Small-M fused path (M <= 256, K a multiple of 64). workspace: fp32 [splits, M, N] for split-K.
-int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out,
-                    int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes,
-                    cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (M > 256 || (K & 63) || (lda & 7) || (ldo & 7)) return -1;
-  W4Params p{};
-  p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
-  p.wq = (const uint8_t*)wq; p.sf = (const uint8_t*)sf; p.gscale = gscale; p.bias = (const bf16*)bias;
-  p.mp = (M + 15) & ~15;
-  p.status = device_status_word();
-  const int sms = b200_num_sms();
-  const int tiles_n = (N + 127) / 128, kblocks = K / 64;
-  int splits = 1;
-  if (tiles_n < sms) {
-    splits = sms / tiles_n;
-    if (splits > kblocks / 4) splits = kblocks / 4 > 0 ? kblocks / 4 : 1;
-    if (splits > 16) splits = 16;
-    while (splits > 1 && (!workspace || (size_t)splits * M * N * 4 > ws_bytes)) --splits;
-  }
-  const int kb_per = (kblocks + splits - 1) / splits;
-  splits = (kblocks + kb_per - 1) / kb_per;
-  p.splits = splits; p.kb_per_split = kb_per; p.workspace = (float*)workspace;
-  const int stage_bytes = 16384 + p.mp * 128;
-  int stages = (200 * 1024) / stage_bytes;
-  if (stages > kQMaxStages) stages = kQMaxStages;
-  if (stages > kb_per) stages = kb_per;
-  if (stages < 2) stages = 2;
-  p.stages = stages;
-  uint32_t tmem_cols = 32;
-  while ((int)tmem_cols < p.mp) tmem_cols <<= 1;
-  CUtensorMap tmA;
-  if (!encode_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, p.mp, 64, CU_TENSOR_MAP_SWIZZLE_128B))
-    return -3;
-  static bool set = false;
-  if (!set) {
-    cudaFuncSetAttribute(gemm_w4a16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    set = true;
-  }
-  const size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(QBars);
-  gemm_w4a16_swap_kernel<<<dim3(tiles_n, splits), kQThreads, smem, stream>>>(tmA, p, tmem_cols);
-  if (cudaGetLastError() != cudaSuccess) return -2;
-  if (splits > 1) {
-    const size_t total = (size_t)M * N;
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > sms * 8) blocks = sms * 8;
-    w4_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, p.out, ldo, p.bias);
-    if (cudaGetLastError() != cudaSuccess) return -2;
-  }
-  return 0;
 }
 
 int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int gemma, const float* scale,

@@ -1,0 +1,386 @@
+// NVFP4-weight x 16-bit-activation GEMM for decode-sized batches (M <= 128), swap-AB:
+// out[M, N] = A[M, K] * dequant(W)[N, K]^T, W = e2m1 nibbles * e4m3 scale per 16 * fp32 global.
+//
+// The packed weights are the only large stream (K / 2 bytes per row), so the kernel is built
+// around keeping them moving: TMA brings 128-row x 256-element packed blocks (16 KB) into a deep
+// ring; eight converter warps expand them to f16 with the hardware conversions
+// (cvt.rn.f16x2.e2m1x2 for two nibbles, cvt.rn.f16x2.e4m3x2 for two scales, one HMUL2 per two
+// elements) straight into 128-byte-swizzled K-major tiles; one thread issues f16 tcgen05 MMAs
+// with the weights as the 128-row operand and the (pre-cast f16) activations as the narrow N
+// operand. value x block scale is exact in f16 (at most 5 significant bits, magnitude <= 2688);
+// the fp32 global scale is applied to the accumulators in the epilogue. Block scales of the
+// CTA's K range sit in shared memory, loaded once. Split-K over blockIdx.y with fp32 partials.
+//
+// Reference: src/vt/cuda/cuda_matmul_nvfp4_w4a16.cu (portable wmma W4A16), Marlin dense NVFP4.
+#include <cuda_fp16.h>
+
+#include "api.h"
+#include "sm100.cuh"
+
+namespace b200 {
+
+using bf16 = __nv_bfloat16;
+
+static constexpr int kWThreads = 11 * 32;   // raw TMA | MMA | act TMA | 8 converter / epilogue warps
+static constexpr int kRawBytes = 128 * 128;  // 128 rows x 256 nibbles
+static constexpr int kExpBytes = 2 * 128 * 128;   // two 64-column f16 tiles
+static constexpr int kMaxRS = 4, kES = 2;
+static constexpr int kSfWords = 64;          // scale words per row in shared memory (4096 elements)
+static constexpr int kSfStride = 129;
+
+struct W4SParams {
+  int M, N, K;
+  bf16* out;
+  int ldo;
+  const uint8_t* sf;      // [N, K/16] e4m3
+  const float* gscale;
+  const bf16* bias;
+  int mp, rs, splits, ne_per_split;
+  float* workspace;       // [splits, M, N] fp32 (splits > 1)
+  int* status;
+};
+
+struct alignas(8) W4SBars {
+  uint64_t raw_full[kMaxRS], raw_empty[kMaxRS];
+  uint64_t exp_full[kES], exp_empty[kES];
+  uint64_t act_full[kES];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+};
+
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// kind::f16 with f16 A and B, f32 accumulation, both K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// Eight e2m1 nibbles (low nibble first) -> four f16x2.
+__device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
+  asm volatile(
+      "{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+// Two e4m3 bytes -> f16x2.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(uint16_t v) {
+  uint32_t r;
+  asm volatile("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
+  __half2 x = *reinterpret_cast<__half2*>(&a), y = *reinterpret_cast<__half2*>(&b);
+  __half2 z = __hmul2(x, y);
+  return *reinterpret_cast<uint32_t*>(&z);
+}
+
+__global__ void __launch_bounds__(kWThreads, 1)
+    gemm_w4a16_stream_kernel(const __grid_constant__ CUtensorMap tmW,
+                             const __grid_constant__ CUtensorMap tmA, W4SParams p, uint32_t tmem_cols) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int RS = p.rs;
+  const int act_bytes = p.mp * 256;                 // two 64-column f16 tiles of mp rows
+  uint8_t* sRaw = smem;
+  uint8_t* sExp = sRaw + (size_t)RS * kRawBytes;
+  uint8_t* sAct = sExp + (size_t)kES * kExpBytes;
+  uint32_t* sS = reinterpret_cast<uint32_t*>(sAct + (size_t)kES * act_bytes);
+  W4SBars* bars = reinterpret_cast<W4SBars*>(reinterpret_cast<uint8_t*>(sS) + kSfWords * kSfStride * 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tn = blockIdx.x, split = blockIdx.y;
+  const int n0 = tn * 128;
+  const int ne_total = (p.K + 127) / 128;
+  const int e0 = split * p.ne_per_split;
+  const int ne = max(0, min(ne_total, e0 + p.ne_per_split) - e0);
+  const int k0 = e0 * 128;                          // first element of this split
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kMaxRS; ++s) {
+      mbar_init(&bars->raw_full[s], 1);
+      mbar_init(&bars->raw_empty[s], 16);           // 8 warps x 2 halves
+    }
+    for (int s = 0; s < kES; ++s) {
+      mbar_init(&bars->exp_full[s], 8);
+      mbar_init(&bars->exp_empty[s], 1);
+      mbar_init(&bars->act_full[s], 1);
+    }
+    mbar_init(&bars->acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
+  // block scales of this CTA's rows and K range: word w of row r = scales of elements
+  // [k0 + 64 w, k0 + 64 w + 64); lanes run along K for the global read, along rows later
+  {
+    const int words_row = p.K / 64;                 // 4-byte words per weight row
+    const int w_first = k0 / 64;
+    const int nwords = min(kSfWords, ne * 2);
+    for (int idx = threadIdx.x; idx < nwords * 128; idx += blockDim.x) {
+      const int r = idx / nwords, w = idx % nwords;
+      uint32_t v = 0;
+      if (n0 + r < p.N && w_first + w < words_row)
+        v = *reinterpret_cast<const uint32_t*>(p.sf + (size_t)(n0 + r) * (p.K / 16) + (size_t)(w_first + w) * 4);
+      sS[w * kSfStride + r] = v;
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- packed-weight producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmW);
+      const int nr = (ne + 1) / 2;
+      for (int i = 0; i < nr; ++i) {
+        const int rs = i % RS;
+        if (!mbar_wait(&bars->raw_empty[rs], ((i / RS) & 1) ^ 1, p.status)) break;
+        mbar_expect_tx(&bars->raw_full[rs], kRawBytes);
+        tma_load_2d(sRaw + (size_t)rs * kRawBytes, &tmW, &bars->raw_full[rs], k0 / 2 + i * 128, n0);
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- activation producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      for (int e = 0; e < ne; ++e) {
+        const int es = e % kES;
+        if (!mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status)) break;
+        uint8_t* dst = sAct + (size_t)es * act_bytes;
+        mbar_expect_tx(&bars->act_full[es], act_bytes);
+        tma_load_2d(dst, &tmA, &bars->act_full[es], k0 + e * 128, 0);
+        tma_load_2d(dst + p.mp * 128, &tmA, &bars->act_full[es], k0 + e * 128 + 64, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(128, p.mp);
+      bool ok = true;
+      for (int e = 0; e < ne; ++e) {
+        const int es = e % kES;
+        const uint32_t ph = (e / kES) & 1;
+        if (!mbar_wait(&bars->exp_full[es], ph, p.status) || !mbar_wait(&bars->act_full[es], ph, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t w_addr = smem_u32(sExp + (size_t)es * kExpBytes);
+        const uint32_t a_addr = smem_u32(sAct + (size_t)es * act_bytes);
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt) {
+          const uint64_t wdesc = umma_desc_k_sw128(w_addr + kt * 16384, 1024);
+          const uint64_t adesc = umma_desc_k_sw128(a_addr + kt * p.mp * 128, 1024);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (e | kt | k) != 0);
+        }
+        umma_commit(&bars->exp_empty[es]);
+      }
+      if (ok) umma_commit(&bars->acc_full);
+    }
+  } else {
+    // ---------------- converters (then epilogue) ----------------
+    const int cw = warp - 3;                        // 0..7
+    const int ct = cw * 32 + lane;                  // 0..255
+    const int r = ct & 127;                         // weight row of the tile
+    const int q = ct >> 7;                          // which 64-element tile of the stage
+    bool ok = true;
+    for (int e = 0; e < ne && ok; ++e) {
+      const int es = e % kES, ri = e >> 1, rs = ri % RS;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status) &&
+                                       mbar_wait(&bars->raw_full[rs], (ri / RS) & 1, p.status));
+      if (!ok) break;
+      const uint8_t* raw = sRaw + (size_t)rs * kRawBytes + (size_t)r * 128;
+      const int c0 = (e & 1) * 4 + q * 2;           // 16-byte chunks of the raw row (swizzled)
+      const uint4 ra = *reinterpret_cast<const uint4*>(raw + (((c0 + 0) ^ (r & 7)) << 4));
+      const uint4 rb = *reinterpret_cast<const uint4*>(raw + (((c0 + 1) ^ (r & 7)) << 4));
+      const uint32_t sw = sS[(e * 2 + q) * kSfStride + r];   // 4 scales, one per 16 elements
+      const uint32_t s01 = cvt_e4m3x2((uint16_t)(sw & 0xffffu));
+      const uint32_t s23 = cvt_e4m3x2((uint16_t)(sw >> 16));
+      const uint32_t sc[4] = {__byte_perm(s01, 0, 0x1010), __byte_perm(s01, 0, 0x3232),
+                              __byte_perm(s23, 0, 0x1010), __byte_perm(s23, 0, 0x3232)};
+      const uint32_t words[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+      uint8_t* dst = sExp + (size_t)es * kExpBytes + (size_t)q * 16384 + (size_t)r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {                 // 8 elements -> one 16-byte chunk of the f16 tile
+        uint32_t h[4];
+        cvt_e2m1x8(words[c], h);
+        const uint32_t s = sc[c >> 1];
+        *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) =
+            make_uint4(hmul2_bits(h[0], s), hmul2_bits(h[1], s), hmul2_bits(h[2], s), hmul2_bits(h[3], s));
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars->exp_full[es]);
+        mbar_arrive(&bars->raw_empty[rs]);
+      }
+    }
+    // ---- epilogue: TMEM lane = weight row; two warps share a lane quarter and split the columns
+    if (ok && ne > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full, 0, p.status));
+    if (ok) {
+      tc_fence_after_sync();
+      const int quarter = warp & 3, half = cw >> 2;
+      const int n = n0 + quarter * 32 + lane;
+      const bool row_ok = n < p.N;
+      const float g = *p.gscale;
+      const float bias_v = (p.bias && p.splits == 1 && row_ok) ? __bfloat162float(p.bias[n]) : 0.f;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const int nch = p.mp / 16;
+      const int c_lo = half == 0 ? 0 : nch / 2, c_hi = half == 0 ? nch / 2 : nch;
+      for (int c = c_lo; c < c_hi; ++c) {
+        uint32_t rr[16];
+        if (ne > 0) {
+          tmem_ld_32x32b_x16(t_addr + c * 16, rr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) rr[i] = 0;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c * 16 + i;
+            if (m < p.M) {
+              const float v = __uint_as_float(rr[i]) * g;
+              if (p.splits > 1) p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
+              else p.out[(size_t)m * p.ldo + n] = __float2bfloat16(v + bias_v);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+__global__ void w4s_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, bf16* out,
+                                         int ldo, const bf16* __restrict__ bias) {
+  const size_t total = (size_t)M * N;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / N), n = (int)(i % N);
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += ws[(size_t)s * total + i];
+    if (bias) acc += __bfloat162float(bias[n]);
+    out[(size_t)m * ldo + n] = __float2bfloat16(acc);
+  }
+}
+
+// bf16 -> f16 with saturation (the MMA runs in f16; activations beyond the f16 range clamp).
+__global__ void __launch_bounds__(256)
+    cast_bf16_f16_kernel(const bf16* __restrict__ a, int lda, __half* __restrict__ out, int M, int K) {
+  const size_t total = (size_t)M * (K / 8);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / (K / 8)), c = (int)(i % (K / 8));
+    const uint4 v = *reinterpret_cast<const uint4*>(a + (size_t)m * lda + c * 8);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = unpack_bf16x2(in[j]);
+      f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+      f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+      __half2 h = __floats2half2_rn(f.x, f.y);
+      o[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)m * K + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+// Small-M fused path (M <= 128, K a multiple of 64). workspace: f16 copy of A (M * K * 2 bytes,
+// rounded up to 256) followed by fp32 [splits, M, N] split-K partials; returns -4 if it is too
+// small for even one split.
+int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out,
+                    int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes,
+                    cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 128 || (K & 63) || (lda & 7) || (ldo & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(workspace)) & 15) return -1;
+  const size_t a16_bytes = (((size_t)M * K * 2) + 255) & ~(size_t)255;
+  if (!workspace || ws_bytes < a16_bytes) return -4;
+  W4SParams p{};
+  p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
+  p.sf = (const uint8_t*)sf; p.gscale = gscale; p.bias = (const bf16*)bias;
+  p.mp = (M + 15) & ~15;
+  p.status = device_status_word();
+  const int sms = b200_num_sms();
+  const int tiles_n = (N + 127) / 128;
+  const int ne_total = (K + 127) / 128;
+  // split-K: fill the SMs, keep at least 4 stages per split, at most 32 (the scale table)
+  int splits = (ne_total + 31) / 32;
+  if (tiles_n * splits < sms) {
+    int want = sms / tiles_n;
+    if (want > ne_total / 4) want = ne_total / 4 > 0 ? ne_total / 4 : 1;
+    if (want > 16) want = 16;
+    if (want > splits) splits = want;
+  }
+  const size_t part_room = ws_bytes - a16_bytes;
+  while (splits > (ne_total + 31) / 32 && (size_t)splits * M * N * 4 > part_room) --splits;
+  int ne_per = (ne_total + splits - 1) / splits;
+  ne_per = (ne_per + 1) & ~1;                       // whole 256-element raw blocks per split
+  if (ne_per > 32) return -4;
+  splits = (ne_total + ne_per - 1) / ne_per;
+  if (splits > 1 && (size_t)splits * M * N * 4 > part_room) return -4;
+  p.splits = splits; p.ne_per_split = ne_per;
+  p.workspace = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + a16_bytes);
+  p.rs = p.mp <= 64 ? 4 : 2;
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < p.mp) tmem_cols <<= 1;
+
+  __half* a16 = reinterpret_cast<__half*>(workspace);
+  {
+    const size_t total = (size_t)M * (K / 8);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > sms * 4) blocks = sms * 4;
+    cast_bf16_f16_kernel<<<blocks, 256, 0, stream>>>((const bf16*)A, lda, a16, M, K);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+  }
+  CUtensorMap tmW, tmA;
+  if (!encode_tmap_2d(&tmW, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, 128,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  if (!encode_tmap_2d(&tmA, a16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, M, K, K, p.mp, 64,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  static bool set = false;
+  if (!set) {
+    cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    set = true;
+  }
+  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)kES * kExpBytes + (size_t)kES * p.mp * 256 +
+                      (size_t)kSfWords * kSfStride * 4 + 1024 + sizeof(W4SBars);
+  gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, p, tmem_cols);
+  if (cudaGetLastError() != cudaSuccess) return -2;
+  if (splits > 1) {
+    const size_t total = (size_t)M * N;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > sms * 8) blocks = sms * 8;
+    w4s_splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, p.out, ldo, p.bias);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+  }
+  return 0;
+}
+
+}  // extern "C"

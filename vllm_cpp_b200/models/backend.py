@@ -140,7 +140,7 @@ class GpuBackend:
             from ..ops import quant as Q
             N, K = w.shape
             scratch = None
-            if a.shape[0] > 256:
+            if a.shape[0] > 128:
                 # one expansion buffer per device, shared by every layer (stream ordered)
                 key = (a.device, N * K)
                 scratch = _SHARED_SCRATCH.get(key)

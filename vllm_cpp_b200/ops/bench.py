@@ -109,6 +109,43 @@ def small_case(name: str):
         M.moe_sort(ids, 0, E, ws)
         M.moe_gather(x, ws, E, T * k)
         fn = lambda: M.grouped_gemm(ws.xs, wgu, ws.gu, ws, T * k)
+    elif name == "gemm_streamk_small":
+        # Llama-8B down projection at a mixed-step batch: 80 pair tiles on 74 CTA pairs, so the six
+        # tiles of the ragged wave run as stream-K
+        a = torch.randn(1280, 14336, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(4096, 14336, device=dev, dtype=torch.bfloat16) * 0.05
+        fn = lambda: ops.gemm(a, w)
+    elif name == "gemm_gated_small":
+        a = torch.randn(1280, 4096, device=dev, dtype=torch.bfloat16)
+        wg = torch.randn(14336, 4096, device=dev, dtype=torch.bfloat16) * 0.05
+        wu = torch.randn(14336, 4096, device=dev, dtype=torch.bfloat16) * 0.05
+        wil = ops.interleave_gate_up(wg, wu)
+        del wg, wu
+        fn = lambda: ops.gemm_gated(a, wil, 0)
+    elif name == "gemm_fp8_small":
+        from . import quant as Q
+        a8 = torch.randn(4096, 4096, device=dev).to(torch.float8_e4m3fn)
+        w8 = (torch.randn(6144, 4096, device=dev) * 0.05).to(torch.float8_e4m3fn)
+        sa = torch.ones(1, device=dev)
+        sw = torch.ones(1, device=dev)
+        fn = lambda: Q.gemm_fp8(a8, w8, sa, sw)
+    elif name == "gemm_w4a16_small":
+        from . import quant as Q
+        a = torch.randn(64, 4096, device=dev, dtype=torch.bfloat16)
+        packed = torch.randint(0, 256, (28672, 2048), device=dev, dtype=torch.uint8)
+        sf = torch.full((28672, 256), 0x38, device=dev, dtype=torch.uint8)     # e4m3 1.0
+        g = torch.full((1,), 0.01, device=dev)
+        fn = lambda: Q.gemm_w4a16(a, packed, sf, g)
+    elif name == "mla_decode_small":
+        from . import mla as MLA
+        B, H, ctx, mbs = 128, 16, 1024, 64
+        nb = ctx // mbs
+        cache = torch.randn(B * nb + 1, mbs, 576, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        qabs = torch.randn(B, H, 576, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(B, H, 512, device=dev, dtype=torch.bfloat16)
+        fn = lambda: MLA.mla_decode(qabs, cache, bt, sl, out, 576 ** -0.5, mbs)
     else:
         raise SystemExit(f"unknown case {name}")
     ms = _time(fn, iters=3, warmup=1)
@@ -122,7 +159,8 @@ def main():
     ap.add_argument("--case", default=None,
                     help="run one small case only (for profiler captures): "
                          "gemm_small | gemm_decode_small | prefill_small | decode_small | gdn_scan_small | "
-                         "gdn_decode_small | moe_small")
+                         "gdn_decode_small | moe_small | gemm_streamk_small | gemm_gated_small | "
+                         "gemm_fp8_small | gemm_w4a16_small | mla_decode_small")
     args = ap.parse_args()
     if args.case:
         return small_case(args.case)

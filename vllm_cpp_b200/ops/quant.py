@@ -50,7 +50,7 @@ def nvfp4_dequant(packed, sf, gscale, out=None):
 
 def gemm_w4a16(a, packed, sf, gscale, out=None, bias=None, scratch=None):
     """a bf16 [M, K]; packed uint8 [N, K/2]; sf e4m3 bytes [N, K/16]; gscale fp32 [1] (multiplier).
-    M <= 256 runs the fused expand-in-shared-memory kernel; larger M expands the matrix into
+    M <= 128 runs the fused expand-in-shared-memory kernel; larger M expands the matrix into
     ``scratch`` (bf16 [N, K]) once and runs the bf16 GEMM."""
     _declare()
     from . import gemm
@@ -58,8 +58,8 @@ def gemm_w4a16(a, packed, sf, gscale, out=None, bias=None, scratch=None):
     N = packed.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-    if M <= 256:
-        ws = workspace(a.device, 16 << 20, "w4")
+    if M <= 128:
+        ws = workspace(a.device, 64 << 20, "w4")
         check(lib().b200_gemm_w4a16(ptr(a), a.stride(0), ptr(packed), ptr(sf), ptr(gscale), ptr(out),
                                     out.stride(0), ptr(bias), M, N, K, ptr(ws), ws.numel(), stream_ptr()),
               "gemm_w4a16")
