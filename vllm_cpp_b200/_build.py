@@ -118,10 +118,27 @@ def build_capi(verbose: bool = False) -> Path:
     return capi
 
 
+def build_cpu(verbose: bool = False) -> Path:
+    """``_cpu.so``: the native CPU backend (thread pool + bf16 ops). Host floating point is pinned
+    with -ffp-contract=off; the vector tiers are selected at run time inside the library."""
+    out = PKG / "_cpu.so"
+    srcs = sorted((CSRC / "cpu").glob("*.cpp"))
+    if not srcs:
+        return out
+    hdrs = sorted((CSRC / "cpu").glob("*.h"))
+    if any(_newer(s, hdrs, out) for s in srcs):
+        _run([CXX, "-O3", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-ffp-contract=off",
+              "-fno-math-errno", "-shared", "-o", str(out), *map(str, srcs)])
+        if verbose:
+            print(f"built {out} from {len(srcs)} C++ sources")
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose)
     if (CSRC / "engine").exists():
         build_engine(verbose)
+    build_cpu(verbose)
 
 
 if __name__ == "__main__":

@@ -382,6 +382,9 @@ class EngineArgs:
     # spec_decode.SpeculativeConfig; method "ngram" is wired through the engine (prompt-lookup
     # drafts, argmax verification), the other methods have their building blocks only
     speculative_config: Optional[object] = None
+    # device "cpu": "torch" = the fp32 PyTorch oracle the GPU path is compared with,
+    # "native" = the C++ thread-pool backend (csrc/cpu)
+    cpu_backend: str = "torch"
     enable_cuda_graphs: bool = True
     seed: int = 0
     device: str = "cuda"

@@ -75,6 +75,9 @@ class LLM:
         self.max_model_len = max_len
         _, cls = registry.resolve(cfg.architecture)
         self.model = cls(cfg, device=device, parallel=par, comm=self.comm, max_position=max_len)
+        if torch.device(device).type == "cpu" and args.cpu_backend == "native":
+            from ..models.backend import CpuNativeBackend
+            self.model.be = CpuNativeBackend(device)
         if tensors is not None:
             self.model.load_weights(tensors)
         else:

@@ -126,6 +126,62 @@ class CpuBackend:
         return logits.argmax(-1)
 
 
+class CpuNativeBackend(CpuBackend):
+    """The CPU execution path proper: the C++ thread-pool backend (``csrc/cpu``) for the ops of
+    a decoder forward pass; anything it does not cover falls through to the oracle."""
+    name = "cpu-native"
+
+    def __init__(self, device="cpu"):
+        super().__init__(device)
+        from ..ops import cpu_native
+        self.n = cpu_native
+        cpu_native.lib()
+
+    def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        if isinstance(w, QuantWeight) or a.dtype != torch.bfloat16 or a.stride(-1) != 1:
+            return super().gemm(a, w, bias, residual, out, out_dtype)
+        return self.n.gemm(a, w, bias, residual, out, out.dtype if out is not None else out_dtype)
+
+    def rmsnorm(self, x, w, eps, residual=None, out=None, gemma=False):
+        if x.dtype != torch.bfloat16 or (out is not None and out.data_ptr() == x.data_ptr()):
+            return super().rmsnorm(x, w, eps, residual, out, gemma)
+        return self.n.rmsnorm(x, w, eps, residual, out, gemma)
+
+    def act_and_mul(self, x, kind=0, out=None, interleaved=False):
+        assert not interleaved
+        if x.dtype != torch.bfloat16:
+            return super().act_and_mul(x, kind, out)
+        return self.n.act_and_mul(x, kind, out)
+
+    def embedding(self, ids, table, out=None, vocab_start=0, vocab_total=None, scale=1.0):
+        if table.dtype != torch.bfloat16:
+            return super().embedding(ids, table, out, vocab_start, vocab_total, scale)
+        return self.n.embedding(ids, table, out, vocab_start, scale)
+
+    def rope_kv(self, qkv, positions, table, *, num_q_heads, num_kv_heads, head_dim, rot_dim,
+                neox, q_norm, k_norm, eps, gemma, slot_mapping, kv_cache, block_size,
+                q_head_stride=None, offsets=None):
+        if qkv.dtype != torch.bfloat16 or q_head_stride is not None or offsets is not None:
+            return super().rope_kv(qkv, positions, table, num_q_heads=num_q_heads, num_kv_heads=num_kv_heads,
+                                   head_dim=head_dim, rot_dim=rot_dim, neox=neox, q_norm=q_norm, k_norm=k_norm,
+                                   eps=eps, gemma=gemma, slot_mapping=slot_mapping, kv_cache=kv_cache,
+                                   block_size=block_size)
+        self.n.rope_kv(qkv, positions, table, num_q_heads=num_q_heads, num_kv_heads=num_kv_heads,
+                       head_dim=head_dim, rot_dim=rot_dim, neox=neox, q_norm=q_norm, k_norm=k_norm, eps=eps,
+                       gemma=gemma, slot_mapping=slot_mapping, kv_cache=kv_cache, block_size=block_size)
+
+    def attention(self, q, kv_cache, ctx, group, *, num_q_heads, num_kv_heads, head_dim,
+                  block_size, scale, out=None, softcap=0.0, window=0):
+        if q.dtype != torch.bfloat16 or q.stride(-1) != 1:
+            return super().attention(q, kv_cache, ctx, group, num_q_heads=num_q_heads, num_kv_heads=num_kv_heads,
+                                     head_dim=head_dim, block_size=block_size, scale=scale, out=out,
+                                     softcap=softcap, window=window)
+        return self.n.paged_attention(q, kv_cache, ctx.block_table[group], ctx.seq_lens, ctx.query_start,
+                                      num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                                      block_size=block_size, scale=scale, softcap=softcap, window=window,
+                                      out=out)
+
+
 class GpuBackend:
     name = "cuda"
 
