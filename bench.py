@@ -180,9 +180,14 @@ def main() -> int:
     def new_prompt():
         return torch.randint(0, cfg.vocab_size, (IN,), generator=gen).tolist()
 
+    # per-request latency bookkeeping (host clock): time to first token and time per output token
+    t_submit, t_first, n_out = {}, {}, {}
+    ttft_ms, tpot_ms = [], []
+
     def submit(out_len):
-        llm.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=out_len,
-                                                     ignore_eos=True))
+        rid = llm.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=out_len,
+                                                           ignore_eos=True))
+        t_submit[rid] = time.perf_counter()
 
     # ---- ramp to steady state (untimed): staggered output lengths for the first wave
     llm.runner.warmup_graphs()
@@ -194,10 +199,21 @@ def main() -> int:
     def step_and_refill():
         """One engine step; finished requests are replaced at once (closed loop)."""
         outs = llm.step()
+        now = time.perf_counter()
         fin = 0
         for st in outs:
+            rid = st.request_id
+            if rid not in t_first:
+                t_first[rid] = now
+                if rid in t_submit:
+                    ttft_ms.append((now - t_submit[rid]) * 1e3)
+            n_out[rid] = n_out.get(rid, 0) + 1
             if st.finished:
                 fin += 1
+                if n_out[rid] > 1:
+                    tpot_ms.append((now - t_first[rid]) * 1e3 / (n_out[rid] - 1))
+                for d in (t_submit, t_first, n_out):
+                    d.pop(rid, None)
         for _ in range(fin):
             submit(OUT)
         return outs
@@ -230,6 +246,8 @@ def main() -> int:
     barrier()
     llm.runner.step_events = []
     llm.runner.time_steps = True
+    ttft_ms.clear()
+    tpot_ms.clear()
     sampler.start()
     t0 = time.perf_counter()
     for i in range(args.steps):
@@ -246,7 +264,11 @@ def main() -> int:
     d2h = (llm.runner.d2h_bytes - d2h0) / args.steps
     status = llm.runner.ops.read_status()
 
-    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
+    def p50(xs):
+        return sorted(xs)[len(xs) // 2] if xs else -1.0
+
+    # latencies of the requests that got their first token / finished inside the timed region
+    t = torch.tensor([dev_ms, wall * 1e3, p50(ttft_ms), p50(tpot_ms)], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if dp:
@@ -256,6 +278,10 @@ def main() -> int:
             tokens, launches, h2d, d2h, status = (int(sums[0]), int(sums[1]), float(sums[2]),
                                                   float(sums[3]), int(sums[4]))
     dev_ms, wall_ms = float(t[0]), float(t[1])
+    lat = {"p50_ttft_ms": round(float(t[2]), 2) if float(t[2]) >= 0 else None,
+           "p50_tpot_ms": round(float(t[3]), 3) if float(t[3]) >= 0 else None,
+           "note": "host clock, requests whose first token / last token fell inside the timed "
+                   "region; worst rank"}
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / (wall_ms / 1e3)
     if rank == 0:
@@ -277,6 +303,7 @@ def main() -> int:
                        "async_scheduling": not args.sync_scheduling,
                        **({"layers_override": args.layers} if args.layers > 0 else {})},
             "clocks": clocks,
+            "latency": lat,
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "wall_ms_per_step": round(wall_ms / args.steps, 4)},
             "gpu_launches": int(launches), "output_tokens": tokens, "kernel_status": status,

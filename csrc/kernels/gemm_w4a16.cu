@@ -8,8 +8,9 @@
 // elements) straight into 128-byte-swizzled K-major tiles; one thread issues f16 tcgen05 MMAs
 // with the weights as the 128-row operand and the (pre-cast f16) activations as the narrow N
 // operand. value x block scale is exact in f16 (at most 5 significant bits, magnitude <= 2688);
-// the fp32 global scale is applied to the accumulators in the epilogue. Block scales of the
-// CTA's K range sit in shared memory, loaded once. Split-K over blockIdx.y with fp32 partials.
+// the fp32 global scale is applied to the accumulators in the epilogue. Each converter thread
+// reads its four block scales of a stage as one word, one stage ahead. Split-K over blockIdx.y
+// with fp32 partials.
 //
 // Reference: src/vt/cuda/cuda_matmul_nvfp4_w4a16.cu (portable wmma W4A16), Marlin dense NVFP4.
 #include <cuda_fp16.h>
@@ -21,12 +22,10 @@ namespace b200 {
 
 using bf16 = __nv_bfloat16;
 
-static constexpr int kWThreads = 11 * 32;   // raw TMA | MMA | act TMA | 8 converter / epilogue warps
+static constexpr int kWThreads = 19 * 32;   // raw TMA | MMA | act TMA | 16 converter / epilogue warps
 static constexpr int kRawBytes = 128 * 128;  // 128 rows x 256 nibbles
 static constexpr int kExpBytes = 2 * 128 * 128;   // two 64-column f16 tiles
-static constexpr int kMaxRS = 4, kES = 2;
-static constexpr int kSfWords = 64;          // scale words per row in shared memory (4096 elements)
-static constexpr int kSfStride = 129;
+static constexpr int kMaxRS = 4, kMaxES = 3, kMaxAS = 6;
 
 struct W4SParams {
   int M, N, K;
@@ -35,15 +34,15 @@ struct W4SParams {
   const uint8_t* sf;      // [N, K/16] e4m3
   const float* gscale;
   const bf16* bias;
-  int mp, rs, splits, ne_per_split;
+  int mp, rs, es, as, splits, ne_per_split;
   float* workspace;       // [splits, M, N] fp32 (splits > 1)
   int* status;
 };
 
 struct alignas(8) W4SBars {
   uint64_t raw_full[kMaxRS], raw_empty[kMaxRS];
-  uint64_t exp_full[kES], exp_empty[kES];
-  uint64_t act_full[kES];
+  uint64_t exp_full[kMaxES], exp_empty[kMaxES];
+  uint64_t act_full[kMaxAS], act_empty[kMaxAS];
   uint64_t acc_full;
   uint32_t tmem_base;
 };
@@ -90,13 +89,12 @@ __global__ void __launch_bounds__(kWThreads, 1)
                              const __grid_constant__ CUtensorMap tmA, W4SParams p, uint32_t tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int RS = p.rs;
+  const int RS = p.rs, kES = p.es, AS = p.as;
   const int act_bytes = p.mp * 256;                 // two 64-column f16 tiles of mp rows
   uint8_t* sRaw = smem;
   uint8_t* sExp = sRaw + (size_t)RS * kRawBytes;
   uint8_t* sAct = sExp + (size_t)kES * kExpBytes;
-  uint32_t* sS = reinterpret_cast<uint32_t*>(sAct + (size_t)kES * act_bytes);
-  W4SBars* bars = reinterpret_cast<W4SBars*>(reinterpret_cast<uint8_t*>(sS) + kSfWords * kSfStride * 4);
+  W4SBars* bars = reinterpret_cast<W4SBars*>(sAct + (size_t)AS * act_bytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tn = blockIdx.x, split = blockIdx.y;
@@ -109,31 +107,20 @@ __global__ void __launch_bounds__(kWThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxRS; ++s) {
       mbar_init(&bars->raw_full[s], 1);
-      mbar_init(&bars->raw_empty[s], 16);           // 8 warps x 2 halves
+      mbar_init(&bars->raw_empty[s], 32);           // 16 warps x 2 halves
     }
-    for (int s = 0; s < kES; ++s) {
-      mbar_init(&bars->exp_full[s], 8);
+    for (int s = 0; s < kMaxES; ++s) {
+      mbar_init(&bars->exp_full[s], 16);
       mbar_init(&bars->exp_empty[s], 1);
+    }
+    for (int s = 0; s < kMaxAS; ++s) {
       mbar_init(&bars->act_full[s], 1);
+      mbar_init(&bars->act_empty[s], 1);
     }
     mbar_init(&bars->acc_full, 1);
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
-  // block scales of this CTA's rows and K range: word w of row r = scales of elements
-  // [k0 + 64 w, k0 + 64 w + 64); lanes run along K for the global read, along rows later
-  {
-    const int words_row = p.K / 64;                 // 4-byte words per weight row
-    const int w_first = k0 / 64;
-    const int nwords = min(kSfWords, ne * 2);
-    for (int idx = threadIdx.x; idx < nwords * 128; idx += blockDim.x) {
-      const int r = idx / nwords, w = idx % nwords;
-      uint32_t v = 0;
-      if (n0 + r < p.N && w_first + w < words_row)
-        v = *reinterpret_cast<const uint32_t*>(p.sf + (size_t)(n0 + r) * (p.K / 16) + (size_t)(w_first + w) * 4);
-      sS[w * kSfStride + r] = v;
-    }
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -146,7 +133,7 @@ __global__ void __launch_bounds__(kWThreads, 1)
       const int nr = (ne + 1) / 2;
       for (int i = 0; i < nr; ++i) {
         const int rs = i % RS;
-        if (!mbar_wait(&bars->raw_empty[rs], ((i / RS) & 1) ^ 1, p.status)) break;
+        if (!mbar_wait_backoff(&bars->raw_empty[rs], ((i / RS) & 1) ^ 1, p.status)) break;
         mbar_expect_tx(&bars->raw_full[rs], kRawBytes);
         tma_load_2d(sRaw + (size_t)rs * kRawBytes, &tmW, &bars->raw_full[rs], k0 / 2 + i * 128, n0);
       }
@@ -155,13 +142,14 @@ __global__ void __launch_bounds__(kWThreads, 1)
     // ---------------- activation producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
+      // own ring, deeper than the expanded-weight ring: the loads do not wait for the converters
       for (int e = 0; e < ne; ++e) {
-        const int es = e % kES;
-        if (!mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status)) break;
-        uint8_t* dst = sAct + (size_t)es * act_bytes;
-        mbar_expect_tx(&bars->act_full[es], act_bytes);
-        tma_load_2d(dst, &tmA, &bars->act_full[es], k0 + e * 128, 0);
-        tma_load_2d(dst + p.mp * 128, &tmA, &bars->act_full[es], k0 + e * 128 + 64, 0);
+        const int as = e % AS;
+        if (!mbar_wait_backoff(&bars->act_empty[as], ((e / AS) & 1) ^ 1, p.status)) break;
+        uint8_t* dst = sAct + (size_t)as * act_bytes;
+        mbar_expect_tx(&bars->act_full[as], act_bytes);
+        tma_load_2d(dst, &tmA, &bars->act_full[as], k0 + e * 128, 0);
+        tma_load_2d(dst + p.mp * 128, &tmA, &bars->act_full[as], k0 + e * 128 + 64, 0);
       }
     }
   } else if (warp == 1) {
@@ -170,15 +158,15 @@ __global__ void __launch_bounds__(kWThreads, 1)
       const uint32_t idesc = umma_idesc_f16(128, p.mp);
       bool ok = true;
       for (int e = 0; e < ne; ++e) {
-        const int es = e % kES;
-        const uint32_t ph = (e / kES) & 1;
-        if (!mbar_wait(&bars->exp_full[es], ph, p.status) || !mbar_wait(&bars->act_full[es], ph, p.status)) {
+        const int es = e % kES, as = e % AS;
+        if (!mbar_wait_backoff(&bars->exp_full[es], (e / kES) & 1, p.status) ||
+            !mbar_wait_backoff(&bars->act_full[as], (e / AS) & 1, p.status)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t w_addr = smem_u32(sExp + (size_t)es * kExpBytes);
-        const uint32_t a_addr = smem_u32(sAct + (size_t)es * act_bytes);
+        const uint32_t a_addr = smem_u32(sAct + (size_t)as * act_bytes);
 #pragma unroll
         for (int kt = 0; kt < 2; ++kt) {
           const uint64_t wdesc = umma_desc_k_sw128(w_addr + kt * 16384, 1024);
@@ -188,38 +176,48 @@ __global__ void __launch_bounds__(kWThreads, 1)
             umma_f16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (e | kt | k) != 0);
         }
         umma_commit(&bars->exp_empty[es]);
+        umma_commit(&bars->act_empty[as]);
       }
       if (ok) umma_commit(&bars->acc_full);
     }
   } else {
     // ---------------- converters (then epilogue) ----------------
-    const int cw = warp - 3;                        // 0..7
-    const int ct = cw * 32 + lane;                  // 0..255
+    const int cw = warp - 3;                        // 0..15
+    const int ct = cw * 32 + lane;                  // 0..511
     const int r = ct & 127;                         // weight row of the tile
-    const int q = ct >> 7;                          // which 64-element tile of the stage
+    const int q4 = ct >> 7;                         // which 32 elements of the stage's 128
+    const int q = q4 >> 1, hh = q4 & 1;             // 64-element tile, half of it
     bool ok = true;
+    // this thread's two block scales of a stage are half of one 4-byte word of the scale matrix;
+    // the word of the next stage is fetched while the current one is converted
+    const int words_row = p.K / 64;
+    const bool row_in = n0 + r < p.N;
+    const uint32_t* sf_row = reinterpret_cast<const uint32_t*>(p.sf + (size_t)(n0 + (row_in ? r : 0)) * (p.K / 16));
+    auto scale_word = [&](int e) -> uint32_t {
+      const int w = k0 / 64 + e * 2 + q;
+      return (row_in && e < ne && w < words_row) ? __ldg(sf_row + w) : 0u;
+    };
+    uint32_t sw_next = scale_word(0);
     for (int e = 0; e < ne && ok; ++e) {
+      const uint32_t sw = sw_next;
+      sw_next = scale_word(e + 1);
       const int es = e % kES, ri = e >> 1, rs = ri % RS;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status) &&
                                        mbar_wait(&bars->raw_full[rs], (ri / RS) & 1, p.status));
       if (!ok) break;
       const uint8_t* raw = sRaw + (size_t)rs * kRawBytes + (size_t)r * 128;
-      const int c0 = (e & 1) * 4 + q * 2;           // 16-byte chunks of the raw row (swizzled)
-      const uint4 ra = *reinterpret_cast<const uint4*>(raw + (((c0 + 0) ^ (r & 7)) << 4));
-      const uint4 rb = *reinterpret_cast<const uint4*>(raw + (((c0 + 1) ^ (r & 7)) << 4));
-      const uint32_t sw = sS[(e * 2 + q) * kSfStride + r];   // 4 scales, one per 16 elements
-      const uint32_t s01 = cvt_e4m3x2((uint16_t)(sw & 0xffffu));
-      const uint32_t s23 = cvt_e4m3x2((uint16_t)(sw >> 16));
-      const uint32_t sc[4] = {__byte_perm(s01, 0, 0x1010), __byte_perm(s01, 0, 0x3232),
-                              __byte_perm(s23, 0, 0x1010), __byte_perm(s23, 0, 0x3232)};
-      const uint32_t words[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+      const int c0 = (e & 1) * 4 + q4;              // 16-byte chunk of the raw row (swizzled)
+      const uint4 ra = *reinterpret_cast<const uint4*>(raw + ((c0 ^ (r & 7)) << 4));
+      const uint32_t s2 = cvt_e4m3x2((uint16_t)(hh ? (sw >> 16) : (sw & 0xffffu)));
+      const uint32_t sc[2] = {__byte_perm(s2, 0, 0x1010), __byte_perm(s2, 0, 0x3232)};
+      const uint32_t words[4] = {ra.x, ra.y, ra.z, ra.w};
       uint8_t* dst = sExp + (size_t)es * kExpBytes + (size_t)q * 16384 + (size_t)r * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {                 // 8 elements -> one 16-byte chunk of the f16 tile
+      for (int c = 0; c < 4; ++c) {                 // 8 elements -> one 16-byte chunk of the f16 tile
         uint32_t h[4];
         cvt_e2m1x8(words[c], h);
         const uint32_t s = sc[c >> 1];
-        *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(dst + (((hh * 4 + c) ^ (r & 7)) << 4)) =
             make_uint4(hmul2_bits(h[0], s), hmul2_bits(h[1], s), hmul2_bits(h[2], s), hmul2_bits(h[3], s));
       }
       fence_proxy_async_smem();
@@ -233,14 +231,14 @@ __global__ void __launch_bounds__(kWThreads, 1)
     if (ok && ne > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full, 0, p.status));
     if (ok) {
       tc_fence_after_sync();
-      const int quarter = warp & 3, half = cw >> 2;
+      const int quarter = warp & 3, part = cw >> 2;   // four warps share a lane quarter
       const int n = n0 + quarter * 32 + lane;
       const bool row_ok = n < p.N;
       const float g = *p.gscale;
       const float bias_v = (p.bias && p.splits == 1 && row_ok) ? __bfloat162float(p.bias[n]) : 0.f;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
       const int nch = p.mp / 16;
-      const int c_lo = half == 0 ? 0 : nch / 2, c_hi = half == 0 ? nch / 2 : nch;
+      const int c_lo = nch * part / 4, c_hi = nch * (part + 1) / 4;
       for (int c = c_lo; c < c_hi; ++c) {
         uint32_t rr[16];
         if (ne > 0) {
@@ -328,8 +326,8 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
   const int sms = b200_num_sms();
   const int tiles_n = (N + 127) / 128;
   const int ne_total = (K + 127) / 128;
-  // split-K: fill the SMs, keep at least 4 stages per split, at most 32 (the scale table)
-  int splits = (ne_total + 31) / 32;
+  // split-K: fill the SMs, keep at least 4 stages per split
+  int splits = 1;
   if (tiles_n * splits < sms) {
     int want = sms / tiles_n;
     if (want > ne_total / 4) want = ne_total / 4 > 0 ? ne_total / 4 : 1;
@@ -337,15 +335,17 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
     if (want > splits) splits = want;
   }
   const size_t part_room = ws_bytes - a16_bytes;
-  while (splits > (ne_total + 31) / 32 && (size_t)splits * M * N * 4 > part_room) --splits;
+  while (splits > 1 && (size_t)splits * M * N * 4 > part_room) --splits;
   int ne_per = (ne_total + splits - 1) / splits;
   ne_per = (ne_per + 1) & ~1;                       // whole 256-element raw blocks per split
-  if (ne_per > 32) return -4;
   splits = (ne_total + ne_per - 1) / ne_per;
   if (splits > 1 && (size_t)splits * M * N * 4 > part_room) return -4;
   p.splits = splits; p.ne_per_split = ne_per;
   p.workspace = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + a16_bytes);
-  p.rs = p.mp <= 64 ? 4 : 2;
+  // ring depths by activation tile size (mp * 256 bytes per stage), about 200 KB in all
+  if (p.mp <= 32) { p.rs = 4; p.es = 3; p.as = 6; }
+  else if (p.mp <= 64) { p.rs = 3; p.es = 3; p.as = 4; }
+  else { p.rs = 2; p.es = 2; p.as = 3; }
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < p.mp) tmem_cols <<= 1;
 
@@ -369,8 +369,8 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
     cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     set = true;
   }
-  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)kES * kExpBytes + (size_t)kES * p.mp * 256 +
-                      (size_t)kSfWords * kSfStride * 4 + 1024 + sizeof(W4SBars);
+  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)p.es * kExpBytes + (size_t)p.as * p.mp * 256 + 1024 +
+                      sizeof(W4SBars);
   gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, p, tmem_cols);
   if (cudaGetLastError() != cudaSuccess) return -2;
   if (splits > 1) {

@@ -103,6 +103,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return true;
 }
 
+// Same, for single-thread producer / issuer warps that share their SM sub-partition with warps
+// doing real work: sleeps between polls so that the polling does not compete for issue slots.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(48);
+    if (((++it) & 0x3ff) == 0) {
+      if (clock64() - t0 > kSpinLimitCycles) {
+        if (status) atomicExch(status, (int)kErrMbarTimeout);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // Make generic-proxy shared-memory writes visible to the async proxy (TMA / tcgen05).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
