@@ -70,6 +70,10 @@ struct GemmParams {
   // so a tile holds both halves of 128 outputs; out[M, N / 2] = act(gate) * up. 0 = off,
   // otherwise activation kind + 1 (1 SiLU, 2 GELU-tanh, 3 GELU-erf).
   int act_fuse;
+  // fp8 (e4m3 x e4m3) instantiation of the pair kernel: out = acc * a_scale * w_scale[(n)]
+  const float* scale_a;
+  const float* scale_w;
+  int scale_w_per_channel;
   int sk;                         // number of leading tiles in the stream-K region (0 = none)
   float* sk_partials;
   uint32_t* sk_flags;
@@ -547,15 +551,18 @@ __device__ __forceinline__ void epilogue_store_gated(const GemmParams& p, const 
   }
 }
 
-template <int BN>
+// FP8 = false: bf16 operands, 64 elements per 128-byte smem row. FP8 = true: e4m3 operands
+// (kind::f8f6f4), 128 elements per row; everything else (tiles, rings, stream-K) is shared.
+template <int BN, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
                           const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  constexpr int kBK = FP8 ? 128 : b200::kBK;          // elements per k-block (128 bytes per row)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  constexpr int kABytes = kBM * kBK * 2;
-  constexpr int kBBytes = (BN / 2) * kBK * 2;
+  constexpr int kABytes = kBM * 128;
+  constexpr int kBBytes = (BN / 2) * 128;
   constexpr int kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN;
   const int stages = p.stages;
@@ -620,7 +627,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * kBM, BN);
+      constexpr uint32_t idesc = FP8 ? umma_idesc_e4m3(2 * kBM, BN) : umma_idesc_bf16(2 * kBM, BN);
       uint32_t it = 0, tc = 0;
       bool ok = true;
       SegState seg = seg_init_w(p, kblocks, pair, npairs);
@@ -641,8 +648,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint64_t adesc = umma_desc_k_sw128(a_addr, 1024);
           uint64_t bdesc = umma_desc_k_sw128(b_addr, 1024);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_bf16_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
+          for (int k = 0; k < 4; ++k) {     // four 32-byte K steps per 128-byte row
+            if (FP8) umma_f8f6f4_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
+            else umma_bf16_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
+          }
           umma_commit_pair(&bars->empty[s], 3);
         }
         if (ok) umma_commit_pair(&bars->acc_full[buf], 3);
@@ -717,6 +726,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int i = 0; i < 32; ++i) f[i] = __ldcg(src + (size_t)i * kBM);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] += f[i];
+        }
+        if (FP8) {
+          const float sa = *p.scale_a;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = tn * BN + c * 32 + i;
+            const float sw = p.scale_w_per_channel ? (col < p.N ? p.scale_w[col] : 0.f) : *p.scale_w;
+            v[i] *= sa * sw;
+          }
         }
       };
       if (BN == 256 && p.act_fuse) {
@@ -1086,13 +1104,14 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
 }
 
 // CTA-pair launch: clusters of two, as many as can be resident at once (at most one per SM pair).
-template <int BN>
+template <int BN, bool FP8 = false>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
                        cudaStream_t stream) {
-  constexpr int stage_bytes = kBM * kBK * 2 + (BN / 2) * kBK * 2;
+  constexpr int stage_bytes = kBM * 128 + (BN / 2) * 128;
+  constexpr int kbk = FP8 ? 128 : kBK;
   int stages = (kSmemBudget - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  int kblocks = (p.K + kBK - 1) / kBK;
+  int kblocks = (p.K + kbk - 1) / kbk;
   if (stages > kblocks + 1) stages = kblocks + 1;
   if (stages < 2) stages = 2;
   p.stages = stages;
@@ -1113,11 +1132,11 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (!max_clusters[dev]) {
-    cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          kSmemBudget + 4096);
     cfg.gridDim = dim3(b200_num_sms() & ~1);
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel<BN>, &cfg) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_bf16_pair_kernel<BN, FP8>, &cfg) != cudaSuccess || n < 1) {
       cudaGetLastError();
       return -2;
     }
@@ -1138,7 +1157,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   }
   cfg.gridDim = dim3(2 * pairs);
   cfg.dynamicSmemBytes = smem;
-  if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN>, tmA, tmB, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN, FP8>, tmA, tmB, p) != cudaSuccess) {
     cudaGetLastError();
     return -2;
   }
@@ -1174,6 +1193,29 @@ extern "C" int b200_gemm_bf16_gated(const void* A, int lda, const void* W, int l
   if (kind < 0 || kind > 2) return -1;
   return gemm_bf16_impl(A, lda, W, ldw, out, ldo, 0, nullptr, nullptr, 0, M, N, K, nullptr, 0,
                         force_path, nullptr, stream, kind + 1);
+}
+
+// e4m3 x e4m3 -> bf16 on the CTA-pair kernel (M > 256): out = (A W^T) * a_scale * w_scale (+ bias).
+// Reference: MatmulFp8CublasLt / MatmulFp8Cutlass in src/vt/cuda/cuda_matmul.cu.
+extern "C" int b200_gemm_fp8_pair(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                                  const float* a_scale, const float* w_scale, int w_scale_per_channel,
+                                  const void* bias, int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((K & 15) || (lda & 15) || (ldw & 15) || (N & 7) || (ldo & 7)) return -1;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.scale_a = a_scale; p.scale_w = w_scale; p.scale_w_per_channel = w_scale_per_channel;
+  p.status = device_status_word();
+  p.sk = 1;
+  p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+  p.tiles_n = (N + 255) / 256;
+  CUtensorMap tA, tB;
+  if (!encode_tmap_2d(&tA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap_2d(&tB, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldw, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -3;
+  return launch_pair<256, true>(tA, tB, p, stream);
 }
 
 // Same GEMM with the tensor-parallel prologue / epilogue described by `tp`.

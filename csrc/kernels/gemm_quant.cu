@@ -311,11 +311,20 @@ using namespace b200;
 
 extern "C" {
 
+int b200_gemm_fp8_pair(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
+                       const float* a_scale, const float* w_scale, int w_scale_per_channel, const void* bias,
+                       int M, int N, int K, cudaStream_t stream);
+
 int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int ldo, const float* a_scale,
                   const float* w_scale, int w_scale_per_channel, const void* bias, int M, int N, int K,
                   cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K & 15) || (lda & 15) || (ldw & 15) || (N & 7) || (ldo & 7)) return -1;
+  // prefill-sized batches: CTA pairs, 256 x 256 tiles, stream-K (the 128 x 128 kernel below keeps
+  // the small batches)
+  if (M > 256 && N >= 256)
+    return b200_gemm_fp8_pair(A, lda, W, ldw, out, ldo, a_scale, w_scale, w_scale_per_channel, bias, M, N, K,
+                              stream);
   CUtensorMap tmA, tmB;
   if (!encode_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, kQM, kQKB, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldw, kQN, kQKB, CU_TENSOR_MAP_SWIZZLE_128B))

@@ -16,7 +16,8 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("M,N,K,per_channel", [(128, 256, 256, False), (300, 520, 384, True), (7, 4096, 4096, False),
-                                               (1000, 1024, 2048, True)])
+                                               (1000, 1024, 2048, True), (1280, 4096, 4096, False),
+                                               (520, 4104, 1040, True)])
 def test_gemm_fp8(M, N, K, per_channel):
     torch.manual_seed(0)
     a = torch.randn(M, K, device=DEV)
