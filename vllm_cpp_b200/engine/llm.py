@@ -254,3 +254,21 @@ class LLM:
 
     def stats(self):
         return self.core.scheduler().make_stats()
+
+    def step_stats(self) -> dict:
+        """Counters of the last step: queue depths, KV usage, scheduled tokens, the host time
+        spent scheduling / updating and the device time of the step (when the runner records
+        CUDA events, ``runner.time_steps``)."""
+        st = self.core.scheduler().make_stats()
+        c = self.core
+        d = {"num_running": st.num_running_reqs, "num_waiting": st.num_waiting_reqs,
+             "kv_cache_usage": st.kv_cache_usage, "scheduled_tokens": st.step_scheduled_tokens,
+             "prefix_cache_queries": st.prefix_cache_queries, "prefix_cache_hits": st.prefix_cache_hits,
+             "num_preempted": st.num_preempted,
+             "schedule_ms": getattr(c, "last_schedule_ms", 0.0), "execute_ms": getattr(c, "last_execute_ms", 0.0),
+             "update_ms": getattr(c, "last_update_ms", 0.0),
+             "h2d_bytes": self.runner.h2d_bytes, "d2h_bytes": self.runner.d2h_bytes,
+             "kernel_launches": self.runner.launches}
+        if self.runner.spec is not None:
+            d.update({"spec_" + k: v for k, v in self.runner.spec_stats.items()})
+        return d

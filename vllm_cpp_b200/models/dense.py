@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from ..config import ModelConfig, ParallelConfig
+from ..utils import nvtx
 from .backend import make_backend
 from .base import BufferPool, StepContext, normal_, shard_cols, shard_rows
 from .rope import rope_parameters, softmax_scale
@@ -349,6 +350,8 @@ class DenseModel:
         pos = ctx.positions[:T]
         first = True
         for l, L in enumerate(self.layers):
+            if nvtx.ENABLED:          # one flat marker per layer (ranges would need a pop at every exit)
+                torch.cuda.nvtx.mark(f"layer {l}")
             grp = self.layer_group[l]
             window = c.sliding_window if (c.sliding_window and (
                 not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0

@@ -16,6 +16,8 @@ from typing import Optional
 import numpy as np
 import torch
 
+from ..utils import nvtx
+
 from .. import _engine as E
 from ..models.base import StepContext
 
@@ -313,7 +315,8 @@ class ModelRunner(E.ModelRunnerBase):
             self._graph_sampled = True
         else:
             ctx = self._context(info)
-            self._logits = self.model.forward(ctx)
+            with nvtx.range(f"forward T={T} R={R}"):
+                self._logits = self.model.forward(ctx)
             self._graph_sampled = False
         self.num_kernel_steps += 1
 
