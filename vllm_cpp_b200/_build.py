@@ -134,6 +134,28 @@ def build_cpu(verbose: bool = False) -> Path:
     return out
 
 
+def build_sanitize_driver(kind: str = "address,undefined", verbose: bool = False) -> Path:
+    """Compiles the host engine (no Python, no CUDA) with ``csrc/engine_sanitize/sanitize_main.cpp``
+    under ``-fsanitize=<kind>`` into ``build/sanitize_<kind>``; running it exercises the
+    scheduler, KV-cache manager, input batch, offload policies and the LMCache codec."""
+    tag = kind.replace(",", "_")
+    out = BUILD / f"sanitize_{tag}"
+    skip = ("bindings", "tokenizer_bindings", "structured_bindings", "offload_bindings", "extras_bindings")
+    srcs = [s for s in sorted((CSRC / "engine").rglob("*.cpp")) if s.stem not in skip]
+    srcs.append(CSRC / "engine_sanitize" / "sanitize_main.cpp")
+    hdrs = sorted((CSRC / "engine").rglob("*.h"))
+    BUILD.mkdir(parents=True, exist_ok=True)
+    # the sanitizer runtimes ship with the distribution compiler, not necessarily with $CXX
+    cxx = os.environ.get("SANITIZE_CXX") or ("/usr/bin/g++" if Path("/usr/bin/g++").exists() else CXX)
+    if any(_newer(s, hdrs, out) for s in srcs):
+        _run([cxx, "-O1", "-g", "-std=c++20", "-fno-omit-frame-pointer", f"-fsanitize={kind}",
+              "-fno-sanitize-recover=all", "-pthread", "-I", str(ROOT / "include"), "-I", str(CSRC),
+              "-I", str(CSRC / "engine"), "-o", str(out), *map(str, srcs)])
+        if verbose:
+            print(f"built {out}")
+    return out
+
+
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose)
     if (CSRC / "engine").exists():
