@@ -58,9 +58,12 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self) -> dict:
+    def stop(self, since: float = 0.0) -> dict:
+        """Summary of the samples taken at or after ``since`` (perf_counter time). The sampler is
+        started before the warm-up steps: the start-up of nvidia-smi (NVML initialisation) stalls
+        kernel launches of this process for a moment and must not land in the timed region."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -69,7 +72,9 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ts, ln in self.lines:
+            if ts < since:
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -192,9 +197,16 @@ def main() -> int:
     # ---- ramp to steady state (untimed): staggered output lengths for the first wave
     llm.runner.warmup_graphs()
     note("graphs captured")
+    # First wave: staggered output lengths so that one request finishes per step afterwards. No
+    # first-wave request may finish before the whole wave has been prefilled (C * IN tokens at
+    # the batched-token budget per step): its replacement would queue behind the remaining
+    # prompts, all such replacements would then be admitted together and finish together, and
+    # that burst would come round every OUT steps for ever.
+    fill_steps = min(OUT - 1, (C * IN + args.max_num_batched_tokens - 1) // args.max_num_batched_tokens + 2)
     for i in range(C):
-        submit(1 + (i * OUT) // C)
+        submit(fill_steps + (i * (OUT - fill_steps)) // C)
     ramp_steps = 0
+    trace = []      # verbose: (scheduled tokens, finished, preempted so far, running, waiting) per step
 
     def step_and_refill():
         """One engine step; finished requests are replaced at once (closed loop)."""
@@ -216,6 +228,9 @@ def main() -> int:
                     d.pop(rid, None)
         for _ in range(fin):
             submit(OUT)
+        if args.verbose:
+            ss = llm.step_stats()
+            trace.append((ss["scheduled_tokens"], fin, ss["num_preempted"], ss["num_running"], ss["num_waiting"]))
         return outs
 
     # the ramp ends once every first-wave request has finished (all live requests are
@@ -235,11 +250,13 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.5)                 # let nvidia-smi finish starting before anything is measured
     for _ in range(args.warmup):
         step_and_refill()
 
     # ---- timed region
-    sampler = ClockSampler(local_rank)
     h2d0, d2h0 = llm.runner.h2d_bytes, llm.runner.d2h_bytes
     launches0 = _lib.LAUNCHES[0]
     tokens = 0
@@ -248,15 +265,29 @@ def main() -> int:
     llm.runner.time_steps = True
     ttft_ms.clear()
     tpot_ms.clear()
-    sampler.start()
     t0 = time.perf_counter()
+    host_step, sched_tokens = [], []
     for i in range(args.steps):
+        ts = time.perf_counter()
         outs = step_and_refill()
+        host_step.append(time.perf_counter() - ts)
+        if args.verbose:
+            sched_tokens.append(llm.step_stats()["scheduled_tokens"])
         for st in outs:
             tokens += 1  # one new token per returned request per step (no speculative decode)
     barrier()
     wall = time.perf_counter() - t0
-    clocks = sampler.stop()
+    if args.verbose:
+        ev = [e for e in llm.runner.step_events if e[1] is not None]
+        per = [round(a.elapsed_time(b), 2) for a, b in ev]
+        gaps = [round(ev[i][1].elapsed_time(ev[i + 1][0]), 2) for i in range(len(ev) - 1)]
+        note(f"device ms per step: {per}")
+        note(f"device gaps between steps (ms): {gaps}")
+        note(f"host wall per step (ms): {[round(x * 1e3, 2) for x in host_step]}")
+        note(f"scheduled tokens per step: {sched_tokens}")
+        note(f"(tokens, finished, preempted, running, waiting) around the start of the timed region: "
+             f"{trace[-(args.steps + args.warmup + 8):][:24]}")
+    clocks = sampler.stop(since=t0)
     dev_ms = llm.runner.device_step_ms()
     llm.runner.time_steps = False
     launches = _lib.LAUNCHES[0] - launches0

@@ -127,7 +127,15 @@ def check(rc: int, what: str) -> None:
         raise KernelError(f"{what}: {_CODES.get(rc, 'error')} (code {rc})")
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """Handle of the current CUDA stream of the current device. Called once per kernel launch, so
+    it goes through the raw C entry point (``torch.cuda.current_stream()`` builds a Stream object
+    and resolves the device through several Python layers, ~14 us a call)."""
+    if _RAW_STREAM is not None:
+        return _RAW_STREAM(torch._C._cuda_getDevice())
     return torch.cuda.current_stream().cuda_stream
 
 
