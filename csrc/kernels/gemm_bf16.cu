@@ -1252,7 +1252,8 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
                           int N, int K, void* workspace, size_t ws_bytes, int force_path,
                           const B200TpGemm* tp, cudaStream_t stream, int act_fuse) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (act_fuse && (tp || M <= 256 || (N & 255) || bias || residual || out_f32)) return -1;
+  if (act_fuse && (tp || M <= 128 || (N & 255) || bias || residual || out_f32)) return -1;
+  if (act_fuse && force_path == 0) force_path = 9;      // the gated epilogue lives in the pair kernel
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
        reinterpret_cast<uintptr_t>(out)) & 15)
@@ -1287,7 +1288,17 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   const int kblocks = (K + kBK - 1) / kBK;
 
   bool use_swap = (M <= 256);
-  if (force_path == 1) use_swap = false;
+  // Small batches. An MMA instruction takes about the same time whatever its N, so swap-AB (the
+  // batch as the narrow N operand) spends one instruction per 128 weight rows x 16 k and becomes
+  // issue-bound on wide weight matrices; there the batch goes on the (padded) M side and 256
+  // weight rows share an instruction, with stream-K filling the SMs. Measured on B200:
+  // N >= 16384: 1-CTA 128 x 256 tiles + stream-K up to 128 rows, CTA pairs above;
+  // narrower matrices: swap-AB up to 128 rows, 128 x 128 tiles + stream-K above.
+  if (force_path == 0 && !tp && M <= 256) {
+    if (N >= 16384) force_path = M <= 128 ? 5 : 9;
+    else if (M > 128) force_path = 6;
+  }
+  if (force_path == 1 || force_path >= 3) use_swap = false;     // an explicit tiling was asked for
   if (force_path == 2 && M <= 256) use_swap = true;
 
   if (use_swap) {

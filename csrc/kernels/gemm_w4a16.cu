@@ -24,6 +24,7 @@ using bf16 = __nv_bfloat16;
 
 static constexpr int kWThreads = 19 * 32;   // raw TMA | MMA | act TMA | 16 converter / epilogue warps
 static constexpr int kRawBytes = 128 * 128;  // 128 rows x 256 nibbles
+static constexpr int kSfBytes = 128 * 16;    // 128 rows x 16 block scales (one raw stage)
 static constexpr int kExpBytes = 2 * 128 * 128;   // two 64-column f16 tiles
 static constexpr int kMaxRS = 4, kMaxES = 3, kMaxAS = 6;
 
@@ -35,6 +36,7 @@ struct W4SParams {
   const float* gscale;
   const bf16* bias;
   int mp, rs, es, as, splits, ne_per_split;
+  int sf_tma;             // block scales arrive by TMA with each raw stage (needs K % 256 == 0)
   float* workspace;       // [splits, M, N] fp32 (splits > 1)
   int* status;
 };
@@ -86,7 +88,8 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
 
 __global__ void __launch_bounds__(kWThreads, 1)
     gemm_w4a16_stream_kernel(const __grid_constant__ CUtensorMap tmW,
-                             const __grid_constant__ CUtensorMap tmA, W4SParams p, uint32_t tmem_cols) {
+                             const __grid_constant__ CUtensorMap tmA,
+                             const __grid_constant__ CUtensorMap tmS, W4SParams p, uint32_t tmem_cols) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int RS = p.rs, kES = p.es, AS = p.as;
@@ -94,7 +97,8 @@ __global__ void __launch_bounds__(kWThreads, 1)
   uint8_t* sRaw = smem;
   uint8_t* sExp = sRaw + (size_t)RS * kRawBytes;
   uint8_t* sAct = sExp + (size_t)kES * kExpBytes;
-  W4SBars* bars = reinterpret_cast<W4SBars*>(sAct + (size_t)AS * act_bytes);
+  uint8_t* sSf = sAct + (size_t)AS * act_bytes;      // RS x 2 KB of block scales
+  W4SBars* bars = reinterpret_cast<W4SBars*>(sSf + (size_t)kMaxRS * kSfBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tn = blockIdx.x, split = blockIdx.y;
@@ -134,8 +138,9 @@ __global__ void __launch_bounds__(kWThreads, 1)
       for (int i = 0; i < nr; ++i) {
         const int rs = i % RS;
         if (!mbar_wait_backoff(&bars->raw_empty[rs], ((i / RS) & 1) ^ 1, p.status)) break;
-        mbar_expect_tx(&bars->raw_full[rs], kRawBytes);
+        mbar_expect_tx(&bars->raw_full[rs], kRawBytes + (p.sf_tma ? kSfBytes : 0));
         tma_load_2d(sRaw + (size_t)rs * kRawBytes, &tmW, &bars->raw_full[rs], k0 / 2 + i * 128, n0);
+        if (p.sf_tma) tma_load_2d(sSf + (size_t)rs * kSfBytes, &tmS, &bars->raw_full[rs], k0 / 16 + i * 16, n0);
       }
     }
   } else if (warp == 2) {
@@ -197,14 +202,16 @@ __global__ void __launch_bounds__(kWThreads, 1)
       const int w = k0 / 64 + e * 2 + q;
       return (row_in && e < ne && w < words_row) ? __ldg(sf_row + w) : 0u;
     };
-    uint32_t sw_next = scale_word(0);
+    uint32_t sw_next = p.sf_tma ? 0u : scale_word(0);
     for (int e = 0; e < ne && ok; ++e) {
-      const uint32_t sw = sw_next;
-      sw_next = scale_word(e + 1);
+      uint32_t sw = sw_next;
+      if (!p.sf_tma) sw_next = scale_word(e + 1);
       const int es = e % kES, ri = e >> 1, rs = ri % RS;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status) &&
                                        mbar_wait(&bars->raw_full[rs], (ri / RS) & 1, p.status));
       if (!ok) break;
+      if (p.sf_tma)   // the four scales of this thread's 64-element tile: bytes (e & 1) * 8 + q * 4 of its row
+        sw = *reinterpret_cast<const uint32_t*>(sSf + (size_t)rs * kSfBytes + r * 16 + (e & 1) * 8 + q * 4);
       const uint8_t* raw = sRaw + (size_t)rs * kRawBytes + (size_t)r * 128;
       const int c0 = (e & 1) * 4 + q4;              // 16-byte chunk of the raw row (swizzled)
       const uint4 ra = *reinterpret_cast<const uint4*>(raw + ((c0 ^ (r & 7)) << 4));
@@ -357,21 +364,26 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
     cast_bf16_f16_kernel<<<blocks, 256, 0, stream>>>((const bf16*)A, lda, a16, M, K);
     if (cudaGetLastError() != cudaSuccess) return -2;
   }
-  CUtensorMap tmW, tmA;
+  CUtensorMap tmW, tmA, tmS;
+  p.sf_tma = ((K & 255) == 0 && (reinterpret_cast<uintptr_t>(sf) & 15) == 0) ? 1 : 0;
   if (!encode_tmap_2d(&tmW, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, 128,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
   if (!encode_tmap_2d(&tmA, a16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, M, K, K, p.mp, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
+  tmS = tmW;
+  if (p.sf_tma && !encode_tmap_2d(&tmS, sf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 16, K / 16, 128, 16,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE))
+    return -3;
   static bool set = false;
   if (!set) {
     cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     set = true;
   }
-  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)p.es * kExpBytes + (size_t)p.as * p.mp * 256 + 1024 +
-                      sizeof(W4SBars);
-  gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, p, tmem_cols);
+  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)p.es * kExpBytes + (size_t)p.as * p.mp * 256 +
+                      (size_t)kMaxRS * kSfBytes + 1024 + sizeof(W4SBars);
+  gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, tmS, p, tmem_cols);
   if (cudaGetLastError() != cudaSuccess) return -2;
   if (splits > 1) {
     const size_t total = (size_t)M * N;

@@ -105,7 +105,7 @@ def gemm_gated(a: torch.Tensor, w_il: torch.Tensor, kind: int = ACT_SILU, *,
                out: torch.Tensor | None = None, scratch: torch.Tensor | None = None,
                force_path: int = 0) -> torch.Tensor:
     """``act(a @ w_gate^T) * (a @ w_up^T)`` with ``w_il`` from :func:`interleave_gate_up`.
-    Above 256 rows the activation runs in the GEMM epilogue (one kernel, the merged
+    Above 128 rows the activation runs in the GEMM epilogue (one kernel, the merged
     projection never reaches memory); below, the small-M GEMM writes the interleaved
     projection to ``scratch`` and the activation kernel reads it."""
     M, K = a.shape
@@ -113,7 +113,7 @@ def gemm_gated(a: torch.Tensor, w_il: torch.Tensor, kind: int = ACT_SILU, *,
     assert a.dtype == torch.bfloat16 and w_il.dtype == torch.bfloat16 and N % 256 == 0
     if out is None:
         out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
-    if M > 256:
+    if M > 128:
         check(lib().b200_gemm_bf16_gated(ptr(a), a.stride(0), ptr(w_il), w_il.stride(0), ptr(out),
                                          out.stride(0), M, N, K, kind, force_path, stream_ptr()),
               f"gemm_gated M={M} N={N} K={K}")
