@@ -31,7 +31,7 @@ MODEL = "llama-3.1-8b"
 CONCURRENCY = 256
 INPUT_LEN = 1024
 OUTPUT_LEN = 256
-PUBLISHED_BASELINE = None  # the reference publishes no number for this config
+PUBLISHED_BASELINE = None  # the reference publishes no number for this model / hardware
 
 
 class ClockSampler:
@@ -94,7 +94,7 @@ class ClockSampler:
 
 def run_reference(args) -> int:
     # The reference ships no setup.py / pyproject.toml, so the one permitted offline install
-    # (`pip install --no-index --target baseline/_ref /root/reference`) stops with
+    # (`pip install --no-index --target baseline/_ref <reference checkout>`) stops with
     # "Neither 'setup.py' nor 'pyproject.toml' found"; there is nothing to import or run.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a CMake/C++ project: pip install --target "

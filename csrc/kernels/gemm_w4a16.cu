@@ -1,13 +1,14 @@
-// NVFP4-weight x 16-bit-activation GEMM for decode-sized batches (M <= 128), swap-AB:
+// NVFP4-weight x 16-bit-activation GEMM for decode-sized batches (M <= 128):
 // out[M, N] = A[M, K] * dequant(W)[N, K]^T, W = e2m1 nibbles * e4m3 scale per 16 * fp32 global.
 //
 // The packed weights are the only large stream (K / 2 bytes per row), so the kernel is built
-// around keeping them moving: TMA brings 128-row x 256-element packed blocks (16 KB) into a deep
-// ring; eight converter warps expand them to f16 with the hardware conversions
+// around keeping them moving: TMA brings 256-row x 256-element packed blocks (32 KB) into a
+// ring; sixteen converter warps expand them to f16 with the hardware conversions
 // (cvt.rn.f16x2.e2m1x2 for two nibbles, cvt.rn.f16x2.e4m3x2 for two scales, one HMUL2 per two
 // elements) straight into 128-byte-swizzled K-major tiles; one thread issues f16 tcgen05 MMAs
-// with the weights as the 128-row operand and the (pre-cast f16) activations as the narrow N
-// operand. value x block scale is exact in f16 (at most 5 significant bits, magnitude <= 2688);
+// with the (pre-cast f16, zero-padded) batch as the 128-row operand and 256 weight rows as the N
+// operand - an MMA instruction costs about the same whatever its N, so the wide side is where the
+// weights go. value x block scale is exact in f16 (at most 5 significant bits, magnitude <= 2688);
 // the fp32 global scale is applied to the accumulators in the epilogue. Each converter thread
 // reads its four block scales of a stage as one word, one stage ahead. Split-K over blockIdx.y
 // with fp32 partials.
@@ -23,10 +24,12 @@ namespace b200 {
 using bf16 = __nv_bfloat16;
 
 static constexpr int kWThreads = 19 * 32;   // raw TMA | MMA | act TMA | 16 converter / epilogue warps
-static constexpr int kRawBytes = 128 * 128;  // 128 rows x 256 nibbles
-static constexpr int kSfBytes = 128 * 16;    // 128 rows x 16 block scales (one raw stage)
-static constexpr int kExpBytes = 2 * 128 * 128;   // two 64-column f16 tiles
-static constexpr int kMaxRS = 4, kMaxES = 3, kMaxAS = 6;
+static constexpr int kWN = 256;              // weight rows per CTA (the MMA's N)
+static constexpr int kRawBytes = kWN * 128;  // 256 rows x 256 nibbles
+static constexpr int kSfBytes = kWN * 16;    // 256 rows x 16 block scales (one raw stage)
+static constexpr int kExpBytes = kWN * 128;  // 256 rows x 64 f16: one SW128 K-major tile
+static constexpr int kActBytes = 128 * 128;  // 128 (padded batch) rows x 64 f16
+static constexpr int kMaxRS = 2, kMaxES = 3, kMaxAS = 3;
 
 struct W4SParams {
   int M, N, K;
@@ -35,7 +38,7 @@ struct W4SParams {
   const uint8_t* sf;      // [N, K/16] e4m3
   const float* gscale;
   const bf16* bias;
-  int mp, rs, es, as, splits, ne_per_split;
+  int splits, ne_per_split;   // stages of 64 k-elements per split (a multiple of 4)
   int sf_tma;             // block scales arrive by TMA with each raw stage (needs K % 256 == 0)
   float* workspace;       // [splits, M, N] fp32 (splits > 1)
   int* status;
@@ -89,52 +92,52 @@ __device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, uint32_t b) {
 __global__ void __launch_bounds__(kWThreads, 1)
     gemm_w4a16_stream_kernel(const __grid_constant__ CUtensorMap tmW,
                              const __grid_constant__ CUtensorMap tmA,
-                             const __grid_constant__ CUtensorMap tmS, W4SParams p, uint32_t tmem_cols) {
+                             const __grid_constant__ CUtensorMap tmS, W4SParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int RS = p.rs, kES = p.es, AS = p.as;
-  const int act_bytes = p.mp * 256;                 // two 64-column f16 tiles of mp rows
+  constexpr int RS = kMaxRS, ES = kMaxES, AS = kMaxAS;
   uint8_t* sRaw = smem;
   uint8_t* sExp = sRaw + (size_t)RS * kRawBytes;
-  uint8_t* sAct = sExp + (size_t)kES * kExpBytes;
-  uint8_t* sSf = sAct + (size_t)AS * act_bytes;      // RS x 2 KB of block scales
-  W4SBars* bars = reinterpret_cast<W4SBars*>(sSf + (size_t)kMaxRS * kSfBytes);
+  uint8_t* sAct = sExp + (size_t)ES * kExpBytes;
+  uint8_t* sSf = sAct + (size_t)AS * kActBytes;      // RS x 4 KB of block scales
+  W4SBars* bars = reinterpret_cast<W4SBars*>(sSf + (size_t)RS * kSfBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tn = blockIdx.x, split = blockIdx.y;
-  const int n0 = tn * 128;
-  const int ne_total = (p.K + 127) / 128;
+  const int n0 = tn * kWN;
+  const int ne_total = (p.K + 63) / 64;
   const int e0 = split * p.ne_per_split;
   const int ne = max(0, min(ne_total, e0 + p.ne_per_split) - e0);
-  const int k0 = e0 * 128;                          // first element of this split
+  const int k0 = e0 * 64;                           // first element of this split (multiple of 256)
+  constexpr uint32_t kTmemCols = kWN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kMaxRS; ++s) {
+    for (int s = 0; s < RS; ++s) {
       mbar_init(&bars->raw_full[s], 1);
-      mbar_init(&bars->raw_empty[s], 32);           // 16 warps x 2 halves
+      mbar_init(&bars->raw_empty[s], 64);           // 16 warps x 4 sub-stages
     }
-    for (int s = 0; s < kMaxES; ++s) {
+    for (int s = 0; s < ES; ++s) {
       mbar_init(&bars->exp_full[s], 16);
       mbar_init(&bars->exp_empty[s], 1);
     }
-    for (int s = 0; s < kMaxAS; ++s) {
+    for (int s = 0; s < AS; ++s) {
       mbar_init(&bars->act_full[s], 1);
       mbar_init(&bars->act_empty[s], 1);
     }
     mbar_init(&bars->acc_full, 1);
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, kTmemCols); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
   if (warp == 0) {
-    // ---------------- packed-weight producer ----------------
+    // ---------------- packed-weight (and scale) producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmW);
-      const int nr = (ne + 1) / 2;
+      const int nr = (ne + 3) / 4;
       for (int i = 0; i < nr; ++i) {
         const int rs = i % RS;
         if (!mbar_wait_backoff(&bars->raw_empty[rs], ((i / RS) & 1) ^ 1, p.status)) break;
@@ -147,39 +150,30 @@ __global__ void __launch_bounds__(kWThreads, 1)
     // ---------------- activation producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
-      // own ring, deeper than the expanded-weight ring: the loads do not wait for the converters
       for (int e = 0; e < ne; ++e) {
         const int as = e % AS;
         if (!mbar_wait_backoff(&bars->act_empty[as], ((e / AS) & 1) ^ 1, p.status)) break;
-        uint8_t* dst = sAct + (size_t)as * act_bytes;
-        mbar_expect_tx(&bars->act_full[as], act_bytes);
-        tma_load_2d(dst, &tmA, &bars->act_full[as], k0 + e * 128, 0);
-        tma_load_2d(dst + p.mp * 128, &tmA, &bars->act_full[as], k0 + e * 128 + 64, 0);
+        mbar_expect_tx(&bars->act_full[as], kActBytes);
+        tma_load_2d(sAct + (size_t)as * kActBytes, &tmA, &bars->act_full[as], k0 + e * 64, 0);
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+    // ---------------- MMA issuer: D[128 batch rows, 256 weight rows] ----------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(128, p.mp);
+      constexpr uint32_t idesc = umma_idesc_f16(128, kWN);
       bool ok = true;
       for (int e = 0; e < ne; ++e) {
-        const int es = e % kES, as = e % AS;
-        if (!mbar_wait_backoff(&bars->exp_full[es], (e / kES) & 1, p.status) ||
+        const int es = e % ES, as = e % AS;
+        if (!mbar_wait_backoff(&bars->exp_full[es], (e / ES) & 1, p.status) ||
             !mbar_wait_backoff(&bars->act_full[as], (e / AS) & 1, p.status)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t w_addr = smem_u32(sExp + (size_t)es * kExpBytes);
-        const uint32_t a_addr = smem_u32(sAct + (size_t)as * act_bytes);
+        const uint64_t adesc = umma_desc_k_sw128(smem_u32(sAct + (size_t)as * kActBytes), 1024);
+        const uint64_t bdesc = umma_desc_k_sw128(smem_u32(sExp + (size_t)es * kExpBytes), 1024);
 #pragma unroll
-        for (int kt = 0; kt < 2; ++kt) {
-          const uint64_t wdesc = umma_desc_k_sw128(w_addr + kt * 16384, 1024);
-          const uint64_t adesc = umma_desc_k_sw128(a_addr + kt * p.mp * 128, 1024);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tmem_base, wdesc + 2 * k, adesc + 2 * k, idesc, (e | kt | k) != 0);
-        }
+        for (int k = 0; k < 4; ++k) umma_f16_ss(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (e | k) != 0);
         umma_commit(&bars->exp_empty[es]);
         umma_commit(&bars->act_empty[as]);
       }
@@ -189,43 +183,40 @@ __global__ void __launch_bounds__(kWThreads, 1)
     // ---------------- converters (then epilogue) ----------------
     const int cw = warp - 3;                        // 0..15
     const int ct = cw * 32 + lane;                  // 0..511
-    const int r = ct & 127;                         // weight row of the tile
-    const int q4 = ct >> 7;                         // which 32 elements of the stage's 128
-    const int q = q4 >> 1, hh = q4 & 1;             // 64-element tile, half of it
+    const int r = ct & 255;                         // weight row of the tile
+    const int h = ct >> 8;                          // which 32 of the stage's 64 elements
     bool ok = true;
-    // this thread's two block scales of a stage are half of one 4-byte word of the scale matrix;
-    // the word of the next stage is fetched while the current one is converted
-    const int words_row = p.K / 64;
     const bool row_in = n0 + r < p.N;
-    const uint32_t* sf_row = reinterpret_cast<const uint32_t*>(p.sf + (size_t)(n0 + (row_in ? r : 0)) * (p.K / 16));
-    auto scale_word = [&](int e) -> uint32_t {
-      const int w = k0 / 64 + e * 2 + q;
-      return (row_in && e < ne && w < words_row) ? __ldg(sf_row + w) : 0u;
+    const uint8_t* sf_row = p.sf + (size_t)(n0 + (row_in ? r : 0)) * (p.K / 16);
+    auto scale_pair = [&](int e) -> uint32_t {        // no-TMA fallback: two e4m3 bytes from global
+      const int b = k0 / 16 + e * 4 + h * 2;
+      return (row_in && e < ne && b < p.K / 16)      // K % 64 == 0: the pair is in range together
+                 ? (uint32_t)*reinterpret_cast<const uint16_t*>(sf_row + b) : 0u;
     };
-    uint32_t sw_next = p.sf_tma ? 0u : scale_word(0);
+    uint32_t sp_next = p.sf_tma ? 0u : scale_pair(0);
     for (int e = 0; e < ne && ok; ++e) {
-      uint32_t sw = sw_next;
-      if (!p.sf_tma) sw_next = scale_word(e + 1);
-      const int es = e % kES, ri = e >> 1, rs = ri % RS;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->exp_empty[es], ((e / kES) & 1) ^ 1, p.status) &&
+      uint32_t sp = sp_next;
+      if (!p.sf_tma) sp_next = scale_pair(e + 1);
+      const int es = e % ES, ri = e >> 2, rs = ri % RS, sub = e & 3;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->exp_empty[es], ((e / ES) & 1) ^ 1, p.status) &&
                                        mbar_wait(&bars->raw_full[rs], (ri / RS) & 1, p.status));
       if (!ok) break;
-      if (p.sf_tma)   // the four scales of this thread's 64-element tile: bytes (e & 1) * 8 + q * 4 of its row
-        sw = *reinterpret_cast<const uint32_t*>(sSf + (size_t)rs * kSfBytes + r * 16 + (e & 1) * 8 + q * 4);
+      if (p.sf_tma)
+        sp = *reinterpret_cast<const uint16_t*>(sSf + (size_t)rs * kSfBytes + r * 16 + sub * 4 + h * 2);
       const uint8_t* raw = sRaw + (size_t)rs * kRawBytes + (size_t)r * 128;
-      const int c0 = (e & 1) * 4 + q4;              // 16-byte chunk of the raw row (swizzled)
+      const int c0 = sub * 2 + h;                   // 16-byte chunk of the raw row (swizzled)
       const uint4 ra = *reinterpret_cast<const uint4*>(raw + ((c0 ^ (r & 7)) << 4));
-      const uint32_t s2 = cvt_e4m3x2((uint16_t)(hh ? (sw >> 16) : (sw & 0xffffu)));
+      const uint32_t s2 = cvt_e4m3x2((uint16_t)sp);
       const uint32_t sc[2] = {__byte_perm(s2, 0, 0x1010), __byte_perm(s2, 0, 0x3232)};
       const uint32_t words[4] = {ra.x, ra.y, ra.z, ra.w};
-      uint8_t* dst = sExp + (size_t)es * kExpBytes + (size_t)q * 16384 + (size_t)r * 128;
+      uint8_t* dst = sExp + (size_t)es * kExpBytes + (size_t)r * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {                 // 8 elements -> one 16-byte chunk of the f16 tile
-        uint32_t h[4];
-        cvt_e2m1x8(words[c], h);
+        uint32_t hh[4];
+        cvt_e2m1x8(words[c], hh);
         const uint32_t s = sc[c >> 1];
-        *reinterpret_cast<uint4*>(dst + (((hh * 4 + c) ^ (r & 7)) << 4)) =
-            make_uint4(hmul2_bits(h[0], s), hmul2_bits(h[1], s), hmul2_bits(h[2], s), hmul2_bits(h[3], s));
+        *reinterpret_cast<uint4*>(dst + (((h * 4 + c) ^ (r & 7)) << 4)) =
+            make_uint4(hmul2_bits(hh[0], s), hmul2_bits(hh[1], s), hmul2_bits(hh[2], s), hmul2_bits(hh[3], s));
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -234,35 +225,52 @@ __global__ void __launch_bounds__(kWThreads, 1)
         mbar_arrive(&bars->raw_empty[rs]);
       }
     }
-    // ---- epilogue: TMEM lane = weight row; two warps share a lane quarter and split the columns
+    // ---- epilogue: TMEM lane = batch row m, column = weight row n; four warps share a lane
+    // quarter and take 64 columns each
     if (ok && ne > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full, 0, p.status));
     if (ok) {
       tc_fence_after_sync();
-      const int quarter = warp & 3, part = cw >> 2;   // four warps share a lane quarter
-      const int n = n0 + quarter * 32 + lane;
-      const bool row_ok = n < p.N;
+      const int quarter = warp & 3, part = cw >> 2;
+      const int m = quarter * 32 + lane;
       const float g = *p.gscale;
-      const float bias_v = (p.bias && p.splits == 1 && row_ok) ? __bfloat162float(p.bias[n]) : 0.f;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      const int nch = p.mp / 16;
-      const int c_lo = nch * part / 4, c_hi = nch * (part + 1) / 4;
-      for (int c = c_lo; c < c_hi; ++c) {
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        const int col = part * 64 + c * 16;
         uint32_t rr[16];
         if (ne > 0) {
-          tmem_ld_32x32b_x16(t_addr + c * 16, rr);
+          tmem_ld_32x32b_x16(t_addr + col, rr);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) rr[i] = 0;
         }
-        if (row_ok) {
+        const int n = n0 + col;
+        if (m < p.M && n < p.N) {
+          float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = c * 16 + i;
-            if (m < p.M) {
-              const float v = __uint_as_float(rr[i]) * g;
-              if (p.splits > 1) p.workspace[((size_t)split * p.M + m) * p.N + n] = v;
-              else p.out[(size_t)m * p.ldo + n] = __float2bfloat16(v + bias_v);
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(rr[i]) * g;
+          if (p.splits > 1) {
+            float* o = p.workspace + ((size_t)split * p.M + m) * p.N + n;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              if (n + i < p.N) *reinterpret_cast<float4*>(o + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          } else {
+            bf16* o = p.out + (size_t)m * p.ldo + n;
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              if (n + i < p.N) {
+                if (p.bias) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[i + j] += __bfloat162float(p.bias[n + i + j]);
+                }
+                uint4 w;
+                w.x = pack_bf16x2(v[i + 0], v[i + 1]);
+                w.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                w.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                w.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(o + i) = w;
+              }
             }
           }
         }
@@ -272,7 +280,7 @@ __global__ void __launch_bounds__(kWThreads, 1)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 __global__ void w4s_splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, bf16* out,
@@ -328,33 +336,24 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
   W4SParams p{};
   p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
   p.sf = (const uint8_t*)sf; p.gscale = gscale; p.bias = (const bf16*)bias;
-  p.mp = (M + 15) & ~15;
   p.status = device_status_word();
   const int sms = b200_num_sms();
-  const int tiles_n = (N + 127) / 128;
-  const int ne_total = (K + 127) / 128;
-  // split-K: fill the SMs, keep at least 4 stages per split
+  const int tiles_n = (N + kWN - 1) / kWN;
+  const int ne_total = (K + 63) / 64;
+  // split-K in whole 256-element raw blocks: fill the SMs, at least 8 stages per split
   int splits = 1;
-  if (tiles_n * splits < sms) {
-    int want = sms / tiles_n;
-    if (want > ne_total / 4) want = ne_total / 4 > 0 ? ne_total / 4 : 1;
-    if (want > 16) want = 16;
-    if (want > splits) splits = want;
+  if (tiles_n < sms) {
+    splits = sms / tiles_n;
+    if (splits > ne_total / 8) splits = ne_total / 8 > 0 ? ne_total / 8 : 1;
+    if (splits > 16) splits = 16;
   }
   const size_t part_room = ws_bytes - a16_bytes;
   while (splits > 1 && (size_t)splits * M * N * 4 > part_room) --splits;
   int ne_per = (ne_total + splits - 1) / splits;
-  ne_per = (ne_per + 1) & ~1;                       // whole 256-element raw blocks per split
+  ne_per = (ne_per + 3) & ~3;
   splits = (ne_total + ne_per - 1) / ne_per;
-  if (splits > 1 && (size_t)splits * M * N * 4 > part_room) return -4;
   p.splits = splits; p.ne_per_split = ne_per;
   p.workspace = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + a16_bytes);
-  // ring depths by activation tile size (mp * 256 bytes per stage), about 200 KB in all
-  if (p.mp <= 32) { p.rs = 4; p.es = 3; p.as = 6; }
-  else if (p.mp <= 64) { p.rs = 3; p.es = 3; p.as = 4; }
-  else { p.rs = 2; p.es = 2; p.as = 3; }
-  uint32_t tmem_cols = 32;
-  while ((int)tmem_cols < p.mp) tmem_cols <<= 1;
 
   __half* a16 = reinterpret_cast<__half*>(workspace);
   {
@@ -366,24 +365,26 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
   }
   CUtensorMap tmW, tmA, tmS;
   p.sf_tma = ((K & 255) == 0 && (reinterpret_cast<uintptr_t>(sf) & 15) == 0) ? 1 : 0;
-  if (!encode_tmap_2d(&tmW, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, 128,
+  if (!encode_tmap_2d(&tmW, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, kWN, 128,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  if (!encode_tmap_2d(&tmA, a16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, M, K, K, p.mp, 64,
+  if (!encode_tmap_2d(&tmA, a16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, M, K, K, 128, 64,
                       CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
   tmS = tmW;
-  if (p.sf_tma && !encode_tmap_2d(&tmS, sf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 16, K / 16, 128, 16,
+  if (p.sf_tma && !encode_tmap_2d(&tmS, sf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 16, K / 16, kWN, 16,
                                   CU_TENSOR_MAP_SWIZZLE_NONE))
     return -3;
   static bool set = false;
   if (!set) {
-    cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     set = true;
   }
-  const size_t smem = (size_t)p.rs * kRawBytes + (size_t)p.es * kExpBytes + (size_t)p.as * p.mp * 256 +
+  const size_t smem = (size_t)kMaxRS * kRawBytes + (size_t)kMaxES * kExpBytes + (size_t)kMaxAS * kActBytes +
                       (size_t)kMaxRS * kSfBytes + 1024 + sizeof(W4SBars);
-  gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, tmS, p, tmem_cols);
+  static_assert((size_t)kMaxRS * kRawBytes + (size_t)kMaxES * kExpBytes + (size_t)kMaxAS * kActBytes +
+                        (size_t)kMaxRS * kSfBytes + 1024 + sizeof(W4SBars) <= 224 * 1024, "shared memory budget");
+  gemm_w4a16_stream_kernel<<<dim3(tiles_n, splits), kWThreads, smem, stream>>>(tmW, tmA, tmS, p);
   if (cudaGetLastError() != cudaSuccess) return -2;
   if (splits > 1) {
     const size_t total = (size_t)M * N;
