@@ -1,5 +1,7 @@
 #include "lmcache.h"
 
+#include "../core/hashing.h"
+
 #include <arpa/inet.h>
 #include <netdb.h>
 #include <netinet/in.h>
@@ -176,6 +178,34 @@ uint64_t TokenHasher::fold(const std::string& d) {
   uint64_t v = 0;
   for (int i = 0; i < 8 && i < (int)d.size(); ++i) v = (v << 8) | (uint8_t)d[i];
   return v;
+}
+
+// ====================================================================== peer-agreeing chunk keys
+uint64_t vllm_none_hash(const std::string& seed) {
+  CborWriter w;
+  w.text(seed);
+  const std::string& b = w.data();
+  return TokenHasher::fold(sha256(b.data(), b.size()));
+}
+
+std::vector<ChunkEntry> vllm_chunk_hashes(const std::vector<uint32_t>& ids, int chunk_size, bool save_unfull,
+                                          const std::string& seed) {
+  std::vector<ChunkEntry> out;
+  uint64_t prefix = vllm_none_hash(seed);
+  for (size_t i = 0; i < ids.size(); i += chunk_size) {
+    const size_t end = std::min(ids.size(), i + (size_t)chunk_size);
+    if (end - i < (size_t)chunk_size && !save_unfull) break;
+    CborWriter w;
+    w.array(3);
+    w.uint(prefix);
+    w.array(end - i);
+    for (size_t j = i; j < end; ++j) w.uint(ids[j]);
+    w.array(0);
+    const std::string& b = w.data();
+    prefix = TokenHasher::fold(sha256(b.data(), b.size()));
+    out.push_back(ChunkEntry{(int)i, (int)end, prefix});
+  }
+  return out;
 }
 
 // ====================================================================== dtype / key

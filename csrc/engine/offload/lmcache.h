@@ -38,6 +38,18 @@ class TokenHasher {
   std::string none_hash_;
 };
 
+// ------------------------------------------------------------------ peer-agreeing chunk keys
+// The chunk hash a vLLM + LMCache peer keys on (LMCache's ChunkedTokenDatabase with vLLM's
+// sha256_cbor hash): prefix = fold8(sha256(cbor(str(seed)))); per chunk
+// prefix = fold8(sha256(cbor([prefix, [tokens...], []]))), fold8 = first 8 bytes big-endian.
+struct ChunkEntry {
+  int start = 0, end = 0;
+  uint64_t chunk_hash = 0;
+};
+uint64_t vllm_none_hash(const std::string& seed = "0");
+std::vector<ChunkEntry> vllm_chunk_hashes(const std::vector<uint32_t>& token_ids, int chunk_size = 256,
+                                          bool save_unfull_chunk = false, const std::string& seed = "0");
+
 // ------------------------------------------------------------------ wire enums
 enum class Command : int32_t { kPut = 1, kGet = 2, kExist = 3, kList = 4, kHealth = 5 };
 enum class ReturnCode : int32_t { kSuccess = 200, kFail = 400 };

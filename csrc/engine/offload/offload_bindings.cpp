@@ -90,6 +90,12 @@ void bind_offload(py::module_& m) {
           return out;
         })
         .def_static("fold", [](py::bytes d) { return lm::TokenHasher::fold(std::string(d)); });
+    l.def("vllm_none_hash", &lm::vllm_none_hash, py::arg("seed") = "0");
+    l.def("vllm_chunk_hashes", [](const std::vector<uint32_t>& t, int chunk, bool keep_tail, const std::string& seed) {
+      py::list out;
+      for (auto& e : lm::vllm_chunk_hashes(t, chunk, keep_tail, seed)) out.append(py::make_tuple(e.start, e.end, e.chunk_hash));
+      return out;
+    }, py::arg("token_ids"), py::arg("chunk_size") = 256, py::arg("save_unfull_chunk") = false, py::arg("seed") = "0");
     py::enum_<lm::Command>(l, "Command").value("PUT", lm::Command::kPut).value("GET", lm::Command::kGet)
         .value("EXIST", lm::Command::kExist).value("LIST", lm::Command::kList).value("HEALTH", lm::Command::kHealth);
     py::enum_<lm::ReturnCode>(l, "ReturnCode").value("SUCCESS", lm::ReturnCode::kSuccess).value("FAIL", lm::ReturnCode::kFail);

@@ -43,6 +43,21 @@ def test_token_hasher_matches_lmcache():
     assert lm.TokenHasher.fold(h.hash_tokens([0])) == 3377122253324089119
 
 
+def test_vllm_sha256_cbor_chunk_keys_agree_with_a_peer():
+    """Keys derived by a real vLLM + LMCache pair (ChunkedTokenDatabase, sha256_cbor, seed 0)."""
+    assert lm.vllm_none_hash("0") == 5625442194607170974
+    assert [(a, b, f"{h:x}") for a, b, h in lm.vllm_chunk_hashes(list(range(1, 257)))] == \
+        [(0, 256, "b44cfe1cb25a9be0")]
+    assert [f"{h:x}" for _, _, h in lm.vllm_chunk_hashes(list(range(1000, 1512)))] == \
+        ["33d6862800fff40c", "893ec9ccb64be34a"]
+    assert [(a, b, f"{h:x}") for a, b, h in lm.vllm_chunk_hashes([10, 11, 12, 13, 14, 15], 4, True)] == \
+        [(0, 4, "3b0e6619ff2ca93b"), (4, 6, "eeaac88b910fc20b")]
+    assert lm.vllm_chunk_hashes([10, 11, 12, 13, 14, 15], 4, False)[-1][:2] == (0, 4)
+    assert lm.vllm_chunk_hashes([7, 8, 9]) == []
+    h = lm.vllm_chunk_hashes(list(range(8)), 8)[0][2]
+    assert lm.CacheKey("some/model", 4, 3, h, lm.Dtype.FLOAT32).to_string() == "some/model@4@3@1edac42a0285a5f9@float"
+
+
 def test_cache_key_strings():
     k = lm.CacheKey("gpt2", 1, 0, 3735928559, lm.Dtype.BFLOAT16)
     assert k.to_string() == "gpt2@1@0@deadbeef@bfloat16"

@@ -35,12 +35,18 @@ def parse_url(url: str) -> tuple[str, int]:
 
 class LMCacheStore:
     def __init__(self, url: str, model_name: str, kv_caches: Sequence[torch.Tensor], block_size: int,
-                 chunk_size: int = 256, world_size: int = 1, worker_id: int = 0, connect: bool = True):
+                 chunk_size: int = 256, world_size: int = 1, worker_id: int = 0, connect: bool = True,
+                 hash_algo: str = "blake3"):
         """``kv_caches``: one ``[num_blocks, 2, block_size, Hkv, D]`` tensor per attention layer."""
         host, port = parse_url(url)
         self.client = lm.RemoteClient(host, port)
         if connect:
             self.client.connect()
+        # "blake3": LMCache's own rolling chunk hash; "vllm": the sha256_cbor chain a vLLM +
+        # LMCache peer keys on (ChunkedTokenDatabase), so that both sides hit each other's chunks
+        if hash_algo not in ("blake3", "vllm"):
+            raise ValueError(f"unknown LMCache hash_algo {hash_algo!r}")
+        self.hash_algo = hash_algo
         self.hasher = lm.TokenHasher(chunk_size)
         self.model_name, self.world_size, self.worker_id = model_name, world_size, worker_id
         self.kv_caches = list(kv_caches)
@@ -53,11 +59,13 @@ class LMCacheStore:
 
     # ------------------------------------------------------------------ keys
     def chunk_keys(self, token_ids: Sequence[int]) -> list[str]:
-        keys = []
-        for d in self.hasher.chunk_hashes([int(t) & 0xFFFFFFFF for t in token_ids]):
-            keys.append(lm.CacheKey(self.model_name, self.world_size, self.worker_id,
-                                    lm.TokenHasher.fold(d), self.dtype).to_string())
-        return keys
+        toks = [int(t) & 0xFFFFFFFF for t in token_ids]
+        if self.hash_algo == "vllm":
+            hashes = [h for _, _, h in lm.vllm_chunk_hashes(toks, self.chunk_size)]
+        else:
+            hashes = [lm.TokenHasher.fold(d) for d in self.hasher.chunk_hashes(toks)]
+        return [lm.CacheKey(self.model_name, self.world_size, self.worker_id, h, self.dtype).to_string()
+                for h in hashes]
 
     # ------------------------------------------------------------------ paged cache <-> planes
     def _slots(self, block_ids: Sequence[int], start: int, end: int) -> torch.Tensor:
