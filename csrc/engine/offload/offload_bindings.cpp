@@ -10,6 +10,39 @@ namespace py = pybind11;
 using namespace b200;
 using namespace b200::offload;
 
+// Lets a KV connector be written in Python: the request is handed over as plain data (id, all
+// token ids) so that nothing on the Python side aliases scheduler state.
+class PyKVConnector : public KVConnectorHook {
+ public:
+  std::optional<std::pair<int, bool>> get_num_new_matched_tokens(const Request& req, int num_computed) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const KVConnectorHook*>(this), "get_num_new_matched_tokens");
+    if (!f) return std::make_pair(0, false);
+    py::object r = f(req.request_id, req.all_token_ids, num_computed);
+    if (r.is_none()) return std::nullopt;
+    auto t = r.cast<std::pair<int, bool>>();
+    return t;
+  }
+  void update_state_after_alloc(const Request& req, const std::vector<std::vector<int32_t>>& block_ids,
+                                int num_external_tokens) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const KVConnectorHook*>(this), "update_state_after_alloc");
+    if (f) f(req.request_id, req.all_token_ids, block_ids, num_external_tokens);
+  }
+  std::shared_ptr<void> build_connector_meta(const SchedulerOutput&) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const KVConnectorHook*>(this), "build_connector_meta");
+    if (f) f();
+    return nullptr;
+  }
+  bool request_finished(const Request& req, const std::vector<std::vector<int32_t>>& block_ids) override {
+    py::gil_scoped_acquire gil;
+    py::function f = py::get_override(static_cast<const KVConnectorHook*>(this), "request_finished");
+    if (!f) return false;
+    return f(req.request_id, req.all_token_ids, block_ids, req.num_computed_tokens).cast<bool>();
+  }
+};
+
 void bind_offload(py::module_& m) {
   py::class_<CachePolicy>(m, "CachePolicy")
       .def_static("make", &CachePolicy::make)
@@ -185,7 +218,7 @@ void bind_offload(py::module_& m) {
         .def("health", &lm::RemoteClient::health, py::call_guard<py::gil_scoped_release>());
   }
 
-  py::class_<KVConnectorHook>(m, "KVConnectorHook");
+  py::class_<KVConnectorHook, PyKVConnector>(m, "KVConnectorHook").def(py::init<>());
   py::class_<OffloadConnector, KVConnectorHook>(m, "OffloadConnector")
       .def(py::init<std::shared_ptr<TieringManager>, int>(), py::arg("tiers"), py::arg("block_size"))
       .def("take_meta", &OffloadConnector::take_meta)

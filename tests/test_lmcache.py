@@ -118,7 +118,7 @@ class MockServer(threading.Thread):
         super().__init__(daemon=True)
         self.sock = socket.socket()
         self.sock.bind(("127.0.0.1", 0))
-        self.sock.listen(1)
+        self.sock.listen(8)
         self.port = self.sock.getsockname()[1]
         self.store = {}
 
@@ -133,7 +133,11 @@ class MockServer(threading.Thread):
         return b
 
     def run(self):
-        c, _ = self.sock.accept()
+        while True:
+            c, _ = self.sock.accept()
+            threading.Thread(target=self._serve, args=(c,), daemon=True).start()
+
+    def _serve(self, c):
         while True:
             hdr = self._recv(c, 186)
             if hdr is None:
@@ -190,3 +194,33 @@ def test_client_against_mock_server_and_store_roundtrip():
             b2 = blocks2[t // bs]
             assert torch.equal(c1[b1, :, o], c2[b2, :, o])
     store.client.close()
+
+
+def test_engine_reuses_kv_from_lmcache_server():
+    """Engine A serves a prompt and stores its KV chunks; engine B (fresh process state, same
+    weights) finds them at admission, loads them into its own blocks and produces the same
+    tokens while computing only the tail of the prompt."""
+    from vllm_cpp_b200.config import EngineArgs, synthetic_config
+    from vllm_cpp_b200.engine import LLM, SamplingParams
+    srv = MockServer()
+    srv.start()
+    cfg = synthetic_config("tiny-dense")
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=g).tolist()
+    ktc = {"kv_connector": "LMCacheConnector", "url": f"lm://127.0.0.1:{srv.port}", "chunk_size": 32}
+
+    def engine(with_cache):
+        return LLM(EngineArgs(model_config=cfg, device="cpu", block_size=16, max_model_len=128, max_num_seqs=2,
+                              max_num_batched_tokens=128, num_blocks=32, seed=0,
+                              kv_transfer_config=ktc if with_cache else None))
+
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    plain = engine(False).generate([prompt], sp)[0].outputs[0].token_ids
+    a = engine(True)
+    assert a.generate([prompt], sp)[0].outputs[0].token_ids == plain
+    assert a.offload.stored_chunks == 2 and len(srv.store) == 2          # 64 of the 75 computed tokens
+    b = engine(True)
+    out = b.generate([prompt], sp)[0]
+    assert out.outputs[0].token_ids == plain
+    assert b.offload.loaded_tokens == 64 and out.num_cached_tokens == 64
+    assert b.offload.stored_chunks == 0                                  # nothing new to send

@@ -109,7 +109,18 @@ class LLM:
             eos = [e for e in {cfg.eos_token_id, tk.eos_id} if e is not None and e >= 0]
             self.structured = E.StructuredOutputManager(tb, cfg.vocab_size, eos)
         self.offload = None
-        if args.kv_transfer_config:
+        if args.kv_transfer_config and args.kv_transfer_config.get("kv_connector") == "LMCacheConnector":
+            from ..worker.lmcache import LMCacheConnector, LMCacheStore
+            ktc = args.kv_transfer_config
+            caches = self.model.kv_caches
+            caches = list(caches.values()) if isinstance(caches, dict) else list(caches)
+            store = LMCacheStore(ktc["url"], ktc.get("model_name", f"{cfg.architecture}:{cfg.hidden_size}x{cfg.num_layers}"),
+                                 caches, args.block_size, chunk_size=int(ktc.get("chunk_size", 256)),
+                                 world_size=par.tensor_parallel_size, worker_id=par.rank,
+                                 hash_algo=ktc.get("hash_algo", "blake3"))
+            self.offload = LMCacheConnector(store)
+            self.runner.offload = self.offload
+        elif args.kv_transfer_config:
             from ..worker.offload import KVOffloadWorker
             caches = self.model.kv_caches
             caches = list(caches.values()) if isinstance(caches, dict) else list(caches)

@@ -143,3 +143,59 @@ class LMCacheStore:
             self.stats["hit_chunks"] += 1
             done += C
         return done
+
+
+class LMCacheConnector(E.KVConnectorHook):
+    """Scheduler-side KV connector over an :class:`LMCacheStore` (synchronous loads).
+
+    At admission the scheduler asks how many tokens beyond its own prefix-cache hit the server
+    holds; after the blocks are allocated the load is queued and ``run_step_plan`` (called by the
+    runner before the forward pass) fills them; a finished request's complete chunks are stored.
+    Configuration: ``EngineArgs.kv_transfer_config = {"kv_connector": "LMCacheConnector",
+    "url": "lm://host:port", "chunk_size": 256, "hash_algo": "blake3" | "vllm",
+    "model_name": ...}``; the chunk size must be a multiple of the KV block size.
+
+    Reference: ``src/vllm/v1/kv_offload/lmcache/lmcache_connector.cpp``.
+    """
+
+    def __init__(self, store: LMCacheStore):
+        super().__init__()
+        if store.chunk_size % store.block_size:
+            raise ValueError("LMCache chunk_size must be a multiple of the KV block size")
+        self.store = store
+        self._loads: list = []
+        self._lookups: dict[str, int] = {}
+        self.loaded_tokens = 0
+        self.stored_chunks = 0
+
+    @property
+    def connector(self):          # same attribute the offload worker exposes to the engine
+        return self
+
+    # ---- scheduler hooks (plain data in, see the C++ trampoline)
+    def get_num_new_matched_tokens(self, req_id, token_ids, num_computed):
+        # at least one token of the request must still be computed locally
+        have = self.store.lookup(token_ids[: len(token_ids) - 1])
+        self._lookups[req_id] = have
+        return (max(0, have - num_computed), False)
+
+    def update_state_after_alloc(self, req_id, token_ids, block_ids, num_external_tokens):
+        have = self._lookups.pop(req_id, 0)
+        if num_external_tokens > 0 and have > 0:
+            self._loads.append((list(token_ids), list(block_ids[0]), have))
+
+    def build_connector_meta(self):
+        return None
+
+    def request_finished(self, req_id, token_ids, block_ids, num_computed_tokens):
+        # KV exists for the computed tokens only (the last sampled token has none yet)
+        n = min(int(num_computed_tokens), len(token_ids))
+        if n >= self.store.chunk_size:
+            self.stored_chunks += self.store.store(list(token_ids[:n]), list(block_ids[0]))
+        return False
+
+    # ---- worker hook
+    def run_step_plan(self) -> None:
+        loads, self._loads = self._loads, []
+        for token_ids, blocks, n in loads:
+            self.loaded_tokens += self.store.load(token_ids, blocks, n)
