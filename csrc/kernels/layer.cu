@@ -1,0 +1,154 @@
+// One call per decoder layer: the launch sequence of a pre-norm dense transformer block
+// (RMSNorm+residual -> QKV GEMM -> qk-norm/RoPE/KV-cache write -> paged attention (decode rows
+// first, then prefill tiles) -> o GEMM -> RMSNorm+residual -> gated MLP) issued from native code.
+// The model classes otherwise sequence these launches from Python, ~10 calls per layer; for
+// batches where the GPU step is short (data-parallel replicas, tensor-parallel shards, small
+// models) that host time is what bounds the step. This entry covers the plain configuration
+// (no biases, no sandwich / post norms, no tensor parallelism); everything else keeps the
+// per-op path.
+//
+// Reference: Qwen3DenseModel::ForwardDevice, src/vllm/model_executor/models/qwen3.cpp:135-244
+// (the reference's forward is native code throughout).
+#include "api.h"
+#include "sm100.cuh"
+
+extern "C" {
+
+int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* out, int ldo, int T,
+                 int H, float eps, int gemma, cudaStream_t stream);
+int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_stride, int Hq,
+                 int Hkv, int D, int rot, const void* positions, const void* cos_sin,
+                 const void* q_norm_w, const void* k_norm_w, float eps, int gemma, int neox,
+                 const void* slot_mapping, void* kv_cache, int block_size, void* q_out, int T,
+                 cudaStream_t stream);
+int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, void* lse, const void* kv_cache,
+                      int64_t num_blocks, int block_size, int Hq, int Hkv, int D, const void* block_table,
+                      int max_blocks, const void* seq_lens, const void* q_start, const void* tile_req,
+                      const void* tile_q0, int num_tiles, int total_q, float scale, float softcap,
+                      int window, int causal, cudaStream_t stream);
+int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo, const void* kv_cache,
+                        int64_t num_blocks, int block_size, int Hq, int Hkv, int D,
+                        const void* block_table, int max_blocks, const void* seq_lens, int B,
+                        float scale, float softcap, int window, int splits, void* tmp_o, void* tmp_lse,
+                        cudaStream_t stream);
+int b200_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kv_cache, int block_size,
+                     int Hq, int Hkv, int D, const void* block_table, int max_blocks,
+                     const void* seq_lens, int B, float scale, float softcap, int window, int splits,
+                     void* tmp_o, void* tmp_lse, cudaStream_t stream);
+int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind, cudaStream_t stream);
+int b200_gemm_bf16_gated(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
+                         int N, int K, int kind, int force_path, cudaStream_t stream);
+
+// Weights of one layer (device pointers; q_norm / k_norm may be null).
+typedef struct B200DenseLayerWeights {
+  const void* ln1;
+  const void* qkv;        // [(Hq + 2 Hkv) D, H]
+  const void* q_norm;
+  const void* k_norm;
+  const void* o;          // [H, Hq D]
+  const void* ln2;
+  const void* gate_up;    // [2 I, H], interleaved in blocks of 128 if gate_up_interleaved
+  const void* down;       // [H, I]
+  void* kv_cache;         // [num_blocks, 2, block_size, Hkv, D]
+} B200DenseLayerWeights;
+
+// Shapes, step metadata (device pointers into the packed step buffer) and activation buffers.
+typedef struct B200DenseStep {
+  int T, H, Hq, Hkv, D, rot, inter, block_size;
+  int neox, gemma, act_kind, gate_up_interleaved;
+  float eps, scale, softcap;
+  int window;
+  long long num_blocks;
+  const void* positions;
+  const void* cos_sin;
+  const void* slot_mapping;
+  const void* block_table;
+  int max_blocks;
+  const void* seq_lens;
+  int num_decodes, decode_splits, decode_tc;
+  void* decode_tmp_o;
+  void* decode_tmp_lse;
+  int num_prefills, num_tiles, num_prefill_tokens;
+  const void* prefill_q_start;
+  const void* tile_req;
+  const void* tile_q0;
+  void* hidden;           // [T, H] in: previous block's output (or the embeddings); out: this block's
+  void* resid;            // [T, H] residual stream
+  void* normed;           // [T, H]
+  void* qkv_buf;          // [T, (Hq + 2 Hkv) D]
+  void* attn;             // [T, Hq D]
+  void* gate_up_buf;      // [T, 2 I]
+  void* act;              // [T, I]
+  void* gemm_ws;
+  unsigned long long gemm_ws_bytes;
+  int first_layer;        // the residual stream starts here: resid = hidden, no add
+} B200DenseStep;
+
+#define B200_TRY(call)          \
+  do {                          \
+    int rc_ = (call);           \
+    if (rc_ != 0) return rc_ < 0 ? rc_ : -rc_; \
+    ++launches;                 \
+  } while (0)
+
+// Returns the number of launcher calls made (>= 1 kernel each), or a negative error code.
+int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream) {
+  if (!w || !s || s->T <= 0) return 0;
+  int launches = 0;
+  const int T = s->T, H = s->H, D = s->D, Hq = s->Hq, Hkv = s->Hkv;
+  const int qkv_w = (Hq + 2 * Hkv) * D;
+  using bf16 = __nv_bfloat16;
+  // ---- attention block
+  if (s->first_layer) {
+    if (cudaMemcpyAsync(s->resid, s->hidden, (size_t)T * H * sizeof(bf16), cudaMemcpyDeviceToDevice, stream) !=
+        cudaSuccess)
+      return -2;
+    B200_TRY(b200_rmsnorm(s->hidden, H, nullptr, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
+  } else {
+    B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
+  }
+  B200_TRY(b200_gemm_bf16(s->normed, H, w->qkv, H, s->qkv_buf, qkv_w, 0, nullptr, nullptr, 0, T, qkv_w, H,
+                          s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+  B200_TRY(b200_rope_kv(s->qkv_buf, qkv_w, 0, Hq * D, (Hq + Hkv) * D, D, Hq, Hkv, D, s->rot, s->positions,
+                        s->cos_sin, w->q_norm, w->k_norm, s->eps, s->gemma, s->neox, s->slot_mapping,
+                        w->kv_cache, s->block_size, nullptr, T, stream));
+  const int nd = s->num_decodes;
+  if (nd > 0) {
+    if (s->decode_tc)
+      B200_TRY(b200_attn_decode_tc(s->qkv_buf, qkv_w, s->attn, Hq * D, w->kv_cache, s->num_blocks, s->block_size,
+                                   Hq, Hkv, D, s->block_table, s->max_blocks, s->seq_lens, nd, s->scale,
+                                   s->softcap, s->window, s->decode_splits, s->decode_tmp_o, s->decode_tmp_lse,
+                                   stream));
+    else
+      B200_TRY(b200_attn_decode(s->qkv_buf, qkv_w, s->attn, Hq * D, w->kv_cache, s->block_size, Hq, Hkv, D,
+                                s->block_table, s->max_blocks, s->seq_lens, nd, s->scale, s->softcap, s->window,
+                                s->decode_splits, s->decode_tmp_o, s->decode_tmp_lse, stream));
+  }
+  if (s->num_prefills > 0) {
+    const bf16* q = reinterpret_cast<const bf16*>(s->qkv_buf) + (size_t)nd * qkv_w;
+    bf16* o = reinterpret_cast<bf16*>(s->attn) + (size_t)nd * Hq * D;
+    const int32_t* bt = reinterpret_cast<const int32_t*>(s->block_table) + (size_t)nd * s->max_blocks;
+    const int32_t* sl = reinterpret_cast<const int32_t*>(s->seq_lens) + nd;
+    B200_TRY(b200_attn_prefill(q, qkv_w, o, Hq * D, nullptr, w->kv_cache, s->num_blocks, s->block_size, Hq, Hkv, D,
+                               bt, s->max_blocks, sl, s->prefill_q_start, s->tile_req, s->tile_q0, s->num_tiles,
+                               s->num_prefill_tokens, s->scale, s->softcap, s->window, 1, stream));
+  }
+  B200_TRY(b200_gemm_bf16(s->attn, Hq * D, w->o, Hq * D, s->hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D,
+                          s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+  // ---- MLP block
+  B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln2, s->normed, H, T, H, s->eps, s->gemma, stream));
+  const int I = s->inter;
+  if (s->gate_up_interleaved && T > 128) {
+    B200_TRY(b200_gemm_bf16_gated(s->normed, H, w->gate_up, H, s->act, I, T, 2 * I, H, s->act_kind, 0, stream));
+  } else {
+    B200_TRY(b200_gemm_bf16(s->normed, H, w->gate_up, H, s->gate_up_buf, 2 * I, 0, nullptr, nullptr, 0, T, 2 * I,
+                            H, s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+    B200_TRY(b200_act_and_mul(s->gate_up_buf, 2 * I, s->act, T, I,
+                              s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), stream));
+  }
+  B200_TRY(b200_gemm_bf16(s->act, I, w->down, I, s->hidden, H, 0, nullptr, nullptr, 0, T, H, I, s->gemm_ws,
+                          (size_t)s->gemm_ws_bytes, 0, stream));
+  return launches;
+}
+
+}  // extern "C"

@@ -6,6 +6,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from vllm_cpp_b200 import ops  # noqa: E402
+from vllm_cpp_b200.ops import _lib  # noqa: E402
 from vllm_cpp_b200.config import EngineArgs, synthetic_config  # noqa: E402
 from vllm_cpp_b200.engine import LLM, SamplingParams  # noqa: E402
 
@@ -124,3 +125,34 @@ def test_opt_model_gpu_vs_cpu():
     assert [a[0] for a in gpu] == [a[0] for a in cpu]
     hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(gpu, cpu))
     assert hit / sum(len(a) for a in gpu) > 0.7
+
+
+def test_native_layer_entry_same_logits_as_per_op_path():
+    """The native per-layer entry issues the same kernels with the same arguments as the
+    Python-sequenced path: logits of every step (prefill chunks, mixed, decode) are bit-equal."""
+    cfg = _cfg()
+    llm = LLM(EngineArgs(model_config=cfg, device="cuda", block_size=16, num_blocks=200, max_model_len=640,
+                         max_num_seqs=4, max_num_batched_tokens=160, enable_cuda_graphs=False))
+    m = llm.runner.model
+    assert m._native_layers_ok()
+    orig = type(m).forward
+    seen = []
+
+    def both(self, ctx):
+        self.native_layers = False
+        a = orig(self, ctx).clone()
+        self.native_layers = True
+        n0 = _lib.LAUNCHES[0]
+        b = orig(self, ctx)
+        seen.append((ctx.num_decodes, ctx.num_prefills, _lib.LAUNCHES[0] - n0, torch.equal(a, b)))
+        return b
+
+    type(m).forward = both
+    try:
+        llm.generate(_prompts(cfg, (200, 9, 70, 150)), SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    finally:
+        type(m).forward = orig
+    assert any(nd and npf for nd, npf, _, _ in seen) and any(nd and not npf for nd, npf, _, _ in seen)
+    assert all(eq for *_, eq in seen), seen
+    assert all(n >= 8 * cfg.num_layers for _, _, n, _ in seen)       # the launches are counted
+    assert ops.read_status() == 0

@@ -53,6 +53,7 @@ class DenseModel:
             softmax_scale(c.rope, c.head_dim)
         self.bufs = BufferPool(self.device)
         self.gate_up_il = False      # set by load_weights when it stores gate / up interleaved
+        self.native_layers = None    # decided at the first forward; False forces the per-op path
         self.w: dict[str, torch.Tensor] = {}
         self.layers: list[dict[str, torch.Tensor]] = []
 
@@ -194,6 +195,7 @@ class DenseModel:
         if method != "nvfp4":
             raise ValueError(f"unsupported weight quantisation {method!r}")
         from .backend import QuantWeight
+        self.native_layers = None
         for L in self.layers:
             for k in self.QUANT_KEYS:
                 w = L.get(k)
@@ -324,6 +326,77 @@ class DenseModel:
             logits = c.final_logit_softcap * torch.tanh(logits / c.final_logit_softcap)
         return logits
 
+    # ------------------------------------------------------------------ native layer entry
+    def _native_layers_ok(self) -> bool:
+        """The plain pre-norm configuration on one GPU: its blocks run through the native
+        per-layer entry (one call per layer instead of ~10 launches sequenced from Python)."""
+        c = self.cfg
+        if self.device.type != "cuda" or self.tp > 1 or type(self).forward is not DenseModel.forward:
+            return False
+        if (c.post_norm or c.sandwich_norm or c.attention_bias or c.mlp_bias or c.sliding_window
+                or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):
+            return False
+        from .backend import QuantWeight
+        return not any(isinstance(v, QuantWeight) for L in self.layers for v in L.values())
+
+    def _native_weights(self):
+        ws = getattr(self, "_native_w", None)
+        if ws is None or len(ws) != len(self.layers) or ws[0].kv_cache != self.kv_caches[0].data_ptr() \
+                or ws[0].qkv != self.layers[0]["qkv"].data_ptr():
+            from ..ops.layer import DenseLayerWeights
+            ws = []
+            for l, L in enumerate(self.layers):
+                w = DenseLayerWeights()
+                w.ln1, w.qkv, w.o, w.ln2 = L["ln1"].data_ptr(), L["qkv"].data_ptr(), L["o"].data_ptr(), L["ln2"].data_ptr()
+                w.q_norm = L["q_norm"].data_ptr() if L.get("q_norm") is not None else None
+                w.k_norm = L["k_norm"].data_ptr() if L.get("k_norm") is not None else None
+                w.gate_up, w.down = L["gate_up"].data_ptr(), L["down"].data_ptr()
+                w.kv_cache = self.kv_caches[l].data_ptr()
+                ws.append(w)
+            self._native_w = ws
+        return ws
+
+    def _run_native_layers(self, ctx, T, hidden, resid, normed, qkv, attn, gate_up, act, act_kind) -> bool:
+        from .. import ops
+        from ..ops.layer import DenseStep, dense_layer
+        c = self.cfg
+        grp = self.layer_group[0]
+        G = self.hq // self.hkv
+        nd = ctx.num_decodes
+        splits, tmp = ctx.decode_splits, ctx.extra.get("decode_tmp")
+        use_tc = ops._decode_uses_tc(self.D, G, self.block_size)
+        bt = ctx.block_table[grp]
+        if nd > 0 and splits <= 0:
+            splits = ops.attn_decode_splits(nd, self.hkv, G, self.D, bt.shape[1] * self.block_size,
+                                            self.block_size if use_tc else 0)
+        if nd > 0 and splits > 1 and tmp is None:
+            return False                      # the per-op path allocates the split buffers
+        s = DenseStep()
+        s.T, s.H, s.Hq, s.Hkv, s.D, s.rot, s.inter, s.block_size = (T, c.hidden_size, self.hq, self.hkv, self.D,
+                                                                  self.rot, self.inter, self.block_size)
+        s.neox, s.gemma, s.act_kind, s.gate_up_interleaved = int(c.rope.neox), int(c.gemma_norm), act_kind, \
+            int(self.gate_up_il)
+        s.eps, s.scale, s.softcap, s.window = c.rms_norm_eps, self.scale, c.attn_logit_softcap or 0.0, 0
+        s.num_blocks = self.kv_caches[0].shape[0]
+        s.positions, s.cos_sin = ctx.positions.data_ptr(), self.rope_table.data_ptr()
+        s.slot_mapping = ctx.slot_mapping[grp].data_ptr()
+        s.block_table, s.max_blocks, s.seq_lens = bt.data_ptr(), bt.stride(0), ctx.seq_lens.data_ptr()
+        s.num_decodes, s.decode_splits, s.decode_tc = nd, max(1, splits), int(use_tc)
+        if tmp is not None:
+            s.decode_tmp_o, s.decode_tmp_lse = tmp[0].data_ptr(), tmp[1].data_ptr()
+        s.num_prefills, s.num_tiles, s.num_prefill_tokens = ctx.num_prefills, ctx.num_tiles, T - nd
+        if ctx.num_prefills > 0:
+            s.prefill_q_start, s.tile_req, s.tile_q0 = (ctx.prefill_q_start.data_ptr(), ctx.tile_req.data_ptr(),
+                                                        ctx.tile_q0.data_ptr())
+        s.hidden, s.resid, s.normed = hidden.data_ptr(), resid.data_ptr(), normed.data_ptr()
+        s.qkv_buf, s.attn, s.gate_up_buf, s.act = qkv.data_ptr(), attn.data_ptr(), gate_up.data_ptr(), act.data_ptr()
+        ws = ops.workspace(self.device, ops.GEMM_WS_BYTES)
+        s.gemm_ws, s.gemm_ws_bytes = ws.data_ptr(), ws.numel()
+        for l, w in enumerate(self._native_weights()):
+            s.first_layer = int(l == 0)
+            dense_layer(w, s)
+        return True
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Returns fp32 logits ``[num_logits, vocab]`` for the rows in ``ctx.logits_indices``."""
         if getattr(self, "tpf", None) is not None:
@@ -349,7 +422,13 @@ class DenseModel:
             self.comm.all_reduce(hidden)
         pos = ctx.positions[:T]
         first = True
-        for l, L in enumerate(self.layers):
+        layers = self.layers
+        if self.native_layers is None:
+            self.native_layers = self._native_layers_ok()
+        if self.native_layers and T > 0 and not nvtx.ENABLED and \
+                self._run_native_layers(ctx, T, hidden, resid, normed, qkv, attn, gate_up, act, act_kind):
+            layers = []                        # every block already ran
+        for l, L in enumerate(layers):
             if nvtx.ENABLED:          # one flat marker per layer (ranges would need a pop at every exit)
                 torch.cuda.nvtx.mark(f"layer {l}")
             grp = self.layer_group[l]

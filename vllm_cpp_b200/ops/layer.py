@@ -1,0 +1,43 @@
+"""ctypes view of the native per-layer launch entry (``csrc/kernels/layer.cu``): one call issues
+every kernel of a pre-norm dense decoder block, instead of ~10 Python-level launches."""
+from __future__ import annotations
+
+import ctypes as C
+
+from ._lib import LAUNCHES, KernelError, lib, stream_ptr
+
+P, I, F = C.c_void_p, C.c_int, C.c_float
+
+
+class DenseLayerWeights(C.Structure):
+    _fields_ = [("ln1", P), ("qkv", P), ("q_norm", P), ("k_norm", P), ("o", P), ("ln2", P), ("gate_up", P),
+                ("down", P), ("kv_cache", P)]
+
+
+class DenseStep(C.Structure):
+    _fields_ = [("T", I), ("H", I), ("Hq", I), ("Hkv", I), ("D", I), ("rot", I), ("inter", I), ("block_size", I),
+                ("neox", I), ("gemma", I), ("act_kind", I), ("gate_up_interleaved", I),
+                ("eps", F), ("scale", F), ("softcap", F), ("window", I), ("num_blocks", C.c_longlong),
+                ("positions", P), ("cos_sin", P), ("slot_mapping", P), ("block_table", P), ("max_blocks", I),
+                ("seq_lens", P), ("num_decodes", I), ("decode_splits", I), ("decode_tc", I),
+                ("decode_tmp_o", P), ("decode_tmp_lse", P),
+                ("num_prefills", I), ("num_tiles", I), ("num_prefill_tokens", I),
+                ("prefill_q_start", P), ("tile_req", P), ("tile_q0", P),
+                ("hidden", P), ("resid", P), ("normed", P), ("qkv_buf", P), ("attn", P), ("gate_up_buf", P),
+                ("act", P), ("gemm_ws", P), ("gemm_ws_bytes", C.c_ulonglong), ("first_layer", I)]
+
+
+_declared = False
+
+
+def dense_layer(weights: DenseLayerWeights, step: DenseStep) -> None:
+    global _declared
+    L = lib()
+    if not _declared:
+        L.b200_dense_layer.argtypes = [C.POINTER(DenseLayerWeights), C.POINTER(DenseStep), P]
+        L.b200_dense_layer.restype = I
+        _declared = True
+    rc = L.b200_dense_layer(C.byref(weights), C.byref(step), stream_ptr())
+    if rc < 0:
+        raise KernelError(f"dense_layer: kernel launcher returned {rc}")
+    LAUNCHES[0] += rc
