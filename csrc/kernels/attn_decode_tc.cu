@@ -76,12 +76,33 @@ __device__ __forceinline__ bool softmax_group_sync(uint64_t* bar, uint32_t& phas
   phase ^= 1;
   return __all_sync(0xffffffffu, ok);
 }
+// Warp-wide float max in one instruction (sm_100a).
+__device__ __forceinline__ float warp_max_f32(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
+#ifdef B200_DECODE_TIMING
+// Instrumented build only: cycles that each role of CTA (0,0,0) spends in its waits.
+__device__ long long g_decode_timing[32];
+#define DT_DECL long long dt_t0 = 0; const bool dt_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0
+#define DT_BEGIN() do { if (dt_on) dt_t0 = clock64(); } while (0)
+#define DT_END(slot) do { if (dt_on) g_decode_timing[slot] += clock64() - dt_t0; } while (0)
+#else
+#define DT_DECL
+#define DT_BEGIN() do {} while (0)
+#define DT_END(slot) do {} while (0)
+#endif
+
+// GP: the GQA group size rounded up to 4 / 8 / 16; the softmax only touches those columns of
+// S^T (the MMA's N stays 16, its minimum at 128 rows).
+template <int GP>
 __global__ void __launch_bounds__(192, 2)
     attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                           const __grid_constant__ CUtensorMap tmKV, DecodeTcParams p) {
@@ -153,6 +174,10 @@ __global__ void __launch_bounds__(192, 2)
         const int rows_per_load = min(p.block_size, kTok);
         const int loads = kTok / rows_per_load;
         bool ok = true;
+        DT_DECL;
+#ifdef B200_DECODE_TIMING
+        const long long dt_tot0 = clock64();
+#endif
         for (int j = 0; j < ntiles && ok; ++j) {
           const int tok0 = tok_base + j * kTok;
           int blk[16];
@@ -164,7 +189,9 @@ __global__ void __launch_bounds__(192, 2)
             const int it = 2 * j + kv;
             const int sl = it % kSlots;
             const uint32_t ph = (it / kSlots) & 1;
+            DT_BEGIN();
             if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
+            DT_END(1);
             uint8_t* dst = sKV + sl * kSlotBytes;
             mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
             for (int l = 0; l < loads; ++l) {
@@ -176,21 +203,34 @@ __global__ void __launch_bounds__(192, 2)
             }
           }
         }
+#ifdef B200_DECODE_TIMING
+        if (dt_on) g_decode_timing[0] += clock64() - dt_tot0;
+#endif
       }
     } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_qk = umma_idesc_bf16(kTok, kNQ, 0, 0);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(D, kNQ, 1, 0);  // A (V^T) is MN-major
+        DT_DECL;
+#ifdef B200_DECODE_TIMING
+        const long long dt_tot0 = clock64();
+#endif
+        DT_BEGIN();
         bool ok = mbar_wait(&bars->q_full, 0, p.status);
+        DT_END(3);
         const uint32_t q_addr = smem_u32(sQ);
         for (int j = 0; j <= ntiles && ok; ++j) {
           if (j < ntiles) {
             const int it = 2 * j, sl = it % kSlots;
             const uint32_t ph = (it / kSlots) & 1;
             const int sb = j & 1;
+            DT_BEGIN();
             if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
+            DT_END(4);
+            DT_BEGIN();
             if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+            DT_END(5);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -208,8 +248,12 @@ __global__ void __launch_bounds__(192, 2)
             const int it = 2 * i + 1, sl = it % kSlots;
             const uint32_t ph = (it / kSlots) & 1;
             const int pb = i & 1;
+            DT_BEGIN();
             if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
+            DT_END(6);
+            DT_BEGIN();
             if (!mbar_wait(&bars->p_full[pb], (i >> 1) & 1, p.status)) { ok = false; break; }
+            DT_END(7);
             tc_fence_after_sync();
             const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
             const uint32_t p_addr = smem_u32(sP + pb * 4096);
@@ -224,21 +268,33 @@ __global__ void __launch_bounds__(192, 2)
             umma_commit(&bars->pv_done);
           }
         }
+#ifdef B200_DECODE_TIMING
+        if (dt_on) g_decode_timing[2] += clock64() - dt_tot0;
+#endif
       }
     } else {
       // ---------------- softmax / correction: thread t owns token t of the tile ----------------
       const int quarter = warp & 3;
       const int t = quarter * 32 + lane;
       const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-      float m[kNQ], lsum[kNQ];
+      float m[GP], lsum[GP];
 #pragma unroll
-      for (int g = 0; g < kNQ; ++g) { m[g] = -INFINITY; lsum[g] = 0.f; }
+      for (int g = 0; g < GP; ++g) { m[g] = -INFINITY; lsum[g] = 0.f; }
+      const bool capped = p.softcap2 > 0.f;
       bool ok = true;
       uint32_t gphase = 0;
+#ifdef B200_DECODE_TIMING
+      long long dt_t0 = 0;
+      const bool dt_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && warp == 2 && lane == 0;
+      const long long dt_tot0 = clock64();
+#endif
       for (int j = 0; j < ntiles && ok; ++j) {
         const int sb = j & 1;
+        DT_BEGIN();
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (j >> 1) & 1, p.status));
+        DT_END(9);
         if (!ok) break;
+        DT_BEGIN();
         tc_fence_after_sync();
         uint32_t r[16];
         tmem_ld_32x32b_x16(tmem_s + sb * 16 + lane_off, r);
@@ -246,29 +302,37 @@ __global__ void __launch_bounds__(192, 2)
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
+        DT_END(13);
+        DT_BEGIN();
         const int tok = tok_base + j * kTok + t;
         const bool valid = tok < seq_len && tok >= begin;
-        float s[kNQ];
+        float s[GP];
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
+        for (int g = 0; g < GP; ++g) {
           float v = __uint_as_float(r[g]) * p.scale_log2;
-          if (p.softcap2 > 0.f) v = p.softcap2 * tanhf(v / p.softcap2);
+          if (capped) v = p.softcap2 * tanhf(v / p.softcap2);
           s[g] = valid ? v : -INFINITY;
         }
-        // tile max per head over the 128 tokens
+        // tile max per head over the 128 tokens: one warp reduction per head, then 4 partials
+        {
+          float wm[GP];
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
-          float v = s[g];
+          for (int g = 0; g < GP; ++g) wm[g] = warp_max_f32(s[g]);
+          if (lane == 0) {
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-          if (lane == 0) bars->red_max[sb][quarter][g] = v;
+            for (int g = 0; g < GP; ++g) bars->red_max[sb][quarter][g] = wm[g];
+          }
         }
+        DT_END(14);
+        DT_BEGIN();
         ok = softmax_group_sync(&bars->grp, gphase, lane, p.status);
+        DT_END(10);
         if (!ok) break;
+        DT_BEGIN();
         bool rescale = false;
-        float alpha[kNQ];
+        float alpha[GP];
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
+        for (int g = 0; g < GP; ++g) {
           const float tm = fmaxf(fmaxf(bars->red_max[sb][0][g], bars->red_max[sb][1][g]),
                                  fmaxf(bars->red_max[sb][2][g], bars->red_max[sb][3][g]));
           alpha[g] = 1.f;
@@ -280,14 +344,17 @@ __global__ void __launch_bounds__(192, 2)
             m[g] = tm;
           }
         }
-        // P^T buffer free? (PV of tile j-2 finished reading it; this also pins the phase of
-        // pv_done so that the wait below cannot alias an older phase)
+        // P^T buffer free? (PV of tile j-2 finished reading it.) This also bounds how far
+        // pv_done can lag: it has completed at least j-1 times here, so the parity wait of the
+        // rescale below (its j-th completion) cannot be satisfied by an older phase.
         const int pb = j & 1;
+        DT_END(16);
+        DT_BEGIN();
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty[pb], ((j >> 1) & 1) ^ 1, p.status));
+        DT_END(11);
         if (!ok) break;
-        bool pv_waited = false;
+        DT_BEGIN();
         if (rescale && j > 0) {
-          pv_waited = true;
           // all PV products issued so far must have landed before O^T is rescaled in place
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
           if (!ok) break;
@@ -296,16 +363,16 @@ __global__ void __launch_bounds__(192, 2)
           tmem_ld_32x32b_x16(tmem_o + lane_off, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < kNQ; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
+          for (int g = 0; g < GP; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
           tmem_st_32x32b_x16(tmem_o + lane_off, o);
           tmem_st_wait();
 #pragma unroll
-          for (int g = 0; g < kNQ; ++g) lsum[g] *= alpha[g];
+          for (int g = 0; g < GP; ++g) lsum[g] *= alpha[g];
         }
         uint8_t* pbuf = sP + pb * 4096 + (t >> 6) * 2048;
         const int c = t & 63;
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
+        for (int g = 0; g < GP; ++g) {
           if (g < G) {
             const float pv = valid ? fast_exp2(s[g] - m[g]) : 0.f;
             const __nv_bfloat16 pb16 = __float2bfloat16(pv);
@@ -314,24 +381,26 @@ __global__ void __launch_bounds__(192, 2)
                                               (c & 7) * 2) = pb16;
           }
         }
-        // Observe every completion of pv_done in order (one per tile): a parity wait that
-        // skipped phases could be satisfied by an older one. PV(j) cannot start before
-        // PV(j-1) has finished anyway, so this costs nothing.
-        if (j > 0 && !pv_waited) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
-          if (!ok) break;
-        }
+        DT_END(15);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[pb]);
       }
+#ifdef B200_DECODE_TIMING
+      if (dt_on) g_decode_timing[8] += clock64() - dt_tot0;
+#endif
       // ---------------- epilogue: O^T / l ----------------
+      // pv_done completes once per tile and the loop only guarantees ntiles-2 completions seen
+      // (through p_empty), so observe the last two in order: a parity wait two phases ahead
+      // would be satisfied by the older phase.
+      if (ok && ntiles >= 2)
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (ntiles - 2) & 1, p.status));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (ntiles - 1) & 1, p.status));
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
+        for (int g = 0; g < GP; ++g) {
           float v = lsum[g];
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -345,7 +414,7 @@ __global__ void __launch_bounds__(192, 2)
         tmem_ld_wait();
         const int d = t;  // TMEM lane of O^T = head dim index
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
+        for (int g = 0; g < GP; ++g) {
           if (g < G) {
             const float l = bars->red_sum[0][g] + bars->red_sum[1][g] + bars->red_sum[2][g] +
                             bars->red_sum[3][g];
@@ -396,6 +465,17 @@ struct DKeyHash {
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_DECODE_TIMING
+extern "C" int b200_decode_timing_read(long long* host32, int reset) {
+  if (cudaMemcpyFromSymbol(host32, g_decode_timing, sizeof(long long) * 32) != cudaSuccess) return -1;
+  if (reset) {
+    long long z[32] = {0};
+    if (cudaMemcpyToSymbol(g_decode_timing, z, sizeof(z)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+#endif
 
 // The merge kernel of the CUDA-core path (attn_decode.cu) combines the split partials.
 extern "C" int b200_attn_decode_merge(const void* tmp_o, const void* tmp_lse, void* out, int ldo,
@@ -458,12 +538,16 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
   constexpr size_t smem = (size_t)kSlots * kSlotBytes + 4096 + 8192 + 1024 + sizeof(DecodeTcBars);
   static bool set = false;
   if (!set) {
-    cudaFuncSetAttribute(attn_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     set = true;
   }
   dim3 grid(B, Hkv, splits);
-  attn_decode_tc_kernel<<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  const int G = Hq / Hkv;
+  if (G <= 4) attn_decode_tc_kernel<4><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  else if (G <= 8) attn_decode_tc_kernel<8><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
+  else attn_decode_tc_kernel<16><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
   if (cudaGetLastError() != cudaSuccess) return -2;
   if (splits > 1)
     return b200_attn_decode_merge(tmp_o, tmp_lse, out, ldo, B, Hq, D, splits, stream);

@@ -12,6 +12,8 @@ Reference forward: ``src/vllm/model_executor/models/qwen3.cpp:135-244``,
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config import ModelConfig, ParallelConfig
@@ -332,6 +334,8 @@ class DenseModel:
         per-layer entry (one call per layer instead of ~10 launches sequenced from Python)."""
         c = self.cfg
         if self.device.type != "cuda" or self.tp > 1 or type(self).forward is not DenseModel.forward:
+            return False
+        if os.environ.get("B200_NATIVE_LAYERS", "1") == "0":      # debugging: keep the per-op path
             return False
         if (c.post_norm or c.sandwich_norm or c.attention_bias or c.mlp_bias or c.sliding_window
                 or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):

@@ -275,8 +275,10 @@ def _decode_uses_tc(head_dim: int, group: int, block_size: int) -> bool:
 def attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len,
                        block_size: int = 16) -> int:
     if _decode_uses_tc(head_dim, group, block_size):
+        # two CTAs fit on an SM: split only while every split still gets a slot in the first
+        # wave (a second, ragged wave plus the merge kernel costs more than it gains)
         ctas = max(1, batch * num_kv_heads)
-        want = -(-2 * num_sms() // ctas)
+        want = (2 * num_sms()) // ctas
         tiles = max(1, -(-max_seq_len // 128))
         return max(1, min(want, max(1, tiles // 2), 32))
     return lib().b200_attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len)

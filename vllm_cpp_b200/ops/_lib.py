@@ -13,7 +13,8 @@ from pathlib import Path
 import torch  # noqa: F401  (loads libcudart before the kernel library resolves against it)
 
 _PKG = Path(__file__).resolve().parent.parent
-_LIB_PATH = _PKG / "_kernels.so"
+# B200_KERNELS_SO: load another build of the library (e.g. one compiled with instrumentation)
+_LIB_PATH = Path(os.environ["B200_KERNELS_SO"]) if os.environ.get("B200_KERNELS_SO") else _PKG / "_kernels.so"
 _lib = None
 
 
