@@ -12,7 +12,8 @@
 //
 // O^T stays in TMEM across tiles (16 fp32 columns); the running max is raised lazily (only
 // when a tile exceeds it by more than 2^8), and raising it rescales those 16 columns in
-// place. K and V tiles share one TMA ring of 32 KB slots, two CTAs fit on an SM.
+// place. K and V tiles share one TMA ring of 32 KB slots, filled in the order the MMA warp
+// consumes them (K0 K1 V0 K2 V1 ...); two CTAs fit on an SM.
 //
 // Replaces the CUDA-core decode kernels of the reference
 // (src/vt/cuda/cuda_paged_attn.cu:302 PagedAttentionDecodeOptKernel, :430 ...GqaKernel) and
@@ -178,29 +179,32 @@ __global__ void __launch_bounds__(192, 2)
 #ifdef B200_DECODE_TIMING
         const long long dt_tot0 = clock64();
 #endif
-        for (int j = 0; j < ntiles && ok; ++j) {
+        // Load order K0 K1 V0 K2 V1 K3 ... V(n-1): exactly the order in which the MMA warp
+        // consumes the tiles, with K running one tile further ahead than V (a V slot is held
+        // until the softmax of its tile is done; K slots turn over as soon as QK has run).
+        const int nseq = 2 * ntiles;
+        for (int sq = 0; sq < nseq && ok; ++sq) {
+          int kv, j;
+          if (sq == 0) { kv = 0; j = 0; }
+          else if (sq == nseq - 1) { kv = 1; j = ntiles - 1; }
+          else if (sq & 1) { kv = 0; j = (sq + 1) >> 1; }
+          else { kv = 1; j = (sq - 2) >> 1; }
           const int tok0 = tok_base + j * kTok;
-          int blk[16];
+          const int sl = sq % kSlots;
+          const uint32_t ph = (sq / kSlots) & 1;
+          DT_BEGIN();
+          if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
+          DT_END(1);
+          uint8_t* dst = sKV + sl * kSlotBytes;
+          mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
           for (int l = 0; l < loads; ++l) {
-            const int bi = (tok0 + l * rows_per_load) / p.block_size;
-            blk[l] = (bi < nblk_valid) ? bt[bi] : bt[0];
-          }
-          for (int kv = 0; kv < 2 && ok; ++kv) {
-            const int it = 2 * j + kv;
-            const int sl = it % kSlots;
-            const uint32_t ph = (it / kSlots) & 1;
-            DT_BEGIN();
-            if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
-            DT_END(1);
-            uint8_t* dst = sKV + sl * kSlotBytes;
-            mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
-            for (int l = 0; l < loads; ++l) {
-              const int off = (tok0 + l * rows_per_load) % p.block_size;
-              const int row = (blk[l] * 2 + kv) * p.block_size + off;
-              tma_load_3d(dst + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 0, hkv, row);
-              tma_load_3d(dst + 16384 + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 64,
-                          hkv, row);
-            }
+            const int tk = tok0 + l * rows_per_load;
+            const int bi = tk / p.block_size;
+            const int blk = (bi < nblk_valid) ? bt[bi] : bt[0];
+            const int row = (blk * 2 + kv) * p.block_size + tk % p.block_size;
+            tma_load_3d(dst + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 0, hkv, row);
+            tma_load_3d(dst + 16384 + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 64, hkv,
+                        row);
           }
         }
 #ifdef B200_DECODE_TIMING
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(192, 2)
         const uint32_t q_addr = smem_u32(sQ);
         for (int j = 0; j <= ntiles && ok; ++j) {
           if (j < ntiles) {
-            const int it = 2 * j, sl = it % kSlots;
+            const int it = j == 0 ? 0 : 2 * j - 1, sl = it % kSlots;     // K(j) in load order
             const uint32_t ph = (it / kSlots) & 1;
             const int sb = j & 1;
             DT_BEGIN();
@@ -245,7 +249,7 @@ __global__ void __launch_bounds__(192, 2)
           }
           if (j >= 1) {
             const int i = j - 1;
-            const int it = 2 * i + 1, sl = it % kSlots;
+            const int it = i == ntiles - 1 ? 2 * ntiles - 1 : 2 * i + 2, sl = it % kSlots;  // V(i)
             const uint32_t ph = (it / kSlots) & 1;
             const int pb = i & 1;
             DT_BEGIN();
