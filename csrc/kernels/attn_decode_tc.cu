@@ -77,12 +77,6 @@ __device__ __forceinline__ bool softmax_group_sync(uint64_t* bar, uint32_t& phas
   phase ^= 1;
   return __all_sync(0xffffffffu, ok);
 }
-// Warp-wide float max in one instruction (sm_100a).
-__device__ __forceinline__ float warp_max_f32(float v) {
-  float r;
-  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
-  return r;
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

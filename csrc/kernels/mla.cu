@@ -255,12 +255,14 @@ __global__ void __launch_bounds__(192, 1)
         float s[kNQ];
 #pragma unroll
         for (int g = 0; g < kNQ; ++g) s[g] = valid ? __uint_as_float(r[g]) * p.scale_log2 : -INFINITY;
+        {
+          float wm[kNQ];
 #pragma unroll
-        for (int g = 0; g < kNQ; ++g) {
-          float v = s[g];
+          for (int g = 0; g < kNQ; ++g) wm[g] = warp_max_f32(s[g]);
+          if (lane == 0) {
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-          if (lane == 0) bars->red_max[sb][quarter][g] = v;
+            for (int g = 0; g < kNQ; ++g) bars->red_max[sb][quarter][g] = wm[g];
+          }
         }
         ok = mla_group_sync(&bars->grp, gphase, lane, p.status);
         if (!ok) break;
@@ -282,9 +284,9 @@ __global__ void __launch_bounds__(192, 1)
         const int pb = j & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty[pb], ((j >> 1) & 1) ^ 1, p.status));
         if (!ok) break;
-        bool pv_waited = false;
+        // p_empty above means PV(j-2) is complete, so pv_done has completed at least j-1 times
+        // and this parity wait (its j-th completion) cannot be satisfied by an older phase
         if (rescale && j > 0) {
-          pv_waited = true;
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
           if (!ok) break;
           tc_fence_after_sync();
@@ -312,18 +314,14 @@ __global__ void __launch_bounds__(192, 1)
             *reinterpret_cast<bf16*>(pbuf + g * 128 + (((c >> 3) ^ (g & 7)) << 4) + (c & 7) * 2) = pb16;
           }
         }
-        // Observe every completion of pv_done in order (one per tile): a parity wait that
-        // skipped phases could be satisfied by an older one. PV(j) cannot start before
-        // PV(j-1) has finished anyway, so this costs nothing.
-        if (j > 0 && !pv_waited) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
-          if (!ok) break;
-        }
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[pb]);
       }
+      // observe the last two completions in order (the loop only guarantees ntiles-2 seen)
+      if (ok && ntiles >= 2)
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (ntiles - 2) & 1, p.status));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (ntiles - 1) & 1, p.status));
       if (ok) {
         tc_fence_after_sync();

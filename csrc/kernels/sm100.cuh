@@ -430,6 +430,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_nvfp4(int m, int n, int sfa_id
 // ------------------------------------------------------------------------------------
 // Small numeric helpers
 // ------------------------------------------------------------------------------------
+// Warp-wide float max in one instruction (sm_100a).
+__device__ __forceinline__ float warp_max_f32(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
