@@ -113,16 +113,6 @@ __global__ void __launch_bounds__(192, 2)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x, hkv = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
-  const int seq_len = p.seq_lens[b];
-  int begin = 0;
-  if (p.window > 0) begin = max(0, seq_len - p.window);
-  const int start = (begin / kTok) * kTok;           // tile-aligned start of the kv range
-  const int span = max(0, seq_len - start);
-  const int tiles_total = (span + kTok - 1) / kTok;
-  const int tiles_per_split = (tiles_total + p.splits - 1) / p.splits;
-  const int tile0 = split * tiles_per_split;
-  const int ntiles = max(0, min(tiles_total, tile0 + tiles_per_split) - tile0);
-  const int tok_base = start + tile0 * kTok;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -154,6 +144,20 @@ __global__ void __launch_bounds__(192, 2)
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t tmem_s = tmem_base;        // 2 x 16 columns
   const uint32_t tmem_o = tmem_base + 32;   // 16 columns
+
+  // Everything above touches only shared memory and TMEM and may overlap the previous kernel.
+  pdl_wait();
+  pdl_launch_dependents();
+  const int seq_len = p.seq_lens[b];
+  int begin = 0;
+  if (p.window > 0) begin = max(0, seq_len - p.window);
+  const int start = (begin / kTok) * kTok;           // tile-aligned start of the kv range
+  const int span = max(0, seq_len - start);
+  const int tiles_total = (span + kTok - 1) / kTok;
+  const int tiles_per_split = (tiles_total + p.splits - 1) / p.splits;
+  const int tile0 = split * tiles_per_split;
+  const int ntiles = max(0, min(tiles_total, tile0 + tiles_per_split) - tile0);
+  const int tok_base = start + tile0 * kTok;
 
   if (ntiles > 0) {
     if (warp == 0) {
@@ -543,10 +547,11 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
   }
   dim3 grid(B, Hkv, splits);
   const int G = Hq / Hkv;
-  if (G <= 4) attn_decode_tc_kernel<4><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  else if (G <= 8) attn_decode_tc_kernel<8><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  else attn_decode_tc_kernel<16><<<grid, 192, smem, stream>>>(tmQ, tmKV, p);
-  if (cudaGetLastError() != cudaSuccess) return -2;
+  cudaError_t le;
+  if (G <= 4) le = launch_pdl(attn_decode_tc_kernel<4>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  else if (G <= 8) le = launch_pdl(attn_decode_tc_kernel<8>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  else le = launch_pdl(attn_decode_tc_kernel<16>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  if (le != cudaSuccess) return -2;
   if (splits > 1)
     return b200_attn_decode_merge(tmp_o, tmp_lse, out, ldo, B, Hq, D, splits, stream);
   return 0;

@@ -1,6 +1,7 @@
 // Host-side helpers shared by all kernel launchers: tensor-map encoding through the
 // driver entry point, a per-device status word that kernels write when a bounded wait
 // runs out, and device-property queries.
+#include <cstdlib>
 #include <cudaTypedefs.h>
 
 #include <mutex>
@@ -56,6 +57,14 @@ bool encode_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtyp
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 int* device_status_word() {

@@ -215,6 +215,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -817,6 +819,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -936,6 +940,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, i
                                      void* out, int ldo, int out_f32,
                                      const __nv_bfloat16* __restrict__ bias,
                                      const __nv_bfloat16* __restrict__ residual, int ldr) {
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
   const int n4 = N >> 2;
   const size_t total = (size_t)M * n4;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
@@ -1099,8 +1105,14 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
     }
     p.sk = sk_tiles;
   }
-  gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmA2, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  // Tensor-parallel launches stay ordinary: their CTAs wait on other ranks, and nothing should
+  // become resident beside them early.
+  if (p.tp_world > 1 || p.ag_flags) {
+    gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmA2, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
+  return launch_pdl(gemm_bf16_tn_kernel<BN>, dim3(grid), dim3(kGemmThreads), smem, stream, tmA, tmA2, tmB, p) ==
+                 cudaSuccess ? 0 : -2;
 }
 
 // CTA-pair launch: clusters of two, as many as can be resident at once (at most one per SM pair).
@@ -1347,15 +1359,25 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     }
     size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
     dim3 grid(p.tiles_n, splits);
-    gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, tmA2, p, tmem_cols);
-    if (cudaGetLastError() != cudaSuccess) return -2;
+    if (tp) {
+      gemm_bf16_swap_kernel<<<grid, kGemmThreads, smem, stream>>>(tmW, tmA, tmA2, p, tmem_cols);
+      if (cudaGetLastError() != cudaSuccess) return -2;
+    } else if (launch_pdl(gemm_bf16_swap_kernel, grid, dim3(kGemmThreads), smem, stream, tmW, tmA, tmA2, p,
+                          tmem_cols) != cudaSuccess) {
+      return -2;
+    }
     if (splits > 1 && !(tp && tp->scatter)) {
       size_t total = (size_t)M * (N / 4);
       int blocks = (int)((total + 255) / 256);
       if (blocks > sms * 8) blocks = sms * 8;
-      splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, out, ldo,
-                                                       out_f32, p.bias, p.residual, ldr);
-      if (cudaGetLastError() != cudaSuccess) return -2;
+      if (tp) {
+        splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.workspace, splits, M, N, out, ldo,
+                                                         out_f32, p.bias, p.residual, ldr);
+        if (cudaGetLastError() != cudaSuccess) return -2;
+      } else if (launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, stream, (const float*)p.workspace,
+                            splits, M, N, out, ldo, out_f32, p.bias, p.residual, ldr) != cudaSuccess) {
+        return -2;
+      }
     }
     return 0;
   }

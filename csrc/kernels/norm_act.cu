@@ -37,6 +37,8 @@ __global__ void __launch_bounds__(256)
                    float eps, int gemma) {
   __shared__ float red[32];
   extern __shared__ uint4 row_cache[];  // H/8 vectors
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
   const int t = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * ldx);
   uint4* rr = residual ? reinterpret_cast<uint4*>(residual + (size_t)t * H) : nullptr;
@@ -117,6 +119,8 @@ __device__ __forceinline__ float act_fn(float g, int kind) {
 __global__ void __launch_bounds__(256)
     act_and_mul_kernel(const __nv_bfloat16* __restrict__ x, int ldx, __nv_bfloat16* out, int I,
                        int T, int kind_flags) {
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
   const int kind = kind_flags & 0xff;
   const bool il = (kind_flags & 0x100) != 0;
   const int nv = I >> 3;
@@ -250,10 +254,8 @@ int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* ou
   if ((H & 7) || (ldx & 7) || (ldo & 7) || H > 32768) return -1;
   int threads = H / 8 >= 256 ? 256 : ((H / 8 + 31) / 32) * 32;
   if (threads < 32) threads = 32;
-  rmsnorm_kernel<<<T, threads, (size_t)H * 2, stream>>>((const bf16*)x, ldx, (bf16*)residual,
-                                                        (const bf16*)w, (bf16*)out, ldo, H, eps,
-                                                        gemma);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), (size_t)H * 2, stream, (const bf16*)x, ldx,
+                    (bf16*)residual, (const bf16*)w, (bf16*)out, ldo, H, eps, gemma) == cudaSuccess ? 0 : -2;
 }
 
 int b200_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,
@@ -269,9 +271,8 @@ int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind,
   if (T <= 0) return 0;
   if ((I & 7) || (ldx & 7)) return -1;
   if ((kind & 0x100) && (I & 127)) return -1;      // interleaved layout needs whole blocks
-  act_and_mul_kernel<<<ew_grid((size_t)T * (I / 8)), 256, 0, stream>>>((const bf16*)x, ldx,
-                                                                      (bf16*)out, I, T, kind);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_pdl(act_and_mul_kernel, dim3(ew_grid((size_t)T * (I / 8))), dim3(256), 0, stream, (const bf16*)x,
+                    ldx, (bf16*)out, I, T, kind) == cudaSuccess ? 0 : -2;
 }
 
 int b200_eltwise(const void* a, const void* b, void* out, size_t n, int kind, float scalar,

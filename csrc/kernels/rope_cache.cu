@@ -37,6 +37,8 @@ struct RopeKvParams {
 // One warp per (token, head). Heads 0..Hq-1 are q, Hq..Hq+Hkv-1 are k, then Hkv v heads.
 __global__ void __launch_bounds__(128) rope_kv_kernel(RopeKvParams p, int T) {
   __shared__ float buf[4][256];
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nheads = p.Hq + 2 * p.Hkv;
   const long long gw = (long long)blockIdx.x * 4 + warp;
@@ -191,8 +193,7 @@ int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_
   p.block_size = block_size; p.q_out = (bf16*)q_out;
   long long warps = (long long)T * (Hq + 2 * Hkv);
   int blocks = (int)((warps + 3) / 4);
-  rope_kv_kernel<<<blocks, 128, 0, stream>>>(p, T);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_pdl(rope_kv_kernel, dim3(blocks), dim3(128), 0, stream, p, T) == cudaSuccess ? 0 : -2;
 }
 
 int b200_reshape_and_cache(const void* k, int ldk, const void* v, int ldv, const void* slots,

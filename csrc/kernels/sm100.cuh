@@ -464,4 +464,38 @@ bool encode_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtyp
                     uint32_t b2, CUtensorMapSwizzle swizzle);
 // Process-wide device status word (lazily allocated per device).
 int* device_status_word();
+
+// ------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched through launch_pdl() may become resident
+// while its predecessor in the stream is still running: everything it does before pdl_wait()
+// (barrier init, TMEM allocation, descriptor prefetch) overlaps the predecessor's tail, and
+// pdl_wait() returns only when the predecessor grid has completed and its writes are visible.
+// Rule for kernels launched this way: no global read of produced data and no global write before
+// pdl_wait(). pdl_launch_dependents() only affects when the successor may become resident; both
+// instructions are no-ops in a kernel launched the ordinary way.
+// B200_PDL=0 in the environment makes launch_pdl() an ordinary launch.
+// ------------------------------------------------------------------------------------
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(static_cast<Args&&>(args))...);
+}
+#endif
 }  // namespace b200
