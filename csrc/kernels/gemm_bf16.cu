@@ -59,6 +59,9 @@ struct GemmParams {
   // gather prologue (all-gather + GEMM): A is this rank's copy of the gathered activations,
   // filled by peer stores; the producer waits until every row of a 32-row group has landed.
   const uint32_t* ag_flags;
+  // The weight operand is not written by earlier work in the stream: its first ring stages may be
+  // fetched before the wait on the predecessor kernel (programmatic dependent launch).
+  int w_early;
   int ag_flag_parity_stride;
   const uint32_t* op_counter;     // device-side op counter; its low bit selects the parity
   // ---- stream-K (tn kernel only) ---------------------------------------------------------
@@ -215,6 +218,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // Weights that nothing in the stream writes: fetch the weight halves of the first ring stages of
+  // this CTA's first segment before waiting on the predecessor kernel.
+  int npre = 0;
+  if (warp == 0 && lane == 0 && p.w_early && !p.ag_flags) {
+    SegState seg0 = seg_init_w(p, kblocks, blockIdx.x, gridDim.x);
+    int t0, ka, kz;
+    if (seg_next(seg0, num_tiles, kblocks, t0, ka, kz)) {
+      int tm0, tn0;
+      tile_coords(t0, p.tiles_m, p.tiles_n, tm0, tn0);
+      tma_prefetch_desc(&tmB);
+      npre = min(kz - ka, stages);
+      for (int i = 0; i < npre; ++i) {
+        mbar_expect_tx(&bars->full[i], kStageBytes);
+        tma_load_2d(smem + (size_t)i * kStageBytes + kABytes, &tmB, &bars->full[i], (ka + i) * kBK, tn0 * BN);
+      }
+    }
+  }
   pdl_wait();                 // predecessor grid complete, its writes visible
   pdl_launch_dependents();    // the successor may become resident (it waits the same way)
 
@@ -248,9 +268,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { ok = false; break; }
           uint8_t* a_dst = smem + (size_t)s * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
-          mbar_expect_tx(&bars->full[s], kStageBytes);
+          if ((int)it >= npre) {  // (the first npre stages already expect their bytes and hold B)
+            mbar_expect_tx(&bars->full[s], kStageBytes);
+            tma_load_2d(b_dst, &tmB, &bars->full[s], kb * kBK, tn * BN);
+          }
           tma_load_2d(a_dst, ta, &bars->full[s], kb * kBK, tm * kBM);
-          tma_load_2d(b_dst, &tmB, &bars->full[s], kb * kBK, tn * BN);
         }
       }
       if (!ok) bars->failed = 1;
@@ -819,6 +841,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  // Weights that nothing in the stream writes: fill the first ring stages' weight halves while
+  // the predecessor kernel is still running; the activation halves follow after the wait.
+  int npre = 0;
+  if (warp == 0 && lane == 0 && p.w_early && !p.ag_flags) {
+    tma_prefetch_desc(&tmW);
+    npre = min(nkb, stages);
+    for (int i = 0; i < npre; ++i) {
+      mbar_expect_tx(&bars->full[i], stage_bytes);
+      tma_load_2d(smem + (size_t)i * stage_bytes, &tmW, &bars->full[i], (kb0 + i) * kBK, bz * p.N + tn * kBM);
+    }
+  }
   pdl_wait();                 // predecessor grid complete, its writes visible
   pdl_launch_dependents();    // the successor may become resident (it waits the same way)
 
@@ -841,8 +874,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { bars->failed = 1; break; }
         uint8_t* w_dst = smem + (size_t)s * stage_bytes;
         uint8_t* a_dst = w_dst + kWBytes;
-        mbar_expect_tx(&bars->full[s], stage_bytes);
-        tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, bz * p.N + tn * kBM);
+        if (i >= npre) {         // (the first npre stages already expect their bytes and hold W)
+          mbar_expect_tx(&bars->full[s], stage_bytes);
+          tma_load_2d(w_dst, &tmW, &bars->full[s], (kb0 + i) * kBK, bz * p.N + tn * kBM);
+        }
         tma_load_2d(a_dst, ta, &bars->full[s], bz * p.batch_a_cols + (kb0 + i) * kBK, 0);
       }
     }
@@ -1264,6 +1299,9 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
                           int N, int K, void* workspace, size_t ws_bytes, int force_path,
                           const B200TpGemm* tp, cudaStream_t stream, int act_fuse) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // bit 8 of force_path: W is a constant weight (nothing in the stream writes it)
+  const int w_early = (force_path >> 8) & 1;
+  force_path &= 0xff;
   if (act_fuse && (tp || M <= 128 || (N & 255) || bias || residual || out_f32)) return -1;
   if (act_fuse && force_path == 0) force_path = 9;      // the gated epilogue lives in the pair kernel
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
@@ -1272,6 +1310,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     return -1;
   if (tp && tp->scatter && !out) out = const_cast<void*>(A);  // unused by the scatter epilogue
   GemmParams p{};
+  p.w_early = (w_early && !tp) ? 1 : 0;
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_f32 = out_f32;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);

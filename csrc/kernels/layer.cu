@@ -84,6 +84,10 @@ typedef struct B200DenseStep {
   int first_layer;        // the residual stream starts here: resid = hidden, no add
 } B200DenseStep;
 
+// force_path bit 8: the weight operand is constant, its first tiles may be fetched before the
+// predecessor kernel has finished
+static constexpr int kConstW = 0x100;
+
 #define B200_TRY(call)          \
   do {                          \
     int rc_ = (call);           \
@@ -108,7 +112,7 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
     B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
   }
   B200_TRY(b200_gemm_bf16(s->normed, H, w->qkv, H, s->qkv_buf, qkv_w, 0, nullptr, nullptr, 0, T, qkv_w, H,
-                          s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+                          s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
   B200_TRY(b200_rope_kv(s->qkv_buf, qkv_w, 0, Hq * D, (Hq + Hkv) * D, D, Hq, Hkv, D, s->rot, s->positions,
                         s->cos_sin, w->q_norm, w->k_norm, s->eps, s->gemma, s->neox, s->slot_mapping,
                         w->kv_cache, s->block_size, nullptr, T, stream));
@@ -134,7 +138,7 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
                                s->num_prefill_tokens, s->scale, s->softcap, s->window, 1, stream));
   }
   B200_TRY(b200_gemm_bf16(s->attn, Hq * D, w->o, Hq * D, s->hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D,
-                          s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+                          s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
   // ---- MLP block
   B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln2, s->normed, H, T, H, s->eps, s->gemma, stream));
   const int I = s->inter;
@@ -142,12 +146,12 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
     B200_TRY(b200_gemm_bf16_gated(s->normed, H, w->gate_up, H, s->act, I, T, 2 * I, H, s->act_kind, 0, stream));
   } else {
     B200_TRY(b200_gemm_bf16(s->normed, H, w->gate_up, H, s->gate_up_buf, 2 * I, 0, nullptr, nullptr, 0, T, 2 * I,
-                            H, s->gemm_ws, (size_t)s->gemm_ws_bytes, 0, stream));
+                            H, s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
     B200_TRY(b200_act_and_mul(s->gate_up_buf, 2 * I, s->act, T, I,
                               s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), stream));
   }
   B200_TRY(b200_gemm_bf16(s->act, I, w->down, I, s->hidden, H, 0, nullptr, nullptr, 0, T, H, I, s->gemm_ws,
-                          (size_t)s->gemm_ws_bytes, 0, stream));
+                          (size_t)s->gemm_ws_bytes, kConstW, stream));
   return launches;
 }
 

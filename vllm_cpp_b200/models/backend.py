@@ -192,6 +192,8 @@ class GpuBackend:
         ops.lib()  # fail loudly here if the kernel library is missing
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
+        """``w`` is always a model weight here (never written by a kernel of the step), which
+        lets the GEMM start fetching it before the previous kernel has finished."""
         if isinstance(w, QuantWeight):
             from ..ops import quant as Q
             N, K = w.shape
@@ -207,7 +209,7 @@ class GpuBackend:
             if residual is not None:
                 y = self.ops.add(y, residual) if out is None else out.copy_(self.ops.add(y, residual))
             return y
-        return self.ops.gemm(a, w, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
+        return self.ops.gemm(a, w, bias=bias, residual=residual, out=out, out_dtype=out_dtype, const_w=True)
 
     def rmsnorm(self, x, w, eps, residual=None, out=None, gemma=False):
         return self.ops.rmsnorm(x, w, eps, residual=residual, out=out, gemma=gemma)

@@ -33,8 +33,11 @@ GEMM_WS_BYTES = 64 << 20
 
 def gemm(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
-         out_dtype: torch.dtype = torch.bfloat16, force_path: int = 0) -> torch.Tensor:
-    """``out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ residual)``; bf16 inputs, fp32 accumulate."""
+         out_dtype: torch.dtype = torch.bfloat16, force_path: int = 0,
+         const_w: bool = False) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ residual)``; bf16 inputs, fp32 accumulate.
+    ``const_w``: ``w`` is a model weight that no kernel in the stream writes, so the GEMM may
+    fetch its first tiles while the previous kernel is still running."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
     assert a.stride(1) == 1 and w.stride(1) == 1
@@ -48,7 +51,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
         ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0),
         1 if out.dtype == torch.float32 else 0, ptr(bias), ptr(residual),
         residual.stride(0) if residual is not None else 0, M, N, K, ptr(ws), ws.numel(),
-        force_path, stream_ptr())
+        force_path | (0x100 if const_w else 0), stream_ptr())
     check(rc, f"gemm M={M} N={N} K={K}")
     return out
 
@@ -120,7 +123,7 @@ def gemm_gated(a: torch.Tensor, w_il: torch.Tensor, kind: int = ACT_SILU, *,
         return out
     if scratch is None:
         scratch = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-    gemm(a, w_il, out=scratch)
+    gemm(a, w_il, out=scratch, const_w=True)      # w_il is a model weight by construction
     return act_and_mul(scratch, kind, out, interleaved=True)
 
 
