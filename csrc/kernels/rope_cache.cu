@@ -32,6 +32,7 @@ struct RopeKvParams {
   __nv_bfloat16* kv_cache;
   int block_size;
   __nv_bfloat16* q_out;  // optional separate q destination [T, Hq*D]; null => in place
+  int vec4;              // D == rot == 128, neox, 8-byte aligned rows: the vectorised path applies
 };
 
 // One warp per (token, head). Heads 0..Hq-1 are q, Hq..Hq+Hkv-1 are k, then Hkv v heads.
@@ -67,6 +68,57 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(RopeKvParams p, int T) {
   const bool is_q = h < p.Hq;
   __nv_bfloat16* src = is_q ? row + p.q_off + h * p.q_head_stride : row + p.k_off + (h - p.Hq) * D;
   const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
+
+  if (p.vec4) {
+    // Head of 128 dims, full neox rotation: lane l holds dims 4l..4l+3 (one 8-byte load), its
+    // rotation partner (dim +-64) sits in lane l ^ 16. No shared memory, one load and one store.
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
+    const float2 lo = unpack_bf16x2(raw.x), hi = unpack_bf16x2(raw.y);
+    float x[4] = {lo.x, lo.y, hi.x, hi.y};
+    if (nw) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = rsqrtf(ss / 128.f + p.eps);
+      const float g = p.gemma ? 1.f : 0.f;
+      const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
+      const float2 w0 = unpack_bf16x2(wr.x), w1 = unpack_bf16x2(wr.y);
+      const float w[4] = {w0.x, w0.y, w1.x, w1.y};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        x[k] = __bfloat162float(__float2bfloat16(x[k] * inv * (w[k] + g)));   // norm output is bf16
+    }
+    const float* cs = p.cos_sin + (size_t)p.positions[t] * 128;
+    const int j = (lane & 15) * 4;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + j);
+    const float4 s4 = *reinterpret_cast<const float4*>(cs + 64 + j);
+    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    float y[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[k], 16);
+      y[k] = lane < 16 ? x[k] * c[k] - other * sn[k] : x[k] * c[k] + other * sn[k];
+    }
+    uint2 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    if (is_q) {
+      __nv_bfloat16* dst = p.q_out ? p.q_out + ((size_t)t * p.Hq + h) * 128 : src;
+      *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+    } else {
+      if (p.slot_mapping) {
+        const int64_t slot = p.slot_mapping[t];
+        if (slot >= 0) {
+          const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+          __nv_bfloat16* dst =
+              p.kv_cache + (((blk * 2 + 0) * p.block_size + off) * p.Hkv + (h - p.Hq)) * (int64_t)128;
+          *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+        }
+      }
+      *reinterpret_cast<uint2*>(src + lane * 4) = o;   // the activation row keeps the rotated k too
+    }
+    return;
+  }
 
   float ss = 0.f;
   for (int i = lane; i < D; i += 32) {
@@ -191,6 +243,11 @@ int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_
   p.eps = eps; p.gemma = gemma; p.neox = neox;
   p.slot_mapping = (const int64_t*)slot_mapping; p.kv_cache = (bf16*)kv_cache;
   p.block_size = block_size; p.q_out = (bf16*)q_out;
+  const uintptr_t ptr_bits = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                             reinterpret_cast<uintptr_t>(kv_cache) | reinterpret_cast<uintptr_t>(q_norm_w) |
+                             reinterpret_cast<uintptr_t>(k_norm_w);
+  p.vec4 = (D == 128 && rot == 128 && neox && cos_sin && !((ld | q_off | k_off | v_off | q_head_stride) & 3) &&
+            !(ptr_bits & 7) && !(reinterpret_cast<uintptr_t>(cos_sin) & 15)) ? 1 : 0;
   long long warps = (long long)T * (Hq + 2 * Hkv);
   int blocks = (int)((warps + 3) / 4);
   return launch_pdl(rope_kv_kernel, dim3(blocks), dim3(128), 0, stream, p, T) == cudaSuccess ? 0 : -2;
