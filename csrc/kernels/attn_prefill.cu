@@ -10,7 +10,8 @@
 // while the softmax warps work on tile j; S is double-buffered in TMEM; O lives in registers
 // and is rescaled when the running max moves.
 //
-// K and V tiles share one ring of three TMA slots; pages are fetched with 3-D TMA boxes
+// K and V tiles share one ring of three TMA slots, filled in the order the MMA warp consumes them
+// (K0 K1 V0 K2 V1 ...); pages are fetched with 3-D TMA boxes
 // (64 dims x 1 head x min(block_size, 64) tokens) straight from the paged cache
 // [num_blocks, 2, block_size, Hkv, D].
 //
@@ -63,6 +64,18 @@ __device__ __forceinline__ float ex2_fast(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+#ifdef B200_PREFILL_TIMING
+// Instrumented build only: cycles that the roles of one CTA (the last tile, head 0) spend per phase.
+__device__ long long g_prefill_timing[32];
+#define PT_ON(cond) const bool pt_on = (cond); long long pt_t0 = 0
+#define PT_BEGIN() do { if (pt_on) pt_t0 = clock64(); } while (0)
+#define PT_END(slot) do { if (pt_on) g_prefill_timing[slot] += clock64() - pt_t0; } while (0)
+#else
+#define PT_ON(cond)
+#define PT_BEGIN() do {} while (0)
+#define PT_END(slot) do {} while (0)
+#endif
 
 // D = 256 keeps two softmax threads per query row (warps w and w + 4 share a TMEM lane
 // quarter): both reduce the full score row, each writes half of P and owns half of O.
@@ -143,27 +156,31 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       const int rows_per_load = min(p.block_size, kKT);
       const int loads = kKT / rows_per_load;
       bool ok = true;
-      for (int j = 0; j < ntiles && ok; ++j) {
+      // Load order K0 K1 V0 K2 V1 K3 ... V(n-1): the order in which the MMA warp consumes the
+      // tiles, with K one tile further ahead than V (V slots are held until the softmax of their
+      // tile is done; K slots turn over as soon as QK^T has run).
+      const int nseq = 2 * ntiles;
+      for (int sq = 0; sq < nseq && ok; ++sq) {
+        int kv, j;
+        if (sq == 0) { kv = 0; j = 0; }
+        else if (sq == nseq - 1) { kv = 1; j = ntiles - 1; }
+        else if (sq & 1) { kv = 0; j = (sq + 1) >> 1; }
+        else { kv = 1; j = (sq - 2) >> 1; }
         const int tok0 = (kt0 + j) * kKT;
-        int blk[8];
+        const int sl = sq % kRing;
+        const uint32_t ph = (sq / kRing) & 1;
+        if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
+        uint8_t* dst = sKV + sl * kSlotBytes;
+        mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
         for (int l = 0; l < loads; ++l) {
-          const int bi = (tok0 + l * rows_per_load) / p.block_size;
-          int b = (bi < nblk_valid) ? bt[bi] : bt[0];
-          blk[l] = b < 0 ? 0 : b;
-        }
-        for (int kv = 0; kv < 2 && ok; ++kv) {
-          const int it = 2 * j + kv, sl = it % kRing;
-          const uint32_t ph = (it / kRing) & 1;
-          if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
-          uint8_t* dst = sKV + sl * kSlotBytes;
-          mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
-          for (int l = 0; l < loads; ++l) {
-            const int off = (tok0 + l * rows_per_load) % p.block_size;
-            const int row = (blk[l] * 2 + kv) * p.block_size + off;
-            for (int dh = 0; dh < kDH; ++dh)
-              tma_load_3d(dst + dh * kKVHalf + l * rows_per_load * 128, &tmKV,
-                          &bars->kv_full[sl], dh * 64, hkv, row);
-          }
+          const int tk = tok0 + l * rows_per_load;
+          const int bi = tk / p.block_size;
+          int blk = (bi < nblk_valid) ? bt[bi] : bt[0];
+          if (blk < 0) blk = 0;
+          const int row = (blk * 2 + kv) * p.block_size + tk % p.block_size;
+          for (int dh = 0; dh < kDH; ++dh)
+            tma_load_3d(dst + dh * kKVHalf + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl],
+                        dh * 64, hkv, row);
         }
       }
     }
@@ -171,13 +188,18 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kQT, kKT, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kQT, D, 0, 1);  // B (V) is MN-major
+      PT_ON(blockIdx.x == gridDim.x - 1 && blockIdx.y == 0);
       bool ok = mbar_wait(&bars->q_full, 0, p.status);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       for (int j = 0; j <= ntiles && ok; ++j) {
         if (j < ntiles) {
-          const int it = 2 * j, sl = it % kRing, sb = j & 1;
+          const int it = j == 0 ? 0 : 2 * j - 1, sl = it % kRing, sb = j & 1;   // K(j) in load order
+          PT_BEGIN();
           if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
+          PT_END(0);
+          PT_BEGIN();
           if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+          PT_END(1);
           tc_fence_after_sync();
           const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -192,10 +214,16 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         }
         if (j >= 1) {
           const int i = j - 1;
-          const int it = 2 * i + 1, sl = it % kRing;
+          const int it = i == ntiles - 1 ? 2 * ntiles - 1 : 2 * i + 2, sl = it % kRing;       // V(i)
+          PT_BEGIN();
           if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
+          PT_END(2);
+          PT_BEGIN();
           if (!mbar_wait(&bars->p_full, i & 1, p.status)) { ok = false; break; }
+          PT_END(3);
+          PT_BEGIN();
           if (!mbar_wait(&bars->o_empty, (i & 1) ^ 1, p.status)) { ok = false; break; }
+          PT_END(4);
           tc_fence_after_sync();
           const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -228,10 +256,17 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     for (int i = 0; i < kDO; ++i) o[i] = 0.f;
     bool ok = true;
     uint8_t* prow = sP + r * 128;
+    PT_ON(blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && warp == 2 && lane == 0);
+#ifdef B200_PREFILL_TIMING
+    const long long pt_tot0 = clock64();
+#endif
     for (int j = 0; j < ntiles && ok; ++j) {
       const int sb = j & 1;
+      PT_BEGIN();
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (j >> 1) & 1, p.status));
+      PT_END(8);
       if (!ok) break;
+      PT_BEGIN();
       tc_fence_after_sync();
       const int kbase = (kt0 + j) * kKT;
       const uint32_t s_addr = tmem_s0 + sb * kKT + lane_off;
@@ -243,6 +278,8 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[sb]);   // S is in registers now
+      PT_END(9);
+      PT_BEGIN();
       // scaled scores (log2 domain), soft-cap, mask
       if (cap || need_mask) {
 #pragma unroll
@@ -274,9 +311,13 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       const float m_new = fmaxf(m, fmaxf(mx0, mx1));
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = (m_new == -INFINITY) ? 1.f : ex2_fast(m - m_new);
+      PT_END(10);
+      PT_BEGIN();
       // P buffer must be free (PV of tile j-1 finished reading it)
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty, (j & 1) ^ 1, p.status));
+      PT_END(11);
       if (!ok) break;
+      PT_BEGIN();
       float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {     // 8 chunks of 8 columns = 16 bytes each
@@ -299,10 +340,14 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
+      PT_END(12);
       // deferred accumulate of PV_{j-1}
       if (j >= 1) {
+        PT_BEGIN();
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (j - 1) & 1, p.status));
+        PT_END(13);
         if (!ok) break;
+        PT_BEGIN();
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < kDO / 32; ++c) {
@@ -316,9 +361,13 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->o_empty);
+        PT_END(14);
       }
       alpha_prev = alpha;
     }
+#ifdef B200_PREFILL_TIMING
+    if (pt_on) { g_prefill_timing[15] += clock64() - pt_tot0; g_prefill_timing[16] += ntiles; }
+#endif
     if (ok && ntiles > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (ntiles - 1) & 1, p.status));
       if (ok) {
@@ -392,6 +441,17 @@ static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_PREFILL_TIMING
+extern "C" int b200_prefill_timing_read(long long* host32, int reset) {
+  if (cudaMemcpyFromSymbol(host32, g_prefill_timing, sizeof(long long) * 32) != cudaSuccess) return -1;
+  if (reset) {
+    long long z[32] = {0};
+    if (cudaMemcpyToSymbol(g_prefill_timing, z, sizeof(z)) != cudaSuccess) return -1;
+  }
+  return 0;
+}
+#endif
 
 extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, void* lse,
                                  const void* kv_cache, int64_t num_blocks, int block_size, int Hq,
