@@ -266,8 +266,8 @@ __global__ void __launch_bounds__(192, 2)
                            umma_desc_k_sw128(p_addr + poff, 1024), idesc_pv, (i | kk) != 0);
             }
             umma_commit(&bars->kv_empty[sl]);
+            umma_commit(&bars->pv_done);      // before p_empty: whoever sees p_empty has this arrival too
             umma_commit(&bars->p_empty[pb]);
-            umma_commit(&bars->pv_done);
           }
         }
 #ifdef B200_DECODE_TIMING

@@ -7,8 +7,9 @@
 // cross-thread reductions), P written to smem as bf16 in the UMMA K-major swizzled layout,
 // then  PV = P V  with V as an MN-major operand (the pages land in smem exactly as they sit
 // in the cache, d contiguous). QK^T of tile j+1 and PV of tile j-1 run on the tensor pipe
-// while the softmax warps work on tile j; S is double-buffered in TMEM; O lives in registers
-// and is rescaled when the running max moves.
+// while the softmax warps work on tile j; S is double-buffered in TMEM; O is accumulated in
+// TMEM by the tensor pipe and rescaled in place only when a row's reference max is raised
+// (lazily, by more than 2^8).
 //
 // K and V tiles share one ring of three TMA slots, filled in the order the MMA warp consumes them
 // (K0 K1 V0 K2 V1 ...); pages are fetched with 3-D TMA boxes
@@ -55,7 +56,7 @@ struct alignas(8) PrefillBars {
   uint64_t q_full;
   uint64_t kv_full[kRing], kv_empty[kRing];
   uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, p_empty, o_full, o_empty;
+  uint64_t p_full, p_empty, o_full;
   uint32_t tmem_base;
 };
 
@@ -131,7 +132,6 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     mbar_init(&bars->p_full, 4 * kSplit);
     mbar_init(&bars->p_empty, 1);
     mbar_init(&bars->o_full, 1);
-    mbar_init(&bars->o_empty, 4 * kSplit);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -221,9 +221,6 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
           PT_BEGIN();
           if (!mbar_wait(&bars->p_full, i & 1, p.status)) { ok = false; break; }
           PT_END(3);
-          PT_BEGIN();
-          if (!mbar_wait(&bars->o_empty, (i & 1) ^ 1, p.status)) { ok = false; break; }
-          PT_END(4);
           tc_fence_after_sync();
           const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -231,11 +228,11 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
             // V: MN-major; 64-dim blocks are kKVHalf apart, 8-token groups 1024 B apart,
             // 16 tokens per instruction = 2048 B.
             umma_bf16_ss(tmem_o, umma_desc_k_sw128(p_addr + kk * 32, 1024),
-                         umma_desc_mn_sw128(v_addr + kk * 2048, kKVHalf, 1024), idesc_pv, kk != 0);
+                         umma_desc_mn_sw128(v_addr + kk * 2048, kKVHalf, 1024), idesc_pv, (i | kk) != 0);
           }
           umma_commit(&bars->kv_empty[sl]);
+          umma_commit(&bars->o_full);     // before p_empty: whoever sees p_empty has this arrival too
           umma_commit(&bars->p_empty);
-          umma_commit(&bars->o_full);
         }
       }
     }
@@ -250,10 +247,11 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     const int hi = min(p.causal ? q_pos : (seq_len - 1), seq_len - 1);
     const float sc = p.scale_log2;
     const bool cap = p.softcap2 > 0.f;
-    float m = -INFINITY, l = 0.f, alpha_prev = 1.f;   // m in the scaled log2 domain
-    float o[kDO];
-#pragma unroll
-    for (int i = 0; i < kDO; ++i) o[i] = 0.f;
+    // m: reference maximum of the row in the scaled log2 domain. It is raised lazily: only when a
+    // tile exceeds it by more than 2^8, so P stays below 256 and the rescale of O is rare. O is
+    // accumulated by the tensor pipe in TMEM across tiles; a raise rescales this thread's row of
+    // O in place (TMEM lane == query row, so no other thread is involved).
+    float m = -INFINITY, l = 0.f;
     bool ok = true;
     uint8_t* prow = sP + r * 128;
     PT_ON(blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && warp == 2 && lane == 0);
@@ -308,15 +306,38 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
         mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
       }
-      const float m_new = fmaxf(m, fmaxf(mx0, mx1));
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_new == -INFINITY) ? 1.f : ex2_fast(m - m_new);
+      const float tile_max = fmaxf(mx0, mx1);
+      float alpha = 1.f;
+      bool rescale = false;
+      if (tile_max > m + 8.f) {          // also the first finite tile: m == -inf
+        if (m != -INFINITY) {
+          alpha = ex2_fast(m - tile_max);
+          rescale = j > 0;
+        }
+        m = tile_max;
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;
       PT_END(10);
       PT_BEGIN();
-      // P buffer must be free (PV of tile j-1 finished reading it)
+      // PV of tile j-1 has completed: the P buffer is free and O holds every product so far
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty, (j & 1) ^ 1, p.status));
       PT_END(11);
       if (!ok) break;
+      PT_BEGIN();
+      if (__any_sync(0xffffffffu, rescale)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kDO / 32; ++c) {
+          uint32_t rr[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
+        }
+        tmem_st_wait();
+      }
+      PT_END(14);
       PT_BEGIN();
       float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
@@ -336,65 +357,48 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
           *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l = l * alpha + (rs0 + rs1);
-      m = m_new;
       fence_proxy_async_smem();
+      tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
       PT_END(12);
-      // deferred accumulate of PV_{j-1}
-      if (j >= 1) {
-        PT_BEGIN();
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (j - 1) & 1, p.status));
-        PT_END(13);
-        if (!ok) break;
-        PT_BEGIN();
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < kDO / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(rr[i]));
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->o_empty);
-        PT_END(14);
-      }
-      alpha_prev = alpha;
     }
 #ifdef B200_PREFILL_TIMING
     if (pt_on) { g_prefill_timing[15] += clock64() - pt_tot0; g_prefill_timing[16] += ntiles; }
 #endif
     if (ok && ntiles > 0) {
+      // o_full completes once per PV; p_empty of the last iteration showed PV(ntiles-2) complete,
+      // so this parity wait can only be satisfied by the last product
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, (ntiles - 1) & 1, p.status));
-      if (ok) {
-        tc_fence_after_sync();
+      if (ok) tc_fence_after_sync();
+    }
+    if (ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + (size_t)(q_begin + q0 + r) * p.ldo + h * D + part * kDO;
 #pragma unroll
-        for (int c = 0; c < kDO / 32; ++c) {
-          uint32_t rr[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);
+      for (int c = 0; c < kDO / 32; ++c) {
+        uint32_t rr[32];
+        if (ntiles > 0) {
+          tmem_ld_32x32b_x32(tmem_o + lane_off + part * kDO + c * 32, rr);   // (whole warp)
           tmem_ld_wait();
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_prev, __uint_as_float(rr[i]));
+          for (int i = 0; i < 32; ++i) rr[i] = 0;
+        }
+        if (r < rows) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(rr[i + 0]) * inv, __uint_as_float(rr[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(rr[i + 2]) * inv, __uint_as_float(rr[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(rr[i + 4]) * inv, __uint_as_float(rr[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(rr[i + 6]) * inv, __uint_as_float(rr[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
+          }
         }
       }
     }
     if (ok && r < rows) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = p.out + (size_t)(q_begin + q0 + r) * p.ldo + h * D + part * kDO;
-#pragma unroll
-      for (int i = 0; i < kDO; i += 8) {
-        uint4 w;
-        w.x = pack_bf16x2(o[i + 0] * inv, o[i + 1] * inv);
-        w.y = pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv);
-        w.z = pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv);
-        w.w = pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + i) = w;
-      }
       if (p.lse && part == 0) {
         const float ln2 = 0.6931471805599453f;
         p.lse[(size_t)(q_begin + q0 + r) * p.Hq + h] = l > 0.f ? (m + log2f(l)) * ln2 : -INFINITY;

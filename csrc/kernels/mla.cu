@@ -224,8 +224,8 @@ __global__ void __launch_bounds__(192, 1)
               umma_commit(&bars->kv_empty[sl]);
             }
             if (ok) {
+              umma_commit(&bars->pv_done);    // before p_empty: whoever sees p_empty has this arrival too
               umma_commit(&bars->p_empty[pb]);
-              umma_commit(&bars->pv_done);
             }
           }
         }
