@@ -69,6 +69,32 @@ def test_gemm_small_m_swap_splitk(M, N, K):
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(32, 4096, 4096), (64, 28672, 4096), (200, 1024, 1024), (1280, 4096, 4096)])
+def test_gemm_const_weight_early_fetch_in_a_chain(M, N, K):
+    """``const_w`` lets the GEMM fetch weight tiles before the previous kernel has finished; the
+    activations still have to wait for it. A chain norm -> GEMM -> norm -> GEMM, launched back to
+    back, must give the same bits as the same chain without the flag."""
+    torch.manual_seed(11)
+    x0 = _rand(M, K)
+    g = _rand(K)
+    w1 = _rand(N, K, scale=0.05)
+    w2 = _rand(K, N, scale=0.02)
+
+    def chain(flag):
+        x = x0
+        for _ in range(3):
+            h = ops.rmsnorm(x, g, 1e-6)
+            y = ops.gemm(h, w1, const_w=flag)
+            x = ops.gemm(y, w2, const_w=flag)
+        return x
+
+    a, b = chain(False), chain(True)
+    assert torch.equal(a, b)
+    h = ops.rmsnorm(x0, g, 1e-6)
+    assert _rel_err(ops.gemm(h, w1, const_w=True), ref.gemm(h, w1)) < 6e-3
+    assert ops.read_status() == 0
+
+
 def test_gemm_epilogues():
     torch.manual_seed(2)
     for M in (7, 700):
