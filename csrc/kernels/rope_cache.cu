@@ -32,7 +32,7 @@ struct RopeKvParams {
   __nv_bfloat16* kv_cache;
   int block_size;
   __nv_bfloat16* q_out;  // optional separate q destination [T, Hq*D]; null => in place
-  int vec4;              // D == rot == 128, neox, 8-byte aligned rows: the vectorised path applies
+  int vec4;              // D == rot == 128, neox, 8-byte aligned rows: rope_kv_vec4_kernel applies
 };
 
 // One warp per (token, head). Heads 0..Hq-1 are q, Hq..Hq+Hkv-1 are k, then Hkv v heads.
@@ -68,57 +68,6 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(RopeKvParams p, int T) {
   const bool is_q = h < p.Hq;
   __nv_bfloat16* src = is_q ? row + p.q_off + h * p.q_head_stride : row + p.k_off + (h - p.Hq) * D;
   const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
-
-  if (p.vec4) {
-    // Head of 128 dims, full neox rotation: lane l holds dims 4l..4l+3 (one 8-byte load), its
-    // rotation partner (dim +-64) sits in lane l ^ 16. No shared memory, one load and one store.
-    const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-    const float2 lo = unpack_bf16x2(raw.x), hi = unpack_bf16x2(raw.y);
-    float x[4] = {lo.x, lo.y, hi.x, hi.y};
-    if (nw) {
-      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float inv = rsqrtf(ss / 128.f + p.eps);
-      const float g = p.gemma ? 1.f : 0.f;
-      const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
-      const float2 w0 = unpack_bf16x2(wr.x), w1 = unpack_bf16x2(wr.y);
-      const float w[4] = {w0.x, w0.y, w1.x, w1.y};
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        x[k] = __bfloat162float(__float2bfloat16(x[k] * inv * (w[k] + g)));   // norm output is bf16
-    }
-    const float* cs = p.cos_sin + (size_t)p.positions[t] * 128;
-    const int j = (lane & 15) * 4;
-    const float4 c4 = *reinterpret_cast<const float4*>(cs + j);
-    const float4 s4 = *reinterpret_cast<const float4*>(cs + 64 + j);
-    const float c[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-    float y[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float other = __shfl_xor_sync(0xffffffffu, x[k], 16);
-      y[k] = lane < 16 ? x[k] * c[k] - other * sn[k] : x[k] * c[k] + other * sn[k];
-    }
-    uint2 o;
-    o.x = pack_bf16x2(y[0], y[1]);
-    o.y = pack_bf16x2(y[2], y[3]);
-    if (is_q) {
-      __nv_bfloat16* dst = p.q_out ? p.q_out + ((size_t)t * p.Hq + h) * 128 : src;
-      *reinterpret_cast<uint2*>(dst + lane * 4) = o;
-    } else {
-      if (p.slot_mapping) {
-        const int64_t slot = p.slot_mapping[t];
-        if (slot >= 0) {
-          const int64_t blk = slot / p.block_size, off = slot % p.block_size;
-          __nv_bfloat16* dst =
-              p.kv_cache + (((blk * 2 + 0) * p.block_size + off) * p.Hkv + (h - p.Hq)) * (int64_t)128;
-          *reinterpret_cast<uint2*>(dst + lane * 4) = o;
-        }
-      }
-      *reinterpret_cast<uint2*>(src + lane * 4) = o;   // the activation row keeps the rotated k too
-    }
-    return;
-  }
 
   float ss = 0.f;
   for (int i = lane; i < D; i += 32) {
@@ -171,6 +120,101 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(RopeKvParams p, int T) {
     // Keep the rotated k in the activation row too (prefill reads it from the cache only,
     // but the in-place row stays consistent for callers that look at it).
     if (!is_q) src[i] = o;
+  }
+}
+
+// Vectorised form for 128-dim heads with a full neox rotation (p.vec4): one warp takes kHG
+// consecutive heads of one token. Lane l holds dims 4l..4l+3 of a head (one 8-byte load), its
+// rotation partner (dim +-64) sits in lane l ^ 16; the token's cos / sin row and cache slot are
+// fetched once per warp and the kHG head loads are issued together, so the dependent global
+// round trips are paid once per eight heads instead of once per head.
+static constexpr int kHG = 8;
+__global__ void __launch_bounds__(128) rope_kv_vec4_kernel(RopeKvParams p, int T) {
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nheads = p.Hq + 2 * p.Hkv;
+  const int groups = (nheads + kHG - 1) / kHG;
+  const long long gw = (long long)blockIdx.x * 4 + warp;
+  if (gw >= (long long)T * groups) return;
+  const int t = (int)(gw / groups);
+  const int h0 = (int)(gw % groups) * kHG;
+  const int nh = min(kHG, nheads - h0);
+  __nv_bfloat16* row = p.qkv + (size_t)t * p.ld;
+  const int kv0 = p.Hq;              // first k head
+  const int v0 = p.Hq + p.Hkv;       // first v head
+
+  const __nv_bfloat16* src[kHG];
+  uint2 raw[kHG];
+#pragma unroll
+  for (int i = 0; i < kHG; ++i) {
+    const int h = h0 + i;
+    src[i] = h < kv0 ? row + p.q_off + h * p.q_head_stride
+                     : (h < v0 ? row + p.k_off + (h - kv0) * 128 : row + p.v_off + (h - v0) * 128);
+    if (i < nh) raw[i] = *reinterpret_cast<const uint2*>(src[i] + lane * 4);
+  }
+  // cache slot of the token (k and v heads) and its rotation row
+  __nv_bfloat16* kdst = nullptr;
+  __nv_bfloat16* vdst = nullptr;
+  if (p.slot_mapping && h0 + nh > kv0) {
+    const int64_t slot = p.slot_mapping[t];
+    if (slot >= 0) {
+      const int64_t blk = slot / p.block_size, off = slot % p.block_size;
+      kdst = p.kv_cache + ((blk * 2 + 0) * p.block_size + off) * (int64_t)p.Hkv * 128;
+      vdst = p.kv_cache + ((blk * 2 + 1) * p.block_size + off) * (int64_t)p.Hkv * 128;
+    }
+  }
+  float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+  if (h0 < v0) {
+    const float* cs = p.cos_sin + (size_t)p.positions[t] * 128;
+    const int j = (lane & 15) * 4;
+    const float4 c4 = *reinterpret_cast<const float4*>(cs + j);
+    const float4 s4 = *reinterpret_cast<const float4*>(cs + 64 + j);
+    c[0] = c4.x; c[1] = c4.y; c[2] = c4.z; c[3] = c4.w;
+    sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+  }
+  const float g = p.gemma ? 1.f : 0.f;
+#pragma unroll
+  for (int i = 0; i < kHG; ++i) {
+    if (i >= nh) break;
+    const int h = h0 + i;
+    if (h >= v0) {                       // v head: straight copy into the cache
+      if (vdst) *reinterpret_cast<uint2*>(vdst + (h - v0) * 128 + lane * 4) = raw[i];
+      continue;
+    }
+    const bool is_q = h < kv0;
+    const __nv_bfloat16* nw = is_q ? p.q_norm_w : p.k_norm_w;
+    const float2 lo = unpack_bf16x2(raw[i].x), hi = unpack_bf16x2(raw[i].y);
+    float x[4] = {lo.x, lo.y, hi.x, hi.y};
+    if (nw) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float inv = rsqrtf(ss / 128.f + p.eps);
+      const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
+      const float2 w0 = unpack_bf16x2(wr.x), w1 = unpack_bf16x2(wr.y);
+      const float w[4] = {w0.x, w0.y, w1.x, w1.y};
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        x[k] = __bfloat162float(__float2bfloat16(x[k] * inv * (w[k] + g)));   // norm output is bf16
+    }
+    float y[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[k], 16);
+      y[k] = lane < 16 ? x[k] * c[k] - other * sn[k] : x[k] * c[k] + other * sn[k];
+    }
+    uint2 o;
+    o.x = pack_bf16x2(y[0], y[1]);
+    o.y = pack_bf16x2(y[2], y[3]);
+    if (is_q) {
+      __nv_bfloat16* dst = p.q_out ? p.q_out + ((size_t)t * p.Hq + h) * 128 : const_cast<__nv_bfloat16*>(src[i]);
+      *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+    } else {
+      if (kdst) *reinterpret_cast<uint2*>(kdst + (h - kv0) * 128 + lane * 4) = o;
+      // the activation row keeps the rotated k too
+      *reinterpret_cast<uint2*>(const_cast<__nv_bfloat16*>(src[i]) + lane * 4) = o;
+    }
   }
 }
 
@@ -250,6 +294,12 @@ int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_
             !(ptr_bits & 7) && !(reinterpret_cast<uintptr_t>(cos_sin) & 15)) ? 1 : 0;
   long long warps = (long long)T * (Hq + 2 * Hkv);
   int blocks = (int)((warps + 3) / 4);
+  if (p.vec4) {
+    const int groups = (Hq + 2 * Hkv + kHG - 1) / kHG;
+    const long long w4 = (long long)T * groups;
+    return launch_pdl(rope_kv_vec4_kernel, dim3((unsigned)((w4 + 3) / 4)), dim3(128), 0, stream, p, T) == cudaSuccess
+               ? 0 : -2;
+  }
   return launch_pdl(rope_kv_kernel, dim3(blocks), dim3(128), 0, stream, p, T) == cudaSuccess ? 0 : -2;
 }
 
