@@ -657,10 +657,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           GT_END(4);
           uint8_t* a_dst = smem + (size_t)s * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
+#ifdef B200_GEMM_EXP_NOLOAD
+          // experiment (instrumented builds only): no operand traffic, the MMAs read whatever is in
+          // shared memory; isolates the tensor pipe's own rate from the TMA writes
+          (void)a_dst; (void)b_dst;
+          if (rank == 0) mbar_arrive(&bars->full[s]);
+#else
           if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
           const uint32_t leader_bar = mapa_u32(smem_u32(&bars->full[s]), 0);
           tma_load_2d_pair(a_dst, &tmA, leader_bar, kb * kBK, tm * 2 * kBM + (int)rank * kBM);
           tma_load_2d_pair(b_dst, &tmB, leader_bar, kb * kBK, tn * BN + (int)rank * (BN / 2));
+#endif
         }
       }
       if (!ok) bars->failed = 1;

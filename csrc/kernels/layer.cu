@@ -9,6 +9,8 @@
 //
 // Reference: Qwen3DenseModel::ForwardDevice, src/vllm/model_executor/models/qwen3.cpp:135-244
 // (the reference's forward is native code throughout).
+#include <cstddef>
+
 #include "api.h"
 #include "sm100.cuh"
 
@@ -94,6 +96,14 @@ static constexpr int kConstW = 0x100;
     if (rc_ != 0) return rc_ < 0 ? rc_ : -rc_; \
     ++launches;                 \
   } while (0)
+
+// Layout check for bindings: sizes of the two structs and the offsets of their last members.
+void b200_dense_layer_abi(int* out4) {
+  out4[0] = (int)sizeof(B200DenseLayerWeights);
+  out4[1] = (int)sizeof(B200DenseStep);
+  out4[2] = (int)offsetof(B200DenseLayerWeights, kv_cache);
+  out4[3] = (int)offsetof(B200DenseStep, first_layer);
+}
 
 // Returns the number of launcher calls made (>= 1 kernel each), or a negative error code.
 int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream) {

@@ -71,3 +71,18 @@ def test_fp8_scales(tmp_path):
         got = loader.dequant_fp8(q, scale, (128, 128))
         assert torch.allclose(got.float(), q.float() * full, rtol=1e-2, atol=1e-3)
         assert (got.float() - w).abs().max() < 0.3
+
+
+def test_native_layer_binding_matches_the_c_structs():
+    """The ctypes mirror of the per-layer launch entry has the C structs' size and layout (the
+    kernel library loads without a GPU)."""
+    import ctypes
+    from vllm_cpp_b200.ops import _lib
+    from vllm_cpp_b200.ops.layer import DenseLayerWeights, DenseStep
+    if not _lib.available():
+        import pytest
+        pytest.skip("kernel library not built")
+    out = (ctypes.c_int * 4)()
+    _lib.lib().b200_dense_layer_abi(out)
+    assert list(out) == [ctypes.sizeof(DenseLayerWeights), ctypes.sizeof(DenseStep),
+                         DenseLayerWeights.kv_cache.offset, DenseStep.first_layer.offset]
