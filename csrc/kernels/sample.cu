@@ -86,11 +86,23 @@ __global__ void __launch_bounds__(kSB)
                           float* pv, int* pi) {
   __shared__ ArgPair sh[32];
   const int row = blockIdx.y, blk = blockIdx.x;
-  const int per = (V + blocks_per_row - 1) / blocks_per_row;
+  const int per = (((V + blocks_per_row - 1) / blocks_per_row) + 3) & ~3;   // multiple of 4
   const int lo = blk * per, hi = min(V, lo + per);
   const float* x = logits + (size_t)row * ld;
   ArgPair a{-FLT_MAX, 0x7fffffff};
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+  int i0 = lo;
+  if (!(ld & 3) && !(reinterpret_cast<uintptr_t>(logits) & 15)) {
+    // 16-byte loads over the aligned part of the slice (lo is a multiple of 4)
+    const int hi4 = lo + ((hi - lo) & ~3);
+    for (int i = lo + threadIdx.x * 4; i < hi4; i += blockDim.x * 4) {
+      const float4 q = *reinterpret_cast<const float4*>(x + i);
+      const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) a = arg_better(a, ArgPair{v[k] != v[k] ? -FLT_MAX : v[k], i + k});
+    }
+    i0 = max(lo, hi4);
+  }
+  for (int i = i0 + threadIdx.x; i < hi; i += blockDim.x) {
     float v = x[i];
     if (v != v) v = -FLT_MAX;
     a = arg_better(a, ArgPair{v, i});
