@@ -338,8 +338,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_addr + c * 32, r);
           tmem_ld_wait();
+          if (row < p.M) {       // the owner only reads the rows that exist
 #pragma unroll
-          for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)(c * 32 + i) * kBM, __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) __stcg(dst + (size_t)(c * 32 + i) * kBM, __uint_as_float(r[i]));
+          }
         }
         __threadfence();
         tc_fence_before_sync();
@@ -1149,6 +1151,9 @@ static void plan_streamk(long tiles, int kblocks, int max_workers, int* nworkers
       *nworkers = (int)tiles * parts;
       *sk_tiles = (int)tiles;
     }
+    // (With 50-88 % of the workers owning a tile, cutting the whole k-range evenly over all workers
+    // was measured slower than leaving the rest idle: 71 against 60 us for 32 x 28672 x 4096. The
+    // tiles lose their common k-phase and with it the sharing of the activation rows in L2.)
     return;
   }
   const int r = (int)(tiles % max_workers);
