@@ -32,6 +32,9 @@ CONCURRENCY = 256
 INPUT_LEN = 1024
 OUTPUT_LEN = 256
 PUBLISHED_BASELINE = None  # the reference publishes no number for this model / hardware
+MODEL_LABELS = {"llama-3.1-8b": "Llama-3.1-8B-shaped", "qwen3-0.6b": "Qwen3-0.6B-shaped",
+                "qwen3-coder-30b-a3b": "Qwen3-Coder-30B-A3B-shaped",
+                "deepseek-v2-lite": "DeepSeek-V2-Lite-shaped", "qwen3.6-27b": "Qwen3.6-27B-shaped"}
 
 
 class ClockSampler:
@@ -92,13 +95,139 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+REF_LABELS = {
+    "Output token throughput (tok/s):": "output_tok_s",
+    "Benchmark duration (s):": "duration_s",
+    "Total generated tokens:": "total_output",
+    "Total input tokens:": "total_input",
+    "Successful requests:": "completed",
+    "Median TTFT (ms):": "p50_ttft_ms",
+    "Median TPOT (ms):": "p50_tpot_ms",
+    "Median ITL (ms):": "p50_itl_ms",
+}
+
+
+def parse_reference_report(text: str) -> dict:
+    """Numbers of the reference bench tool's result block (reference:
+    examples/bench/bench_core.h `PrintReport`, fixed-width "label value" lines)."""
+    out = {}
+    for line in text.splitlines():
+        for label, key in REF_LABELS.items():
+            if line.startswith(label):
+                try:
+                    out[key] = float(line[len(label):].strip())
+                except ValueError:
+                    pass
+    return out
+
+
 def run_reference(args) -> int:
-    # The reference ships no setup.py / pyproject.toml, so the one permitted offline install
-    # (`pip install --no-index --target baseline/_ref <reference checkout>`) stops with
-    # "Neither 'setup.py' nor 'pyproject.toml' found"; there is nothing to import or run.
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference is a CMake/C++ project: pip install --target "
-                                     "baseline/_ref fails (neither setup.py nor pyproject.toml)"}))
+    """The reference arm: the unmodified reference engine, built from its own CMake project for
+    sm_100a (`baseline/_ref/cuda/bin/vllm-bench`, its stock bench tool), loads a random-init
+    checkpoint of the same architecture through its own loader and serves the same workload
+    (concurrency, input and output lengths, greedy, ignore-eos) through its own engine loop.
+    Nothing of this repository's package is imported here. The reference has no multi-GPU mode:
+    at N > 1 every rank starts one stock process on its own GPU with 1/N of the concurrent
+    requests; tokens add up and the slowest process sets the time."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    def unavailable(why: str) -> int:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why[:400]}))
+        return 0
+
+    exe = os.path.join(here, "baseline", "_ref", "cuda", "bin", "vllm-bench")
+    if not os.path.exists(exe):
+        return unavailable("baseline/_ref/cuda/bin/vllm-bench is missing: the reference's CMake "
+                           "build for sm_100a has not been installed into baseline/_ref")
+    sys.path.insert(0, os.path.join(here, "baseline"))
+    import ref_assets
+    if args.model not in ref_assets.SHAPES:
+        return unavailable(f"no reference checkpoint recipe for --model {args.model}")
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        return unavailable("no GPU visible to the reference arm")
+    if world > 1:
+        dist.init_process_group("gloo")
+    scratch = os.environ.get("B200_BENCH_SCRATCH", "/tmp")
+    ckpt = os.path.join(scratch, f"b200_ref_ckpt_{args.model}" + (f"_L{args.layers}" if args.layers else ""))
+    C_total, IN, OUT = args.concurrency, args.input_len, args.output_len
+    C = C_total // world + (1 if rank < C_total % world else 0)
+    n_prompts = 2 * C
+    try:
+        if rank == 0 and not os.path.exists(os.path.join(ckpt, "done")):
+            torch.cuda.set_device(local_rank)
+            ref_assets.write_checkpoint(ckpt, args.model, layers=args.layers or None)
+            open(os.path.join(ckpt, "done"), "w").close()
+        if world > 1:
+            dist.barrier()
+        prompts = ref_assets.write_prompts(os.path.join(scratch, f"b200_ref_prompts_{rank}.json"),
+                                           n_prompts, IN, seed=1 + rank)
+    except OSError as e:
+        return unavailable(f"could not write the synthetic checkpoint: {e}")
+    torch.cuda.empty_cache()
+    cmd = [exe, "--model", ckpt, "--dataset-path", prompts, "--num-prompts", str(n_prompts),
+           "--input-len", str(IN), "--output-len", str(OUT), "--concurrency", str(C),
+           "--max-num-batched-tokens", str(args.max_num_batched_tokens)]
+    env = dict(os.environ)
+    env["CUDA_VISIBLE_DEVICES"] = str(local_rank)
+    sampler = ClockSampler(local_rank)
+    if world > 1:
+        dist.barrier()
+    sampler.start()
+    t0 = time.perf_counter()
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=args.watchdog)
+        rc, out, err = r.returncode, r.stdout, r.stderr
+    except subprocess.TimeoutExpired as e:
+        rc, out, err = -9, (e.stdout or b"").decode(errors="replace") if isinstance(e.stdout, bytes) else (e.stdout or ""), "timed out"
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop(since=t0)
+    rep = parse_reference_report(out)
+    ok = rc == 0 and "output_tok_s" in rep and rep.get("duration_s", 0) > 0
+    mine = {"ok": ok, "rc": rc, "rep": rep, "wall": wall, "err": (err or "")[-300:]}
+    if world > 1:
+        allr = [None] * world
+        dist.all_gather_object(allr, mine)
+    else:
+        allr = [mine]
+    if rank != 0:
+        return 0
+    bad = [a for a in allr if not a["ok"]]
+    if bad:
+        return unavailable(f"reference vllm-bench failed (exit {bad[0]['rc']}): {bad[0]['err']!r}")
+    tokens = sum(a["rep"]["total_output"] for a in allr)
+    dur = max(a["rep"]["duration_s"] for a in allr)
+    value = tokens / dur
+    print(json.dumps({
+        "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (random-digit prompts of the named length, random-init weights)",
+        "impl": "reference",
+        "config": {"model": MODEL_LABELS.get(args.model, args.model), "global_batch": C_total,
+                   "seq_len": IN + OUT, "input_len": IN, "output_len": OUT,
+                   "parallelism": "tp1" if world == 1 else f"dp{world}",
+                   "reference_parallelism": ("1 stock process" if world == 1 else
+                                             f"{world} stock processes, one per GPU (the reference "
+                                             "has no multi-GPU mode)"),
+                   "mode": f"closed loop, {n_prompts * world} requests at concurrency {C_total}, "
+                           "whole run timed by the tool's own clock (steps/warmup do not apply)",
+                   "max_num_batched_tokens": args.max_num_batched_tokens,
+                   "command": " ".join(["vllm-bench"] + cmd[1:])},
+        "clocks": clocks,
+        "latency": {"p50_ttft_ms": max(a["rep"].get("p50_ttft_ms", -1) for a in allr),
+                    "p50_tpot_ms": max(a["rep"].get("p50_tpot_ms", -1) for a in allr)},
+        "e2e": {"value": round(value, 2), "unit": "tok/s", "h2d_bytes_per_step": None,
+                "d2h_bytes_per_step": None,
+                "note": "the tool times its engine loop with the host clock from text in to "
+                        "tokens out, so this is the same number as value"},
+        "gpu_launches": None, "output_tokens": int(tokens), "wall_s_with_load": round(max(a["wall"] for a in allr), 1),
+    }))
     return 0
 
 
@@ -112,11 +241,14 @@ def main() -> int:
     ap.add_argument("--concurrency", type=int, default=CONCURRENCY)
     ap.add_argument("--input-len", type=int, default=INPUT_LEN)
     ap.add_argument("--output-len", type=int, default=OUTPUT_LEN)
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
-                    help="N > 1: dp = one engine replica per GPU, the concurrent requests are split "
-                         "between them (the model fits on one GPU; this is the faster deployment); "
-                         "tp = one tensor-parallel engine over all GPUs with the fused "
-                         "GEMM + collective kernels")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"],
+                    help="N > 1: tp = one tensor-parallel (and, for MoE models, expert-parallel) "
+                         "engine over all GPUs with the fused GEMM + collective kernels; "
+                         "dp = one engine replica per GPU, the concurrent requests split between "
+                         "them (a comparison mode, no collective on the hot path)")
+    ap.add_argument("--unfused", action="store_true",
+                    help="tp: GEMM kernels + NCCL collectives instead of the fused kernels "
+                         "(the baseline the fused path is compared with)")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--layers", type=int, default=0,
                     help="diagnostic: override the number of layers (the JSON line then carries "
@@ -178,7 +310,9 @@ def main() -> int:
         enable_cuda_graphs=not args.no_graphs, enable_prefix_caching=True,
         async_scheduling=not args.sync_scheduling,
         parallel=(ParallelConfig(local_rank=local_rank) if dp else
-                  ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank))))
+                  ParallelConfig(tensor_parallel_size=world, rank=rank, local_rank=local_rank,
+                                 enable_expert_parallel=bool(cfg.num_experts) and world > 1,
+                                 fused_collectives=not args.unfused))))
     note("engine built")
     gen = torch.Generator().manual_seed(1 + (rank if dp else 0))
 
@@ -324,12 +458,18 @@ def main() -> int:
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
             "dtype": "bf16", "data": "synthetic (uniform-random prompt ids, random-init weights)",
             "impl": "ours",
-            "config": {"model": "Llama-3.1-8B-shaped", "global_batch": C_total, "seq_len": IN + OUT,
+            "config": {"model": MODEL_LABELS.get(args.model, args.model), "global_batch": C_total,
+                       "seq_len": IN + OUT,
                        "input_len": IN, "output_len": OUT,
-                       "parallelism": (f"dp{world}" if dp else f"tp{world}"),
+                       "parallelism": (f"dp{world}" if dp else
+                                       (f"tp{world}+ep{world}" if cfg.num_experts and world > 1
+                                        else f"tp{world}")),
+                       "collectives": ("none" if world == 1 or dp else
+                                       ("GEMM + NCCL" if args.unfused else
+                                        "fused GEMM + reduce-scatter / all-gather kernels over peer memory")),
                        "mode": "continuous batching, steady state",
                        "max_num_batched_tokens": args.max_num_batched_tokens,
-                       "l2": "weights (16 GB) and KV (>40 GB) per step exceed L2 (126 MB)",
+                       "l2": "the weights and the KV cache read in every step exceed L2 (126 MB) many times over",
                        "ramp_steps": ramp_steps, "cuda_graphs": not args.no_graphs,
                        "async_scheduling": not args.sync_scheduling,
                        **({"layers_override": args.layers} if args.layers > 0 else {})},

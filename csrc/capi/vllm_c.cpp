@@ -148,7 +148,7 @@ struct vllm_engine {
 struct vllm_request {
   vllm_engine* engine = nullptr;
   std::string rid;
-  vllm_stream_callback cb = nullptr;
+  vllm_token_callback cb = nullptr;
   void* user = nullptr;
   std::thread worker;
   std::mutex mu;
@@ -162,7 +162,7 @@ struct vllm_request {
 namespace {
 
 // Drains the stream of `rid`, calling `cb` per delta. Needs the GIL. Fills the totals.
-vllm_status drain(vllm_engine* e, const std::string& rid, vllm_stream_callback cb, void* user,
+vllm_status drain(vllm_engine* e, const std::string& rid, vllm_token_callback cb, void* user,
                   std::string* text, std::string* reason, int* completion_tokens,
                   const std::atomic<bool>* cancelled) {
   PyObject* gen = PyObject_CallMethod(bridge(), "stream", "Os", e->handle, rid.c_str());
@@ -245,7 +245,6 @@ vllm_model_params vllm_model_params_default(void) {
   p.num_blocks = 256;
   p.max_model_len = 0;
   p.max_num_seqs = 8;
-  p.tensor_parallel_size = 1;
   return p;
 }
 
@@ -262,12 +261,32 @@ vllm_sampling_params vllm_sampling_params_default(void) {
 }
 
 vllm_status vllm_engine_load(const vllm_model_params* params, vllm_engine** out) {
+  return vllm_engine_load_ex(params, nullptr, out);
+}
+
+vllm_status vllm_engine_load_ex(const vllm_model_params* params, const vllm_engine_options* options,
+                                vllm_engine** out) {
   g_last_error.clear();
   if (!params || !out || !params->model_path || !*params->model_path) {
     set_error("vllm_engine_load: params, out and params->model_path are required");
     return VLLM_ERR_INVALID_ARGUMENT;
   }
   *out = nullptr;
+  // options: the caller's struct may be older (smaller) than ours; read only what it has
+  int32_t tp = 0, ep = 0;
+  const char* device = nullptr;
+  if (options) {
+    auto has = [&](size_t off, size_t sz) { return options->struct_size >= off + sz; };
+    if (has(offsetof(vllm_engine_options, tensor_parallel_size), sizeof(int32_t)))
+      tp = options->tensor_parallel_size;
+    if (has(offsetof(vllm_engine_options, enable_expert_parallel), sizeof(int32_t)))
+      ep = options->enable_expert_parallel;
+    if (has(offsetof(vllm_engine_options, device), sizeof(const char*))) device = options->device;
+  } else {
+    if (const char* v = std::getenv("VLLM_TENSOR_PARALLEL_SIZE")) tp = std::atoi(v);
+    if (const char* v = std::getenv("VLLM_ENABLE_EXPERT_PARALLEL")) ep = std::atoi(v);
+    device = std::getenv("VLLM_DEVICE");
+  }
   Gil gil;
   if (!bridge()) return take_py_error(VLLM_ERR_MODEL_LOAD);
   PyObject* d = PyDict_New();
@@ -279,9 +298,9 @@ vllm_status vllm_engine_load(const vllm_model_params* params, vllm_engine** out)
   dict_set(d, "max_num_seqs", PyLong_FromLong(params->max_num_seqs > 0 ? params->max_num_seqs : 8));
   dict_set(d, "tool_parser", str_or_none(params->tool_parser && *params->tool_parser ? params->tool_parser : nullptr));
   dict_set(d, "reasoning_parser", str_or_none(params->reasoning_parser));
-  dict_set(d, "tensor_parallel_size", PyLong_FromLong(params->tensor_parallel_size > 0 ? params->tensor_parallel_size : 1));
-  dict_set(d, "enable_expert_parallel", PyBool_FromLong(params->enable_expert_parallel));
-  dict_set(d, "device", str_or_none(params->device));
+  dict_set(d, "tensor_parallel_size", PyLong_FromLong(tp > 0 ? tp : 1));
+  dict_set(d, "enable_expert_parallel", PyBool_FromLong(ep != 0));
+  dict_set(d, "device", str_or_none(device));
   PyObject* h = PyObject_CallMethod(bridge(), "load", "O", d);
   Py_DECREF(d);
   if (!h) return take_py_error(VLLM_ERR_MODEL_LOAD);
@@ -311,7 +330,7 @@ void vllm_engine_free(vllm_engine* engine) {
 }
 
 vllm_status vllm_complete_stream(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
-                                 vllm_stream_callback cb, void* user) {
+                                 vllm_token_callback cb, void* user) {
   g_last_error.clear();
   if (!engine || !prompt || !params) {
     set_error("vllm_complete_stream: engine, prompt and params are required");
@@ -347,7 +366,7 @@ vllm_status vllm_complete(vllm_engine* engine, const char* prompt, const vllm_sa
 }
 
 vllm_status vllm_request_submit(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
-                                vllm_stream_callback cb, void* user, vllm_request** out) {
+                                vllm_token_callback cb, void* user, vllm_request** out) {
   g_last_error.clear();
   if (!engine || !prompt || !params || !out) {
     set_error("vllm_request_submit: engine, prompt, params and out are required");
@@ -389,12 +408,17 @@ vllm_status vllm_request_submit(vllm_engine* engine, const char* prompt, const v
   return VLLM_OK;
 }
 
-void vllm_request_cancel(vllm_request* request) {
-  if (!request || request->done.load() || request->cancelled.exchange(true)) return;
+vllm_status vllm_request_cancel(vllm_request* request) {
+  if (!request) {
+    set_error("vllm_request_cancel: request is NULL");
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  if (request->done.load() || request->cancelled.exchange(true)) return VLLM_OK;
   Gil gil;
   PyObject* r = PyObject_CallMethod(bridge(), "abort", "Os", request->engine->handle, request->rid.c_str());
   if (!r) PyErr_Clear();
   Py_XDECREF(r);
+  return VLLM_OK;
 }
 
 vllm_status vllm_request_wait(vllm_request* request) {
@@ -446,7 +470,7 @@ vllm_status vllm_chat(vllm_engine* engine, const char* request_json, char** out_
 
 namespace {
 struct ChunkSink {
-  vllm_stream_callback cb;
+  vllm_token_callback cb;
   void* user;
 };
 PyObject* chunk_trampoline(PyObject* self, PyObject* args) {
@@ -466,7 +490,7 @@ PyObject* chunk_trampoline(PyObject* self, PyObject* args) {
 PyMethodDef g_chunk_def = {"on_chunk", chunk_trampoline, METH_VARARGS, "forwards one chunk to the C callback"};
 }  // namespace
 
-vllm_status vllm_chat_stream(vllm_engine* engine, const char* request_json, vllm_stream_callback cb, void* user) {
+vllm_status vllm_chat_stream(vllm_engine* engine, const char* request_json, vllm_token_callback cb, void* user) {
   g_last_error.clear();
   if (!engine || !request_json) {
     set_error("vllm_chat_stream: engine and request_json are required");

@@ -4,9 +4,12 @@
  * Handle based, never throws, never exits: every entry point returns a vllm_status and leaves
  * a message for vllm_last_error() (per thread) when it fails. Strings handed to the caller
  * are released with vllm_string_free / vllm_completion_free; strings handed in are copied.
- * The surface (19 symbols, struct layouts, defaults) follows the reference project's
- * include/vllm.h so that a program written against it links unchanged; the fields that the
- * multi-GPU engine needs are appended at the end of vllm_model_params, hence ABI version 6.
+ * The 19 symbols, the struct layouts (field order, widths, the int32 flags) and the defaults
+ * are those of the reference project's include/vllm.h at ABI version 5, so a program compiled
+ * against that header loads this library unchanged. What the multi-GPU engine needs on top
+ * (tensor-parallel size, expert parallelism, device) comes through vllm_engine_load_ex and its
+ * size-prefixed vllm_engine_options, or through the environment (VLLM_TENSOR_PARALLEL_SIZE,
+ * VLLM_ENABLE_EXPERT_PARALLEL, VLLM_DEVICE) for callers that only know vllm_engine_load.
  *
  * The engine behind the handle runs in an embedded Python interpreter (one per process);
  * calls may come from any thread.
@@ -28,7 +31,7 @@ extern "C" {
 #define VLLM_API __attribute__((visibility("default")))
 #endif
 
-#define VLLM_ABI_VERSION 6
+#define VLLM_ABI_VERSION 5
 
 typedef enum vllm_status {
   VLLM_OK = 0,
@@ -50,11 +53,16 @@ typedef struct vllm_model_params {
   int32_t max_num_seqs;               /* <= 0: 8 */
   const char* tool_parser;            /* NULL or "": detect from the chat template, else hermes */
   const char* reasoning_parser;       /* NULL: detect; "none": off */
-  /* ---- appended in ABI version 6 ---- */
+} vllm_model_params;
+
+/* Options beyond vllm_model_params. struct_size = sizeof(vllm_engine_options) as the caller
+ * compiled it: the library reads no field that lies beyond it, so the struct can grow. */
+typedef struct vllm_engine_options {
+  size_t struct_size;
   int32_t tensor_parallel_size;       /* <= 0: 1 */
   int32_t enable_expert_parallel;     /* 0 / 1 */
   const char* device;                 /* NULL: "cuda" */
-} vllm_model_params;
+} vllm_engine_options;
 
 typedef struct vllm_sampling_params {
   float temperature;
@@ -63,21 +71,21 @@ typedef struct vllm_sampling_params {
   float min_p;
   int32_t max_tokens;
   uint64_t seed;
-  bool has_seed;
+  int32_t has_seed;                   /* 0: unseeded */
   float presence_penalty;
   float frequency_penalty;
   float repetition_penalty;           /* must be > 0: a zeroed struct is invalid */
   int32_t min_tokens;
-  bool ignore_eos;
+  int32_t ignore_eos;                 /* 0 / 1 */
   const char* const* stop;
-  size_t n_stop;
+  int32_t n_stop;
   /* at most one structured-output constraint */
   const char* structured_json;
   const char* structured_regex;
   const char* const* structured_choice;
-  size_t n_structured_choice;
+  int32_t n_structured_choice;
   const char* structured_grammar;
-  bool structured_json_object;
+  int32_t structured_json_object;     /* 0 / 1 */
 } vllm_sampling_params;
 
 typedef struct vllm_completion {
@@ -89,25 +97,28 @@ typedef struct vllm_completion {
 
 /* delta: UTF-8 text produced since the last call ("" allowed); finished: last call.
  * Return false to stop the generation (the call still returns VLLM_OK). */
-typedef bool (*vllm_stream_callback)(const char* delta, bool finished, void* user);
+typedef bool (*vllm_token_callback)(const char* delta, bool finished, void* user);
 
 VLLM_API vllm_model_params vllm_model_params_default(void);
 VLLM_API vllm_sampling_params vllm_sampling_params_default(void);
 
 VLLM_API vllm_status vllm_engine_load(const vllm_model_params* params, vllm_engine** out);
+/* Not in the reference: vllm_engine_load plus options (NULL options = vllm_engine_load). */
+VLLM_API vllm_status vllm_engine_load_ex(const vllm_model_params* params,
+                                         const vllm_engine_options* options, vllm_engine** out);
 VLLM_API void vllm_engine_free(vllm_engine* engine);   /* NULL is a no-op */
 
 VLLM_API vllm_status vllm_complete(vllm_engine* engine, const char* prompt,
                                    const vllm_sampling_params* params, vllm_completion* out);
 VLLM_API vllm_status vllm_complete_stream(vllm_engine* engine, const char* prompt,
                                           const vllm_sampling_params* params,
-                                          vllm_stream_callback cb, void* user);
+                                          vllm_token_callback cb, void* user);
 
 /* Non-blocking requests: deltas arrive on a thread the library owns. */
 VLLM_API vllm_status vllm_request_submit(vllm_engine* engine, const char* prompt,
                                          const vllm_sampling_params* params,
-                                         vllm_stream_callback cb, void* user, vllm_request** out);
-VLLM_API void vllm_request_cancel(vllm_request* request);        /* idempotent */
+                                         vllm_token_callback cb, void* user, vllm_request** out);
+VLLM_API vllm_status vllm_request_cancel(vllm_request* request); /* idempotent */
 VLLM_API vllm_status vllm_request_wait(vllm_request* request);   /* blocks until finished */
 VLLM_API bool vllm_request_done(const vllm_request* request);
 VLLM_API const char* vllm_request_error(const vllm_request* request);   /* NULL: none */
@@ -118,7 +129,7 @@ VLLM_API void vllm_request_free(vllm_request* request);          /* joins the de
 VLLM_API vllm_status vllm_chat(vllm_engine* engine, const char* request_json, char** out_json);
 /* Same with one chat.completion.chunk JSON per callback. */
 VLLM_API vllm_status vllm_chat_stream(vllm_engine* engine, const char* request_json,
-                                      vllm_stream_callback cb, void* user);
+                                      vllm_token_callback cb, void* user);
 
 VLLM_API void vllm_string_free(char* s);
 VLLM_API void vllm_completion_free(vllm_completion* c);

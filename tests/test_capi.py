@@ -15,27 +15,35 @@ LIB = os.path.join(ROOT, "vllm_cpp_b200", "libvllm_b200.so")
 SYMBOLS = """vllm_model_params_default vllm_sampling_params_default vllm_engine_load vllm_engine_free
 vllm_complete vllm_complete_stream vllm_request_submit vllm_request_cancel vllm_request_wait vllm_request_done
 vllm_request_error vllm_request_free vllm_chat vllm_chat_stream vllm_string_free vllm_completion_free
-vllm_last_error vllm_version vllm_abi_version""".split()
+vllm_last_error vllm_version vllm_abi_version vllm_engine_load_ex""".split()
 
 
 class ModelParams(ctypes.Structure):
     _fields_ = [("model_path", ctypes.c_char_p), ("tokenizer_config_path", ctypes.c_char_p),
                 ("block_size", ctypes.c_int32), ("num_blocks", ctypes.c_int32), ("max_model_len", ctypes.c_int32),
                 ("max_num_seqs", ctypes.c_int32), ("tool_parser", ctypes.c_char_p),
-                ("reasoning_parser", ctypes.c_char_p), ("tensor_parallel_size", ctypes.c_int32),
+                ("reasoning_parser", ctypes.c_char_p)]
+
+
+class EngineOptions(ctypes.Structure):
+    _fields_ = [("struct_size", ctypes.c_size_t), ("tensor_parallel_size", ctypes.c_int32),
                 ("enable_expert_parallel", ctypes.c_int32), ("device", ctypes.c_char_p)]
+
+
+def cpu_options():
+    return EngineOptions(ctypes.sizeof(EngineOptions), 1, 0, b"cpu")
 
 
 class SamplingParams(ctypes.Structure):
     _fields_ = [("temperature", ctypes.c_float), ("top_p", ctypes.c_float), ("top_k", ctypes.c_int32),
                 ("min_p", ctypes.c_float), ("max_tokens", ctypes.c_int32), ("seed", ctypes.c_uint64),
-                ("has_seed", ctypes.c_bool), ("presence_penalty", ctypes.c_float),
+                ("has_seed", ctypes.c_int32), ("presence_penalty", ctypes.c_float),
                 ("frequency_penalty", ctypes.c_float), ("repetition_penalty", ctypes.c_float),
-                ("min_tokens", ctypes.c_int32), ("ignore_eos", ctypes.c_bool),
-                ("stop", ctypes.POINTER(ctypes.c_char_p)), ("n_stop", ctypes.c_size_t),
+                ("min_tokens", ctypes.c_int32), ("ignore_eos", ctypes.c_int32),
+                ("stop", ctypes.POINTER(ctypes.c_char_p)), ("n_stop", ctypes.c_int32),
                 ("structured_json", ctypes.c_char_p), ("structured_regex", ctypes.c_char_p),
-                ("structured_choice", ctypes.POINTER(ctypes.c_char_p)), ("n_structured_choice", ctypes.c_size_t),
-                ("structured_grammar", ctypes.c_char_p), ("structured_json_object", ctypes.c_bool)]
+                ("structured_choice", ctypes.POINTER(ctypes.c_char_p)), ("n_structured_choice", ctypes.c_int32),
+                ("structured_grammar", ctypes.c_char_p), ("structured_json_object", ctypes.c_int32)]
 
 
 class Completion(ctypes.Structure):
@@ -56,7 +64,7 @@ def lib():
     l.vllm_version.restype = ctypes.c_char_p
     l.vllm_request_error.restype = ctypes.c_char_p
     l.vllm_request_done.restype = ctypes.c_bool
-    for f in ("vllm_engine_free", "vllm_request_cancel", "vllm_request_free", "vllm_string_free",
+    for f in ("vllm_engine_free", "vllm_request_free", "vllm_string_free",
               "vllm_completion_free"):
         getattr(l, f).restype = None
     l.vllm_engine_free.argtypes = [ctypes.c_void_p]
@@ -65,6 +73,8 @@ def lib():
               "vllm_request_error"):
         getattr(l, f).argtypes = [ctypes.c_void_p]
     l.vllm_engine_load.argtypes = [ctypes.POINTER(ModelParams), ctypes.POINTER(ctypes.c_void_p)]
+    l.vllm_engine_load_ex.argtypes = [ctypes.POINTER(ModelParams), ctypes.POINTER(EngineOptions),
+                                      ctypes.POINTER(ctypes.c_void_p)]
     l.vllm_complete.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), ctypes.POINTER(Completion)]
     l.vllm_complete_stream.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), CB, ctypes.c_void_p]
     l.vllm_request_submit.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.POINTER(SamplingParams), CB,
@@ -84,7 +94,7 @@ def ckpt(tmp_path_factory):
 def test_exported_symbols_and_header():
     out = subprocess.run(["nm", "-D", "--defined-only", LIB], capture_output=True, text=True).stdout
     exported = sorted(l.split()[-1] for l in out.splitlines() if " T " in l)
-    assert exported == sorted(SYMBOLS)           # exactly the 19 entry points, nothing else
+    assert exported == sorted(SYMBOLS)           # the reference's 19 entry points + vllm_engine_load_ex
     hdr = os.path.join(ROOT, "include", "vllm.h")
     r = subprocess.run(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", hdr],
                        capture_output=True, text=True)
@@ -92,15 +102,17 @@ def test_exported_symbols_and_header():
 
 
 def test_defaults_and_errors(lib):
-    assert lib.vllm_abi_version() == 6 and lib.vllm_version()
+    assert lib.vllm_abi_version() == 5 and lib.vllm_version()
     mp, sp = lib.vllm_model_params_default(), lib.vllm_sampling_params_default()
-    assert (mp.block_size, mp.num_blocks, mp.max_num_seqs, mp.tensor_parallel_size) == (32, 256, 8, 1)
+    assert (mp.block_size, mp.num_blocks, mp.max_num_seqs) == (32, 256, 8)
+    # the reference's layouts on LP64: 6 pointers/ints = 48 bytes, sampling params 120 bytes
+    assert ctypes.sizeof(ModelParams) == 48 and ctypes.sizeof(SamplingParams) == 120
     assert sp.repetition_penalty == 1.0 and sp.temperature == 1.0 and sp.top_p == 1.0
     eng = ctypes.c_void_p()
     assert lib.vllm_engine_load(None, ctypes.byref(eng)) == 1 and b"required" in lib.vllm_last_error()
     mp.model_path = b"/nonexistent/model"
-    mp.device = b"cpu"
-    assert lib.vllm_engine_load(ctypes.byref(mp), ctypes.byref(eng)) in (2, 3) and not eng.value
+    opt = cpu_options()
+    assert lib.vllm_engine_load_ex(ctypes.byref(mp), ctypes.byref(opt), ctypes.byref(eng)) in (2, 3) and not eng.value
     assert lib.vllm_last_error()
     lib.vllm_engine_free(None)                   # no-op
     assert lib.vllm_request_done(None)
@@ -108,9 +120,12 @@ def test_defaults_and_errors(lib):
 
 def test_full_surface_through_ctypes(lib, ckpt):
     mp = lib.vllm_model_params_default()
-    mp.model_path, mp.device, mp.max_model_len, mp.block_size = ckpt.encode(), b"cpu", 256, 16
+    mp.model_path, mp.max_model_len, mp.block_size = ckpt.encode(), 256, 16
     eng = ctypes.c_void_p()
-    assert lib.vllm_engine_load(ctypes.byref(mp), ctypes.byref(eng)) == 0, lib.vllm_last_error()
+    # an options struct from an older caller (struct_size stops before `device`) is read only as
+    # far as it goes: tensor_parallel_size is honoured, device falls back to the default
+    opt = cpu_options()
+    assert lib.vllm_engine_load_ex(ctypes.byref(mp), ctypes.byref(opt), ctypes.byref(eng)) == 0, lib.vllm_last_error()
     sp = lib.vllm_sampling_params_default()
     sp.temperature, sp.max_tokens = 0.0, 6
     out = Completion()
@@ -147,7 +162,8 @@ def test_full_surface_through_ctypes(lib, ckpt):
     assert lib.vllm_request_submit(eng, b"hello", ctypes.byref(sp), cb2, None, ctypes.byref(req)) == 0
     assert lib.vllm_request_wait(req) == 0 and lib.vllm_request_done(req) and lib.vllm_request_error(req) is None
     assert got and got[-1][1] is True
-    lib.vllm_request_cancel(req)                 # idempotent after completion
+    assert lib.vllm_request_cancel(req) == 0     # idempotent after completion
+    assert lib.vllm_request_cancel(None) == 1
     lib.vllm_request_free(req)
     # chat: JSON in, JSON out, and chunks
     body = json.dumps({"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0}).encode()
@@ -190,11 +206,13 @@ int main(int argc, char** argv) {
   efree_t efree = (efree_t)dlsym(h, "vllm_engine_free");
   err_t err = (err_t)dlsym(h, "vllm_last_error");
   vllm_model_params mp = mpd();
-  mp.model_path = argv[2]; mp.device = "cpu"; mp.max_model_len = 128; mp.block_size = 16;
+  mp.model_path = argv[2]; mp.max_model_len = 128; mp.block_size = 16;
   vllm_engine* e = NULL;
   if (load(&mp, &e) != VLLM_OK) { fprintf(stderr, "load: %s\n", err()); return 3; }
   vllm_sampling_params sp = spd();
-  sp.temperature = 0.0f; sp.max_tokens = 4;
+  sp.temperature = 0.0f; sp.max_tokens = 4; sp.ignore_eos = 1;
+  const char* stops[1] = {"\x01never\x02"};
+  sp.stop = stops; sp.n_stop = 1;
   vllm_completion c;
   if (complete(e, "The quick", &sp, &c) != VLLM_OK) { fprintf(stderr, "complete: %s\n", err()); return 4; }
   printf("OK %d %d %s\n", c.prompt_tokens, c.completion_tokens, c.finish_reason);
@@ -205,14 +223,25 @@ int main(int argc, char** argv) {
 """
 
 
-def test_plain_c_program_with_dlopen(tmp_path, ckpt):
+REFERENCE_INCLUDE = os.environ.get("VLLM_REFERENCE_INCLUDE", "/root/reference/include")
+
+
+@pytest.mark.parametrize("header", ["ours", "reference"])
+def test_plain_c_program_with_dlopen(tmp_path, ckpt, header):
+    """A C program that only knows the header: built once against this repository's vllm.h and
+    once against the reference project's own header (ABI 5), which must drive the library
+    unchanged: same struct layouts, same signatures."""
+    inc = os.path.join(ROOT, "include") if header == "ours" else REFERENCE_INCLUDE
+    if not os.path.exists(os.path.join(inc, "vllm.h")):
+        pytest.skip("reference header not available")
     src = tmp_path / "drv.c"
     src.write_text(C_PROGRAM)
     exe = tmp_path / "drv"
-    r = subprocess.run(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe), "-ldl"],
+    r = subprocess.run(["gcc", "-std=c99", "-I", inc, str(src), "-o", str(exe), "-ldl"],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     env = dict(os.environ)
+    env["VLLM_DEVICE"] = "cpu"
     site = sysconfig.get_paths()["purelib"]
     env["PYTHONPATH"] = os.pathsep.join([ROOT, site, env.get("PYTHONPATH", "")])
     r = subprocess.run([str(exe), LIB, ckpt], capture_output=True, text=True, env=env, timeout=300)
