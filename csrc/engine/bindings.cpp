@@ -230,7 +230,9 @@ PYBIND11_MODULE(_engine, m) {
       .def_readwrite("req_ids", &ModelRunnerOutput::req_ids)
       .def_readwrite("sampled_token_ids", &ModelRunnerOutput::sampled_token_ids)
       .def_readwrite("logprobs", &ModelRunnerOutput::logprobs)
-      .def_readwrite("num_nans_in_logits", &ModelRunnerOutput::num_nans_in_logits);
+      .def_readwrite("num_nans_in_logits", &ModelRunnerOutput::num_nans_in_logits)
+      .def_readwrite("finished_sending", &ModelRunnerOutput::finished_sending)
+      .def_readwrite("finished_recving", &ModelRunnerOutput::finished_recving);
   py::class_<DraftTokenIds>(m, "DraftTokenIds")
       .def(py::init<>())
       .def_readwrite("req_ids", &DraftTokenIds::req_ids)
@@ -380,10 +382,13 @@ PYBIND11_MODULE(_engine, m) {
 
   // ---- scheduler
   py::class_<Scheduler>(m, "Scheduler")
-      .def(py::init([](const SchedulerConfig& c, const KVCacheConfig& k) {
-        return c.async_scheduling ? static_cast<Scheduler*>(new AsyncScheduler(c, k))
-                                  : new Scheduler(c, k);
-      }))
+      .def(py::init([](const SchedulerConfig& c, const KVCacheConfig& k, py::object connector) {
+        // keep_alive below ties the connector's lifetime to the scheduler's
+        KVConnectorHook* hook = connector.is_none() ? nullptr : connector.cast<KVConnectorHook*>();
+        return c.async_scheduling ? static_cast<Scheduler*>(new AsyncScheduler(c, k, nullptr, hook))
+                                  : new Scheduler(c, k, nullptr, hook);
+      }), py::arg("scheduler_config"), py::arg("kv_cache_config"), py::arg("kv_connector") = py::none(),
+          py::keep_alive<1, 4>())
       .def("add_request", [](Scheduler& s, const EngineCoreRequest& r) {
         EngineCoreRequest rr = r;
         rr.sampling_params.post_init();
@@ -398,6 +403,7 @@ PYBIND11_MODULE(_engine, m) {
       .def("get_request", &Scheduler::get_request)
       .def("num_running", &Scheduler::num_running)
       .def("num_waiting", &Scheduler::num_waiting)
+      .def("num_delayed_free", &Scheduler::num_delayed_free)
       .def("has_unfinished_requests", &Scheduler::has_unfinished_requests)
       .def("has_requests", &Scheduler::has_requests)
       .def("reset_prefix_cache", &Scheduler::reset_prefix_cache)

@@ -177,9 +177,13 @@ SchedulerOutput Scheduler::schedule() {
         req->status = RequestStatus::kWaiting;
       }
       if (req->status == RequestStatus::kWaitingForRemoteKvs) {
-        waiting_.pop();
-        skipped.push_back(req);
-        continue;
+        // promoted once the runner has reported the transfer complete (update_from_output)
+        if (!promote_after_remote_kv(*req)) {
+          waiting_.pop();
+          skipped.push_back(req);
+          continue;
+        }
+        req->status = RequestStatus::kWaiting;
       }
       int num_local = 0, num_external = 0;
       bool load_async = false;
@@ -402,6 +406,15 @@ EngineCoreOutputs Scheduler::update_from_output(const SchedulerOutput& so,
                                   [&](const RequestPtr& r) { return stopped_set.count(r.get()) > 0; }),
                    running_.end());
   }
+  // external KV transfers the runner saw complete during this step
+  for (auto& id : mro.finished_recving)
+    if (requests_.count(id)) finished_recving_.insert(id);
+  for (auto& id : mro.finished_sending) {
+    auto it = delayed_free_.find(id);
+    if (it == delayed_free_.end()) continue;
+    kv_->free(*it->second);
+    delayed_free_.erase(it);
+  }
   auto st = kv_->take_prefix_cache_stats();
   pc_queries_ += st.queries;
   pc_hits_ += st.hits;
@@ -415,8 +428,28 @@ void Scheduler::free_request(const RequestPtr& req) {
   if (connector_) delay = connector_->request_finished(*req, kv_->get_block_ids(req->request_id));
   if (so_ && req->use_structured_output) so_->release(*req);
   finished_req_ids_.insert(req->request_id);
-  if (!delay) kv_->free(*req);
+  finished_recving_.erase(req->request_id);
+  if (delay) delayed_free_[req->request_id] = req;   // blocks stay until finished_sending names it
+  else kv_->free(*req);
   requests_.erase(req->request_id);
+}
+
+// A request whose prefix is being loaded by the connector holds its blocks but computes
+// nothing. When the runner reports the load complete, the loaded blocks become ordinary
+// computed (and cacheable) blocks and the request goes back to plain waiting. The last prompt
+// token is always left to compute, so that the request produces logits.
+bool Scheduler::promote_after_remote_kv(Request& req) {
+  auto it = finished_recving_.find(req.request_id);
+  if (it == finished_recving_.end()) return false;
+  const auto ids = kv_->get_block_ids(req.request_id);
+  int n = ids.empty() ? 0 : (int)ids[0].size() * kv_->block_size();
+  n = std::min(n, req.num_tokens());
+  if (n == req.num_tokens()) n -= 1;
+  if (n > 0) kv_->cache_blocks(req, n);
+  req.num_computed_tokens = std::max(n, 0);
+  if (req.num_cached_tokens < 0) req.num_cached_tokens = req.num_computed_tokens;
+  finished_recving_.erase(it);
+  return true;
 }
 
 void Scheduler::finish_requests(const std::vector<std::string>& ids, RequestStatus status) {

@@ -100,6 +100,7 @@ class Scheduler {
   bool has_requests() const { return has_unfinished_requests() || has_finished_requests(); }
   int num_running() const { return (int)running_.size(); }
   int num_waiting() const { return (int)waiting_.size(); }
+  int num_delayed_free() const { return (int)delayed_free_.size(); }
   bool reset_prefix_cache() { return kv_->reset_prefix_cache(); }
   SchedulerStats make_stats();
   KVCacheManager& kv_cache_manager() { return *kv_; }
@@ -121,6 +122,7 @@ class Scheduler {
   void preempt_request(const RequestPtr& req);
   void free_request(const RequestPtr& req);
   bool check_stop(Request& req);
+  bool promote_after_remote_kv(Request& req);
 
   SchedulerConfig cfg_;
   KVCacheConfig kv_cfg_;
@@ -131,6 +133,10 @@ class Scheduler {
   RequestQueue waiting_;
   std::vector<RequestPtr> running_;
   std::set<std::string> finished_req_ids_;
+  // external KV connector: loads the runner has reported complete but the waiting loop has not
+  // consumed yet, and finished requests whose blocks the connector is still sending
+  std::set<std::string> finished_recving_;
+  std::unordered_map<std::string, RequestPtr> delayed_free_;
   int num_preempted_since_stats_ = 0;
   int last_step_tokens_ = 0;
   int64_t pc_queries_ = 0, pc_hits_ = 0;

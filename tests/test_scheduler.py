@@ -379,3 +379,65 @@ def test_runner_failure_marks_engine_dead():
     with pytest.raises(E.EngineDeadError):
         c.add_request_async(req("b", 4))
     c.shutdown(True)
+
+
+class AsyncLoadConnector(E.KVConnectorHook):
+    """A connector that answers "N tokens are available remotely and will arrive asynchronously"
+    and asks for the blocks of finished requests to be kept while it sends them."""
+
+    def __init__(self, external_tokens, delay_free=False):
+        super().__init__()
+        self.external, self.delay = external_tokens, delay_free
+        self.alloc = []
+
+    def get_num_new_matched_tokens(self, rid, token_ids, num_computed):
+        return (max(0, self.external - num_computed), True)
+
+    def update_state_after_alloc(self, rid, token_ids, block_ids, num_external):
+        self.alloc.append((rid, [list(b) for b in block_ids], num_external))
+
+    def request_finished(self, rid, token_ids, block_ids, num_computed):
+        return self.delay
+
+
+def test_async_remote_kv_load_is_promoted_when_the_runner_reports_it():
+    """A request whose prefix loads asynchronously holds its blocks and computes nothing until
+    the runner names it in finished_recving; then only the rest of the prompt is scheduled."""
+    conn = AsyncLoadConnector(external_tokens=8)
+    c = E.SchedulerConfig(max_num_batched_tokens=64, max_num_seqs=8, max_model_len=256)
+    s = E.Scheduler(c, kv_cfg(100, block_size=4), conn)
+    s.add_request(req("a", 10, max_tokens=2))
+    free0 = s.num_free_blocks()
+    so = s.schedule()
+    assert so.total_num_scheduled_tokens == 0 and s.num_waiting() == 1 and s.num_running() == 0
+    assert conn.alloc and conn.alloc[0][2] == 8 and s.num_free_blocks() == free0 - 2
+    s.update_from_output(so, E.ModelRunnerOutput())
+    # not reported yet: still parked, every step
+    so = s.schedule()
+    assert so.total_num_scheduled_tokens == 0 and s.num_waiting() == 1
+    done = E.ModelRunnerOutput()
+    done.finished_recving = {"a"}
+    s.update_from_output(so, done)
+    so = s.schedule()
+    assert so.num_scheduled_tokens == {"a": 2}          # 10 prompt tokens - 8 loaded
+    assert s.num_running() == 1 and s.num_waiting() == 0
+    s.update_from_output(so, mro(so))
+    so, outs = step(s)
+    assert outs.outputs[0].finish_reason is not None and s.num_free_blocks() == free0
+
+
+def test_delayed_free_releases_blocks_on_finished_sending():
+    conn = AsyncLoadConnector(external_tokens=0, delay_free=True)
+    conn.get_num_new_matched_tokens = lambda rid, toks, n: (0, False)
+    c = E.SchedulerConfig(max_num_batched_tokens=64, max_num_seqs=8, max_model_len=256)
+    s = E.Scheduler(c, kv_cfg(100, block_size=4), conn)
+    free0 = s.num_free_blocks()
+    s.add_request(req("a", 10, max_tokens=1))
+    so, outs = step(s)
+    assert outs.outputs[0].finish_reason is not None
+    assert s.num_delayed_free() == 1 and s.num_free_blocks() < free0    # the connector still sends
+    so = s.schedule()
+    sent = E.ModelRunnerOutput()
+    sent.finished_sending = {"a"}
+    s.update_from_output(so, sent)
+    assert s.num_delayed_free() == 0 and s.num_free_blocks() == free0

@@ -2,6 +2,11 @@
 backend, 4 prompts of 128 uniform-random ids, 64 greedy tokens each, block size 16, one process.
 
     python -m vllm_cpp_b200.entrypoints.bench_cpu [--backend native|torch] [--threads N] [--layers L]
+    python -m vllm_cpp_b200.entrypoints.bench_cpu --impl reference --reference-bin <vllm-bench>
+
+The second form times the same workload on the reference project's own CPU build (its stock
+bench tool, CMake option VLLM_CPP_CUDA=OFF) with a random-init checkpoint of the same shape
+written by ``baseline/ref_assets.py``; the stock tool fixes the block size at 32.
 
 Prints one JSON line with prefill and decode token rates and the wall time of the run.
 Reference: the CPU rows of docs/BENCHMARKS.md (prefill / decode tok/s of the CPU backend).
@@ -15,6 +20,41 @@ import time
 import torch
 
 
+def run_reference(args) -> int:
+    import importlib.util
+    import os
+    import subprocess
+    import tempfile
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    exe = args.reference_bin if os.path.isabs(args.reference_bin) else os.path.join(root, args.reference_bin)
+    if not os.path.exists(exe):
+        print(json.dumps({"impl": "reference", "unavailable": f"{args.reference_bin} not built"}))
+        return 0
+    spec = importlib.util.spec_from_file_location("ref_assets", os.path.join(root, "baseline", "ref_assets.py"))
+    ref_assets = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_assets)
+    with tempfile.TemporaryDirectory() as d:
+        ref_assets.write_checkpoint(d, "qwen3-0.6b", layers=args.layers or None)
+        prompts = ref_assets.write_prompts(os.path.join(d, "prompts.json"), args.prompts, args.input_len)
+        r = subprocess.run([exe, "--model", d, "--dataset-path", prompts, "--num-prompts", str(args.prompts),
+                            "--input-len", str(args.input_len), "--output-len", str(args.output_len),
+                            "--concurrency", str(args.prompts)], capture_output=True, text=True)
+    rep = {}
+    for line in r.stdout.splitlines():
+        for label, key in (("Benchmark duration (s):", "wall_s"), ("Output token throughput (tok/s):", "output_tok_s"),
+                           ("Input (prefill) token throughput (tok/s):", "input_tok_s"),
+                           ("Median TTFT (ms):", "p50_ttft_ms"), ("Median TPOT (ms):", "p50_tpot_ms")):
+            if line.startswith(label):
+                rep[key] = float(line[len(label):].strip())
+    if r.returncode != 0 or "wall_s" not in rep:
+        print(json.dumps({"impl": "reference", "unavailable": (r.stderr or r.stdout)[-300:]}))
+        return 0
+    print(json.dumps({"config": "Qwen3-0.6B-shaped bf16, CPU, %d x %d -> %d, block 32 (fixed by the tool)"
+                                % (args.prompts, args.input_len, args.output_len),
+                      "impl": "reference", **rep}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="native", choices=["native", "torch"])
@@ -23,7 +63,11 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=4)
     ap.add_argument("--input-len", type=int, default=128)
     ap.add_argument("--output-len", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reference-bin", default="baseline/_ref/cpu/bin/vllm-bench")
     args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return run_reference(args)
     from ..config import EngineArgs, synthetic_config
     from ..engine import LLM, SamplingParams
     if args.threads > 0:
@@ -62,7 +106,9 @@ def main(argv=None) -> int:
         "threads": (__import__("vllm_cpp_b200.ops.cpu_native", fromlist=["x"]).num_threads()
                     if args.backend == "native" else torch.get_num_threads()),
         "prefill_tok_s": round(n_in / t_prefill, 1), "decode_tok_s": round(n_out / t_decode, 1),
-        "decode_steps": steps, "wall_s": round(t_prefill + t_decode, 2)}))
+        "decode_steps": steps, "wall_s": round(t_prefill + t_decode, 2),
+        "output_tok_s": round(args.prompts * args.output_len / (t_prefill + t_decode), 2),
+        "p50_ttft_ms": round(t_prefill * 1e3, 1), "p50_tpot_ms": round(t_decode / max(steps, 1) * 1e3, 2)}))
     return 0
 
 
