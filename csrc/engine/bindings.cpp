@@ -528,6 +528,7 @@ PYBIND11_MODULE(_engine, m) {
       .def_readonly("any_top_k_top_p", &StepInfo::any_top_k_top_p)
       .def_readonly("any_min_p", &StepInfo::any_min_p)
       .def_readonly("any_logprobs", &StepInfo::any_logprobs)
+      .def_readonly("any_logit_edits", &StepInfo::any_logit_edits)
       .def_readonly("req_ids", &StepInfo::req_ids)
       .def_readonly("num_scheduled", &StepInfo::num_scheduled)
       .def_readonly("produces_token", &StepInfo::produces_token)

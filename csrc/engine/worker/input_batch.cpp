@@ -286,6 +286,10 @@ StepInfo InputBatch::prepare(const SchedulerOutput& so, const StepLayout& L, uin
       }
       if (sp.has_penalties()) info.any_penalties = true;
       if (sp.logprobs) info.any_logprobs = true;
+      const int n_out_now = (int)s.token_ids.size() - s.num_prompt_tokens;
+      if (!sp.logit_bias.empty() || !sp.allowed_token_ids.empty() || !sp.bad_words_token_ids.empty() ||
+          n_out_now < sp.min_tokens)
+        info.any_logit_edits = true;
     }
     info.max_logprobs.push_back(sp.logprobs ? *sp.logprobs : -1);
     info.req_ids.push_back(s.req_id);

@@ -74,6 +74,8 @@ struct StepInfo {
   int num_splice = 0;
   bool all_greedy = true, any_penalties = false, any_top_k_top_p = false, any_min_p = false;
   bool any_logprobs = false;
+  // a sampling row has a logit bias, an allow / ban list or a min_tokens ban still in force
+  bool any_logit_edits = false;
   std::vector<std::string> req_ids;        // batch order
   std::vector<int> num_scheduled;          // per request
   std::vector<uint8_t> produces_token;     // request finishes its known tokens this step

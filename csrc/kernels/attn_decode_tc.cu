@@ -538,12 +538,11 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
   p.tmp_o = (float*)tmp_o; p.tmp_lse = (float*)tmp_lse;
   p.status = device_status_word();
   constexpr size_t smem = (size_t)kSlots * kSlotBytes + 4096 + 8192 + 1024 + sizeof(DecodeTcBars);
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(attn_decode_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    set = true;
   }
   dim3 grid(B, Hkv, splits);
   const int G = Hq / Hkv;

@@ -432,11 +432,10 @@ static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const
   constexpr int kDH = D / 64;
   constexpr size_t smem = (size_t)kDH * 16384 + (size_t)kRing * kDH * 8192 + 16384 + 1024 +
                           sizeof(PrefillBars);
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-    set = true;
   }
   attn_prefill_kernel<D><<<grid, 64 + 128 * (D > 128 ? 2 : 1), smem, stream>>>(tmQ, tmKV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

@@ -97,11 +97,14 @@ int b200_num_sms() {
   return n;
 }
 
-// Reads (and clears) the status word of the current device. Synchronises the device.
+// Reads (and clears) the status word of the current device. Synchronises the whole device
+// first: a pageable cudaMemcpy alone orders only against the legacy default stream, and kernels
+// launched on non-blocking streams could still be running their bounded waits.
 int b200_read_status() {
   int* w = b200::device_status_word();
   if (!w) return -1;
   int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
   cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost);
   if (v != 0) cudaMemset(w, 0, sizeof(int));
   return v;

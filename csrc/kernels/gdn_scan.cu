@@ -573,11 +573,10 @@ extern "C" int b200_gdn_chunk_scan(const void* q, const void* k, const void* v, 
       !encode_tmap_2d(&tmQs, qs, BF, 2, (uint64_t)NT * kC, (uint64_t)Hv * kD, (uint64_t)Hv * kD, kC, 64, SW) ||
       !encode_tmap_2d(&tmP, pbuf, BF, 2, (uint64_t)NT * Hv * kC, kC, kC, kC, 64, SW))
     return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPrepSmem);
     cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kScanSmem);
-    attr_set = true;
   }
   PrepParams pp{};
   pp.g = g; pp.beta = beta; pp.q = (const bf16*)q;

@@ -1174,11 +1174,10 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
   if (stages < 2) stages = 2;
   p.stages = stages;
   size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_bf16_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          kSmemBudget + 4096);
-    attr_set = true;
   }
   int tiles = p.tiles_m * p.tiles_n;
   int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
@@ -1191,12 +1190,10 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
     }
     p.sk = sk_tiles;
   }
-  // Tensor-parallel launches stay ordinary: their CTAs wait on other ranks, and nothing should
-  // become resident beside them early.
-  if (p.tp_world > 1 || p.ag_flags) {
-    gemm_bf16_tn_kernel<BN><<<grid, kGemmThreads, smem, stream>>>(tmA, tmA2, tmB, p);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
-  }
+  // Tensor-parallel launches use programmatic dependent launch like the rest of the chain: the
+  // kernel touches nothing a peer can see before its wait on the predecessor, every CTA of a
+  // grid is resident before its dependents may start (the grid never exceeds the SM count), and
+  // a kernel only ever waits for work that precedes it in its peers' streams.
   return launch_pdl(gemm_bf16_tn_kernel<BN>, dim3(grid), dim3(kGemmThreads), smem, stream, tmA, tmA2, tmB, p) ==
                  cudaSuccess ? 0 : -2;
 }
@@ -1452,11 +1449,10 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     if (!get_tmap_bf16(&tmA, A, M, K, lda, mp, kBK)) return -3;
     tmA2 = tmA;
     if (tp && tp->gather && tp->a_alt && !get_tmap_bf16(&tmA2, tp->a_alt, M, K, lda, mp, kBK)) return -3;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce attr_once;
+    if (attr_once.first()) {
       cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            kSmemBudget + 4096);
-      attr_set = true;
     }
     size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
     dim3 grid(p.tiles_n, splits);
@@ -1498,6 +1494,9 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   // epilogue live in the 1-CTA kernel.
   if (force_path == 5) { use256 = true; p.sk = !tp; }
   if (force_path == 6) { use256 = false; p.sk = !tp; }
+  // tensor-parallel shards are narrow (N / world or K / world): few tiles or a ragged last wave
+  // are the rule, so the tiled path always plans stream-K there
+  if (tp && force_path == 1) p.sk = 1;
   // 256-row pair tiles pad M up to a multiple of 256; where 128-row tiles would do noticeably
   // fewer rows (e.g. M = 1056: 1280 against 1152) the 1-CTA 128 x 256 tile with stream-K is faster
   // (measured 907-1253 against 699-1175 TFLOP/s on the four Llama-8B projections at M = 1056).
@@ -1570,11 +1569,10 @@ extern "C" int b200_gemm_bf16_batched(const void* A, int lda, int a_batch_cols, 
   CUtensorMap tmW, tmA;
   if (!get_tmap_bf16(&tmW, W, (uint64_t)batch * N, K, ldw, kBM, kBK)) return -3;
   if (!get_tmap_bf16(&tmA, A, M, (uint64_t)lda, lda, mp, kBK)) return -3;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_bf16_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          kSmemBudget + 4096);
-    attr_set = true;
   }
   const size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
   gemm_bf16_swap_kernel<<<dim3(p.tiles_n, 1, batch), kGemmThreads, smem, stream>>>(tmW, tmA, tmA, p, tmem_cols);
@@ -1625,9 +1623,15 @@ extern "C" const char* b200_gemm_bf16_smallm_static_error(void) { return b200::g
 extern "C" int b200_gemm_bf16_smallm_static_status(int* out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !out) return -1;
-  if (!g_static_dev[dev].ready) { *out = 0; return 0; }
-  return cudaMemcpy(out, g_static_dev[dev].status, sizeof(int), cudaMemcpyDeviceToHost) ==
-                 cudaSuccess ? 0 : -2;
+  int* word = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_dev[dev].ready) word = g_static_dev[dev].status;
+  }
+  if (!word) { *out = 0; return 0; }
+  // every stream of the device, non-blocking ones included, must have drained before the read
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  return cudaMemcpy(out, word, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* W, int ldw,

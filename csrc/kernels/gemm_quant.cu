@@ -338,10 +338,9 @@ int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int
   p.stages = kblocks + 1 < 6 ? (kblocks + 1 < 2 ? 2 : kblocks + 1) : 6;
   p.status = device_status_word();
   const size_t smem = (size_t)p.stages * (kQM * kQKB + kQN * kQKB) + 1024 + sizeof(QBars);
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 6 * 32768 + 2048 + (int)sizeof(QBars));
-    set = true;
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();

@@ -375,10 +375,9 @@ int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, cons
   if (p.sf_tma && !encode_tmap_2d(&tmS, sf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 16, K / 16, kWN, 16,
                                   CU_TENSOR_MAP_SWIZZLE_NONE))
     return -3;
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_w4a16_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-    set = true;
   }
   const size_t smem = (size_t)kMaxRS * kRawBytes + (size_t)kMaxES * kExpBytes + (size_t)kMaxAS * kActBytes +
                       (size_t)kMaxRS * kSfBytes + 1024 + sizeof(W4SBars);

@@ -165,4 +165,179 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
   return launches;
 }
 
+
+// ---- tensor-parallel stack ----------------------------------------------------------------
+int b200_tp_reduce_norm_gather(const struct B200TpReduce* a, cudaStream_t stream);
+
+// Peer-mapped buffers of the fused tensor-parallel path (see tp_fused.cu): per rank a receive
+// buffer, a gathered-activation buffer and the counters, each with two parities.
+typedef struct B200TpLayers {
+  int world, rank;
+  int rpr_max;                 // capacity of a rank's row shard (multiple of 32)
+  int max_tokens;              // capacity of the gathered buffer (multiple of 32)
+  void* recv[8];               // [2][world * k-splits][rpr][H] bf16
+  void* rs_flags[8];           // [2][rpr_max / 32]
+  void* x_full[8];             // [2][max_tokens][H] bf16
+  void* ag_flags[8];           // [2][max_tokens / 32]
+  void* op_counter;            // local
+  void* done_counter;          // local
+  void* residual;              // local shard [rpr_max][H]
+  const void* final_norm;      // the norm after the last block
+} B200TpLayers;
+
+struct B200TpReduce {          // mirrors tp_fused.cu
+  int world, rank, rows_per_rank, M, H;
+  const void* recv;
+  long long recv_parity_stride;
+  void* rs_flags;
+  int rs_flag_parity_stride;
+  int expected_rs;
+  int nsrc;
+  void* residual;
+  const void* norm_w;
+  float eps;
+  int gemma;
+  void* peer_x[8];
+  long long x_parity_stride;
+  void* peer_ag_flags[8];
+  int ag_flag_parity_stride;
+  int ag_groups;
+  void* op_counter;
+  void* done_counter;
+};
+
+void b200_tp_layers_abi(int* out2) {
+  out2[0] = (int)sizeof(B200TpLayers);
+  out2[1] = (int)offsetof(B200TpLayers, final_norm);
+}
+
+namespace {
+struct TpIssue {
+  const B200TpLayers* c;
+  const B200DenseStep* s;
+  cudaStream_t stream;
+  int rpr;                     // rows per rank of this step
+  long long recv_parity, x_parity;
+  int rs_groups, ag_groups;
+
+  int gather_gemm(const void* W, int N, void* out, int ldo, int out_f32) const {
+    B200TpGemm d{};
+    d.world = c->world; d.rank = c->rank; d.rows_per_rank = rpr;
+    d.gather = 1;
+    d.a_alt = reinterpret_cast<const __nv_bfloat16*>(c->x_full[c->rank]) + x_parity;
+    d.ag_flags = c->ag_flags[c->rank];
+    d.ag_flag_parity_stride = ag_groups;
+    d.op_counter = c->op_counter;
+    d.out_f32 = out_f32;
+    return b200_gemm_bf16_tp(c->x_full[c->rank], s->H, W, s->H, out, ldo, s->T, N, s->H, &d, nullptr, stream);
+  }
+  // partial a[T, K] x W[H, K]^T scattered to the row owners; *expected / *nsrc feed the reduce
+  int scatter_gemm(const void* a, int K, const void* W, int* expected, int* nsrc) const {
+    B200TpGemm d{};
+    d.world = c->world; d.rank = c->rank; d.rows_per_rank = rpr;
+    d.scatter = 1;
+    for (int r = 0; r < c->world; ++r) { d.peer_recv[r] = c->recv[r]; d.peer_rs_flags[r] = c->rs_flags[r]; }
+    d.recv_parity_stride = recv_parity;
+    d.rs_flag_parity_stride = rs_groups;
+    d.op_counter = c->op_counter;
+    int splits = 1;
+    if (s->T <= 256) {
+      // small batches: split K so that more than H / 128 CTAs stream the weight shard; every
+      // (rank, split) pair owns a source slot of the receive buffer
+      const int tiles_n = (s->H + 127) / 128, kblocks = (K + 63) / 64;
+      splits = b200_num_sms() / tiles_n;
+      if (splits > kblocks / 4) splits = kblocks / 4;
+      if (splits > c->rpr_max / rpr) splits = c->rpr_max / rpr;
+      if (splits > 8) splits = 8;
+      if (splits < 1) splits = 1;
+      const int kb_per = (kblocks + splits - 1) / splits;
+      splits = (kblocks + kb_per - 1) / kb_per;
+    }
+    d.scatter_splits = splits;
+    *nsrc = c->world * splits;
+    return b200_gemm_bf16_tp(a, K, W, K, nullptr, s->H, s->T, s->H, K, &d, expected, stream);
+  }
+  int reduce(int expected, int nsrc, const void* norm_w) const {
+    B200TpReduce a{};
+    a.world = c->world; a.rank = c->rank; a.rows_per_rank = rpr; a.M = s->T; a.H = s->H;
+    a.recv = c->recv[c->rank];
+    a.recv_parity_stride = recv_parity;
+    a.rs_flags = c->rs_flags[c->rank];
+    a.rs_flag_parity_stride = rs_groups;
+    a.expected_rs = expected;
+    a.nsrc = nsrc;
+    a.residual = c->residual;
+    a.norm_w = norm_w;
+    a.eps = s->eps; a.gemma = s->gemma;
+    for (int r = 0; r < c->world; ++r) { a.peer_x[r] = c->x_full[r]; a.peer_ag_flags[r] = c->ag_flags[r]; }
+    a.x_parity_stride = x_parity;
+    a.ag_flag_parity_stride = ag_groups;
+    a.ag_groups = ag_groups;
+    a.op_counter = c->op_counter;
+    a.done_counter = c->done_counter;
+    return b200_tp_reduce_norm_gather(&a, stream);
+  }
+};
+}  // namespace
+
+// All blocks of the fused tensor-parallel forward. On entry the first norm has run
+// (b200_tp_first_norm: gathered buffer = norm(embeddings), residual shard initialised); on return
+// the gathered buffer holds the final norm's output. s->Hq / Hkv / inter are this rank's shards.
+// Returns the number of launcher calls made or a negative error code.
+int b200_dense_layers_tp(const B200DenseLayerWeights* w, int num_layers, const B200DenseStep* s,
+                         const B200TpLayers* c, cudaStream_t stream) {
+  if (!w || !s || !c || s->T <= 0 || num_layers <= 0) return 0;
+  if (c->world < 2 || c->world > 8 || (c->rpr_max & 31) || (c->max_tokens & 31) || s->T > c->max_tokens)
+    return -1;
+  int launches = 0;
+  const int T = s->T, H = s->H, D = s->D, Hq = s->Hq, Hkv = s->Hkv, I = s->inter;
+  const int qkv_w = (Hq + 2 * Hkv) * D;
+  using bf16 = __nv_bfloat16;
+  TpIssue tp;
+  tp.c = c; tp.s = s; tp.stream = stream;
+  tp.rpr = (((T + c->world - 1) / c->world) + 31) & ~31;
+  if (tp.rpr > c->rpr_max) return -1;
+  tp.recv_parity = (long long)c->world * c->rpr_max * H;
+  tp.x_parity = (long long)c->max_tokens * H;
+  tp.rs_groups = c->rpr_max / 32;
+  tp.ag_groups = c->max_tokens / 32;
+  const int nd = s->num_decodes;
+  for (int l = 0; l < num_layers; ++l) {
+    const B200DenseLayerWeights* L = w + l;
+    B200_TRY(tp.gather_gemm(L->qkv, qkv_w, s->qkv_buf, qkv_w, 0));
+    B200_TRY(b200_rope_kv(s->qkv_buf, qkv_w, 0, Hq * D, (Hq + Hkv) * D, D, Hq, Hkv, D, s->rot, s->positions,
+                          s->cos_sin, L->q_norm, L->k_norm, s->eps, s->gemma, s->neox, s->slot_mapping,
+                          L->kv_cache, s->block_size, nullptr, T, stream));
+    if (nd > 0) {
+      if (s->decode_tc)
+        B200_TRY(b200_attn_decode_tc(s->qkv_buf, qkv_w, s->attn, Hq * D, L->kv_cache, s->num_blocks, s->block_size,
+                                     Hq, Hkv, D, s->block_table, s->max_blocks, s->seq_lens, nd, s->scale,
+                                     s->softcap, s->window, s->decode_splits, s->decode_tmp_o,
+                                     s->decode_tmp_lse, stream));
+      else
+        B200_TRY(b200_attn_decode(s->qkv_buf, qkv_w, s->attn, Hq * D, L->kv_cache, s->block_size, Hq, Hkv, D,
+                                  s->block_table, s->max_blocks, s->seq_lens, nd, s->scale, s->softcap,
+                                  s->window, s->decode_splits, s->decode_tmp_o, s->decode_tmp_lse, stream));
+    }
+    if (s->num_prefills > 0) {
+      const bf16* q = reinterpret_cast<const bf16*>(s->qkv_buf) + (size_t)nd * qkv_w;
+      bf16* o = reinterpret_cast<bf16*>(s->attn) + (size_t)nd * Hq * D;
+      const int32_t* bt = reinterpret_cast<const int32_t*>(s->block_table) + (size_t)nd * s->max_blocks;
+      const int32_t* sl = reinterpret_cast<const int32_t*>(s->seq_lens) + nd;
+      B200_TRY(b200_attn_prefill(q, qkv_w, o, Hq * D, nullptr, L->kv_cache, s->num_blocks, s->block_size, Hq, Hkv,
+                                 D, bt, s->max_blocks, sl, s->prefill_q_start, s->tile_req, s->tile_q0,
+                                 s->num_tiles, s->num_prefill_tokens, s->scale, s->softcap, s->window, 1, stream));
+    }
+    int expected = 0, nsrc = 0;
+    B200_TRY(tp.scatter_gemm(s->attn, Hq * D, L->o, &expected, &nsrc));
+    B200_TRY(tp.reduce(expected, nsrc, L->ln2));
+    B200_TRY(tp.gather_gemm(L->gate_up, 2 * I, s->gate_up_buf, 2 * I, 0));
+    B200_TRY(b200_act_and_mul(s->gate_up_buf, 2 * I, s->act, T, I,
+                              s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), stream));
+    B200_TRY(tp.scatter_gemm(s->act, I, L->down, &expected, &nsrc));
+    B200_TRY(tp.reduce(expected, nsrc, l + 1 < num_layers ? w[l + 1].ln1 : c->final_norm));
+  }
+  return launches;
+}
+
 }  // extern "C"

@@ -512,10 +512,9 @@ int b200_mla_decode(const void* qabs, void* out, int ldo, const void* cache, int
   p.splits = splits; p.tmp_o = (float*)tmp_o; p.tmp_lse = (float*)tmp_lse;
   p.status = device_status_word();
   constexpr size_t smem = (size_t)kSlots * kSlotBytes + kQBytes + 8192 + 1024 + sizeof(MlaBars);
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    set = true;
   }
   mla_decode_kernel<<<dim3(B, splits), 192, smem, stream>>>(tmQ, tmC, p);
   if (cudaGetLastError() != cudaSuccess) return -2;

@@ -455,11 +455,10 @@ int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, in
   if (stages > nkb) stages = nkb < 2 ? 2 : nkb;
   p.stages = stages; p.act_silu = 0; p.status = device_status_word();
   const size_t smem = (size_t)stages * stage + 1024 + sizeof(GroupedBars);
-  static bool set = false;
-  if (!set) {
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
     cudaFuncSetAttribute(moe_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          220 * 1024);
-    set = true;
   }
   dim3 grid((N + kGBM - 1) / kGBM, max_chunks);
   moe_grouped_gemm_kernel<<<grid, 192, smem, stream>>>(tmW, tmX, p);

@@ -130,6 +130,41 @@ __global__ void __launch_bounds__(32)
   if (threadIdx.x == 0) out[row] = (a.i >= V || a.i < 0) ? 0 : a.i;
 }
 
+// Vocabulary-parallel greedy sampling: each rank reduces its own logits shard to one
+// (value, global index) candidate per row; after the candidates of all ranks have been gathered
+// ([n][world] pairs, 8 bytes each) the best one wins, ties going to the lowest index, so the
+// result equals the argmax over the full row.
+__global__ void __launch_bounds__(32)
+    argmax_candidate_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
+                            int blocks_per_row, int V, int index_base, int2* __restrict__ out) {
+  const int row = blockIdx.x;
+  ArgPair a{-FLT_MAX, 0x7fffffff};
+  for (int i = threadIdx.x; i < blocks_per_row; i += 32)
+    a = arg_better(a, ArgPair{pv[row * blocks_per_row + i], pi[row * blocks_per_row + i]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgPair b;
+    b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+    b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = arg_better(a, b);
+  }
+  if (threadIdx.x == 0) {
+    const bool ok = a.i >= 0 && a.i < V;
+    out[row] = make_int2(__float_as_int(ok ? a.v : -FLT_MAX), ok ? index_base + a.i : 0x7fffffff);
+  }
+}
+__global__ void argmax_combine_kernel(const int2* __restrict__ cand, int n, int world, int V_total,
+                                      int64_t* __restrict__ out) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  ArgPair a{-FLT_MAX, 0x7fffffff};
+  for (int r = 0; r < world; ++r) {
+    const int2 c = cand[(size_t)r * n + row];     // rank-major, as an all-gather along dim 0 lays it out
+    a = arg_better(a, ArgPair{__int_as_float(c.x), c.y});
+  }
+  out[row] = (a.i < 0 || a.i >= V_total) ? 0 : a.i;
+}
+
 // ---- temperature: rows with temperature < eps are left untouched (greedy rows) ----
 __global__ void temperature_kernel(float* logits, int ld, int V, const float* __restrict__ temp) {
   const int row = blockIdx.y;
@@ -414,6 +449,34 @@ int b200_argmax(const void* logits, int ld, int n, int V, void* out_i64, void* s
                                                   (float*)scratch_f, (int*)scratch_i);
   argmax_final_kernel<<<n, 32, 0, stream>>>((const float*)scratch_f, (const int*)scratch_i, bpr,
                                             (int64_t*)out_i64, V);
+  RET_LAUNCH;
+}
+
+// Local stage of the vocabulary-parallel argmax: cand_out[n] (8 bytes each) = best (value,
+// index_base + column) of this rank's logits[n, V]; columns at or beyond v_valid are ignored
+// (padding of the last shard).
+int b200_argmax_candidates(const void* logits, int ld, int n, int V, int v_valid, int index_base,
+                           void* cand_out, void* scratch_f, void* scratch_i, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (v_valid > V) v_valid = V;
+  if (v_valid <= 0) {   // nothing of the vocabulary lives here: candidates that never win
+    argmax_candidate_kernel<<<n, 32, 0, stream>>>(nullptr, nullptr, 0, 0, index_base, (int2*)cand_out);
+    RET_LAUNCH;
+  }
+  const int bpr = b200_argmax_blocks_per_row(n, v_valid);
+  dim3 grid(bpr, n);
+  argmax_partial_kernel<<<grid, kSB, 0, stream>>>((const float*)logits, ld, v_valid, bpr,
+                                                  (float*)scratch_f, (int*)scratch_i);
+  argmax_candidate_kernel<<<n, 32, 0, stream>>>((const float*)scratch_f, (const int*)scratch_i, bpr, v_valid,
+                                                index_base, (int2*)cand_out);
+  RET_LAUNCH;
+}
+// Final stage: cand[world][n] pairs -> out[n] int64 token ids.
+int b200_argmax_combine(const void* cand, int n, int world, int V_total, void* out_i64,
+                        cudaStream_t stream) {
+  if (n <= 0) return 0;
+  argmax_combine_kernel<<<(n + 127) / 128, 128, 0, stream>>>((const int2*)cand, n, world, V_total,
+                                                             (int64_t*)out_i64);
   RET_LAUNCH;
 }
 

@@ -13,6 +13,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <stdint.h>
 
 namespace b200 {
@@ -476,6 +477,18 @@ int* device_status_word();
 // B200_PDL=0 in the environment makes launch_pdl() an ordinary launch.
 // ------------------------------------------------------------------------------------
 bool pdl_enabled();
+// Per-device once flag for settings that belong to a (function, device) pair, such as
+// cudaFuncSetAttribute: first() is true exactly once for every device that is current when it
+// is called (up to 64 devices per process).
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    const unsigned long long bit = 1ull << dev;
+    return (done.fetch_or(bit) & bit) == 0;
+  }
+};
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

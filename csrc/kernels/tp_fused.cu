@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(ReduceNormPa
   __shared__ float red[32];
   __shared__ int s_ok;
   extern __shared__ uint4 row_cache[];  // H/8 vectors
+  pdl_wait();                 // the scatter GEMM of this rank is complete
+  pdl_launch_dependents();
   const uint32_t k = *p.op_counter;
   const uint32_t par = k & 1, npar = par ^ 1;
   const int rl = blockIdx.x;
@@ -303,8 +305,8 @@ int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream) {
   p.ag_groups = a->ag_groups;
   p.op_counter = (uint32_t*)a->op_counter; p.done_counter = (uint32_t*)a->done_counter;
   p.status = device_status_word();
-  tp_reduce_norm_gather_kernel<<<a->rows_per_rank, 256, (size_t)a->H * 2, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_pdl(tp_reduce_norm_gather_kernel, dim3(a->rows_per_rank), dim3(256), (size_t)a->H * 2, stream,
+                    p) == cudaSuccess ? 0 : -2;
 }
 
 int b200_tp_first_norm(const void* hidden, void* residual_shard, const void* w, void* x_full,

@@ -34,7 +34,10 @@ def _rel(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (7, 1024, 14336), (256, 2048, 512)])
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (7, 1024, 14336), (256, 2048, 512),
+                                   # at least as many 128-column tiles as SMs: the unsplit branch,
+                                   # which writes the output directly and never touches the array
+                                   (16, 19200, 256)])
 def test_static_scratch_gemm_matches_workspace_gemm(M, N, K):
     lib = _load()
     torch.cuda.set_device(0)

@@ -256,6 +256,7 @@ class DenseModel:
             self.bufs.reserve(name, max_tokens, cols)
         self.bufs.reserve("last", max_reqs, c.hidden_size)
         self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
+        self.bufs.reserve("argmax_cand", max_reqs, 2, torch.int32)
 
     # ------------------------------------------------------------------ forward
     # ------------------------------------------------------------------ fused TP forward
@@ -270,6 +271,10 @@ class DenseModel:
     def enable_fused_tp(self, max_tokens: int) -> None:
         from ..parallel.tp_fused import TpFusedContext
         self.tpf = TpFusedContext(self.comm, self.device, self.cfg.hidden_size, max_tokens)
+        # with a "greedy_out" buffer in the step context the forward returns None and leaves the
+        # argmax ids there (see the end of _forward_tp_fused)
+        self.samples_greedy = type(self)._forward_tp_fused is DenseModel._forward_tp_fused and \
+            self.cfg.final_logit_softcap <= 0
 
     def _forward_tp_fused(self, ctx: StepContext) -> torch.Tensor:
         """Sequence-parallel forward: every o_proj / down_proj is GEMM + reduce-scatter (scatter
@@ -289,7 +294,16 @@ class DenseModel:
         tpf.first_norm(hidden, self.layers[0]["ln1"], eps, c.gemma_norm)
         pos = ctx.positions[:T]
         n_layers = len(self.layers)
-        for l, L in enumerate(self.layers):
+        layers = self.layers
+        if self.native_layers is None:
+            self.native_layers = self._native_tp_ok()
+        if self.native_layers and not nvtx.ENABLED:
+            s = self._native_step(ctx, T, qkv, attn, gate_up, act, act_kind)
+            if s is not None:
+                from ..ops.layer import dense_layers_tp
+                dense_layers_tp(self._native_weights(), s, tpf.native_ctx(self.w["final_norm"]))
+                layers = []                    # every block already ran
+        for l, L in enumerate(layers):
             grp = self.layer_group[l]
             window = c.sliding_window if (c.sliding_window and (
                 not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
@@ -319,6 +333,18 @@ class DenseModel:
             last = tpf.gather_rows(T, ctx.logits_indices[:n], self.bufs.get("last", n, H))
             logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
             be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
+        greedy_out = ctx.extra.get("greedy_out")
+        if greedy_out is not None and c.final_logit_softcap <= 0:
+            # Vocabulary-parallel greedy sampling: every rank reduces its shard to one candidate
+            # per row and only those 8-byte pairs cross the link, not [n, vocab] fp32 logits
+            # (a monotone logits scale does not change the argmax).
+            from .. import ops
+            cand = self.bufs.get("argmax_cand", n, 2, torch.int32)
+            valid = max(0, min(self.vocab_shard, c.vocab_size - self.vocab_start))
+            ops.argmax_candidates(logits, valid, self.vocab_start, cand)
+            allc = self.comm.all_gather(cand, dim=0)
+            ops.argmax_combine(allc, n, self.tp, c.vocab_size, greedy_out[:n])
+            return None
         logits = self.comm.all_gather(logits, dim=-1)
         if logits.shape[1] != c.vocab_size:
             logits = logits[:, : c.vocab_size]
@@ -360,9 +386,11 @@ class DenseModel:
             self._native_w = ws
         return ws
 
-    def _run_native_layers(self, ctx, T, hidden, resid, normed, qkv, attn, gate_up, act, act_kind) -> bool:
+    def _native_step(self, ctx, T, qkv, attn, gate_up, act, act_kind, hidden=None, resid=None, normed=None):
+        """The shapes, step metadata and activation buffers of one forward as the native layer
+        entries take them; None when this step needs the per-op path (split-KV buffers absent)."""
         from .. import ops
-        from ..ops.layer import DenseStep, dense_layer
+        from ..ops.layer import DenseStep
         c = self.cfg
         grp = self.layer_group[0]
         G = self.hq // self.hkv
@@ -374,7 +402,7 @@ class DenseModel:
             splits = ops.attn_decode_splits(nd, self.hkv, G, self.D, bt.shape[1] * self.block_size,
                                             self.block_size if use_tc else 0)
         if nd > 0 and splits > 1 and tmp is None:
-            return False                      # the per-op path allocates the split buffers
+            return None                       # the per-op path allocates the split buffers
         s = DenseStep()
         s.T, s.H, s.Hq, s.Hkv, s.D, s.rot, s.inter, s.block_size = (T, c.hidden_size, self.hq, self.hkv, self.D,
                                                                   self.rot, self.inter, self.block_size)
@@ -392,14 +420,31 @@ class DenseModel:
         if ctx.num_prefills > 0:
             s.prefill_q_start, s.tile_req, s.tile_q0 = (ctx.prefill_q_start.data_ptr(), ctx.tile_req.data_ptr(),
                                                         ctx.tile_q0.data_ptr())
-        s.hidden, s.resid, s.normed = hidden.data_ptr(), resid.data_ptr(), normed.data_ptr()
+        if hidden is not None:
+            s.hidden, s.resid, s.normed = hidden.data_ptr(), resid.data_ptr(), normed.data_ptr()
         s.qkv_buf, s.attn, s.gate_up_buf, s.act = qkv.data_ptr(), attn.data_ptr(), gate_up.data_ptr(), act.data_ptr()
         ws = ops.workspace(self.device, ops.GEMM_WS_BYTES)
         s.gemm_ws, s.gemm_ws_bytes = ws.data_ptr(), ws.numel()
+        return s
+
+    def _run_native_layers(self, ctx, T, hidden, resid, normed, qkv, attn, gate_up, act, act_kind) -> bool:
+        from ..ops.layer import dense_layer
+        s = self._native_step(ctx, T, qkv, attn, gate_up, act, act_kind, hidden, resid, normed)
+        if s is None:
+            return False
         for l, w in enumerate(self._native_weights()):
             s.first_layer = int(l == 0)
             dense_layer(w, s)
         return True
+
+    def _native_tp_ok(self) -> bool:
+        """The fused tensor-parallel stack has a native entry for the plain pre-norm block with one
+        KV-cache group (the same configurations as the one-GPU native entry)."""
+        c = self.cfg
+        if os.environ.get("B200_NATIVE_LAYERS", "1") == "0" or type(self)._forward_tp_fused is not \
+                DenseModel._forward_tp_fused:
+            return False
+        return not (c.mlp_bias or c.sliding_window or len(set(self.layer_group)) != 1)
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Returns fp32 logits ``[num_logits, vocab]`` for the rows in ``ctx.logits_indices``."""

@@ -347,6 +347,25 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     return out
 
 
+def argmax_candidates(logits: torch.Tensor, v_valid: int, index_base: int, out: torch.Tensor) -> torch.Tensor:
+    """Local stage of the vocabulary-parallel argmax: ``out[n, 2]`` int32 = (bits of the best
+    value, ``index_base`` + its column) over the first ``v_valid`` columns of this rank's shard."""
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() >= 2 * n
+    ws = workspace(logits.device, max(n, 1) * 64 * 8 + 1024, "argmax")
+    check(lib().b200_argmax_candidates(ptr(logits), logits.stride(0), n, V, v_valid, index_base, ptr(out),
+                                       ptr(ws[: n * 64 * 4]), ptr(ws[n * 64 * 4: n * 64 * 8]), stream_ptr()),
+          "argmax_candidates")
+    return out
+
+
+def argmax_combine(cand: torch.Tensor, n: int, world: int, vocab: int, out: torch.Tensor) -> torch.Tensor:
+    """Final stage: ``cand[world, n, 2]`` (rank-major) -> ``out[n]`` int64 ids; ties go to the
+    lowest index, as in :func:`argmax` over the full row."""
+    check(lib().b200_argmax_combine(ptr(cand), n, world, vocab, ptr(out), stream_ptr()), "argmax_combine")
+    return out
+
+
 def apply_temperature(logits, temperature):
     n, V = logits.shape
     check(lib().b200_apply_temperature(ptr(logits), logits.stride(0), n, V, ptr(temperature),

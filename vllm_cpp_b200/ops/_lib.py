@@ -75,6 +75,8 @@ _SIGS = {
     "b200_attn_decode_tc": ([P, I, P, I, P, L, I, I, I, I, P, I, P, I, F, F, I, I, P, P, P], I),
     "b200_merge_attn_states": ([P, P, P, P, P, P, I, I, I, P], I),
     "b200_argmax": ([P, I, I, I, P, P, P, P], I),
+    "b200_argmax_candidates": ([P, I, I, I, I, I, P, P, P, P], I),
+    "b200_argmax_combine": ([P, I, I, I, P, P], I),
     "b200_apply_temperature": ([P, I, I, I, P, P], I),
     "b200_apply_penalties": ([P, I, I, P, P, P, I, P, P, P, P], I),
     "b200_sparse_edit": ([P, I, I, P, P, P, I, I, P], I),

@@ -41,3 +41,40 @@ def dense_layer(weights: DenseLayerWeights, step: DenseStep) -> None:
     if rc < 0:
         raise KernelError(f"dense_layer: kernel launcher returned {rc}")
     LAUNCHES[0] += rc
+
+
+class TpLayers(C.Structure):
+    """Peer-mapped buffers of the fused tensor-parallel path as ``b200_dense_layers_tp`` takes them."""
+    _fields_ = [("world", I), ("rank", I), ("rpr_max", I), ("max_tokens", I),
+                ("recv", P * 8), ("rs_flags", P * 8), ("x_full", P * 8), ("ag_flags", P * 8),
+                ("op_counter", P), ("done_counter", P), ("residual", P), ("final_norm", P)]
+
+
+_tp_declared = False
+
+
+def dense_layers_tp(weights: list, step: DenseStep, tp: TpLayers) -> None:
+    """Every block of the fused tensor-parallel forward in one native call."""
+    global _tp_declared
+    L = lib()
+    n = len(weights)
+    arr = getattr(dense_layers_tp, "_arr", None)
+    if arr is None or arr[0] is not weights:
+        packed = (DenseLayerWeights * n)(*weights)
+        arr = (weights, packed)
+        dense_layers_tp._arr = arr
+    if not _tp_declared:
+        L.b200_dense_layers_tp.argtypes = [C.POINTER(DenseLayerWeights), I, C.POINTER(DenseStep),
+                                           C.POINTER(TpLayers), P]
+        L.b200_dense_layers_tp.restype = I
+        L.b200_tp_layers_abi.argtypes = [C.POINTER(I)]
+        L.b200_tp_layers_abi.restype = None
+        abi = (I * 2)()
+        L.b200_tp_layers_abi(abi)
+        if (abi[0], abi[1]) != (C.sizeof(TpLayers), TpLayers.final_norm.offset):
+            raise KernelError("TpLayers layout differs between the binding and the kernel library")
+        _tp_declared = True
+    rc = L.b200_dense_layers_tp(arr[1], n, C.byref(step), C.byref(tp), stream_ptr())
+    if rc < 0:
+        raise KernelError(f"dense_layers_tp: kernel launcher returned {rc}")
+    LAUNCHES[0] += rc

@@ -257,6 +257,24 @@ class TpFusedContext:
             self._arange = torch.arange(self.max_tokens, dtype=torch.int32, device=self.device)
         return self.gather_rows(T, self._arange[:T], out)
 
+    def native_ctx(self, final_norm: torch.Tensor):
+        """The buffer table as the native layer-stack entry takes it (built once)."""
+        c = getattr(self, "_native", None)
+        if c is None or c.final_norm != final_norm.data_ptr():
+            from ..ops.layer import TpLayers
+            c = TpLayers()
+            c.world, c.rank, c.rpr_max, c.max_tokens = self.world, self.rank, self.rpr_max, self.max_tokens
+            for r in range(self.world):
+                c.recv[r] = self.recv.ptrs[r]
+                c.rs_flags[r] = self._rs_flags(r)
+                c.x_full[r] = self.x_full.ptrs[r]
+                c.ag_flags[r] = self._ag_flags(r)
+            c.op_counter, c.done_counter = self._op_counter(), self._done_counter()
+            c.residual = self.residual.data_ptr()
+            c.final_norm = final_norm.data_ptr()
+            self._native = c
+        return c
+
     def close(self):
         for b in (self.recv, self.x_full, self.flags):
             b.close()

@@ -96,6 +96,7 @@ class ModelRunner(E.ModelRunnerBase):
                                         pin_memory=self.is_cuda)
         self.last_sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
         self.graphs: dict[int, tuple] = {}
+        self._model_samples_greedy = bool(getattr(model, "samples_greedy", False))
         self.enable_graphs = enable_cuda_graphs and self.is_cuda
         self.graph_sizes = decode_graph_sizes(max_num_seqs) if self.enable_graphs else []
         self._info = None
@@ -231,10 +232,13 @@ class ModelRunner(E.ModelRunnerBase):
         # warm-up run on a side stream (allocations, tensor maps, lazy module state)
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
+        if self._model_samples_greedy:
+            ctx.extra["greedy_out"] = self.sampled
         with torch.cuda.stream(s):
             for _ in range(2):
                 logits = self.model.forward(ctx)
-                self.ops.argmax(logits, out=self.sampled[:size])
+                if logits is not None:
+                    self.ops.argmax(logits, out=self.sampled[:size])
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         from ..ops import _lib
@@ -242,7 +246,8 @@ class ModelRunner(E.ModelRunnerBase):
         n0 = _lib.LAUNCHES[0]
         with torch.cuda.graph(g):
             logits = self.model.forward(ctx)
-            self.ops.argmax(logits, out=self.sampled[:size])
+            if logits is not None:
+                self.ops.argmax(logits, out=self.sampled[:size])
         self.graphs[size] = (g, logits, _lib.LAUNCHES[0] - n0)
         return self.graphs[size]
 
@@ -280,8 +285,11 @@ class ModelRunner(E.ModelRunnerBase):
         self._scheduled_spec = dict(so.scheduled_spec_decode_tokens) if self.spec else {}
         R, T = info.num_reqs, info.num_tokens
         decode_only = info.num_prefills == 0 and info.num_decodes == R
-        pad = self._pad_size(R) if (decode_only and self.enable_graphs and info.all_greedy
-                                    and not info.any_penalties and not info.any_logprobs) else None
+        # plain greedy step: nothing edits the logits, the sampled id is the row's argmax
+        plain_greedy = (info.all_greedy and not info.any_penalties and not info.any_logprobs
+                        and not info.any_logit_edits and not so.structured_output_request_ids
+                        and self.spec is None)
+        pad = self._pad_size(R) if (decode_only and self.enable_graphs and plain_greedy) else None
         if pad is not None and pad > R:
             hv = self.host_views
             hv["input_ids"][R:pad].zero_()
@@ -311,13 +319,17 @@ class ModelRunner(E.ModelRunnerBase):
             g[0].replay()
             from ..ops import _lib as _l
             _l.LAUNCHES[0] += g[2]  # launcher calls folded into the replayed graph
-            self._logits = g[1][:R]
+            self._logits = g[1][:R] if g[1] is not None else None
             self._graph_sampled = True
         else:
             ctx = self._context(info)
+            if plain_greedy and self._model_samples_greedy:
+                # the model writes the argmax ids itself (tensor parallel: candidates per vocabulary
+                # shard are exchanged instead of the logits)
+                ctx.extra["greedy_out"] = self.sampled
             with nvtx.range(f"forward T={T} R={R}"):
                 self._logits = self.model.forward(ctx)
-            self._graph_sampled = False
+            self._graph_sampled = self._logits is None
         self.num_kernel_steps += 1
 
     def _sample_device(self, info, grammar) -> torch.Tensor:
