@@ -273,8 +273,7 @@ class DenseModel:
         self.tpf = TpFusedContext(self.comm, self.device, self.cfg.hidden_size, max_tokens)
         # with a "greedy_out" buffer in the step context the forward returns None and leaves the
         # argmax ids there (see the end of _forward_tp_fused)
-        self.samples_greedy = type(self)._forward_tp_fused is DenseModel._forward_tp_fused and \
-            self.cfg.final_logit_softcap <= 0
+        self.samples_greedy = self.cfg.final_logit_softcap <= 0
 
     def _forward_tp_fused(self, ctx: StepContext) -> torch.Tensor:
         """Sequence-parallel forward: every o_proj / down_proj is GEMM + reduce-scatter (scatter
@@ -324,6 +323,13 @@ class DenseModel:
             exp = tpf.gemm_scatter(act, L["down"])
             nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
             tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)
+        return self._tp_fused_logits(ctx, T)
+
+    def _tp_fused_logits(self, ctx: StepContext, T: int):
+        """lm_head over the gathered final-norm rows. With a ``greedy_out`` buffer in the step
+        context the argmax ids are left there and None is returned; otherwise fp32 logits
+        ``[num_logits, vocab]`` (all-gathered over the vocabulary shards)."""
+        c, be, tpf, H = self.cfg, self.be, self.tpf, self.cfg.hidden_size
         if ctx.decode_only_full_logits:
             n = T
             logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
@@ -337,7 +343,7 @@ class DenseModel:
         if greedy_out is not None and c.final_logit_softcap <= 0:
             # Vocabulary-parallel greedy sampling: every rank reduces its shard to one candidate
             # per row and only those 8-byte pairs cross the link, not [n, vocab] fp32 logits
-            # (a monotone logits scale does not change the argmax).
+            # (a positive logits scale does not change the argmax).
             from .. import ops
             cand = self.bufs.get("argmax_cand", n, 2, torch.int32)
             valid = max(0, min(self.vocab_shard, c.vocab_size - self.vocab_start))

@@ -168,6 +168,7 @@ class MoeModel(DenseModel):
         self.bufs.reserve("router", max_tokens, self.E, torch.float32)
         self.bufs.reserve("last", max_reqs, c.hidden_size)
         self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
+        self.bufs.reserve("argmax_cand", max_reqs, 2, torch.int32)
         if self.device.type == "cuda":
             from ..ops.moe import MoeWorkspace
             self.moe_ws = MoeWorkspace(self.device, max_tokens, self.k, self.e_local,
@@ -307,14 +308,4 @@ class MoeModel(DenseModel):
             nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
             # every source rank delivers 32 arrivals per 32-row group (see moe_combine_kernel)
             tpf.reduce_norm_gather(T, tpf.world * 32, nw, eps, False, nsrc=tpf.world)
-        if ctx.decode_only_full_logits:
-            n = T
-            logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
-            tpf.gemm_gather(T, self.w["lm_head"], logits)
-        else:
-            n = ctx.num_logits
-            last = tpf.gather_rows(T, ctx.logits_indices[:n], self.bufs.get("last", n, H))
-            logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
-            be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
-        logits = self.comm.all_gather(logits, dim=-1)
-        return logits[:, : c.vocab_size] if logits.shape[1] != c.vocab_size else logits
+        return self._tp_fused_logits(ctx, T)

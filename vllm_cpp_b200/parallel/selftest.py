@@ -74,21 +74,30 @@ def check_primitives(comm, device, results):
     return ok
 
 
-def check_engine(comm, device, results, local_rank):
+def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
+    """Greedy tokens of one model shape: TP=1 vs TP=world over NCCL vs TP=world fused (native
+    layer stack and per-op launch sequence). MoE shapes run expert parallel at TP=world."""
     from vllm_cpp_b200 import ops
     from vllm_cpp_b200.config import EngineArgs, ParallelConfig, synthetic_config
     from vllm_cpp_b200.engine import LLM, SamplingParams
-    cfg = synthetic_config("tiny-qwen3")
+    cfg = synthetic_config(shape)
     cfg.head_dim = 128
     cfg.num_heads, cfg.num_kv_heads = 8, 8
-    cfg.hidden_size, cfg.intermediate_size, cfg.num_layers = 512, 1024, 3
+    cfg.hidden_size, cfg.num_layers = 512, 3
+    if shape == "tiny-moe":
+        cfg.moe_intermediate_size = 256
+    else:
+        cfg.intermediate_size = 1024
+    tag = shape.replace("tiny-", "")
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 9, 300, 40)]
     sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
 
-    def run(tp, fused):
+    def run(tp, fused, native=True):
+        os.environ["B200_NATIVE_LAYERS"] = "1" if native else "0"
         par = ParallelConfig(tensor_parallel_size=tp, rank=comm.rank if tp > 1 else 0,
-                             local_rank=local_rank, fused_collectives=fused)
+                             local_rank=local_rank, fused_collectives=fused,
+                             enable_expert_parallel=bool(cfg.num_experts) and tp > 1)
         llm = LLM(EngineArgs(model_config=cfg, device="cuda", block_size=16, num_blocks=200,
                              max_model_len=640, max_num_seqs=4, max_num_batched_tokens=256,
                              parallel=par))
@@ -102,6 +111,8 @@ def check_engine(comm, device, results, local_rank):
     base = run(1, False)
     nccl = run(comm.world, False)
     fused = run(comm.world, True)
+    per_op = run(comm.world, True, native=False)
+    os.environ.pop("B200_NATIVE_LAYERS", None)
 
     def agree(a, b):
         hit = tot = 0
@@ -115,16 +126,19 @@ def check_engine(comm, device, results, local_rank):
             tot += len(x)
         return hit / tot
 
-    results["engine_first_tokens_equal"] = [x[0] for x in fused] == [x[0] for x in base]
-    results["engine_agree_fused_vs_tp1"] = agree(fused, base)
-    results["engine_agree_nccl_vs_tp1"] = agree(nccl, base)
-    results["engine_agree_fused_vs_nccl"] = agree(fused, nccl)
-    results["engine_status"] = ops.read_status()
+    R = {}
+    R["first_tokens_equal"] = [x[0] for x in fused] == [x[0] for x in base]
+    R["agree_fused_vs_tp1"] = agree(fused, base)
+    R["agree_nccl_vs_tp1"] = agree(nccl, base)
+    R["agree_fused_vs_nccl"] = agree(fused, nccl)
+    R["native_equals_per_op"] = fused == per_op      # same kernels, same arguments: same bits
+    R["status"] = ops.read_status()
     # every rank must hold the same tokens
     same = comm.all_gather_object(fused)
-    results["engine_ranks_identical"] = all(s == same[0] for s in same)
-    return (results["engine_first_tokens_equal"] and results["engine_agree_fused_vs_tp1"] > 0.7
-            and results["engine_ranks_identical"] and results["engine_status"] == 0)
+    R["ranks_identical"] = all(s == same[0] for s in same)
+    results[f"engine_{tag}"] = R
+    return (R["first_tokens_equal"] and R["agree_fused_vs_tp1"] > 0.7 and R["native_equals_per_op"]
+            and R["ranks_identical"] and R["status"] == 0)
 
 
 def bench_block(comm, device, results):
@@ -189,6 +203,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--skip-engine", action="store_true")
+    ap.add_argument("--shapes", default="tiny-qwen3,tiny-moe",
+                    help="comma-separated model shapes for the engine check")
     args = ap.parse_args()
     rank, local_rank = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local_rank)
@@ -199,7 +215,8 @@ def main():
     results = {"world": comm.world}
     ok = check_primitives(comm, device, results)
     if not args.skip_engine:
-        ok = check_engine(comm, device, results, local_rank) and ok
+        for shape in [x for x in args.shapes.split(",") if x]:
+            ok = check_engine(comm, device, results, local_rank, shape) and ok
     if args.bench:
         bench_block(comm, device, results)
     flag = torch.tensor([1 if ok else 0], device=device)
