@@ -37,6 +37,8 @@ typedef struct B200TpGemm {
   const void* op_counter;      // local device word, bumped by b200_tp_reduce_norm_gather
   int out_f32;                 // gather mode: fp32 output (lm_head)
   int scatter_splits;          // scatter mode, M <= 256: k-splits, each its own source slot
+  int act_fuse;                // gather mode, M > 256: 0, or activation kind + 1 for the gated
+                               // epilogue (out[M, N / 2] = act(gate) * up, W rows interleaved)
 } B200TpGemm;
 
 int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,

@@ -4,6 +4,7 @@
 #include <cstdlib>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -67,6 +68,12 @@ bool pdl_enabled() {
   return on;
 }
 
+// Limit, in SM clock cycles, of the waits on another GPU's progress (the gather / scatter
+// counters of the fused tensor-parallel kernels). Process-wide; kernels take it as a parameter at
+// launch, so a change applies to the launches that follow.
+static std::atomic<long long> g_peer_wait_cycles{kPeerWaitCycles};
+long long peer_wait_cycles() { return g_peer_wait_cycles.load(std::memory_order_relaxed); }
+
 int* device_status_word() {
   static std::mutex mu;
   static std::unordered_map<int, int*> words;
@@ -111,6 +118,13 @@ int b200_read_status() {
 }
 
 void* b200_status_ptr() { return b200::device_status_word(); }
+
+// Sets the peer-wait limit (cycles; <= 0 restores the default of about 9 s) and returns the
+// previous one. Serving sets it from the step deadline; tests set it to about a millisecond to
+// make a wait on a counter that nothing raises run out.
+long long b200_set_peer_wait_cycles(long long cycles) {
+  return b200::g_peer_wait_cycles.exchange(cycles > 0 ? cycles : b200::kPeerWaitCycles);
+}
 
 const char* b200_kernel_arch() { return "sm_100a"; }
 

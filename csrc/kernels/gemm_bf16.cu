@@ -59,6 +59,7 @@ struct GemmParams {
   // gather prologue (all-gather + GEMM): A is this rank's copy of the gathered activations,
   // filled by peer stores; the producer waits until every row of a 32-row group has landed.
   const uint32_t* ag_flags;
+  long long peer_wait;            // limit of a wait on the gather counters, in cycles
   // The weight operand is not written by earlier work in the stream: its first ring stages may be
   // fetched before the wait on the predecessor kernel (programmatic dependent launch).
   int w_early;
@@ -83,14 +84,15 @@ struct GemmParams {
 };
 
 // Bounded system-scope acquire wait on a counter another GPU increments.
-__device__ __forceinline__ bool wait_counter_ge(const uint32_t* ctr, uint32_t target, int* status) {
+__device__ __forceinline__ bool wait_counter_ge(const uint32_t* ctr, uint32_t target, int* status,
+                                                long long limit) {
   long long t0 = clock64();
   uint32_t it = 0;
   while (true) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
     if (v >= target) return true;
-    if (((++it) & 0xff) == 0 && clock64() - t0 > kPeerWaitCycles) {
+    if (((++it) & 0xff) == 0 && clock64() - t0 > limit) {
       if (status) atomicExch(status, (int)kErrFlagTimeout);
       return false;
     }
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int g = tm * 4; g < tm * 4 + 4 && ok; ++g) {
             const int need = min(32, p.M - g * 32);
             if (need > 0)
-              ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g, need, p.status);
+              ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g, need, p.status, p.peer_wait);
           }
           if (!ok) break;
           fence_proxy_async_global();
@@ -596,6 +598,7 @@ __device__ long long g_gemm_timing[16];
 template <int BN, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                          const __grid_constant__ CUtensorMap tmA_alt,
                           const __grid_constant__ CUtensorMap tmB, GemmParams p) {
   constexpr int kBK = FP8 ? 128 : b200::kBK;          // elements per k-block (128 bytes per row)
   extern __shared__ uint8_t smem_raw[];
@@ -607,6 +610,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   constexpr uint32_t kTmemCols = 2 * BN;
   const int stages = p.stages;
   GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + (size_t)stages * kStageBytes);
+  // scatter epilogue: 4 KB per epilogue warp to turn "lane = row" accumulator chunks into row-
+  // contiguous 128-byte pieces before they cross NVLink
+  uint8_t* stage_smem = reinterpret_cast<uint8_t*>(bars) + ((sizeof(GemmBarriers) + 127) & ~size_t(127));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -642,7 +648,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       GT_ON(blockIdx.x == 0);
-      tma_prefetch_desc(&tmA);
+      // gather mode: A has one copy per parity of the op counter, pick the one just written
+      const CUtensorMap* ta = (p.ag_flags && ((*p.op_counter - 1) & 1)) ? &tmA_alt : &tmA;
+      tma_prefetch_desc(ta);
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
@@ -651,6 +659,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       while (ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1)) {
         int tm, tn;
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        if (p.ag_flags) {
+          // all-gather + GEMM: this CTA's 128 rows of the tile must have landed (four 32-row groups)
+          const uint32_t par = (*p.op_counter - 1) & 1;
+          const int g0 = (tm * 2 + (int)rank) * 4;
+          for (int g = g0; g < g0 + 4 && ok; ++g) {
+            const int need = min(32, p.M - g * 32);
+            if (need > 0)
+              ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g, need, p.status, p.peer_wait);
+          }
+          if (!ok) break;
+          fence_proxy_async_global();
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
@@ -667,7 +687,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #else
           if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
           const uint32_t leader_bar = mapa_u32(smem_u32(&bars->full[s]), 0);
-          tma_load_2d_pair(a_dst, &tmA, leader_bar, kb * kBK, tm * 2 * kBM + (int)rank * kBM);
+          tma_load_2d_pair(a_dst, ta, leader_bar, kb * kBK, tm * 2 * kBM + (int)rank * kBM);
           tma_load_2d_pair(b_dst, &tmB, leader_bar, kb * kBK, tn * BN + (int)rank * (BN / 2));
 #endif
         }
@@ -815,6 +835,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int col0 = tn * 128 + c * 32;
           if (row < p.M && col0 < (p.N >> 1)) epilogue_store_gated(p, g, u, row, col0);
         }
+      } else if (!FP8 && p.tp_world > 1 && p.peer_recv[0]) {
+        // GEMM + reduce-scatter: the bf16 partial rows go to the rank that owns them. Two 32-column
+        // accumulator chunks are staged in shared memory (16-byte pieces, XOR-swizzled by row so
+        // that neither side has bank conflicts) and leave as 128 contiguous bytes per row, eight
+        // lanes to a row, instead of 32 separate 16-byte pieces per store instruction.
+        uint8_t* st = stage_smem + (size_t)quarter * 4096;
+        const uint32_t par = *p.op_counter & 1;
+        const int row_base = tm * 2 * kBM + (int)rank * kBM + quarter * 32;
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v[32];
+            load_chunk(c2 * 2 + h, v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w;
+              w.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+              w.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+              w.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+              w.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+              const int piece = h * 4 + j;
+              *reinterpret_cast<uint4*>(st + lane * 128 + ((piece ^ (lane & 7)) << 4)) = w;
+            }
+          }
+          __syncwarp();
+          const int piece = lane & 7;
+          const int col = tn * BN + c2 * 64 + piece * 8;
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int rl = rr * 4 + (lane >> 3);
+            const int grow = row_base + rl;
+            if (grow < p.M && col < p.N) {
+              const uint4 w = *reinterpret_cast<const uint4*>(st + rl * 128 + ((piece ^ (rl & 7)) << 4));
+              const int owner = grow / p.rows_per_rank;
+              __nv_bfloat16* o = p.peer_recv[owner] + par * p.recv_parity_stride +
+                                 ((size_t)p.tp_rank * p.rows_per_rank + (grow - owner * p.rows_per_rank)) * p.N + col;
+              *reinterpret_cast<uint4*>(o) = w;
+            }
+          }
+          __syncwarp();
+        }
+        // this warp's 32 rows x BN columns are on their way to the owner: publish
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && row_base < p.M) {
+          const int owner = row_base / p.rows_per_rank;
+          signal_counter(p.peer_rs_flags[owner] + par * p.rs_flag_parity_stride +
+                         (row_base - owner * p.rows_per_rank) / 32);
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -913,7 +983,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t par = (*p.op_counter - 1) & 1;
         for (int g = 0; g * 32 < p.M && ag_ok; ++g)
           ag_ok = wait_counter_ge(p.ag_flags + par * p.ag_flag_parity_stride + g,
-                                  min(32, p.M - g * 32), p.status);
+                                  min(32, p.M - g * 32), p.status, p.peer_wait);
         fence_proxy_async_global();
       }
       for (int i = 0; i < nkb && ag_ok; ++i) {
@@ -1200,17 +1270,19 @@ static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUte
 
 // CTA-pair launch: clusters of two, as many as can be resident at once (at most one per SM pair).
 template <int BN, bool FP8 = false>
-static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p,
+static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB, GemmParams& p,
                        cudaStream_t stream) {
   constexpr int stage_bytes = kBM * 128 + (BN / 2) * 128;
   constexpr int kbk = FP8 ? 128 : kBK;
-  int stages = (kSmemBudget - 2048) / stage_bytes;
+  // the scatter epilogue stages its stores in 16 KB behind the barriers
+  const int epi_bytes = (p.tp_world > 1 && p.peer_recv[0]) ? 16384 + 128 : 0;
+  int stages = (kSmemBudget - 2048 - epi_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   int kblocks = (p.K + kbk - 1) / kbk;
   if (stages > kblocks + 1) stages = kblocks + 1;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
+  size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers) + epi_bytes;
   static int max_clusters[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1252,7 +1324,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
   }
   cfg.gridDim = dim3(2 * pairs);
   cfg.dynamicSmemBytes = smem;
-  if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN, FP8>, tmA, tmB, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN, FP8>, tmA, tmA2, tmB, p) != cudaSuccess) {
     cudaGetLastError();
     return -2;
   }
@@ -1262,6 +1334,14 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParam
 }  // namespace b200
 
 using namespace b200;
+
+static bool tp_pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B200_TP_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                           int out_f32, const void* bias, const void* residual, int ldr, int M,
@@ -1321,7 +1401,7 @@ extern "C" int b200_gemm_fp8_pair(const void* A, int lda, const void* W, int ldw
   if (!encode_tmap_2d(&tA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, lda, kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_tmap_2d(&tB, W, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldw, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return -3;
-  return launch_pair<256, true>(tA, tB, p, stream);
+  return launch_pair<256, true>(tA, tA, tB, p, stream);
 }
 
 // Same GEMM with the tensor-parallel prologue / epilogue described by `tp`.
@@ -1341,7 +1421,9 @@ extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw,
       s = (kblocks + kb_per - 1) / kb_per;      // the launcher's effective split count
       *expected_rs = tp->world * tiles_n * 4 * s;
     }
-    else {
+    else if (tp_pair_enabled()) {
+      *expected_rs = tp->world * (N > 128 ? (N + 255) / 256 : (N + 127) / 128);   // pair tiles
+    } else {
       // the tiled path picks BN below; mirror the choice
       const int sms = b200_num_sms();
       int tm = (M + 127) / 128, tn256 = (N + 255) / 256, tn128 = (N + 127) / 128;
@@ -1349,8 +1431,10 @@ extern "C" int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw,
       *expected_rs = tp->world * ((N >= 256 && w256 * 2 * 100 <= w128 * 135) ? tn256 : tn128);
     }
   }
+  // gather mode may fuse the gated activation (W rows in [128 gate | 128 up] blocks, out[M, N / 2])
+  const int act = (!swap && tp->gather && !tp->scatter && tp_pair_enabled()) ? tp->act_fuse : 0;
   return gemm_bf16_impl(A, lda, W, ldw, out, ldo, tp->scatter ? 0 : tp->out_f32, nullptr, nullptr,
-                        0, M, N, K, nullptr, 0, swap ? 2 : 1, tp, stream);
+                        0, M, N, K, nullptr, 0, swap ? 2 : 1, tp, stream, act);
 }
 
 static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
@@ -1361,7 +1445,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   // bit 8 of force_path: W is a constant weight (nothing in the stream writes it)
   const int w_early = (force_path >> 8) & 1;
   force_path &= 0xff;
-  if (act_fuse && (tp || M <= 128 || (N & 255) || bias || residual || out_f32)) return -1;
+  if (act_fuse && ((tp && tp->scatter) || M <= 128 || (N & 255) || bias || residual || out_f32)) return -1;
   if (act_fuse && force_path == 0) force_path = 9;      // the gated epilogue lives in the pair kernel
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ldo & 7) || (residual && (ldr & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W) |
@@ -1376,6 +1460,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
   p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   p.ldr = ldr;
   p.status = device_status_word();
+  p.peer_wait = peer_wait_cycles();
   if (tp) {
     p.tp_world = tp->world;
     p.tp_rank = tp->rank;
@@ -1504,23 +1589,28 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     const long rows256 = (long)((M + 255) / 256) * 256, rows128 = (long)((M + 127) / 128) * 128;
     if (rows256 * 100 > rows128 * 108) { force_path = 5; use256 = true; p.sk = 1; }
   }
-  const bool pair_path = !tp && (force_path == 0 || (force_path >= 7 && force_path <= 10));
+  // Tensor-parallel GEMMs above the small-M range run on CTA pairs as well (gather prologue,
+  // staged scatter epilogue); B200_TP_PAIR=0 keeps them on the 1-CTA tile.
+  const bool tp_pair = tp && force_path == 1 && M > 256 && tp_pair_enabled();
+  const bool pair_path = tp_pair || (!tp && (force_path == 0 || (force_path >= 7 && force_path <= 10)));
   if (act_fuse && !pair_path) return -1;
   p.act_fuse = act_fuse;
   if (pair_path) {
-    const bool bn256 = act_fuse || (force_path == 0 ? (N > 128) : (force_path == 7 || force_path == 9));
-    p.sk = (force_path == 0 || force_path >= 9) ? 1 : 0;
+    const bool bn256 = act_fuse || ((force_path == 0 || tp_pair) ? (N > 128) : (force_path == 7 || force_path == 9));
+    p.sk = (force_path == 0 || force_path >= 9 || tp_pair) ? 1 : 0;
     p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
-    CUtensorMap tA, tB;
+    CUtensorMap tA, tA2, tB;
     if (!get_tmap_bf16(&tA, A, M, K, lda, kBM, kBK)) return -3;
+    tA2 = tA;
+    if (tp && tp->gather && tp->a_alt && !get_tmap_bf16(&tA2, tp->a_alt, M, K, lda, kBM, kBK)) return -3;
     if (bn256) {
       p.tiles_n = tn256;
       if (!get_tmap_bf16(&tB, W, N, K, ldw, 128, kBK)) return -3;
-      return launch_pair<256>(tA, tB, p, stream);
+      return launch_pair<256>(tA, tA2, tB, p, stream);
     }
     p.tiles_n = tn128;
     if (!get_tmap_bf16(&tB, W, N, K, ldw, 64, kBK)) return -3;
-    return launch_pair<128>(tA, tB, p, stream);
+    return launch_pair<128>(tA, tA2, tB, p, stream);
   }
   CUtensorMap tmA, tmA2, tmB;
   if (!get_tmap_bf16(&tmA, A, M, K, lda, kBM, kBK)) return -3;

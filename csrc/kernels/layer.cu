@@ -220,8 +220,9 @@ struct TpIssue {
   long long recv_parity, x_parity;
   int rs_groups, ag_groups;
 
-  int gather_gemm(const void* W, int N, void* out, int ldo, int out_f32) const {
+  int gather_gemm(const void* W, int N, void* out, int ldo, int out_f32, int act_fuse = 0) const {
     B200TpGemm d{};
+    d.act_fuse = act_fuse;
     d.world = c->world; d.rank = c->rank; d.rows_per_rank = rpr;
     d.gather = 1;
     d.a_alt = reinterpret_cast<const __nv_bfloat16*>(c->x_full[c->rank]) + x_parity;
@@ -331,9 +332,14 @@ int b200_dense_layers_tp(const B200DenseLayerWeights* w, int num_layers, const B
     int expected = 0, nsrc = 0;
     B200_TRY(tp.scatter_gemm(s->attn, Hq * D, L->o, &expected, &nsrc));
     B200_TRY(tp.reduce(expected, nsrc, L->ln2));
-    B200_TRY(tp.gather_gemm(L->gate_up, 2 * I, s->gate_up_buf, 2 * I, 0));
-    B200_TRY(b200_act_and_mul(s->gate_up_buf, 2 * I, s->act, T, I,
-                              s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), stream));
+    if (s->gate_up_interleaved && T > 256 && ((2 * I) & 255) == 0) {
+      // the gated activation runs in the GEMM's epilogue (CTA-pair tiles hold gate and up halves)
+      B200_TRY(tp.gather_gemm(L->gate_up, 2 * I, s->act, I, 0, s->act_kind + 1));
+    } else {
+      B200_TRY(tp.gather_gemm(L->gate_up, 2 * I, s->gate_up_buf, 2 * I, 0));
+      B200_TRY(b200_act_and_mul(s->gate_up_buf, 2 * I, s->act, T, I,
+                                s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), stream));
+    }
     B200_TRY(tp.scatter_gemm(s->act, I, L->down, &expected, &nsrc));
     B200_TRY(tp.reduce(expected, nsrc, l + 1 < num_layers ? w[l + 1].ln1 : c->final_norm));
   }

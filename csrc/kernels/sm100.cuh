@@ -465,6 +465,7 @@ bool encode_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtyp
                     uint32_t b2, CUtensorMapSwizzle swizzle);
 // Process-wide device status word (lazily allocated per device).
 int* device_status_word();
+long long peer_wait_cycles();   // current limit of waits on other GPUs (b200_set_peer_wait_cycles)
 
 // ------------------------------------------------------------------------------------
 // Programmatic dependent launch. A kernel launched through launch_pdl() may become resident

@@ -46,16 +46,18 @@ struct ReduceNormParams {
   uint32_t* op_counter;               // local
   uint32_t* done_counter;             // local
   int* status;
+  long long peer_wait;                // limit of the wait on the arrival counters, in cycles
 };
 
-__device__ __forceinline__ bool wait_ge_sys(const uint32_t* ctr, uint32_t target, int* status) {
+__device__ __forceinline__ bool wait_ge_sys(const uint32_t* ctr, uint32_t target, int* status,
+                                            long long limit) {
   long long t0 = clock64();
   uint32_t it = 0;
   while (true) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
     if (v >= target) return true;
-    if (((++it) & 0xff) == 0 && clock64() - t0 > kPeerWaitCycles) {
+    if (((++it) & 0xff) == 0 && clock64() - t0 > limit) {
       if (status) atomicExch(status, (int)kErrFlagTimeout);
       return false;
     }
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(ReduceNormPa
   }
   if (threadIdx.x == 0) {
     s_ok = valid ? (wait_ge_sys(p.rs_flags + par * p.rs_flag_parity_stride + rl / 32,
-                                (uint32_t)p.expected_rs, p.status) ? 1 : 0)
+                                (uint32_t)p.expected_rs, p.status, p.peer_wait) ? 1 : 0)
                  : 1;
   }
   __syncthreads();
@@ -242,14 +244,14 @@ __global__ void __launch_bounds__(128)
     tp_gather_rows_kernel(const __nv_bfloat16* __restrict__ x_base, long long x_parity_stride,
                           int H, const int32_t* __restrict__ idx, const uint32_t* ag_flags,
                           int ag_flag_parity_stride, const uint32_t* op_counter, int M,
-                          __nv_bfloat16* out, int* status) {
+                          __nv_bfloat16* out, int* status, long long peer_wait) {
   __shared__ int s_ok;
   const uint32_t par = (*op_counter - 1) & 1;
   int src = idx[blockIdx.x];
   if (src < 0 || src >= M) src = 0;
   if (threadIdx.x == 0)
     s_ok = wait_ge_sys(ag_flags + par * ag_flag_parity_stride + src / 32,
-                       (uint32_t)min(32, M - (src / 32) * 32), status) ? 1 : 0;
+                       (uint32_t)min(32, M - (src / 32) * 32), status, peer_wait) ? 1 : 0;
   __syncthreads();
   if (!s_ok) return;
   const uint4* s = reinterpret_cast<const uint4*>(x_base + par * x_parity_stride + (size_t)src * H);
@@ -305,6 +307,7 @@ int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream) {
   p.ag_groups = a->ag_groups;
   p.op_counter = (uint32_t*)a->op_counter; p.done_counter = (uint32_t*)a->done_counter;
   p.status = device_status_word();
+  p.peer_wait = peer_wait_cycles();
   return launch_pdl(tp_reduce_norm_gather_kernel, dim3(a->rows_per_rank), dim3(256), (size_t)a->H * 2, stream,
                     p) == cudaSuccess ? 0 : -2;
 }
@@ -330,7 +333,7 @@ int b200_tp_gather_rows(const void* x_base, long long x_parity_stride, int H, co
   tp_gather_rows_kernel<<<n, 128, 0, stream>>>(
       (const __nv_bfloat16*)x_base, x_parity_stride, H, (const int32_t*)idx,
       (const uint32_t*)ag_flags, ag_flag_parity_stride, (const uint32_t*)op_counter, M,
-      (__nv_bfloat16*)out, device_status_word());
+      (__nv_bfloat16*)out, device_status_word(), peer_wait_cycles());
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -318,8 +318,11 @@ class DenseModel:
                          softcap=c.attn_logit_softcap, window=window)
             exp = tpf.gemm_scatter(attn, L["o"])
             tpf.reduce_norm_gather(T, exp, L["ln2"], eps, c.gemma_norm)
-            tpf.gemm_gather(T, L["gate_up"], gate_up)
-            be.act_and_mul(gate_up, act_kind, out=act, interleaved=self.gate_up_il)
+            if self.gate_up_il and T > 256 and (2 * self.inter) % 256 == 0:
+                tpf.gemm_gather(T, L["gate_up"], act, act_fuse=act_kind + 1)
+            else:
+                tpf.gemm_gather(T, L["gate_up"], gate_up)
+                be.act_and_mul(gate_up, act_kind, out=act, interleaved=self.gate_up_il)
             exp = tpf.gemm_scatter(act, L["down"])
             nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
             tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)

@@ -55,6 +55,7 @@ _SIGS = {
     "b200_num_sms": ([], I),
     "b200_read_status": ([], I),
     "b200_status_ptr": ([], P),
+    "b200_set_peer_wait_cycles": ([ctypes.c_longlong], ctypes.c_longlong),
     "b200_gemm_bf16": ([P, I, P, I, P, I, I, P, P, I, I, I, I, P, Z, I, P], I),
     "b200_rmsnorm": ([P, I, P, P, P, I, I, I, F, I, P], I),
     "b200_layernorm": ([P, P, P, P, I, I, F, P], I),
@@ -144,3 +145,23 @@ def stream_ptr() -> int:
 
 def ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
+
+
+class _DevPtr:
+    def __init__(self, p: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (p, False),
+                                         "version": 3, "strides": None}
+
+
+def device_view(p: int, nbytes: int, device) -> torch.Tensor:
+    """uint8 tensor over ``nbytes`` of device memory that the kernel library owns."""
+    return torch.as_tensor(_DevPtr(p, nbytes), device=device)
+
+
+def status_word(device) -> torch.Tensor:
+    """int32[1] view of the current device's kernel status word (non-zero after a bounded wait
+    inside a kernel ran out; see ``b200_read_status``)."""
+    p = lib().b200_status_ptr()
+    if not p:
+        raise KernelError("the kernel status word could not be allocated")
+    return device_view(p, 4, device).view(torch.int32)

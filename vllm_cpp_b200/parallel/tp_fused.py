@@ -33,7 +33,7 @@ class B200TpGemm(ctypes.Structure):
                 ("a_alt", ctypes.c_void_p),
                 ("ag_flags", ctypes.c_void_p), ("ag_flag_parity_stride", ctypes.c_int),
                 ("op_counter", ctypes.c_void_p), ("out_f32", ctypes.c_int),
-                ("scatter_splits", ctypes.c_int)]
+                ("scatter_splits", ctypes.c_int), ("act_fuse", ctypes.c_int)]
 
 
 class B200TpReduce(ctypes.Structure):
@@ -227,8 +227,11 @@ class TpFusedContext:
         a.done_counter = self._done_counter()
         check(lib().b200_tp_reduce_norm_gather(ctypes.byref(a), stream_ptr()), "tp_reduce")
 
-    def gemm_gather(self, T: int, w: torch.Tensor, out: torch.Tensor, wait: bool = True):
-        """``out = x_gathered @ w^T`` where the producer waits for the gathered rows tile by tile."""
+    def gemm_gather(self, T: int, w: torch.Tensor, out: torch.Tensor, wait: bool = True,
+                    act_fuse: int = 0):
+        """``out = x_gathered @ w^T`` where the producer waits for the gathered rows tile by tile.
+        ``act_fuse`` (activation kind + 1, T > 256 only): ``w`` holds [128 gate | 128 up] row blocks
+        and ``out[T, N / 2] = act(gate) * up`` comes out of the epilogue."""
         x = self._x_view[0][:T]      # parity-0 copy; the kernel switches to a_alt by device parity
         d = B200TpGemm()
         d.world, d.rank, d.rows_per_rank = self.world, self.rank, self.rows_per_rank(T)
@@ -238,6 +241,7 @@ class TpFusedContext:
         d.ag_flag_parity_stride = self.ag_groups
         d.op_counter = self._op_counter()
         d.out_f32 = 1 if out.dtype == torch.float32 else 0
+        d.act_fuse = act_fuse
         check(lib().b200_gemm_bf16_tp(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(out),
                                       out.stride(0), T, w.shape[0], x.shape[1], ctypes.byref(d),
                                       None, stream_ptr()), "gemm_gather")

@@ -47,8 +47,12 @@ def decode_graph_sizes(max_num_seqs: int) -> list[int]:
 class ModelRunner(E.ModelRunnerBase):
     def __init__(self, model, *, block_size: int, num_blocks: int, max_num_seqs: int,
                  max_num_batched_tokens: int, max_model_len: int, enable_cuda_graphs: bool = True,
-                 async_mode: bool = False, speculative_config=None):
+                 async_mode: bool = False, speculative_config=None, step_channel=None):
         super().__init__()
+        # Multi-rank serving: the rank that owns the scheduler publishes every step (the packed
+        # step buffer and what the sampler needs) on this channel; the other ranks run
+        # ``serve_steps`` and never see a request. None: this rank schedules for itself.
+        self.step_channel = step_channel
         # Speculative decoding, n-gram (prompt lookup) drafts verified by argmax comparison:
         # a request scheduled with k drafts runs k + 1 query tokens, gets k + 1 logits rows and
         # keeps the longest prefix of drafts that the target agrees with plus one more token.
@@ -112,6 +116,10 @@ class ModelRunner(E.ModelRunnerBase):
             from .. import ops
             self.ops = ops
             self.copy_stream = torch.cuda.Stream(device=self.device)
+            # the kernels' status word rides on every step's device->host copy of the sampled ids
+            from ..ops import _lib
+            self._status_dev = _lib.status_word(self.device)
+            self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
             Hq, Hkv, D = model.hq, model.hkv, model.D
             self._decode_tmp: dict[int, tuple] = {}
             self._Hq, self._Hkv, self._D = Hq, Hkv, D
@@ -354,28 +362,28 @@ class ModelRunner(E.ModelRunnerBase):
             return t if idx is None else t[idx].contiguous()
 
         dev = self.device
-        if grammar is not None and grammar.structured_output_request_ids:
-            rid = {info.req_ids[j]: info.logits_row0[j] for j in rows}
-            row_ids = torch.tensor([rid.get(r, -1) for r in grammar.structured_output_request_ids],
-                                   dtype=torch.int32, device=dev)
-            mask = torch.tensor(grammar.bitmask, dtype=torch.int32, device=dev).view(
-                len(grammar.structured_output_request_ids), grammar.words_per_row)
-            ops.apply_bitmask(logits, mask, row_ids)
-        br, btk, bv, nr, nt = self.batch.logit_edits(info, self._eos)
-        if br:
+        edits = self._pending_edits
+        if edits is None:
+            edits = self._host_sampler_edits(info, grammar)
+        if edits.get("grammar"):
+            row_ids, bitmask, words = edits["grammar"]
+            mask = torch.tensor(bitmask, dtype=torch.int32, device=dev).view(len(row_ids), words)
+            ops.apply_bitmask(logits, mask, torch.tensor(row_ids, dtype=torch.int32, device=dev))
+        if edits.get("bias"):
+            br, btk, bv = edits["bias"]
             ops.apply_logit_bias(logits, torch.tensor(br, dtype=torch.int32, device=dev),
                                  torch.tensor(btk, dtype=torch.int32, device=dev),
                                  torch.tensor(bv, dtype=torch.float32, device=dev))
-        if nr:
+        if edits.get("ban"):
+            nr, nt = edits["ban"]
             ops.apply_token_mask(logits, torch.tensor(nr, dtype=torch.int32, device=dev),
                                  torch.tensor(nt, dtype=torch.int32, device=dev))
-        if info.any_penalties:
-            pr, pt, pc = self.batch.penalty_entries(info)
-            if pr:
-                ops.apply_penalties(logits, torch.tensor(pr, dtype=torch.int32, device=dev),
-                                    torch.tensor(pt, dtype=torch.int32, device=dev),
-                                    torch.tensor(pc, dtype=torch.int32, device=dev),
-                                    per_row("rep_pen"), per_row("freq_pen"), per_row("pres_pen"))
+        if edits.get("penalties"):
+            pr, pt, pc = edits["penalties"]
+            ops.apply_penalties(logits, torch.tensor(pr, dtype=torch.int32, device=dev),
+                                torch.tensor(pt, dtype=torch.int32, device=dev),
+                                torch.tensor(pc, dtype=torch.int32, device=dev),
+                                per_row("rep_pen"), per_row("freq_pen"), per_row("pres_pen"))
         greedy = ops.argmax(logits, out=self.sampled[:n])
         if info.all_greedy:
             return greedy
@@ -389,6 +397,30 @@ class ModelRunner(E.ModelRunnerBase):
         rnd = ops.random_sample(probs, per_row("seeds"), per_row("steps"))
         out = ops.merge_greedy_random(greedy.clone(), rnd, temp, out=self.sampled[:n])
         return out
+
+    _pending_edits = None    # a worker rank: the sampler inputs the scheduling rank sent
+
+    def _host_sampler_edits(self, info, grammar) -> dict:
+        """Everything the sampler takes from host-side request state, as plain lists: grammar
+        bitmask rows, logit bias, banned tokens, penalty counts. Computed on the rank that owns
+        the requests; the other ranks receive it with the step."""
+        edits: dict = {}
+        rows = [i for i, p in enumerate(info.produces_token) if p]
+        if grammar is not None and grammar.structured_output_request_ids:
+            rid = {info.req_ids[j]: info.logits_row0[j] for j in rows}
+            edits["grammar"] = ([rid.get(r, -1) for r in grammar.structured_output_request_ids],
+                                list(grammar.bitmask), grammar.words_per_row)
+        if info.any_logit_edits:
+            br, btk, bv, nr, nt = self.batch.logit_edits(info, self._eos)
+            if br:
+                edits["bias"] = (list(br), list(btk), list(bv))
+            if nr:
+                edits["ban"] = (list(nr), list(nt))
+        if info.any_penalties:
+            pr, pt, pc = self.batch.penalty_entries(info)
+            if pr:
+                edits["penalties"] = (list(pr), list(pt), list(pc))
+        return edits
 
     def _sample_cpu(self, info, grammar) -> torch.Tensor:
         from ..sample import cpu_sampler
@@ -419,6 +451,17 @@ class ModelRunner(E.ModelRunnerBase):
                 out.append([lr])
             row += 1 + info.num_draft[r]
         return out
+
+    STATUS_NAMES = {1: "an mbarrier wait inside a kernel pipeline ran out",
+                    2: "a wait on another GPU's progress ran out (a peer rank is late or gone)",
+                    3: "a kernel rejected its arguments", 4: "misaligned shared memory"}
+
+    def _check_status(self, value: int) -> None:
+        """A kernel that gave up a bounded wait skipped its work: what was sampled in this step
+        is not to be trusted and peers may be out of step. The engine stops serving."""
+        if value != 0:
+            raise E.EngineDeadError(f"GPU kernel status {value}: {self.STATUS_NAMES.get(value, 'unknown error')}; "
+                                    "the step's output was discarded")
 
     def _mark_step_end(self) -> None:
         if self.time_steps and self.is_cuda and self.step_events and self.step_events[-1][1] is None:
@@ -480,8 +523,11 @@ class ModelRunner(E.ModelRunnerBase):
         self._mark_step_end()
         if self.is_cuda:
             self.sampled_host[:n].copy_(ids[:n], non_blocking=True)
+            self._status_host.copy_(self._status_dev, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            self._check_status(int(self._status_host[0]))
             host = self.sampled_host[:n].tolist()
+            self.d2h_bytes += 4
         else:
             host = ids[:n].tolist()
         self.d2h_bytes += n * 8
@@ -508,16 +554,19 @@ class ModelRunner(E.ModelRunnerBase):
                                                    ids.data_ptr(), n, _lib.stream_ptr()), "scatter")
         ev = torch.cuda.Event()
         host = torch.empty(n, dtype=torch.int64, pin_memory=True)
+        status = torch.empty(1, dtype=torch.int32, pin_memory=True)
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream())
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(ready)
             host.copy_(ids[:n], non_blocking=True)
+            status.copy_(self._status_dev, non_blocking=True)
             ev.record(self.copy_stream)
-        self.d2h_bytes += n * 8
+        self.d2h_bytes += n * 8 + 4
 
         def get():
             ev.synchronize()
+            self._check_status(int(status[0]))
             return self._build_output(info, host.tolist())
 
         return get
