@@ -220,3 +220,57 @@ def test_server_streaming(server):
     st, body = _req(port, "POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "count"}],
                                                            "max_tokens": 6, "temperature": 0})
     assert json.loads(body)["choices"][0]["message"]["content"] == text
+
+
+def test_server_with_tensor_parallel_workers(tmp_path):
+    """``--tensor-parallel-size 2``: this process is rank 0 (scheduler + HTTP), a child process is
+    rank 1 and only runs the published steps. Same completions as the single-rank server, and a
+    lost worker turns into EngineDeadError on the host instead of a hang. CPU ranks over gloo."""
+    import time
+
+    from vllm_cpp_b200 import _engine as E
+    from vllm_cpp_b200 import loader
+    from vllm_cpp_b200.config import EngineArgs, ParallelConfig, synthetic_config
+    from vllm_cpp_b200.entrypoints.api_server import ServerState, make_server
+    from vllm_cpp_b200.parallel.launch import launch_engine
+    d = loader.write_synthetic_checkpoint(str(tmp_path / "ck"), synthetic_config("tiny-qwen3"), seed=5)
+
+    def serve(tp):
+        args = EngineArgs(model=d, device="cpu", block_size=16, num_blocks=128, max_model_len=256, max_num_seqs=8,
+                          max_num_batched_tokens=128, parallel=ParallelConfig(tensor_parallel_size=tp))
+        llm, workers = launch_engine(args)
+        state = ServerState(llm, "tiny", tool_parser="hermes", default_max_tokens=8)
+        srv = make_server(state, "127.0.0.1", 0)
+        threading.Thread(target=srv.serve_forever, daemon=True).start()
+        return llm, workers, state, srv
+
+    body = {"prompt": "The quick brown", "max_tokens": 8, "temperature": 0}
+    llm1, _, st1, srv1 = serve(1)
+    want = json.loads(_req(srv1.server_address[1], "POST", "/v1/completions", body)[1])["choices"][0]["text"]
+    srv1.shutdown()
+    st1.engine.shutdown()
+
+    llm2, workers, st2, srv2 = serve(2)
+    try:
+        assert workers is not None and len(workers.procs) == 1
+        code, out = _req(srv2.server_address[1], "POST", "/v1/completions", body)
+        assert code == 200 and json.loads(out)["choices"][0]["text"] == want
+        # a sampled request exercises the sampler-input message to the worker
+        code, out = _req(srv2.server_address[1], "POST", "/v1/completions",
+                         {"prompt": "abc", "max_tokens": 4, "temperature": 0.7, "seed": 3, "presence_penalty": 0.5})
+        assert code == 200
+        # the worker dies between steps: the host notices, the next step raises
+        workers.procs[0].kill()
+        t0 = time.time()
+        while workers.failed is None and time.time() - t0 < 10:
+            time.sleep(0.1)
+        assert workers.failed and "rank 1" in workers.failed
+        llm2.add_request([1, 2, 3], E.SamplingParams(max_tokens=2))
+        with pytest.raises(E.EngineDeadError):
+            llm2.step()
+    finally:
+        srv2.shutdown()
+        st2.engine.shutdown()
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()

@@ -15,15 +15,15 @@ from . import _engine as E
 class EngineHandle:
     def __init__(self, params: dict):
         from .config import EngineArgs, ParallelConfig
-        from .engine import LLM
         from .entrypoints.api_server import ServerState
+        from .parallel.launch import launch_engine
         par = ParallelConfig(tensor_parallel_size=max(1, params.get("tensor_parallel_size") or 1),
                              enable_expert_parallel=bool(params.get("enable_expert_parallel")))
         args = EngineArgs(model=params["model_path"], tokenizer=params.get("tokenizer_config_path") or None,
                           block_size=params.get("block_size") or 32, num_blocks=params.get("num_blocks") or 256,
                           max_model_len=params.get("max_model_len") or 0, max_num_seqs=params.get("max_num_seqs") or 8,
                           device=params.get("device") or "cuda", parallel=par)
-        self.llm = LLM(args)
+        self.llm, _ = launch_engine(args)
         tool = params.get("tool_parser") or "auto"
         reason = params.get("reasoning_parser")
         self.state = ServerState(self.llm, params["model_path"], tool_parser=tool,

@@ -360,6 +360,10 @@ class ParallelConfig:
     rank: int = 0
     local_rank: int = 0
     fused_collectives: bool = True      # False => GEMM kernel + NCCL call (the baseline mode)
+    # True: rank 0 owns the scheduler and publishes every step to the other ranks, which run
+    # ``LLM.serve_as_worker()`` and never see a request (serving). False: every rank runs its own
+    # scheduler and must be fed identical requests (offline batches driven by one script per rank).
+    driver_worker: bool = False
 
     @property
     def world_size(self) -> int:

@@ -87,6 +87,11 @@ class LLM:
             self.model.quantize_weights("nvfp4")
         budget = args.resolve_max_num_batched_tokens(cfg)
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
+        if par.tensor_parallel_size > 1:
+            # every rank must size its cache alike: the scheduler counts one set of blocks
+            num_blocks = min(self.comm.all_gather_object(int(num_blocks)))
+        self.is_driver = par.rank == 0 or not par.driver_worker
+        channel = self._make_step_channel(par) if (par.driver_worker and par.tensor_parallel_size > 1) else None
         use_async = args.async_scheduling if args.async_scheduling is not None else False
         spec = args.speculative_config
         if spec is not None and spec.method == "ngram":
@@ -94,7 +99,7 @@ class LLM:
         self.runner = ModelRunner(self.model, block_size=args.block_size, num_blocks=num_blocks,
                                   max_num_seqs=args.max_num_seqs, max_num_batched_tokens=budget,
                                   max_model_len=max_len, enable_cuda_graphs=args.enable_cuda_graphs,
-                                  async_mode=use_async, speculative_config=spec)
+                                  async_mode=use_async, speculative_config=spec, step_channel=channel)
         sc = E.SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=args.max_num_seqs,
                                max_model_len=max_len, policy=args.scheduling_policy,
                                async_scheduling=use_async,
@@ -144,6 +149,34 @@ class LLM:
             return SingleComm()
         return TorchComm()
 
+    def _make_step_channel(self, par: ParallelConfig):
+        """What the scheduling rank publishes steps on: a host-side (gloo) group beside the NCCL
+        one, so that control messages never queue behind GPU work; a communicator handed in by
+        the caller (thread ranks in tests) serves as its own channel."""
+        from ..parallel.comm import TorchComm
+        if isinstance(self.comm, TorchComm):
+            import torch.distributed as dist
+            return TorchComm(dist.new_group(backend="gloo"))
+        return self.comm
+
+    def serve_as_worker(self) -> None:
+        """Rank > 0 of a ``driver_worker`` engine: run the steps rank 0 publishes until it stops."""
+        if self.is_driver:
+            raise RuntimeError("serve_as_worker() is for the ranks that own no scheduler")
+        self.runner.serve_steps()
+
+    workers = None     # parallel.launch.WorkerGroup when this process started the other ranks
+
+    def shutdown(self) -> None:
+        """Ends the worker ranks' loops (driver_worker engines); harmless otherwise."""
+        if self.is_driver and self.runner.step_channel is not None:
+            if self.workers is None or self.workers.failed is None:
+                self.runner.stop_workers()
+            self.runner.step_channel = None
+        if self.workers is not None:
+            self.workers.shutdown()
+            self.workers = None
+
     def _size_kv_cache(self, args: EngineArgs, budget: int, max_len: int) -> int:
         per_block = self.model.kv_bytes_per_block(args.block_size)
         if self.device.type != "cuda":
@@ -163,6 +196,8 @@ class LLM:
     def add_request(self, prompt_token_ids: Sequence[int], params: "E.SamplingParams",
                     request_id: Optional[str] = None, priority: int = 0,
                     prompt: Optional[str] = None) -> str:
+        if not self.is_driver:
+            raise RuntimeError("this rank owns no scheduler: requests go to rank 0")
         rid = request_id or f"req-{next(self._counter)}"
         toks = list(prompt_token_ids)
         if len(toks) >= self.max_model_len:
@@ -193,6 +228,9 @@ class LLM:
     def step(self) -> list[RequestOutput]:
         """One engine step; returns the requests that produced tokens (finished ones are
         flagged and dropped from the live table)."""
+        if self.workers is not None and self.workers.failed:
+            # a rank is gone: the next collective could never complete
+            raise E.EngineDeadError(f"tensor-parallel worker lost: {self.workers.failed}")
         outs, _ = self.core.step_with_batch_queue() if self.use_async else self.core.step()
         done = []
         for o in outs.outputs:

@@ -547,20 +547,25 @@ def build_arg_parser() -> argparse.ArgumentParser:
     ap.add_argument("--default-max-tokens", type=int, default=256)
     ap.add_argument("--api-key", default=None)
     ap.add_argument("--device", default="cuda")
-    ap.add_argument("--tensor-parallel-size", type=int, default=1)
+    ap.add_argument("--tensor-parallel-size", type=int, default=1,
+                    help="ranks (one process per GPU); this process is rank 0 and starts the others")
+    ap.add_argument("--enable-expert-parallel", action="store_true",
+                    help="MoE models: experts are split over the ranks instead of sharded")
     return ap
 
 
 def main(argv=None) -> int:
-    from ..config import EngineArgs
-    from ..engine import LLM
+    from ..config import EngineArgs, ParallelConfig
+    from ..parallel.launch import launch_engine
     a = build_arg_parser().parse_args(argv)
     kw = dict(model=a.model, tokenizer=a.tokenizer, device=a.device, block_size=a.block_size,
               max_num_seqs=a.max_num_seqs, max_model_len=a.max_model_len,
               max_num_batched_tokens=a.max_num_batched_tokens,
               gpu_memory_utilization=a.gpu_memory_utilization, async_scheduling=a.async_scheduling,
               enable_prefix_caching=a.enable_prefix_caching)
-    llm = LLM(EngineArgs(**{k: v for k, v in kw.items() if v is not None}))
+    kw["parallel"] = ParallelConfig(tensor_parallel_size=max(1, a.tensor_parallel_size),
+                                    enable_expert_parallel=a.enable_expert_parallel)
+    llm, _workers = launch_engine(EngineArgs(**{k: v for k, v in kw.items() if v is not None}))
     tpl = open(a.chat_template).read() if a.chat_template else None
     state = ServerState(llm, a.served_model_name or a.model, a.tool_call_parser, a.reasoning_parser, tpl,
                         a.default_max_tokens, a.api_key)

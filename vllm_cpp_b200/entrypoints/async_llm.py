@@ -88,6 +88,8 @@ class AsyncLLM:
         self._stop = True
         self._wake.set()
         self._thread.join(timeout=10)
+        if hasattr(self.llm, "shutdown"):
+            self.llm.shutdown()          # ends the worker ranks of a multi-rank engine
 
     # ------------------------------------------------------------------ engine thread
     def _deliver(self, st: RequestOutput) -> None:

@@ -17,7 +17,9 @@ from ..ops import reference as ref
 EPS = 1e-5
 
 
-def sample(runner, info, logits: torch.Tensor, grammar) -> torch.Tensor:
+def sample(runner, info, logits: torch.Tensor, edits: dict) -> torch.Tensor:
+    """``edits``: the host-side sampler inputs of the step as plain lists (grammar bitmask rows,
+    logit bias, banned tokens, penalty counts; see ``ModelRunner._host_sampler_edits``)."""
     n = info.num_logits
     logits = logits[:n].float().clone()
     rows = [i for i, p in enumerate(info.produces_token) if p]
@@ -29,22 +31,22 @@ def sample(runner, info, logits: torch.Tensor, grammar) -> torch.Tensor:
     def per_row(name):
         return v[name][: info.num_reqs][row_req]
 
-    if grammar is not None and grammar.structured_output_request_ids:
-        rid = {info.req_ids[j]: info.logits_row0[j] for j in rows}
-        words = grammar.words_per_row
-        mask = torch.tensor(grammar.bitmask, dtype=torch.int32).view(-1, words)
+    if edits.get("grammar"):
+        row_ids, bitmask, words = edits["grammar"]
+        mask = torch.tensor(bitmask, dtype=torch.int32).view(-1, words)
         V = logits.shape[1]
         bits = ((mask[:, :, None] >> torch.arange(32)) & 1).reshape(mask.shape[0], -1)[:, :V].bool()
-        for mi, r in enumerate(grammar.structured_output_request_ids):
-            if r in rid:
-                logits[rid[r]][~bits[mi]] = -math.inf
-    br, btk, bv, nr, nt = runner.batch.logit_edits(info, runner._eos)
-    for r, t, x in zip(br, btk, bv):
-        logits[r, t] += x
-    for r, t in zip(nr, nt):
-        logits[r, t] = -math.inf
-    if info.any_penalties:
-        pr, pt, pc = runner.batch.penalty_entries(info)
+        for mi, row in enumerate(row_ids):
+            if row >= 0:
+                logits[row][~bits[mi]] = -math.inf
+    if edits.get("bias"):
+        for r, t, x in zip(*edits["bias"]):
+            logits[r, t] += x
+    if edits.get("ban"):
+        for r, t in zip(*edits["ban"]):
+            logits[r, t] = -math.inf
+    if edits.get("penalties"):
+        pr, pt, pc = edits["penalties"]
         rep, freq, pres = per_row("rep_pen"), per_row("freq_pen"), per_row("pres_pen")
         for r, t, c in zip(pr, pt, pc):
             x = logits[r, t]

@@ -32,6 +32,17 @@ _DT = {"input_ids": (torch.int64, 8), "positions": (torch.int64, 8), "slot_mappi
        "sample_rows": (torch.int32, 4)}
 
 
+# StepInfo fields a rank needs to run a step it did not prepare itself
+STEP_INFO_FIELDS = ("num_reqs", "num_tokens", "num_decodes", "num_prefills", "num_prefill_tokens",
+                    "num_tiles", "max_query_len", "max_seq_len", "num_logits", "num_splice", "all_greedy",
+                    "any_penalties", "any_top_k_top_p", "any_min_p", "any_logprobs", "any_logit_edits",
+                    "req_ids", "produces_token", "max_logprobs", "num_draft", "logits_row0")
+
+
+def _plain(v):
+    return list(v) if isinstance(v, (list, tuple)) else v
+
+
 def decode_graph_sizes(max_num_seqs: int) -> list[int]:
     """Padded decode batch sizes that get a captured graph: 1,2,4,8,16,24,...,max."""
     sizes = [s for s in (1, 2, 4, 8) if s <= max_num_seqs]
@@ -305,6 +316,19 @@ class ModelRunner(E.ModelRunnerBase):
             hv["seq_lens"][R:pad].zero_()
             for g in range(self.num_groups):
                 hv["slot_mapping"][g][R:pad].fill_(-1)
+        if self.step_channel is not None:
+            # the other ranks run this step from the same packed buffer; they never see requests
+            self.step_channel.broadcast_object(
+                {"kind": "step", "pad": pad, "plain": plain_greedy,
+                 "info": {f: _plain(getattr(info, f)) for f in STEP_INFO_FIELDS},
+                 "buf": self.host_buf.numpy().tobytes()})
+        self._launch_step(info, pad, plain_greedy)
+
+    def _launch_step(self, info, pad, plain_greedy) -> None:
+        """Host->device copy of the packed step buffer, forward pass (graph replay for padded
+        decode-only batches). Runs on every rank; ``info`` is the StepInfo or its plain copy."""
+        R, T = info.num_reqs, info.num_tokens
+        self._step_plain = plain_greedy
         # one packed host->device copy per step
         if self.time_steps and self.is_cuda:
             e0 = torch.cuda.Event(enable_timing=True)
@@ -347,8 +371,14 @@ class ModelRunner(E.ModelRunnerBase):
         v = self.views
         if self._graph_sampled:
             return self.sampled[:n]
+        edits = self._pending_edits
+        if edits is None:
+            edits = self._host_sampler_edits(info, grammar)
+            if self.step_channel is not None and not self._step_plain:
+                self.step_channel.broadcast_object({"kind": "sample", "edits": edits})
         if not self.is_cuda:
-            return self._sample_cpu(info, grammar)
+            from ..sample import cpu_sampler
+            return cpu_sampler.sample(self, info, self._logits, edits)
         ops = self.ops
         # row-compacted per-request scalars (rows that sample are a subset of the batch)
         rows = [i for i, p in enumerate(info.produces_token) if p]
@@ -362,9 +392,6 @@ class ModelRunner(E.ModelRunnerBase):
             return t if idx is None else t[idx].contiguous()
 
         dev = self.device
-        edits = self._pending_edits
-        if edits is None:
-            edits = self._host_sampler_edits(info, grammar)
         if edits.get("grammar"):
             row_ids, bitmask, words = edits["grammar"]
             mask = torch.tensor(bitmask, dtype=torch.int32, device=dev).view(len(row_ids), words)
@@ -422,9 +449,53 @@ class ModelRunner(E.ModelRunnerBase):
                 edits["penalties"] = (list(pr), list(pt), list(pc))
         return edits
 
-    def _sample_cpu(self, info, grammar) -> torch.Tensor:
-        from ..sample import cpu_sampler
-        return cpu_sampler.sample(self, info, self._logits, grammar)
+    # ------------------------------------------------------------------ worker ranks
+    def serve_steps(self) -> None:
+        """Loop of a rank that owns no scheduler: run every step the scheduling rank publishes
+        (same packed buffer, same sampler inputs, so every rank samples the same ids and keeps
+        them on its device for the next step's input splice) until it says stop."""
+        import types
+        ch = self.step_channel
+        try:
+            while True:
+                msg = ch.broadcast_object(None)
+                if msg["kind"] == "stop":
+                    return
+                if msg["kind"] != "step":
+                    raise RuntimeError(f"worker rank: unexpected message {msg['kind']!r}")
+                info = types.SimpleNamespace(**msg["info"])
+                self._step_no += 1
+                k = self._step_no % len(self.host_bufs)
+                self.host_buf, self.host_views = self.host_bufs[k], self.host_views_all[k]
+                self.host_buf.numpy()[:] = np.frombuffer(msg["buf"], dtype=np.uint8)
+                self._info = info
+                self._launch_step(info, msg["pad"], msg["plain"])
+                n = info.num_logits
+                if n == 0:
+                    continue
+                if not msg["plain"]:
+                    m2 = ch.broadcast_object(None)
+                    if m2["kind"] != "sample":
+                        raise RuntimeError("worker rank: expected the sampler inputs of the step")
+                    self._pending_edits = m2["edits"]
+                try:
+                    ids = self._sample_device(info, None)
+                finally:
+                    self._pending_edits = None
+                if self.async_mode and self.is_cuda:
+                    from ..ops import _lib
+                    ids = ids.clone()
+                    _lib.check(_lib.lib().b200_scatter_sampled(
+                        self.last_sampled.data_ptr(), self.views["sample_rows"].data_ptr(), ids.data_ptr(), n,
+                        _lib.stream_ptr()), "scatter")
+        except BaseException:
+            if hasattr(ch, "abort"):
+                ch.abort()          # the other ranks' next collective raises instead of waiting
+            raise
+
+    def stop_workers(self) -> None:
+        if self.step_channel is not None:
+            self.step_channel.broadcast_object({"kind": "stop"})
 
     def _logprobs_rows(self, info, ids: torch.Tensor):
         if not info.any_logprobs:
