@@ -643,6 +643,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   cluster_sync_all();            // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();                 // predecessor grid complete, its writes visible
+  pdl_launch_dependents();    // the successor may become resident (it waits the same way)
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -1288,11 +1290,15 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return -2;
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: barriers, TMEM and the cluster handshake are set up while the
+  // predecessor drains; the kernel reads and writes nothing global before its pdl_wait()
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = kSmemBudget + 4096;
   cfg.stream = stream;
@@ -1324,6 +1330,7 @@ static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
   }
   cfg.gridDim = dim3(2 * pairs);
   cfg.dynamicSmemBytes = smem;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, gemm_bf16_pair_kernel<BN, FP8>, tmA, tmA2, tmB, p) != cudaSuccess) {
     cudaGetLastError();
     return -2;

@@ -186,17 +186,22 @@ def bench_block(comm, device, results):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t)
 
-        tf, tn = timeit(fused), timeit(nccl)
+        tf = timeit(fused)
+        st_fused = ops.read_status()
+        tn = timeit(nccl)
+        st_nccl = ops.read_status()
         flops = 2.0 * T * (I // W) * H + 2.0 * T * H * (2 * I // W)
         nv_bytes = 2.0 * T * H * 2 * (W - 1) / W          # scatter out + gather in, per rank
         roof_ms = max(flops / 1393e12, nv_bytes / 770e9) * 1e3
         rows.append(dict(T=T, fused_ms=tf, nccl_ms=tn, speedup=tn / tf, roofline_ms=roof_ms,
-                         frac_of_roofline=roof_ms / tf))
+                         frac_of_roofline=roof_ms / tf, nvlink_mb_per_rank=nv_bytes / 1e6,
+                         status_after_fused=st_fused, status_after_nccl=st_nccl))
         torch.cuda.synchronize()
         comm.barrier()
         tpf.close()
     results["block_bench"] = rows
-    results["block_bench_status"] = ops.read_status()
+    results["block_bench_status"] = max([ops.read_status()] + [max(r["status_after_fused"], r["status_after_nccl"])
+                                                               for r in rows])
 
 
 def main():
