@@ -44,6 +44,194 @@ typedef struct B200TpGemm {
 int b200_gemm_bf16_tp(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
                       int N, int K, const B200TpGemm* tp, int* expected_rs, cudaStream_t stream);
 
+// ---- argument structs of the multi-kernel entry points -----------------------------------
+// Weights of one layer (device pointers; q_norm / k_norm may be null).
+typedef struct B200DenseLayerWeights {
+  const void* ln1;
+  const void* qkv;        // [(Hq + 2 Hkv) D, H]
+  const void* q_norm;
+  const void* k_norm;
+  const void* o;          // [H, Hq D]
+  const void* ln2;
+  const void* gate_up;    // [2 I, H], interleaved in blocks of 128 if gate_up_interleaved
+  const void* down;       // [H, I]
+  void* kv_cache;         // [num_blocks, 2, block_size, Hkv, D]
+} B200DenseLayerWeights;
+
+// Shapes, step metadata (device pointers into the packed step buffer) and activation buffers.
+typedef struct B200DenseStep {
+  int T, H, Hq, Hkv, D, rot, inter, block_size;
+  int neox, gemma, act_kind, gate_up_interleaved;
+  float eps, scale, softcap;
+  int window;
+  long long num_blocks;
+  const void* positions;
+  const void* cos_sin;
+  const void* slot_mapping;
+  const void* block_table;
+  int max_blocks;
+  const void* seq_lens;
+  int num_decodes, decode_splits, decode_tc;
+  void* decode_tmp_o;
+  void* decode_tmp_lse;
+  int num_prefills, num_tiles, num_prefill_tokens;
+  const void* prefill_q_start;
+  const void* tile_req;
+  const void* tile_q0;
+  void* hidden;           // [T, H] in: previous block's output (or the embeddings); out: this block's
+  void* resid;            // [T, H] residual stream
+  void* normed;           // [T, H]
+  void* qkv_buf;          // [T, (Hq + 2 Hkv) D]
+  void* attn;             // [T, Hq D]
+  void* gate_up_buf;      // [T, 2 I]
+  void* act;              // [T, I]
+  void* gemm_ws;
+  unsigned long long gemm_ws_bytes;
+  int first_layer;        // the residual stream starts here: resid = hidden, no add
+} B200DenseStep;
+
+// Peer-mapped buffers of the fused tensor-parallel path (see tp_fused.cu): per rank a receive
+// buffer, a gathered-activation buffer and the counters, each with two parities.
+typedef struct B200TpLayers {
+  int world, rank;
+  int rpr_max;                 // capacity of a rank's row shard (multiple of 32)
+  int max_tokens;              // capacity of the gathered buffer (multiple of 32)
+  void* recv[8];               // [2][world * k-splits][rpr][H] bf16
+  void* rs_flags[8];           // [2][rpr_max / 32]
+  void* x_full[8];             // [2][max_tokens][H] bf16
+  void* ag_flags[8];           // [2][max_tokens / 32]
+  void* op_counter;            // local
+  void* done_counter;          // local
+  void* residual;              // local shard [rpr_max][H]
+  const void* final_norm;      // the norm after the last block
+} B200TpLayers;
+
+// Owner-side reduce of the fused tensor-parallel path (tp_fused.cu).
+typedef struct B200TpReduce {
+  int world, rank, rows_per_rank, M, H;
+  const void* recv;
+  long long recv_parity_stride;
+  void* rs_flags;
+  int rs_flag_parity_stride;
+  int expected_rs;
+  int nsrc;
+  void* residual;
+  const void* norm_w;
+  float eps;
+  int gemma;
+  void* peer_x[8];
+  long long x_parity_stride;
+  void* peer_ag_flags[8];
+  int ag_flag_parity_stride;
+  int ag_groups;
+  void* op_counter;
+  void* done_counter;
+} B200TpReduce;
+
+// Row-owner scatter of the MoE combine (moe.cu): the same receive slots and counters as the
+// scatter epilogue of the GEMM.
+typedef struct B200MoeScatter {
+  int world, rank, rows_per_rank;
+  void* peer_recv[8];
+  void* peer_rs_flags[8];
+  long long recv_parity_stride;
+  int rs_flag_parity_stride;
+  const void* op_counter;
+} B200MoeScatter;
+
+// ---- every other launcher, by source file ----------------------------------------------
+// ---- attn_decode.cu
+int b200_attn_decode_splits(int B, int Hkv, int G, int D, int max_seq_len);
+int b200_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kv_cache, int block_size, int Hq, int Hkv, int D, const void* block_table, int max_blocks, const void* seq_lens, int B, float scale, float softcap, int window, int splits, void* tmp_o, void* tmp_lse, cudaStream_t stream);
+int b200_attn_decode_merge(const void* tmp_o, const void* tmp_lse, void* out, int ldo, int B, int Hq, int D, int splits, cudaStream_t stream);
+int b200_merge_attn_states(const void* a, const void* lse_a, const void* b, const void* lse_b, void* out, void* lse_out, int T, int H, int D, cudaStream_t stream);
+// ---- attn_decode_tc.cu
+int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo, const void* kv_cache, int64_t num_blocks, int block_size, int Hq, int Hkv, int D, const void* block_table, int max_blocks, const void* seq_lens, int B, float scale, float softcap, int window, int splits, void* tmp_o, void* tmp_lse, cudaStream_t stream);
+// ---- attn_prefill.cu
+int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, void* lse, const void* kv_cache, int64_t num_blocks, int block_size, int Hq, int Hkv, int D, const void* block_table, int max_blocks, const void* seq_lens, const void* q_start, const void* tile_req, const void* tile_q0, int num_tiles, int total_q, float scale, float softcap, int window, int causal, cudaStream_t stream);
+// ---- common.cu
+long long b200_set_peer_wait_cycles(long long cycles);
+// ---- gdn.cu
+int b200_gdn_conv1d_fwd(const void* x, long ldx, const void* w, void* conv_state, const int* qsl, const int* slots, const int* has_init, void* out, long ldo, int n_seq, int total_tokens, int C, cudaStream_t stream);
+int b200_gdn_conv1d_update(const void* x, long ldx, const void* w, void* conv_state, const int* slots, void* out, long ldo, int B, int C, cudaStream_t stream);
+int b200_gdn_post_conv(const void* xc, long ld, int T, int Hk, int Hv, int Dk, const void* a, const void* b, long ldab, const float* A_log, const float* dt_bias, void* q_out, void* k_out, float* g, float* beta, float eps, cudaStream_t stream);
+int b200_gdn_packed_decode(const void* xc, long ld, const void* a, const void* b, long ldab, const float* A_log, const float* dt_bias, float* state, const int* slots, void* out, int B, int Hk, int Hv, int Dk, int Dv, float eps, cudaStream_t stream);
+int b200_rmsnorm_gated(const void* x, long ldx, const void* z, long ldz, const void* w, void* out, long ldo, long R, int D, float eps, int gate_kind, int heads, cudaStream_t stream);
+// ---- gdn_scan.cu
+int b200_gdn_chunk_scan(const void* q, const void* k, const void* v, long ldv, int v_col0, const float* g, const float* beta, int T, int Hk, int Hv, const int* chunk_tok0, const int* chunk_len, int NT, const int* seq_chunk0, const int* slots, const int* has_init, int n_seq, float* state, void* u, void* w, void* qs, void* pbuf, float* gc, void* out, cudaStream_t stream);
+// ---- gemm_bf16.cu
+int b200_gemm_bf16_gated(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int kind, int force_path, cudaStream_t stream);
+int b200_gemm_fp8_pair(const void* A, int lda, const void* W, int ldw, void* out, int ldo, const float* a_scale, const float* w_scale, int w_scale_per_channel, const void* bias, int M, int N, int K, cudaStream_t stream);
+int b200_gemm_bf16_batched(const void* A, int lda, int a_batch_cols, const void* W, int ldw, void* out, int ldo, long long out_batch_stride, int M, int N, int K, int batch, cudaStream_t stream);
+// ---- gemm_quant.cu
+int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int ldo, const float* a_scale, const float* w_scale, int w_scale_per_channel, const void* bias, int M, int N, int K, cudaStream_t stream);
+int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, void* out, long N, int K, cudaStream_t stream);
+int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int gemma, const float* scale, void* out, long ldo, long T, int H, cudaStream_t stream);
+int b200_quant_nvfp4(const void* x, long ldx, const float* gscale, void* out, void* sf, long T, int K, int mode, int swizzle, cudaStream_t stream);
+// ---- gemm_w4a16.cu
+int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out, int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes, cudaStream_t stream);
+// ---- layer.cu
+void b200_dense_layer_abi(int* out4);
+int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream);
+void b200_tp_layers_abi(int* out2);
+int b200_dense_layers_tp(const B200DenseLayerWeights* w, int num_layers, const B200DenseStep* s, const B200TpLayers* c, cudaStream_t stream);
+// ---- mla.cu
+int b200_mla_decode(const void* qabs, void* out, int ldo, const void* cache, int64_t num_blocks, int block_size, int Hq, const void* block_table, int max_blocks, const void* seq_lens, int B, float scale, int splits, void* tmp_o, void* tmp_lse, cudaStream_t stream);
+int b200_mla_gather_latent(const void* cache, const void* block_table, int max_blocks, const void* seq_lens, const void* dense_base, int block_size, void* dense, int num_reqs, int max_req_blocks, cudaStream_t stream);
+int b200_mla_assemble_kv(const void* kvb, const void* dense, void* cache, int N, int H, int block_size, cudaStream_t stream);
+int b200_mla_pad_q(const void* q, long ldq, void* out, int T, int H, cudaStream_t stream);
+int b200_mla_copy_qpe(const void* q, long ldq, void* qabs, int T, int H, cudaStream_t stream);
+// ---- moe.cu
+int b200_moe_router_topk(const void* logits_f32, int ld, int T, int E, int k, int renorm, int scoring, const void* e_bias, int n_group, int topk_group, float routed_scale, void* topk_ids, void* topk_w, cudaStream_t stream);
+int b200_moe_sort(const void* topk_ids, int T, int k, int e0, int e1, void* meta, void* sorted_token, void* pair_pos, void* chunk_expert, void* chunk_row0, void* chunk_n, int max_chunks, cudaStream_t stream);
+int b200_moe_gather(const void* x, int ldx, const void* sorted_token, const void* meta, int E, void* xs, int H, int max_rows, cudaStream_t stream);
+int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, int N, int K, void* out, const void* chunk_expert, const void* chunk_row0, const void* chunk_n, const void* meta, int max_chunks, cudaStream_t stream);
+int b200_moe_combine(const void* y, const void* pair_pos, const void* topk_w, int T, int k, int H, const void* shared, const void* shared_gate, void* out, const B200MoeScatter* sc, cudaStream_t stream);
+int b200_shared_gate(const void* x, int ldx, const void* w, int T, int H, void* out, cudaStream_t stream);
+// ---- norm_act.cu
+int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* out, int ldo, int T, int H, float eps, int gemma, cudaStream_t stream);
+int b200_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps, cudaStream_t stream);
+int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind, cudaStream_t stream);
+int b200_eltwise(const void* a, const void* b, void* out, size_t n, int kind, float scalar, cudaStream_t stream);
+int b200_cast_bf16_f32(const void* a, void* out, size_t n, cudaStream_t stream);
+int b200_cast_f32_bf16(const void* a, void* out, size_t n, cudaStream_t stream);
+int b200_embedding(const void* ids, const void* table, void* out, int T, int H, int64_t vocab_start, int64_t vocab_rows, int64_t vocab_total, float scale, cudaStream_t stream);
+int b200_gather_rows(const void* x, const void* idx, void* out, int n_out, int n_src, int row_bytes, cudaStream_t stream);
+// ---- rope_cache.cu
+int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_stride, int Hq, int Hkv, int D, int rot, const void* positions, const void* cos_sin, const void* q_norm_w, const void* k_norm_w, float eps, int gemma, int neox, const void* slot_mapping, void* kv_cache, int block_size, void* q_out, int T, cudaStream_t stream);
+int b200_reshape_and_cache(const void* k, int ldk, const void* v, int ldv, const void* slots, void* cache, int block_size, int Hkv, int D, int T, cudaStream_t stream);
+int b200_concat_and_cache_mla(const void* kv_c, int ldc, const void* k_pe, int ldr, const void* slots, void* cache, int Lc, int Lr, int T, cudaStream_t stream);
+int b200_rope_table(const void* inv_freq_f64, void* out_f32, int max_pos, int half, float mscale, cudaStream_t stream);
+// ---- sample.cu
+int b200_argmax_blocks_per_row(int n, int V);
+int b200_argmax(const void* logits, int ld, int n, int V, void* out_i64, void* scratch_f, void* scratch_i, cudaStream_t stream);
+int b200_argmax_candidates(const void* logits, int ld, int n, int V, int v_valid, int index_base, void* cand_out, void* scratch_f, void* scratch_i, cudaStream_t stream);
+int b200_argmax_combine(const void* cand, int n, int world, int V_total, void* out_i64, cudaStream_t stream);
+int b200_apply_temperature(void* logits, int ld, int n, int V, const void* temp, cudaStream_t stream);
+int b200_apply_penalties(void* logits, int ld, int V, const void* rows, const void* toks, const void* out_cnt, int n_entries, const void* rep, const void* freq, const void* pres, cudaStream_t stream);
+int b200_sparse_edit(void* logits, int ld, int V, const void* rows, const void* toks, const void* vals, int n_entries, int mode, cudaStream_t stream);
+int b200_apply_bitmask(void* logits, int ld, int V, const void* mask, int n_mask_rows, const void* row_ids, cudaStream_t stream);
+int b200_apply_min_p(void* logits, int ld, int n, int V, const void* min_p, cudaStream_t stream);
+int b200_apply_top_k_top_p(void* logits, int ld, int n, int V, const void* top_k, const void* top_p, cudaStream_t stream);
+int b200_softmax(const void* logits, int ld, void* out, int ldo, int n, int V, int log_mode, cudaStream_t stream);
+int b200_random_sample(const void* probs, int ld, int n, int V, const void* seeds, const void* steps, void* out_i64, cudaStream_t stream);
+int b200_merge_greedy_random(const void* g, const void* r, const void* temp, void* out, int n, cudaStream_t stream);
+int b200_token_rank(const void* logprobs, int ld, int n, int V, const void* toks, void* out_lp, void* out_rank, cudaStream_t stream);
+int b200_greedy_reject(const void* target_argmax, const void* draft, const void* cu_draft, int n, int max_spec, void* out, cudaStream_t stream);
+int b200_splice_sampled(void* input_ids, const void* dst_idx, const void* src_row, const void* last_sampled, int n, cudaStream_t stream);
+int b200_scatter_sampled(void* last_sampled, const void* row_of, const void* sampled, int n, cudaStream_t stream);
+uint64_t b200_splitmix64(uint64_t z);
+// ---- tp_fused.cu
+int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream);
+int b200_tp_first_norm(const void* hidden, void* residual_shard, const void* w, void* x_full, long long x_parity_stride, void* ag_flags, int ag_flag_parity_stride, int ag_groups, void* rs_flags, int rs_flag_parity_stride, int rank, int rows_per_rank, int M, int H, float eps, int gemma, void* op_counter, void* done_counter, cudaStream_t stream);
+int b200_tp_gather_rows(const void* x_base, long long x_parity_stride, int H, const void* idx, int n, const void* ag_flags, int ag_flag_parity_stride, const void* op_counter, int M, void* out, cudaStream_t stream);
+void* b200_symm_alloc(size_t bytes);
+int b200_symm_free(void* p);
+int b200_ipc_get_handle(void* p, void* out64);
+void* b200_ipc_open(const void* handle64);
+int b200_ipc_close(void* p);
+int b200_memset_async(void* p, int v, size_t bytes, cudaStream_t stream);
+
 // ---- small-M GEMM that allocates nothing ------------------------------------------------
 // This entry point has no counterpart in the reference project. It exists for callers that
 // need a decode-sized GEMM (M <= 256) but may not allocate at that point: a plug-in inside

@@ -83,17 +83,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-#ifdef B200_DECODE_TIMING
-// Instrumented build only: cycles that each role of CTA (0,0,0) spends in its waits.
-__device__ long long g_decode_timing[32];
-#define DT_DECL long long dt_t0 = 0; const bool dt_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0
-#define DT_BEGIN() do { if (dt_on) dt_t0 = clock64(); } while (0)
-#define DT_END(slot) do { if (dt_on) g_decode_timing[slot] += clock64() - dt_t0; } while (0)
-#else
-#define DT_DECL
-#define DT_BEGIN() do {} while (0)
-#define DT_END(slot) do {} while (0)
-#endif
 
 // GP: the GQA group size rounded up to 4 / 8 / 16; the softmax only touches those columns of
 // S^T (the MMA's N stays 16, its minimum at 128 rows).
@@ -173,10 +162,6 @@ __global__ void __launch_bounds__(192, 2)
         const int rows_per_load = min(p.block_size, kTok);
         const int loads = kTok / rows_per_load;
         bool ok = true;
-        DT_DECL;
-#ifdef B200_DECODE_TIMING
-        const long long dt_tot0 = clock64();
-#endif
         // Load order K0 K1 V0 K2 V1 K3 ... V(n-1): exactly the order in which the MMA warp
         // consumes the tiles, with K running one tile further ahead than V (a V slot is held
         // until the softmax of its tile is done; K slots turn over as soon as QK has run).
@@ -190,9 +175,7 @@ __global__ void __launch_bounds__(192, 2)
           const int tok0 = tok_base + j * kTok;
           const int sl = sq % kSlots;
           const uint32_t ph = (sq / kSlots) & 1;
-          DT_BEGIN();
           if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; break; }
-          DT_END(1);
           uint8_t* dst = sKV + sl * kSlotBytes;
           mbar_expect_tx(&bars->kv_full[sl], kSlotBytes);
           for (int l = 0; l < loads; ++l) {
@@ -205,34 +188,21 @@ __global__ void __launch_bounds__(192, 2)
                         row);
           }
         }
-#ifdef B200_DECODE_TIMING
-        if (dt_on) g_decode_timing[0] += clock64() - dt_tot0;
-#endif
       }
     } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_qk = umma_idesc_bf16(kTok, kNQ, 0, 0);
         constexpr uint32_t idesc_pv = umma_idesc_bf16(D, kNQ, 1, 0);  // A (V^T) is MN-major
-        DT_DECL;
-#ifdef B200_DECODE_TIMING
-        const long long dt_tot0 = clock64();
-#endif
-        DT_BEGIN();
         bool ok = mbar_wait(&bars->q_full, 0, p.status);
-        DT_END(3);
         const uint32_t q_addr = smem_u32(sQ);
         for (int j = 0; j <= ntiles && ok; ++j) {
           if (j < ntiles) {
             const int it = j == 0 ? 0 : 2 * j - 1, sl = it % kSlots;     // K(j) in load order
             const uint32_t ph = (it / kSlots) & 1;
             const int sb = j & 1;
-            DT_BEGIN();
             if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
-            DT_END(4);
-            DT_BEGIN();
             if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
-            DT_END(5);
             tc_fence_after_sync();
             const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -250,12 +220,8 @@ __global__ void __launch_bounds__(192, 2)
             const int it = i == ntiles - 1 ? 2 * ntiles - 1 : 2 * i + 2, sl = it % kSlots;  // V(i)
             const uint32_t ph = (it / kSlots) & 1;
             const int pb = i & 1;
-            DT_BEGIN();
             if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
-            DT_END(6);
-            DT_BEGIN();
             if (!mbar_wait(&bars->p_full[pb], (i >> 1) & 1, p.status)) { ok = false; break; }
-            DT_END(7);
             tc_fence_after_sync();
             const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
             const uint32_t p_addr = smem_u32(sP + pb * 4096);
@@ -270,9 +236,6 @@ __global__ void __launch_bounds__(192, 2)
             umma_commit(&bars->p_empty[pb]);
           }
         }
-#ifdef B200_DECODE_TIMING
-        if (dt_on) g_decode_timing[2] += clock64() - dt_tot0;
-#endif
       }
     } else {
       // ---------------- softmax / correction: thread t owns token t of the tile ----------------
@@ -285,18 +248,10 @@ __global__ void __launch_bounds__(192, 2)
       const bool capped = p.softcap2 > 0.f;
       bool ok = true;
       uint32_t gphase = 0;
-#ifdef B200_DECODE_TIMING
-      long long dt_t0 = 0;
-      const bool dt_on = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && warp == 2 && lane == 0;
-      const long long dt_tot0 = clock64();
-#endif
       for (int j = 0; j < ntiles && ok; ++j) {
         const int sb = j & 1;
-        DT_BEGIN();
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (j >> 1) & 1, p.status));
-        DT_END(9);
         if (!ok) break;
-        DT_BEGIN();
         tc_fence_after_sync();
         uint32_t r[16];
         tmem_ld_32x32b_x16(tmem_s + sb * 16 + lane_off, r);
@@ -304,8 +259,6 @@ __global__ void __launch_bounds__(192, 2)
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
-        DT_END(13);
-        DT_BEGIN();
         const int tok = tok_base + j * kTok + t;
         const bool valid = tok < seq_len && tok >= begin;
         float s[GP];
@@ -325,12 +278,8 @@ __global__ void __launch_bounds__(192, 2)
             for (int g = 0; g < GP; ++g) bars->red_max[sb][quarter][g] = wm[g];
           }
         }
-        DT_END(14);
-        DT_BEGIN();
         ok = softmax_group_sync(&bars->grp, gphase, lane, p.status);
-        DT_END(10);
         if (!ok) break;
-        DT_BEGIN();
         bool rescale = false;
         float alpha[GP];
 #pragma unroll
@@ -350,12 +299,8 @@ __global__ void __launch_bounds__(192, 2)
         // pv_done can lag: it has completed at least j-1 times here, so the parity wait of the
         // rescale below (its j-th completion) cannot be satisfied by an older phase.
         const int pb = j & 1;
-        DT_END(16);
-        DT_BEGIN();
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty[pb], ((j >> 1) & 1) ^ 1, p.status));
-        DT_END(11);
         if (!ok) break;
-        DT_BEGIN();
         if (rescale && j > 0) {
           // all PV products issued so far must have landed before O^T is rescaled in place
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
@@ -383,15 +328,11 @@ __global__ void __launch_bounds__(192, 2)
                                               (c & 7) * 2) = pb16;
           }
         }
-        DT_END(15);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full[pb]);
       }
-#ifdef B200_DECODE_TIMING
-      if (dt_on) g_decode_timing[8] += clock64() - dt_tot0;
-#endif
       // ---------------- epilogue: O^T / l ----------------
       // pv_done completes once per tile and the loop only guarantees ntiles-2 completions seen
       // (through p_empty), so observe the last two in order: a parity wait two phases ahead
@@ -468,16 +409,6 @@ struct DKeyHash {
 
 using namespace b200;
 
-#ifdef B200_DECODE_TIMING
-extern "C" int b200_decode_timing_read(long long* host32, int reset) {
-  if (cudaMemcpyFromSymbol(host32, g_decode_timing, sizeof(long long) * 32) != cudaSuccess) return -1;
-  if (reset) {
-    long long z[32] = {0};
-    if (cudaMemcpyToSymbol(g_decode_timing, z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
 
 // The merge kernel of the CUDA-core path (attn_decode.cu) combines the split partials.
 extern "C" int b200_attn_decode_merge(const void* tmp_o, const void* tmp_lse, void* out, int ldo,

@@ -66,17 +66,6 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
-#ifdef B200_PREFILL_TIMING
-// Instrumented build only: cycles that the roles of one CTA (the last tile, head 0) spend per phase.
-__device__ long long g_prefill_timing[32];
-#define PT_ON(cond) const bool pt_on = (cond); long long pt_t0 = 0
-#define PT_BEGIN() do { if (pt_on) pt_t0 = clock64(); } while (0)
-#define PT_END(slot) do { if (pt_on) g_prefill_timing[slot] += clock64() - pt_t0; } while (0)
-#else
-#define PT_ON(cond)
-#define PT_BEGIN() do {} while (0)
-#define PT_END(slot) do {} while (0)
-#endif
 
 // D = 256 keeps two softmax threads per query row (warps w and w + 4 share a TMEM lane
 // quarter): both reduce the full score row, each writes half of P and owns half of O.
@@ -188,18 +177,13 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kQT, kKT, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kQT, D, 0, 1);  // B (V) is MN-major
-      PT_ON(blockIdx.x == gridDim.x - 1 && blockIdx.y == 0);
       bool ok = mbar_wait(&bars->q_full, 0, p.status);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       for (int j = 0; j <= ntiles && ok; ++j) {
         if (j < ntiles) {
           const int it = j == 0 ? 0 : 2 * j - 1, sl = it % kRing, sb = j & 1;   // K(j) in load order
-          PT_BEGIN();
           if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
-          PT_END(0);
-          PT_BEGIN();
           if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
-          PT_END(1);
           tc_fence_after_sync();
           const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -215,12 +199,8 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         if (j >= 1) {
           const int i = j - 1;
           const int it = i == ntiles - 1 ? 2 * ntiles - 1 : 2 * i + 2, sl = it % kRing;       // V(i)
-          PT_BEGIN();
           if (!mbar_wait(&bars->kv_full[sl], (it / kRing) & 1, p.status)) { ok = false; break; }
-          PT_END(2);
-          PT_BEGIN();
           if (!mbar_wait(&bars->p_full, i & 1, p.status)) { ok = false; break; }
-          PT_END(3);
           tc_fence_after_sync();
           const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
@@ -254,17 +234,10 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     uint8_t* prow = sP + r * 128;
-    PT_ON(blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && warp == 2 && lane == 0);
-#ifdef B200_PREFILL_TIMING
-    const long long pt_tot0 = clock64();
-#endif
     for (int j = 0; j < ntiles && ok; ++j) {
       const int sb = j & 1;
-      PT_BEGIN();
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[sb], (j >> 1) & 1, p.status));
-      PT_END(8);
       if (!ok) break;
-      PT_BEGIN();
       tc_fence_after_sync();
       const int kbase = (kt0 + j) * kKT;
       const uint32_t s_addr = tmem_s0 + sb * kKT + lane_off;
@@ -276,8 +249,6 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->s_empty[sb]);   // S is in registers now
-      PT_END(9);
-      PT_BEGIN();
       // scaled scores (log2 domain), soft-cap, mask
       if (cap || need_mask) {
 #pragma unroll
@@ -317,13 +288,9 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         m = tile_max;
       }
       const float m_use = (m == -INFINITY) ? 0.f : m;
-      PT_END(10);
-      PT_BEGIN();
       // PV of tile j-1 has completed: the P buffer is free and O holds every product so far
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->p_empty, (j & 1) ^ 1, p.status));
-      PT_END(11);
       if (!ok) break;
-      PT_BEGIN();
       if (__any_sync(0xffffffffu, rescale)) {
         tc_fence_after_sync();
 #pragma unroll
@@ -337,8 +304,6 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
         }
         tmem_st_wait();
       }
-      PT_END(14);
-      PT_BEGIN();
       float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {     // 8 chunks of 8 columns = 16 bytes each
@@ -361,11 +326,7 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
-      PT_END(12);
     }
-#ifdef B200_PREFILL_TIMING
-    if (pt_on) { g_prefill_timing[15] += clock64() - pt_tot0; g_prefill_timing[16] += ntiles; }
-#endif
     if (ok && ntiles > 0) {
       // o_full completes once per PV; p_empty of the last iteration showed PV(ntiles-2) complete,
       // so this parity wait can only be satisfied by the last product
@@ -445,16 +406,6 @@ static int launch_prefill(const CUtensorMap& tmQ, const CUtensorMap& tmKV, const
 
 using namespace b200;
 
-#ifdef B200_PREFILL_TIMING
-extern "C" int b200_prefill_timing_read(long long* host32, int reset) {
-  if (cudaMemcpyFromSymbol(host32, g_prefill_timing, sizeof(long long) * 32) != cudaSuccess) return -1;
-  if (reset) {
-    long long z[32] = {0};
-    if (cudaMemcpyToSymbol(g_prefill_timing, z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
 
 extern "C" int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, void* lse,
                                  const void* kv_cache, int64_t num_blocks, int block_size, int Hq,

@@ -581,19 +581,6 @@ __device__ __forceinline__ void epilogue_store_gated(const GemmParams& p, const 
 
 // FP8 = false: bf16 operands, 64 elements per 128-byte smem row. FP8 = true: e4m3 operands
 // (kind::f8f6f4), 128 elements per row; everything else (tiles, rings, stream-K) is shared.
-#ifdef B200_GEMM_TIMING
-// Instrumented build only: cycles the roles of the first CTA pair spend waiting.
-__device__ long long g_gemm_timing[16];
-#define GT_ON(cond) const bool gt_on = (cond); long long gt_t0 = 0
-#define GT_BEGIN() do { if (gt_on) gt_t0 = clock64(); } while (0)
-#define GT_END(slot) do { if (gt_on) g_gemm_timing[slot] += clock64() - gt_t0; } while (0)
-#define GT_ADD(slot, v) do { if (gt_on) g_gemm_timing[slot] += (v); } while (0)
-#else
-#define GT_ON(cond)
-#define GT_BEGIN() do {} while (0)
-#define GT_END(slot) do {} while (0)
-#define GT_ADD(slot, v) do {} while (0)
-#endif
 
 template <int BN, bool FP8 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -649,7 +636,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
-      GT_ON(blockIdx.x == 0);
       // gather mode: A has one copy per parity of the op counter, pick the one just written
       const CUtensorMap* ta = (p.ag_flags && ((*p.op_counter - 1) & 1)) ? &tmA_alt : &tmA;
       tma_prefetch_desc(ta);
@@ -676,22 +662,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
-          GT_BEGIN();
           if (!mbar_wait(&bars->empty[s], ph ^ 1, p.status)) { ok = false; break; }
-          GT_END(4);
           uint8_t* a_dst = smem + (size_t)s * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
-#ifdef B200_GEMM_EXP_NOLOAD
-          // experiment (instrumented builds only): no operand traffic, the MMAs read whatever is in
-          // shared memory; isolates the tensor pipe's own rate from the TMA writes
-          (void)a_dst; (void)b_dst;
-          if (rank == 0) mbar_arrive(&bars->full[s]);
-#else
           if (rank == 0) mbar_expect_tx(&bars->full[s], 2 * kStageBytes);
           const uint32_t leader_bar = mapa_u32(smem_u32(&bars->full[s]), 0);
           tma_load_2d_pair(a_dst, ta, leader_bar, kb * kBK, tm * 2 * kBM + (int)rank * kBM);
           tma_load_2d_pair(b_dst, &tmB, leader_bar, kb * kBK, tn * BN + (int)rank * (BN / 2));
-#endif
         }
       }
       if (!ok) bars->failed = 1;
@@ -702,27 +679,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       constexpr uint32_t idesc = FP8 ? umma_idesc_e4m3(2 * kBM, BN) : umma_idesc_bf16(2 * kBM, BN);
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      GT_ON(blockIdx.x == 0);
-#ifdef B200_GEMM_TIMING
-      const long long gt_tot0 = clock64();
-#endif
       SegState seg = seg_init_w(p, kblocks, pair, npairs);
       int t, kb0, kb1;
       for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
         int buf = tc & 1;
         uint32_t aph = (tc >> 1) & 1;
-        GT_BEGIN();
         if (!mbar_wait(&bars->acc_empty[buf], aph ^ 1, p.status)) { ok = false; break; }
-        GT_END(0);
         tc_fence_after_sync();
         uint32_t d_tmem = tmem_base + buf * BN;
-        GT_ADD(3, kb1 - kb0);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           int s = it % stages;
           uint32_t ph = (it / stages) & 1;
-          GT_BEGIN();
           if (!mbar_wait(&bars->full[s], ph, p.status)) { ok = false; break; }
-          GT_END(1);
           tc_fence_after_sync();
           uint32_t a_addr = smem_u32(smem + (size_t)s * kStageBytes);
           uint32_t b_addr = a_addr + kABytes;
@@ -737,9 +705,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         if (ok) umma_commit_pair(&bars->acc_full[buf], 3);
       }
-#ifdef B200_GEMM_TIMING
-      if (gt_on) g_gemm_timing[2] += clock64() - gt_tot0;
-#endif
       if (!ok) bars->failed = 1;
     }
   } else {
@@ -748,10 +713,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int me = blockIdx.x;                        // partial slot / flag owner
     uint32_t tc = 0;
     bool ok = true;
-    GT_ON(blockIdx.x == 0 && warp == 2 && lane == 0);
-#ifdef B200_GEMM_TIMING
-    const long long gt_tot0 = clock64();
-#endif
     SegState seg = seg_init_w(p, kblocks, pair, npairs);
     int t, kb0, kb1;
     for (; ok && seg_next(seg, num_tiles, kblocks, t, kb0, kb1); ++tc) {
@@ -759,12 +720,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       int buf = tc & 1;
       uint32_t aph = (tc >> 1) & 1;
-      GT_BEGIN();
       ok = mbar_wait(&bars->acc_full[buf], aph, p.status);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      GT_END(6);
-      GT_ADD(8, 1);
       tc_fence_after_sync();
       const int row = tm * 2 * kBM + (int)rank * kBM + quarter * 32 + lane;
       const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
@@ -903,9 +861,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         mbar_arrive_cluster(leader_acc_empty);
       }
     }
-#ifdef B200_GEMM_TIMING
-    if (gt_on) g_gemm_timing[7] += clock64() - gt_tot0;
-#endif
   }
 
   tc_fence_before_sync();
@@ -1355,16 +1310,6 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
                           int N, int K, void* workspace, size_t ws_bytes, int force_path,
                           const B200TpGemm* tp, cudaStream_t stream, int act_fuse = 0);
 
-#ifdef B200_GEMM_TIMING
-extern "C" int b200_gemm_timing_read(long long* host16, int reset) {
-  if (cudaMemcpyFromSymbol(host16, b200::g_gemm_timing, sizeof(long long) * 16) != cudaSuccess) return -1;
-  if (reset) {
-    long long z[16] = {0};
-    if (cudaMemcpyToSymbol(b200::g_gemm_timing, z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return 0;
-}
-#endif
 
 extern "C" int b200_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* out, int ldo,
                               int out_f32, const void* bias, const void* residual, int ldr, int M,

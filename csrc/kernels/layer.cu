@@ -16,76 +16,6 @@
 
 extern "C" {
 
-int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* out, int ldo, int T,
-                 int H, float eps, int gemma, cudaStream_t stream);
-int b200_rope_kv(void* qkv, int ld, int q_off, int k_off, int v_off, int q_head_stride, int Hq,
-                 int Hkv, int D, int rot, const void* positions, const void* cos_sin,
-                 const void* q_norm_w, const void* k_norm_w, float eps, int gemma, int neox,
-                 const void* slot_mapping, void* kv_cache, int block_size, void* q_out, int T,
-                 cudaStream_t stream);
-int b200_attn_prefill(const void* q, int ldq, void* out, int ldo, void* lse, const void* kv_cache,
-                      int64_t num_blocks, int block_size, int Hq, int Hkv, int D, const void* block_table,
-                      int max_blocks, const void* seq_lens, const void* q_start, const void* tile_req,
-                      const void* tile_q0, int num_tiles, int total_q, float scale, float softcap,
-                      int window, int causal, cudaStream_t stream);
-int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo, const void* kv_cache,
-                        int64_t num_blocks, int block_size, int Hq, int Hkv, int D,
-                        const void* block_table, int max_blocks, const void* seq_lens, int B,
-                        float scale, float softcap, int window, int splits, void* tmp_o, void* tmp_lse,
-                        cudaStream_t stream);
-int b200_attn_decode(const void* q, int ldq, void* out, int ldo, const void* kv_cache, int block_size,
-                     int Hq, int Hkv, int D, const void* block_table, int max_blocks,
-                     const void* seq_lens, int B, float scale, float softcap, int window, int splits,
-                     void* tmp_o, void* tmp_lse, cudaStream_t stream);
-int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind, cudaStream_t stream);
-int b200_gemm_bf16_gated(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
-                         int N, int K, int kind, int force_path, cudaStream_t stream);
-
-// Weights of one layer (device pointers; q_norm / k_norm may be null).
-typedef struct B200DenseLayerWeights {
-  const void* ln1;
-  const void* qkv;        // [(Hq + 2 Hkv) D, H]
-  const void* q_norm;
-  const void* k_norm;
-  const void* o;          // [H, Hq D]
-  const void* ln2;
-  const void* gate_up;    // [2 I, H], interleaved in blocks of 128 if gate_up_interleaved
-  const void* down;       // [H, I]
-  void* kv_cache;         // [num_blocks, 2, block_size, Hkv, D]
-} B200DenseLayerWeights;
-
-// Shapes, step metadata (device pointers into the packed step buffer) and activation buffers.
-typedef struct B200DenseStep {
-  int T, H, Hq, Hkv, D, rot, inter, block_size;
-  int neox, gemma, act_kind, gate_up_interleaved;
-  float eps, scale, softcap;
-  int window;
-  long long num_blocks;
-  const void* positions;
-  const void* cos_sin;
-  const void* slot_mapping;
-  const void* block_table;
-  int max_blocks;
-  const void* seq_lens;
-  int num_decodes, decode_splits, decode_tc;
-  void* decode_tmp_o;
-  void* decode_tmp_lse;
-  int num_prefills, num_tiles, num_prefill_tokens;
-  const void* prefill_q_start;
-  const void* tile_req;
-  const void* tile_q0;
-  void* hidden;           // [T, H] in: previous block's output (or the embeddings); out: this block's
-  void* resid;            // [T, H] residual stream
-  void* normed;           // [T, H]
-  void* qkv_buf;          // [T, (Hq + 2 Hkv) D]
-  void* attn;             // [T, Hq D]
-  void* gate_up_buf;      // [T, 2 I]
-  void* act;              // [T, I]
-  void* gemm_ws;
-  unsigned long long gemm_ws_bytes;
-  int first_layer;        // the residual stream starts here: resid = hidden, no add
-} B200DenseStep;
-
 // force_path bit 8: the weight operand is constant, its first tiles may be fetched before the
 // predecessor kernel has finished
 static constexpr int kConstW = 0x100;
@@ -167,45 +97,6 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
 
 
 // ---- tensor-parallel stack ----------------------------------------------------------------
-int b200_tp_reduce_norm_gather(const struct B200TpReduce* a, cudaStream_t stream);
-
-// Peer-mapped buffers of the fused tensor-parallel path (see tp_fused.cu): per rank a receive
-// buffer, a gathered-activation buffer and the counters, each with two parities.
-typedef struct B200TpLayers {
-  int world, rank;
-  int rpr_max;                 // capacity of a rank's row shard (multiple of 32)
-  int max_tokens;              // capacity of the gathered buffer (multiple of 32)
-  void* recv[8];               // [2][world * k-splits][rpr][H] bf16
-  void* rs_flags[8];           // [2][rpr_max / 32]
-  void* x_full[8];             // [2][max_tokens][H] bf16
-  void* ag_flags[8];           // [2][max_tokens / 32]
-  void* op_counter;            // local
-  void* done_counter;          // local
-  void* residual;              // local shard [rpr_max][H]
-  const void* final_norm;      // the norm after the last block
-} B200TpLayers;
-
-struct B200TpReduce {          // mirrors tp_fused.cu
-  int world, rank, rows_per_rank, M, H;
-  const void* recv;
-  long long recv_parity_stride;
-  void* rs_flags;
-  int rs_flag_parity_stride;
-  int expected_rs;
-  int nsrc;
-  void* residual;
-  const void* norm_w;
-  float eps;
-  int gemma;
-  void* peer_x[8];
-  long long x_parity_stride;
-  void* peer_ag_flags[8];
-  int ag_flag_parity_stride;
-  int ag_groups;
-  void* op_counter;
-  void* done_counter;
-};
-
 void b200_tp_layers_abi(int* out2) {
   out2[0] = (int)sizeof(B200TpLayers);
   out2[1] = (int)offsetof(B200TpLayers, final_norm);

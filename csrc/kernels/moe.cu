@@ -465,14 +465,6 @@ int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, in
   RETL;
 }
 
-typedef struct B200MoeScatter {
-  int world, rank, rows_per_rank;
-  void* peer_recv[8];
-  void* peer_rs_flags[8];
-  long long recv_parity_stride;
-  int rs_flag_parity_stride;
-  const void* op_counter;
-} B200MoeScatter;
 
 int b200_moe_combine(const void* y, const void* pair_pos, const void* topk_w, int T, int k, int H,
                      const void* shared, const void* shared_gate, void* out,

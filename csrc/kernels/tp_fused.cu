@@ -265,26 +265,6 @@ using namespace b200;
 
 extern "C" {
 
-typedef struct B200TpReduce {
-  int world, rank, rows_per_rank, M, H;
-  const void* recv;
-  long long recv_parity_stride;
-  void* rs_flags;
-  int rs_flag_parity_stride;
-  int expected_rs;
-  int nsrc;
-  void* residual;
-  const void* norm_w;
-  float eps;
-  int gemma;
-  void* peer_x[8];
-  long long x_parity_stride;
-  void* peer_ag_flags[8];
-  int ag_flag_parity_stride;
-  int ag_groups;
-  void* op_counter;
-  void* done_counter;
-} B200TpReduce;
 
 int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream) {
   if (!a || a->world < 1 || a->world > 8 || (a->H & 7) || a->H > 32768 || (a->rows_per_rank & 31))
