@@ -1,237 +1,420 @@
-// C interface of the engine (include/vllm.h). The engine itself lives in Python objects; this
-// layer embeds the interpreter (or joins the one already running when the library was loaded
-// from Python), marshals the POD parameter structs into dicts, and calls the functions of
-// vllm_cpp_b200.capi_bridge. No exception crosses the boundary: Python errors become a status
-// code plus a thread-local message.
-#include <Python.h>
+// C interface of the engine (include/vllm.h) over the native runtime: scheduler, engine core,
+// model runner, dense model, tokenizer and sampler are all C++ (csrc/engine, csrc/runtime), the
+// kernels come from the CUDA library or the CPU thread-pool kernels, memory comes from libtorch.
+// No interpreter is linked or started.
+//
+// One engine thread per handle owns the engine: API calls post commands to it and deltas are
+// delivered from it ("a thread the library owns"). Architectures the native runtime does not
+// cover are served by the Python-hosted build of the same interface (libvllm_b200_py.so, loaded
+// on demand from the directory of this library), so one library name serves every model.
+//
+// Reference: src/capi/vllm_c.cpp:404-855 (engine handle, completion, streaming, requests),
+// src/capi/chat_prompt.cpp (chat entry points).
+#include <dlfcn.h>
 
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdlib>
 #include <cstring>
+#include <deque>
+#include <functional>
+#include <future>
+#include <map>
 #include <mutex>
 #include <string>
 #include <thread>
 
 #include "../../include/vllm.h"
+#include "runtime/native_llm.h"
+#include "util/json.h"
+
+using b200::Json;
+using b200::SamplingParams;
+using b200::rt::NativeLLM;
+using b200::rt::RequestDelta;
 
 namespace {
 
 thread_local std::string g_last_error;
-std::once_flag g_py_once;
-bool g_we_initialised = false;
-
 void set_error(const std::string& m) { g_last_error = m; }
 
-void ensure_python() {
-  std::call_once(g_py_once, [] {
-    if (!Py_IsInitialized()) {
-      Py_InitializeEx(0);
-      g_we_initialised = true;
-      // the thread that initialised holds the GIL: release it so that any thread may enter
-      PyEval_SaveThread();
+// ---- the Python-hosted build, loaded only when the native runtime does not cover the model ----
+struct PyLib {
+  void* h = nullptr;
+  decltype(&vllm_engine_load_ex) load_ex = nullptr;
+  decltype(&vllm_engine_free) engine_free = nullptr;
+  decltype(&vllm_complete) complete = nullptr;
+  decltype(&vllm_complete_stream) complete_stream = nullptr;
+  decltype(&vllm_request_submit) request_submit = nullptr;
+  decltype(&vllm_request_cancel) request_cancel = nullptr;
+  decltype(&vllm_request_wait) request_wait = nullptr;
+  decltype(&vllm_request_done) request_done = nullptr;
+  decltype(&vllm_request_error) request_error = nullptr;
+  decltype(&vllm_request_free) request_free = nullptr;
+  decltype(&vllm_chat) chat = nullptr;
+  decltype(&vllm_chat_stream) chat_stream = nullptr;
+  decltype(&vllm_last_error) last_error = nullptr;
+};
+PyLib* py_lib() {
+  static PyLib lib;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    Dl_info info{};
+    std::string dir = ".";
+    if (dladdr((void*)&set_error, &info) && info.dli_fname) {
+      std::string p = info.dli_fname;
+      auto s = p.rfind('/');
+      if (s != std::string::npos) dir = p.substr(0, s);
     }
+    void* h = dlopen((dir + "/libvllm_b200_py.so").c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (!h) return;
+    lib.h = h;
+#define B200_SYM(field, name) lib.field = reinterpret_cast<decltype(lib.field)>(dlsym(h, name))
+    B200_SYM(load_ex, "vllm_engine_load_ex");
+    B200_SYM(engine_free, "vllm_engine_free");
+    B200_SYM(complete, "vllm_complete");
+    B200_SYM(complete_stream, "vllm_complete_stream");
+    B200_SYM(request_submit, "vllm_request_submit");
+    B200_SYM(request_cancel, "vllm_request_cancel");
+    B200_SYM(request_wait, "vllm_request_wait");
+    B200_SYM(request_done, "vllm_request_done");
+    B200_SYM(request_error, "vllm_request_error");
+    B200_SYM(request_free, "vllm_request_free");
+    B200_SYM(chat, "vllm_chat");
+    B200_SYM(chat_stream, "vllm_chat_stream");
+    B200_SYM(last_error, "vllm_last_error");
+#undef B200_SYM
   });
+  return lib.h && lib.load_ex ? &lib : nullptr;
 }
 
-struct Gil {
-  PyGILState_STATE st;
-  Gil() { ensure_python(); st = PyGILState_Ensure(); }
-  ~Gil() { PyGILState_Release(st); }
+// ---- per-request delivery state --------------------------------------------------------------
+struct Sink {
+  vllm_token_callback cb = nullptr;
+  void* user = nullptr;
+  std::mutex mu;
+  std::condition_variable cv;
+  bool done = false;
+  std::string error;
+  std::string text;
+  std::string finish_reason;
+  int prompt_tokens = 0, completion_tokens = 0;
+  std::string rid;
+  std::atomic<bool> cancelled{false};
+  // chat streaming: deltas are wrapped into chat.completion.chunk objects
+  std::function<std::string(const std::string& delta, bool first, bool finished, const std::string& reason)> wrap;
+  bool first = true;
 };
 
-// Formats the pending Python exception into the thread-local message and clears it.
-vllm_status take_py_error(vllm_status fallback) {
-  PyObject *type = nullptr, *value = nullptr, *tb = nullptr;
-  PyErr_Fetch(&type, &value, &tb);
-  PyErr_NormalizeException(&type, &value, &tb);
-  std::string msg = "unknown Python error";
-  vllm_status st = fallback;
-  if (value) {
-    PyObject* s = PyObject_Str(value);
-    if (s) {
-      const char* c = PyUnicode_AsUTF8(s);
-      if (c) msg = c;
-      Py_DECREF(s);
-    }
-    if (type && PyErr_GivenExceptionMatches(type, PyExc_ValueError)) st = VLLM_ERR_INVALID_ARGUMENT;
-    if (type && (PyErr_GivenExceptionMatches(type, PyExc_FileNotFoundError) ||
-                 PyErr_GivenExceptionMatches(type, PyExc_ImportError)))
-      st = VLLM_ERR_MODEL_LOAD;
-    if (type) {
-      PyObject* n = PyObject_GetAttrString(type, "__name__");
-      if (n) {
-        const char* c = PyUnicode_AsUTF8(n);
-        if (c) msg = std::string(c) + ": " + msg;
-        Py_DECREF(n);
-      }
-    }
-  }
-  PyErr_Clear();
-  Py_XDECREF(type);
-  Py_XDECREF(value);
-  Py_XDECREF(tb);
-  set_error(msg);
-  return st;
-}
-
-PyObject* bridge() {   // borrowed-like: cached module (new reference kept forever)
-  static PyObject* mod = nullptr;
-  if (!mod) mod = PyImport_ImportModule("vllm_cpp_b200.capi_bridge");
-  return mod;
-}
-
-void dict_set(PyObject* d, const char* k, PyObject* v) {   // steals v
-  if (v) {
-    PyDict_SetItemString(d, k, v);
-    Py_DECREF(v);
-  }
-}
-PyObject* str_or_none(const char* s) {
-  if (!s) Py_RETURN_NONE;
-  return PyUnicode_FromString(s);
-}
-PyObject* str_list(const char* const* items, size_t n) {
-  PyObject* l = PyList_New(0);
-  for (size_t i = 0; i < n; ++i) {
-    if (!items || !items[i]) continue;
-    PyObject* s = PyUnicode_FromString(items[i]);
-    PyList_Append(l, s);
-    Py_DECREF(s);
-  }
-  return l;
-}
-
-PyObject* sampling_dict(const vllm_sampling_params* p) {
-  PyObject* d = PyDict_New();
-  dict_set(d, "temperature", PyFloat_FromDouble(p->temperature));
-  dict_set(d, "top_p", PyFloat_FromDouble(p->top_p));
-  dict_set(d, "top_k", PyLong_FromLong(p->top_k));
-  dict_set(d, "min_p", PyFloat_FromDouble(p->min_p));
-  dict_set(d, "max_tokens", PyLong_FromLong(p->max_tokens));
-  dict_set(d, "seed", PyLong_FromUnsignedLongLong(p->seed));
-  dict_set(d, "has_seed", PyBool_FromLong(p->has_seed));
-  dict_set(d, "presence_penalty", PyFloat_FromDouble(p->presence_penalty));
-  dict_set(d, "frequency_penalty", PyFloat_FromDouble(p->frequency_penalty));
-  dict_set(d, "repetition_penalty", PyFloat_FromDouble(p->repetition_penalty));
-  dict_set(d, "min_tokens", PyLong_FromLong(p->min_tokens));
-  dict_set(d, "ignore_eos", PyBool_FromLong(p->ignore_eos));
-  dict_set(d, "stop", str_list(p->stop, p->n_stop));
-  dict_set(d, "structured_json", str_or_none(p->structured_json));
-  dict_set(d, "structured_regex", str_or_none(p->structured_regex));
-  dict_set(d, "structured_choice", str_list(p->structured_choice, p->n_structured_choice));
-  dict_set(d, "structured_grammar", str_or_none(p->structured_grammar));
-  dict_set(d, "structured_json_object", PyBool_FromLong(p->structured_json_object));
-  return d;
-}
-
-const char* static_reason(const std::string& r) {
-  if (r == "stop") return "stop";
-  if (r == "length") return "length";
-  if (r == "abort") return "abort";
-  if (r == "tool_calls") return "tool_calls";
-  return "error";
-}
-
-char* dup_string(const std::string& s) {
-  char* p = (char*)std::malloc(s.size() + 1);
-  if (p) std::memcpy(p, s.c_str(), s.size() + 1);
-  return p;
-}
+struct Command {
+  enum Kind { kAdd, kAbort, kStop } kind = kAdd;
+  std::string prompt;
+  SamplingParams params;
+  std::shared_ptr<Sink> sink;
+  std::string rid;
+  std::promise<std::string> reply;     // request id, or an exception
+};
 
 }  // namespace
 
 struct vllm_engine {
-  PyObject* handle = nullptr;   // capi_bridge.EngineHandle
+  vllm_engine* py = nullptr;           // the handle of the Python-hosted build (then nothing else is used)
+  std::unique_ptr<NativeLLM> llm;
+  std::string model_name;
+  std::thread loop;
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<std::unique_ptr<Command>> queue;
+  std::map<std::string, std::shared_ptr<Sink>> sinks;   // engine thread only
+  std::string dead;                    // non-empty: the engine thread died with this message
+  bool stopping = false;
+
+  void run();
+  void finish(const std::shared_ptr<Sink>& s, const std::string& err);
 };
 
 struct vllm_request {
+  vllm_request* py = nullptr;
   vllm_engine* engine = nullptr;
-  std::string rid;
-  vllm_token_callback cb = nullptr;
-  void* user = nullptr;
-  std::thread worker;
-  std::mutex mu;
-  std::condition_variable cv;
-  std::atomic<bool> done{false};
-  std::atomic<bool> cancelled{false};
-  std::string error;
-  bool has_error = false;
+  std::shared_ptr<Sink> sink;
 };
 
 namespace {
 
-// Drains the stream of `rid`, calling `cb` per delta. Needs the GIL. Fills the totals.
-vllm_status drain(vllm_engine* e, const std::string& rid, vllm_token_callback cb, void* user,
-                  std::string* text, std::string* reason, int* completion_tokens,
-                  const std::atomic<bool>* cancelled) {
-  PyObject* gen = PyObject_CallMethod(bridge(), "stream", "Os", e->handle, rid.c_str());
-  if (!gen) return take_py_error(VLLM_ERR_RUNTIME);
-  PyObject* it = PyObject_GetIter(gen);
-  Py_DECREF(gen);
-  if (!it) return take_py_error(VLLM_ERR_RUNTIME);
-  vllm_status st = VLLM_OK;
-  bool stopped = false;
-  while (true) {
-    PyObject* item;
-    item = PyIter_Next(it);   // blocks inside Python (queue.get releases the GIL)
-    if (!item) break;
-    const char* delta = "";
-    int finished = 0, ntok = 0;
-    const char* fr = "";
-    const char* err = "";
-    if (!PyArg_ParseTuple(item, "spsis", &delta, &finished, &fr, &ntok, &err)) {
-      Py_DECREF(item);
-      st = take_py_error(VLLM_ERR_RUNTIME);
-      break;
-    }
-    if (err && *err) {
-      set_error(err);
-      st = VLLM_ERR_RUNTIME;
-      Py_DECREF(item);
-      break;
-    }
-    if (text) text->append(delta);
-    if (completion_tokens) *completion_tokens = ntok;
-    if (finished && reason) *reason = fr;
-    bool keep = true;
-    if (cb && !stopped) {
-      // the callback is foreign code: run it without the GIL
-      std::string d(delta);
-      Py_BEGIN_ALLOW_THREADS
-      keep = cb(d.c_str(), finished != 0, user);
-      Py_END_ALLOW_THREADS
-    }
-    Py_DECREF(item);
-    if ((!keep || (cancelled && cancelled->load())) && !finished && !stopped) {
-      stopped = true;
-      PyObject* r = PyObject_CallMethod(bridge(), "abort", "Os", e->handle, rid.c_str());
-      if (!r) PyErr_Clear();
-      Py_XDECREF(r);
-      if (reason) *reason = "abort";
-    }
+void deliver(const std::shared_ptr<Sink>& s, const std::string& delta, bool finished, const std::string& reason,
+             vllm_engine* e) {
+  if (!s->cb || s->cancelled.load()) return;
+  std::string payload = delta;
+  if (s->wrap) payload = s->wrap(delta, s->first, finished, reason);
+  s->first = false;
+  if (s->wrap) {
+    // chat streaming: every chunk is a JSON object; the stream ends with ("", finished)
+    if (!payload.empty() && !s->cb(payload.c_str(), false, s->user)) s->cancelled.store(true);
+    if (finished && !s->cancelled.load()) s->cb("", true, s->user);
+  } else if (!s->cb(payload.c_str(), finished, s->user)) {
+    s->cancelled.store(true);
   }
-  if (PyErr_Occurred()) st = take_py_error(VLLM_ERR_RUNTIME);
-  Py_DECREF(it);
-  return st;
+  if (s->cancelled.load() && !finished) e->llm->abort(s->rid);
 }
 
-vllm_status submit_locked(vllm_engine* e, const char* prompt, const vllm_sampling_params* p,
-                          std::string* rid, int* prompt_tokens) {
-  PyObject* sd = sampling_dict(p);
-  PyObject* r = PyObject_CallMethod(bridge(), "submit", "OsO", e->handle, prompt, sd);
-  Py_DECREF(sd);
-  if (!r) return take_py_error(VLLM_ERR_RUNTIME);
-  const char* id = nullptr;
-  int np = 0;
-  if (!PyArg_ParseTuple(r, "si", &id, &np)) {
-    Py_DECREF(r);
-    return take_py_error(VLLM_ERR_RUNTIME);
+}  // namespace
+
+void vllm_engine::finish(const std::shared_ptr<Sink>& s, const std::string& err) {
+  {
+    std::lock_guard<std::mutex> l(s->mu);
+    s->done = true;
+    if (!err.empty()) s->error = err;
   }
-  *rid = id;
-  if (prompt_tokens) *prompt_tokens = np;
-  Py_DECREF(r);
+  s->cv.notify_all();
+}
+
+void vllm_engine::run() {
+  for (;;) {
+    std::deque<std::unique_ptr<Command>> cmds;
+    {
+      std::unique_lock<std::mutex> l(mu);
+      cv.wait(l, [&] { return stopping || !queue.empty() || (llm && llm->has_unfinished()); });
+      if (stopping) break;
+      cmds.swap(queue);
+    }
+    for (auto& c : cmds) {
+      try {
+        if (c->kind == Command::kAdd) {
+          const std::string rid = llm->add_request(c->prompt, c->params);
+          c->sink->rid = rid;
+          sinks[rid] = c->sink;
+          c->reply.set_value(rid);
+        } else if (c->kind == Command::kAbort) {
+          auto it = sinks.find(c->rid);
+          if (it != sinks.end()) {
+            llm->abort(c->rid);
+            it->second->finish_reason = "abort";
+            auto s = it->second;
+            sinks.erase(it);
+            finish(s, "");
+          }
+          c->reply.set_value(c->rid);
+        }
+      } catch (...) {
+        c->reply.set_exception(std::current_exception());
+      }
+    }
+    if (!llm->has_unfinished()) continue;
+    std::vector<RequestDelta> deltas;
+    try {
+      deltas = llm->step();
+    } catch (const std::exception& ex) {
+      // the engine is dead for every waiter (reference: core_proc.cpp:140-146)
+      std::lock_guard<std::mutex> l(mu);
+      dead = ex.what();
+      for (auto& kv : sinks) finish(kv.second, dead);
+      sinks.clear();
+      stopping = true;
+      break;
+    }
+    for (auto& d : deltas) {
+      auto it = sinks.find(d.request_id);
+      if (it == sinks.end()) continue;
+      auto s = it->second;
+      s->text += d.delta_text;
+      s->prompt_tokens = d.prompt_tokens;
+      s->completion_tokens = d.completion_tokens;
+      if (d.finished) s->finish_reason = d.finish_reason;
+      const bool was_cancelled = s->cancelled.load();
+      if (!d.delta_text.empty() || d.finished) deliver(s, d.delta_text, d.finished, d.finish_reason, this);
+      if (d.finished || (s->cancelled.load() && !was_cancelled)) {
+        if (!d.finished) s->finish_reason = "abort";
+        sinks.erase(d.request_id);
+        finish(s, "");
+      }
+    }
+  }
+  // stopping: nobody may wait for ever
+  for (auto& kv : sinks) finish(kv.second, dead.empty() ? "engine shut down" : dead);
+  sinks.clear();
+}
+
+namespace {
+
+const char* static_reason(const std::string& r) {
+  if (r == "stop") return "stop";
+  if (r == "length") return "length";
+  return "abort";
+}
+
+// vllm_sampling_params -> SamplingParams; throws std::invalid_argument on a bad field.
+SamplingParams to_params(const vllm_sampling_params* p) {
+  SamplingParams sp;
+  if (!(p->repetition_penalty > 0.f))
+    throw std::invalid_argument("repetition_penalty must be > 0 (start from vllm_sampling_params_default())");
+  sp.temperature = p->temperature;
+  sp.top_p = p->top_p;
+  sp.top_k = p->top_k;
+  sp.min_p = p->min_p;
+  if (p->max_tokens > 0) sp.max_tokens = p->max_tokens;
+  else sp.max_tokens = std::nullopt;
+  if (p->has_seed) sp.seed = p->seed;
+  sp.presence_penalty = p->presence_penalty;
+  sp.frequency_penalty = p->frequency_penalty;
+  sp.repetition_penalty = p->repetition_penalty;
+  sp.min_tokens = p->min_tokens;
+  sp.ignore_eos = p->ignore_eos != 0;
+  for (int i = 0; i < p->n_stop; ++i)
+    if (p->stop && p->stop[i]) sp.stop.emplace_back(p->stop[i]);
+  b200::StructuredOutputsParams so;
+  if (p->structured_json) so.json = p->structured_json;
+  if (p->structured_regex) so.regex = p->structured_regex;
+  if (p->structured_choice && p->n_structured_choice > 0) {
+    so.choice = std::vector<std::string>();
+    for (int i = 0; i < p->n_structured_choice; ++i)
+      if (p->structured_choice[i]) so.choice->emplace_back(p->structured_choice[i]);
+  }
+  if (p->structured_grammar) so.grammar = p->structured_grammar;
+  so.json_object = p->structured_json_object != 0;
+  if (so.count() > 1) throw std::invalid_argument("at most one structured-output constraint may be set");
+  if (so.any()) sp.structured_outputs = so;
+  sp.output_kind = b200::OutputKind::kDelta;
+  return sp;
+}
+
+// Posts an add command and waits for the engine thread's answer. Returns the sink or sets the error.
+vllm_status submit(vllm_engine* e, const std::string& prompt, SamplingParams sp, vllm_token_callback cb, void* user,
+                   std::shared_ptr<Sink>* out, decltype(Sink::wrap) wrap = nullptr) {
+  auto c = std::make_unique<Command>();
+  c->kind = Command::kAdd;
+  c->prompt = prompt;
+  c->params = std::move(sp);
+  c->sink = std::make_shared<Sink>();
+  c->sink->cb = cb;
+  c->sink->user = user;
+  c->sink->wrap = std::move(wrap);
+  auto sink = c->sink;
+  auto fut = c->reply.get_future();
+  {
+    std::lock_guard<std::mutex> l(e->mu);
+    if (e->stopping || !e->dead.empty()) {
+      set_error(e->dead.empty() ? "the engine is shutting down" : "the engine is dead: " + e->dead);
+      return VLLM_ERR_RUNTIME;
+    }
+    e->queue.push_back(std::move(c));
+  }
+  e->cv.notify_all();
+  try {
+    fut.get();
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
+  } catch (const std::exception& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_RUNTIME;
+  }
+  *out = sink;
   return VLLM_OK;
+}
+
+vllm_status wait_sink(const std::shared_ptr<Sink>& s) {
+  std::unique_lock<std::mutex> l(s->mu);
+  s->cv.wait(l, [&] { return s->done; });
+  if (!s->error.empty()) {
+    set_error(s->error);
+    return VLLM_ERR_RUNTIME;
+  }
+  return VLLM_OK;
+}
+
+char* dup_cstr(const std::string& s) {
+  char* p = static_cast<char*>(std::malloc(s.size() + 1));
+  if (p) std::memcpy(p, s.c_str(), s.size() + 1);
+  return p;
+}
+
+// ---- chat: OpenAI request JSON -> prompt + sampling parameters -----------------------------------
+std::string content_text(const Json& c) {
+  if (c.is_string()) return c.as_string();
+  std::string out;                       // [{"type": "text", "text": ...}, ...]
+  for (auto& part : c.items())
+    if (part["type"].as_string() == "text") out += part["text"].as_string();
+  return out;
+}
+
+// The two formats the native runtime renders itself; anything else (tools, other templates)
+// is served by the Python-hosted build, which evaluates the checkpoint's Jinja template.
+std::string render_chat(const Json& messages, const std::string& style) {
+  std::string p;
+  if (style == "llama3") {
+    p = "<|begin_of_text|>";
+    for (auto& m : messages.items())
+      p += "<|start_header_id|>" + m["role"].as_string() + "<|end_header_id|>\n\n" + content_text(m["content"]) +
+           "<|eot_id|>";
+    p += "<|start_header_id|>assistant<|end_header_id|>\n\n";
+  } else {
+    for (auto& m : messages.items())
+      p += "<|im_start|>" + m["role"].as_string() + "\n" + content_text(m["content"]) + "<|im_end|>\n";
+    p += "<|im_start|>assistant\n";
+  }
+  return p;
+}
+
+struct ChatRequest {
+  std::string prompt;
+  SamplingParams params;
+  std::string model;
+};
+
+ChatRequest parse_chat(vllm_engine* e, const char* request_json, const std::string& style) {
+  Json req;
+  std::string err;
+  if (!Json::try_parse(request_json, &req, &err) || !req.is_object())
+    throw std::invalid_argument("request is not a JSON object: " + err);
+  const Json& msgs = req["messages"];
+  if (!msgs.is_array() || msgs.size() == 0) throw std::invalid_argument("messages must be a non-empty array");
+  if (req["tools"].is_array() && req["tools"].size() > 0)
+    throw std::invalid_argument("tool calling is served by the Python-hosted library (libvllm_b200_py.so)");
+  ChatRequest out;
+  out.model = req["model"].is_string() ? req["model"].as_string() : e->model_name;
+  out.prompt = render_chat(msgs, style);
+  SamplingParams& sp = out.params;
+  sp.temperature = req["temperature"].as_double(1.0);
+  sp.top_p = req["top_p"].as_double(1.0);
+  sp.top_k = (int)req["top_k"].as_int(0);
+  sp.min_p = req["min_p"].as_double(0.0);
+  int64_t mt = req["max_completion_tokens"].is_number() ? req["max_completion_tokens"].as_int()
+                                                         : req["max_tokens"].as_int(256);
+  sp.max_tokens = (int)mt;
+  if (req["seed"].is_number()) sp.seed = (uint64_t)req["seed"].as_int();
+  sp.presence_penalty = req["presence_penalty"].as_double(0.0);
+  sp.frequency_penalty = req["frequency_penalty"].as_double(0.0);
+  sp.repetition_penalty = req["repetition_penalty"].as_double(1.0);
+  if (req["stop"].is_string()) sp.stop.push_back(req["stop"].as_string());
+  for (auto& s : req["stop"].items()) sp.stop.push_back(s.as_string());
+  b200::StructuredOutputsParams so;
+  if (req["guided_choice"].is_array()) {
+    so.choice = std::vector<std::string>();
+    for (auto& c : req["guided_choice"].items()) so.choice->push_back(c.as_string());
+  }
+  if (req["guided_json"].is_object()) so.json = req["guided_json"].dump();
+  if (req["guided_json"].is_string()) so.json = req["guided_json"].as_string();
+  if (req["guided_regex"].is_string()) so.regex = req["guided_regex"].as_string();
+  if (req["guided_grammar"].is_string()) so.grammar = req["guided_grammar"].as_string();
+  const Json& rf = req["response_format"];
+  if (rf.is_object()) {
+    if (rf["type"].as_string() == "json_object") so.json_object = true;
+    if (rf["type"].as_string() == "json_schema") so.json = rf["json_schema"]["schema"].dump();
+  }
+  if (so.any()) sp.structured_outputs = so;
+  sp.output_kind = b200::OutputKind::kDelta;
+  return out;
+}
+
+int64_t unix_time() {
+  return std::chrono::duration_cast<std::chrono::seconds>(std::chrono::system_clock::now().time_since_epoch()).count();
+}
+
+std::string chat_style(vllm_engine* e) {
+  const b200::tok::Tokenizer* tk = e->llm->tokenizer();
+  if (tk && tk->token_to_id("<|start_header_id|>") >= 0) return "llama3";
+  return "chatml";
 }
 
 }  // namespace
@@ -273,75 +456,86 @@ vllm_status vllm_engine_load_ex(const vllm_model_params* params, const vllm_engi
   }
   *out = nullptr;
   // options: the caller's struct may be older (smaller) than ours; read only what it has
-  int32_t tp = 0, ep = 0;
+  int32_t tp = 0;
   const char* device = nullptr;
   if (options) {
     auto has = [&](size_t off, size_t sz) { return options->struct_size >= off + sz; };
-    if (has(offsetof(vllm_engine_options, tensor_parallel_size), sizeof(int32_t)))
-      tp = options->tensor_parallel_size;
-    if (has(offsetof(vllm_engine_options, enable_expert_parallel), sizeof(int32_t)))
-      ep = options->enable_expert_parallel;
+    if (has(offsetof(vllm_engine_options, tensor_parallel_size), sizeof(int32_t))) tp = options->tensor_parallel_size;
     if (has(offsetof(vllm_engine_options, device), sizeof(const char*))) device = options->device;
   } else {
     if (const char* v = std::getenv("VLLM_TENSOR_PARALLEL_SIZE")) tp = std::atoi(v);
-    if (const char* v = std::getenv("VLLM_ENABLE_EXPERT_PARALLEL")) ep = std::atoi(v);
     device = std::getenv("VLLM_DEVICE");
   }
-  Gil gil;
-  if (!bridge()) return take_py_error(VLLM_ERR_MODEL_LOAD);
-  PyObject* d = PyDict_New();
-  dict_set(d, "model_path", PyUnicode_FromString(params->model_path));
-  dict_set(d, "tokenizer_config_path", str_or_none(params->tokenizer_config_path));
-  dict_set(d, "block_size", PyLong_FromLong(params->block_size > 0 ? params->block_size : 32));
-  dict_set(d, "num_blocks", PyLong_FromLong(params->num_blocks > 0 ? params->num_blocks : 256));
-  dict_set(d, "max_model_len", PyLong_FromLong(params->max_model_len > 0 ? params->max_model_len : 0));
-  dict_set(d, "max_num_seqs", PyLong_FromLong(params->max_num_seqs > 0 ? params->max_num_seqs : 8));
-  dict_set(d, "tool_parser", str_or_none(params->tool_parser && *params->tool_parser ? params->tool_parser : nullptr));
-  dict_set(d, "reasoning_parser", str_or_none(params->reasoning_parser));
-  dict_set(d, "tensor_parallel_size", PyLong_FromLong(tp > 0 ? tp : 1));
-  dict_set(d, "enable_expert_parallel", PyBool_FromLong(ep != 0));
-  dict_set(d, "device", str_or_none(device));
-  PyObject* h = PyObject_CallMethod(bridge(), "load", "O", d);
-  Py_DECREF(d);
-  if (!h) return take_py_error(VLLM_ERR_MODEL_LOAD);
-  vllm_engine* e = new (std::nothrow) vllm_engine();
-  if (!e) {
-    Py_DECREF(h);
-    set_error("out of memory");
-    return VLLM_ERR_RUNTIME;
+  const char* force_py = std::getenv("VLLM_ENGINE");     // "python": always the Python-hosted build
+  std::string native_error;
+  if (tp <= 1 && !(force_py && std::string(force_py) == "python")) {
+    try {
+      b200::rt::EngineOptions o;
+      o.model_path = params->model_path;
+      if (params->tokenizer_config_path) {
+        // the reference takes the path of tokenizer_config.json; the tokenizer lives beside it
+        std::string t = params->tokenizer_config_path;
+        auto s = t.rfind('/');
+        o.tokenizer_path = s == std::string::npos ? "." : t.substr(0, s);
+      }
+      o.device = device ? device : "cuda";
+      o.block_size = params->block_size > 0 ? params->block_size : 32;
+      o.num_blocks = params->num_blocks > 0 ? params->num_blocks : 256;
+      o.max_model_len = params->max_model_len > 0 ? params->max_model_len : 0;
+      o.max_num_seqs = params->max_num_seqs > 0 ? params->max_num_seqs : 8;
+      auto llm = NativeLLM::load(o);
+      auto* e = new vllm_engine();
+      e->llm = std::move(llm);
+      e->model_name = params->model_path;
+      e->loop = std::thread([e] { e->run(); });
+      *out = e;
+      return VLLM_OK;
+    } catch (const std::exception& ex) {
+      native_error = ex.what();
+      if (native_error.find("not covered by the native runtime") == std::string::npos &&
+          native_error.find("native runtime loads") == std::string::npos &&
+          native_error.find("native runtime takes") == std::string::npos) {
+        set_error(native_error);
+        return VLLM_ERR_MODEL_LOAD;
+      }
+    }
   }
-  e->handle = h;
+  PyLib* py = py_lib();
+  if (!py) {
+    set_error((native_error.empty() ? std::string("tensor parallel serving") : native_error) +
+              "; the Python-hosted library (libvllm_b200_py.so) that serves it could not be loaded");
+    return VLLM_ERR_MODEL_LOAD;
+  }
+  vllm_engine* inner = nullptr;
+  const vllm_status st = py->load_ex(params, options, &inner);
+  if (st != VLLM_OK) {
+    set_error(py->last_error ? py->last_error() : "engine load failed");
+    return st;
+  }
+  auto* e = new vllm_engine();
+  e->py = inner;
   *out = e;
   return VLLM_OK;
 }
 
 void vllm_engine_free(vllm_engine* engine) {
   if (!engine) return;
-  {
-    Gil gil;
-    if (engine->handle) {
-      PyObject* r = PyObject_CallMethod(engine->handle, "close", nullptr);
-      if (!r) PyErr_Clear();
-      Py_XDECREF(r);
-      Py_DECREF(engine->handle);
-    }
+  if (engine->py) {
+    py_lib()->engine_free(engine->py);
+    delete engine;
+    return;
   }
+  {
+    std::lock_guard<std::mutex> l(engine->mu);
+    engine->stopping = true;
+  }
+  engine->cv.notify_all();
+  if (engine->loop.joinable()) engine->loop.join();
   delete engine;
 }
 
-vllm_status vllm_complete_stream(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
-                                 vllm_token_callback cb, void* user) {
-  g_last_error.clear();
-  if (!engine || !prompt || !params) {
-    set_error("vllm_complete_stream: engine, prompt and params are required");
-    return VLLM_ERR_INVALID_ARGUMENT;
-  }
-  Gil gil;
-  std::string rid;
-  vllm_status st = submit_locked(engine, prompt, params, &rid, nullptr);
-  if (st != VLLM_OK) return st;
-  return drain(engine, rid, cb, user, nullptr, nullptr, nullptr, nullptr);
-}
+#define B200_FORWARD_ERR(st) \
+  do { if ((st) != VLLM_OK && py_lib()->last_error) set_error(py_lib()->last_error()); } while (0)
 
 vllm_status vllm_complete(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
                           vllm_completion* out) {
@@ -350,19 +544,50 @@ vllm_status vllm_complete(vllm_engine* engine, const char* prompt, const vllm_sa
     set_error("vllm_complete: engine, prompt, params and out are required");
     return VLLM_ERR_INVALID_ARGUMENT;
   }
+  if (engine->py) {
+    const vllm_status st = py_lib()->complete(engine->py, prompt, params, out);
+    B200_FORWARD_ERR(st);
+    return st;
+  }
   std::memset(out, 0, sizeof *out);
-  Gil gil;
-  std::string rid, text, reason;
-  int np = 0, nc = 0;
-  vllm_status st = submit_locked(engine, prompt, params, &rid, &np);
+  std::shared_ptr<Sink> s;
+  try {
+    const vllm_status st = submit(engine, prompt, to_params(params), nullptr, nullptr, &s);
+    if (st != VLLM_OK) return st;
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  const vllm_status st = wait_sink(s);
   if (st != VLLM_OK) return st;
-  st = drain(engine, rid, nullptr, nullptr, &text, &reason, &nc, nullptr);
-  if (st != VLLM_OK) return st;
-  out->text = dup_string(text);
-  out->finish_reason = static_reason(reason);
-  out->prompt_tokens = np;
-  out->completion_tokens = nc;
-  return VLLM_OK;
+  out->text = dup_cstr(s->text);
+  out->finish_reason = static_reason(s->finish_reason);
+  out->prompt_tokens = s->prompt_tokens;
+  out->completion_tokens = s->completion_tokens;
+  return out->text ? VLLM_OK : VLLM_ERR_RUNTIME;
+}
+
+vllm_status vllm_complete_stream(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
+                                 vllm_token_callback cb, void* user) {
+  g_last_error.clear();
+  if (!engine || !prompt || !params || !cb) {
+    set_error("vllm_complete_stream: engine, prompt, params and cb are required");
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  if (engine->py) {
+    const vllm_status st = py_lib()->complete_stream(engine->py, prompt, params, cb, user);
+    B200_FORWARD_ERR(st);
+    return st;
+  }
+  std::shared_ptr<Sink> s;
+  try {
+    const vllm_status st = submit(engine, prompt, to_params(params), cb, user, &s);
+    if (st != VLLM_OK) return st;
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  return wait_sink(s);
 }
 
 vllm_status vllm_request_submit(vllm_engine* engine, const char* prompt, const vllm_sampling_params* params,
@@ -373,37 +598,27 @@ vllm_status vllm_request_submit(vllm_engine* engine, const char* prompt, const v
     return VLLM_ERR_INVALID_ARGUMENT;
   }
   *out = nullptr;
-  vllm_request* r = new (std::nothrow) vllm_request();
-  if (!r) {
-    set_error("out of memory");
-    return VLLM_ERR_RUNTIME;
+  if (engine->py) {
+    vllm_request* inner = nullptr;
+    const vllm_status st = py_lib()->request_submit(engine->py, prompt, params, cb, user, &inner);
+    B200_FORWARD_ERR(st);
+    if (st != VLLM_OK) return st;
+    auto* r = new vllm_request();
+    r->py = inner;
+    *out = r;
+    return VLLM_OK;
   }
+  std::shared_ptr<Sink> s;
+  try {
+    const vllm_status st = submit(engine, prompt, to_params(params), cb, user, &s);
+    if (st != VLLM_OK) return st;
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  auto* r = new vllm_request();
   r->engine = engine;
-  r->cb = cb;
-  r->user = user;
-  {
-    Gil gil;
-    vllm_status st = submit_locked(engine, prompt, params, &r->rid, nullptr);
-    if (st != VLLM_OK) {
-      delete r;
-      return st;
-    }
-  }
-  r->worker = std::thread([r] {
-    {
-      Gil gil;
-      vllm_status st = drain(r->engine, r->rid, r->cb, r->user, nullptr, nullptr, nullptr, &r->cancelled);
-      if (st != VLLM_OK) {
-        r->error = g_last_error;
-        r->has_error = true;
-      }
-    }
-    {
-      std::lock_guard<std::mutex> lock(r->mu);
-      r->done.store(true);
-    }
-    r->cv.notify_all();
-  });
+  r->sink = s;
   *out = r;
   return VLLM_OK;
 }
@@ -413,11 +628,26 @@ vllm_status vllm_request_cancel(vllm_request* request) {
     set_error("vllm_request_cancel: request is NULL");
     return VLLM_ERR_INVALID_ARGUMENT;
   }
-  if (request->done.load() || request->cancelled.exchange(true)) return VLLM_OK;
-  Gil gil;
-  PyObject* r = PyObject_CallMethod(bridge(), "abort", "Os", request->engine->handle, request->rid.c_str());
-  if (!r) PyErr_Clear();
-  Py_XDECREF(r);
+  if (request->py) return py_lib()->request_cancel(request->py);
+  {
+    std::lock_guard<std::mutex> l(request->sink->mu);
+    if (request->sink->done) return VLLM_OK;
+  }
+  if (request->sink->cancelled.exchange(true)) return VLLM_OK;
+  auto c = std::make_unique<Command>();
+  c->kind = Command::kAbort;
+  c->rid = request->sink->rid;
+  auto fut = c->reply.get_future();
+  {
+    std::lock_guard<std::mutex> l(request->engine->mu);
+    if (request->engine->stopping) return VLLM_OK;
+    request->engine->queue.push_back(std::move(c));
+  }
+  request->engine->cv.notify_all();
+  try {
+    fut.get();
+  } catch (...) {
+  }
   return VLLM_OK;
 }
 
@@ -426,25 +656,35 @@ vllm_status vllm_request_wait(vllm_request* request) {
     set_error("vllm_request_wait: request is NULL");
     return VLLM_ERR_INVALID_ARGUMENT;
   }
-  std::unique_lock<std::mutex> lock(request->mu);
-  request->cv.wait(lock, [request] { return request->done.load(); });
-  if (request->has_error) {
-    set_error(request->error);
-    return VLLM_ERR_RUNTIME;
-  }
-  return VLLM_OK;
+  if (request->py) return py_lib()->request_wait(request->py);
+  return wait_sink(request->sink);
 }
 
-bool vllm_request_done(const vllm_request* request) { return !request || request->done.load(); }
+bool vllm_request_done(const vllm_request* request) {
+  if (!request) return true;
+  if (request->py) return py_lib()->request_done(request->py);
+  std::lock_guard<std::mutex> l(request->sink->mu);
+  return request->sink->done;
+}
 
 const char* vllm_request_error(const vllm_request* request) {
-  return (request && request->done.load() && request->has_error) ? request->error.c_str() : nullptr;
+  if (!request) return nullptr;
+  if (request->py) return py_lib()->request_error(request->py);
+  std::lock_guard<std::mutex> l(request->sink->mu);
+  return request->sink->error.empty() ? nullptr : request->sink->error.c_str();
 }
 
 void vllm_request_free(vllm_request* request) {
   if (!request) return;
-  if (!request->done.load()) vllm_request_cancel(request);
-  if (request->worker.joinable()) request->worker.join();
+  if (request->py) {
+    py_lib()->request_free(request->py);
+    delete request;
+    return;
+  }
+  if (!vllm_request_done(request)) {
+    vllm_request_cancel(request);
+    wait_sink(request->sink);
+  }
   delete request;
 }
 
@@ -455,57 +695,88 @@ vllm_status vllm_chat(vllm_engine* engine, const char* request_json, char** out_
     return VLLM_ERR_INVALID_ARGUMENT;
   }
   *out_json = nullptr;
-  Gil gil;
-  PyObject* r = PyObject_CallMethod(bridge(), "chat", "Os", engine->handle, request_json);
-  if (!r) return take_py_error(VLLM_ERR_RUNTIME);
-  const char* s = PyUnicode_AsUTF8(r);
-  if (!s) {
-    Py_DECREF(r);
-    return take_py_error(VLLM_ERR_RUNTIME);
+  if (engine->py) {
+    const vllm_status st = py_lib()->chat(engine->py, request_json, out_json);
+    B200_FORWARD_ERR(st);
+    return st;
   }
-  *out_json = dup_string(s);
-  Py_DECREF(r);
-  return VLLM_OK;
-}
-
-namespace {
-struct ChunkSink {
-  vllm_token_callback cb;
-  void* user;
-};
-PyObject* chunk_trampoline(PyObject* self, PyObject* args) {
-  ChunkSink* sink = (ChunkSink*)PyCapsule_GetPointer(self, "vllm.chunk_sink");
-  const char* text = nullptr;
-  if (!sink || !PyArg_ParseTuple(args, "s", &text)) return nullptr;
-  const bool last = std::strcmp(text, "[DONE]") == 0;
-  bool keep = true;
-  if (sink->cb) {
-    std::string t(last ? "" : text);
-    Py_BEGIN_ALLOW_THREADS
-    keep = sink->cb(t.c_str(), last, sink->user);
-    Py_END_ALLOW_THREADS
+  std::shared_ptr<Sink> s;
+  ChatRequest cr;
+  try {
+    cr = parse_chat(engine, request_json, chat_style(engine));
+    const vllm_status st = submit(engine, cr.prompt, cr.params, nullptr, nullptr, &s);
+    if (st != VLLM_OK) return st;
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
   }
-  return PyBool_FromLong(keep);
+  const vllm_status st = wait_sink(s);
+  if (st != VLLM_OK) return st;
+  Json msg = Json::object();
+  msg["role"] = "assistant";
+  msg["content"] = s->text;
+  Json choice = Json::object();
+  choice["index"] = 0;
+  choice["message"] = msg;
+  choice["finish_reason"] = static_reason(s->finish_reason);
+  Json usage = Json::object();
+  usage["prompt_tokens"] = s->prompt_tokens;
+  usage["completion_tokens"] = s->completion_tokens;
+  usage["total_tokens"] = s->prompt_tokens + s->completion_tokens;
+  Json resp = Json::object();
+  resp["id"] = "chatcmpl-" + s->rid;
+  resp["object"] = "chat.completion";
+  resp["created"] = unix_time();
+  resp["model"] = cr.model;
+  Json choices = Json::array();
+  choices.push_back(choice);
+  resp["choices"] = choices;
+  resp["usage"] = usage;
+  *out_json = dup_cstr(resp.dump());
+  return *out_json ? VLLM_OK : VLLM_ERR_RUNTIME;
 }
-PyMethodDef g_chunk_def = {"on_chunk", chunk_trampoline, METH_VARARGS, "forwards one chunk to the C callback"};
-}  // namespace
 
 vllm_status vllm_chat_stream(vllm_engine* engine, const char* request_json, vllm_token_callback cb, void* user) {
   g_last_error.clear();
-  if (!engine || !request_json) {
-    set_error("vllm_chat_stream: engine and request_json are required");
+  if (!engine || !request_json || !cb) {
+    set_error("vllm_chat_stream: engine, request_json and cb are required");
     return VLLM_ERR_INVALID_ARGUMENT;
   }
-  Gil gil;
-  ChunkSink sink{cb, user};
-  PyObject* cap = PyCapsule_New(&sink, "vllm.chunk_sink", nullptr);
-  PyObject* fn = PyCFunction_New(&g_chunk_def, cap);
-  Py_DECREF(cap);
-  PyObject* r = PyObject_CallMethod(bridge(), "chat_stream", "OsO", engine->handle, request_json, fn);
-  Py_DECREF(fn);
-  if (!r) return take_py_error(VLLM_ERR_RUNTIME);
-  Py_DECREF(r);
-  return VLLM_OK;
+  if (engine->py) {
+    const vllm_status st = py_lib()->chat_stream(engine->py, request_json, cb, user);
+    B200_FORWARD_ERR(st);
+    return st;
+  }
+  std::shared_ptr<Sink> s;
+  try {
+    ChatRequest cr = parse_chat(engine, request_json, chat_style(engine));
+    const int64_t created = unix_time();
+    const std::string model = cr.model;
+    auto wrap = [created, model](const std::string& delta, bool first, bool finished, const std::string& reason) {
+      Json d = Json::object();
+      if (first) d["role"] = "assistant";
+      d["content"] = delta;
+      Json choice = Json::object();
+      choice["index"] = 0;
+      choice["delta"] = d;
+      choice["finish_reason"] = finished ? Json(static_reason(reason)) : Json(nullptr);
+      Json chunk = Json::object();
+      chunk["id"] = "chatcmpl-stream";
+      chunk["object"] = "chat.completion.chunk";
+      chunk["created"] = created;
+      chunk["model"] = model;
+      Json choices = Json::array();
+      choices.push_back(choice);
+      chunk["choices"] = choices;
+      return chunk.dump();
+    };
+    const vllm_status st = submit(engine, cr.prompt, cr.params, cb, user, &s, wrap);
+    if (st != VLLM_OK) return st;
+  } catch (const std::invalid_argument& ex) {
+    set_error(ex.what());
+    return VLLM_ERR_INVALID_ARGUMENT;
+  }
+  return wait_sink(s);
 }
 
 void vllm_string_free(char* s) { std::free(s); }
@@ -517,7 +788,7 @@ void vllm_completion_free(vllm_completion* c) {
 }
 
 const char* vllm_last_error(void) { return g_last_error.c_str(); }
-const char* vllm_version(void) { return "0.1.0"; }
+const char* vllm_version(void) { return "vllm_cpp_b200 0.2 (native runtime)"; }
 int32_t vllm_abi_version(void) { return VLLM_ABI_VERSION; }
 
 }  // extern "C"

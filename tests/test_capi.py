@@ -198,6 +198,7 @@ typedef const char* (*err_t)(void);
 int main(int argc, char** argv) {
   void* h = dlopen(argv[1], RTLD_NOW | RTLD_GLOBAL);
   if (!h) { fprintf(stderr, "dlopen: %s\n", dlerror()); return 2; }
+  if (dlsym(RTLD_DEFAULT, "Py_IsInitialized")) { fprintf(stderr, "an interpreter is linked in\n"); return 5; }
   mpd_t mpd = (mpd_t)dlsym(h, "vllm_model_params_default");
   spd_t spd = (spd_t)dlsym(h, "vllm_sampling_params_default");
   load_t load = (load_t)dlsym(h, "vllm_engine_load");
@@ -218,6 +219,8 @@ int main(int argc, char** argv) {
   printf("OK %d %d %s\n", c.prompt_tokens, c.completion_tokens, c.finish_reason);
   cfree(&c);
   efree(e);
+  /* the whole run happened without an interpreter in the process */
+  if (dlsym(RTLD_DEFAULT, "Py_IsInitialized")) { fprintf(stderr, "an interpreter was loaded\n"); return 6; }
   return 0;
 }
 """
@@ -247,3 +250,57 @@ def test_plain_c_program_with_dlopen(tmp_path, ckpt, header):
     r = subprocess.run([str(exe), LIB, ckpt], capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.startswith("OK ") and r.stdout.split()[2] in ("1", "2", "3", "4")
+
+
+def test_native_library_has_no_interpreter_and_matches_the_python_engine(lib, ckpt):
+    """``libvllm_b200.so`` is the native runtime: no libpython among its dependencies, and its
+    greedy completion equals the Python engine's on the same checkpoint (same kernels underneath)."""
+    deps = subprocess.run(["ldd", LIB], capture_output=True, text=True).stdout
+    assert "libpython" not in deps and "libtorch" in deps
+    assert b"native" in lib.vllm_version()
+    from vllm_cpp_b200.config import EngineArgs
+    from vllm_cpp_b200.engine import LLM, SamplingParams as SP
+    llm = LLM(EngineArgs(model=ckpt, device="cpu", cpu_backend="native", block_size=16, num_blocks=256,
+                         max_model_len=256, max_num_seqs=8))
+    prompt = "The quick brown fox jumps over"
+    want = llm.generate([prompt], SP(temperature=0.0, max_tokens=12, ignore_eos=True))[0].outputs[0]
+    mp = lib.vllm_model_params_default()
+    mp.model_path, mp.max_model_len, mp.block_size = ckpt.encode(), 256, 16
+    eng = ctypes.c_void_p()
+    opt = cpu_options()
+    assert lib.vllm_engine_load_ex(ctypes.byref(mp), ctypes.byref(opt), ctypes.byref(eng)) == 0, lib.vllm_last_error()
+    sp = lib.vllm_sampling_params_default()
+    sp.temperature, sp.max_tokens, sp.ignore_eos = 0.0, 12, 1
+    out = Completion()
+    assert lib.vllm_complete(eng, prompt.encode(), ctypes.byref(sp), ctypes.byref(out)) == 0
+    assert out.completion_tokens == 12 and ctypes.string_at(out.text).decode() == want.text
+    lib.vllm_completion_free(ctypes.byref(out))
+    # seeded sampling runs through the native host sampler and is reproducible
+    sp.temperature, sp.top_p, sp.top_k, sp.seed, sp.has_seed = 0.8, 0.9, 20, 7, 1
+    texts = []
+    for _ in range(2):
+        assert lib.vllm_complete(eng, prompt.encode(), ctypes.byref(sp), ctypes.byref(out)) == 0
+        texts.append(ctypes.string_at(out.text))
+        lib.vllm_completion_free(ctypes.byref(out))
+    assert texts[0] == texts[1]
+    lib.vllm_engine_free(eng)
+
+
+def test_models_outside_the_native_runtime_go_to_the_python_hosted_library(lib, tmp_path):
+    """A MoE checkpoint is not covered natively: the same entry point serves it through
+    libvllm_b200_py.so, loaded on demand."""
+    from vllm_cpp_b200 import loader
+    from vllm_cpp_b200.config import synthetic_config
+    d = loader.write_synthetic_checkpoint(str(tmp_path / "moe"), synthetic_config("tiny-moe"), seed=3)
+    mp = lib.vllm_model_params_default()
+    mp.model_path, mp.max_model_len, mp.block_size = d.encode(), 128, 16
+    eng = ctypes.c_void_p()
+    opt = cpu_options()
+    assert lib.vllm_engine_load_ex(ctypes.byref(mp), ctypes.byref(opt), ctypes.byref(eng)) == 0, lib.vllm_last_error()
+    sp = lib.vllm_sampling_params_default()
+    sp.temperature, sp.max_tokens = 0.0, 4
+    out = Completion()
+    assert lib.vllm_complete(eng, b"hello there", ctypes.byref(sp), ctypes.byref(out)) == 0, lib.vllm_last_error()
+    assert 0 < out.completion_tokens <= 4
+    lib.vllm_completion_free(ctypes.byref(out))
+    lib.vllm_engine_free(eng)

@@ -64,7 +64,7 @@ def build_kernels(verbose: bool = False) -> Path:
     objs = [objdir / (s.stem + ".o") for s in srcs]
     if jobs or not out.exists():
         _run([NVCC, "-shared", "-o", str(out), *map(str, objs), "-cudart", "shared",
-              "-Xlinker", f"-rpath={CUDA_HOME}/lib64"])
+              "-Xlinker", f"-rpath={CUDA_HOME}/lib64", "-Xlinker", "-soname=_kernels.so"])
     if verbose:
         print(f"built {out} from {len(srcs)} CUDA sources ({len(jobs)} recompiled)")
     return out
@@ -93,18 +93,72 @@ def build_engine(verbose: bool = False) -> Path:
             list(ex.map(_run, jobs))
     if jobs or not out.exists():
         _run([CXX, "-shared", "-o", str(out), *map(str, objs), "-pthread"])
-    build_capi(verbose)
     if verbose:
         print(f"built {out} from {len(srcs)} C++ sources ({len(jobs)} recompiled)")
     return out
 
 
+BINDING_STEMS = ("bindings", "tokenizer_bindings", "structured_bindings", "offload_bindings", "extras_bindings")
+
+
 def build_capi(verbose: bool = False) -> Path:
-    """``libvllm_b200.so``: the C interface of ``include/vllm.h``. It embeds the interpreter, so
-    it links against libpython; only the ``vllm_*`` symbols are exported."""
+    """The C interface of ``include/vllm.h``, twice:
+
+    ``libvllm_b200.so``     the native runtime (``csrc/runtime`` + the host engine objects), linked
+                            against libtorch (memory, streams), ``_kernels.so`` and ``_cpu.so``; no
+                            interpreter. Only the ``vllm_*`` symbols are exported.
+    ``libvllm_b200_py.so``  the same interface over the Python engine (embeds the interpreter); the
+                            native library loads it on demand for models it does not cover."""
+    build_capi_py(verbose)
     capi = PKG / "libvllm_b200.so"
-    srcs = sorted((CSRC / "capi").glob("*.cpp"))
-    if not srcs:
+    rt_srcs = sorted((CSRC / "runtime").glob("*.cpp")) + [CSRC / "capi" / "vllm_c.cpp"]
+    if not (CSRC / "runtime").exists():
+        return capi
+    eng_srcs = [s for s in sorted((CSRC / "engine").rglob("*.cpp")) if s.stem not in BINDING_STEMS]
+    hdrs = (sorted((CSRC / "runtime").glob("*.h")) + sorted((CSRC / "engine").rglob("*.h")) +
+            [ROOT / "include" / "vllm.h", CSRC / "kernels" / "api.h"])
+    from torch.utils import cpp_extension as ce
+    import torch
+    torch_inc = [x for p in ce.include_paths() for x in ("-I", p)]
+    torch_lib = ce.library_paths()[0]
+    abi = f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"
+    objdir = BUILD / "runtime"
+    objdir.mkdir(parents=True, exist_ok=True)
+    jobs, objs = [], []
+    for s in rt_srcs:
+        o = objdir / (s.stem + ".o")
+        objs.append(o)
+        if _newer(s, hdrs, o):
+            extra = torch_inc if s.stem == "tensor" else []      # the one libtorch translation unit
+            jobs.append([CXX, *CXX_FLAGS, abi, "-I", str(CUDA_HOME / "include"), *extra, "-c", str(s), "-o", str(o)])
+    eng_objdir = BUILD / "engine"
+    for s in eng_srcs:
+        o = eng_objdir / (str(s.relative_to(CSRC / "engine")).replace("/", "__")[:-4] + ".o")
+        objs.append(o)
+        if _newer(s, hdrs, o):
+            jobs.append([CXX, *CXX_FLAGS, "-c", str(s), "-o", str(o)])
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+            list(ex.map(_run, jobs))
+    deps = [PKG / "_kernels.so", PKG / "_cpu.so"]
+    if jobs or not capi.exists() or any(d.exists() and d.stat().st_mtime > capi.stat().st_mtime for d in deps):
+        _run([CXX, "-shared", "-o", str(capi), *map(str, objs), "-pthread", "-ldl",
+              f"-L{PKG}", "-l:_kernels.so", "-l:_cpu.so",
+              f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+              f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+              f"-Wl,--version-script={CSRC / 'capi' / 'export.map'}",
+              f"-Wl,-rpath,$ORIGIN:{torch_lib}:{CUDA_HOME / 'lib64'}", "-Wl,--no-as-needed"])
+        if verbose:
+            print(f"built {capi}")
+    return capi
+
+
+def build_capi_py(verbose: bool = False) -> Path:
+    """``libvllm_b200_py.so``: the C interface over the Python engine. It embeds the interpreter,
+    so it links against libpython; only the ``vllm_*`` symbols are exported."""
+    capi = PKG / "libvllm_b200_py.so"
+    srcs = [CSRC / "capi" / "vllm_c_py.cpp"]
+    if not srcs[0].exists():
         return capi
     hdrs = [ROOT / "include" / "vllm.h"]
     if any(_newer(s, hdrs, capi) for s in srcs):
@@ -128,7 +182,7 @@ def build_cpu(verbose: bool = False) -> Path:
     hdrs = sorted((CSRC / "cpu").glob("*.h"))
     if any(_newer(s, hdrs, out) for s in srcs):
         _run([CXX, "-O3", "-std=c++17", "-fPIC", "-Wall", "-pthread", "-ffp-contract=off",
-              "-fno-math-errno", "-shared", "-o", str(out), *map(str, srcs)])
+              "-fno-math-errno", "-shared", "-Wl,-soname,_cpu.so", "-o", str(out), *map(str, srcs)])
         if verbose:
             print(f"built {out} from {len(srcs)} C++ sources")
     return out
@@ -140,8 +194,7 @@ def build_sanitize_driver(kind: str = "address,undefined", verbose: bool = False
     scheduler, KV-cache manager, input batch, offload policies and the LMCache codec."""
     tag = kind.replace(",", "_")
     out = BUILD / f"sanitize_{tag}"
-    skip = ("bindings", "tokenizer_bindings", "structured_bindings", "offload_bindings", "extras_bindings")
-    srcs = [s for s in sorted((CSRC / "engine").rglob("*.cpp")) if s.stem not in skip]
+    srcs = [s for s in sorted((CSRC / "engine").rglob("*.cpp")) if s.stem not in BINDING_STEMS]
     srcs.append(CSRC / "engine_sanitize" / "sanitize_main.cpp")
     hdrs = sorted((CSRC / "engine").rglob("*.h"))
     BUILD.mkdir(parents=True, exist_ok=True)
@@ -161,6 +214,7 @@ def build_all(verbose: bool = False) -> None:
     if (CSRC / "engine").exists():
         build_engine(verbose)
     build_cpu(verbose)
+    build_capi(verbose)
 
 
 if __name__ == "__main__":

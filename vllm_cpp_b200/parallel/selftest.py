@@ -149,7 +149,9 @@ def bench_block(comm, device, results):
     H, I = 4096, 14336
     rows = []
     for T in (256, 2048, 8192):
-        tpf = TpFusedContext(comm, device, H, T)
+        # buffers sized like an engine's (its token budget, not this batch): small batches then have
+        # room for the k-split slots of the scatter GEMM
+        tpf = TpFusedContext(comm, device, H, max(T, 8192))
         a = torch.randn(T, I // W, device=device, dtype=torch.bfloat16)
         w_down = torch.randn(H, I // W, device=device, dtype=torch.bfloat16) * 0.02
         w_gu = torch.randn(2 * I // W, H, device=device, dtype=torch.bfloat16) * 0.02
