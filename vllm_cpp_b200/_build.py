@@ -150,6 +150,20 @@ def build_capi(verbose: bool = False) -> Path:
               f"-Wl,-rpath,$ORIGIN:{torch_lib}:{CUDA_HOME / 'lib64'}", "-Wl,--no-as-needed"])
         if verbose:
             print(f"built {capi}")
+    # native executables over the same objects (everything but the C interface)
+    bindir = PKG / "bin"
+    bindir.mkdir(exist_ok=True)
+    lib_objs = [o for o in objs if o.stem != "vllm_c"]
+    for tool, src in (("b200-bench", CSRC / "tools" / "bench_main.cpp"), ("b200-cli", CSRC / "tools" / "cli_main.cpp")):
+        exe = bindir / tool
+        if src.exists() and (jobs or _newer(src, hdrs, exe)):
+            _run([CXX, *CXX_FLAGS, "-o", str(exe), str(src), *map(str, lib_objs), "-pthread", "-ldl",
+                  f"-L{PKG}", "-l:_kernels.so", "-l:_cpu.so",
+                  f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
+                  f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+                  f"-Wl,-rpath,$ORIGIN/..:{torch_lib}:{CUDA_HOME / 'lib64'}", "-Wl,--no-as-needed"])
+            if verbose:
+                print(f"built {exe}")
     return capi
 
 
