@@ -231,6 +231,72 @@ def run_reference(args) -> int:
     return 0
 
 
+def closed_loop(llm, torch, new_prompt, SamplingParams, concurrency: int, num_requests: int, out_len: int):
+    """Runs ``num_requests`` requests with at most ``concurrency`` in flight to completion and
+    times everything on the device: every step is bracketed by CUDA events, the timeline of a
+    request is the event time between the first step that carried it and the steps that produced
+    its first and last token. Returns output tok/s over the event timeline and p50 TTFT / TPOT."""
+    r = llm.runner
+    r.step_events = []
+    r.time_steps = True
+    submitted_at, first_at, last_at, count = {}, {}, {}, {}
+    step_reqs = []                     # per engine step: (ids submitted before it, outputs)
+    pending, done, nxt = [], 0, 0
+
+    def admit():
+        nonlocal nxt
+        while nxt < num_requests and len(submitted_at) - done < concurrency:
+            rid = llm.add_request(new_prompt(), SamplingParams(temperature=0.0, max_tokens=out_len, ignore_eos=True))
+            submitted_at[rid] = None
+            pending.append(rid)
+            nxt += 1
+
+    admit()
+    step_no = 0
+    while done < num_requests:
+        n_ev = len(r.step_events)
+        outs = llm.step()
+        ran = len(r.step_events) > n_ev
+        if ran:
+            for rid in pending:
+                submitted_at[rid] = len(r.step_events) - 1          # index of the first step that could carry it
+            pending.clear()
+        for st in outs:
+            rid = st.request_id
+            ev = len(r.step_events) - 1
+            if rid not in first_at:
+                first_at[rid] = ev
+            last_at[rid] = ev
+            count[rid] = count.get(rid, 0) + 1
+            if st.finished:
+                done += 1
+        admit()
+        step_no += 1
+        if step_no > 200000:
+            break
+    torch.cuda.synchronize()
+    ev = [e for e in r.step_events if e[1] is not None]
+    r.time_steps = False
+    r.step_events = []
+    if not ev:
+        return None
+    t0 = ev[0][0]
+    start = [t0.elapsed_time(a) for a, _ in ev]
+    end = [t0.elapsed_time(b) for _, b in ev]
+    # async scheduling delivers a step's tokens one call later: clamp indices into the recorded range
+    def E(i):
+        return end[min(max(i, 0), len(end) - 1)]
+    ttft = sorted(E(first_at[x]) - start[min(submitted_at[x] or 0, len(start) - 1)] for x in first_at
+                  if submitted_at.get(x) is not None)
+    tpot = sorted((E(last_at[x]) - E(first_at[x])) / (count[x] - 1) for x in first_at if count.get(x, 0) > 1)
+    tokens = sum(count.values())
+    return {"concurrency": concurrency, "requests": num_requests, "output_tokens": tokens,
+            "device_s": round(end[-1] / 1e3, 4), "output_tok_s": round(tokens / (end[-1] / 1e3), 2),
+            "p50_ttft_ms": round(ttft[len(ttft) // 2], 2) if ttft else None,
+            "p50_tpot_ms": round(tpot[len(tpot) // 2], 3) if tpot else None,
+            "timing": "CUDA events around every step, one timeline per run"}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -257,6 +323,8 @@ def main() -> int:
     ap.add_argument("--watchdog", type=int, default=1500,
                     help="seconds after which every rank dumps its Python stacks and exits")
     ap.add_argument("--max-num-batched-tokens", type=int, default=8192)
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra keys (the whole offline batch and the concurrency sweep)")
     ap.add_argument("--sync-scheduling", action="store_true",
                     help="schedule step N+1 only after step N's tokens are on the host")
     args = ap.parse_args()
@@ -449,6 +517,22 @@ def main() -> int:
                    "region; worst rank"}
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / (wall_ms / 1e3)
+    # ---- extra keys, outside the timed region: the whole offline batch of the configuration
+    # (C requests submitted at once, run to completion) and the online sweep at lower concurrency
+    extras = {}
+    if not args.no_extras and not dp:
+        try:
+            while llm.has_unfinished_requests():       # drain the steady-state requests
+                llm.step()
+            t_submit.clear(); t_first.clear(); n_out.clear()
+            extras["offline_batch"] = closed_loop(llm, torch, new_prompt, SamplingParams, C_total, C_total, OUT)
+            sweep = []
+            for c in (1, 8, 64):
+                if c < C_total:
+                    sweep.append(closed_loop(llm, torch, new_prompt, SamplingParams, c, max(2, min(2 * c, 64)), OUT))
+            extras["online_sweep"] = sweep
+        except Exception as e:   # the headline number above stands on its own
+            extras["error"] = f"{type(e).__name__}: {e}"
     if rank == 0:
         print(json.dumps({
             "metric": "output_tokens_per_s", "value": round(value, 2), "unit": "tok/s",
@@ -478,6 +562,7 @@ def main() -> int:
             "e2e": {"value": round(e2e, 2), "unit": "tok/s", "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h), "wall_ms_per_step": round(wall_ms / args.steps, 4)},
             "gpu_launches": int(launches), "output_tokens": tokens, "kernel_status": status,
+            **extras,
         }))
     if world > 1:
         # Orderly teardown: nothing in flight on any rank, drop what holds the communicator (the
