@@ -186,6 +186,7 @@ int b200_moe_router_topk(const void* logits_f32, int ld, int T, int E, int k, in
 int b200_moe_sort(const void* topk_ids, int T, int k, int e0, int e1, void* meta, void* sorted_token, void* pair_pos, void* chunk_expert, void* chunk_row0, void* chunk_n, int max_chunks, cudaStream_t stream);
 int b200_moe_gather(const void* x, int ldx, const void* sorted_token, const void* meta, int E, void* xs, int H, int max_rows, cudaStream_t stream);
 int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, int N, int K, void* out, const void* chunk_expert, const void* chunk_row0, const void* chunk_n, const void* meta, int max_chunks, cudaStream_t stream);
+int b200_moe_grouped_gemm_gated(const void* xs, int max_rows, const void* W, int E, int N, int K, void* out, const void* chunk_expert, const void* chunk_row0, const void* chunk_n, const void* meta, int max_chunks, int kind, cudaStream_t stream);
 int b200_moe_combine(const void* y, const void* pair_pos, const void* topk_w, int T, int k, int H, const void* shared, const void* shared_gate, void* out, const B200MoeScatter* sc, cudaStream_t stream);
 int b200_shared_gate(const void* x, int ldx, const void* w, int T, int H, void* out, cudaStream_t stream);
 // ---- norm_act.cu

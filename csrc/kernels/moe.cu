@@ -189,7 +189,12 @@ struct GroupedParams {
   const int32_t* meta;
   int E;
   int stages;
-  int act_silu;             // fuse silu(gate)*up when the weight rows are [gate(I) | up(I)]?  (unused)
+  // Gated mode (act_fuse = activation kind + 1): W_e is [gate rows (N/2) | up rows (N/2)]; a CTA
+  // takes 128 gate rows and the 128 up rows of the same outputs, keeps one accumulator for each in
+  // TMEM (columns [0, np) and [256, 256 + np)) and writes act(gate) * up to out[rows, N / 2], so the
+  // merged projection never reaches memory. Both values are rounded to bf16 first, as the separate
+  // activation kernel would see them.
+  int act_fuse;
   int* status;
 };
 struct alignas(8) GroupedBars {
@@ -210,7 +215,9 @@ __global__ void __launch_bounds__(192, 1)
   const int np = (rows + 15) & ~15;                 // UMMA N
   constexpr int kWBytes = kGBM * kGBK * 2;
   constexpr int kXBytes = 256 * kGBK * 2;           // TMA box is always 256 rows
-  constexpr int kStage = kWBytes + kXBytes;
+  const bool gated = p.act_fuse != 0;
+  const int half_n = p.N >> 1;                      // gated: outputs per expert
+  const int kStage = kWBytes * (gated ? 2 : 1) + kXBytes;
   const int stages = p.stages;
   GroupedBars* bars = reinterpret_cast<GroupedBars*>(smem + (size_t)stages * kStage);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -221,11 +228,13 @@ __global__ void __launch_bounds__(192, 1)
     mbar_init(&bars->acc_full, 1);
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc(&bars->tmem_base, 256); tmem_relinquish(); }
+  const uint32_t tmem_cols = gated ? 512 : 256;
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, tmem_cols); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
+  const int x_off = kWBytes * (gated ? 2 : 1);
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tmW);
@@ -236,7 +245,8 @@ __global__ void __launch_bounds__(192, 1)
         uint8_t* wd = smem + (size_t)s * kStage;
         mbar_expect_tx(&bars->full[s], kStage);
         tma_load_3d(wd, &tmW, &bars->full[s], i * kGBK, tn * kGBM, e);
-        tma_load_2d(wd + kWBytes, &tmX, &bars->full[s], i * kGBK, row0);
+        if (gated) tma_load_3d(wd + kWBytes, &tmW, &bars->full[s], i * kGBK, half_n + tn * kGBM, e);
+        tma_load_2d(wd + x_off, &tmX, &bars->full[s], i * kGBK, row0);
       }
     }
   } else if (warp == 1) {
@@ -247,14 +257,48 @@ __global__ void __launch_bounds__(192, 1)
         const int s = i % stages;
         if (!mbar_wait(&bars->full[s], (i / stages) & 1, p.status)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t wa = smem_u32(smem + (size_t)s * kStage), xa = wa + kWBytes;
+        const uint32_t wa = smem_u32(smem + (size_t)s * kStage), xa = wa + x_off;
 #pragma unroll
-        for (int kk = 0; kk < kGBK / 16; ++kk)
+        for (int kk = 0; kk < kGBK / 16; ++kk) {
           umma_bf16_ss(tmem_base, umma_desc_k_sw128(wa + kk * 32, 1024),
                        umma_desc_k_sw128(xa + kk * 32, 1024), idesc, (i | kk) != 0);
+          if (gated)
+            umma_bf16_ss(tmem_base + 256, umma_desc_k_sw128(wa + kWBytes + kk * 32, 1024),
+                         umma_desc_k_sw128(xa + kk * 32, 1024), idesc, (i | kk) != 0);
+        }
         umma_commit(&bars->empty[s]);
       }
       if (ok) umma_commit(&bars->acc_full);
+    }
+  } else if (gated) {
+    const int quarter = warp & 3;
+    bool ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full, 0, p.status));
+    tc_fence_after_sync();
+    const int n = tn * kGBM + quarter * 32 + lane;        // output column of this thread
+    const uint32_t ta = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int kind = p.act_fuse - 1;
+    if (ok) {
+      for (int c = 0; c < np / 16; ++c) {
+        uint32_t g[16], u[16];
+        tmem_ld_32x32b_x16(ta + c * 16, g);
+        tmem_ld_32x32b_x16(ta + 256 + c * 16, u);
+        tmem_ld_wait();
+        if (n < half_n) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c * 16 + i;
+            if (m < rows) {
+              const float gg = __bfloat162float(__float2bfloat16(__uint_as_float(g[i])));
+              const float uu = __bfloat162float(__float2bfloat16(__uint_as_float(u[i])));
+              float a;
+              if (kind == 0) a = gg / (1.f + __expf(-gg));
+              else if (kind == 1) a = 0.5f * gg * (1.f + tanhf(0.7978845608028654f * (gg + 0.044715f * gg * gg * gg)));
+              else a = 0.5f * gg * (1.f + erff(gg * 0.7071067811865476f));
+              p.out[(size_t)(row0 + m) * half_n + n] = __float2bfloat16(a * uu);
+            }
+          }
+        }
+      }
     }
   } else {
     const int quarter = warp & 3;
@@ -281,7 +325,7 @@ __global__ void __launch_bounds__(192, 1)
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
 }
 
 // ---------------------------------------------------------------------------------- combine
@@ -429,12 +473,13 @@ int b200_moe_gather(const void* x, int ldx, const void* sorted_token, const void
 }
 
 // out[P, N] = grouped(xs[P, K], W[E, N, K]); xs must have at least max_rows + 256 rows allocated.
-int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, int N, int K,
-                          void* out, const void* chunk_expert, const void* chunk_row0,
-                          const void* chunk_n, const void* meta, int max_chunks,
-                          cudaStream_t stream) {
+static int moe_grouped_gemm_impl(const void* xs, int max_rows, const void* W, int E, int N, int K,
+                                 void* out, const void* chunk_expert, const void* chunk_row0,
+                                 const void* chunk_n, const void* meta, int max_chunks, int act_fuse,
+                                 cudaStream_t stream) {
   if (max_rows <= 0) return 0;
   if ((K & 7) || (N & 7)) return -1;
+  if (act_fuse && ((N & 1) || ((N / 2) & 7) || act_fuse < 1 || act_fuse > 3)) return -1;
   static std::mutex mu;
   CUtensorMap tmW, tmX;
   if (!encode_tmap_3d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
@@ -448,21 +493,38 @@ int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, in
   p.N = N; p.K = K; p.out = (bf16*)out;
   p.chunk_expert = (const int32_t*)chunk_expert; p.chunk_row0 = (const int32_t*)chunk_row0;
   p.chunk_n = (const int32_t*)chunk_n; p.meta = (const int32_t*)meta; p.E = E;
-  constexpr int stage = kGBM * kGBK * 2 + 256 * kGBK * 2;
+  const int stage = kGBM * kGBK * 2 * (act_fuse ? 2 : 1) + 256 * kGBK * 2;
   int stages = (200 * 1024) / stage;
   if (stages > kGMaxStages) stages = kGMaxStages;
   const int nkb = (K + kGBK - 1) / kGBK;
   if (stages > nkb) stages = nkb < 2 ? 2 : nkb;
-  p.stages = stages; p.act_silu = 0; p.status = device_status_word();
+  p.stages = stages; p.act_fuse = act_fuse; p.status = device_status_word();
   const size_t smem = (size_t)stages * stage + 1024 + sizeof(GroupedBars);
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(moe_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          220 * 1024);
   }
-  dim3 grid((N + kGBM - 1) / kGBM, max_chunks);
+  dim3 grid(((act_fuse ? N / 2 : N) + kGBM - 1) / kGBM, max_chunks);
   moe_grouped_gemm_kernel<<<grid, 192, smem, stream>>>(tmW, tmX, p);
   RETL;
+}
+
+int b200_moe_grouped_gemm(const void* xs, int max_rows, const void* W, int E, int N, int K,
+                          void* out, const void* chunk_expert, const void* chunk_row0,
+                          const void* chunk_n, const void* meta, int max_chunks,
+                          cudaStream_t stream) {
+  return moe_grouped_gemm_impl(xs, max_rows, W, E, N, K, out, chunk_expert, chunk_row0, chunk_n, meta, max_chunks, 0,
+                               stream);
+}
+// Gate / up projection with the gated activation in the epilogue: W [E, 2 I, K] with rows
+// [gate (I) | up (I)], out[P, I] = act(xs W_gate^T) * (xs W_up^T). kind: 0 SiLU, 1 GELU-tanh, 2 GELU-erf.
+int b200_moe_grouped_gemm_gated(const void* xs, int max_rows, const void* W, int E, int N, int K,
+                                void* out, const void* chunk_expert, const void* chunk_row0,
+                                const void* chunk_n, const void* meta, int max_chunks, int kind,
+                                cudaStream_t stream) {
+  return moe_grouped_gemm_impl(xs, max_rows, W, E, N, K, out, chunk_expert, chunk_row0, chunk_n, meta, max_chunks,
+                               kind + 1, stream);
 }
 
 

@@ -41,6 +41,10 @@ def test_router_grouped_sigmoid_bias():
     assert torch.allclose(w.sum(-1), ew.sum(-1), atol=1e-5)
 
 
+def local_pairs(ids, e0, el):
+    return int(((ids >= e0) & (ids < e0 + el)).sum().item())
+
+
 @pytest.mark.parametrize("T,E,k,H,I,e0,el", [(5, 8, 2, 256, 128, 0, 8), (300, 16, 4, 512, 256, 0, 16),
                                              (700, 8, 2, 256, 128, 4, 4), (64, 128, 8, 2048, 768, 0, 128)])
 def test_moe_block_matches_reference(T, E, k, H, I, e0, el):
@@ -58,6 +62,11 @@ def test_moe_block_matches_reference(T, E, k, H, I, e0, el):
     M.moe_gather(x, ws, el, P)
     M.grouped_gemm(ws.xs, wgu, ws.gu, ws, P)
     ops.act_and_mul(ws.gu[:P], 0, out=ws.act[:P])
+    # the gated grouped GEMM (both halves in TMEM, activation in the epilogue) gives the same bits
+    unfused = ws.act[:local_pairs(ids, e0, el)].clone()
+    ws.act.zero_()
+    M.grouped_gemm_gated(ws.xs, wgu, ws.act, ws, P, kind=0)
+    assert torch.equal(ws.act[:unfused.shape[0]], unfused)
     M.grouped_gemm(ws.act, wd, ws.y, ws, P)
     out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
     M.combine(ws.y, ws, w, out)

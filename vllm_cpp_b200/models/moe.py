@@ -14,6 +14,8 @@ Reference forward: ``src/vllm/model_executor/models/qwen3_moe.cpp:64-95`` and ``
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config import ModelConfig, ParallelConfig
@@ -194,8 +196,11 @@ class MoeModel(DenseModel):
         P = T * self.k
         chunks = min(ws.max_chunks, self.e_local + (P + 255) // 256)
         M.moe_gather(x, ws, self.e_local, P)
-        M.grouped_gemm(ws.xs, L["w_gate_up"], ws.gu, ws, P, chunks)
-        self.be.act_and_mul(ws.gu[:P], ACT_KIND.get(c.hidden_act, 0), out=ws.act[:P])
+        if os.environ.get("B200_MOE_FUSED_ACT", "1") != "0":
+            M.grouped_gemm_gated(ws.xs, L["w_gate_up"], ws.act, ws, P, chunks, kind=ACT_KIND.get(c.hidden_act, 0))
+        else:
+            M.grouped_gemm(ws.xs, L["w_gate_up"], ws.gu, ws, P, chunks)
+            self.be.act_and_mul(ws.gu[:P], ACT_KIND.get(c.hidden_act, 0), out=ws.act[:P])
         M.grouped_gemm(ws.act, L["w_down"], ws.y, ws, P, chunks)
         out = None if scatter is not None else self.bufs.get("moe_out", T, c.hidden_size)
         M.combine(ws.y, ws, w, out, scatter=scatter)

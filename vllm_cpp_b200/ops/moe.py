@@ -29,6 +29,7 @@ def _declare():
     _lib.declare("b200_moe_sort", [P, I, I, I, I, P, P, P, P, P, P, I, P], I)
     _lib.declare("b200_moe_gather", [P, I, P, P, I, P, I, I, P], I)
     _lib.declare("b200_moe_grouped_gemm", [P, I, P, I, I, I, P, P, P, P, P, I, P], I)
+    _lib.declare("b200_moe_grouped_gemm_gated", [P, I, P, I, I, I, P, P, P, P, P, I, I, P], I)
     _lib.declare("b200_moe_combine", [P, P, P, I, I, I, P, P, P, ctypes.POINTER(B200MoeScatter), P], I)
     _lib.declare("b200_shared_gate", [P, I, P, I, I, P, P], I)
     lib()
@@ -97,6 +98,20 @@ def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ws: MoeWo
                                       ptr(ws.chunk_expert), ptr(ws.chunk_row0), ptr(ws.chunk_n),
                                       ptr(ws.meta), max_chunks or ws.max_chunks, stream_ptr()),
           "moe_grouped_gemm")
+    return out
+
+
+def grouped_gemm_gated(xs: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, ws: MoeWorkspace,
+                       max_rows: int, max_chunks: int | None = None, kind: int = 0):
+    """out[pos] = act(xs[pos] @ w_gate^T) * (xs[pos] @ w_up^T); ``w_gate_up``: [E, 2 I, K] with rows
+    [gate | up]. One kernel: both halves accumulate in TMEM and the activation runs in the
+    epilogue, so the merged projection is never written."""
+    _declare()
+    E, N, K = w_gate_up.shape
+    check(lib().b200_moe_grouped_gemm_gated(ptr(xs), max_rows, ptr(w_gate_up), E, N, K, ptr(out),
+                                            ptr(ws.chunk_expert), ptr(ws.chunk_row0), ptr(ws.chunk_n),
+                                            ptr(ws.meta), max_chunks or ws.max_chunks, kind, stream_ptr()),
+          "moe_grouped_gemm_gated")
     return out
 
 
