@@ -522,15 +522,20 @@ def main() -> int:
     extras = {}
     if not args.no_extras and not dp:
         try:
+            note("extras: draining the steady-state requests")
             while llm.has_unfinished_requests():       # drain the steady-state requests
                 llm.step()
+            torch.cuda.synchronize()
             t_submit.clear(); t_first.clear(); n_out.clear()
+            note("extras: offline batch")
             extras["offline_batch"] = closed_loop(llm, torch, new_prompt, SamplingParams, C_total, C_total, OUT)
             sweep = []
             for c in (1, 8, 64):
                 if c < C_total:
+                    note(f"extras: concurrency {c}")
                     sweep.append(closed_loop(llm, torch, new_prompt, SamplingParams, c, max(2, min(2 * c, 64)), OUT))
             extras["online_sweep"] = sweep
+            note("extras done")
         except Exception as e:   # the headline number above stands on its own
             extras["error"] = f"{type(e).__name__}: {e}"
     if rank == 0:

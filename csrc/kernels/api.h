@@ -172,6 +172,7 @@ int b200_quant_nvfp4(const void* x, long ldx, const float* gscale, void* out, vo
 int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out, int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes, cudaStream_t stream);
 // ---- layer.cu
 void b200_dense_layer_abi(int* out4);
+int b200_dense_attn_half(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream);
 int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream);
 void b200_tp_layers_abi(int* out2);
 int b200_dense_layers_tp(const B200DenseLayerWeights* w, int num_layers, const B200DenseStep* s, const B200TpLayers* c, cudaStream_t stream);

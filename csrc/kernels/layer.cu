@@ -35,14 +35,15 @@ void b200_dense_layer_abi(int* out4) {
   out4[3] = (int)offsetof(B200DenseStep, first_layer);
 }
 
-// Returns the number of launcher calls made (>= 1 kernel each), or a negative error code.
-int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream) {
+// Attention half of a block: (add+)RMSNorm -> QKV GEMM -> qk-norm / RoPE / KV-cache write ->
+// paged attention (decode rows, then prefill tiles) -> o_proj GEMM into s->hidden. Returns the
+// number of launcher calls made or a negative error code.
+int b200_dense_attn_half(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream) {
   if (!w || !s || s->T <= 0) return 0;
   int launches = 0;
   const int T = s->T, H = s->H, D = s->D, Hq = s->Hq, Hkv = s->Hkv;
   const int qkv_w = (Hq + 2 * Hkv) * D;
   using bf16 = __nv_bfloat16;
-  // ---- attention block
   if (s->first_layer) {
     if (cudaMemcpyAsync(s->resid, s->hidden, (size_t)T * H * sizeof(bf16), cudaMemcpyDeviceToDevice, stream) !=
         cudaSuccess)
@@ -79,6 +80,16 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
   }
   B200_TRY(b200_gemm_bf16(s->attn, Hq * D, w->o, Hq * D, s->hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D,
                           s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
+  return launches;
+}
+
+// Whole block: the attention half, then add+RMSNorm and the gated MLP into s->hidden.
+// Returns the number of launcher calls made (>= 1 kernel each), or a negative error code.
+int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cudaStream_t stream) {
+  if (!w || !s || s->T <= 0) return 0;
+  int launches = b200_dense_attn_half(w, s, stream);
+  if (launches < 0) return launches;
+  const int T = s->T, H = s->H;
   // ---- MLP block
   B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln2, s->normed, H, T, H, s->eps, s->gemma, stream));
   const int I = s->inter;
@@ -94,7 +105,6 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
                           (size_t)s->gemm_ws_bytes, kConstW, stream));
   return launches;
 }
-
 
 // ---- tensor-parallel stack ----------------------------------------------------------------
 void b200_tp_layers_abi(int* out2) {

@@ -1,8 +1,10 @@
 #include "runtime/dense_model.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <stdexcept>
+#include <vector>
 
 #include "kernels/api.h"
 #include "runtime/cpu_ops.h"
@@ -33,12 +35,13 @@ DenseConfig DenseConfig::from_hf(const Json& cfg_in) {
   DenseConfig c;
   const auto& archs = t["architectures"];
   c.architecture = archs.size() ? archs[0].as_string() : "LlamaForCausalLM";
-  static const char* kSupported[] = {"LlamaForCausalLM", "MistralForCausalLM", "Qwen3ForCausalLM"};
+  static const char* kSupported[] = {"LlamaForCausalLM", "MistralForCausalLM", "Qwen3ForCausalLM",
+                                     "Qwen3MoeForCausalLM"};
   bool ok = false;
   for (auto* a : kSupported) ok = ok || c.architecture == a;
   if (!ok)
     throw std::runtime_error("architecture " + c.architecture + " is not covered by the native runtime "
-                             "(dense Llama / Mistral / Qwen3 families)");
+                             "(Llama / Mistral / Qwen3 / Qwen3-MoE families)");
   c.hidden = (int)t["hidden_size"].as_int();
   c.heads = (int)t["num_attention_heads"].as_int();
   c.head_dim = (int)t["head_dim"].as_int(c.heads ? c.hidden / c.heads : 0);
@@ -49,7 +52,17 @@ DenseConfig DenseConfig::from_hf(const Json& cfg_in) {
   c.eps = (float)t["rms_norm_eps"].as_double(1e-6);
   c.max_position = (int)t["max_position_embeddings"].as_int(8192);
   c.tie_embeddings = t["tie_word_embeddings"].as_bool(false);
-  c.qk_norm = c.architecture == "Qwen3ForCausalLM";
+  c.qk_norm = c.architecture == "Qwen3ForCausalLM" || c.architecture == "Qwen3MoeForCausalLM";
+  if (c.architecture == "Qwen3MoeForCausalLM") {
+    c.num_experts = (int)t["num_experts"].as_int();
+    c.experts_per_token = (int)t["num_experts_per_tok"].as_int();
+    c.moe_inter = (int)t["moe_intermediate_size"].as_int();
+    c.norm_topk_prob = t["norm_topk_prob"].as_bool(true);
+    if (c.num_experts <= 0 || c.experts_per_token <= 0 || c.experts_per_token > c.num_experts || c.moe_inter <= 0)
+      throw std::runtime_error("config.json: inconsistent mixture-of-experts shape");
+    if (t["mlp_only_layers"].size() > 0 || t["decoder_sparse_step"].as_int(1) != 1)
+      throw std::runtime_error("mixed dense / sparse layer patterns are not covered by the native runtime");
+  }
   const std::string act = t["hidden_act"].is_string() ? t["hidden_act"].as_string() : "silu";
   if (act == "silu") c.act_kind = 0;
   else if (act == "gelu_tanh" || act == "gelu_pytorch_tanh") c.act_kind = 1;
@@ -188,22 +201,44 @@ void DenseModel::load_weights(const std::string& model_dir) {
     L.qkv = put(stage.data(), stage.size());
     const TensorView& o = bf16(p + "self_attn.o_proj.weight", {c.hidden, (int64_t)c.heads * c.head_dim});
     L.o = put(o.data, o.nbytes);
-    const TensorView& g = bf16(p + "mlp.gate_proj.weight", {c.inter, c.hidden});
-    const TensorView& u = bf16(p + "mlp.up_proj.weight", {c.inter, c.hidden});
-    stage.resize(g.nbytes + u.nbytes);
     const size_t row = H * 2;
-    if (gate_up_interleaved_) {
-      for (int b = 0; b < c.inter / 128; ++b) {
-        std::memcpy(stage.data() + (size_t)(2 * b) * 128 * row, g.data + (size_t)b * 128 * row, 128 * row);
-        std::memcpy(stage.data() + (size_t)(2 * b + 1) * 128 * row, u.data + (size_t)b * 128 * row, 128 * row);
+    if (c.num_experts > 0) {
+      const int E = c.num_experts, I = c.moe_inter;
+      const TensorView& rt = bf16(p + "mlp.gate.weight", {E, c.hidden});
+      L.router = put(rt.data, rt.nbytes);
+      const size_t gu_bytes = (size_t)2 * I * row, dn_bytes = (size_t)c.hidden * I * 2;
+      // experts are uploaded one at a time into the stacked device tensors (no host copy of all)
+      L.w_gate_up = alloc((size_t)E * gu_bytes, dev_);
+      L.w_down = alloc((size_t)E * dn_bytes, dev_);
+      weight_bytes_ += (int64_t)E * (int64_t)(gu_bytes + dn_bytes);
+      for (int e = 0; e < E; ++e) {
+        const std::string q2 = p + "mlp.experts." + std::to_string(e) + ".";
+        const TensorView& g = bf16(q2 + "gate_proj.weight", {I, c.hidden});
+        const TensorView& u = bf16(q2 + "up_proj.weight", {I, c.hidden});
+        const TensorView& dn = bf16(q2 + "down_proj.weight", {c.hidden, I});
+        uint8_t* gu_dst = L.w_gate_up.as<uint8_t>() + (size_t)e * gu_bytes;
+        copy(gu_dst, dev_, g.data, Device{}, g.nbytes);
+        copy(gu_dst + g.nbytes, dev_, u.data, Device{}, u.nbytes);
+        copy(L.w_down.as<uint8_t>() + (size_t)e * dn_bytes, dev_, dn.data, Device{}, dn.nbytes);
       }
+      if (dev_.cuda) synchronize(dev_);
     } else {
-      std::memcpy(stage.data(), g.data, g.nbytes);
-      std::memcpy(stage.data() + g.nbytes, u.data, u.nbytes);
+      const TensorView& g = bf16(p + "mlp.gate_proj.weight", {c.inter, c.hidden});
+      const TensorView& u = bf16(p + "mlp.up_proj.weight", {c.inter, c.hidden});
+      stage.resize(g.nbytes + u.nbytes);
+      if (gate_up_interleaved_) {
+        for (int b = 0; b < c.inter / 128; ++b) {
+          std::memcpy(stage.data() + (size_t)(2 * b) * 128 * row, g.data + (size_t)b * 128 * row, 128 * row);
+          std::memcpy(stage.data() + (size_t)(2 * b + 1) * 128 * row, u.data + (size_t)b * 128 * row, 128 * row);
+        }
+      } else {
+        std::memcpy(stage.data(), g.data, g.nbytes);
+        std::memcpy(stage.data() + g.nbytes, u.data, u.nbytes);
+      }
+      L.gate_up = put(stage.data(), stage.size());
+      const TensorView& dn = bf16(p + "mlp.down_proj.weight", {c.hidden, c.inter});
+      L.down = put(dn.data, dn.nbytes);
     }
-    L.gate_up = put(stage.data(), stage.size());
-    const TensorView& dn = bf16(p + "mlp.down_proj.weight", {c.hidden, c.inter});
-    L.down = put(dn.data, dn.nbytes);
     const TensorView& n1 = bf16(p + "input_layernorm.weight", {c.hidden});
     const TensorView& n2 = bf16(p + "post_attention_layernorm.weight", {c.hidden});
     L.ln1 = put(n1.data, n1.nbytes);
@@ -244,6 +279,22 @@ void DenseModel::reserve(int max_tokens, int max_reqs) {
   last_ = alloc((size_t)max_reqs * c.hidden * 2, dev_);
   logits_ = alloc((size_t)max_reqs * c.vocab_size * sizeof(float), dev_);
   if (dev_.cuda) gemm_ws_ = alloc(kGemmWsBytes, dev_);
+  if (c.num_experts > 0) {
+    const size_t P = T * c.experts_per_token, E = (size_t)c.num_experts;
+    max_chunks_ = (int)(E + (P + 255) / 256);
+    router_logits_ = alloc(T * E * sizeof(float), dev_);
+    topk_ids_ = alloc(P * 4, dev_);
+    topk_w_ = alloc(P * 4, dev_);
+    moe_meta_ = alloc((3 * E + 2) * 4, dev_, true);
+    sorted_token_ = alloc(P * 4, dev_, true);
+    pair_pos_ = alloc(P * 4, dev_, true);
+    chunk_expert_ = alloc((size_t)max_chunks_ * 4, dev_, true);
+    chunk_row0_ = alloc((size_t)max_chunks_ * 4, dev_, true);
+    chunk_n_ = alloc((size_t)max_chunks_ * 4, dev_, true);
+    xs_ = alloc((P + 256) * c.hidden * 2, dev_, true);
+    moe_act_ = alloc((P + 256) * c.moe_inter * 2, dev_, true);
+    moe_y_ = alloc((P + 256) * c.hidden * 2, dev_, true);
+  }
 }
 
 // ------------------------------------------------------------------------------- forward
@@ -310,9 +361,19 @@ void DenseModel::forward_cuda(const StepInputs& in) {
     w.o = L.o.data(); w.ln2 = L.ln2.data(); w.gate_up = L.gate_up.data(); w.down = L.down.data();
     w.kv_cache = L.kv_cache.data();
     st.first_layer = l == 0;
-    const int rc = b200_dense_layer(&w, &st, s);
-    check(rc, "dense_layer");
-    launches_ += rc;
+    if (c.num_experts > 0) {
+      const int rc = b200_dense_attn_half(&w, &st, s);
+      check(rc, "attention half");
+      launches_ += rc;
+      check(b200_rmsnorm(hidden_.data(), H, resid_.data(), L.ln2.data(), normed_.data(), H, T, H, c.eps, 0, s),
+            "post-attention norm");
+      ++launches_;
+      moe_cuda(L, T);
+    } else {
+      const int rc = b200_dense_layer(&w, &st, s);
+      check(rc, "dense_layer");
+      launches_ += rc;
+    }
   }
   check(b200_rmsnorm(hidden_.data(), H, resid_.data(), final_norm_.data(), normed_.data(), H, T, H, c.eps, 0, s),
         "final norm");
@@ -351,6 +412,10 @@ void DenseModel::forward_cpu(const StepInputs& in) {
                             in.query_start, in.num_reqs, Hq, Hkv, D, block_size_, scale_, 0.f, 0, attn, Hq * D);
     b200cpu_matmul_bt(attn, Hq * D, L.o.as<uint16_t>(), Hq * D, hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D);
     b200cpu_rmsnorm(hidden, H, L.ln2.as<uint16_t>(), c.eps, resid, H, normed, H, T, H, 0);
+    if (c.num_experts > 0) {
+      moe_cpu(L, T);
+      continue;
+    }
     b200cpu_matmul_bt(normed, H, L.gate_up.as<uint16_t>(), H, gate_up, 2 * I, 0, nullptr, nullptr, 0, T, 2 * I, H);
     b200cpu_act_and_mul(gate_up, 2 * I, act, I, T, I, c.act_kind);
     b200cpu_matmul_bt(act, I, L.down.as<uint16_t>(), I, hidden, H, 0, nullptr, nullptr, 0, T, H, I);
@@ -361,6 +426,111 @@ void DenseModel::forward_cpu(const StepInputs& in) {
     std::memcpy(last + (size_t)i * H, normed + (size_t)in.logits_indices[i] * H, (size_t)H * 2);
   b200cpu_matmul_bt(last, H, lm_head_.as<uint16_t>(), H, logits_.data(), c.vocab_size, 1, nullptr, nullptr, 0,
                     in.num_logits, c.vocab_size, H);
+}
+
+
+// ------------------------------------------------------------------------------- experts
+// Router GEMM (fp32 logits) -> softmax top-k -> device-side sort by expert -> gather -> grouped
+// gate/up GEMM with the gated activation in its epilogue -> grouped down GEMM -> weighted combine
+// into hidden_. Reference: src/vt/cuda/cuda_moe.cu:62,406 and qwen3_moe.cpp.
+void DenseModel::moe_cuda(const Layer& L, int T) {
+  const DenseConfig& c = cfg_;
+  cudaStream_t s = (cudaStream_t)current_stream(dev_);
+  const int H = c.hidden, E = c.num_experts, k = c.experts_per_token, I = c.moe_inter, P = T * k;
+  check(b200_gemm_bf16(normed_.data(), H, L.router.data(), H, router_logits_.data(), E, 1, nullptr, nullptr, 0, T, E,
+                       H, gemm_ws_.data(), gemm_ws_.nbytes(), kConstW, s), "router");
+  check(b200_moe_router_topk(router_logits_.data(), E, T, E, k, c.norm_topk_prob ? 1 : 0, 0, nullptr, 1, 1, 1.0f,
+                             topk_ids_.data(), topk_w_.data(), s), "router_topk");
+  check(b200_moe_sort(topk_ids_.data(), T, k, 0, E, moe_meta_.data(), sorted_token_.data(), pair_pos_.data(),
+                      chunk_expert_.data(), chunk_row0_.data(), chunk_n_.data(), max_chunks_, s), "moe_sort");
+  check(b200_moe_gather(normed_.data(), H, sorted_token_.data(), moe_meta_.data(), E, xs_.data(), H, P, s),
+        "moe_gather");
+  int chunks = E + (P + 255) / 256;
+  if (chunks > max_chunks_) chunks = max_chunks_;
+  check(b200_moe_grouped_gemm_gated(xs_.data(), P, L.w_gate_up.data(), E, 2 * I, H, moe_act_.data(),
+                                    chunk_expert_.data(), chunk_row0_.data(), chunk_n_.data(), moe_meta_.data(),
+                                    chunks, c.act_kind, s), "experts gate/up");
+  check(b200_moe_grouped_gemm(moe_act_.data(), P, L.w_down.data(), E, H, I, moe_y_.data(), chunk_expert_.data(),
+                              chunk_row0_.data(), chunk_n_.data(), moe_meta_.data(), chunks, s), "experts down");
+  check(b200_moe_combine(moe_y_.data(), pair_pos_.data(), topk_w_.data(), T, k, H, nullptr, nullptr, hidden_.data(),
+                         nullptr, s), "moe_combine");
+  launches_ += 7;
+}
+
+// The same block on the host: the thread-pool GEMM per expert over its gathered rows; fp32
+// accumulation per token in ascending expert order, one bf16 rounding at the end.
+void DenseModel::moe_cpu(const Layer& L, int T) {
+  const DenseConfig& c = cfg_;
+  const int H = c.hidden, E = c.num_experts, k = c.experts_per_token, I = c.moe_inter;
+  const uint16_t* x = normed_.as<uint16_t>();
+  float* logits = router_logits_.as<float>();
+  b200cpu_matmul_bt(x, H, L.router.as<uint16_t>(), H, logits, E, 1, nullptr, nullptr, 0, T, E, H);
+  std::vector<std::vector<int>> rows_of(E);
+  std::vector<std::vector<float>> weight_of(E);
+  std::vector<float> score(E);
+  for (int t = 0; t < T; ++t) {
+    const float* lr = logits + (size_t)t * E;
+    float mx = lr[0];
+    for (int e = 1; e < E; ++e) mx = std::max(mx, lr[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) { score[e] = std::exp(lr[e] - mx); sum += score[e]; }
+    for (int e = 0; e < E; ++e) score[e] /= sum;
+    int ids[64];
+    float w[64], wsum = 0.f;
+    std::vector<char> taken(E, 0);
+    for (int j = 0; j < k && j < 64; ++j) {       // ties go to the lowest expert index
+      int best = -1;
+      for (int e = 0; e < E; ++e)
+        if (!taken[e] && (best < 0 || score[e] > score[best])) best = e;
+      taken[best] = 1;
+      ids[j] = best;
+      w[j] = score[best];
+      wsum += w[j];
+    }
+    for (int j = 0; j < k && j < 64; ++j) {
+      rows_of[ids[j]].push_back(t);
+      weight_of[ids[j]].push_back(c.norm_topk_prob && wsum > 0 ? w[j] / wsum : w[j]);
+    }
+  }
+  std::vector<float> acc((size_t)T * H, 0.f);
+  std::vector<uint16_t> xs, gu, a, y;
+  const size_t gu_elems = (size_t)2 * I * H, dn_elems = (size_t)H * I;
+  for (int e = 0; e < E; ++e) {
+    const int n = (int)rows_of[e].size();
+    if (n == 0) continue;
+    xs.resize((size_t)n * H);
+    gu.resize((size_t)n * 2 * I);
+    a.resize((size_t)n * I);
+    y.resize((size_t)n * H);
+    for (int r = 0; r < n; ++r) std::memcpy(xs.data() + (size_t)r * H, x + (size_t)rows_of[e][r] * H, (size_t)H * 2);
+    b200cpu_matmul_bt(xs.data(), H, L.w_gate_up.as<uint16_t>() + (size_t)e * gu_elems, H, gu.data(), 2 * I, 0, nullptr,
+                      nullptr, 0, n, 2 * I, H);
+    b200cpu_act_and_mul(gu.data(), 2 * I, a.data(), I, n, I, c.act_kind);
+    b200cpu_matmul_bt(a.data(), I, L.w_down.as<uint16_t>() + (size_t)e * dn_elems, I, y.data(), H, 0, nullptr, nullptr, 0,
+                      n, H, I);
+    for (int r = 0; r < n; ++r) {
+      float* dst = acc.data() + (size_t)rows_of[e][r] * H;
+      const float wt = weight_of[e][r];
+      const uint16_t* src = y.data() + (size_t)r * H;
+      for (int i = 0; i < H; ++i) {
+        uint32_t bits = (uint32_t)src[i] << 16;
+        float v;
+        std::memcpy(&v, &bits, 4);
+        dst[i] += wt * v;
+      }
+    }
+  }
+  uint16_t* out = hidden_.as<uint16_t>();
+  for (size_t i = 0; i < acc.size(); ++i) {
+    uint32_t bits;
+    std::memcpy(&bits, &acc[i], 4);
+    if ((bits & 0x7fffffffu) > 0x7f800000u) {          // NaN stays NaN
+      out[i] = (uint16_t)((bits >> 16) | 0x40);
+    } else {
+      bits += 0x7fffu + ((bits >> 16) & 1);            // round to nearest even
+      out[i] = (uint16_t)(bits >> 16);
+    }
+  }
 }
 
 }  // namespace b200::rt

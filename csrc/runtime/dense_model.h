@@ -1,5 +1,6 @@
-// Native dense decoder (Llama / Mistral / Qwen3 shapes: pre-norm blocks, RMSNorm, rotary
-// embeddings, grouped-query attention over the paged KV cache, gated MLP, no biases): weights
+// Native decoder (Llama / Mistral / Qwen3 shapes: pre-norm blocks, RMSNorm, rotary embeddings,
+// grouped-query attention over the paged KV cache, gated MLP, no biases; Qwen3-MoE: the same
+// attention with a routed mixture of experts in place of the MLP): weights
 // read from safetensors into device memory, forward pass as a sequence of launcher calls —
 // the sm_100a kernel library on a GPU (one native call per block, csrc/kernels/layer.cu), the
 // thread-pool CPU kernels (csrc/cpu) otherwise. No interpreter is involved anywhere.
@@ -33,6 +34,9 @@ struct DenseConfig {
   int original_max_position = 8192;
   int rotary_dim = 0;                  // 0: head_dim
   int eos_token_id = -1, bos_token_id = -1;
+  // mixture of experts (Qwen3-MoE): 0 experts = dense MLP
+  int num_experts = 0, experts_per_token = 0, moe_inter = 0;
+  bool norm_topk_prob = true;
 
   // Throws std::runtime_error naming what the native runtime does not cover.
   static DenseConfig from_hf(const Json& cfg);
@@ -72,7 +76,10 @@ class DenseModel {
  private:
   struct Layer {
     Buffer ln1, qkv, q_norm, k_norm, o, ln2, gate_up, down, kv_cache;
+    Buffer router, w_gate_up, w_down;    // MoE: [E, H], [E, 2 I, H] rows [gate | up], [E, H, I]
   };
+  void moe_cuda(const Layer& L, int T);
+  void moe_cpu(const Layer& L, int T);
   Buffer upload(const void* src, size_t nbytes);
   void forward_cuda(const StepInputs& in);
   void forward_cpu(const StepInputs& in);
@@ -89,6 +96,10 @@ class DenseModel {
   Buffer hidden_, resid_, normed_, qkv_, attn_, gate_up_, act_, last_, logits_, gemm_ws_, decode_tmp_o_,
       decode_tmp_lse_, argmax_ws_;
   int decode_tmp_batch_ = 0, decode_tmp_splits_ = 0;
+  // MoE workspace (sized by reserve): router logits, top-k, expert-sorted rows
+  Buffer router_logits_, topk_ids_, topk_w_, moe_meta_, sorted_token_, pair_pos_, chunk_expert_, chunk_row0_,
+      chunk_n_, xs_, moe_act_, moe_y_;
+  int max_chunks_ = 0;
 };
 
 }  // namespace b200::rt
