@@ -211,15 +211,27 @@ void DenseModel::load_weights(const std::string& model_dir) {
       L.w_gate_up = alloc((size_t)E * gu_bytes, dev_);
       L.w_down = alloc((size_t)E * dn_bytes, dev_);
       weight_bytes_ += (int64_t)E * (int64_t)(gu_bytes + dn_bytes);
+      const bool stacked = st.has(p + "mlp.experts.gate_proj.weight");   // [E, I, H] / [E, H, I] tensors
+      const TensorView* sg = stacked ? &bf16(p + "mlp.experts.gate_proj.weight", {E, I, c.hidden}) : nullptr;
+      const TensorView* su = stacked ? &bf16(p + "mlp.experts.up_proj.weight", {E, I, c.hidden}) : nullptr;
+      const TensorView* sd = stacked ? &bf16(p + "mlp.experts.down_proj.weight", {E, c.hidden, I}) : nullptr;
       for (int e = 0; e < E; ++e) {
-        const std::string q2 = p + "mlp.experts." + std::to_string(e) + ".";
-        const TensorView& g = bf16(q2 + "gate_proj.weight", {I, c.hidden});
-        const TensorView& u = bf16(q2 + "up_proj.weight", {I, c.hidden});
-        const TensorView& dn = bf16(q2 + "down_proj.weight", {c.hidden, I});
+        const uint8_t *gp, *up, *dp;
+        const size_t half = (size_t)I * row;
+        if (stacked) {
+          gp = sg->data + (size_t)e * half;
+          up = su->data + (size_t)e * half;
+          dp = sd->data + (size_t)e * dn_bytes;
+        } else {
+          const std::string q2 = p + "mlp.experts." + std::to_string(e) + ".";
+          gp = bf16(q2 + "gate_proj.weight", {I, c.hidden}).data;
+          up = bf16(q2 + "up_proj.weight", {I, c.hidden}).data;
+          dp = bf16(q2 + "down_proj.weight", {c.hidden, I}).data;
+        }
         uint8_t* gu_dst = L.w_gate_up.as<uint8_t>() + (size_t)e * gu_bytes;
-        copy(gu_dst, dev_, g.data, Device{}, g.nbytes);
-        copy(gu_dst + g.nbytes, dev_, u.data, Device{}, u.nbytes);
-        copy(L.w_down.as<uint8_t>() + (size_t)e * dn_bytes, dev_, dn.data, Device{}, dn.nbytes);
+        copy(gu_dst, dev_, gp, Device{}, half);
+        copy(gu_dst + half, dev_, up, Device{}, half);
+        copy(L.w_down.as<uint8_t>() + (size_t)e * dn_bytes, dev_, dp, Device{}, dn_bytes);
       }
       if (dev_.cuda) synchronize(dev_);
     } else {

@@ -91,12 +91,13 @@ def ckpt(tmp_path_factory):
     return loader.write_synthetic_checkpoint(str(tmp_path_factory.mktemp("c") / "ck"), synthetic_config("tiny-qwen3"), seed=5)
 
 
-@pytest.fixture(scope="module")
-def ckpt_gpu(tmp_path_factory):
-    """A Qwen3-shaped checkpoint with head_dim 128 (the tensor-core attention kernels' shape)."""
+@pytest.fixture(scope="module", params=["tiny-qwen3", "tiny-moe"])
+def ckpt_gpu(request, tmp_path_factory):
+    """Dense and mixture-of-experts checkpoints with head_dim 128 (the tensor-core attention
+    kernels' shape)."""
     from vllm_cpp_b200 import loader
     from vllm_cpp_b200.config import synthetic_config
-    cfg = synthetic_config("tiny-qwen3")
+    cfg = synthetic_config(request.param)
     cfg.head_dim = 128
     return loader.write_synthetic_checkpoint(str(tmp_path_factory.mktemp("g") / "ck"), cfg, seed=6)
 

@@ -124,11 +124,29 @@ _CODES = {-1: "rejected shape/alignment", -2: "launch failure", -3: "tensor-map 
 
 LAUNCHES = [0]  # launcher calls made by this process (each launches >= 1 kernel)
 
+# B200_SYNC_CHECK=1: synchronise the device after every launcher call and name the first one
+# after which the device reports an error (asynchronous faults otherwise surface far from
+# their cause). A debugging aid: it serialises host and device.
+SYNC_CHECK = os.environ.get("B200_SYNC_CHECK", "0") == "1"
+
+
+def sync_check(what: str) -> None:
+    try:
+        torch.cuda.synchronize()
+    except Exception as e:  # the context is gone: report and leave without running destructors
+        import sys
+        sys.stderr.write(f"\nB200_SYNC_CHECK: the device reported an error after launcher '{what}': "
+                         f"{str(e).splitlines()[0]}\n")
+        sys.stderr.flush()
+        os._exit(3)
+
 
 def check(rc: int, what: str) -> None:
     LAUNCHES[0] += 1
     if rc != 0:
         raise KernelError(f"{what}: {_CODES.get(rc, 'error')} (code {rc})")
+    if SYNC_CHECK:
+        sync_check(what)
 
 
 _RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)

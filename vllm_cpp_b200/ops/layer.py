@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import ctypes as C
 
+from . import _lib as _lib_mod
 from ._lib import LAUNCHES, KernelError, lib, stream_ptr
 
 P, I, F = C.c_void_p, C.c_int, C.c_float
@@ -41,6 +42,9 @@ def dense_layer(weights: DenseLayerWeights, step: DenseStep) -> None:
     if rc < 0:
         raise KernelError(f"dense_layer: kernel launcher returned {rc}")
     LAUNCHES[0] += rc
+    if _lib_mod.SYNC_CHECK:
+        _lib_mod.sync_check(f"dense_layer T={step.T} decodes={step.num_decodes} prefills={step.num_prefills} "
+                            f"splits={step.decode_splits}")
 
 
 class TpLayers(C.Structure):

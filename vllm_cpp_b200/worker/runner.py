@@ -350,6 +350,8 @@ class ModelRunner(E.ModelRunnerBase):
             g = self.graphs.get(pad) or self._capture(pad)
             g[0].replay()
             from ..ops import _lib as _l
+            if _l.SYNC_CHECK:
+                _l.sync_check(f"graph replay, padded batch {pad}")
             _l.LAUNCHES[0] += g[2]  # launcher calls folded into the replayed graph
             self._logits = g[1][:R] if g[1] is not None else None
             self._graph_sampled = True
