@@ -349,3 +349,38 @@ def test_native_mixture_of_experts_matches_the_python_engine(lib, tmp_path):
             break
         same += 1
     assert same >= 5, (got, want.text)          # a near-tie may flip late tokens, never the first ones
+
+
+@pytest.mark.gpu
+def test_native_library_on_the_gpu_matches_the_python_engine(lib, ckpt_gpu):
+    """The same C entry points on cuda:0: kernels launched from the native runner (one call per
+    block, expert kernels for the mixture-of-experts checkpoint), device sampler, status word
+    checked every step; greedy text equals the Python engine's."""
+    from vllm_cpp_b200.config import EngineArgs
+    from vllm_cpp_b200.engine import LLM, SamplingParams as SP
+    prompts = ["The quick brown fox jumps over the lazy dog and", "hello"]
+    llm = LLM(EngineArgs(model=ckpt_gpu, device="cuda", block_size=16, num_blocks=256, max_model_len=512,
+                         max_num_seqs=8, enable_cuda_graphs=False))
+    want = [o.outputs[0].text for o in llm.generate(prompts, SP(temperature=0.0, max_tokens=16, ignore_eos=True))]
+    del llm
+    mp = lib.vllm_model_params_default()
+    mp.model_path, mp.max_model_len, mp.block_size = ckpt_gpu.encode(), 512, 16
+    eng = ctypes.c_void_p()
+    opt = EngineOptions(ctypes.sizeof(EngineOptions), 1, 0, b"cuda")
+    assert lib.vllm_engine_load_ex(ctypes.byref(mp), ctypes.byref(opt), ctypes.byref(eng)) == 0, lib.vllm_last_error()
+    sp = lib.vllm_sampling_params_default()
+    sp.temperature, sp.max_tokens, sp.ignore_eos = 0.0, 16, 1
+    out = Completion()
+    for p, w in zip(prompts, want):
+        assert lib.vllm_complete(eng, p.encode(), ctypes.byref(sp), ctypes.byref(out)) == 0, lib.vllm_last_error()
+        assert out.completion_tokens == 16 and ctypes.string_at(out.text).decode() == w
+        lib.vllm_completion_free(ctypes.byref(out))
+    # sampled, penalised request through the device sampler pipeline; reproducible with a seed
+    sp.temperature, sp.top_p, sp.top_k, sp.seed, sp.has_seed, sp.presence_penalty = 0.9, 0.9, 40, 11, 1, 0.3
+    got = []
+    for _ in range(2):
+        assert lib.vllm_complete(eng, b"once upon a time", ctypes.byref(sp), ctypes.byref(out)) == 0
+        got.append(ctypes.string_at(out.text))
+        lib.vllm_completion_free(ctypes.byref(out))
+    assert got[0] == got[1]
+    lib.vllm_engine_free(eng)

@@ -131,6 +131,8 @@ SYNC_CHECK = os.environ.get("B200_SYNC_CHECK", "0") == "1"
 
 
 def sync_check(what: str) -> None:
+    if torch.cuda.is_current_stream_capturing():
+        return
     try:
         torch.cuda.synchronize()
     except Exception as e:  # the context is gone: report and leave without running destructors
