@@ -111,6 +111,7 @@ class ModelRunner(E.ModelRunnerBase):
                                         pin_memory=self.is_cuda)
         self.last_sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
         self.graphs: dict[int, tuple] = {}
+        self._replays: dict[int, int] = {}      # B200_SYNC_CHECK bookkeeping
         self._model_samples_greedy = bool(getattr(model, "samples_greedy", False))
         self.enable_graphs = enable_cuda_graphs and self.is_cuda
         self.graph_sizes = decode_graph_sizes(max_num_seqs) if self.enable_graphs else []
@@ -351,7 +352,11 @@ class ModelRunner(E.ModelRunnerBase):
             g[0].replay()
             from ..ops import _lib as _l
             if _l.SYNC_CHECK:
-                _l.sync_check(f"graph replay, padded batch {pad}")
+                sl = self.host_views["seq_lens"][:R]
+                _l.sync_check(f"graph replay, padded batch {pad}, {R} requests, sequence lengths "
+                              f"{int(sl.min())}..{int(sl.max())}, {info.num_splice} spliced ids, replay "
+                              f"{self._replays.get(pad, 0)} of this graph")
+                self._replays[pad] = self._replays.get(pad, 0) + 1
             _l.LAUNCHES[0] += g[2]  # launcher calls folded into the replayed graph
             self._logits = g[1][:R] if g[1] is not None else None
             self._graph_sampled = True
