@@ -11,6 +11,7 @@ Reference: ``src/vllm/v1/worker/gpu/runner.cpp:373`` (initialize_kv_cache), ``:6
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import numpy as np
@@ -347,7 +348,15 @@ class ModelRunner(E.ModelRunnerBase):
             _lib.check(_lib.lib().b200_splice_sampled(
                 v["input_ids"].data_ptr(), v["splice_dst"].data_ptr(), v["splice_src"].data_ptr(),
                 self.last_sampled.data_ptr(), info.num_splice, _lib.stream_ptr()), "splice")
-        if pad is not None:
+        if pad is not None and os.environ.get("B200_EAGER_PADDED") == "1":
+            # debugging: the launches a decode graph of this padded size holds, issued one by one
+            ctx = self._context(info, padded=pad)
+            self._logits = self.model.forward(ctx)
+            if self._logits is not None:
+                self.ops.argmax(self._logits, out=self.sampled[:pad])
+                self._logits = self._logits[:R]
+            self._graph_sampled = True
+        elif pad is not None:
             g = self.graphs.get(pad) or self._capture(pad)
             g[0].replay()
             from ..ops import _lib as _l
