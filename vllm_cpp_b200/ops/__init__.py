@@ -16,14 +16,19 @@ ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 EW_ADD, EW_RELU, EW_MUL_SCALAR, EW_SOFTCAP, EW_SIGMOID_MUL, EW_MUL = 0, 1, 2, 3, 4, 5
 
 _workspaces: dict[tuple[int, str], torch.Tensor] = {}
+_retired_workspaces: list[torch.Tensor] = []
 
 
 def workspace(device: torch.device, nbytes: int, tag: str = "gemm") -> torch.Tensor:
-    """Persistent per-device scratch (never freed, so pointers captured in CUDA graphs stay valid)."""
+    """Persistent per-device scratch. Never freed: a CUDA graph captured while a smaller buffer was
+    current keeps that buffer's address, so a buffer that is outgrown is retired, not released
+    (releasing it would hand the captured address to some other tensor)."""
     key = (device.index or 0, tag)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
-        w = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        if w is not None:
+            _retired_workspaces.append(w)
+        w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = w
     return w
 

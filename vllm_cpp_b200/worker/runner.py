@@ -11,7 +11,6 @@ Reference: ``src/vllm/v1/worker/gpu/runner.cpp:373`` (initialize_kv_cache), ``:6
 """
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import numpy as np
@@ -112,7 +111,6 @@ class ModelRunner(E.ModelRunnerBase):
                                         pin_memory=self.is_cuda)
         self.last_sampled = torch.zeros(max_num_seqs, dtype=torch.int64, device=self.device)
         self.graphs: dict[int, tuple] = {}
-        self._replays: dict[int, int] = {}      # B200_SYNC_CHECK bookkeeping
         self._model_samples_greedy = bool(getattr(model, "samples_greedy", False))
         self.enable_graphs = enable_cuda_graphs and self.is_cuda
         self.graph_sizes = decode_graph_sizes(max_num_seqs) if self.enable_graphs else []
@@ -348,24 +346,12 @@ class ModelRunner(E.ModelRunnerBase):
             _lib.check(_lib.lib().b200_splice_sampled(
                 v["input_ids"].data_ptr(), v["splice_dst"].data_ptr(), v["splice_src"].data_ptr(),
                 self.last_sampled.data_ptr(), info.num_splice, _lib.stream_ptr()), "splice")
-        if pad is not None and os.environ.get("B200_EAGER_PADDED") == "1":
-            # debugging: the launches a decode graph of this padded size holds, issued one by one
-            ctx = self._context(info, padded=pad)
-            self._logits = self.model.forward(ctx)
-            if self._logits is not None:
-                self.ops.argmax(self._logits, out=self.sampled[:pad])
-                self._logits = self._logits[:R]
-            self._graph_sampled = True
-        elif pad is not None:
+        if pad is not None:
             g = self.graphs.get(pad) or self._capture(pad)
             g[0].replay()
             from ..ops import _lib as _l
             if _l.SYNC_CHECK:
-                sl = self.host_views["seq_lens"][:R]
-                _l.sync_check(f"graph replay, padded batch {pad}, {R} requests, sequence lengths "
-                              f"{int(sl.min())}..{int(sl.max())}, {info.num_splice} spliced ids, replay "
-                              f"{self._replays.get(pad, 0)} of this graph")
-                self._replays[pad] = self._replays.get(pad, 0) + 1
+                _l.sync_check(f"graph replay, padded batch {pad}, {R} requests")
             _l.LAUNCHES[0] += g[2]  # launcher calls folded into the replayed graph
             self._logits = g[1][:R] if g[1] is not None else None
             self._graph_sampled = True
