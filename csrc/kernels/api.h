@@ -12,6 +12,9 @@ extern "C" {
 #endif
 
 int b200_num_sms();
+// Allocates the per-device scratch of the launchers (stream-K partials) for the current device.
+// Call once per device before the first stream capture. 0 on success.
+int b200_init_device();
 int b200_read_status();
 void* b200_status_ptr();
 const char* b200_kernel_arch();

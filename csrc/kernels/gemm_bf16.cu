@@ -1133,8 +1133,10 @@ static bool get_tmap_bf16(CUtensorMap* out, const void* p, uint64_t rows, uint64
 static constexpr int kSmemBudget = 220 * 1024;
 
 // Stream-K scratch of the current device: one 128 x 256 fp32 partial per CTA plus four flags per
-// CTA. Allocated on first use outside stream capture; GEMMs that share it must be ordered on one
-// stream (two streams running stream-K GEMMs at once would mix their partials).
+// CTA. b200_init_device() allocates it when a device is set up; a first use that finds none
+// allocates it too unless the stream is capturing (a capture that early keeps the plan without
+// stream-K). GEMMs that share it must be ordered on one stream (two streams running stream-K
+// GEMMs at once would mix their partials).
 static bool streamk_scratch(cudaStream_t stream, float** partials, uint32_t** flags) {
   static std::mutex mu;
   static float* g_part[64] = {};
@@ -1770,4 +1772,12 @@ extern "C" int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* 
     if (cudaGetLastError() != cudaSuccess) { g_static_err = "reduce launch failed"; return -2; }
   }
   return 0;
+}
+
+// Per-device set-up of everything the launchers would otherwise allocate on first use: the
+// stream-K scratch. Call it once per device before the first capture; 0 on success.
+extern "C" int b200_init_device() {
+  float* p = nullptr;
+  uint32_t* f = nullptr;
+  return streamk_scratch(nullptr, &p, &f) ? 0 : -2;
 }

@@ -34,6 +34,7 @@ NativeRunner::NativeRunner(std::unique_ptr<DenseModel> model, int block_size, in
       layout_(StepLayout::make(max_tokens_, max_num_seqs, max_blocks_, 1, 0)),
       batch_(max_num_seqs, max_model_len, max_tokens_, std::vector<int>{block_size}) {
   set_device(dev_);
+  if (dev_.cuda && b200_init_device() != 0) throw std::runtime_error("kernel library: device set-up failed");
   model_->alloc_kv_cache(num_blocks, block_size);
   model_->reserve(max_tokens_, max_num_seqs);
   host_buf_ = alloc_pinned(layout_.total_bytes);

@@ -16,9 +16,7 @@ def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
     return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
 
 
-def _rel_err(a, b):
-    a, b = a.float(), b.float()
-    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+from _numerics import rel_err as _rel_err  # noqa: E402
 
 
 def test_library_loaded_and_status_clean():

@@ -11,8 +11,8 @@ DEV = "cuda"
 
 
 def _rel(a, b):
-    a, b = a.float(), b.float()
-    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+    from _numerics import rel_err
+    return rel_err(a, b, row_tol=0.15, abs_tol=0.1)
 
 
 @pytest.mark.parametrize("M,N,K,per_channel", [(128, 256, 256, False), (300, 520, 384, True), (7, 4096, 4096, False),

@@ -59,17 +59,23 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 
 
 class BufferPool:
-    """Persistent activation buffers keyed by name; grown on demand, never shrunk or moved
-    while a CUDA graph that captured them is alive (callers size them up front)."""
+    """Persistent activation buffers keyed by name; grown on demand, never shrunk. A buffer that
+    is outgrown is kept alive (a CUDA graph captured earlier still holds its address)."""
 
     def __init__(self, device):
         self.device = device
         self._bufs: dict[str, torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []
+        if torch.device(device).type == "cuda":
+            from .. import ops
+            ops.init_device(torch.device(device))
 
     def get(self, name: str, rows: int, cols: int, dtype=torch.bfloat16) -> torch.Tensor:
         b = self._bufs.get(name)
         if b is None or b.shape[0] < rows or b.shape[1] != cols or b.dtype != dtype:
             cap = rows if b is None else max(rows, b.shape[0])
+            if b is not None:
+                self._retired.append(b)
             b = torch.empty((cap, cols), dtype=dtype, device=self.device)
             self._bufs[name] = b
         return b[:rows]

@@ -15,6 +15,19 @@ from ._lib import check, lib, ptr, stream_ptr
 ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 EW_ADD, EW_RELU, EW_MUL_SCALAR, EW_SOFTCAP, EW_SIGMOID_MUL, EW_MUL = 0, 1, 2, 3, 4, 5
 
+_inited_devices: set[int] = set()
+
+
+def init_device(device: torch.device) -> None:
+    """Per-device set-up of the kernel library (stream-K scratch), once, before any capture."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if device.type != "cuda" or idx in _inited_devices:
+        return
+    with torch.cuda.device(idx):
+        check(lib().b200_init_device(), "init_device")
+    _inited_devices.add(idx)
+
+
 _workspaces: dict[tuple[int, str], torch.Tensor] = {}
 _retired_workspaces: list[torch.Tensor] = []
 
@@ -26,7 +39,9 @@ def workspace(device: torch.device, nbytes: int, tag: str = "gemm") -> torch.Ten
     key = (device.index or 0, tag)
     w = _workspaces.get(key)
     if w is None or w.numel() < nbytes:
-        if w is not None:
+        if w is None:
+            init_device(device)
+        else:
             _retired_workspaces.append(w)
         w = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = w

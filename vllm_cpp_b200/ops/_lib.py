@@ -53,6 +53,7 @@ Z = ctypes.c_size_t
 
 _SIGS = {
     "b200_num_sms": ([], I),
+    "b200_init_device": ([], I),
     "b200_read_status": ([], I),
     "b200_status_ptr": ([], P),
     "b200_set_peer_wait_cycles": ([ctypes.c_longlong], ctypes.c_longlong),
