@@ -20,8 +20,10 @@ _inited_devices: set[int] = set()
 
 def init_device(device: torch.device) -> None:
     """Per-device set-up of the kernel library (stream-K scratch), once, before any capture."""
+    if device.type != "cuda":
+        return
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    if device.type != "cuda" or idx in _inited_devices:
+    if idx in _inited_devices:
         return
     with torch.cuda.device(idx):
         check(lib().b200_init_device(), "init_device")
