@@ -313,6 +313,7 @@ class Qwen35Model(DenseModel):
         self.bufs.reserve("gdn_beta", max_tokens, self.gv, torch.float32)
         self.bufs.reserve("last", max_reqs, c.hidden_size)
         self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
+        self.bufs.reserve("argmax_cand", max_reqs, 2, torch.int32)
         for l in self.gdn_layers:
             self.conv_state[l] = torch.zeros((max_reqs, self.conv_dim, 3), dtype=self.dtype, device=self.device)
             self.ssm_state[l] = torch.zeros((max_reqs, self.gv, 128, 128), dtype=torch.float32,
@@ -333,7 +334,8 @@ class Qwen35Model(DenseModel):
                                            c.hidden_size, self.moe_inter)
 
     def fused_tp_supported(self) -> bool:
-        return False
+        return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+                and self.cfg.hidden_size % 8 == 0)
 
     # ------------------------------------------------------------------ expert block
     _moe_block = MoeModel._moe_block
@@ -359,11 +361,16 @@ class Qwen35Model(DenseModel):
         return hidden
 
     # ------------------------------------------------------------------ GDN layer
-    def _gdn_layer(self, l: int, L: dict, x: torch.Tensor, ctx: StepContext, T: int, meta: dict):
-        """x: normed hidden [T, H] -> core attention output after the gated norm [T, gv*128]."""
+    def _gdn_layer(self, l: int, L: dict, x: torch.Tensor | None, ctx: StepContext, T: int, meta: dict):
+        """x: normed hidden [T, H] -> core attention output after the gated norm [T, gv*128].
+        ``x`` None: the input is the gathered activation buffer of the fused tensor-parallel path
+        (the in_proj GEMM waits for its rows tile by tile)."""
         be = self.be
         proj = self.bufs.get("gdn_in", T, self.in_w_pad)
-        be.gemm(x, L["in_proj"], out=proj)
+        if x is None:
+            self.tpf.gemm_gather(T, L["in_proj"], proj)
+        else:
+            be.gemm(x, L["in_proj"], out=proj)
         core = self.bufs.get("gdn_core", T, self.gv * 128)
         nd = ctx.num_decodes
         mixed = proj[:, : self.conv_dim]
@@ -447,7 +454,82 @@ class Qwen35Model(DenseModel):
         return meta
 
     # ------------------------------------------------------------------ forward
+    def _forward_tp_fused_gdn(self, ctx: StepContext):
+        """The hybrid stack with every collective inside a kernel: out_proj / o_proj / down_proj
+        scatter their partial rows in the GEMM epilogue, the owner reduces + adds the residual +
+        normalises (Gemma-style weight) + all-gathers, in_proj / qkv / gate_up wait for gathered
+        rows tile by tile, and the MoE combine (routed sum + gated shared expert) stores into the
+        owners' receive slots."""
+        c, be, T, tpf = self.cfg, self.be, ctx.num_tokens, self.tpf
+        H, eps, D = c.hidden_size, c.rms_norm_eps, self.D
+        act_kind = ACT_KIND.get(c.hidden_act, 0)
+        hidden = self.bufs.get("hidden", T, H)
+        normed = self.bufs.get("normed", T, H)
+        qkv = self.bufs.get("qkv", T, (2 * self.hq + 2 * self.hkv) * D)
+        attn = self.bufs.get("attn", T, self.hq * D)
+        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                     vocab_total=c.vocab_size)
+        self.comm.all_reduce(hidden)
+        tpf.first_norm(hidden, self.layers[0]["ln1"], eps, True)
+        pos = ctx.positions[:T]
+        meta = self._step_meta(ctx, T)
+        k_off = 2 * self.hq * D
+        sc = None
+        if self.has_moe:
+            from ..ops import moe as M
+            sc = M.B200MoeScatter()
+            sc.world, sc.rank, sc.rows_per_rank = tpf.world, tpf.rank, tpf.rows_per_rank(T)
+            for r in range(tpf.world):
+                sc.peer_recv[r] = tpf.recv.ptrs[r]
+                sc.peer_rs_flags[r] = tpf._rs_flags(r)
+            sc.recv_parity_stride, sc.rs_flag_parity_stride = tpf.recv_parity, tpf.rs_groups
+            sc.op_counter = tpf._op_counter()
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            if self.is_gdn[l]:
+                core = self._gdn_layer(l, L, None, ctx, T, meta)
+                exp = tpf.gemm_scatter(core, L["out"])
+            else:
+                tpf.gemm_gather(T, L["qkv"], qkv)
+                qv = qkv[:, :k_off].view(T, self.hq, 2 * D)
+                qc = self.bufs.get("q_compact", T, self.hq * D)
+                be.ops.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                               head_dim=D, rot_dim=self.rot, neox=c.rope.neox, q_norm=L.get("q_norm"),
+                               k_norm=L.get("k_norm"), eps=eps, gemma=True,
+                               slot_mapping=ctx.slot_mapping[0][:T], kv_cache=self.kv_caches[l],
+                               block_size=self.block_size, q_out=qc, q_head_stride=2 * D,
+                               offsets=(0, k_off, k_off + self.hkv * D))
+                be.attention(qc, self.kv_caches[l], ctx, 0, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                             head_dim=D, block_size=self.block_size, scale=self.scale, out=attn)
+                gate = self.bufs.get("gate_compact", T, self.hq * D)
+                gate.view(T, self.hq, D).copy_(qv[:, :, D:])
+                gated = be.sigmoid_mul(attn, gate)
+                exp = tpf.gemm_scatter(gated, L["o"])
+            tpf.reduce_norm_gather(T, exp, L["ln2"], eps, True)
+            nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
+            if self.has_moe:
+                from ..ops import moe as M
+                tpf.gather_all(T, normed)
+                so = sg = None
+                if "s_gate_up" in L:
+                    gu = self.bufs.get("s_gate_up", T, 2 * self.shared_inter)
+                    be.gemm(normed, L["s_gate_up"], out=gu)
+                    a_ = be.act_and_mul(gu, act_kind, out=self.bufs.get("s_act", T, self.shared_inter))
+                    so = be.gemm(a_, L["s_down"], out=self.bufs.get("s_out", T, H))
+                    sg = M.shared_gate(normed, L["s_gate"][0])
+                self._moe_block(normed, L, T, scatter=sc, shared=so, shared_gate=sg)
+                tpf.reduce_norm_gather(T, tpf.world * 32, nw, eps, True, nsrc=tpf.world)
+            else:
+                gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
+                tpf.gemm_gather(T, L["gate_up"], gate_up)
+                a_ = be.act_and_mul(gate_up, act_kind, out=self.bufs.get("act", T, self.inter))
+                exp = tpf.gemm_scatter(a_, L["down"])
+                tpf.reduce_norm_gather(T, exp, nw, eps, True)
+        return self._tp_fused_logits(ctx, T)
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if getattr(self, "tpf", None) is not None:
+            return self._forward_tp_fused_gdn(ctx)
         c, be, T = self.cfg, self.be, ctx.num_tokens
         H, eps, D = c.hidden_size, c.rms_norm_eps, self.D
         act_kind = ACT_KIND.get(c.hidden_act, 0)

@@ -210,6 +210,7 @@ class DeepseekV2Model(MoeModel):
         self.bufs.reserve("router", max_tokens, self.E, torch.float32)
         self.bufs.reserve("last", max_reqs, c.hidden_size)
         self.bufs.reserve("logits", max_reqs, self.vocab_shard, torch.float32)
+        self.bufs.reserve("argmax_cand", max_reqs, 2, torch.int32)
         # never-written pad columns of the attention buffer must stay finite
         self.bufs.get("attn_pad", max_tokens, H * 256).zero_()
         if self.device.type == "cuda":
@@ -218,7 +219,8 @@ class DeepseekV2Model(MoeModel):
                                        self.moe_inter)
 
     def fused_tp_supported(self) -> bool:
-        return False
+        return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+                and self.cfg.hidden_size % 8 == 0)
 
     # ------------------------------------------------------------------ attention
     def _decode_plan(self, B: int, max_seq_len: int):
@@ -322,7 +324,71 @@ class DeepseekV2Model(MoeModel):
         kpe.copy_(rot(kpe))
 
     # ------------------------------------------------------------------ forward
+    def _forward_tp_fused_mla(self, ctx: StepContext):
+        """Tensor-parallel heads + expert-parallel experts with every collective inside a kernel:
+        o_proj / down_proj scatter their partial rows to the owners in the GEMM epilogue, the owner
+        reduces + adds the residual + normalises + all-gathers, q / kv_a / gate_up GEMMs wait for the
+        gathered rows tile by tile, and the MoE combine (routed sum + this rank's part of the shared
+        experts) stores straight into the owners' receive slots. The would-be collective sites in
+        the reference: ``src/vllm/model_executor/layers/attention/mla_attention.cpp:487`` and
+        ``src/vllm/model_executor/models/deepseek_v2.cpp:289,464-466``."""
+        from ..ops.moe import B200MoeScatter
+        c, be, T, tpf = self.cfg, self.be, ctx.num_tokens, self.tpf
+        Hd, eps = c.hidden_size, c.rms_norm_eps
+        act_kind = ACT_KIND.get(c.hidden_act, 0)
+        hidden = self.bufs.get("hidden", T, Hd)
+        normed = self.bufs.get("normed", T, Hd)
+        qa = self.bufs.get("qa", T, self.qa_w)
+        attn = self.bufs.get("attn_pad", T, self.H * 256)
+        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                     vocab_total=c.vocab_size)
+        self.comm.all_reduce(hidden)
+        tpf.first_norm(hidden, self.layers[0]["ln1"], eps, False)
+        pos = ctx.positions[:T]
+        meta = self._prefill_meta(ctx) if ctx.num_prefills > 0 else {}
+        kvc = qa[:, self.q_w: self.q_w + 512]
+        kpe = qa[:, self.q_w + 512:]
+        sc = B200MoeScatter()
+        sc.world, sc.rank, sc.rows_per_rank = tpf.world, tpf.rank, tpf.rows_per_rank(T)
+        for r in range(tpf.world):
+            sc.peer_recv[r] = tpf.recv.ptrs[r]
+            sc.peer_rs_flags[r] = tpf._rs_flags(r)
+        sc.recv_parity_stride, sc.rs_flag_parity_stride = tpf.recv_parity, tpf.rs_groups
+        sc.op_counter = tpf._op_counter()
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            tpf.gemm_gather(T, L["qkv_a"], qa)
+            be.ops.rope_kv(qa, pos, self.rope_table, num_q_heads=self.H, num_kv_heads=1, head_dim=64,
+                           rot_dim=64, neox=False, q_head_stride=192, offsets=(128, self.q_w + 512, 0))
+            be.ops.rmsnorm(kvc, L["kv_ln"], eps, out=kvc)
+            be.ops.concat_and_cache_mla(kvc, kpe, ctx.slot_mapping[0][:T], self.kv_caches[l])
+            self._attention_gpu(l, L, qa, ctx, T, meta, attn)
+            exp = tpf.gemm_scatter(attn, L["o"])
+            tpf.reduce_norm_gather(T, exp, L["ln2"], eps, False)
+            nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
+            if l < self.dense_layers:
+                gu = self.bufs.get("gate_up", T, 2 * self.inter)
+                tpf.gemm_gather(T, L["gate_up"], gu)
+                a_ = be.act_and_mul(gu, act_kind, out=self.bufs.get("act", T, self.inter))
+                exp = tpf.gemm_scatter(a_, L["down"])
+                tpf.reduce_norm_gather(T, exp, nw, eps, False)
+                continue
+            # gathered rows -> local copy that the router, the expert gather and the shared experts read
+            tpf.gather_all(T, normed)
+            shared = None
+            if "s_gate_up" in L:
+                gu = self.bufs.get("gate_up", T, 2 * self.shared_inter)
+                be.gemm(normed, L["s_gate_up"], out=gu)
+                a_ = be.act_and_mul(gu, act_kind, out=self.bufs.get("act", T, self.shared_inter))
+                shared = be.gemm(a_, L["s_down"], out=self.bufs.get("shared_out", T, Hd))
+            self._moe_block(normed, L, T, scatter=sc, shared=shared)
+            # every source rank delivers 32 arrivals per 32-row group (see moe_combine_kernel)
+            tpf.reduce_norm_gather(T, tpf.world * 32, nw, eps, False, nsrc=tpf.world)
+        return self._tp_fused_logits(ctx, T)
+
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if getattr(self, "tpf", None) is not None:
+            return self._forward_tp_fused_mla(ctx)
         c, be, T = self.cfg, self.be, ctx.num_tokens
         Hd, eps = c.hidden_size, c.rms_norm_eps
         cuda = self.device.type == "cuda"

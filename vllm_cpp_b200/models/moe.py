@@ -180,9 +180,12 @@ class MoeModel(DenseModel):
         return super().weight_bytes()
 
     # ------------------------------------------------------------------ MoE block
-    def _moe_block(self, x: torch.Tensor, L: dict, T: int, scatter=None) -> torch.Tensor:
+    def _moe_block(self, x: torch.Tensor, L: dict, T: int, scatter=None, shared=None,
+                   shared_gate=None) -> torch.Tensor:
         """Routed experts over ``x`` [T, H]. Returns this rank's (partial, if EP) output, or
-        stores it into the owners' receive slots when ``scatter`` is given."""
+        stores it into the owners' receive slots when ``scatter`` is given. ``shared`` [T, H]
+        (this rank's part of the shared experts' output), scaled per row by ``shared_gate`` [T]
+        when given, is added in the combine kernel."""
         c = self.cfg
         if self.device.type != "cuda":
             return self._moe_block_cpu(x, L)
@@ -203,7 +206,7 @@ class MoeModel(DenseModel):
             self.be.act_and_mul(ws.gu[:P], ACT_KIND.get(c.hidden_act, 0), out=ws.act[:P])
         M.grouped_gemm(ws.act, L["w_down"], ws.y, ws, P, chunks)
         out = None if scatter is not None else self.bufs.get("moe_out", T, c.hidden_size)
-        M.combine(ws.y, ws, w, out, scatter=scatter)
+        M.combine(ws.y, ws, w, out, shared=shared, shared_gate=shared_gate, scatter=scatter)
         return out
 
     def _moe_block_cpu(self, x, L):

@@ -81,13 +81,22 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
     from vllm_cpp_b200.config import EngineArgs, ParallelConfig, synthetic_config
     from vllm_cpp_b200.engine import LLM, SamplingParams
     cfg = synthetic_config(shape)
-    cfg.head_dim = 128
-    cfg.num_heads, cfg.num_kv_heads = 8, 8
-    cfg.hidden_size, cfg.num_layers = 512, 3
-    if shape == "tiny-moe":
-        cfg.moe_intermediate_size = 256
+    cfg.hidden_size, cfg.intermediate_size = 512, 1024
+    if shape == "tiny-mla":
+        # 8 heads of 192 (one per rank at world 8), 8 experts + 2 shared, first block dense
+        cfg.num_heads, cfg.num_kv_heads, cfg.num_layers = 8, 8, 3
+        cfg.moe_intermediate_size, cfg.num_shared_experts = 256, 2
+    elif shape in ("tiny-gdn", "tiny-gdn-moe"):
+        # 4 blocks (3 linear-attention + 1 full attention), heads divisible by 8 ranks
+        cfg.num_heads, cfg.num_kv_heads = 8, 8
+        cfg.linear_num_key_heads, cfg.linear_num_value_heads = 8, 16
+        if cfg.num_experts:
+            cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size = 256, 512
     else:
-        cfg.intermediate_size = 1024
+        cfg.head_dim = 128
+        cfg.num_heads, cfg.num_kv_heads, cfg.num_layers = 8, 8, 3
+        if shape == "tiny-moe":
+            cfg.moe_intermediate_size = 256
     tag = shape.replace("tiny-", "")
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 9, 300, 40)]
@@ -111,7 +120,8 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
     base = run(1, False)
     nccl = run(comm.world, False)
     fused = run(comm.world, True)
-    per_op = run(comm.world, True, native=False)
+    # the native layer stack exists for the plain dense block only; elsewhere both runs are the same path
+    per_op = run(comm.world, True, native=False) if shape == "tiny-qwen3" else fused
     os.environ.pop("B200_NATIVE_LAYERS", None)
 
     def agree(a, b):
