@@ -14,25 +14,10 @@
 #include <immintrin.h>
 #endif
 
+#include "cpu_common.h"
 #include "cpu_threadpool.h"
 
 namespace b200cpu {
-
-using bf16_t = uint16_t;
-
-static inline float bf16_to_f32(bf16_t v) {
-  uint32_t u = (uint32_t)v << 16;
-  float f;
-  std::memcpy(&f, &u, 4);
-  return f;
-}
-static inline bf16_t f32_to_bf16(float f) {
-  uint32_t u;
-  std::memcpy(&u, &f, 4);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (bf16_t)((u >> 16) | 0x40);   // quiet NaN
-  u += 0x7fffu + ((u >> 16) & 1u);                                            // nearest even
-  return (bf16_t)(u >> 16);
-}
 
 static bool has_avx2() {
 #if defined(__x86_64__)

@@ -14,6 +14,8 @@ Reference: ``src/vllm/model_executor/models/qwen3_5.cpp:3138-3490`` (GdnBlockPag
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config import ModelConfig, ParallelConfig
@@ -412,6 +414,16 @@ class Qwen35Model(DenseModel):
         seq = ctx.seq_lens[:R].tolist()
         slots = ctx.state_slots[:R].tolist()
         has_init = [1 if seq[i] - (qsl[i + 1] - qsl[i]) > 0 else 0 for i in range(R)]
+        if (mixed.dtype == torch.bfloat16 and ssm.dtype == torch.float32 and conv_state.is_contiguous()
+                and ssm.is_contiguous() and os.environ.get("B200_CPU_ORACLE", "0") != "1"):
+            # native thread-pool ops (csrc/cpu/cpu_ops_ext.cpp); the PyTorch path below is their oracle
+            from ..ops import cpu_native as N
+            xc = N.gdn_conv1d(mixed, L["conv_w"], conv_state, qsl, slots, has_init)
+            q, k, g, beta = N.gdn_post_conv(xc, self.gk, self.gv, a, b, L["A_log"], L["dt_bias"])
+            v = xc[:, 2 * self.gk * 128:].view(T, self.gv, 128)
+            out = N.gdn_recurrent(q, k, v, g, beta, ssm, qsl, slots, has_init)
+            core.copy_(out.reshape(T, -1).to(core.dtype))
+            return
         xc, st = G.ref_conv1d(mixed, L["conv_w"], conv_state, qsl, slots, has_init)
         conv_state.copy_(st)
         q, k, g, beta = G.ref_post_conv(xc, self.gk, self.gv, a, b, L["A_log"], L["dt_bias"])

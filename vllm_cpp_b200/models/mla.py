@@ -15,6 +15,8 @@ Reference: ``src/vllm/model_executor/models/deepseek_v2.cpp``, ``mla_attention.c
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..config import ModelConfig, ParallelConfig
@@ -298,9 +300,17 @@ class DeepseekV2Model(MoeModel):
     def _attention_cpu(self, l: int, L: dict, qa: torch.Tensor, ctx: StepContext, T: int, attn: torch.Tensor):
         from ..ops import mla as M
         H = self.H
-        q = qa[:, : self.q_w].reshape(T, H, 192)
-        out = M.ref_mla_attention(q, self.kv_caches[l], ctx.block_table[0], ctx.seq_lens, ctx.query_start,
-                                  L["kv_b"], H, self.scale, self.block_size)
+        if qa.dtype == torch.bfloat16 and os.environ.get("B200_CPU_ORACLE", "0") != "1":
+            # native thread-pool op (csrc/cpu/cpu_ops_ext.cpp); the PyTorch restatement is its oracle
+            from ..ops import cpu_native as N
+            q = qa[:, : self.q_w].view(T, H, 192)
+            R = ctx.num_reqs
+            out = N.mla_attention(q, self.kv_caches[l], ctx.block_table[0][:R], ctx.seq_lens[:R],
+                                  ctx.query_start[: R + 1], L["kv_b"], H, self.scale, self.block_size)
+        else:
+            q = qa[:, : self.q_w].reshape(T, H, 192)
+            out = M.ref_mla_attention(q, self.kv_caches[l], ctx.block_table[0], ctx.seq_lens, ctx.query_start,
+                                      L["kv_b"], H, self.scale, self.block_size)
         a = attn.view(T, H, 256)
         a.zero_()
         a[:, :, :128] = out.to(attn.dtype)

@@ -212,6 +212,15 @@ class MoeModel(DenseModel):
     def _moe_block_cpu(self, x, L):
         from ..ops import moe as M
         c = self.cfg
+        if x.dtype == torch.bfloat16 and os.environ.get("B200_CPU_ORACLE", "0") != "1":
+            # native thread-pool ops (csrc/cpu/cpu_ops_ext.cpp); the PyTorch restatement below is
+            # their oracle
+            from ..ops import cpu_native as N
+            logits = N.gemm(x.contiguous(), L["router"], out_dtype=torch.float32)
+            ids, w = N.moe_router_topk(logits, self.k, renorm=c.norm_topk_prob,
+                                       routed_scale=c.routed_scaling_factor)
+            return N.moe_experts(x.contiguous(), ids, w, L["w_gate_up"], L["w_down"], e0=self.e0,
+                                 act_kind=ACT_KIND.get(c.hidden_act, 0))
         logits = (x.float() @ L["router"].float().t())
         ids, w = M.ref_router_topk(logits, self.k, renorm=c.norm_topk_prob,
                                    routed_scale=c.routed_scaling_factor)
