@@ -78,6 +78,13 @@ void ThreadPool::parallel_for(int64_t n, int64_t grain, const std::function<void
     fn(0, n);
     return;
   }
+  // One job at a time: a second caller (another host thread driving its own model, or a call made
+  // from inside a job) runs its range inline instead of waiting for the pool.
+  std::unique_lock<std::mutex> job(job_mu_, std::try_to_lock);
+  if (!job.owns_lock()) {
+    fn(0, n);
+    return;
+  }
   {
     std::lock_guard<std::mutex> lock(mu_);
     fn_ = &fn;

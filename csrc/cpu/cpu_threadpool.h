@@ -1,7 +1,9 @@
 // Persistent worker pool for the CPU backend. Work is always split by OUTPUT index (rows of a
 // GEMM, tokens of a norm, (request, head) pairs of attention), every output element is computed
 // by exactly one thread with a fixed summation order, so results are bit-identical for any
-// thread count. Workers spin briefly between ops and then park on a condition variable.
+// thread count. Workers spin briefly between ops and then park on a condition variable. The pool
+// runs one job at a time; a caller that finds it busy computes its whole range itself (same
+// result, since the partition never changes what one output element sums).
 // Reference: src/vt/cpu/cpu_threadpool.{h,cpp}.
 #pragma once
 #include <atomic>
@@ -29,6 +31,7 @@ class ThreadPool {
   void worker_loop(int id);
   std::vector<std::thread> workers_;
   std::mutex mu_;
+  std::mutex job_mu_;       // held by the caller whose job the workers are running
   std::condition_variable cv_;
   std::atomic<uint64_t> epoch_{0};
   std::atomic<int> pending_{0};

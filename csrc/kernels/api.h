@@ -172,6 +172,10 @@ int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, 
 int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int gemma, const float* scale, void* out, long ldo, long T, int H, cudaStream_t stream);
 int b200_quant_nvfp4(const void* x, long ldx, const float* gscale, void* out, void* sf, long T, int K, int mode, int swizzle, cudaStream_t stream);
 // ---- gemm_w4a16.cu
+// NVFP4 x NVFP4 (W4A4) on the block-scaled tensor-core path; scales in the 128 x 4 chunk layout
+// (b200_nvfp4_sf_to_chunks / b200_quant_nvfp4 with swizzle = 1). K a multiple of 256.
+int b200_gemm_nvfp4(const void* aq, const void* sfa, const float* g_a, const void* wq, const void* sfw, const float* g_w, void* out, int ldo, const void* bias, int M, int N, int K, int n_tile, void* workspace, size_t ws_bytes, cudaStream_t stream);
+int b200_nvfp4_sf_to_chunks(const void* sf, long rows, int K, int pad_rows, void* out, cudaStream_t stream);
 int b200_gemm_w4a16(const void* A, int lda, const void* wq, const void* sf, const float* gscale, void* out, int ldo, const void* bias, int M, int N, int K, void* workspace, size_t ws_bytes, cudaStream_t stream);
 // ---- layer.cu
 void b200_dense_layer_abi(int* out4);

@@ -1,4 +1,4 @@
-// Paged decode attention on tcgen05 with swapped operands (head_dim 128, GQA group <= 16).
+// Paged decode attention on tcgen05 with swapped operands (head_dim 128 or 256, GQA group <= 16).
 //
 // One CTA = one (sequence, kv head, kv split). The KV stream is the 128-row MMA operand and
 // the few query heads that share the kv head are the narrow N operand, so every K/V byte is
@@ -12,8 +12,10 @@
 //
 // O^T stays in TMEM across tiles (16 fp32 columns); the running max is raised lazily (only
 // when a tile exceeds it by more than 2^8), and raising it rescales those 16 columns in
-// place. K and V tiles share one TMA ring of 32 KB slots, filled in the order the MMA warp
-// consumes them (K0 K1 V0 K2 V1 ...); two CTAs fit on an SM.
+// place. K and V tiles share one TMA ring of 128 x D bf16 slots, filled in the order the MMA warp
+// consumes them (K0 K1 V0 K2 V1 ...); two CTAs fit on an SM at head_dim 128. At head_dim 256 the
+// P V product runs as two M = 128 instructions (one per half of the head dim), O^T takes two
+// 16-column accumulators and one CTA fits on an SM.
 //
 // Replaces the CUDA-core decode kernels of the reference
 // (src/vt/cuda/cuda_paged_attn.cu:302 PagedAttentionDecodeOptKernel, :430 ...GqaKernel) and
@@ -29,7 +31,12 @@ namespace b200 {
 static constexpr int kTok = 128;        // tokens per tile
 static constexpr int kNQ = 16;          // padded query heads (UMMA N)
 static constexpr int kSlots = 3;        // K/V ring slots
-static constexpr int kSlotBytes = 128 * 128 * 2;
+template <int D>
+struct DecodeTcSmem {
+  static constexpr int slot_bytes = kTok * D * 2;      // one K or V tile
+  static constexpr int q_bytes = (D / 64) * 2048;      // 16 query rows, 64-element chunks of 2 KB
+  static constexpr int p_bytes = 8192;                 // 2 buffers x (2 token halves x 2 KB)
+};
 
 struct DecodeTcParams {
   __nv_bfloat16* out;
@@ -86,17 +93,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // GP: the GQA group size rounded up to 4 / 8 / 16; the softmax only touches those columns of
 // S^T (the MMA's N stays 16, its minimum at 128 rows).
-template <int GP>
-__global__ void __launch_bounds__(192, 2)
+template <int GP, int D>
+__global__ void __launch_bounds__(192, D == 128 ? 2 : 1)
     attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                           const __grid_constant__ CUtensorMap tmKV, DecodeTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  constexpr int D = 128;
-  uint8_t* sKV = smem;                               // kSlots * 32 KB
-  uint8_t* sQ = sKV + kSlots * kSlotBytes;           // 2 halves * 2 KB
-  uint8_t* sP = sQ + 4096;                           // 2 buffers * (2 halves * 2 KB)
+  constexpr int kSlotBytes = DecodeTcSmem<D>::slot_bytes;
+  constexpr int kQBytes = DecodeTcSmem<D>::q_bytes;
+  constexpr int kChunks = D / 64;                    // 64-element (128-byte) chunks of the head dim
+  constexpr int kChunkBytes = kTok * 128;            // one chunk of a K / V tile: 128 tokens x 128 bytes
+  uint8_t* sKV = smem;                               // kSlots tiles
+  uint8_t* sQ = sKV + kSlots * kSlotBytes;           // kChunks x 2 KB
+  uint8_t* sP = sQ + kQBytes;                        // 2 buffers * (2 halves * 2 KB)
   DecodeTcBars* bars = reinterpret_cast<DecodeTcBars*>(sP + 8192);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +142,7 @@ __global__ void __launch_bounds__(192, 2)
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t tmem_s = tmem_base;        // 2 x 16 columns
-  const uint32_t tmem_o = tmem_base + 32;   // 16 columns
+  const uint32_t tmem_o = tmem_base + 32;   // 16 columns per 128 rows of the head dim
 
   // Everything above touches only shared memory and TMEM and may overlap the previous kernel.
   pdl_wait();
@@ -154,9 +164,9 @@ __global__ void __launch_bounds__(192, 2)
       if (lane == 0) {
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmKV);
-        mbar_expect_tx(&bars->q_full, 4096);
-        tma_load_3d(sQ, &tmQ, &bars->q_full, 0, hkv * G, b);
-        tma_load_3d(sQ + 2048, &tmQ, &bars->q_full, 64, hkv * G, b);
+        mbar_expect_tx(&bars->q_full, kQBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) tma_load_3d(sQ + c * 2048, &tmQ, &bars->q_full, c * 64, hkv * G, b);
         const int32_t* bt = p.block_table + (size_t)b * p.max_blocks;
         const int nblk_valid = (seq_len + p.block_size - 1) / p.block_size;
         const int rows_per_load = min(p.block_size, kTok);
@@ -183,9 +193,10 @@ __global__ void __launch_bounds__(192, 2)
             const int bi = tk / p.block_size;
             const int blk = (bi < nblk_valid) ? bt[bi] : bt[0];
             const int row = (blk * 2 + kv) * p.block_size + tk % p.block_size;
-            tma_load_3d(dst + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 0, hkv, row);
-            tma_load_3d(dst + 16384 + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], 64, hkv,
-                        row);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c)
+              tma_load_3d(dst + c * kChunkBytes + l * rows_per_load * 128, &tmKV, &bars->kv_full[sl], c * 64, hkv,
+                          row);
           }
         }
       }
@@ -193,7 +204,7 @@ __global__ void __launch_bounds__(192, 2)
       // ------------------------------ MMA issuer ------------------------------
       if (lane == 0) {
         constexpr uint32_t idesc_qk = umma_idesc_bf16(kTok, kNQ, 0, 0);
-        constexpr uint32_t idesc_pv = umma_idesc_bf16(D, kNQ, 1, 0);  // A (V^T) is MN-major
+        constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kNQ, 1, 0);  // A (V^T) is MN-major
         bool ok = mbar_wait(&bars->q_full, 0, p.status);
         const uint32_t q_addr = smem_u32(sQ);
         for (int j = 0; j <= ntiles && ok; ++j) {
@@ -207,7 +218,7 @@ __global__ void __launch_bounds__(192, 2)
             const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-              const uint32_t koff = (kk / 4) * 16384 + (kk % 4) * 32;
+              const uint32_t koff = (kk / 4) * kChunkBytes + (kk % 4) * 32;
               const uint32_t qoff = (kk / 4) * 2048 + (kk % 4) * 32;
               umma_bf16_ss(tmem_s + sb * 16, umma_desc_k_sw128(k_addr + koff, 1024),
                            umma_desc_k_sw128(q_addr + qoff, 1024), idesc_qk, kk != 0);
@@ -226,10 +237,14 @@ __global__ void __launch_bounds__(192, 2)
             const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
             const uint32_t p_addr = smem_u32(sP + pb * 4096);
 #pragma unroll
-            for (int kk = 0; kk < kTok / 16; ++kk) {
-              const uint32_t poff = (kk / 4) * 2048 + (kk % 4) * 32;
-              umma_bf16_ss(tmem_o, umma_desc_mn_sw128(v_addr + kk * 2048, 16384, 1024),
-                           umma_desc_k_sw128(p_addr + poff, 1024), idesc_pv, (i | kk) != 0);
+            for (int dh = 0; dh < D / 128; ++dh) {       // 128 rows of the head dim per instruction
+#pragma unroll
+              for (int kk = 0; kk < kTok / 16; ++kk) {
+                const uint32_t poff = (kk / 4) * 2048 + (kk % 4) * 32;
+                umma_bf16_ss(tmem_o + dh * 16,
+                             umma_desc_mn_sw128(v_addr + dh * 2 * kChunkBytes + kk * 2048, kChunkBytes, 1024),
+                             umma_desc_k_sw128(p_addr + poff, 1024), idesc_pv, (i | kk) != 0);
+              }
             }
             umma_commit(&bars->kv_empty[sl]);
             umma_commit(&bars->pv_done);      // before p_empty: whoever sees p_empty has this arrival too
@@ -306,12 +321,15 @@ __global__ void __launch_bounds__(192, 2)
           ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done, (j - 1) & 1, p.status));
           if (!ok) break;
           tc_fence_after_sync();
-          uint32_t o[16];
-          tmem_ld_32x32b_x16(tmem_o + lane_off, o);
-          tmem_ld_wait();
 #pragma unroll
-          for (int g = 0; g < GP; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
-          tmem_st_32x32b_x16(tmem_o + lane_off, o);
+          for (int dh = 0; dh < D / 128; ++dh) {
+            uint32_t o[16];
+            tmem_ld_32x32b_x16(tmem_o + dh * 16 + lane_off, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < GP; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
+            tmem_st_32x32b_x16(tmem_o + dh * 16 + lane_off, o);
+          }
           tmem_st_wait();
 #pragma unroll
           for (int g = 0; g < GP; ++g) lsum[g] *= alpha[g];
@@ -352,23 +370,26 @@ __global__ void __launch_bounds__(192, 2)
         ok = softmax_group_sync(&bars->grp, gphase, lane, p.status);
       }
       if (ok) {
-        uint32_t o[16];
-        tmem_ld_32x32b_x16(tmem_o + lane_off, o);
-        tmem_ld_wait();
-        const int d = t;  // TMEM lane of O^T = head dim index
 #pragma unroll
-        for (int g = 0; g < GP; ++g) {
-          if (g < G) {
-            const float l = bars->red_sum[0][g] + bars->red_sum[1][g] + bars->red_sum[2][g] +
-                            bars->red_sum[3][g];
-            const float v = l > 0.f ? __uint_as_float(o[g]) / l : 0.f;
-            const int hq = hkv * G + g;
-            if (p.splits == 1) {
-              p.out[(size_t)b * p.ldo + (size_t)hq * D + d] = __float2bfloat16(v);
-            } else {
-              const size_t row = ((size_t)b * p.Hq + hq) * p.splits + split;
-              p.tmp_o[row * D + d] = v;
-              if (d == 0) p.tmp_lse[row] = l > 0.f ? m[g] + log2f(l) : -INFINITY;
+        for (int dh = 0; dh < D / 128; ++dh) {
+          uint32_t o[16];
+          tmem_ld_32x32b_x16(tmem_o + dh * 16 + lane_off, o);
+          tmem_ld_wait();
+          const int d = dh * 128 + t;  // TMEM lane of O^T = head dim index within its half
+#pragma unroll
+          for (int g = 0; g < GP; ++g) {
+            if (g < G) {
+              const float l = bars->red_sum[0][g] + bars->red_sum[1][g] + bars->red_sum[2][g] +
+                              bars->red_sum[3][g];
+              const float v = l > 0.f ? __uint_as_float(o[g]) / l : 0.f;
+              const int hq = hkv * G + g;
+              if (p.splits == 1) {
+                p.out[(size_t)b * p.ldo + (size_t)hq * D + d] = __float2bfloat16(v);
+              } else {
+                const size_t row = ((size_t)b * p.Hq + hq) * p.splits + split;
+                p.tmp_o[row * D + d] = v;
+                if (d == 0) p.tmp_lse[row] = l > 0.f ? m[g] + log2f(l) : -INFINITY;
+              }
             }
           }
         }
@@ -376,15 +397,16 @@ __global__ void __launch_bounds__(192, 2)
     }
   } else if (warp >= 2) {
     // empty split (or empty sequence): neutral partial / zero output
-    const int d = (warp & 3) * 32 + lane;
-    for (int g = 0; g < G; ++g) {
-      const int hq = hkv * G + g;
-      if (p.splits == 1) {
-        p.out[(size_t)b * p.ldo + (size_t)hq * D + d] = __float2bfloat16(0.f);
-      } else {
-        const size_t row = ((size_t)b * p.Hq + hq) * p.splits + split;
-        p.tmp_o[row * D + d] = 0.f;
-        if (d == 0) p.tmp_lse[row] = -INFINITY;
+    for (int d = (warp & 3) * 32 + lane; d < D; d += 128) {
+      for (int g = 0; g < G; ++g) {
+        const int hq = hkv * G + g;
+        if (p.splits == 1) {
+          p.out[(size_t)b * p.ldo + (size_t)hq * D + d] = __float2bfloat16(0.f);
+        } else {
+          const size_t row = ((size_t)b * p.Hq + hq) * p.splits + split;
+          p.tmp_o[row * D + d] = 0.f;
+          if (d == 0) p.tmp_lse[row] = -INFINITY;
+        }
       }
     }
   }
@@ -405,6 +427,23 @@ struct DKeyHash {
   }
 };
 
+template <int D>
+static cudaError_t launch_decode_tc(int G, dim3 grid, cudaStream_t stream, const CUtensorMap& tmQ,
+                                    const CUtensorMap& tmKV, const DecodeTcParams& p) {
+  constexpr size_t smem = (size_t)kSlots * DecodeTcSmem<D>::slot_bytes + DecodeTcSmem<D>::q_bytes +
+                          DecodeTcSmem<D>::p_bytes + 1024 + sizeof(DecodeTcBars);
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static PerDeviceOnce attr_once;
+  if (attr_once.first()) {
+    cudaFuncSetAttribute(attn_decode_tc_kernel<4, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<8, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<16, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  if (G <= 4) return launch_pdl(attn_decode_tc_kernel<4, D>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  if (G <= 8) return launch_pdl(attn_decode_tc_kernel<8, D>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  return launch_pdl(attn_decode_tc_kernel<16, D>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -421,7 +460,7 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
                                    float softcap, int window, int splits, void* tmp_o,
                                    void* tmp_lse, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (D != 128 || Hq % Hkv || Hq / Hkv > kNQ || (ldq & 7)) return -1;
+  if ((D != 128 && D != 256) || Hq % Hkv || Hq / Hkv > kNQ || (ldq & 7)) return -1;
   if (block_size < 8 || (block_size & 7) || (block_size < kTok && kTok % block_size) ||
       (block_size > kTok && block_size % kTok) || kTok / (block_size < kTok ? block_size : kTok) > 16)
     return -1;
@@ -468,19 +507,11 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
   p.window = window; p.splits = splits;
   p.tmp_o = (float*)tmp_o; p.tmp_lse = (float*)tmp_lse;
   p.status = device_status_word();
-  constexpr size_t smem = (size_t)kSlots * kSlotBytes + 4096 + 8192 + 1024 + sizeof(DecodeTcBars);
-  static PerDeviceOnce attr_once;
-  if (attr_once.first()) {
-    cudaFuncSetAttribute(attn_decode_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attn_decode_tc_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attn_decode_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  }
   dim3 grid(B, Hkv, splits);
   const int G = Hq / Hkv;
   cudaError_t le;
-  if (G <= 4) le = launch_pdl(attn_decode_tc_kernel<4>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
-  else if (G <= 8) le = launch_pdl(attn_decode_tc_kernel<8>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
-  else le = launch_pdl(attn_decode_tc_kernel<16>, grid, dim3(192), smem, stream, tmQ, tmKV, p);
+  if (D == 128) le = launch_decode_tc<128>(G, grid, stream, tmQ, tmKV, p);
+  else le = launch_decode_tc<256>(G, grid, stream, tmQ, tmKV, p);
   if (le != cudaSuccess) return -2;
   if (splits > 1)
     return b200_attn_decode_merge(tmp_o, tmp_lse, out, ldo, B, Hq, D, splits, stream);

@@ -310,12 +310,14 @@ def test_attn_decode_tcgen05_persistent(Hq, Hkv, bs, splits):
         assert _rel_err(out, exp) < 1e-2
 
 
+@pytest.mark.parametrize("D", [128, 256])
 @pytest.mark.parametrize("Hq,Hkv,bs,splits", [(32, 8, 16, 0), (4, 1, 32, 1), (32, 4, 16, 3),
-                                              (16, 16, 64, 2), (8, 1, 128, 4), (16, 1, 16, 2)])
-def test_attn_decode_tcgen05(Hq, Hkv, bs, splits):
-    """tcgen05 swapped-operand decode kernel vs the fp32 oracle and vs the CUDA-core kernel."""
+                                              (16, 16, 64, 2), (8, 1, 128, 4), (16, 1, 16, 2),
+                                              (24, 4, 32, 2)])
+def test_attn_decode_tcgen05(Hq, Hkv, bs, splits, D):
+    """tcgen05 swapped-operand decode kernel (head_dim 128 and 256) vs the fp32 oracle and vs the
+    CUDA-core kernel."""
     torch.manual_seed(21)
-    D = 128
     seq_lens = [1, 127, 128, 129, 700, 1234, 0, 31]
     lens_for_cache = [max(s, 1) for s in seq_lens]
     cache, bt = _make_paged(lens_for_cache, Hkv, D, bs)

@@ -87,3 +87,27 @@ def test_quant_nvfp4_activations():
     t, gidx = 77, 5
     off = ((t // 128) * (K // 64) + gidx // 4) * 512 + (t % 32) * 16 + ((t % 128) // 32) * 4 + gidx % 4
     assert s3[off].item() == sf[t, gidx].item()
+
+
+@pytest.mark.parametrize("n_tile", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (64, 768, 1024), (200, 1280, 2048), (16, 5120, 5120),
+                                   (1000, 520, 512)])
+def test_gemm_nvfp4_w4a4_block_scaled_mma(M, N, K, n_tile):
+    """kind::mxf4nvf4 with both operands in NVFP4 and the block scales in tensor memory, against the
+    fp32 product of the dequantised operands (the GEMM itself is exact up to the bf16 output)."""
+    torch.manual_seed(2)
+    x = (torch.randn(M, K, device=DEV) * 0.7).to(torch.bfloat16)
+    w = torch.randn(N, K, device=DEV) * 0.05
+    wp, wsf, g_w = Q.ref_quant_nvfp4_weights(w)
+    g_a = (448.0 * 6.0 / x.float().abs().max()).reshape(1)
+    ap, sfa = Q.quant_nvfp4(x, g_a, swizzle=True)
+    sfa_rows = Q.quant_nvfp4(x, g_a, swizzle=False)[1]
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    out = Q.gemm_nvfp4(ap, sfa, g_a, wp, Q.nvfp4_sf_chunks(wsf, 256), g_w, bias=bias, n_tile=n_tile)
+    assert ops.read_status() == 0
+    a_deq = Q.ref_dequant_nvfp4(ap, sfa_rows, 1.0 / g_a)
+    exp = a_deq @ Q.ref_dequant_nvfp4(wp, wsf, g_w).t() + bias.float()
+    assert _rel(out, exp) < 6e-3
+    # and the quantisation error of the activations stays what 4 bits allow
+    full = x.float() @ Q.ref_dequant_nvfp4(wp, wsf, g_w).t() + bias.float()
+    assert ((out.float() - full).norm() / full.norm()).item() < 0.2

@@ -6,6 +6,8 @@ same ops with the fp32 PyTorch restatements; it is the oracle the GPU path is co
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..ops import reference as ref
@@ -15,11 +17,28 @@ class QuantWeight:
     """NVFP4 weight of a linear layer: E2M1 pairs, one E4M3 scale per 16 values, fp32 tensor
     scale (multiplier). ``shape`` mimics the dense [N, K] weight it replaces."""
 
-    def __init__(self, packed, sf, gscale):
+    def __init__(self, packed, sf, gscale, input_gscale=None):
         self.packed, self.sf, self.gscale = packed, sf, gscale
         self.shape = (packed.shape[0], packed.shape[1] * 2)
         self.device = packed.device
         self._scratch = None
+        self._sf_chunks = None
+        # W4A4: global scale of the activation quantiser (448 * 6 / expected amax); checkpoints
+        # calibrated for W4A4 carry it, otherwise a fixed scale that keeps block maxima between
+        # 0.05 and 10^4 representable
+        self.input_gscale = input_gscale
+
+    def sf_chunks(self):
+        """Block scales in the 128 x 4 chunk layout of the block-scaled MMA (built once)."""
+        if self._sf_chunks is None:
+            from ..ops.quant import nvfp4_sf_chunks
+            self._sf_chunks = nvfp4_sf_chunks(self.sf, 256)
+        return self._sf_chunks
+
+    def act_gscale(self):
+        if self.input_gscale is None:
+            self.input_gscale = torch.full((1,), 4.0, dtype=torch.float32, device=self.device)
+        return self.input_gscale
 
     def numel(self):
         return self.packed.numel() + self.sf.numel()
@@ -190,6 +209,17 @@ class GpuBackend:
         self.ops = ops
         self.device = torch.device(device)
         ops.lib()  # fail loudly here if the kernel library is missing
+        # NVFP4 weights: "bf16" keeps activations in bf16 (W4A16), "nvfp4" quantises them per call
+        # and runs W4A4 on kind::mxf4nvf4 (what NVFP4 checkpoints are calibrated for)
+        self.w4a4 = os.environ.get("B200_NVFP4_ACTIVATIONS", "bf16") == "nvfp4"
+
+    def _w4a4_buffers(self, T: int, K: int):
+        """Persistent (packed activations, scale chunks) scratch of the activation quantiser."""
+        from .. import ops
+        rows = (T + 127) // 128 * 128
+        pk = ops.workspace(self.device, rows * (K // 2), "w4a4_act")
+        sf = ops.workspace(self.device, rows * (K // 16), "w4a4_sf")
+        return pk[: T * (K // 2)].view(T, K // 2), sf[: rows * (K // 16)]
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
         """``w`` is always a model weight here (never written by a kernel of the step), which
@@ -197,6 +227,14 @@ class GpuBackend:
         if isinstance(w, QuantWeight):
             from ..ops import quant as Q
             N, K = w.shape
+            if self.w4a4 and K % 256 == 0 and N % 8 == 0 and a.stride(-1) == 1:
+                # activations quantised to NVFP4 on the fly, both operands on the block-scaled MMA
+                g_a = w.act_gscale()
+                ap, sfa = Q.quant_nvfp4(a, g_a, swizzle=True, out=self._w4a4_buffers(a.shape[0], K))
+                y = Q.gemm_nvfp4(ap, sfa, g_a, w.packed, w.sf_chunks(), w.gscale, out=out, bias=bias)
+                if residual is not None:
+                    y = self.ops.add(y, residual) if out is None else out.copy_(self.ops.add(y, residual))
+                return y
             scratch = None
             if a.shape[0] > 128:
                 # one expansion buffer per device, shared by every layer (stream ordered)

@@ -290,9 +290,9 @@ def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, *, block_table: torch.
 
 
 def _decode_uses_tc(head_dim: int, group: int, block_size: int) -> bool:
-    """The tcgen05 swapped-operand decode kernel covers head_dim 128, GQA groups up to 16 and
-    page sizes that tile 128 tokens; everything else takes the CUDA-core kernel."""
-    if head_dim != 128 or group > 16 or block_size < 8 or block_size % 8:
+    """The tcgen05 swapped-operand decode kernel covers head_dim 128 and 256, GQA groups up to 16
+    and page sizes that tile 128 tokens; everything else takes the CUDA-core kernel."""
+    if head_dim not in (128, 256) or group > 16 or block_size < 8 or block_size % 8:
         return False
     return (128 % block_size == 0) if block_size <= 128 else (block_size % 128 == 0)
 
@@ -300,10 +300,10 @@ def _decode_uses_tc(head_dim: int, group: int, block_size: int) -> bool:
 def attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len,
                        block_size: int = 16) -> int:
     if _decode_uses_tc(head_dim, group, block_size):
-        # two CTAs fit on an SM: split only while every split still gets a slot in the first
-        # wave (a second, ragged wave plus the merge kernel costs more than it gains)
+        # two CTAs fit on an SM (one at head_dim 256): split only while every split still gets a
+        # slot in the first wave (a second, ragged wave plus the merge kernel costs more than it gains)
         ctas = max(1, batch * num_kv_heads)
-        want = (2 * num_sms()) // ctas
+        want = ((2 if head_dim == 128 else 1) * num_sms()) // ctas
         tiles = max(1, -(-max_seq_len // 128))
         return max(1, min(want, max(1, tiles // 2), 32))
     return lib().b200_attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len)

@@ -19,6 +19,8 @@ def _declare():
     _lib.declare("b200_gemm_fp8", [P, I, P, I, P, I, P, P, I, P, I, I, I, P], I)
     _lib.declare("b200_nvfp4_dequant", [P, P, P, P, L, I, P], I)
     _lib.declare("b200_gemm_w4a16", [P, I, P, P, P, P, I, P, I, I, I, P, Z, P], I)
+    _lib.declare("b200_gemm_nvfp4", [P, P, P, P, P, P, P, I, P, I, I, I, I, P, Z, P], I)
+    _lib.declare("b200_nvfp4_sf_to_chunks", [P, L, I, I, P, P], I)
     _lib.declare("b200_quant_fp8", [P, L, P, F, I, P, P, L, L, I, P], I)
     _lib.declare("b200_quant_nvfp4", [P, L, P, P, P, L, I, I, I, P], I)
     lib()
@@ -81,17 +83,51 @@ def quant_fp8(x, scale, out=None, norm_weight=None, eps=1e-6, gemma=False):
     return out
 
 
-def quant_nvfp4(x, gscale, K=None, silu_mul=False, swizzle=False):
-    """Returns (packed uint8 [T, K/2], block scales uint8). gscale fp32 [1]."""
+def quant_nvfp4(x, gscale, K=None, silu_mul=False, swizzle=False, out=None):
+    """Returns (packed uint8 [T, K/2], block scales uint8). gscale fp32 [1]. ``out``: a
+    (packed, scales) pair to write into (scale rows past T are left as they are: they only
+    ever meet zero-filled activation rows)."""
     _declare()
     T = x.shape[0]
     K = K or (x.shape[1] // 2 if silu_mul else x.shape[1])
-    packed = torch.empty((T, K // 2), dtype=torch.uint8, device=x.device)
     n_sf = ((T + 127) // 128) * 128 * (K // 16) if swizzle else T * (K // 16)
-    sf = torch.zeros(n_sf, dtype=torch.uint8, device=x.device)
+    if out is not None:
+        packed, sf = out
+        assert packed.shape == (T, K // 2) and sf.numel() >= n_sf
+    else:
+        packed = torch.empty((T, K // 2), dtype=torch.uint8, device=x.device)
+        sf = torch.zeros(n_sf, dtype=torch.uint8, device=x.device)
     check(lib().b200_quant_nvfp4(ptr(x), x.stride(0), ptr(gscale), ptr(packed), ptr(sf), T, K,
                                  int(silu_mul), int(swizzle), stream_ptr()), "quant_nvfp4")
     return packed, (sf if swizzle else sf.view(T, K // 16))
+
+
+def nvfp4_sf_chunks(sf: torch.Tensor, pad_rows: int = 256) -> torch.Tensor:
+    """Row-major e4m3 block scales ``[rows, K/16]`` -> the 128 x 4 chunk layout the block-scaled MMA
+    reads (rows padded with zero scales to a multiple of ``pad_rows``); done once per weight."""
+    _declare()
+    rows, kb = sf.shape
+    padded = (rows + pad_rows - 1) // pad_rows * pad_rows
+    out = torch.empty(padded * kb, dtype=torch.uint8, device=sf.device)
+    check(lib().b200_nvfp4_sf_to_chunks(ptr(sf.contiguous()), rows, kb * 16, pad_rows, ptr(out), stream_ptr()),
+          "nvfp4_sf_to_chunks")
+    return out
+
+
+def gemm_nvfp4(aq, sfa, g_a, wq, sfw, g_w, out=None, bias=None, n_tile: int = 0):
+    """W4A4: ``aq`` uint8 [M, K/2] and ``sfa`` from :func:`quant_nvfp4` (``swizzle=True``, global scale
+    ``g_a``); ``wq`` uint8 [N, K/2], ``sfw`` from :func:`nvfp4_sf_chunks`, ``g_w`` the weight's fp32
+    multiplier. Both products run on ``tcgen05.mma.kind::mxf4nvf4`` with the scales in tensor memory."""
+    _declare()
+    M, kh = aq.shape
+    N = wq.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
+    ws = workspace(aq.device, 64 << 20, "w4")
+    check(lib().b200_gemm_nvfp4(ptr(aq), ptr(sfa), ptr(g_a), ptr(wq), ptr(sfw), ptr(g_w), ptr(out), out.stride(0),
+                                ptr(bias), M, N, kh * 2, n_tile, ptr(ws), ws.numel(), stream_ptr()),
+          f"gemm_nvfp4 M={M} N={N} K={kh * 2}")
+    return out
 
 
 # ------------------------------------------------------------------------------ references
