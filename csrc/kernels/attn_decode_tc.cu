@@ -480,7 +480,7 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
     return true;
   };
   CUtensorMap tmQ, tmKV;
-  if (!get(DKey{q, (uint64_t)B, (uint64_t)Hq, (uint64_t)ldq},
+  if (!get(DKey{q, (uint64_t)B, (uint64_t)Hq | ((uint64_t)D << 32), (uint64_t)ldq},
            [&](CUtensorMap* m) {
              return encode_tmap_3d(m, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)D,
                                    (uint64_t)Hq, (uint64_t)B, (uint64_t)D * 2, (uint64_t)ldq * 2,
@@ -490,7 +490,7 @@ extern "C" int b200_attn_decode_tc(const void* q, int ldq, void* out, int ldo,
     return -3;
   const int box_rows = block_size < kTok ? block_size : kTok;
   const uint64_t rows = (uint64_t)num_blocks * 2 * block_size;
-  if (!get(DKey{kv_cache, rows, (uint64_t)Hkv, (uint64_t)box_rows + 7777},
+  if (!get(DKey{kv_cache, rows, (uint64_t)Hkv | ((uint64_t)D << 32), (uint64_t)box_rows + 7777},
            [&](CUtensorMap* m) {
              return encode_tmap_3d(m, kv_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)D,
                                    (uint64_t)Hkv, rows, (uint64_t)D * 2, (uint64_t)Hkv * D * 2, 64,

@@ -77,9 +77,9 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(ReduceNormPa
   const int row = p.rank * p.rows_per_rank + rl;
   const bool valid = row < p.M;
   if (blockIdx.x == 0) {
-    // counters of the other parity were last used one op ago and are idle now
-    for (int i = threadIdx.x; i < p.rows_per_rank / 32; i += blockDim.x)
-      p.rs_flags[npar * p.rs_flag_parity_stride + i] = 0;
+    // Gather counters of the other parity: their readers (this rank's GEMMs of the previous op)
+    // are done, and their next writers (the peers' reduce kernels two ops from now) cannot start
+    // before this rank's next scatter GEMM, which follows this kernel in the stream.
     for (int i = threadIdx.x; i < p.ag_groups; i += blockDim.x)
       p.ag_flags_local[npar * p.ag_flag_parity_stride + i] = 0;
     __threadfence();
@@ -161,6 +161,12 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_gather_kernel(ReduceNormPa
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+      // Last block: every block has consumed its arrival counter. Clear this parity's counters
+      // here, by their consumer, and not at the start of a later op: a peer that runs ahead may
+      // already be signalling the other parity, and nothing may wipe those arrivals. The next
+      // arrivals on THIS parity come from the peers' scatter GEMMs two ops from now, which cannot
+      // start before this rank's next scatter GEMM (after this kernel in the stream) has arrived.
+      for (int i = 0; i < p.rows_per_rank / 32; ++i) p.rs_flags[par * p.rs_flag_parity_stride + i] = 0;
       *p.done_counter = 0;
       __threadfence();
       atomicAdd(p.op_counter, 1u);   // the next fused op uses the other parity
@@ -182,8 +188,8 @@ __global__ void __launch_bounds__(256)
   const uint32_t par = *op_counter & 1, npar = par ^ 1;
   const int row = blockIdx.x;
   if (blockIdx.x == 0) {
-    for (int i = threadIdx.x; i < rows_per_rank / 32; i += blockDim.x)
-      rs_flags[npar * rs_flag_parity_stride + i] = 0;
+    // (the reduce-scatter arrival counters are cleared by the reduce kernel that consumed them; a
+    // peer that is already past this point may be signalling them for the next op)
     for (int i = threadIdx.x; i < ag_groups; i += blockDim.x) {
       ag_flags[npar * ag_flag_parity_stride + i] = 0;
       ag_flags[par * ag_flag_parity_stride + i] = 32;   // everything is local and complete

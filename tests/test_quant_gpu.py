@@ -40,7 +40,9 @@ def test_nvfp4_weights(M, N, K):
     w = torch.randn(N, K, device=DEV) * 0.05
     packed, sf, g = Q.ref_quant_nvfp4_weights(w)
     wd = Q.ref_dequant_nvfp4(packed, sf, g)
-    assert _rel(wd, w) < 0.15                       # the format itself: 4-bit values
+    # the format itself: 4-bit values (a Frobenius bound; single elements may be off by a sixth of
+    # their block's maximum)
+    assert ((wd - w).norm() / w.norm()).item() < 0.15
     got = Q.nvfp4_dequant(packed, sf, g)
     assert torch.equal(got.float(), wd.to(torch.bfloat16).float())
     a = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
@@ -74,13 +76,14 @@ def test_quant_nvfp4_activations():
     gs = (448.0 * 6.0 / x.float().abs().max()).reshape(1).float()
     packed, sf = Q.quant_nvfp4(x, gs)
     deq = Q.ref_dequant_nvfp4(packed, sf, (1.0 / gs))
-    assert _rel(deq, x) < 0.12
+    fro = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item()   # format quality: a norm bound
+    assert fro(deq, x) < 0.12
     # fused silu(gate) * up
     gu = torch.randn(T, 2 * K, device=DEV).to(torch.bfloat16)
     y = (torch.nn.functional.silu(gu[:, :K].float()) * gu[:, K:].float()).to(torch.bfloat16)
     gs2 = (448.0 * 6.0 / y.float().abs().max()).reshape(1).float()
     p2, s2 = Q.quant_nvfp4(gu, gs2, silu_mul=True)
-    assert _rel(Q.ref_dequant_nvfp4(p2, s2, 1.0 / gs2), y) < 0.12
+    assert fro(Q.ref_dequant_nvfp4(p2, s2, 1.0 / gs2), y) < 0.12
     # swizzled scale layout holds the same bytes
     p3, s3 = Q.quant_nvfp4(x, gs, swizzle=True)
     assert torch.equal(p3, packed)

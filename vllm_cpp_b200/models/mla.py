@@ -230,7 +230,9 @@ class DeepseekV2Model(MoeModel):
         if key not in self._splits:
             from ..ops import num_sms
             tiles = max(1, -(-max(self.max_position, 1) // 128))
-            s = max(1, min(-(-2 * num_sms() // max(B, 1)), max(1, tiles // 2), 16))
+            # one CTA fits on an SM (the latent ring takes the shared memory): split only while all
+            # (sequence, split) CTAs still run in one wave
+            s = max(1, min(num_sms() // max(B, 1), max(1, tiles // 2), 16))
             tmp = None
             if s > 1:
                 tmp = (torch.empty((B, self.H, s, 512), dtype=torch.float32, device=self.device),
