@@ -131,6 +131,23 @@ typedef struct B200TpReduce {
   void* done_counter;
 } B200TpReduce;
 
+// One-shot all-reduce (+ residual + RMSNorm) for decode-sized batches: every rank reads all ranks'
+// partial rows over peer pointers. peer_partial[r]: rank r's partial [M, H] of THIS op (the caller
+// alternates two buffers per rank); peer_flags[r]: rank r's array of `world` monotonic arrival
+// counters; seq / done_counter: local uint32 words, zero at start. norm_w null: plain sum.
+typedef struct B200TpOneShot {
+  int world, rank, M, H;
+  const void* peer_partial[8];
+  void* peer_flags[8];
+  void* seq;
+  void* done_counter;
+  void* residual;
+  const void* norm_w;
+  void* out;
+  float eps;
+  int gemma;
+} B200TpOneShot;
+
 // Row-owner scatter of the MoE combine (moe.cu): the same receive slots and counters as the
 // scatter epilogue of the GEMM.
 typedef struct B200MoeScatter {
@@ -232,6 +249,7 @@ int b200_scatter_sampled(void* last_sampled, const void* row_of, const void* sam
 uint64_t b200_splitmix64(uint64_t z);
 // ---- tp_fused.cu
 int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream);
+int b200_tp_oneshot_allreduce_norm(const B200TpOneShot* a, cudaStream_t stream);
 int b200_tp_first_norm(const void* hidden, void* residual_shard, const void* w, void* x_full, long long x_parity_stride, void* ag_flags, int ag_flag_parity_stride, int ag_groups, void* rs_flags, int rs_flag_parity_stride, int rank, int rows_per_rank, int M, int H, float eps, int gemma, void* op_counter, void* done_counter, cudaStream_t stream);
 int b200_tp_gather_rows(const void* x_base, long long x_parity_stride, int H, const void* idx, int n, const void* ag_flags, int ag_flag_parity_stride, const void* op_counter, int M, void* out, cudaStream_t stream);
 void* b200_symm_alloc(size_t bytes);

@@ -265,11 +265,161 @@ __global__ void __launch_bounds__(128)
   for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) d[i] = s[i];
 }
 
+
+// ------------------------------------------------------------------------------------------
+// One-shot all-reduce + residual + RMSNorm for small batches (decode-sized steps).
+// Every rank holds its partial product [M, H] in a buffer its peers can read; every rank reads all
+// `world` partials of every row (its own included) straight from their owners, sums them in rank
+// order (so all ranks get the same bits), adds the residual, and normalises. No scatter, no
+// gather, one kernel between two GEMMs. Synchronisation: monotonic arrival counters, one per
+// source rank, never reset: block 0 tells every peer "my partial number `seq + 1` is complete",
+// each block waits until all peers have said the same, and the last block advances `seq`. The
+// partial buffers alternate with the op's parity: a rank can only overwrite the buffer of op k
+// in its GEMM of op k + 2, which it reaches after the wait of op k + 1, i.e. after every peer has
+// finished reading op k.
+// ------------------------------------------------------------------------------------------
+struct OneShotParams {
+  int world, rank, M, H;
+  const __nv_bfloat16* peer_partial[8];   // this op's partial buffer on every rank
+  uint32_t* peer_flags[8];                // arrival counters [world] on every rank
+  uint32_t* seq;                          // local: completed one-shot ops
+  uint32_t* done_counter;                 // local
+  __nv_bfloat16* residual;                // [M, H] local, updated in place (may be null)
+  const __nv_bfloat16* norm_w;            // null: plain sum, no norm
+  __nv_bfloat16* out;                     // [M, H] normalised rows (or the sum when norm_w is null)
+  float eps;
+  int gemma;
+  int* status;
+  long long peer_wait;
+};
+
+__global__ void __launch_bounds__(256) tp_oneshot_allreduce_norm_kernel(OneShotParams p) {
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  extern __shared__ uint4 row_cache[];
+  const uint32_t target = *p.seq + 1;
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    // the GEMM that wrote this rank's partial is an earlier kernel of this stream: complete and
+    // visible at device scope; publish it to the peers
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flags[threadIdx.x] + p.rank) : "memory");
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    // wrap-safe comparison of monotonic counters
+    const uint32_t* f = p.peer_flags[p.rank] + threadIdx.x;
+    long long t0 = clock64();
+    uint32_t it = 0;
+    while (true) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((int32_t)(v - target) >= 0) break;
+      if (((++it) & 0xff) == 0 && clock64() - t0 > p.peer_wait) {
+        atomicExch(p.status, (int)kErrFlagTimeout);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const int row = blockIdx.x;
+  if (s_ok && row < p.M) {
+    const int nv = p.H >> 3;
+    uint4* rr = p.residual ? reinterpret_cast<uint4*>(p.residual + (size_t)row * p.H) : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int r = 0; r < p.world; ++r) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.peer_partial[r] + (size_t)row * p.H + i * 8);
+        float2 f;
+        f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
+        f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
+        f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
+        f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+      }
+      if (rr) {
+        const uint4 r = rr[i];
+        float2 f;
+        f = unpack_bf16x2(r.x); acc[0] += f.x; acc[1] += f.y;
+        f = unpack_bf16x2(r.y); acc[2] += f.x; acc[3] += f.y;
+        f = unpack_bf16x2(r.z); acc[4] += f.x; acc[5] += f.y;
+        f = unpack_bf16x2(r.w); acc[6] += f.x; acc[7] += f.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      if (rr) rr[i] = o;
+      row_cache[i] = o;
+      float2 f;
+      f = unpack_bf16x2(o.x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(o.y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(o.z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(o.w); ss += f.x * f.x + f.y * f.y;
+    }
+    uint4* orow = reinterpret_cast<uint4*>(p.out + (size_t)row * p.H);
+    if (!p.norm_w) {
+      __syncthreads();
+      for (int i = threadIdx.x; i < nv; i += blockDim.x) orow[i] = row_cache[i];
+    } else {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+      const float inv = rsqrtf(tot / (float)p.H + p.eps);
+      const float g = p.gemma ? 1.f : 0.f;
+      const uint4* wr = reinterpret_cast<const uint4*>(p.norm_w);
+      for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        const uint4 v = row_cache[i], wv = wr[i];
+        uint4 o;
+        float2 a, b;
+        a = unpack_bf16x2(v.x); b = unpack_bf16x2(wv.x); o.x = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+        a = unpack_bf16x2(v.y); b = unpack_bf16x2(wv.y); o.y = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+        a = unpack_bf16x2(v.z); b = unpack_bf16x2(wv.z); o.z = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+        a = unpack_bf16x2(v.w); b = unpack_bf16x2(wv.w); o.w = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+        orow[i] = o;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.done_counter, 1u) == gridDim.x - 1) {
+      *p.done_counter = 0;
+      __threadfence();
+      atomicAdd(p.seq, 1u);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+int b200_tp_oneshot_allreduce_norm(const B200TpOneShot* a, cudaStream_t stream) {
+  if (!a || a->world < 1 || a->world > 8 || a->M <= 0 || (a->H & 7) || a->H > 32768) return -1;
+  OneShotParams p;
+  p.world = a->world; p.rank = a->rank; p.M = a->M; p.H = a->H;
+  for (int i = 0; i < a->world; ++i) {
+    p.peer_partial[i] = (const __nv_bfloat16*)a->peer_partial[i];
+    p.peer_flags[i] = (uint32_t*)a->peer_flags[i];
+  }
+  p.seq = (uint32_t*)a->seq; p.done_counter = (uint32_t*)a->done_counter;
+  p.residual = (__nv_bfloat16*)a->residual; p.norm_w = (const __nv_bfloat16*)a->norm_w;
+  p.out = (__nv_bfloat16*)a->out; p.eps = a->eps; p.gemma = a->gemma;
+  p.status = device_status_word();
+  p.peer_wait = peer_wait_cycles();
+  tp_oneshot_allreduce_norm_kernel<<<a->M, 256, (size_t)a->H * 2, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
 
 
 int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream) {

@@ -70,3 +70,60 @@ def test_engine_raises_engine_dead_after_a_kernel_gave_up(short_peer_wait):
             llm.step()
     assert ops.read_status() == ERR_FLAG_TIMEOUT
     tpf.close()
+
+
+def test_oneshot_allreduce_norm_on_one_gpu_with_a_stand_in_peer():
+    """The one-shot all-reduce + residual + RMSNorm kernel with local buffers standing in for a
+    second rank: numerics against fp32, monotonic counters over several ops, and an arrival that
+    never comes makes the bounded wait report kErrFlagTimeout and leave the engine usable."""
+    import ctypes
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.ops import reference as ref
+    from vllm_cpp_b200.ops._lib import check, lib, ptr, stream_ptr
+    from vllm_cpp_b200.parallel.tp_fused import B200TpOneShot, _declare
+    _declare()
+    dev = torch.device("cuda")
+    T, H = 37, 512
+    torch.manual_seed(0)
+    mine = (torch.randn(T, H, device=dev)).to(torch.bfloat16)
+    peer = (torch.randn(T, H, device=dev)).to(torch.bfloat16)
+    resid = (torch.randn(T, H, device=dev)).to(torch.bfloat16)
+    w = (torch.rand(H, device=dev) + 0.5).to(torch.bfloat16)
+    out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)          # [2 counters | ... | seq @32 | done @48]
+    peer_flags = torch.zeros(64, dtype=torch.int32, device=dev)     # what this rank signals on the "peer"
+
+    def launch(res):
+        a = B200TpOneShot()
+        a.world, a.rank, a.M, a.H = 2, 0, T, H
+        a.peer_partial[0], a.peer_partial[1] = ptr(mine), ptr(peer)
+        a.peer_flags[0], a.peer_flags[1] = ptr(flags), ptr(peer_flags)
+        a.seq, a.done_counter = flags.data_ptr() + 128, flags.data_ptr() + 192
+        a.residual, a.norm_w, a.out = ptr(res), ptr(w), ptr(out)
+        a.eps, a.gemma = 1e-6, 0
+        check(lib().b200_tp_oneshot_allreduce_norm(ctypes.byref(a), stream_ptr()), "oneshot")
+
+    old = lib().b200_set_peer_wait_cycles(2_000_000)       # about a millisecond
+    try:
+        for op in range(3):
+            flags[1] = op + 1                       # the stand-in peer's arrival for this op
+            r = resid.clone()
+            launch(r)
+            torch.cuda.synchronize()
+            s = (mine.float() + peer.float() + resid.float()).to(torch.bfloat16)
+            exp, _ = ref.rmsnorm(s, w, 1e-6)
+            assert torch.equal(r, s)
+            assert ((out.float() - exp.float()).norm() / exp.float().norm()).item() < 5e-3
+            assert int(flags[0]) == op + 1 and int(peer_flags[0]) == op + 1 and int(flags[32]) == op + 1
+            assert ops.read_status() == 0
+        # no arrival for op 4: the wait runs out, the kernel returns and reports it
+        launch(resid.clone())
+        torch.cuda.synchronize()
+        assert ops.read_status() == 2
+        # and the next launch works once the peer has caught up
+        flags[1] = 5
+        launch(resid.clone())
+        torch.cuda.synchronize()
+        assert ops.read_status() == 0
+    finally:
+        lib().b200_set_peer_wait_cycles(old)

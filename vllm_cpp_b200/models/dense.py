@@ -269,8 +269,15 @@ class DenseModel:
                 and c.residual_multiplier == 1.0 and c.hidden_size % 8 == 0)
 
     def enable_fused_tp(self, max_tokens: int) -> None:
-        from ..parallel.tp_fused import TpFusedContext
+        from ..parallel.tp_fused import OneShotAllReduce, TpFusedContext
         self.tpf = TpFusedContext(self.comm, self.device, self.cfg.hidden_size, max_tokens)
+        # decode-sized steps: one-shot all-reduce + norm between plain small-M GEMMs instead of the
+        # scatter / reduce / gather chain (B200_TP_ONESHOT_MAX=0 keeps every step on the chain)
+        self.oneshot_max = min(int(os.environ.get("B200_TP_ONESHOT_MAX", "256")), max_tokens)
+        self.tpf.oneshot = None
+        if self.oneshot_max > 0 and type(self).forward is DenseModel.forward:
+            self.tpf.oneshot = OneShotAllReduce(self.comm, self.device, self.cfg.hidden_size,
+                                                self.oneshot_max)
         # with a "greedy_out" buffer in the step context the forward returns None and leaves the
         # argmax ids there (see the end of _forward_tp_fused)
         self.samples_greedy = self.cfg.final_logit_softcap <= 0
@@ -280,6 +287,8 @@ class DenseModel:
         epilogue), followed by reduce + residual + RMSNorm + all-gather on the row shard, and
         every qkv / gate_up GEMM waits for its gathered rows tile by tile."""
         c, be, T, tpf = self.cfg, self.be, ctx.num_tokens, self.tpf
+        if tpf.oneshot is not None and T <= self.oneshot_max:
+            return self._forward_tp_oneshot(ctx)
         H, eps = c.hidden_size, c.rms_norm_eps
         act_kind = ACT_KIND.get(c.hidden_act, 0)
         hidden = self.bufs.get("hidden", T, H)
@@ -328,6 +337,64 @@ class DenseModel:
             tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)
         return self._tp_fused_logits(ctx, T)
 
+    def _forward_tp_oneshot(self, ctx: StepContext):
+        """Decode-sized steps under tensor parallelism: every projection is a plain small-batch GEMM
+        on this rank's shard; o_proj / down_proj write their partial rows into a peer-readable buffer
+        and ONE kernel per site reads all ranks' partials, adds the residual and applies the next
+        RMSNorm (``OneShotAllReduce``). Same arithmetic on every rank, so all ranks hold the same
+        activations bit for bit. Two sites per block keep the buffer parity of a forward pass fixed."""
+        c, be, T, osr = self.cfg, self.be, ctx.num_tokens, self.tpf.oneshot
+        H, eps = c.hidden_size, c.rms_norm_eps
+        act_kind = ACT_KIND.get(c.hidden_act, 0)
+        hidden = self.bufs.get("hidden", T, H)
+        resid = self.bufs.get("resid", T, H)
+        normed = self.bufs.get("normed", T, H)
+        qkv = self.bufs.get("qkv", T, (self.hq + 2 * self.hkv) * self.D)
+        attn = self.bufs.get("attn", T, self.hq * self.D)
+        gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
+        act = self.bufs.get("act", T, self.inter)
+        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                     vocab_total=c.vocab_size, scale=c.embed_scale)
+        self.comm.all_reduce(hidden)
+        resid.copy_(hidden)
+        x = be.rmsnorm(hidden, self.layers[0]["ln1"], eps, out=normed, gemma=c.gemma_norm)
+        osr.begin_forward()
+        pos = ctx.positions[:T]
+        n_layers = len(self.layers)
+        for l, L in enumerate(self.layers):
+            grp = self.layer_group[l]
+            window = c.sliding_window if (c.sliding_window and (
+                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            be.gemm(x, L["qkv"], out=qkv)
+            be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                       head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
+                       q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=eps,
+                       gemma=c.gemma_norm, slot_mapping=ctx.slot_mapping[grp][:T],
+                       kv_cache=self.kv_caches[l], block_size=self.block_size)
+            be.attention(qkv[:, : self.hq * self.D], self.kv_caches[l], ctx, grp,
+                         num_q_heads=self.hq, num_kv_heads=self.hkv, head_dim=self.D,
+                         block_size=self.block_size, scale=self.scale, out=attn,
+                         softcap=c.attn_logit_softcap, window=window)
+            be.gemm(attn, L["o"], out=osr.partial_out(T))
+            x = osr.allreduce_norm(T, L["ln2"], eps, c.gemma_norm, resid, normed)
+            if self.gate_up_il:
+                a = be.gemm_gated(x, L["gate_up"], act_kind, out=act, scratch=gate_up)
+            else:
+                be.gemm(x, L["gate_up"], out=gate_up)
+                a = be.act_and_mul(gate_up, act_kind, out=act)
+            be.gemm(a, L["down"], out=osr.partial_out(T))
+            nw = self.layers[l + 1]["ln1"] if l + 1 < n_layers else self.w["final_norm"]
+            x = osr.allreduce_norm(T, nw, eps, c.gemma_norm, resid, normed)
+        # `normed` holds the final norm of every row
+        if ctx.decode_only_full_logits:
+            n, last = T, normed
+        else:
+            n = ctx.num_logits
+            last = be.gather_rows(normed, ctx.logits_indices[:n], out=self.bufs.get("last", n, H))
+        logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
+        be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
+        return self._tp_logits_tail(ctx, logits, n)
+
     def _tp_fused_logits(self, ctx: StepContext, T: int):
         """lm_head over the gathered final-norm rows. With a ``greedy_out`` buffer in the step
         context the argmax ids are left there and None is returned; otherwise fp32 logits
@@ -342,6 +409,11 @@ class DenseModel:
             last = tpf.gather_rows(T, ctx.logits_indices[:n], self.bufs.get("last", n, H))
             logits = self.bufs.get("logits", n, self.vocab_shard, torch.float32)
             be.gemm(last, self.w["lm_head"], out=logits, out_dtype=torch.float32)
+        return self._tp_logits_tail(ctx, logits, n)
+
+    def _tp_logits_tail(self, ctx: StepContext, logits: torch.Tensor, n: int):
+        """This rank's vocabulary shard of the logits -> argmax ids (greedy steps) or full logits."""
+        c = self.cfg
         greedy_out = ctx.extra.get("greedy_out")
         if greedy_out is not None and c.final_logit_softcap <= 0:
             # Vocabulary-parallel greedy sampling: every rank reduces its shard to one candidate

@@ -336,8 +336,10 @@ class Qwen35Model(DenseModel):
                                            c.hidden_size, self.moe_inter)
 
     def fused_tp_supported(self) -> bool:
+        # the fused GEMMs take bf16 weights; NVFP4 checkpoints run tensor parallel over NCCL
         return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
-                and self.cfg.hidden_size % 8 == 0)
+                and self.cfg.hidden_size % 8 == 0 and not getattr(self, "quantized", None)
+                and not self.cfg.quant)
 
     # ------------------------------------------------------------------ expert block
     _moe_block = MoeModel._moe_block

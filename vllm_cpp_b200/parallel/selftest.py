@@ -102,8 +102,11 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (150, 9, 300, 40)]
     sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
 
-    def run(tp, fused, native=True):
+    def run(tp, fused, native=True, oneshot=False):
         os.environ["B200_NATIVE_LAYERS"] = "1" if native else "0"
+        # every step of this check is decode-sized: the chain of scatter / reduce / gather kernels
+        # is what `fused` exercises, the one-shot path gets its own run
+        os.environ["B200_TP_ONESHOT_MAX"] = "256" if oneshot else "0"
         par = ParallelConfig(tensor_parallel_size=tp, rank=comm.rank if tp > 1 else 0,
                              local_rank=local_rank, fused_collectives=fused,
                              enable_expert_parallel=bool(cfg.num_experts) and tp > 1)
@@ -120,9 +123,12 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
     base = run(1, False)
     nccl = run(comm.world, False)
     fused = run(comm.world, True)
-    # the native layer stack exists for the plain dense block only; elsewhere both runs are the same path
+    # the native layer stack and the one-shot path exist for the plain dense block only; elsewhere the
+    # runs would repeat the same path
     per_op = run(comm.world, True, native=False) if shape == "tiny-qwen3" else fused
+    oneshot = run(comm.world, True, oneshot=True) if shape == "tiny-qwen3" else fused
     os.environ.pop("B200_NATIVE_LAYERS", None)
+    os.environ.pop("B200_TP_ONESHOT_MAX", None)
 
     def agree(a, b):
         hit = tot = 0
@@ -142,23 +148,28 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
     R["agree_nccl_vs_tp1"] = agree(nccl, base)
     R["agree_fused_vs_nccl"] = agree(fused, nccl)
     R["native_equals_per_op"] = fused == per_op      # same kernels, same arguments: same bits
+    R["agree_oneshot_vs_tp1"] = agree(oneshot, base)
+    R["oneshot_first_tokens_equal"] = [x[0] for x in oneshot] == [x[0] for x in base]
+    same1 = comm.all_gather_object(oneshot)
+    R["oneshot_ranks_identical"] = all(s == same1[0] for s in same1)
     R["status"] = ops.read_status()
     # every rank must hold the same tokens
     same = comm.all_gather_object(fused)
     R["ranks_identical"] = all(s == same[0] for s in same)
     results[f"engine_{tag}"] = R
     return (R["first_tokens_equal"] and R["agree_fused_vs_tp1"] > 0.7 and R["native_equals_per_op"]
-            and R["ranks_identical"] and R["status"] == 0)
+            and R["ranks_identical"] and R["status"] == 0 and R["oneshot_first_tokens_equal"]
+            and R["agree_oneshot_vs_tp1"] > 0.7 and R["oneshot_ranks_identical"])
 
 
 def bench_block(comm, device, results):
     """One transformer block's communication-bound half at Llama-8B width, fused vs NCCL."""
     from vllm_cpp_b200 import ops
-    from vllm_cpp_b200.parallel.tp_fused import TpFusedContext
+    from vllm_cpp_b200.parallel.tp_fused import OneShotAllReduce, TpFusedContext
     W, r = comm.world, comm.rank
     H, I = 4096, 14336
     rows = []
-    for T in (256, 2048, 8192):
+    for T in (64, 256, 2048, 8192):
         # buffers sized like an engine's (its token budget, not this batch): small batches then have
         # room for the k-split slots of the scatter GEMM
         tpf = TpFusedContext(comm, device, H, max(T, 8192))
@@ -183,6 +194,17 @@ def bench_block(comm, device, results):
             x = ops.rmsnorm(tmp, nw, 1e-6, residual=resid)
             ops.gemm(x, w_gu, out=out)
 
+        osr = OneShotAllReduce(comm, device, H, T) if T <= 256 else None
+        xn = torch.empty(T, H, device=device, dtype=torch.bfloat16)
+
+        def oneshot():
+            # decode-sized steps: plain small-batch GEMMs around one all-reduce + norm kernel
+            osr.begin_forward()
+            for _ in range(2):          # two sites keep the buffer parity of a pass fixed
+                ops.gemm(a, w_down, out=osr.partial_out(T))
+                osr.allreduce_norm(T, nw, 1e-6, False, resid, xn)
+                ops.gemm(xn, w_gu, out=out)
+
         def timeit(fn):
             for _ in range(3):
                 fn()
@@ -202,17 +224,25 @@ def bench_block(comm, device, results):
         st_fused = ops.read_status()
         tn = timeit(nccl)
         st_nccl = ops.read_status()
+        t1 = timeit(oneshot) / 2 if osr is not None else None
+        st_one = ops.read_status()
         flops = 2.0 * T * (I // W) * H + 2.0 * T * H * (2 * I // W)
         nv_bytes = 2.0 * T * H * 2 * (W - 1) / W          # scatter out + gather in, per rank
         roof_ms = max(flops / 1393e12, nv_bytes / 770e9) * 1e3
         rows.append(dict(T=T, fused_ms=tf, nccl_ms=tn, speedup=tn / tf, roofline_ms=roof_ms,
                          frac_of_roofline=roof_ms / tf, nvlink_mb_per_rank=nv_bytes / 1e6,
                          status_after_fused=st_fused, status_after_nccl=st_nccl))
+        if t1 is not None:
+            rows[-1].update(oneshot_ms=t1, oneshot_speedup=tn / t1, status_after_oneshot=st_one,
+                            oneshot_nvlink_mb_per_rank=2.0 * T * H * (W - 1) / 1e6)
         torch.cuda.synchronize()
         comm.barrier()
         tpf.close()
+        if osr is not None:
+            osr.close()
     results["block_bench"] = rows
-    results["block_bench_status"] = max([ops.read_status()] + [max(r["status_after_fused"], r["status_after_nccl"])
+    results["block_bench_status"] = max([ops.read_status()] + [max(r["status_after_fused"], r["status_after_nccl"],
+                                                                   r.get("status_after_oneshot", 0))
                                                                for r in rows])
 
 

@@ -50,8 +50,17 @@ class B200TpReduce(ctypes.Structure):
                 ("done_counter", ctypes.c_void_p)]
 
 
+class B200TpOneShot(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("M", ctypes.c_int), ("H", ctypes.c_int),
+                ("peer_partial", ctypes.c_void_p * 8), ("peer_flags", ctypes.c_void_p * 8),
+                ("seq", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
+                ("residual", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("eps", ctypes.c_float), ("gemma", ctypes.c_int)]
+
+
 def _declare():
     P, I, L, F, Z = _lib.P, _lib.I, _lib.L, _lib.F, _lib.Z
+    _lib.declare("b200_tp_oneshot_allreduce_norm", [ctypes.POINTER(B200TpOneShot), P], I)
     _lib.declare("b200_symm_alloc", [Z], P)
     _lib.declare("b200_symm_free", [P], I)
     _lib.declare("b200_ipc_get_handle", [P, P], I)
@@ -114,6 +123,55 @@ class SymmetricBuffer:
 
 def _round_up(a, b):
     return (a + b - 1) // b * b
+
+
+class OneShotAllReduce:
+    """Decode-sized batches: the GEMM writes this rank's partial rows into one of two peer-readable
+    buffers and one kernel per all-reduce site reads every rank's partial, sums in rank order, adds
+    the residual and applies RMSNorm (``tp_oneshot_allreduce_norm_kernel``). The two buffers
+    alternate with the parity of the op within the forward pass (host-known, so the pointers a CUDA
+    graph captures stay right); the arrival counters are monotonic and live on the device."""
+
+    def __init__(self, comm, device, hidden: int, max_tokens: int):
+        self.comm, self.device, self.H = comm, device, hidden
+        self.world, self.rank = comm.world, comm.rank
+        self.max_tokens = max_tokens
+        self.partial = SymmetricBuffer(comm, 2 * max_tokens * hidden * 2, device)
+        # [world arrival counters | pad | seq | done]
+        self.flags = SymmetricBuffer(comm, 256, device)
+        self._views = self.partial.tensor.view(torch.bfloat16).view(2, max_tokens, hidden)
+        self.op = 0                       # ops issued in the current forward pass
+        comm.barrier()
+
+    def begin_forward(self) -> None:
+        self.op = 0
+
+    def partial_out(self, T: int) -> torch.Tensor:
+        """Where the next partial-product GEMM must write its ``[T, H]`` output."""
+        return self._views[self.op & 1][:T]
+
+    def allreduce_norm(self, T: int, weight, eps: float, gemma: bool, residual, out: torch.Tensor):
+        """Sum of all ranks' partials (+ ``residual``, updated in place) -> RMSNorm -> ``out``;
+        ``weight`` None leaves the plain sum in ``out``."""
+        a = B200TpOneShot()
+        a.world, a.rank, a.M, a.H = self.world, self.rank, T, self.H
+        off = (self.op & 1) * self.max_tokens * self.H * 2
+        for r in range(self.world):
+            a.peer_partial[r] = self.partial.ptrs[r] + off
+            a.peer_flags[r] = self.flags.ptrs[r]
+        a.seq = self.flags.local + 128
+        a.done_counter = self.flags.local + 192
+        a.residual = ptr(residual)
+        a.norm_w = ptr(weight)
+        a.out = ptr(out)
+        a.eps, a.gemma = eps, int(gemma)
+        check(lib().b200_tp_oneshot_allreduce_norm(ctypes.byref(a), stream_ptr()), "tp_oneshot")
+        self.op += 1
+        return out
+
+    def close(self):
+        self.partial.close()
+        self.flags.close()
 
 
 class TpFusedContext:
@@ -282,3 +340,5 @@ class TpFusedContext:
     def close(self):
         for b in (self.recv, self.x_full, self.flags):
             b.close()
+        if getattr(self, "oneshot", None) is not None:
+            self.oneshot.close()
