@@ -258,12 +258,12 @@ __global__ void __launch_bounds__(256)
 
 // NVFP4 activation quant: per 16 values, scale = e4m3(amax / 6 * gs) where gs is the global
 // scale (448 * 6 / tensor amax); values = e2m1(x * gs / scale). mode 0: x; mode 1: silu(gate) * up
-// with x = [gate | up] rows of width 2K. Scales row-major [T, K/16] or in the 128x4-swizzled
+// with x = [gate | up] rows of width 2K; mode 2: x * sigmoid(gate) with a separate gate tensor. Scales row-major [T, K/16] or in the 128x4-swizzled
 // layout of block-scaled MMAs (swizzle = 1).
 __global__ void __launch_bounds__(128)
     quant_nvfp4_kernel(const bf16* __restrict__ x, long ldx, const float* __restrict__ gscale,
                        uint8_t* __restrict__ out, uint8_t* __restrict__ sf, long T, int K, int mode,
-                       int swizzle) {
+                       int swizzle, const bf16* __restrict__ gate = nullptr, long ldg = 0) {
   const long groups = T * (long)(K / 16);
   const float gs = *gscale;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < groups; i += (long)gridDim.x * blockDim.x) {
@@ -278,6 +278,10 @@ __global__ void __launch_bounds__(128)
       if (mode == 1) {
         const float u = __bfloat162float(src[K + e]);
         a = __bfloat162float(__float2bfloat16(a / (1.f + __expf(-a)) * u));
+      } else if (mode == 2) {
+        // attention output gate: x * sigmoid(gate), rounded to bf16 as the separate kernel would
+        const float g = __bfloat162float(gate[t * ldg + (long)gidx * 16 + e]);
+        a = __bfloat162float(__float2bfloat16(a / (1.f + __expf(-g))));
       }
       v[e] = a;
       amax = fmaxf(amax, fabsf(a));
@@ -300,6 +304,67 @@ __global__ void __launch_bounds__(128)
       so = ((size_t)rb * (K / 64) + kb) * 512 + (size_t)(r % 32) * 16 + (size_t)(r / 32) * 4 + kk;
     } else {
       so = (size_t)i;
+    }
+    sf[so] = sb;
+  }
+}
+
+// (residual +) RMSNorm -> NVFP4 in one pass over the row: one block per token keeps the row in
+// shared memory between the sum of squares and the quantisation; the updated residual (bf16) is
+// written back when given, the normalised row itself only when `normed` is given. The normalised
+// values are rounded to bf16 before quantisation, as a separate norm kernel would hand them over.
+__global__ void __launch_bounds__(256)
+    rmsnorm_quant_nvfp4_kernel(const bf16* __restrict__ x, long ldx, bf16* residual, const bf16* __restrict__ w,
+                               float eps, int gemma, const float* __restrict__ gscale, uint8_t* __restrict__ out,
+                               uint8_t* __restrict__ sf, bf16* normed, long T, int K, int swizzle) {
+  extern __shared__ float rowf[];          // K floats
+  __shared__ float red[8];
+  const long t = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    float v = __bfloat162float(x[t * ldx + i]);
+    if (residual) {
+      v = __bfloat162float(__float2bfloat16(v + __bfloat162float(residual[t * K + i])));
+      residual[t * K + i] = __float2bfloat16(v);
+    }
+    rowf[i] = v;
+    ss += v * v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = rsqrtf(tot / (float)K + eps);
+  const float gs = *gscale, gadd = gemma ? 1.f : 0.f;
+  for (int gidx = threadIdx.x; gidx < K / 16; gidx += blockDim.x) {
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const int c = gidx * 16 + e;
+      const float n = __bfloat162float(__float2bfloat16(rowf[c] * inv * (__bfloat162float(w[c]) + gadd)));
+      if (normed) normed[t * K + c] = __float2bfloat16(n);
+      v[e] = n;
+      amax = fmaxf(amax, fabsf(n));
+    }
+    const uint8_t sb = float_to_e4m3(amax * gs / 6.f);
+    const float sdec = e4m3_to_float(sb);
+    const float mul = sdec > 0.f ? gs / sdec : 0.f;
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      w0 |= float_to_e2m1(v[e] * mul) << (e * 4);
+      w1 |= float_to_e2m1(v[8 + e] * mul) << (e * 4);
+    }
+    reinterpret_cast<uint2*>(out)[t * (K / 16) + gidx] = make_uint2(w0, w1);
+    size_t so;
+    if (swizzle) {
+      const long rb = t / 128, r = t % 128;
+      so = ((size_t)rb * (K / 64) + gidx / 4) * 512 + (size_t)(r % 32) * 16 + (size_t)(r / 32) * 4 + gidx % 4;
+    } else {
+      so = (size_t)t * (K / 16) + gidx;
     }
     sf[so] = sb;
   }
@@ -377,6 +442,34 @@ int b200_quant_nvfp4(const void* x, long ldx, const float* gscale, void* out, vo
   if (blocks > (long)b200_num_sms() * 32) blocks = (long)b200_num_sms() * 32;
   quant_nvfp4_kernel<<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)x, ldx, gscale, (uint8_t*)out, (uint8_t*)sf,
                                                            T, K, mode, swizzle);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// x * sigmoid(gate) -> NVFP4 (the gated attention output that feeds o_proj).
+int b200_quant_nvfp4_gated(const void* x, long ldx, const void* gate, long ldg, const float* gscale, void* out,
+                           void* sf, long T, int K, int swizzle, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((K & 15) || (swizzle && (K & 63)) || !gate) return -1;
+  const long groups = T * (long)(K / 16);
+  long blocks = (groups + 127) / 128;
+  if (blocks > (long)b200_num_sms() * 32) blocks = (long)b200_num_sms() * 32;
+  quant_nvfp4_kernel<<<(unsigned)blocks, 128, 0, stream>>>((const bf16*)x, ldx, gscale, (uint8_t*)out, (uint8_t*)sf,
+                                                           T, K, 2, swizzle, (const bf16*)gate, ldg);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// (residual += x;) RMSNorm -> NVFP4. residual [T, K] contiguous bf16 or null; normed [T, K] bf16 or null.
+int b200_rmsnorm_quant_nvfp4(const void* x, long ldx, void* residual, const void* weight, float eps, int gemma,
+                             const float* gscale, void* out, void* sf, void* normed, long T, int K, int swizzle,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((K & 15) || (swizzle && (K & 63)) || K > 32768) return -1;
+  static PerDeviceOnce attr_once;
+  if (attr_once.first())
+    cudaFuncSetAttribute(rmsnorm_quant_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4);
+  rmsnorm_quant_nvfp4_kernel<<<(unsigned)T, 256, (size_t)K * 4, stream>>>(
+      (const bf16*)x, ldx, (bf16*)residual, (const bf16*)weight, eps, gemma, gscale, (uint8_t*)out, (uint8_t*)sf,
+      (bf16*)normed, T, K, swizzle);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -153,6 +153,75 @@ __global__ void moe_offsets_kernel(int32_t* meta, int E, int chunk_rows, int32_t
   meta[2 * E] = off;
   meta[3 * E + 1] = nc;
 }
+// Decode-sized batches: histogram, offsets, chunk table and scatter in ONE block (counts and
+// cursors in shared memory) instead of a memset and three launches, one of them a single thread
+// walking the experts. E <= 256. The order of the rows inside an expert depends on the atomics,
+// which is harmless: every row's product is independent and the combine goes through pair_pos.
+__global__ void __launch_bounds__(1024)
+    moe_sort_small_kernel(const int32_t* __restrict__ topk_ids, int P, int k, int e0, int e1, int32_t* meta,
+                          int chunk_rows, int32_t* chunk_expert, int32_t* chunk_row0, int32_t* chunk_n,
+                          int max_chunks, int32_t* sorted_token, int32_t* pair_pos) {
+  __shared__ int cnt[256], off[256], cbase[256], cursor[256];
+  __shared__ int wsum[8], wcsum[8];
+  const int E = e1 - e0, tid = threadIdx.x;
+  if (tid < 256) cnt[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < P; i += blockDim.x) {
+    const int e = topk_ids[i];
+    if (e >= e0 && e < e1) atomicAdd(&cnt[e - e0], 1);
+  }
+  __syncthreads();
+  if (tid < 256) {
+    // exclusive scans of the counts and of the chunk counts over 256 entries: warp scan + 8 totals
+    const int c = tid < E ? cnt[tid] : 0;
+    const int nch = (c + chunk_rows - 1) / chunk_rows;
+    int a = c, b = nch;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ta = __shfl_up_sync(0xffffffffu, a, o), tb = __shfl_up_sync(0xffffffffu, b, o);
+      if ((tid & 31) >= o) { a += ta; b += tb; }
+    }
+    if ((tid & 31) == 31) { wsum[tid >> 5] = a; wcsum[tid >> 5] = b; }
+    off[tid] = a - c;
+    cbase[tid] = b - nch;
+  }
+  __syncthreads();
+  if (tid < 256) {
+    int pa = 0, pb = 0;
+    for (int w = 0; w < (tid >> 5); ++w) { pa += wsum[w]; pb += wcsum[w]; }
+    off[tid] += pa;
+    cbase[tid] += pb;
+  }
+  __syncthreads();
+  if (tid < E) {
+    const int c = cnt[tid], o = off[tid];
+    meta[tid] = c;
+    meta[E + tid] = o;
+    meta[2 * E + 1 + tid] = o + c;          // where the scatter's cursor ends
+    cursor[tid] = o;
+    int nc = cbase[tid];
+    for (int r = 0; r < c && nc < max_chunks; r += chunk_rows, ++nc) {
+      chunk_expert[nc] = tid;
+      chunk_row0[nc] = o + r;
+      chunk_n[nc] = min(chunk_rows, c - r);
+    }
+    if (tid == E - 1) {
+      meta[2 * E] = o + c;
+      meta[3 * E + 1] = min(max_chunks, cbase[tid] + (c + chunk_rows - 1) / chunk_rows);
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < P; i += blockDim.x) {
+    const int e = topk_ids[i];
+    if (e >= e0 && e < e1) {
+      const int pos = atomicAdd(&cursor[e - e0], 1);
+      sorted_token[pos] = i / k;
+      pair_pos[i] = pos;
+    } else {
+      pair_pos[i] = -1;
+    }
+  }
+}
 __global__ void moe_scatter_kernel(const int32_t* __restrict__ topk_ids, int P, int k, int e0,
                                    int e1, int32_t* meta, int E, int32_t* sorted_token,
                                    int32_t* pair_pos) {
@@ -453,6 +522,12 @@ int b200_moe_sort(const void* topk_ids, int T, int k, int e0, int e1, void* meta
                   void* chunk_n, int max_chunks, cudaStream_t stream) {
   const int P = T * k, E = e1 - e0;
   if (P <= 0) return 0;
+  if (E <= 256 && P <= 16384) {
+    moe_sort_small_kernel<<<1, 1024, 0, stream>>>((const int32_t*)topk_ids, P, k, e0, e1, (int32_t*)meta, 256,
+                                                  (int32_t*)chunk_expert, (int32_t*)chunk_row0, (int32_t*)chunk_n,
+                                                  max_chunks, (int32_t*)sorted_token, (int32_t*)pair_pos);
+    RETL;
+  }
   cudaMemsetAsync(meta, 0, (size_t)(3 * E + 2) * sizeof(int32_t), stream);
   moe_hist_kernel<<<(P + 255) / 256, 256, 0, stream>>>((const int32_t*)topk_ids, P, e0, e1,
                                                        (int32_t*)meta);

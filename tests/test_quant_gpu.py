@@ -114,3 +114,40 @@ def test_gemm_nvfp4_w4a4_block_scaled_mma(M, N, K, n_tile):
     # and the quantisation error of the activations stays what 4 bits allow
     full = x.float() @ Q.ref_dequant_nvfp4(wp, wsf, g_w).t() + bias.float()
     assert ((out.float() - full).norm() / full.norm()).item() < 0.2
+
+
+def test_nvfp4_fused_producers():
+    """RMSNorm -> NVFP4 (with the residual add) and x * sigmoid(gate) -> NVFP4 give the same bytes as
+    the separate norm / gate kernel followed by the plain quantiser."""
+    torch.manual_seed(5)
+    T, K = 70, 512
+    x = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    res = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    w = (torch.rand(K, device=DEV) + 0.5).to(torch.bfloat16)
+    gs = torch.full((1,), 300.0, device=DEV)
+    r1 = res.clone()
+    normed = ops.rmsnorm(x, w, 1e-6, residual=r1)
+    p_ref, s_ref = Q.quant_nvfp4(normed, gs)
+    r2 = res.clone()
+    n2 = torch.empty_like(normed)
+    p, s = Q.rmsnorm_quant_nvfp4(x, w, 1e-6, gs, residual=r2, normed=n2)
+    assert torch.equal(r1, r2)
+    # the fused kernel's reduction order differs from the norm kernel's: values may differ in the last bf16 bit
+    assert (n2.float() - normed.float()).abs().max() <= 2 ** -7 * normed.float().abs().max()
+    assert (p == p_ref).float().mean() > 0.97 and (s == s_ref).float().mean() > 0.97
+    deq = Q.ref_dequant_nvfp4(p, s, 1.0 / gs)
+    assert ((deq - n2.float()).norm() / n2.float().norm()).item() < 0.12
+    # swizzled scales carry the same bytes
+    p3, s3 = Q.rmsnorm_quant_nvfp4(x, w, 1e-6, gs, residual=res.clone(), swizzle=True)
+    assert torch.equal(p3, p)
+    t, gidx = 69, 7
+    off = ((t // 128) * (K // 64) + gidx // 4) * 512 + (t % 32) * 16 + ((t % 128) // 32) * 4 + gidx % 4
+    assert int(s3[off]) == int(s[t, gidx])
+    # gated
+    a = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    g = torch.randn(T, K, device=DEV).to(torch.bfloat16)
+    gated = ops.sigmoid_mul(a, g)
+    pg_ref, sg_ref = Q.quant_nvfp4(gated, gs)
+    pg, sg = Q.quant_nvfp4_gated(a, g, gs)
+    assert (pg == pg_ref).float().mean() > 0.97 and (sg == sg_ref).float().mean() > 0.97
+    assert ops.read_status() == 0

@@ -135,9 +135,18 @@ def cmd_quant_gemm_bench(a) -> int:
             w8 = w.to(torch.float8_e4m3fn)
             x8 = x.to(torch.float8_e4m3fn)
             one = torch.ones(1, device=dev)
+            sf_chunks = quant.nvfp4_sf_chunks(sf, 256)
+            g_a = (448.0 * 6.0 / x.float().abs().max()).reshape(1)
+            xq, xsf = quant.quant_nvfp4(x, g_a, swizzle=True)
             arms = {"bf16": lambda: ops.gemm(x, wb),
-                    "w4a16": lambda: quant.gemm_w4a16(x, packed, sf, g),
                     "fp8": lambda: quant.gemm_fp8(x8, w8, one, one)}
+            if M <= 128:
+                arms["w4a16"] = lambda: quant.gemm_w4a16(x, packed, sf, g)
+            if K % 256 == 0:
+                # the GEMM alone (activations already quantised), then with the quantiser in front
+                arms["w4a4"] = lambda: quant.gemm_nvfp4(xq, xsf, g_a, packed, sf_chunks, g)
+                arms["w4a4+quant"] = lambda: quant.gemm_nvfp4(
+                    *quant.quant_nvfp4(x, g_a, swizzle=True, out=(xq, xsf)), g_a, packed, sf_chunks, g)
             for arm, fn in arms.items():
                 for _ in range(3):
                     fn()
@@ -151,7 +160,7 @@ def cmd_quant_gemm_bench(a) -> int:
                     e1.record()
                     torch.cuda.synchronize()
                     best = min(best, e0.elapsed_time(e1))
-                wbytes = {"bf16": 2.0, "w4a16": 0.5 + 1 / 16, "fp8": 1.0}[arm] * N * K
+                wbytes = {"bf16": 2.0, "fp8": 1.0}.get(arm, 0.5 + 1 / 16) * N * K
                 rows.append({"proj": name, "M": M, "N": N, "K": K, "arm": arm, "ms": round(best, 4),
                              "tflops": round(2.0 * M * N * K / best / 1e9, 1),
                              "weight_gbs": round(wbytes / best / 1e6, 1)})

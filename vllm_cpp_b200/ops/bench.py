@@ -136,6 +136,35 @@ def small_case(name: str):
         sf = torch.full((28672, 256), 0x38, device=dev, dtype=torch.uint8)     # e4m3 1.0
         g = torch.full((1,), 0.01, device=dev)
         fn = lambda: Q.gemm_w4a16(a, packed, sf, g)
+    elif name == "gemm_nvfp4_small":
+        # W4A4 on kind::mxf4nvf4, decode-sized batch against the widest projection of a 27B model
+        from . import quant as Q
+        M, N, K = 64, 34816, 5120
+        aq = torch.randint(0, 256, (M, K // 2), device=dev, dtype=torch.uint8)
+        wq = torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8)
+        sfa = torch.full((128 * K // 16,), 0x38, device=dev, dtype=torch.uint8)        # e4m3 1.0
+        sfw = torch.full((N * K // 16,), 0x38, device=dev, dtype=torch.uint8)
+        one = torch.ones(1, device=dev)
+        fn = lambda: Q.gemm_nvfp4(aq, sfa, one, wq, sfw, one)
+    elif name == "gemm_nvfp4_prefill_small":
+        from . import quant as Q
+        M, N, K = 4096, 8192, 5120
+        aq = torch.randint(0, 256, (M, K // 2), device=dev, dtype=torch.uint8)
+        wq = torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8)
+        sfa = torch.full((M * K // 16,), 0x38, device=dev, dtype=torch.uint8)
+        sfw = torch.full((N * K // 16,), 0x38, device=dev, dtype=torch.uint8)
+        one = torch.ones(1, device=dev)
+        fn = lambda: Q.gemm_nvfp4(aq, sfa, one, wq, sfw, one)
+    elif name == "decode_d256_small":
+        # tensor-core decode attention at head_dim 256 (hybrid-attention layers of the 27B shape)
+        B, ctx_len, Hq2, Hkv2, D2, bs2 = 64, 4096, 24, 4, 256, 32
+        nb = ctx_len // bs2
+        cache = torch.randn(B * nb + 1, 2, bs2, Hkv2, D2, device=dev, dtype=torch.bfloat16)
+        bt = torch.arange(B * nb, device=dev, dtype=torch.int32).reshape(B, nb)
+        sl = torch.full((B,), ctx_len, dtype=torch.int32, device=dev)
+        q = torch.randn(B, Hq2 * D2, device=dev, dtype=torch.bfloat16)
+        fn = lambda: ops.attn_decode(q, cache, block_table=bt, seq_lens=sl, num_q_heads=Hq2,
+                                     num_kv_heads=Hkv2, head_dim=D2, block_size=bs2, scale=D2 ** -0.5)
     elif name == "mla_decode_small":
         from . import mla as MLA
         B, H, ctx, mbs = 128, 16, 1024, 64
@@ -160,7 +189,8 @@ def main():
                     help="run one small case only (for profiler captures): "
                          "gemm_small | gemm_decode_small | prefill_small | decode_small | gdn_scan_small | "
                          "gdn_decode_small | moe_small | gemm_streamk_small | gemm_gated_small | "
-                         "gemm_fp8_small | gemm_w4a16_small | mla_decode_small")
+                         "gemm_fp8_small | gemm_w4a16_small | gemm_nvfp4_small | gemm_nvfp4_prefill_small | "
+                         "decode_d256_small | mla_decode_small")
     args = ap.parse_args()
     if args.case:
         return small_case(args.case)

@@ -23,6 +23,8 @@ def _declare():
     _lib.declare("b200_nvfp4_sf_to_chunks", [P, L, I, I, P, P], I)
     _lib.declare("b200_quant_fp8", [P, L, P, F, I, P, P, L, L, I, P], I)
     _lib.declare("b200_quant_nvfp4", [P, L, P, P, P, L, I, I, I, P], I)
+    _lib.declare("b200_quant_nvfp4_gated", [P, L, P, L, P, P, P, L, I, I, P], I)
+    _lib.declare("b200_rmsnorm_quant_nvfp4", [P, L, P, P, F, I, P, P, P, P, L, I, I, P], I)
     lib()
     _declared = True
 
@@ -100,6 +102,42 @@ def quant_nvfp4(x, gscale, K=None, silu_mul=False, swizzle=False, out=None):
     check(lib().b200_quant_nvfp4(ptr(x), x.stride(0), ptr(gscale), ptr(packed), ptr(sf), T, K,
                                  int(silu_mul), int(swizzle), stream_ptr()), "quant_nvfp4")
     return packed, (sf if swizzle else sf.view(T, K // 16))
+
+
+def _nvfp4_out(T, K, swizzle, device, out):
+    n_sf = ((T + 127) // 128) * 128 * (K // 16) if swizzle else T * (K // 16)
+    if out is not None:
+        packed, sf = out
+        assert packed.shape == (T, K // 2) and sf.numel() >= n_sf
+        return packed, sf
+    return (torch.empty((T, K // 2), dtype=torch.uint8, device=device),
+            torch.zeros(n_sf, dtype=torch.uint8, device=device))
+
+
+def quant_nvfp4_gated(x, gate, gscale, swizzle=False, out=None):
+    """``x * sigmoid(gate)`` -> NVFP4 (the gated attention output in front of o_proj); reference
+    producer ``src/vt/cuda/cuda_matmul_nvfp4.cu:1826``."""
+    _declare()
+    T, K = x.shape
+    packed, sf = _nvfp4_out(T, K, swizzle, x.device, out)
+    check(lib().b200_quant_nvfp4_gated(ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(gscale), ptr(packed),
+                                       ptr(sf), T, K, int(swizzle), stream_ptr()), "quant_nvfp4_gated")
+    return packed, (sf if swizzle else sf[: T * (K // 16)].view(T, K // 16))
+
+
+def rmsnorm_quant_nvfp4(x, weight, eps, gscale, residual=None, gemma=False, swizzle=False, out=None,
+                        normed=None):
+    """(``residual += x``;) RMSNorm -> NVFP4 in one kernel; ``normed`` optionally receives the bf16
+    normalised rows too. Reference producer ``src/vt/cuda/cuda_matmul_nvfp4.cu:1667``."""
+    _declare()
+    T, K = x.shape
+    packed, sf = _nvfp4_out(T, K, swizzle, x.device, out)
+    if residual is not None:
+        assert residual.is_contiguous() and residual.shape == (T, K)
+    check(lib().b200_rmsnorm_quant_nvfp4(ptr(x), x.stride(0), ptr(residual), ptr(weight), float(eps), int(gemma),
+                                         ptr(gscale), ptr(packed), ptr(sf), ptr(normed), T, K, int(swizzle),
+                                         stream_ptr()), "rmsnorm_quant_nvfp4")
+    return packed, (sf if swizzle else sf[: T * (K // 16)].view(T, K // 16))
 
 
 def nvfp4_sf_chunks(sf: torch.Tensor, pad_rows: int = 256) -> torch.Tensor:
