@@ -332,13 +332,21 @@ __global__ void __launch_bounds__(256) tp_oneshot_allreduce_norm_kernel(OneShotP
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int r = 0; r < p.world; ++r) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p.peer_partial[r] + (size_t)row * p.H + i * 8);
-        float2 f;
-        f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
-        f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
-        f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
-        f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+      // all peers' loads are issued before the first sum: one NVLink round trip, not `world`
+      uint4 pv[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        if (r < p.world) pv[r] = *reinterpret_cast<const uint4*>(p.peer_partial[r] + (size_t)row * p.H + i * 8);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < p.world) {
+          const uint4 v = pv[r];
+          float2 f;
+          f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
+          f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
+          f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
+          f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+        }
       }
       if (rr) {
         const uint4 r = rr[i];

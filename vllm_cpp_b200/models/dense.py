@@ -143,6 +143,12 @@ class DenseModel:
             emb = torch.cat([emb, torch.zeros(pad, emb.shape[1], dtype=emb.dtype,
                                               device=emb.device)], 0)
         self.w["embed"] = put(emb[self.vocab_start:self.vocab_start + self.vocab_shard])
+        if (tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+                and emb.numel() * 2 <= (4 << 30)):
+            # fused tensor parallel: every rank keeps the whole embedding table (a few GB at most)
+            # and looks its tokens up locally instead of all-reducing [tokens, hidden] every step
+            # (1.0 ms of an 11.5 ms step at 8 GPUs). The lm_head stays sharded over the vocabulary.
+            self.w["embed_full"] = put(emb)
         if c.tie_word_embeddings or "lm_head.weight" not in staged:
             self.w["lm_head"] = self.w["embed"]
         else:
@@ -296,9 +302,7 @@ class DenseModel:
         attn = self.bufs.get("attn", T, self.hq * self.D)
         gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
         act = self.bufs.get("act", T, self.inter)
-        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
-                     vocab_total=c.vocab_size, scale=c.embed_scale)
-        self.comm.all_reduce(hidden)
+        self._tp_embed(ctx, T, hidden)
         tpf.first_norm(hidden, self.layers[0]["ln1"], eps, c.gemma_norm)
         pos = ctx.positions[:T]
         n_layers = len(self.layers)
@@ -337,6 +341,21 @@ class DenseModel:
             tpf.reduce_norm_gather(T, exp, nw, eps, c.gemma_norm)
         return self._tp_fused_logits(ctx, T)
 
+    def _tp_embed(self, ctx: StepContext, T: int, hidden: torch.Tensor) -> None:
+        """Token embeddings of the step on every rank: a local look-up in the replicated table, or the
+        vocabulary-parallel look-up + NCCL all-reduce when the table is sharded. (The collective is
+        not needed to order the passes of the fused chain: every pass ends in the all-gather of
+        ``_tp_logits_tail``, which no rank enters before its last reduce kernel has been issued.)"""
+        c = self.cfg
+        full = self.w.get("embed_full")
+        if full is not None:
+            self.be.embedding(ctx.input_ids[:T], full, out=hidden, vocab_start=0,
+                              vocab_total=full.shape[0], scale=c.embed_scale)
+            return
+        self.be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                          vocab_total=c.vocab_size, scale=c.embed_scale)
+        self.comm.all_reduce(hidden)
+
     def _forward_tp_oneshot(self, ctx: StepContext):
         """Decode-sized steps under tensor parallelism: every projection is a plain small-batch GEMM
         on this rank's shard; o_proj / down_proj write their partial rows into a peer-readable buffer
@@ -353,9 +372,7 @@ class DenseModel:
         attn = self.bufs.get("attn", T, self.hq * self.D)
         gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
         act = self.bufs.get("act", T, self.inter)
-        be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
-                     vocab_total=c.vocab_size, scale=c.embed_scale)
-        self.comm.all_reduce(hidden)
+        self._tp_embed(ctx, T, hidden)
         resid.copy_(hidden)
         x = be.rmsnorm(hidden, self.layers[0]["ln1"], eps, out=normed, gemma=c.gemma_norm)
         osr.begin_forward()
