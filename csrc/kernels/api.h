@@ -135,10 +135,13 @@ typedef struct B200TpReduce {
 // partial rows over peer pointers. peer_partial[r]: rank r's partial [M, H] of THIS op (the caller
 // alternates two buffers per rank); peer_flags[r]: rank r's array of `world` monotonic arrival
 // counters; seq / done_counter: local uint32 words, zero at start. norm_w null: plain sum.
+// mc_partial: the partial buffer of this op through an NVSwitch multicast mapping (then the sum is
+// one multimem.ld_reduce per 16 bytes, reduced in the switch), or null for peer loads.
 typedef struct B200TpOneShot {
   int world, rank, M, H;
   const void* peer_partial[8];
   void* peer_flags[8];
+  const void* mc_partial;
   void* seq;
   void* done_counter;
   void* residual;

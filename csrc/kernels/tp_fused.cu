@@ -281,6 +281,7 @@ __global__ void __launch_bounds__(128)
 struct OneShotParams {
   int world, rank, M, H;
   const __nv_bfloat16* peer_partial[8];   // this op's partial buffer on every rank
+  const __nv_bfloat16* mc_partial;        // the same buffer through an NVSwitch multicast mapping, or null
   uint32_t* peer_flags[8];                // arrival counters [world] on every rank
   uint32_t* seq;                          // local: completed one-shot ops
   uint32_t* done_counter;                 // local
@@ -332,6 +333,20 @@ __global__ void __launch_bounds__(256) tp_oneshot_allreduce_norm_kernel(OneShotP
       float acc[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      if (p.mc_partial) {
+        // NVLS: one load, reduced over all ranks' copies inside the switch (fp32 accumulation, bf16
+        // result; the same bits on every rank, as every rank asks the switch for the same sum)
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                     : "l"(p.mc_partial + (size_t)row * p.H + i * 8)
+                     : "memory");
+        float2 f;
+        f = unpack_bf16x2(v.x); acc[0] = f.x; acc[1] = f.y;
+        f = unpack_bf16x2(v.y); acc[2] = f.x; acc[3] = f.y;
+        f = unpack_bf16x2(v.z); acc[4] = f.x; acc[5] = f.y;
+        f = unpack_bf16x2(v.w); acc[6] = f.x; acc[7] = f.y;
+      } else {
       // all peers' loads are issued before the first sum: one NVLink round trip, not `world`
       uint4 pv[8];
 #pragma unroll
@@ -347,6 +362,7 @@ __global__ void __launch_bounds__(256) tp_oneshot_allreduce_norm_kernel(OneShotP
           f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
           f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
         }
+      }
       }
       if (rr) {
         const uint4 r = rr[i];
@@ -420,6 +436,7 @@ int b200_tp_oneshot_allreduce_norm(const B200TpOneShot* a, cudaStream_t stream) 
     p.peer_partial[i] = (const __nv_bfloat16*)a->peer_partial[i];
     p.peer_flags[i] = (uint32_t*)a->peer_flags[i];
   }
+  p.mc_partial = (const __nv_bfloat16*)a->mc_partial;
   p.seq = (uint32_t*)a->seq; p.done_counter = (uint32_t*)a->done_counter;
   p.residual = (__nv_bfloat16*)a->residual; p.norm_w = (const __nv_bfloat16*)a->norm_w;
   p.out = (__nv_bfloat16*)a->out; p.eps = a->eps; p.gemma = a->gemma;

@@ -162,7 +162,7 @@ def check_engine(comm, device, results, local_rank, shape="tiny-qwen3"):
             and R["agree_oneshot_vs_tp1"] > 0.7 and R["oneshot_ranks_identical"])
 
 
-def bench_block(comm, device, results):
+def bench_block(comm, device, results, nvls=False):
     """One transformer block's communication-bound half at Llama-8B width, fused vs NCCL."""
     from vllm_cpp_b200 import ops
     from vllm_cpp_b200.parallel.tp_fused import OneShotAllReduce, TpFusedContext
@@ -226,6 +226,33 @@ def bench_block(comm, device, results):
         st_nccl = ops.read_status()
         t1 = timeit(oneshot) / 2 if osr is not None else None
         st_one = ops.read_status()
+        nv = None
+        if osr is not None and nvls:
+            # the same kernel summing through the NVSwitch multicast mapping (multimem.ld_reduce)
+            x_p2p = xn.clone()
+            os.environ["B200_TP_NVLS"] = "1"
+            osr_nv = OneShotAllReduce(comm, device, H, T)
+            os.environ.pop("B200_TP_NVLS", None)
+            osr_p2p, osr = osr, osr_nv
+            resid.zero_()
+            oneshot()
+            torch.cuda.synchronize()
+            x_nv = xn.clone()
+            osr = osr_p2p
+            resid.zero_()
+            oneshot()
+            torch.cuda.synchronize()
+            x_p2p = xn.clone()
+            osr = osr_nv
+            t_nv = timeit(oneshot) / 2
+            nv = dict(multicast=bool(osr_nv.mc_base), nvls_ms=t_nv, nvls_speedup=tn / t_nv,
+                      rel_err_vs_peer_loads=_rel(x_nv, x_p2p), status=ops.read_status())
+            same = comm.all_gather_object(float(x_nv.float().sum()))
+            nv["ranks_identical"] = all(v == same[0] for v in same)
+            osr = osr_p2p
+            torch.cuda.synchronize()
+            comm.barrier()
+            osr_nv.close()
         flops = 2.0 * T * (I // W) * H + 2.0 * T * H * (2 * I // W)
         nv_bytes = 2.0 * T * H * 2 * (W - 1) / W          # scatter out + gather in, per rank
         roof_ms = max(flops / 1393e12, nv_bytes / 770e9) * 1e3
@@ -235,6 +262,8 @@ def bench_block(comm, device, results):
         if t1 is not None:
             rows[-1].update(oneshot_ms=t1, oneshot_speedup=tn / t1, status_after_oneshot=st_one,
                             oneshot_nvlink_mb_per_rank=2.0 * T * H * (W - 1) / 1e6)
+        if nv is not None:
+            rows[-1]["nvls"] = nv
         torch.cuda.synchronize()
         comm.barrier()
         tpf.close()
@@ -250,6 +279,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--skip-engine", action="store_true")
+    ap.add_argument("--nvls", action="store_true",
+                    help="also run the one-shot kernel through an NVSwitch multicast mapping")
     ap.add_argument("--shapes", default="tiny-qwen3,tiny-moe",
                     help="comma-separated model shapes for the engine check")
     args = ap.parse_args()
@@ -265,7 +296,7 @@ def main():
         for shape in [x for x in args.shapes.split(",") if x]:
             ok = check_engine(comm, device, results, local_rank, shape) and ok
     if args.bench:
-        bench_block(comm, device, results)
+        bench_block(comm, device, results, nvls=args.nvls)
     flag = torch.tensor([1 if ok else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     results["ok"] = bool(flag.item())

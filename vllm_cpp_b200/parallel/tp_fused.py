@@ -16,6 +16,7 @@ The flow per transformer block (rows = tokens, split into contiguous shards per 
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -53,7 +54,7 @@ class B200TpReduce(ctypes.Structure):
 class B200TpOneShot(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("M", ctypes.c_int), ("H", ctypes.c_int),
                 ("peer_partial", ctypes.c_void_p * 8), ("peer_flags", ctypes.c_void_p * 8),
-                ("seq", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
+                ("mc_partial", ctypes.c_void_p), ("seq", ctypes.c_void_p), ("done_counter", ctypes.c_void_p),
                 ("residual", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("out", ctypes.c_void_p),
                 ("eps", ctypes.c_float), ("gemma", ctypes.c_int)]
 
@@ -136,12 +137,42 @@ class OneShotAllReduce:
         self.comm, self.device, self.H = comm, device, hidden
         self.world, self.rank = comm.world, comm.rank
         self.max_tokens = max_tokens
-        self.partial = SymmetricBuffer(comm, 2 * max_tokens * hidden * 2, device)
+        self.mc_base = 0
+        self.partial = None
+        if os.environ.get("B200_TP_NVLS", "0") == "1" and self.world > 1:
+            self._init_nvls(device, 2 * max_tokens * hidden)
+        if self.partial is None:
+            self.partial = SymmetricBuffer(comm, 2 * max_tokens * hidden * 2, device)
+            self.partial_ptrs = self.partial.ptrs
+            self._views = self.partial.tensor.view(torch.bfloat16).view(2, max_tokens, hidden)
         # [world arrival counters | pad | seq | done]
         self.flags = SymmetricBuffer(comm, 256, device)
-        self._views = self.partial.tensor.view(torch.bfloat16).view(2, max_tokens, hidden)
         self.op = 0                       # ops issued in the current forward pass
         comm.barrier()
+
+    def _init_nvls(self, device, numel: int) -> None:
+        """NVLS variant (B200_TP_NVLS=1, chosen here, at set-up): the partial buffers live in
+        symmetric memory that is also bound to an NVSwitch multicast object, and the kernel sums all
+        ranks' rows with one ``multimem.ld_reduce`` per 16 bytes. The allocation, the handle
+        exchange and the multicast binding are torch's (``torch.distributed._symmetric_memory``).
+        Falls back to peer loads when the system offers no multicast. A rank must not exit while
+        the buffer is bound (peers' GPUs would see NVLink faults): ``close()`` is collective."""
+        try:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            t = symm_mem.empty(numel, dtype=torch.bfloat16, device=device)
+            hdl = symm_mem.rendezvous(t, dist.group.WORLD)
+            mc = int(hdl.multicast_ptr or 0)      # 0 when the system offers no multicast
+        except Exception as e:          # no multicast on this system / this torch build
+            print(f"[tp_fused] NVLS unavailable, using peer loads: {e}", flush=True)
+            return
+        if not mc:
+            return
+        self._symm_tensor, self._symm_handle = t, hdl
+        self.mc_base = mc
+        self.partial = t                 # keeps the allocation alive; no IPC buffer to close
+        self.partial_ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self._views = t.view(2, self.max_tokens, self.H)
 
     def begin_forward(self) -> None:
         self.op = 0
@@ -157,8 +188,9 @@ class OneShotAllReduce:
         a.world, a.rank, a.M, a.H = self.world, self.rank, T, self.H
         off = (self.op & 1) * self.max_tokens * self.H * 2
         for r in range(self.world):
-            a.peer_partial[r] = self.partial.ptrs[r] + off
+            a.peer_partial[r] = self.partial_ptrs[r] + off
             a.peer_flags[r] = self.flags.ptrs[r]
+        a.mc_partial = self.mc_base + off if self.mc_base else None
         a.seq = self.flags.local + 128
         a.done_counter = self.flags.local + 192
         a.residual = ptr(residual)
@@ -170,7 +202,12 @@ class OneShotAllReduce:
         return out
 
     def close(self):
-        self.partial.close()
+        if self.mc_base:
+            torch.cuda.synchronize()
+            self.comm.barrier()          # nobody unbinds while a peer may still read through the switch
+            self._symm_handle = self._symm_tensor = self.partial = None
+        else:
+            self.partial.close()
         self.flags.close()
 
 
