@@ -292,7 +292,8 @@ void b200cpu_paged_attention(const uint16_t* q, int64_t ldq, const uint16_t* kv_
         continue;
       }
       const int qpos = sl - ql + (t - q_start[r]);
-      const int k_lo = window > 0 ? std::max(0, qpos - window + 1) : 0, k_hi = std::min(sl - 1, qpos);
+      const int k_lo = window > 0 ? std::max(0, qpos - window + 1) : (window < 0 ? (qpos / -window) * -window : 0),
+                k_hi = std::min(sl - 1, qpos);
       const int hk = h / G;
       const uint16_t* qv = q + (int64_t)t * ldq + (size_t)h * D;
       const int32_t* bt = block_table + (int64_t)r * max_blocks;

@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(128)
   const int seq_len = p.seq_lens[b];
   int begin = 0;
   if (p.window > 0) begin = max(0, seq_len - p.window);
+  else if (p.window < 0) begin = ((seq_len - 1) / -p.window) * -p.window;   // chunked-local: the query's own chunk
   const int span = seq_len - begin;
   int chunk = (span + p.splits - 1) / p.splits;
   chunk = ((chunk + 15) / 16) * 16;

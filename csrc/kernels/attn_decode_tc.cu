@@ -150,6 +150,7 @@ __global__ void __launch_bounds__(192, D == 128 ? 2 : 1)
   const int seq_len = p.seq_lens[b];
   int begin = 0;
   if (p.window > 0) begin = max(0, seq_len - p.window);
+  else if (p.window < 0 && seq_len > 0) begin = ((seq_len - 1) / -p.window) * -p.window;   // chunked-local
   const int start = (begin / kTok) * kTok;           // tile-aligned start of the kv range
   const int span = max(0, seq_len - start);
   const int tiles_total = (span + kTok - 1) / kTok;

@@ -47,7 +47,8 @@ struct PrefillParams {
   int Hq, Hkv, block_size;
   float scale_log2;            // softmax scale * log2(e)
   float softcap2;              // soft-cap in the log2 domain, 0 = off
-  int window;                  // sliding window (tokens to the left incl. self), 0 = off
+  int window;                  // > 0: sliding window (tokens to the left incl. self); < 0: chunked-local
+                               // attention with chunks of -window tokens (a query sees its own chunk); 0 = off
   int causal;
   int* status;
 };
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
   const int last_pos = p.causal ? (ctx_off + q0 + rows - 1) : (seq_len - 1);
   int first_pos = 0;
   if (p.window > 0) first_pos = max(0, ctx_off + q0 - p.window + 1);
+  else if (p.window < 0) first_pos = ((ctx_off + q0) / -p.window) * -p.window;   // chunk start of the first row
   const int kt0 = first_pos / kKT;
   const int kt1 = last_pos / kKT + 1;           // exclusive
   const int ntiles = kt1 - kt0;
@@ -223,7 +225,7 @@ __global__ void __launch_bounds__(64 + 128 * (D > 128 ? 2 : 1), D > 128 ? 1 : 2)
     const int r = quarter * 32 + lane;              // row inside the tile
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int q_pos = ctx_off + q0 + r;             // absolute position of this query row
-    const int lo = (p.window > 0) ? (q_pos - p.window + 1) : 0;
+    const int lo = (p.window > 0) ? (q_pos - p.window + 1) : (p.window < 0 ? (q_pos / -p.window) * -p.window : 0);
     const int hi = min(p.causal ? q_pos : (seq_len - 1), seq_len - 1);
     const float sc = p.scale_log2;
     const bool cap = p.softcap2 > 0.f;

@@ -32,6 +32,9 @@ FAMILIES = {
                     embedding_multiplier=12.0, logits_scaling=8.0),
     "olmo2": dict(architectures=["Olmo2ForCausalLM"]),
     "glm4": dict(architectures=["Glm4ForCausalLM"], partial_rotary_factor=0.5, attention_bias=True),
+    # chunked-local attention (Llama-4 style layer pattern): a query attends inside its own 32-token chunk
+    "chunked": dict(architectures=["LlamaForCausalLM"], attention_chunk_size=32,
+                    layer_types=["chunked_attention", "chunked_attention", "full_attention"]),
 }
 
 
@@ -57,6 +60,25 @@ def test_family_config_runs_on_the_oracle(name):
     b = [o.outputs[0].token_ids for o in build(cfg, "cpu").generate(prompts_of(cfg), sp)]
     assert a == b and all(len(x) == 6 for x in a)
     assert all(0 <= t < cfg.vocab_size for x in a for t in x)
+
+
+def test_chunked_local_attention_changes_the_result_and_groups_the_layers():
+    """The chunk mask is live (long prompts decode differently from the same weights with full
+    attention) and chunked layers get their own KV-cache group."""
+    cfg = config_of("chunked")
+    assert cfg.attention_chunk_size == 32
+    plain = model_config_from_hf({**BASE, "architectures": ["LlamaForCausalLM"]})
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    a, b = build(cfg, "cpu"), build(plain, "cpu")
+    assert [len(g[0]) for g in a.model.kv_cache_groups(16)] == [1, 2]
+    assert a.model._layer_window(0) == -32 and a.model._layer_window(2) == 0
+    pa = [o.outputs[0].token_ids for o in a.generate(prompts_of(cfg), sp)]
+    pb = [o.outputs[0].token_ids for o in b.generate(prompts_of(cfg), sp)]
+    assert pa != pb
+    # a prompt that fits in one chunk sees the same keys either way
+    short = [[5, 6, 7, 8, 9]]
+    assert [o.outputs[0].token_ids[0] for o in a.generate(short, sp)] == \
+           [o.outputs[0].token_ids[0] for o in b.generate(short, sp)]
 
 
 def test_family_switches_are_read_from_the_config():

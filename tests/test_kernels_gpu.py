@@ -262,6 +262,39 @@ def test_attn_prefill_window_softcap():
     assert ops.read_status() == 0
 
 
+@pytest.mark.parametrize("chunk", [64, 200])
+def test_attn_chunked_local(chunk):
+    """Chunked-local attention (window < 0): a query sees the keys of its own chunk only, in the
+    prefill kernel, the tcgen05 decode kernel and the CUDA-core decode kernel."""
+    torch.manual_seed(12)
+    D, Hq, Hkv, bs = 128, 8, 2, 16
+    q_lens, ctx = [300, 64, 5], [100, 500, 0]
+    seq_lens = [a + b for a, b in zip(q_lens, ctx)]
+    cache, bt = _make_paged(seq_lens, Hkv, D, bs)
+    T = sum(q_lens)
+    q = _rand(T, Hq * D)
+    qs = torch.tensor([0, 300, 364, 369], dtype=torch.int32, device=DEV)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    treq, tq0 = ref.build_prefill_tiles(q_lens)
+    out = ops.attn_prefill(q, cache, block_table=bt, seq_lens=sl, q_start=qs,
+                           tile_req=torch.tensor(treq, dtype=torch.int32, device=DEV),
+                           tile_q0=torch.tensor(tq0, dtype=torch.int32, device=DEV), num_q_heads=Hq,
+                           num_kv_heads=Hkv, head_dim=D, block_size=bs, scale=D ** -0.5, window=-chunk)
+    exp = ref.paged_attention(q, cache, bt, sl, qs, Hq, Hkv, D, bs, D ** -0.5, window=-chunk)
+    assert _rel_err(out, exp) < 1.5e-2
+    # decode: one query per sequence at its last position
+    B = len(seq_lens)
+    qd = _rand(B, Hq * D)
+    qsd = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    expd = ref.paged_attention(qd, cache, bt, sl, qsd, Hq, Hkv, D, bs, D ** -0.5, window=-chunk)
+    for cuda_core in (False, True):
+        got = ops.attn_decode(qd, cache, block_table=bt, seq_lens=sl, num_q_heads=Hq, num_kv_heads=Hkv,
+                              head_dim=D, block_size=bs, scale=D ** -0.5, window=-chunk, splits=2,
+                              force_cuda_core=cuda_core)
+        assert _rel_err(got, expd) < 1e-2
+    assert ops.read_status() == 0
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,bs,splits", [(128, 32, 8, 16, 0), (128, 4, 1, 16, 1),
                                                 (128, 32, 4, 32, 5), (64, 8, 8, 16, 3),
                                                 (256, 24, 4, 16, 2), (128, 16, 8, 16, 4)])

@@ -53,8 +53,9 @@ class ModelConfig:
     mlp_bias: bool = False
     hidden_act: str = "silu"
     sliding_window: int = 0
+    attention_chunk_size: int = 0             # chunked-local attention ("chunked_attention" layers)
     # layer pattern / extras for the non-plain families
-    layer_types: Optional[list] = None        # per-layer "full_attention" | "sliding_attention" | "linear_attention"
+    layer_types: Optional[list] = None        # per-layer "full_attention" | "sliding_attention" | "chunked_attention" | "linear_attention"
     attn_logit_softcap: float = 0.0
     final_logit_softcap: float = 0.0
     embed_scale: float = 1.0
@@ -164,6 +165,7 @@ def model_config_from_hf(cfg: dict) -> ModelConfig:
         rope=_rope_from_hf(t, head_dim), attention_bias=bool(t.get("attention_bias", False)),
         mlp_bias=bool(t.get("mlp_bias", False)), hidden_act=t.get("hidden_act", "silu"),
         sliding_window=int(t.get("sliding_window") or 0), layer_types=t.get("layer_types"),
+        attention_chunk_size=int(t.get("attention_chunk_size") or 0),
         raw=cfg)
     eos = t.get("eos_token_id")
     m.eos_token_id = eos[0] if isinstance(eos, list) else eos

@@ -211,15 +211,27 @@ class DenseModel:
                     L[k] = QuantWeight.from_dense(w)
         self.quantized = method
 
+    def _layer_window(self, l: int) -> int:
+        """Attention span of layer ``l`` as the kernels take it: > 0 a sliding window, < 0
+        chunked-local attention with chunks of that many tokens (a query sees its own chunk,
+        reference ``ChunkedLocalAttentionSpec``), 0 the whole context."""
+        c = self.cfg
+        lt = c.layer_types[l] if c.layer_types else None
+        if c.attention_chunk_size and lt == "chunked_attention":
+            return -c.attention_chunk_size
+        if c.sliding_window and (lt is None or lt == "sliding_attention"):
+            return c.sliding_window
+        return 0
+
     # ------------------------------------------------------------------ KV cache
     def kv_cache_groups(self, block_size: int):
-        """[(layer indices, spec dict)] -- one group for full attention; sliding-window
-        layers form a second group when the model mixes both."""
+        """[(layer indices, spec dict)] -- one group for full attention; sliding-window and
+        chunked-local layers form further groups when the model mixes them."""
         c = self.cfg
-        full, sliding = [], []
+        full, sliding, chunked = [], [], []
         for l in range(c.num_layers):
-            lt = c.layer_types[l] if c.layer_types else "full_attention"
-            (sliding if lt == "sliding_attention" and c.sliding_window else full).append(l)
+            w = self._layer_window(l)
+            (chunked if w < 0 else sliding if (w > 0 and c.layer_types) else full).append(l)
         groups = []
         spec = dict(kind="full", block_size=block_size, num_kv_heads=self.hkv, head_size=self.D,
                     dtype_bytes=2)
@@ -229,6 +241,10 @@ class DenseModel:
             s = dict(spec)
             s.update(kind="sliding", sliding_window=c.sliding_window)
             groups.append((sliding, s))
+        if chunked:
+            s = dict(spec)
+            s.update(kind="chunked", attention_chunk_size=c.attention_chunk_size)
+            groups.append((chunked, s))
         return groups
 
     def alloc_kv_cache(self, num_blocks: int, block_size: int):
@@ -317,8 +333,7 @@ class DenseModel:
                 layers = []                    # every block already ran
         for l, L in enumerate(layers):
             grp = self.layer_group[l]
-            window = c.sliding_window if (c.sliding_window and (
-                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            window = self._layer_window(l)
             tpf.gemm_gather(T, L["qkv"], qkv)
             be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
                        head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
@@ -380,8 +395,7 @@ class DenseModel:
         n_layers = len(self.layers)
         for l, L in enumerate(self.layers):
             grp = self.layer_group[l]
-            window = c.sliding_window if (c.sliding_window and (
-                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            window = self._layer_window(l)
             be.gemm(x, L["qkv"], out=qkv)
             be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
                        head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
@@ -462,7 +476,7 @@ class DenseModel:
         if os.environ.get("B200_NATIVE_LAYERS", "1") == "0":      # debugging: keep the per-op path
             return False
         if (c.post_norm or c.sandwich_norm or c.attention_bias or c.mlp_bias or c.sliding_window
-                or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):
+                or c.attention_chunk_size or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):
             return False
         from .backend import QuantWeight
         return not any(isinstance(v, QuantWeight) for L in self.layers for v in L.values())
@@ -542,7 +556,8 @@ class DenseModel:
         if os.environ.get("B200_NATIVE_LAYERS", "1") == "0" or type(self)._forward_tp_fused is not \
                 DenseModel._forward_tp_fused:
             return False
-        return not (c.mlp_bias or c.sliding_window or len(set(self.layer_group)) != 1)
+        return not (c.mlp_bias or c.sliding_window or c.attention_chunk_size
+                    or len(set(self.layer_group)) != 1)
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Returns fp32 logits ``[num_logits, vocab]`` for the rows in ``ctx.logits_indices``."""
@@ -579,8 +594,7 @@ class DenseModel:
             if nvtx.ENABLED:          # one flat marker per layer (ranges would need a pop at every exit)
                 torch.cuda.nvtx.mark(f"layer {l}")
             grp = self.layer_group[l]
-            window = c.sliding_window if (c.sliding_window and (
-                not c.layer_types or c.layer_types[l] == "sliding_attention")) else 0
+            window = self._layer_window(l)
             # ---- attention block
             if c.post_norm:
                 if first:

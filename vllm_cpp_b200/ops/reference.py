@@ -145,6 +145,8 @@ def paged_attention(q, kv_cache, block_table, seq_lens, q_start, num_q_heads, nu
             mask &= kpos[None, :] <= qpos[:, None]
         if window > 0:
             mask &= kpos[None, :] > qpos[:, None] - window
+        elif window < 0:        # chunked-local attention: a query sees the keys of its own chunk
+            mask &= kpos[None, :] >= (qpos[:, None] // -window) * -window
         s = s.masked_fill(~mask[None], -math.inf)
         l = torch.logsumexp(s, dim=-1)
         p = torch.exp(s - l[..., None])
