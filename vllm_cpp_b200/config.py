@@ -391,6 +391,9 @@ class EngineArgs:
     # device "cpu": "torch" = the fp32 PyTorch oracle the GPU path is compared with,
     # "native" = the C++ thread-pool backend (csrc/cpu)
     cpu_backend: str = "torch"
+    # CPU only: keep the linear-layer weights in GGUF blocks ("q8_0" | "q4_0") and run the GEMMs on
+    # the packed form (integer block dot products); None keeps bf16 weights
+    cpu_weight_quant: Optional[str] = None
     enable_cuda_graphs: bool = True
     seed: int = 0
     device: str = "cuda"

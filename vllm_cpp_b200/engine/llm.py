@@ -85,6 +85,9 @@ class LLM:
         if getattr(cfg, "quant", None) == "nvfp4" and getattr(args, "quantize", True) \
                 and hasattr(self.model, "quantize_weights"):
             self.model.quantize_weights("nvfp4")
+        if args.cpu_weight_quant and torch.device(device).type == "cpu" \
+                and hasattr(self.model, "quantize_weights"):
+            self.model.quantize_weights(args.cpu_weight_quant)
         budget = args.resolve_max_num_batched_tokens(cfg)
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
         if par.tensor_parallel_size > 1:

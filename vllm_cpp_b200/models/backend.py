@@ -60,6 +60,39 @@ class QuantWeight:
         return QuantWeight(packed, sf, g)
 
 
+class BlockQuantWeight:
+    """A linear-layer weight kept in GGUF blocks of 32 values (Q8_0: fp16 scale + int8; Q4_0: fp16
+    scale + nibbles) for the CPU backend's packed GEMM. Re-encoding a tensor that was decoded from
+    the same format is lossless (the block maximum maps back to the same scale)."""
+
+    def __init__(self, packed: torch.Tensor, kind: int, shape):
+        self.packed, self.kind, self.shape = packed, kind, tuple(shape)
+        self.device = packed.device
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, fmt: str) -> "BlockQuantWeight":
+        from ..ops import cpu_native as N
+        kind = {"q8_0": N.Q8_0, "q4_0": N.Q4_0}[fmt]
+        return BlockQuantWeight(N.quantize_blocks(w.float().cpu(), kind), kind, w.shape)
+
+    def numel(self):
+        return self.packed.numel()
+
+    def element_size(self):
+        return 1
+
+    def data_ptr(self):
+        return self.packed.data_ptr()
+
+    def dequant(self) -> torch.Tensor:
+        import numpy as np
+        from ..loader.gguf import dequantize
+        from ..ops import cpu_native as N
+        t = {N.Q8_0: 8, N.Q4_0: 2}[self.kind]
+        return torch.from_numpy(dequantize(self.packed.numpy().reshape(-1), t, self.shape)
+                                .astype(np.float32)).to(torch.bfloat16)
+
+
 _SHARED_SCRATCH: dict = {}
 
 
@@ -70,7 +103,7 @@ class CpuBackend:
         self.device = torch.device(device)
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
-        if isinstance(w, QuantWeight):
+        if isinstance(w, (QuantWeight, BlockQuantWeight)):
             w = w.dequant()
         y = ref.gemm(a, w, bias, residual, out_dtype)
         if out is not None:
@@ -157,7 +190,20 @@ class CpuNativeBackend(CpuBackend):
         cpu_native.lib()
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
-        if isinstance(w, QuantWeight) or a.dtype != torch.bfloat16 or a.stride(-1) != 1:
+        if isinstance(w, BlockQuantWeight) and a.dtype == torch.bfloat16 and a.stride(-1) == 1 \
+                and w.shape[1] % 32 == 0:
+            # weights stay packed: int8 block dot products against per-block quantised activations
+            y = self.n.gemm_quant(a, w.packed, w.kind, out_dtype=torch.float32)
+            if bias is not None:
+                y = y + bias.float()
+            if residual is not None:
+                y = y + residual.float()
+            y = y.to(out.dtype if out is not None else out_dtype)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
+        if isinstance(w, (QuantWeight, BlockQuantWeight)) or a.dtype != torch.bfloat16 or a.stride(-1) != 1:
             return super().gemm(a, w, bias, residual, out, out_dtype)
         return self.n.gemm(a, w, bias, residual, out, out.dtype if out is not None else out_dtype)
 

@@ -200,6 +200,16 @@ class DenseModel:
         """Replaces the linear-layer weights by NVFP4 ``QuantWeight``s (values are rounded
         once here, on whatever device holds them, so CPU oracle and GPU see the same
         numbers)."""
+        if method in ("q8_0", "q4_0"):
+            # CPU backend: GGUF block formats, GEMMs on the packed weights
+            from .backend import BlockQuantWeight
+            for L in self.layers:
+                for k in self.QUANT_KEYS:
+                    w = L.get(k)
+                    if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 32 == 0:
+                        L[k] = BlockQuantWeight.from_dense(w, method)
+            self.quantized = method
+            return
         if method != "nvfp4":
             raise ValueError(f"unsupported weight quantisation {method!r}")
         from .backend import QuantWeight
