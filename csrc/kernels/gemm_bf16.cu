@@ -1201,15 +1201,14 @@ template <int BN>
 static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
                      GemmParams& p, cudaStream_t stream) {
   const int stage_bytes = (p.a_stage_rows > 0 ? p.a_stage_rows * 128 : kBM * kBK * 2) + BN * kBK * 2;
-  const int a_pad = p.a_stage_rows > 0 ? kBM * kBK * 2 : 0;   // room for the last stage's 128-row read
-  int stages = (kSmemBudget - 2048 - a_pad) / stage_bytes;
+  int stages = (kSmemBudget - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   int kblocks = (p.K + kBK - 1) / kBK;
   if (stages > kblocks + 1) stages = kblocks + 1;
   if (stages < 2) stages = 2;
   p.stages = stages;
   // (the last stage's MMA reads a full 128-row A tile from its base: keep that much room)
-  size_t smem = (size_t)stages * stage_bytes + a_pad + 1024 + sizeof(GemmBarriers);
+  size_t smem = (size_t)stages * stage_bytes + (p.a_stage_rows > 0 ? kBM * kBK * 2 : 0) + 1024 + sizeof(GemmBarriers);
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_bf16_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
