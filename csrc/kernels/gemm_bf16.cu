@@ -78,7 +78,6 @@ struct GemmParams {
   const float* scale_a;
   const float* scale_w;
   int scale_w_per_channel;
-  int a_stage_rows;               // 1-CTA tiled kernel: rows of A kept per stage (0 = all 128)
   int sk;                         // number of leading tiles in the stream-K region (0 = none)
   float* sk_partials;
   uint32_t* sk_flags;
@@ -190,13 +189,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  // Small batches (one M tile, few rows) keep only the rows that exist in the A part of a stage, so
-  // more stages (more weight bytes in flight) fit: the MMA still reads 128 rows, the ones past the
-  // stage's A part come out of its B part (finite weight values) and land in output rows that are
-  // never stored.
-  const int kABytes = p.a_stage_rows > 0 ? p.a_stage_rows * 128 : kBM * kBK * 2;
+  constexpr int kABytes = kBM * kBK * 2;
   constexpr int kBBytes = BN * kBK * 2;
-  const int kStageBytes = kABytes + kBBytes;
+  constexpr int kStageBytes = kABytes + kBBytes;
   const int stages = p.stages;
   GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + (size_t)stages * kStageBytes);
 
@@ -1200,15 +1195,14 @@ static void plan_streamk(long tiles, int kblocks, int max_workers, int* nworkers
 template <int BN>
 static int launch_tn(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
                      GemmParams& p, cudaStream_t stream) {
-  const int stage_bytes = (p.a_stage_rows > 0 ? p.a_stage_rows * 128 : kBM * kBK * 2) + BN * kBK * 2;
+  constexpr int stage_bytes = kBM * kBK * 2 + BN * kBK * 2;
   int stages = (kSmemBudget - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   int kblocks = (p.K + kBK - 1) / kBK;
   if (stages > kblocks + 1) stages = kblocks + 1;
   if (stages < 2) stages = 2;
   p.stages = stages;
-  // (the last stage's MMA reads a full 128-row A tile from its base: keep that much room)
-  size_t smem = (size_t)stages * stage_bytes + (p.a_stage_rows > 0 ? kBM * kBK * 2 : 0) + 1024 + sizeof(GemmBarriers);
+  size_t smem = (size_t)stages * stage_bytes + 1024 + sizeof(GemmBarriers);
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_bf16_tn_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1573,13 +1567,7 @@ static int gemm_bf16_impl(const void* A, int lda, const void* W, int ldw, void* 
     return launch_pair<128>(tA, tA2, tB, p, stream);
   }
   CUtensorMap tmA, tmA2, tmB;
-  // one M tile with few rows: keep only those rows (rounded to the 8-row swizzle atom) per stage
-  int a_box_rows = kBM;
-  if (p.tiles_m == 1 && M <= 64 && !tp) {
-    a_box_rows = (M + 7) & ~7;
-    p.a_stage_rows = a_box_rows;
-  }
-  if (!get_tmap_bf16(&tmA, A, M, K, lda, a_box_rows, kBK)) return -3;
+  if (!get_tmap_bf16(&tmA, A, M, K, lda, kBM, kBK)) return -3;
   tmA2 = tmA;
   if (tp && tp->gather && tp->a_alt && !get_tmap_bf16(&tmA2, tp->a_alt, M, K, lda, kBM, kBK)) return -3;
   if (use256) {
