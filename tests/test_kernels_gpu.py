@@ -57,7 +57,7 @@ def test_gemm_stream_k(M, N, K, path):
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 6144, 4096), (16, 128, 64), (33, 4096, 14336),
                                    (64, 28672, 4096), (200, 1024, 1024), (256, 4096, 4096),
-                                   (5, 128256, 1024)])
+                                   (5, 128256, 1024), (1, 28672, 4096), (17, 32768, 512), (64, 16384, 192)])
 def test_gemm_small_m_swap_splitk(M, N, K):
     torch.manual_seed(1)
     a, w = _rand(M, K), _rand(N, K, scale=0.05)
