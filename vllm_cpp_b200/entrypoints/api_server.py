@@ -163,9 +163,13 @@ class Metrics:
 class ServerState:
     def __init__(self, llm, served_model_name: str, tool_parser: Optional[str] = None,
                  reasoning_parser: Optional[str] = None, chat_template: Optional[str] = None,
-                 default_max_tokens: int = 256, api_key: Optional[str] = None):
+                 default_max_tokens: int = 256, api_key: Optional[str] = None, replicas: Optional[list] = None):
         self.llm = llm
-        self.engine = AsyncLLM(llm)
+        if replicas:
+            from .async_llm import DataParallelEngine
+            self.engine = DataParallelEngine([llm] + list(replicas))
+        else:
+            self.engine = AsyncLLM(llm)
         self.tokenizer = llm.tokenizer
         self.model_name = served_model_name
         self.default_max_tokens = default_max_tokens
@@ -549,6 +553,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
     ap.add_argument("--device", default="cuda")
     ap.add_argument("--tensor-parallel-size", type=int, default=1,
                     help="ranks (one process per GPU); this process is rank 0 and starts the others")
+    ap.add_argument("--data-parallel-size", type=int, default=1,
+                    help="engine replicas (one per GPU) behind this server; a request goes to the least loaded one")
     ap.add_argument("--enable-expert-parallel", action="store_true",
                     help="MoE models: experts are split over the ranks instead of sharded")
     return ap
@@ -566,9 +572,19 @@ def main(argv=None) -> int:
     kw["parallel"] = ParallelConfig(tensor_parallel_size=max(1, a.tensor_parallel_size),
                                     enable_expert_parallel=a.enable_expert_parallel)
     llm, _workers = launch_engine(EngineArgs(**{k: v for k, v in kw.items() if v is not None}))
+    replicas = []
+    if a.data_parallel_size > 1:
+        if a.tensor_parallel_size > 1:
+            raise SystemExit("--data-parallel-size with --tensor-parallel-size > 1 is not supported")
+        from ..engine import LLM
+        for r in range(1, a.data_parallel_size):
+            kr = dict(kw)
+            if (a.device or "cuda").startswith("cuda"):
+                kr["device"] = f"cuda:{r}"
+            replicas.append(LLM(EngineArgs(**{k: v for k, v in kr.items() if v is not None})))
     tpl = open(a.chat_template).read() if a.chat_template else None
     state = ServerState(llm, a.served_model_name or a.model, a.tool_call_parser, a.reasoning_parser, tpl,
-                        a.default_max_tokens, a.api_key)
+                        a.default_max_tokens, a.api_key, replicas=replicas)
     srv = make_server(state, a.host, a.port)
     print(f"serving {state.model_name} on http://{a.host}:{a.port} (tool parser: {state.tool_parser}, "
           f"reasoning parser: {state.reasoning_parser})", flush=True)

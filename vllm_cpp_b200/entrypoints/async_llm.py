@@ -138,3 +138,76 @@ class AsyncLLM:
                 for q in self._queues.values():
                     q.put(StreamItem(finished=True, error=self.errored, finish_reason="error"))
                 self._queues.clear()
+
+
+class DataParallelEngine:
+    """N engine replicas (one ``AsyncLLM`` each, typically one per GPU) behind the interface of one:
+    a request goes to the replica with the fewest requests in flight and stays there. The front end
+    of data-parallel serving for models that fit on one GPU (reference: the data-parallel section
+    of ``.agents/specs/tensor-parallelism.md``; the reference itself serves one engine)."""
+
+    def __init__(self, llms: list):
+        self.replicas = [AsyncLLM(l) for l in llms]
+        self.llm = llms[0]
+        self._lock = threading.Lock()
+        self._where: dict[str, int] = {}
+        self._inflight = [0] * len(self.replicas)
+        self._next = 0
+        self.routed = [0] * len(self.replicas)          # requests sent to each replica so far
+
+    @property
+    def errored(self) -> Optional[str]:
+        for r in self.replicas:
+            if r.errored:
+                return r.errored
+        return None
+
+    def submit(self, prompt_token_ids, params, request_id: Optional[str] = None, prompt=None) -> str:
+        with self._lock:
+            i = min(range(len(self.replicas)), key=lambda j: (self._inflight[j], (j - self._next) % len(self.replicas)))
+            self._next = (i + 1) % len(self.replicas)
+            self._next_id = getattr(self, "_next_id", 0) + 1
+            rid = request_id or f"dp{i}-req-{self._next_id}"
+            self._inflight[i] += 1
+            self.routed[i] += 1
+            self._where[rid] = i
+        try:
+            return self.replicas[i].submit(prompt_token_ids, params, request_id=rid, prompt=prompt)
+        except Exception:
+            self._done(rid)
+            raise
+
+    def _done(self, rid: str) -> None:
+        with self._lock:
+            i = self._where.pop(rid, None)
+            if i is not None:
+                self._inflight[i] -= 1
+
+    def stream(self, request_id: str, timeout: Optional[float] = None) -> Iterator[StreamItem]:
+        i = self._where.get(request_id)
+        if i is None:
+            return
+        try:
+            for item in self.replicas[i].stream(request_id, timeout):
+                yield item
+        finally:
+            self._done(request_id)
+
+    def abort(self, request_id: str) -> None:
+        i = self._where.get(request_id)
+        if i is not None:
+            self.replicas[i].abort(request_id)
+
+    def generate(self, prompt_token_ids, params, request_id=None) -> StreamItem:
+        rid = self.submit(prompt_token_ids, params, request_id)
+        text, toks, last = [], [], None
+        for item in self.stream(rid):
+            text.append(item.text)
+            toks.extend(item.token_ids)
+            last = item
+        last.text, last.token_ids = "".join(text), toks
+        return last
+
+    def shutdown(self) -> None:
+        for r in self.replicas:
+            r.shutdown()
