@@ -290,11 +290,12 @@ def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, *, block_table: torch.
 
 
 def _decode_uses_tc(head_dim: int, group: int, block_size: int) -> bool:
-    """The tcgen05 swapped-operand decode kernel covers head_dim 128 and 256, GQA groups up to 16
-    and page sizes that tile 128 tokens; everything else takes the CUDA-core kernel."""
-    if head_dim not in (128, 256) or group > 16 or block_size < 8 or block_size % 8:
-        return False
-    return (128 % block_size == 0) if block_size <= 128 else (block_size % 128 == 0)
+    """Whether the first choice of the attention backend registry, the tcgen05 swapped-operand decode
+    kernel (head_dim 128 and 256, GQA groups up to 16, page sizes that tile 128 tokens), serves this
+    shape; everything else takes the CUDA-core kernel."""
+    from ..models.attention_backends import select
+    b = select("decode", "paged", head_dim=head_dim, group=group, block_size=block_size)
+    return b is not None and b.name == "tcgen05-decode"
 
 
 def attn_decode_splits(batch, num_kv_heads, group, head_dim, max_seq_len,
