@@ -43,9 +43,15 @@ def _run_world(cfg, world, prompts, n=6):
     return results
 
 
-@pytest.mark.parametrize("name,world", [("tiny-dense", 2), ("tiny-qwen3", 2), ("tiny-moe", 2), ("tiny-dense", 4)])
+@pytest.mark.parametrize("name,world", [("tiny-dense", 2), ("tiny-qwen3", 2), ("tiny-moe", 2), ("tiny-dense", 4),
+                                        ("tiny-mla", 2), ("tiny-gdn", 2), ("tiny-gdn+nvfp4", 2)])
 def test_sharded_ranks_agree_with_single_rank(name, world):
+    name, _, quant = name.partition("+")
     cfg = synthetic_config(name)
+    if quant:
+        cfg.quant = quant                               # every rank quantises its own shard
+    if name == "tiny-gdn":
+        cfg.num_heads, cfg.num_kv_heads = 4, 1          # the kv head is replicated on both ranks
     prompts = _prompts(cfg)
     base = _run_world(cfg, 1, prompts)[0]
     ranks = _run_world(cfg, world, prompts)
