@@ -151,3 +151,26 @@ def test_nvfp4_fused_producers():
     pg, sg = Q.quant_nvfp4_gated(a, g, gs)
     assert (pg == pg_ref).float().mean() > 0.97 and (sg == sg_ref).float().mean() > 0.97
     assert ops.read_status() == 0
+
+
+def test_nvfp4_plan_cache_and_autotune(monkeypatch):
+    """Tile-width plans: the heuristic for wide and narrow projections, and the timed choice."""
+    Q._NVFP4_PLANS.clear()
+    assert Q.nvfp4_plan(64, 34816, 5120) == 256
+    assert Q.nvfp4_plan(64, 5120, 17408) == 128
+    assert Q.nvfp4_plan(4096, 5120, 17408) == 256
+    assert (64, 34816, 5120) in Q._NVFP4_PLANS
+    monkeypatch.setenv("B200_NVFP4_AUTOTUNE", "1")
+    Q._NVFP4_PLANS.clear()
+    torch.manual_seed(3)
+    M, N, K = 32, 1024, 1024
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(torch.bfloat16)
+    wp, wsf, g_w = Q.ref_quant_nvfp4_weights(torch.randn(N, K, device=DEV) * 0.05)
+    g_a = (448.0 * 6.0 / x.float().abs().max()).reshape(1)
+    ap, sfa = Q.quant_nvfp4(x, g_a, swizzle=True)
+    sfw = Q.nvfp4_sf_chunks(wsf, 256)
+    a = Q.gemm_nvfp4(ap, sfa, g_a, wp, sfw, g_w)
+    assert Q._NVFP4_PLANS[(64, N, K)] in (128, 256)
+    b = Q.gemm_nvfp4(ap, sfa, g_a, wp, sfw, g_w, n_tile=384 - Q._NVFP4_PLANS[(64, N, K)])
+    assert torch.equal(a, b)                  # the tile width changes the schedule, not the sums
+    assert ops.read_status() == 0

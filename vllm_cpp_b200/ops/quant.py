@@ -152,19 +152,72 @@ def nvfp4_sf_chunks(sf: torch.Tensor, pad_rows: int = 256) -> torch.Tensor:
     return out
 
 
+# (rows bucket, N, K) -> weight rows per CTA; filled by the heuristic or, with B200_NVFP4_AUTOTUNE=1, by
+# timing both tile widths once per shape (outside stream capture)
+_NVFP4_PLANS: dict[tuple[int, int, int], int] = {}
+
+
+def _m_bucket(M: int) -> int:
+    for b in (16, 64, 128, 512, 2048):
+        if M <= b:
+            return b
+    return 8192
+
+
+def nvfp4_plan(M: int, N: int, K: int, run=None) -> int:
+    """Tile width (128 or 256 weight rows per CTA) of the W4A4 GEMM for a shape, cached per
+    (rows bucket, N, K). Heuristic: 256-row tiles unless they leave more than a third of the SMs
+    without a tile at decode sizes, where two 128-row tiles per 256 rows spread better (measured:
+    34816 x 5120 at 64 rows 37 us with 256 against 44 us with 128; 5120 x 17408 36.9 against 34.6).
+    ``run(n_tile)``: when given and B200_NVFP4_AUTOTUNE=1, both widths are timed once with CUDA
+    events and the faster one is kept (reference: the per-shape tactic cache of
+    ``src/vt/cuda/nvfp4_cutlass_tactic_impl.cuh``)."""
+    import os
+    key = (_m_bucket(M), N, K)
+    plan = _NVFP4_PLANS.get(key)
+    if plan is not None:
+        return plan
+    from . import num_sms
+    tiles256 = -(-N // 256) * -(-M // 128)
+    plan = 128 if (M <= 128 and tiles256 * 3 < num_sms() * 2 and N >= 256) else 256
+    if run is not None and os.environ.get("B200_NVFP4_AUTOTUNE", "0") == "1" \
+            and not torch.cuda.is_current_stream_capturing():
+        best = None
+        for nt in (256, 128):
+            for _ in range(2):
+                run(nt)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                run(nt)
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1)
+            if best is None or t < best[0]:
+                best = (t, nt)
+        plan = best[1]
+    _NVFP4_PLANS[key] = plan
+    return plan
+
+
 def gemm_nvfp4(aq, sfa, g_a, wq, sfw, g_w, out=None, bias=None, n_tile: int = 0):
     """W4A4: ``aq`` uint8 [M, K/2] and ``sfa`` from :func:`quant_nvfp4` (``swizzle=True``, global scale
     ``g_a``); ``wq`` uint8 [N, K/2], ``sfw`` from :func:`nvfp4_sf_chunks`, ``g_w`` the weight's fp32
-    multiplier. Both products run on ``tcgen05.mma.kind::mxf4nvf4`` with the scales in tensor memory."""
+    multiplier. Both products run on ``tcgen05.mma.kind::mxf4nvf4`` with the scales in tensor memory.
+    ``n_tile`` 0: the cached plan of the shape (:func:`nvfp4_plan`)."""
     _declare()
     M, kh = aq.shape
     N = wq.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
     ws = workspace(aq.device, 64 << 20, "w4")
-    check(lib().b200_gemm_nvfp4(ptr(aq), ptr(sfa), ptr(g_a), ptr(wq), ptr(sfw), ptr(g_w), ptr(out), out.stride(0),
-                                ptr(bias), M, N, kh * 2, n_tile, ptr(ws), ws.numel(), stream_ptr()),
-          f"gemm_nvfp4 M={M} N={N} K={kh * 2}")
+
+    def run(nt):
+        check(lib().b200_gemm_nvfp4(ptr(aq), ptr(sfa), ptr(g_a), ptr(wq), ptr(sfw), ptr(g_w), ptr(out), out.stride(0),
+                                    ptr(bias), M, N, kh * 2, nt, ptr(ws), ws.numel(), stream_ptr()),
+              f"gemm_nvfp4 M={M} N={N} K={kh * 2}")
+
+    run(n_tile or nvfp4_plan(M, N, kh * 2, run))
     return out
 
 
