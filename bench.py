@@ -554,8 +554,8 @@ def main() -> int:
                                        (f"tp{world}+ep{world}" if cfg.num_experts and world > 1
                                         else f"tp{world}")),
                        "collectives": ("none" if world == 1 or dp else
-                                       ("GEMM + NCCL" if args.unfused else
-                                        "fused GEMM + reduce-scatter / all-gather kernels over peer memory")),
+                                       ("GEMM + NCCL" if (args.unfused or getattr(llm.model, "tpf", None) is None)
+                                        else "fused GEMM + reduce-scatter / all-gather kernels over peer memory")),
                        "mode": "continuous batching, steady state",
                        "max_num_batched_tokens": args.max_num_batched_tokens,
                        "l2": "the weights and the KV cache read in every step exceed L2 (126 MB) many times over",

@@ -33,3 +33,31 @@ def test_attention_backend_registry_priorities():
     assert AB.describe(synthetic_config("deepseek-v2-lite"), 64)["mla"]["decode"] == "mla-absorbed-decode"
     from vllm_cpp_b200 import ops
     assert ops._decode_uses_tc(128, 4, 16) and not ops._decode_uses_tc(64, 4, 16)
+
+
+def test_validation_layer_names_the_broken_rule():
+    import pytest
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.ops.validate import OpArgumentError, validate
+    a = torch.zeros(4, 64, dtype=torch.bfloat16)
+    w = torch.zeros(8, 64, dtype=torch.bfloat16)
+    validate("gemm", a=a, w=w)
+    with pytest.raises(OpArgumentError, match="same K"):
+        validate("gemm", a=a, w=torch.zeros(8, 32, dtype=torch.bfloat16))
+    with pytest.raises(OpArgumentError, match="are bf16"):
+        ops.gemm(a.float(), w)                  # raised before any launcher (or library) is touched
+    with pytest.raises(OpArgumentError, match="rows are contiguous"):
+        validate("gemm", a=a[:, ::2], w=w[:, ::2])
+    with pytest.raises(OpArgumentError, match="multiple of 256"):
+        validate("gemm_nvfp4", aq=torch.zeros(4, 64, dtype=torch.uint8), wq=torch.zeros(8, 64, dtype=torch.uint8),
+                 sfa=torch.zeros(1), sfw=torch.zeros(1), g_a=torch.ones(1), g_w=torch.ones(1))
+    with pytest.raises(OpArgumentError, match="head_dim is 64, 128 or 256"):
+        validate("attn_decode", q=torch.zeros(2, 4 * 96, dtype=torch.bfloat16), num_q_heads=4, num_kv_heads=2,
+                 head_dim=96, block_size=16, kv_cache=torch.zeros(3, 2, 16, 2, 96, dtype=torch.bfloat16),
+                 block_table=torch.zeros(2, 4, dtype=torch.int32), seq_lens=torch.zeros(2, dtype=torch.int32))
+    e = None
+    try:
+        validate("rmsnorm", x=torch.zeros(3, 8, dtype=torch.bfloat16), weight=torch.zeros(7))
+    except OpArgumentError as ex:
+        e = ex
+    assert e is not None and e.op == "rmsnorm" and "weight" in e.rule and "(3, 8)" in str(e)

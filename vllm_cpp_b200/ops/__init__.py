@@ -11,6 +11,7 @@ import torch
 
 from . import _lib
 from ._lib import check, lib, ptr, stream_ptr
+from .validate import OpArgumentError, validate  # noqa: F401
 
 ACT_SILU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
 EW_ADD, EW_RELU, EW_MUL_SCALAR, EW_SOFTCAP, EW_SIGMOID_MUL, EW_MUL = 0, 1, 2, 3, 4, 5
@@ -60,14 +61,15 @@ def gemm(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
     """``out[M,N] = a[M,K] @ w[N,K]^T (+ bias) (+ residual)``; bf16 inputs, fp32 accumulate.
     ``const_w``: ``w`` is a model weight that no kernel in the stream writes, so the GEMM may
     fetch its first tiles while the previous kernel is still running."""
-    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
-    assert a.stride(1) == 1 and w.stride(1) == 1
+    if not (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.shape[1] == w.shape[1] and a.stride(1) == 1 and w.stride(1) == 1
+            and (out is None or (out.stride(1) == 1 and out.shape == (a.shape[0], w.shape[0])))):
+        validate("gemm", a=a, w=w, out=out, bias=bias, residual=residual)   # names the broken rule
+        raise OpArgumentError("gemm", "argument contract", "see ops.validate.RULES['gemm']")
     M, K = a.shape
     N = w.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
-    assert out.stride(1) == 1 and out.shape == (M, N)
     ws = workspace(a.device, GEMM_WS_BYTES)
     rc = lib().b200_gemm_bf16(
         ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out.stride(0),
@@ -83,6 +85,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, *,
             gemma: bool = False) -> torch.Tensor:
     """``out = rmsnorm(x) * w``; with ``residual``: ``residual += x`` first (in place) and the
     norm is taken over the updated residual."""
+    if x.dim() != 2 or weight.numel() != x.shape[1] or x.stride(1) != 1:
+        validate("rmsnorm", x=x, weight=weight, residual=residual)
     T, H = x.shape
     if out is None:
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)

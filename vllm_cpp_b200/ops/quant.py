@@ -206,6 +206,9 @@ def gemm_nvfp4(aq, sfa, g_a, wq, sfw, g_w, out=None, bias=None, n_tile: int = 0)
     multiplier. Both products run on ``tcgen05.mma.kind::mxf4nvf4`` with the scales in tensor memory.
     ``n_tile`` 0: the cached plan of the shape (:func:`nvfp4_plan`)."""
     _declare()
+    if aq.dim() != 2 or wq.dim() != 2 or aq.shape[1] != wq.shape[1] or (aq.shape[1] * 2) % 256 or wq.shape[0] % 8:
+        from .validate import validate
+        validate("gemm_nvfp4", aq=aq, wq=wq, sfa=sfa, sfw=sfw, g_a=g_a, g_w=g_w)
     M, kh = aq.shape
     N = wq.shape[0]
     if out is None:
