@@ -8,10 +8,14 @@
 // rows. tcgen05 with swapped operands, one CTA = one (sequence, kv split):
 //     S^T[128 tok, 16 heads] = C[128 tok, 576] * q'[16, 576]^T
 //     O^T[512, 16]          += C[128 tok, 0:512]^T * P^T          (four M = 128 products)
-// The latent tile streams through a TMA ring in 128-column pieces: five pieces for S (the
-// last one half full), then the four value pieces again for O once P is known (a second L2
-// read instead of 144 KB of shared memory per tile). Softmax as in attn_decode_tc.cu: one
-// thread per token, lazily raised running max, O^T rescaled in TMEM when it moves.
+// Every byte of the latent tile is loaded once. Its four 128-column value pieces go through a ring
+// of five 32 KB slots and stay there from the S product until the O product of the same tile has
+// read them (as the MN-major V^T operand); the 64 rotary columns go through two 16 KB slots that
+// are free again as soon as S has read them. The MMA warp issues S(j+1) on the pieces that could be
+// prefetched (rotary + the first value piece) while the softmax of tile j runs, then O(j), whose
+// four products release the value slots one by one for the rest of tile j+1, then the rest of
+// S(j+1). Softmax as in attn_decode_tc.cu: one thread per token, lazily raised running max, O^T
+// rescaled in TMEM when it moves.
 //
 // Prefill helpers (reference: cuda_mla_prefill.cu GatherMlaCache / ConcatMlaNopeRope / PadV):
 // gather a request's latent rows into a dense buffer, then build per-head K = [k_nope | k_pe]
@@ -29,10 +33,13 @@ typedef __nv_bfloat16 bf16;
 static constexpr int kTok = 128;
 static constexpr int kNQ = 16;
 static constexpr int kLat = 512, kRope = 64, kRow = kLat + kRope;   // 576
-static constexpr int kPieces = 5;          // 128-column pieces of a row (last: 64 columns)
-static constexpr int kVPieces = 4;
-static constexpr int kSlots = 6;
+static constexpr int kVPieces = 4;         // 128-column value pieces of a row (the rotary 64 columns follow)
+static constexpr int kVSlots = 5;          // ring of the value pieces
+static constexpr int kRSlots = 2;          // ring of the rotary pieces
+static constexpr int kSlots = kVSlots + kRSlots;
 static constexpr int kSlotBytes = 128 * 128 * 2;
+static constexpr int kRopeBytes = 128 * 64 * 2;
+static constexpr int kRingBytes = kVSlots * kSlotBytes + kRSlots * kRopeBytes;
 static constexpr int kQBytes = 9 * 2048;   // 9 halves of [16 heads x 64 cols]
 
 struct MlaDecodeParams {
@@ -91,7 +98,8 @@ __global__ void __launch_bounds__(192, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sKV = smem;
-  uint8_t* sQ = sKV + kSlots * kSlotBytes;
+  uint8_t* sRope = sKV + kVSlots * kSlotBytes;
+  uint8_t* sQ = sKV + kRingBytes;
   uint8_t* sP = sQ + kQBytes;                      // 2 buffers x (2 token halves x 2 KB)
   MlaBars* bars = reinterpret_cast<MlaBars*>(sP + 8192);
 
@@ -147,15 +155,21 @@ __global__ void __launch_bounds__(192, 1)
         const int rows_per_load = min(p.block_size, kTok);
         const int loads = kTok / rows_per_load;
         bool ok = true;
-        int it = 0;
-        auto load_piece = [&](int j, int piece) {   // piece < kPieces: columns [128*piece, ...)
-          const int sl = it % kSlots;
-          const uint32_t ph = (it / kSlots) & 1;
+        int itv = 0, itr = 0;
+        // piece < kVPieces: value columns [128 * piece, +128) into the value ring; piece == kVPieces:
+        // the rotary columns [512, 576) into the rotary ring
+        auto load_piece = [&](int j, int piece) {
+          const bool rope = piece == kVPieces;
+          int& it = rope ? itr : itv;
+          const int n = rope ? kRSlots : kVSlots;
+          const int sl = it % n;
+          const uint32_t ph = (it / n) & 1;
           ++it;
-          if (!mbar_wait(&bars->kv_empty[sl], ph ^ 1, p.status)) { ok = false; return; }
-          uint8_t* dst = sKV + sl * kSlotBytes;
-          const int halves = (piece == kPieces - 1) ? 1 : 2;
-          mbar_expect_tx(&bars->kv_full[sl], halves * 16384);
+          const int bi_ = rope ? kVSlots + sl : sl;                // barrier index
+          if (!mbar_wait(&bars->kv_empty[bi_], ph ^ 1, p.status)) { ok = false; return; }
+          uint8_t* dst = rope ? sRope + sl * kRopeBytes : sKV + sl * kSlotBytes;
+          const int halves = rope ? 1 : 2;
+          mbar_expect_tx(&bars->kv_full[bi_], halves * 16384);
           const int tok0 = tok_base + j * kTok;
           for (int l = 0; l < loads; ++l) {
             const int tk = tok0 + l * rows_per_load;
@@ -163,15 +177,15 @@ __global__ void __launch_bounds__(192, 1)
             const int blk = (bi < nblk_valid) ? bt[bi] : bt[0];
             const int row = (blk < 0 ? 0 : blk) * p.block_size + tk % p.block_size;
             for (int hf = 0; hf < halves; ++hf)
-              tma_load_2d(dst + hf * 16384 + l * rows_per_load * 128, &tmC, &bars->kv_full[sl],
+              tma_load_2d(dst + hf * 16384 + l * rows_per_load * 128, &tmC, &bars->kv_full[bi_],
                           piece * 128 + hf * 64, row);
           }
         };
-        for (int j = 0; j <= ntiles && ok; ++j) {
-          if (j < ntiles)
-            for (int pc = 0; pc < kPieces && ok; ++pc) load_piece(j, pc);
-          if (j >= 1)
-            for (int pc = 0; pc < kVPieces && ok; ++pc) load_piece(j - 1, pc);
+        // per tile: rotary piece first (its slot turns over early), then the value pieces in the
+        // order both products read them
+        for (int j = 0; j < ntiles && ok; ++j) {
+          load_piece(j, kVPieces);
+          for (int pc = 0; pc < kVPieces && ok; ++pc) load_piece(j, pc);
         }
       }
     } else if (warp == 1) {
@@ -180,53 +194,60 @@ __global__ void __launch_bounds__(192, 1)
         constexpr uint32_t idesc_pv = umma_idesc_bf16(128, kNQ, 1, 0);
         bool ok = mbar_wait(&bars->q_full, 0, p.status);
         const uint32_t q_addr = smem_u32(sQ);
-        int it = 0;
-        for (int j = 0; j <= ntiles && ok; ++j) {
-          if (j < ntiles) {
-            const int sb = j & 1;
-            if (!mbar_wait(&bars->s_empty[sb], ((j >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
-            for (int pc = 0; pc < kPieces && ok; ++pc) {
-              const int sl = it % kSlots;
-              const uint32_t ph = (it / kSlots) & 1;
-              ++it;
-              if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
-              tc_fence_after_sync();
-              const uint32_t k_addr = smem_u32(sKV + sl * kSlotBytes);
-              const int ksteps = (pc == kPieces - 1) ? 4 : 8;
-              for (int kk = 0; kk < ksteps; ++kk) {
-                const uint32_t koff = (kk / 4) * 16384 + (kk % 4) * 32;
-                const uint32_t qoff = (pc * 2 + kk / 4) * 2048 + (kk % 4) * 32;
-                umma_bf16_ss(tmem_s + sb * 16, umma_desc_k_sw128(k_addr + koff, 1024),
-                             umma_desc_k_sw128(q_addr + qoff, 1024), idesc_qk, (pc | kk) != 0);
-              }
-              umma_commit(&bars->kv_empty[sl]);
-            }
-            if (ok) umma_commit(&bars->s_full[sb]);
+        // value piece pc of tile j sits in value slot (4 j + pc) % 5 on that slot's ((4 j + pc) / 5)-th
+        // use; the rotary piece of tile j in rotary slot j % 2
+        auto s_piece = [&](int j, int pc, bool first) -> bool {      // one piece of S(j) = K(j) Q^T
+          const bool rope = pc == kVPieces;
+          const int f = rope ? j : kVPieces * j + pc, n = rope ? kRSlots : kVSlots;
+          const int sl = f % n, bi_ = rope ? kVSlots + sl : sl;
+          if (!mbar_wait(&bars->kv_full[bi_], (f / n) & 1, p.status)) return false;
+          tc_fence_after_sync();
+          const uint32_t k_addr = smem_u32(rope ? sRope + sl * kRopeBytes : sKV + sl * kSlotBytes);
+          const int ksteps = rope ? 4 : 8;
+          for (int kk = 0; kk < ksteps; ++kk) {
+            const uint32_t koff = (kk / 4) * 16384 + (kk % 4) * 32;
+            const uint32_t qoff = (pc * 2 + kk / 4) * 2048 + (kk % 4) * 32;
+            umma_bf16_ss(tmem_s + (j & 1) * 16, umma_desc_k_sw128(k_addr + koff, 1024),
+                         umma_desc_k_sw128(q_addr + qoff, 1024), idesc_qk, !(first && kk == 0));
           }
-          if (j >= 1 && ok) {
-            const int i = j - 1;
-            const int pb = i & 1;
-            if (!mbar_wait(&bars->p_full[pb], (i >> 1) & 1, p.status)) { ok = false; break; }
-            const uint32_t p_addr = smem_u32(sP + pb * 4096);
-            for (int pc = 0; pc < kVPieces && ok; ++pc) {
-              const int sl = it % kSlots;
-              const uint32_t ph = (it / kSlots) & 1;
-              ++it;
-              if (!mbar_wait(&bars->kv_full[sl], ph, p.status)) { ok = false; break; }
-              tc_fence_after_sync();
-              const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
+          if (rope) umma_commit(&bars->kv_empty[bi_]);    // the value slots stay until O(j) has read them
+          return true;
+        };
+        // S(0): rotary piece, then the value pieces
+        ok = ok && mbar_wait(&bars->s_empty[0], 1, p.status);
+        ok = ok && s_piece(0, kVPieces, true);
+        for (int pc = 0; pc < kVPieces && ok; ++pc) ok = s_piece(0, pc, false);
+        if (ok) umma_commit(&bars->s_full[0]);
+        for (int j = 0; j < ntiles && ok; ++j) {
+          const bool next = j + 1 < ntiles;
+          if (next) {
+            // what of tile j+1 can be in shared memory already: its rotary piece and one value piece
+            const int sb = (j + 1) & 1;
+            if (!mbar_wait(&bars->s_empty[sb], (((j + 1) >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
+            ok = s_piece(j + 1, kVPieces, true) && s_piece(j + 1, 0, false);
+            if (!ok) break;
+          }
+          // O(j) += V(j)^T P(j)^T, releasing the value slots of tile j one by one
+          const int pb = j & 1;
+          if (!mbar_wait(&bars->p_full[pb], (j >> 1) & 1, p.status)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t p_addr = smem_u32(sP + pb * 4096);
+          for (int pc = 0; pc < kVPieces; ++pc) {
+            const int f = kVPieces * j + pc, sl = f % kVSlots;
+            const uint32_t v_addr = smem_u32(sKV + sl * kSlotBytes);
 #pragma unroll
-              for (int kk = 0; kk < kTok / 16; ++kk) {
-                const uint32_t poff = (kk / 4) * 2048 + (kk % 4) * 32;
-                umma_bf16_ss(tmem_o + pc * 16, umma_desc_mn_sw128(v_addr + kk * 2048, 16384, 1024),
-                             umma_desc_k_sw128(p_addr + poff, 1024), idesc_pv, (i | kk) != 0);
-              }
-              umma_commit(&bars->kv_empty[sl]);
+            for (int kk = 0; kk < kTok / 16; ++kk) {
+              const uint32_t poff = (kk / 4) * 2048 + (kk % 4) * 32;
+              umma_bf16_ss(tmem_o + pc * 16, umma_desc_mn_sw128(v_addr + kk * 2048, 16384, 1024),
+                           umma_desc_k_sw128(p_addr + poff, 1024), idesc_pv, (j | kk) != 0);
             }
-            if (ok) {
-              umma_commit(&bars->pv_done);    // before p_empty: whoever sees p_empty has this arrival too
-              umma_commit(&bars->p_empty[pb]);
-            }
+            umma_commit(&bars->kv_empty[sl]);
+          }
+          umma_commit(&bars->pv_done);    // before p_empty: whoever sees p_empty has this arrival too
+          umma_commit(&bars->p_empty[pb]);
+          if (next) {
+            for (int pc = 1; pc < kVPieces && ok; ++pc) ok = s_piece(j + 1, pc, false);
+            if (ok) umma_commit(&bars->s_full[(j + 1) & 1]);
           }
         }
       }
@@ -511,7 +532,7 @@ int b200_mla_decode(const void* qabs, void* out, int ldo, const void* cache, int
   p.scale_log2 = scale * 1.4426950408889634f;
   p.splits = splits; p.tmp_o = (float*)tmp_o; p.tmp_lse = (float*)tmp_lse;
   p.status = device_status_word();
-  constexpr size_t smem = (size_t)kSlots * kSlotBytes + kQBytes + 8192 + 1024 + sizeof(MlaBars);
+  constexpr size_t smem = (size_t)kRingBytes + kQBytes + 8192 + 1024 + sizeof(MlaBars);
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
