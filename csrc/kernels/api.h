@@ -162,6 +162,29 @@ typedef struct B200MoeScatter {
   const void* op_counter;
 } B200MoeScatter;
 
+// A fused-chain program (recipe.cu): rows x width bf16 values, up to four shared-memory row
+// registers, a list of steps over them. Operand rows are addressed as
+// ptr + (row / heads) * ld + (row % heads) * width + col, in elements of the operand's type
+// (bf16, or bytes for fp8 output); ld = 0 for a vector or scalar operand.
+#define B200_CHAIN_MAX_STEPS 16
+#define B200_CHAIN_MAX_OPERANDS 12
+typedef struct B200ChainStep {
+  int op, dst, a, b;
+  int operand, operand2, operand3;
+  int flag;
+  float f;
+} B200ChainStep;
+typedef struct B200ChainOperand {
+  void* ptr;
+  long long ld, col;
+} B200ChainOperand;
+typedef struct B200Chain {
+  int n_steps, n_regs, width, heads;
+  long long rows;
+  B200ChainStep steps[B200_CHAIN_MAX_STEPS];
+  B200ChainOperand operands[B200_CHAIN_MAX_OPERANDS];
+} B200Chain;
+
 // ---- every other launcher, by source file ----------------------------------------------
 // ---- attn_decode.cu
 int b200_attn_decode_splits(int B, int Hkv, int G, int D, int max_seq_len);
@@ -252,6 +275,8 @@ int b200_greedy_reject(const void* target_argmax, const void* draft, const void*
 int b200_splice_sampled(void* input_ids, const void* dst_idx, const void* src_row, const void* last_sampled, int n, cudaStream_t stream);
 int b200_scatter_sampled(void* last_sampled, const void* row_of, const void* sampled, int n, cudaStream_t stream);
 uint64_t b200_splitmix64(uint64_t z);
+// ---- recipe.cu
+int b200_fused_chain(const B200Chain* prog, cudaStream_t stream);
 // ---- tp_fused.cu
 int b200_tp_reduce_norm_gather(const B200TpReduce* a, cudaStream_t stream);
 int b200_tp_oneshot_allreduce_norm(const B200TpOneShot* a, cudaStream_t stream);

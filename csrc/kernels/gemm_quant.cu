@@ -23,6 +23,7 @@
 #include <unordered_map>
 
 #include "api.h"
+#include "quant_codec.cuh"
 #include "sm100.cuh"
 
 namespace b200 {
@@ -177,12 +178,6 @@ __device__ __forceinline__ float e2m1_value(uint32_t code) {
   const float v = mag < 2 ? 0.5f * (float)mag : (float)(2 + (mag & 1)) * (float)(1 << ((mag >> 1) - 1)) * 0.5f;
   return (code & 8u) ? -v : v;
 }
-__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
-  __nv_fp8_e4m3 t;
-  t.__x = b;
-  return (float)t;
-}
-
 // Whole-matrix expansion: packed [N, K/2] + scales [N, K/16] -> bf16 [N, K].
 __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf,
                                      const float* __restrict__ gscale, bf16* __restrict__ out, long N,
@@ -208,24 +203,6 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const u
 // ---------------------------------------------------------------------------------------
 // Producers
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
-  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-}
-__device__ __forceinline__ uint32_t float_to_e2m1(float v) {
-  // round to nearest representable magnitude (ties to even code), saturate at 6
-  const float a = fabsf(v);
-  uint32_t code;
-  if (a <= 0.25f) code = 0;
-  else if (a < 0.75f) code = 1;
-  else if (a <= 1.25f) code = 2;
-  else if (a < 1.75f) code = 3;
-  else if (a <= 2.5f) code = 4;
-  else if (a < 3.5f) code = 5;
-  else if (a <= 5.0f) code = 6;
-  else code = 7;
-  return code | (v < 0.f ? 8u : 0u);
-}
-
 // out = fp8(x / scale) (optionally after RMSNorm with weight w; gemma adds 1 to w).
 __global__ void __launch_bounds__(256)
     quant_fp8_kernel(const bf16* __restrict__ x, long ldx, const bf16* __restrict__ w, float eps, int gemma,

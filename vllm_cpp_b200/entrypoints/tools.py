@@ -14,6 +14,7 @@
 ``dump-ops``         writes inputs and fp32 oracle outputs of the kernel library's ops to an ``.npz``
                      file, for comparing another implementation op by op (reference
                      ``tools/parity/dump_ops.py``)
+``list-recipes``     the fusion-recipe catalogue: steps, available tiers, reference recipe, as JSON
 ``dump-greedy``      greedy token ids of a checkpoint for a prompt file, as JSON (reference
                      ``tools/parity/dump_27b_emulation_greedy.py``: the end-to-end golden)
 """
@@ -168,6 +169,14 @@ def cmd_quant_gemm_bench(a) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------ list-recipes
+def cmd_list_recipes(a) -> int:
+    from ..ops import recipes
+    json.dump(recipes.describe(), sys.stdout, indent=1)
+    sys.stdout.write("\n")
+    return 0
+
+
 # ------------------------------------------------------------------------------ dump-ops
 def cmd_dump_ops(a) -> int:
     """Inputs are drawn from a seeded CPU generator; outputs come from the fp32 references in
@@ -239,6 +248,8 @@ def main(argv=None) -> int:
     p.add_argument("out")
     p.add_argument("--seed", type=int, default=0)
     p.set_defaults(fn=cmd_dump_ops)
+    p = sub.add_parser("list-recipes")
+    p.set_defaults(fn=cmd_list_recipes)
     p = sub.add_parser("dump-greedy")
     p.add_argument("--model", required=True)
     p.add_argument("--prompts", required=True)

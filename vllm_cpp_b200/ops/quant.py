@@ -244,6 +244,26 @@ def ref_quant_nvfp4_weights(w: torch.Tensor):
     return packed, s8.view(torch.uint8).contiguous(), g.to(torch.float32)
 
 
+def ref_quant_nvfp4_activations(x: torch.Tensor, gscale: torch.Tensor):
+    """The activation quantiser restated in PyTorch: per 16 values the scale is
+    e4m3(amax * gscale / 6) and the codes are e2m1(x * gscale / scale), nearest with ties to the
+    even code. Returns (packed uint8 [T, K/2], scale bytes uint8 [T, K/16])."""
+    xf = x.float()
+    T, K = xf.shape
+    gs = gscale.float().reshape(())
+    blocks = xf.reshape(T, K // 16, 16)
+    s8 = (blocks.abs().amax(-1) * gs / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)
+    sdec = s8.float()
+    mul = torch.where(sdec > 0, gs / sdec.clamp_min(1e-30), torch.zeros_like(sdec)).unsqueeze(-1)
+    q = blocks * mul
+    a = q.abs()
+    code = ((a > 0.25).long() + (a >= 0.75).long() + (a > 1.25).long() + (a >= 1.75).long() +
+            (a > 2.5).long() + (a >= 3.5).long() + (a > 5.0).long())
+    code = (code | ((q < 0).long() << 3)).reshape(T, K).to(torch.uint8)
+    packed = (code[:, 0::2] | (code[:, 1::2] << 4)).contiguous()
+    return packed, s8.view(torch.uint8).contiguous()
+
+
 def ref_dequant_nvfp4(packed, sf_bytes, g):
     N, kh = packed.shape
     vals = torch.tensor(FP4_VALUES + [-v for v in FP4_VALUES], device=packed.device)
