@@ -233,6 +233,60 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Dynamic per-tensor fp8: pass 1 takes the maximum magnitude of the tensor (bit pattern of a
+// non-negative float orders like the unsigned integer, so one atomicMax per block), pass 2 divides
+// by amax / 448 and leaves that scale for the GEMM.
+__global__ void __launch_bounds__(256)
+    absmax_bf16_kernel(const bf16* __restrict__ x, long ldx, long T, int H, unsigned* __restrict__ amax_bits) {
+  __shared__ float red[8];
+  const int nv = H >> 3;
+  const long total = T * (long)nv;
+  float m = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / nv;
+    const int c = (int)(i % nv);
+    const uint4 v = *reinterpret_cast<const uint4*>(x + t * ldx + (long)c * 8);
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(wds[j]);
+      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
+    if (m > 0.f && !(m != m)) atomicMax(amax_bits, __float_as_uint(m));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    quant_fp8_dynamic_kernel(const bf16* __restrict__ x, long ldx, const unsigned* __restrict__ amax_bits,
+                             float* __restrict__ scale_out, uint8_t* __restrict__ out, long ldo, long T, int H) {
+  const float s = fmaxf(__uint_as_float(*amax_bits), 1e-12f) / 448.f;
+  const float is = 1.f / s;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = s;
+  const int nv = H >> 3;
+  const long total = T * (long)nv;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / nv;
+    const int c = (int)(i % nv);
+    const uint4 v = *reinterpret_cast<const uint4*>(x + t * ldx + (long)c * 8);
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(wds[j]);
+      const uint32_t two = (uint32_t)float_to_e4m3(f.x * is) | ((uint32_t)float_to_e4m3(f.y * is) << 8);
+      if (j < 2) lo |= two << (16 * j); else hi |= two << (16 * (j - 2));
+    }
+    *reinterpret_cast<uint2*>(out + t * ldo + (long)c * 8) = make_uint2(lo, hi);
+  }
+}
+
 // NVFP4 activation quant: per 16 values, scale = e4m3(amax / 6 * gs) where gs is the global
 // scale (448 * 6 / tensor amax); values = e2m1(x * gs / scale). mode 0: x; mode 1: silu(gate) * up
 // with x = [gate | up] rows of width 2K; mode 2: x * sigmoid(gate) with a separate gate tensor. Scales row-major [T, K/16] or in the 128x4-swizzled
@@ -407,6 +461,21 @@ int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int g
   if (T <= 0) return 0;
   quant_fp8_kernel<<<(unsigned)T, 256, 0, stream>>>((const bf16*)x, ldx, (const bf16*)norm_w, eps, gemma, scale,
                                                     (uint8_t*)out, ldo, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// scratch: two words (maximum bits, then the scale = amax / 448 the GEMM reads as a_scale).
+int b200_quant_fp8_dynamic(const void* x, long ldx, void* scratch, void* out, long ldo, long T, int H,
+                           cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((H & 7) || (ldx & 7) || (ldo & 7) || ((uintptr_t)x & 15) || ((uintptr_t)out & 7)) return -1;
+  if (cudaMemsetAsync(scratch, 0, 4, stream) != cudaSuccess) return -2;
+  const long vecs = T * (long)(H / 8);
+  long blocks = (vecs + 255) / 256;
+  if (blocks > (long)b200_num_sms() * 8) blocks = (long)b200_num_sms() * 8;
+  absmax_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)x, ldx, T, H, (unsigned*)scratch);
+  quant_fp8_dynamic_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const bf16*)x, ldx, (const unsigned*)scratch,
+                                                                 (float*)scratch + 1, (uint8_t*)out, ldo, T, H);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -50,3 +50,80 @@ def test_quantised_gpu_matches_quantised_cpu(name):
     # random-weight hybrid the recurrent state amplifies that rounding difference, so only the
     # dense model is held to a high agreement after the first token.
     assert hit / sum(len(a) for a in gpu) > (0.7 if name == "tiny-dense" else 0.4)
+
+
+def test_fp8_weight_round_trip_and_cpu_model():
+    """Per-channel e4m3 weights: the round trip stays within fp8 precision, and an fp8-configured
+    model runs W8A8 on the CPU oracle (both operands rounded to e4m3, scales applied to the sum)."""
+    from vllm_cpp_b200.models.backend import CpuBackend, Fp8Weight, fp8_quant_activations
+    torch.manual_seed(0)
+    w = torch.randn(24, 64) * 0.05
+    q = Fp8Weight.from_dense(w)
+    assert q.w8.dtype == torch.float8_e4m3fn and q.w_scale.shape == (24,) and q.shape == (24, 64)
+    assert ((q.dequant().float() - w).abs() <= w.abs() * 2 ** -3 + 1e-4).all()     # 3 mantissa bits
+    a = torch.randn(5, 64).to(torch.bfloat16)
+    y = CpuBackend("cpu").gemm(a, q)
+    exact = a.float() @ w.t()
+    assert ((y.float() - exact).norm() / exact.norm()).item() < 0.06
+    a8, s = fp8_quant_activations(a)
+    assert abs(a8.float().abs().max().item() - 448.0) < 1e-3 and s > 0
+    # static activation scale from a checkpoint
+    q.input_scale = torch.tensor([0.02])
+    y2 = CpuBackend("cpu").gemm(a, q)
+    assert ((y2.float() - exact).norm() / exact.norm()).item() < 0.06
+    cfg = synthetic_config("tiny-dense")
+    cfg.quant = "fp8"
+    llm, toks = _run("cpu", cfg, _prompts(cfg))
+    assert isinstance(llm.model.layers[0]["qkv"], Fp8Weight) and all(len(t) == 8 for t in toks)
+    cfg2 = synthetic_config("tiny-dense")
+    _, ref_toks = _run("cpu", cfg2, _prompts(cfg2))
+    assert [t[0] for t in toks] == [t[0] for t in ref_toks]      # 8-bit rounding keeps the first tokens
+
+
+@pytest.mark.gpu
+def test_fp8_dynamic_quantiser_and_backend_gemm():
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.models.backend import CpuBackend, Fp8Weight, GpuBackend
+    from vllm_cpp_b200.ops import quant as Q
+    torch.manual_seed(4)
+    x = (torch.randn(300, 1024, device="cuda") * 2).to(torch.bfloat16)
+    x8, s = Q.quant_fp8_dynamic(x)
+    amax = x.float().abs().max()
+    assert torch.allclose(s, (amax / 448.0).reshape(1), rtol=1e-6)
+    want = (x.float() / s).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (x8.view(torch.uint8) == want.view(torch.uint8)).float().mean().item() > 0.995
+    assert (x8.float() - want.float()).abs().max().item() <= 32.0       # one e4m3 step at the top binade
+    # a strided view (the second half of a merged projection output)
+    big = torch.randn(50, 512, device="cuda").to(torch.bfloat16)
+    v8, sv = Q.quant_fp8_dynamic(big[:, 256:])
+    assert torch.allclose(sv, (big[:, 256:].float().abs().max() / 448.0).reshape(1), rtol=1e-6)
+    # the backend's W8A8 linear against the CPU restatement, dynamic and static activation scales
+    w = torch.randn(520, 1024) * 0.03
+    q = Fp8Weight.from_dense(w)
+    qg = Fp8Weight(q.w8.cuda(), q.w_scale.cuda())
+    bias = torch.randn(520).to(torch.bfloat16)
+    for static in (None, torch.tensor([0.03])):
+        q.input_scale = static
+        qg.input_scale = static.cuda() if static is not None else None
+        for M in (7, 300):
+            got = GpuBackend("cuda").gemm(x[:M], qg, bias=bias.cuda())
+            exp = CpuBackend("cpu").gemm(x[:M].cpu(), q, bias=bias)
+            assert ((got.cpu().float() - exp.float()).norm() / exp.float().norm()).item() < 1e-2
+    assert ops.read_status() == 0
+
+
+@pytest.mark.gpu
+def test_fp8_gpu_model_matches_fp8_cpu_model():
+    from vllm_cpp_b200 import ops
+    from vllm_cpp_b200.models.backend import Fp8Weight
+    cfg = synthetic_config("tiny-dense")
+    cfg.quant = "fp8"
+    cfg.head_dim = 128
+    prompts = _prompts(cfg)
+    _, cpu = _run("cpu", cfg, prompts)
+    llm, gpu = _run("cuda", cfg, prompts)
+    assert isinstance(llm.model.layers[0]["down"], Fp8Weight)
+    assert ops.read_status() == 0
+    assert [a[0] for a in gpu] == [a[0] for a in cpu]
+    hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(gpu, cpu))
+    assert hit / sum(len(a) for a in gpu) > 0.7

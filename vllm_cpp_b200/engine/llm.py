@@ -9,6 +9,8 @@ abort_request`` (``src/vllm/v1/engine/llm_engine.cpp:22-83``).
 """
 from __future__ import annotations
 
+import os
+
 import itertools
 import time
 from dataclasses import dataclass, field
@@ -85,6 +87,10 @@ class LLM:
         if getattr(cfg, "quant", None) == "nvfp4" and getattr(args, "quantize", True) \
                 and hasattr(self.model, "quantize_weights"):
             self.model.quantize_weights("nvfp4")
+        if getattr(cfg, "quant", None) == "fp8" and getattr(args, "quantize", True) \
+                and hasattr(self.model, "quantize_weights") and os.environ.get("B200_FP8_WEIGHTS", "fp8") == "fp8":
+            # fp8 checkpoints run W8A8 on the fp8 tensor cores (B200_FP8_WEIGHTS=bf16: expanded weights)
+            self.model.quantize_weights("fp8")
         if args.cpu_weight_quant and torch.device(device).type == "cpu" \
                 and hasattr(self.model, "quantize_weights"):
             self.model.quantize_weights(args.cpu_weight_quant)

@@ -60,6 +60,48 @@ class QuantWeight:
         return QuantWeight(packed, sf, g)
 
 
+class Fp8Weight:
+    """fp8-e4m3 weight of a linear layer with one fp32 scale per output channel (or per tensor),
+    and optionally the checkpoint's static activation scale; without one the activations are
+    quantised per call with their own maximum (W8A8 on the fp8 tensor cores either way).
+    Reference: the FP8 W8A8 linear method of the 35B-A3B configuration
+    (src/vt/cuda/cuda_matmul_fp8_cutlass.cu, QuantFp8StaticKernel + per-tensor scaled-mm)."""
+
+    def __init__(self, w8, w_scale, input_scale=None):
+        self.w8, self.w_scale, self.input_scale = w8, w_scale.float().contiguous(), input_scale
+        self.shape = tuple(w8.shape)
+        self.device = w8.device
+
+    def numel(self):
+        return self.w8.numel()
+
+    def element_size(self):
+        return 1
+
+    def data_ptr(self):
+        return self.w8.data_ptr()
+
+    def dequant(self):
+        s = self.w_scale.reshape(-1, 1) if self.w_scale.numel() > 1 else self.w_scale
+        return (self.w8.float() * s).to(torch.bfloat16)
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, per_channel: bool = True) -> "Fp8Weight":
+        wf = w.float()
+        amax = wf.abs().amax(1) if per_channel else wf.abs().max().reshape(1)
+        scale = (amax / 448.0).clamp_min(1e-12)
+        w8 = (wf / (scale[:, None] if per_channel else scale)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        return Fp8Weight(w8.contiguous(), scale)
+
+
+def fp8_quant_activations(a: torch.Tensor, input_scale=None):
+    """The activation side of W8A8 restated in PyTorch (the CPU oracle of the fp8 path): per-tensor
+    scale, static when the checkpoint gives one, else max|a| / 448."""
+    af = a.float()
+    s = input_scale.float().reshape(()) if input_scale is not None else (af.abs().max() / 448.0).clamp_min(1e-12 / 448.0)
+    return (af / s).clamp(-448.0, 448.0).to(torch.float8_e4m3fn), s
+
+
 class BlockQuantWeight:
     """A linear-layer weight kept in GGUF blocks of 32 values (Q8_0: fp16 scale + int8; Q4_0: fp16
     scale + nibbles) for the CPU backend's packed GEMM. Re-encoding a tensor that was decoded from
@@ -103,9 +145,21 @@ class CpuBackend:
         self.device = torch.device(device)
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
-        if isinstance(w, (QuantWeight, BlockQuantWeight)):
-            w = w.dequant()
-        y = ref.gemm(a, w, bias, residual, out_dtype)
+        if isinstance(w, Fp8Weight):
+            # both operands in e4m3, products summed in fp32, scales applied to the sum
+            a8, s = fp8_quant_activations(a, w.input_scale)
+            ws = w.w_scale.reshape(1, -1) if w.w_scale.numel() > 1 else w.w_scale
+            y = (a8.float() @ w.w8.float().t()) * s * ws
+            if bias is not None:
+                y = y + bias.float()
+            y = y.to(torch.bfloat16)
+            if residual is not None:
+                y = (y.float() + residual.float()).to(torch.bfloat16)
+            y = y.to(out_dtype)
+        else:
+            if isinstance(w, (QuantWeight, BlockQuantWeight)):
+                w = w.dequant()
+            y = ref.gemm(a, w, bias, residual, out_dtype)
         if out is not None:
             out.copy_(y)
             return out
@@ -203,7 +257,8 @@ class CpuNativeBackend(CpuBackend):
                 out.copy_(y)
                 return out
             return y
-        if isinstance(w, (QuantWeight, BlockQuantWeight)) or a.dtype != torch.bfloat16 or a.stride(-1) != 1:
+        if isinstance(w, (QuantWeight, BlockQuantWeight, Fp8Weight)) or a.dtype != torch.bfloat16 \
+                or a.stride(-1) != 1:
             return super().gemm(a, w, bias, residual, out, out_dtype)
         return self.n.gemm(a, w, bias, residual, out, out.dtype if out is not None else out_dtype)
 
@@ -259,6 +314,11 @@ class GpuBackend:
         # and runs W4A4 on kind::mxf4nvf4 (what NVFP4 checkpoints are calibrated for)
         self.w4a4 = os.environ.get("B200_NVFP4_ACTIVATIONS", "bf16") == "nvfp4"
 
+    def _fp8_buffer(self, T: int, K: int):
+        """Persistent scratch of the fp8 activation quantiser."""
+        from .. import ops
+        return ops.workspace(self.device, T * K, "fp8_act")[: T * K].view(torch.float8_e4m3fn).view(T, K)
+
     def _w4a4_buffers(self, T: int, K: int):
         """Persistent (packed activations, scale chunks) scratch of the activation quantiser."""
         from .. import ops
@@ -270,6 +330,21 @@ class GpuBackend:
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
         """``w`` is always a model weight here (never written by a kernel of the step), which
         lets the GEMM start fetching it before the previous kernel has finished."""
+        if isinstance(w, Fp8Weight):
+            from ..ops import quant as Q
+            N, K = w.shape
+            if a.stride(-1) != 1:
+                a = a.contiguous()
+            a8 = self._fp8_buffer(a.shape[0], K)
+            if w.input_scale is not None:
+                Q.quant_fp8(a, w.input_scale, out=a8)
+                a_scale = w.input_scale
+            else:
+                _, a_scale = Q.quant_fp8_dynamic(a, out=a8)
+            y = Q.gemm_fp8(a8, w.w8, a_scale, w.w_scale, out=out, bias=bias)
+            if residual is not None:
+                y = self.ops.add(y, residual) if out is None else out.copy_(self.ops.add(y, residual))
+            return y
         if isinstance(w, QuantWeight):
             from ..ops import quant as Q
             N, K = w.shape
@@ -306,7 +381,7 @@ class GpuBackend:
 
     def gemm_gated(self, a, w, kind=0, out=None, scratch=None):
         """act(a W_gate^T) * (a W_up^T) for an interleaved gate / up weight."""
-        if isinstance(w, QuantWeight):
+        if isinstance(w, (QuantWeight, Fp8Weight)):
             y = self.gemm(a, w, out=scratch)
             return self.ops.act_and_mul(y, kind, out, interleaved=True)
         return self.ops.gemm_gated(a, w, kind, out=out, scratch=scratch)

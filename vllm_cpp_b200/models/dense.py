@@ -197,9 +197,9 @@ class DenseModel:
     QUANT_KEYS = ("qkv", "o", "gate_up", "down", "in_proj", "out")
 
     def quantize_weights(self, method: str = "nvfp4") -> None:
-        """Replaces the linear-layer weights by NVFP4 ``QuantWeight``s (values are rounded
-        once here, on whatever device holds them, so CPU oracle and GPU see the same
-        numbers)."""
+        """Replaces the linear-layer weights by NVFP4 ``QuantWeight``s, or by ``Fp8Weight``s for
+        ``"fp8"`` (values are rounded once here, on whatever device holds them, so CPU oracle and
+        GPU see the same numbers)."""
         if method in ("q8_0", "q4_0"):
             # CPU backend: GGUF block formats, GEMMs on the packed weights
             from .backend import BlockQuantWeight
@@ -208,6 +208,17 @@ class DenseModel:
                     w = L.get(k)
                     if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 32 == 0:
                         L[k] = BlockQuantWeight.from_dense(w, method)
+            self.quantized = method
+            return
+        if method == "fp8":
+            # W8A8: e4m3 weights with per-channel scales, activations quantised per call
+            from .backend import Fp8Weight
+            self.native_layers = None
+            for L in self.layers:
+                for k in self.QUANT_KEYS:
+                    w = L.get(k)
+                    if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 16 == 0 and w.shape[0] % 8 == 0:
+                        L[k] = Fp8Weight.from_dense(w)
             self.quantized = method
             return
         if method != "nvfp4":
@@ -488,8 +499,8 @@ class DenseModel:
         if (c.post_norm or c.sandwich_norm or c.attention_bias or c.mlp_bias or c.sliding_window
                 or c.attention_chunk_size or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):
             return False
-        from .backend import QuantWeight
-        return not any(isinstance(v, QuantWeight) for L in self.layers for v in L.values())
+        from .backend import Fp8Weight, QuantWeight
+        return not any(isinstance(v, (QuantWeight, Fp8Weight)) for L in self.layers for v in L.values())
 
     def _native_weights(self):
         ws = getattr(self, "_native_w", None)

@@ -22,6 +22,7 @@ def _declare():
     _lib.declare("b200_gemm_nvfp4", [P, P, P, P, P, P, P, I, P, I, I, I, I, P, Z, P], I)
     _lib.declare("b200_nvfp4_sf_to_chunks", [P, L, I, I, P, P], I)
     _lib.declare("b200_quant_fp8", [P, L, P, F, I, P, P, L, L, I, P], I)
+    _lib.declare("b200_quant_fp8_dynamic", [P, L, P, P, L, L, I, P], I)
     _lib.declare("b200_quant_nvfp4", [P, L, P, P, P, L, I, I, I, P], I)
     _lib.declare("b200_quant_nvfp4_gated", [P, L, P, L, P, P, P, L, I, I, P], I)
     _lib.declare("b200_rmsnorm_quant_nvfp4", [P, L, P, P, F, I, P, P, P, P, L, I, I, P], I)
@@ -83,6 +84,20 @@ def quant_fp8(x, scale, out=None, norm_weight=None, eps=1e-6, gemma=False):
     check(lib().b200_quant_fp8(ptr(x), x.stride(0), ptr(norm_weight), eps, int(gemma), ptr(scale), ptr(out),
                                out.stride(0), T, H, stream_ptr()), "quant_fp8")
     return out
+
+
+def quant_fp8_dynamic(x, out=None):
+    """Per-tensor dynamic fp8: scale = max|x| / 448 taken on the device (no host read). Returns
+    (float8_e4m3fn [T, H], scale fp32 [1]); the scale lives in a per-device scratch word, valid
+    until the next call on that device (the GEMM that follows on the stream reads it)."""
+    _declare()
+    T, H = x.shape
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    scratch = workspace(x.device, 8, "fp8_dyn_scale").view(torch.float32)
+    check(lib().b200_quant_fp8_dynamic(ptr(x), x.stride(0), ptr(scratch), ptr(out), out.stride(0), T, H,
+                                       stream_ptr()), "quant_fp8_dynamic")
+    return out, scratch[1:2]
 
 
 def quant_nvfp4(x, gscale, K=None, silu_mul=False, swizzle=False, out=None):
