@@ -384,6 +384,8 @@ def run_interpreter(recipe: FusedRecipe, tensors: dict) -> dict:
     inplace = dict(recipe.inplace)
     for o in recipe.outputs:
         res[o] = tensors[inplace[o]] if o in inplace else outs[o]
+        if isinstance(res[o], tuple) and not swizzle:
+            res[o] = (res[o][0], res[o][1].view(T, K // 16))     # row-major scales, as the quantiser returns them
     return res
 
 
