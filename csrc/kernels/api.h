@@ -59,6 +59,13 @@ typedef struct B200DenseLayerWeights {
   const void* gate_up;    // [2 I, H], interleaved in blocks of 128 if gate_up_interleaved
   const void* down;       // [H, I]
   void* kv_cache;         // [num_blocks, 2, block_size, Hkv, D]
+  // fp8 != 0: qkv / o / gate_up / down are e4m3 [N, K] with one fp32 scale per output channel;
+  // the activations are quantised row by row (one scale per token) in the kernel that makes them
+  int fp8;
+  const float* qkv_scale;
+  const float* o_scale;
+  const float* gate_up_scale;
+  const float* down_scale;
 } B200DenseLayerWeights;
 
 // Shapes, step metadata (device pointers into the packed step buffer) and activation buffers.
@@ -91,6 +98,8 @@ typedef struct B200DenseStep {
   void* gemm_ws;
   unsigned long long gemm_ws_bytes;
   int first_layer;        // the residual stream starts here: resid = hidden, no add
+  void* fp8_act;          // fp8 weights: [T, max(H, Hq D, I)] bytes of quantised activations
+  void* fp8_scales;       // fp8 weights: [T] fp32 per-token scales
 } B200DenseStep;
 
 // Peer-mapped buffers of the fused tensor-parallel path (see tp_fused.cu): per rank a receive
@@ -245,6 +254,7 @@ int b200_moe_combine(const void* y, const void* pair_pos, const void* topk_w, in
 int b200_shared_gate(const void* x, int ldx, const void* w, int T, int H, void* out, cudaStream_t stream);
 // ---- norm_act.cu
 int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* out, int ldo, int T, int H, float eps, int gemma, cudaStream_t stream);
+int b200_quant_fp8_rowwise(const void* x, long ldx, void* residual, const void* norm_w, float eps, int gemma, int mode, int kind_flags, void* out, long ldo, void* scales, int T, int K, cudaStream_t stream);
 int b200_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps, cudaStream_t stream);
 int b200_act_and_mul(const void* x, int ldx, void* out, int T, int I, int kind, cudaStream_t stream);
 int b200_eltwise(const void* a, const void* b, void* out, size_t n, int kind, float scalar, cudaStream_t stream);

@@ -78,6 +78,7 @@ struct GemmParams {
   const float* scale_a;
   const float* scale_w;
   int scale_w_per_channel;
+  int scale_a_per_token;     // scale_a is [M], one per row
   int sk;                         // number of leading tiles in the stream-K region (0 = none)
   float* sk_partials;
   uint32_t* sk_flags;
@@ -777,7 +778,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int i = 0; i < 32; ++i) v[i] += f[i];
         }
         if (FP8) {
-          const float sa = *p.scale_a;
+          const float sa = p.scale_a_per_token ? (row < p.M ? p.scale_a[row] : 0.f) : *p.scale_a;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = tn * BN + c * 32 + i;
@@ -1346,7 +1347,8 @@ extern "C" int b200_gemm_fp8_pair(const void* A, int lda, const void* W, int ldw
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  p.scale_a = a_scale; p.scale_w = w_scale; p.scale_w_per_channel = w_scale_per_channel;
+  p.scale_a = a_scale; p.scale_w = w_scale; p.scale_w_per_channel = w_scale_per_channel & 1;
+  p.scale_a_per_token = (w_scale_per_channel >> 1) & 1;
   p.status = device_status_word();
   p.sk = 1;
   p.tiles_m = (M + 2 * kBM - 1) / (2 * kBM);

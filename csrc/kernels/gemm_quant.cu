@@ -46,7 +46,8 @@ struct Fp8Params {
   int M, N, K;
   bf16* out;
   int ldo;
-  const float* a_scale;      // per-tensor
+  const float* a_scale;      // per-tensor, or [M] with a_scale_per_token
+  int a_scale_per_token;
   const float* w_scale;      // per-tensor or per-channel [N]
   int w_scale_per_channel;
   const bf16* bias;
@@ -123,7 +124,6 @@ __global__ void __launch_bounds__(kQThreads, 1)
     const int quarter = warp & 3;
     uint32_t tc = 0;
     bool ok = true;
-    const float sa = *p.a_scale;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
       const int buf = tc & 1;
@@ -131,6 +131,8 @@ __global__ void __launch_bounds__(kQThreads, 1)
       if (!ok) break;
       tc_fence_after_sync();
       const int row = tm * kQM + quarter * 32 + lane;
+      // one scale for the tensor, or one per token (row) when the activations were quantised row-wise
+      const float sa = p.a_scale_per_token ? (row < p.M ? p.a_scale[row] : 0.f) : *p.a_scale;
       const uint32_t t_addr = tmem_base + buf * kQN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < kQN / 32; ++c) {
@@ -427,7 +429,8 @@ int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int
     return -3;
   Fp8Params p{};
   p.M = M; p.N = N; p.K = K; p.out = (bf16*)out; p.ldo = ldo;
-  p.a_scale = a_scale; p.w_scale = w_scale; p.w_scale_per_channel = w_scale_per_channel;
+  p.a_scale = a_scale; p.w_scale = w_scale; p.w_scale_per_channel = w_scale_per_channel & 1;
+  p.a_scale_per_token = (w_scale_per_channel >> 1) & 1;
   p.bias = (const bf16*)bias;
   p.tiles_m = (M + kQM - 1) / kQM; p.tiles_n = (N + kQN - 1) / kQN;
   const int kblocks = (K + kQKB - 1) / kQKB;

@@ -31,8 +31,8 @@ static constexpr int kConstW = 0x100;
 void b200_dense_layer_abi(int* out4) {
   out4[0] = (int)sizeof(B200DenseLayerWeights);
   out4[1] = (int)sizeof(B200DenseStep);
-  out4[2] = (int)offsetof(B200DenseLayerWeights, kv_cache);
-  out4[3] = (int)offsetof(B200DenseStep, first_layer);
+  out4[2] = (int)offsetof(B200DenseLayerWeights, down_scale);
+  out4[3] = (int)offsetof(B200DenseStep, fp8_scales);
 }
 
 // Attention half of a block: (add+)RMSNorm -> QKV GEMM -> qk-norm / RoPE / KV-cache write ->
@@ -44,16 +44,24 @@ int b200_dense_attn_half(const B200DenseLayerWeights* w, const B200DenseStep* s,
   const int T = s->T, H = s->H, D = s->D, Hq = s->Hq, Hkv = s->Hkv;
   const int qkv_w = (Hq + 2 * Hkv) * D;
   using bf16 = __nv_bfloat16;
-  if (s->first_layer) {
-    if (cudaMemcpyAsync(s->resid, s->hidden, (size_t)T * H * sizeof(bf16), cudaMemcpyDeviceToDevice, stream) !=
-        cudaSuccess)
-      return -2;
-    B200_TRY(b200_rmsnorm(s->hidden, H, nullptr, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
+  const bool fp8 = w->fp8 != 0;
+  if (fp8 && (!s->fp8_act || !s->fp8_scales || !w->qkv_scale || !w->o_scale)) return -1;
+  if (s->first_layer &&
+      cudaMemcpyAsync(s->resid, s->hidden, (size_t)T * H * sizeof(bf16), cudaMemcpyDeviceToDevice, stream) !=
+          cudaSuccess)
+    return -2;
+  void* resid_in = s->first_layer ? nullptr : s->resid;
+  if (fp8) {
+    // (add +) RMSNorm and the row-wise quantisation in one kernel; scales: per token x per channel
+    B200_TRY(b200_quant_fp8_rowwise(s->hidden, H, resid_in, w->ln1, s->eps, s->gemma, 1, 0, s->fp8_act, H,
+                                    s->fp8_scales, T, H, stream));
+    B200_TRY(b200_gemm_fp8(s->fp8_act, H, w->qkv, H, s->qkv_buf, qkv_w, (const float*)s->fp8_scales, w->qkv_scale,
+                           3, nullptr, T, qkv_w, H, stream));
   } else {
-    B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
+    B200_TRY(b200_rmsnorm(s->hidden, H, resid_in, w->ln1, s->normed, H, T, H, s->eps, s->gemma, stream));
+    B200_TRY(b200_gemm_bf16(s->normed, H, w->qkv, H, s->qkv_buf, qkv_w, 0, nullptr, nullptr, 0, T, qkv_w, H,
+                            s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
   }
-  B200_TRY(b200_gemm_bf16(s->normed, H, w->qkv, H, s->qkv_buf, qkv_w, 0, nullptr, nullptr, 0, T, qkv_w, H,
-                          s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
   B200_TRY(b200_rope_kv(s->qkv_buf, qkv_w, 0, Hq * D, (Hq + Hkv) * D, D, Hq, Hkv, D, s->rot, s->positions,
                         s->cos_sin, w->q_norm, w->k_norm, s->eps, s->gemma, s->neox, s->slot_mapping,
                         w->kv_cache, s->block_size, nullptr, T, stream));
@@ -78,8 +86,15 @@ int b200_dense_attn_half(const B200DenseLayerWeights* w, const B200DenseStep* s,
                                bt, s->max_blocks, sl, s->prefill_q_start, s->tile_req, s->tile_q0, s->num_tiles,
                                s->num_prefill_tokens, s->scale, s->softcap, s->window, 1, stream));
   }
-  B200_TRY(b200_gemm_bf16(s->attn, Hq * D, w->o, Hq * D, s->hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D,
-                          s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
+  if (fp8) {
+    B200_TRY(b200_quant_fp8_rowwise(s->attn, Hq * D, nullptr, nullptr, 0.f, 0, 0, 0, s->fp8_act, Hq * D,
+                                    s->fp8_scales, T, Hq * D, stream));
+    B200_TRY(b200_gemm_fp8(s->fp8_act, Hq * D, w->o, Hq * D, s->hidden, H, (const float*)s->fp8_scales, w->o_scale,
+                           3, nullptr, T, H, Hq * D, stream));
+  } else {
+    B200_TRY(b200_gemm_bf16(s->attn, Hq * D, w->o, Hq * D, s->hidden, H, 0, nullptr, nullptr, 0, T, H, Hq * D,
+                            s->gemm_ws, (size_t)s->gemm_ws_bytes, kConstW, stream));
+  }
   return launches;
 }
 
@@ -91,8 +106,22 @@ int b200_dense_layer(const B200DenseLayerWeights* w, const B200DenseStep* s, cud
   if (launches < 0) return launches;
   const int T = s->T, H = s->H;
   // ---- MLP block
-  B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln2, s->normed, H, T, H, s->eps, s->gemma, stream));
   const int I = s->inter;
+  if (w->fp8) {
+    if (!w->gate_up_scale || !w->down_scale) return -1;
+    B200_TRY(b200_quant_fp8_rowwise(s->hidden, H, s->resid, w->ln2, s->eps, s->gemma, 1, 0, s->fp8_act, H,
+                                    s->fp8_scales, T, H, stream));
+    B200_TRY(b200_gemm_fp8(s->fp8_act, H, w->gate_up, H, s->gate_up_buf, 2 * I, (const float*)s->fp8_scales,
+                           w->gate_up_scale, 3, nullptr, T, 2 * I, H, stream));
+    // act(gate) * up and its quantisation in one kernel
+    B200_TRY(b200_quant_fp8_rowwise(s->gate_up_buf, 2 * I, nullptr, nullptr, 0.f, 0, 2,
+                                    s->act_kind | (s->gate_up_interleaved ? 0x100 : 0), s->fp8_act, I,
+                                    s->fp8_scales, T, I, stream));
+    B200_TRY(b200_gemm_fp8(s->fp8_act, I, w->down, I, s->hidden, H, (const float*)s->fp8_scales, w->down_scale, 3,
+                           nullptr, T, H, I, stream));
+    return launches;
+  }
+  B200_TRY(b200_rmsnorm(s->hidden, H, s->resid, w->ln2, s->normed, H, T, H, s->eps, s->gemma, stream));
   if (s->gate_up_interleaved && T > 128) {
     B200_TRY(b200_gemm_bf16_gated(s->normed, H, w->gate_up, H, s->act, I, T, 2 * I, H, s->act_kind, 0, stream));
   } else {

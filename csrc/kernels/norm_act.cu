@@ -9,6 +9,7 @@
 //   embedding gather with a bounds flag in the status word         cuda_ops.cu:600
 //   gather_rows (logits-row gather before lm_head)
 #include "api.h"
+#include "quant_codec.cuh"
 #include "sm100.cuh"
 
 namespace b200 {
@@ -143,6 +144,119 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Row-wise dynamic fp8: each token row gets its own scale (max|v| / 448), written to scales[t]
+// for the GEMM's epilogue, and the producer of the row runs in the same pass:
+//   mode 0  v = x
+//   mode 1  v = RMSNorm(x (+ residual, written back)) -- the arithmetic of rmsnorm_kernel, so the
+//           normalised row has the bytes the bf16 path would hand to its GEMM
+//   mode 2  v = act(gate) * up from [gate | up] rows (kind_flags as act_and_mul_kernel takes them)
+// The row (bf16) stays in shared memory between the producer and the quantisation.
+__global__ void __launch_bounds__(256)
+    rowquant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long ldx, __nv_bfloat16* residual,
+                        const __nv_bfloat16* __restrict__ w, float eps, int gemma, int mode, int kind_flags,
+                        uint8_t* __restrict__ out, long ldo, float* __restrict__ scales, int K) {
+  __shared__ float red[32];
+  extern __shared__ uint4 row_cache[];  // K/8 vectors
+  const long t = blockIdx.x;
+  const int nv = K >> 3;
+  float amax = 0.f;
+  auto vec_amax = [&](const uint4& v) {
+    float2 f;
+    f = unpack_bf16x2(v.x); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    f = unpack_bf16x2(v.y); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    f = unpack_bf16x2(v.z); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    f = unpack_bf16x2(v.w); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+  };
+  if (mode == 1) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + t * ldx);
+    uint4* rr = residual ? reinterpret_cast<uint4*>(residual + t * (long)K) : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      uint4 v = xr[i];
+      if (rr) {
+        uint4 r = rr[i];
+        float2 a, b;
+        a = unpack_bf16x2(v.x); b = unpack_bf16x2(r.x); v.x = pack_bf16x2(a.x + b.x, a.y + b.y);
+        a = unpack_bf16x2(v.y); b = unpack_bf16x2(r.y); v.y = pack_bf16x2(a.x + b.x, a.y + b.y);
+        a = unpack_bf16x2(v.z); b = unpack_bf16x2(r.z); v.z = pack_bf16x2(a.x + b.x, a.y + b.y);
+        a = unpack_bf16x2(v.w); b = unpack_bf16x2(r.w); v.w = pack_bf16x2(a.x + b.x, a.y + b.y);
+        rr[i] = v;
+      }
+      row_cache[i] = v;
+      float2 f;
+      f = unpack_bf16x2(v.x); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(v.y); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(v.z); ss += f.x * f.x + f.y * f.y;
+      f = unpack_bf16x2(v.w); ss += f.x * f.x + f.y * f.y;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)K + eps);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    const float g = gemma ? 1.f : 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 v = row_cache[i];
+      const uint4 wv = wr[i];
+      uint4 o;
+      float2 a, b;
+      a = unpack_bf16x2(v.x); b = unpack_bf16x2(wv.x); o.x = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+      a = unpack_bf16x2(v.y); b = unpack_bf16x2(wv.y); o.y = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+      a = unpack_bf16x2(v.z); b = unpack_bf16x2(wv.z); o.z = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+      a = unpack_bf16x2(v.w); b = unpack_bf16x2(wv.w); o.w = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+      row_cache[i] = o;
+      vec_amax(o);
+    }
+  } else if (mode == 2) {
+    const int kind = kind_flags & 0xff;
+    const bool il = (kind_flags & 0x100) != 0;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const int goff = il ? ((i * 8) >> 7) * 256 + ((i * 8) & 127) : i * 8;
+      const int uoff = il ? goff + 128 : K + i * 8;
+      const uint4 gt = *reinterpret_cast<const uint4*>(x + t * ldx + goff);
+      const uint4 u = *reinterpret_cast<const uint4*>(x + t * ldx + uoff);
+      uint4 o;
+      float2 a, b;
+      a = unpack_bf16x2(gt.x); b = unpack_bf16x2(u.x); o.x = pack_bf16x2(act_fn(a.x, kind) * b.x, act_fn(a.y, kind) * b.y);
+      a = unpack_bf16x2(gt.y); b = unpack_bf16x2(u.y); o.y = pack_bf16x2(act_fn(a.x, kind) * b.x, act_fn(a.y, kind) * b.y);
+      a = unpack_bf16x2(gt.z); b = unpack_bf16x2(u.z); o.z = pack_bf16x2(act_fn(a.x, kind) * b.x, act_fn(a.y, kind) * b.y);
+      a = unpack_bf16x2(gt.w); b = unpack_bf16x2(u.w); o.w = pack_bf16x2(act_fn(a.x, kind) * b.x, act_fn(a.y, kind) * b.y);
+      row_cache[i] = o;
+      vec_amax(o);
+    }
+  } else {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + t * ldx);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 v = xr[i];
+      row_cache[i] = v;
+      vec_amax(v);
+    }
+  }
+  // block maximum (every thread re-reads only the vectors it wrote, so no barrier is needed for
+  // row_cache itself)
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  float m = (lane < nw) ? red[lane] : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float sc = fmaxf(m, 1e-12f) / 448.f;
+  const float is = 1.f / sc;
+  if (threadIdx.x == 0) scales[t] = sc;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = row_cache[i];
+    const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(wds[j]);
+      const uint32_t two = (uint32_t)float_to_e4m3(f.x * is) | ((uint32_t)float_to_e4m3(f.y * is) << 8);
+      if (j < 2) lo |= two << (16 * j); else hi |= two << (16 * (j - 2));
+    }
+    *reinterpret_cast<uint2*>(out + t * ldo + (long)i * 8) = make_uint2(lo, hi);
+  }
+}
+
 enum EwKind : int { kEwAdd = 0, kEwRelu = 1, kEwMulScalar = 2, kEwSoftcap = 3, kEwSigmoidMul = 4,
                     kEwMul = 5 };
 
@@ -256,6 +370,27 @@ int b200_rmsnorm(const void* x, int ldx, void* residual, const void* w, void* ou
   if (threads < 32) threads = 32;
   return launch_pdl(rmsnorm_kernel, dim3(T), dim3(threads), (size_t)H * 2, stream, (const bf16*)x, ldx,
                     (bf16*)residual, (const bf16*)w, (bf16*)out, ldo, H, eps, gemma) == cudaSuccess ? 0 : -2;
+}
+
+// x: mode 0 / 1 rows of K values, mode 2 rows of [gate | up] (2K values). out: fp8 [T, K] (row
+// stride ldo bytes), scales: fp32 [T]. Launched with the thread count b200_rmsnorm uses for this
+// width, so that mode 1 sums in the same order.
+int b200_quant_fp8_rowwise(const void* x, long ldx, void* residual, const void* norm_w, float eps, int gemma,
+                           int mode, int kind_flags, void* out, long ldo, void* scales, int T, int K,
+                           cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldo & 7) || K > 32768 || mode < 0 || mode > 2) return -1;
+  if (((uintptr_t)x & 15) || ((uintptr_t)out & 7) || (mode == 1 && !norm_w)) return -1;
+  if (mode == 2 && (kind_flags & 0x100) && (K & 127)) return -1;
+  int threads = K / 8 >= 256 ? 256 : ((K / 8 + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  static PerDeviceOnce attr_once;
+  if (attr_once.first())
+    cudaFuncSetAttribute(rowquant_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 2);
+  rowquant_fp8_kernel<<<T, threads, (size_t)K * 2, stream>>>((const bf16*)x, ldx, (bf16*)residual, (const bf16*)norm_w,
+                                                           eps, gemma, mode, kind_flags, (uint8_t*)out, ldo,
+                                                           (float*)scales, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 int b200_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

@@ -85,4 +85,4 @@ def test_native_layer_binding_matches_the_c_structs():
     out = (ctypes.c_int * 4)()
     _lib.lib().b200_dense_layer_abi(out)
     assert list(out) == [ctypes.sizeof(DenseLayerWeights), ctypes.sizeof(DenseStep),
-                         DenseLayerWeights.kv_cache.offset, DenseStep.first_layer.offset]
+                         DenseLayerWeights.down_scale.offset, DenseStep.fp8_scales.offset]

@@ -66,7 +66,8 @@ def test_fp8_weight_round_trip_and_cpu_model():
     exact = a.float() @ w.t()
     assert ((y.float() - exact).norm() / exact.norm()).item() < 0.06
     a8, s = fp8_quant_activations(a)
-    assert abs(a8.float().abs().max().item() - 448.0) < 1e-3 and s > 0
+    assert s.shape == (5, 1) and (s > 0).all()                   # one scale per token
+    assert (a8.float().abs().amax(-1) - 448.0).abs().max().item() < 1e-3
     # static activation scale from a checkpoint
     q.input_scale = torch.tensor([0.02])
     y2 = CpuBackend("cpu").gemm(a, q)
@@ -97,6 +98,25 @@ def test_fp8_dynamic_quantiser_and_backend_gemm():
     big = torch.randn(50, 512, device="cuda").to(torch.bfloat16)
     v8, sv = Q.quant_fp8_dynamic(big[:, 256:])
     assert torch.allclose(sv, (big[:, 256:].float().abs().max() / 448.0).reshape(1), rtol=1e-6)
+    # per-token scales, alone and with the producer of the row in the same kernel
+    x8, sc = Q.quant_fp8_rowwise(x)
+    want_s = x.float().abs().amax(-1) / 448.0
+    assert torch.allclose(sc, want_s, rtol=1e-6)
+    want = (x.float() / want_s[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    assert (x8.view(torch.uint8) == want.view(torch.uint8)).float().mean().item() > 0.995
+    wn = (torch.rand(1024, device="cuda") + 0.5).to(torch.bfloat16)
+    res = torch.randn(300, 1024, device="cuda").to(torch.bfloat16)
+    r1, r2 = res.clone(), res.clone()
+    normed = ops.rmsnorm(x, wn, 1e-5, residual=r1)
+    n8, ns = Q.quant_fp8_rowwise(x, norm_weight=wn, eps=1e-5, residual=r2)
+    p8, ps = Q.quant_fp8_rowwise(normed)
+    assert torch.equal(r1, r2) and torch.equal(ns, ps) and torch.equal(n8.view(torch.uint8), p8.view(torch.uint8))
+    for il in (False, True):
+        gu = torch.randn(70, 2 * 512, device="cuda").to(torch.bfloat16)
+        y = ops.act_and_mul(gu, 0, interleaved=il)
+        a8_, as_ = Q.quant_fp8_rowwise(gu, act_kind=0, interleaved=il)
+        b8_, bs_ = Q.quant_fp8_rowwise(y)
+        assert torch.equal(as_, bs_) and torch.equal(a8_.view(torch.uint8), b8_.view(torch.uint8))
     # the backend's W8A8 linear against the CPU restatement, dynamic and static activation scales
     w = torch.randn(520, 1024) * 0.03
     q = Fp8Weight.from_dense(w)

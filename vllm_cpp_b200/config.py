@@ -260,8 +260,16 @@ def load_model_config(model_dir: str) -> ModelConfig:
 
 # ------------------------------------------------------------------ named synthetic shapes
 def synthetic_config(name: str) -> ModelConfig:
-    """Architectures of the benchmark configurations (random-init weights)."""
+    """Architectures of the benchmark configurations (random-init weights). A ``+fp8`` or ``+nvfp4``
+    suffix selects that weight quantisation (``llama-3.1-8b+fp8``), ``+bf16`` none."""
     n = name.lower()
+    if "+" in n:
+        base, q = n.rsplit("+", 1)
+        if q not in ("fp8", "nvfp4", "bf16"):
+            raise ValueError(f"unknown quantisation suffix '+{q}'")
+        cfg = synthetic_config(base)
+        cfg.quant = None if q == "bf16" else q
+        return cfg
     if n in ("qwen3-0.6b", "qwen3_0_6b"):
         return ModelConfig(architecture="Qwen3ForCausalLM", vocab_size=151936, hidden_size=1024,
                            intermediate_size=3072, num_layers=28, num_heads=16, num_kv_heads=8,

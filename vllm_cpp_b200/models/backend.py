@@ -95,11 +95,15 @@ class Fp8Weight:
 
 
 def fp8_quant_activations(a: torch.Tensor, input_scale=None):
-    """The activation side of W8A8 restated in PyTorch (the CPU oracle of the fp8 path): per-tensor
-    scale, static when the checkpoint gives one, else max|a| / 448."""
+    """The activation side of W8A8 restated in PyTorch (the CPU oracle of the fp8 path): the
+    checkpoint's static per-tensor scale when it gives one, else one scale per token,
+    max|row| / 448. Returns (e4m3 values, scale broadcastable over [T, N])."""
     af = a.float()
-    s = input_scale.float().reshape(()) if input_scale is not None else (af.abs().max() / 448.0).clamp_min(1e-12 / 448.0)
-    return (af / s).clamp(-448.0, 448.0).to(torch.float8_e4m3fn), s
+    if input_scale is not None:
+        s = input_scale.float().reshape(())
+    else:
+        s = (af.abs().amax(-1, keepdim=True) / 448.0).clamp_min(1e-12 / 448.0)
+    return (af * (1.0 / s)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn), s
 
 
 class BlockQuantWeight:
@@ -340,7 +344,10 @@ class GpuBackend:
                 Q.quant_fp8(a, w.input_scale, out=a8)
                 a_scale = w.input_scale
             else:
-                _, a_scale = Q.quant_fp8_dynamic(a, out=a8)
+                from .. import ops
+                scales = ops.workspace(self.device, a.shape[0] * 4, "fp8_row_scales").view(torch.float32)[: a.shape[0]]
+                Q.quant_fp8_rowwise(a, out=a8, scales=scales)
+                a_scale = scales
             y = Q.gemm_fp8(a8, w.w8, a_scale, w.w_scale, out=out, bias=bias)
             if residual is not None:
                 y = self.ops.add(y, residual) if out is None else out.copy_(self.ops.add(y, residual))

@@ -500,7 +500,13 @@ class DenseModel:
                 or c.attention_chunk_size or c.residual_multiplier != 1.0 or len(set(self.layer_group)) != 1):
             return False
         from .backend import Fp8Weight, QuantWeight
-        return not any(isinstance(v, (QuantWeight, Fp8Weight)) for L in self.layers for v in L.values())
+        if any(isinstance(v, QuantWeight) for L in self.layers for v in L.values()):
+            return False
+        # fp8: the native block takes all four projections in e4m3 with per-channel scales and
+        # quantises the activations per token; anything else (static scales, a mix) keeps the per-op path
+        n8 = [sum(isinstance(L.get(k), Fp8Weight) and L[k].input_scale is None and L[k].w_scale.numel() > 1
+                  for k in ("qkv", "o", "gate_up", "down")) for L in self.layers]
+        return all(n == 0 for n in n8) or all(n == 4 for n in n8)
 
     def _native_weights(self):
         ws = getattr(self, "_native_w", None)
@@ -515,6 +521,10 @@ class DenseModel:
                 w.k_norm = L["k_norm"].data_ptr() if L.get("k_norm") is not None else None
                 w.gate_up, w.down = L["gate_up"].data_ptr(), L["down"].data_ptr()
                 w.kv_cache = self.kv_caches[l].data_ptr()
+                if hasattr(L["qkv"], "w8"):
+                    w.fp8 = 1
+                    w.qkv_scale, w.o_scale = L["qkv"].w_scale.data_ptr(), L["o"].w_scale.data_ptr()
+                    w.gate_up_scale, w.down_scale = L["gate_up"].w_scale.data_ptr(), L["down"].w_scale.data_ptr()
                 ws.append(w)
             self._native_w = ws
         return ws
@@ -558,6 +568,10 @@ class DenseModel:
         s.qkv_buf, s.attn, s.gate_up_buf, s.act = qkv.data_ptr(), attn.data_ptr(), gate_up.data_ptr(), act.data_ptr()
         ws = ops.workspace(self.device, ops.GEMM_WS_BYTES)
         s.gemm_ws, s.gemm_ws_bytes = ws.data_ptr(), ws.numel()
+        if hasattr(self.layers[0]["qkv"], "w8"):
+            widest = max(c.hidden_size, self.hq * self.D, self.inter)
+            s.fp8_act = ops.workspace(self.device, T * widest, "fp8_act").data_ptr()
+            s.fp8_scales = ops.workspace(self.device, T * 4, "fp8_row_scales").data_ptr()
         return s
 
     def _run_native_layers(self, ctx, T, hidden, resid, normed, qkv, attn, gate_up, act, act_kind) -> bool:

@@ -12,7 +12,8 @@ P, I, F = C.c_void_p, C.c_int, C.c_float
 
 class DenseLayerWeights(C.Structure):
     _fields_ = [("ln1", P), ("qkv", P), ("q_norm", P), ("k_norm", P), ("o", P), ("ln2", P), ("gate_up", P),
-                ("down", P), ("kv_cache", P)]
+                ("down", P), ("kv_cache", P),
+                ("fp8", I), ("qkv_scale", P), ("o_scale", P), ("gate_up_scale", P), ("down_scale", P)]
 
 
 class DenseStep(C.Structure):
@@ -25,7 +26,8 @@ class DenseStep(C.Structure):
                 ("num_prefills", I), ("num_tiles", I), ("num_prefill_tokens", I),
                 ("prefill_q_start", P), ("tile_req", P), ("tile_q0", P),
                 ("hidden", P), ("resid", P), ("normed", P), ("qkv_buf", P), ("attn", P), ("gate_up_buf", P),
-                ("act", P), ("gemm_ws", P), ("gemm_ws_bytes", C.c_ulonglong), ("first_layer", I)]
+                ("act", P), ("gemm_ws", P), ("gemm_ws_bytes", C.c_ulonglong), ("first_layer", I),
+                ("fp8_act", P), ("fp8_scales", P)]
 
 
 _declared = False

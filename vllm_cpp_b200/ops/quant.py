@@ -23,6 +23,7 @@ def _declare():
     _lib.declare("b200_nvfp4_sf_to_chunks", [P, L, I, I, P, P], I)
     _lib.declare("b200_quant_fp8", [P, L, P, F, I, P, P, L, L, I, P], I)
     _lib.declare("b200_quant_fp8_dynamic", [P, L, P, P, L, L, I, P], I)
+    _lib.declare("b200_quant_fp8_rowwise", [P, L, P, P, F, I, I, I, P, L, P, I, I, P], I)
     _lib.declare("b200_quant_nvfp4", [P, L, P, P, P, L, I, I, I, P], I)
     _lib.declare("b200_quant_nvfp4_gated", [P, L, P, L, P, P, P, L, I, I, P], I)
     _lib.declare("b200_rmsnorm_quant_nvfp4", [P, L, P, P, F, I, P, P, P, P, L, I, I, P], I)
@@ -31,14 +32,17 @@ def _declare():
 
 
 def gemm_fp8(a8, w8, a_scale, w_scale, out=None, bias=None):
-    """a8 [M, K], w8 [N, K] float8_e4m3fn; a_scale fp32 [1]; w_scale fp32 [1] or [N]."""
+    """a8 [M, K], w8 [N, K] float8_e4m3fn; a_scale fp32 [1] (per tensor) or [M] (per token, M > 1);
+    w_scale fp32 [1] or [N]."""
     _declare()
     M, K = a8.shape
     N = w8.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a8.device)
+    assert a_scale.numel() in (1, M) and w_scale.numel() in (1, N)
+    flags = int(w_scale.numel() > 1) | (2 if a_scale.numel() == M else 0)     # M == 1: either reading is the same
     check(lib().b200_gemm_fp8(ptr(a8), a8.stride(0), ptr(w8), w8.stride(0), ptr(out), out.stride(0),
-                              ptr(a_scale), ptr(w_scale), int(w_scale.numel() > 1), ptr(bias), M, N, K,
+                              ptr(a_scale), ptr(w_scale), flags, ptr(bias), M, N, K,
                               stream_ptr()), "gemm_fp8")
     return out
 
@@ -84,6 +88,27 @@ def quant_fp8(x, scale, out=None, norm_weight=None, eps=1e-6, gemma=False):
     check(lib().b200_quant_fp8(ptr(x), x.stride(0), ptr(norm_weight), eps, int(gemma), ptr(scale), ptr(out),
                                out.stride(0), T, H, stream_ptr()), "quant_fp8")
     return out
+
+
+def quant_fp8_rowwise(x, out=None, scales=None, norm_weight=None, eps=1e-6, gemma=False, residual=None,
+                      act_kind=None, interleaved=False):
+    """Per-token dynamic fp8: every row gets the scale max|row| / 448. The producer of the row can
+    run in the same kernel: RMSNorm (``norm_weight``; with ``residual`` the sum is written back to
+    it first), or ``act(gate) * up`` over ``[gate | up]`` rows (``act_kind``). Returns
+    (float8_e4m3fn [T, K], scales fp32 [T])."""
+    _declare()
+    T = x.shape[0]
+    mode = 1 if norm_weight is not None else (2 if act_kind is not None else 0)
+    K = x.shape[1] // 2 if mode == 2 else x.shape[1]
+    if out is None:
+        out = torch.empty((T, K), dtype=torch.float8_e4m3fn, device=x.device)
+    if scales is None:
+        scales = torch.empty(T, dtype=torch.float32, device=x.device)
+    flags = (int(act_kind) | (0x100 if interleaved else 0)) if mode == 2 else 0
+    check(lib().b200_quant_fp8_rowwise(ptr(x), x.stride(0), ptr(residual), ptr(norm_weight), eps, int(gemma), mode,
+                                       flags, ptr(out), out.stride(0), ptr(scales), T, K, stream_ptr()),
+          "quant_fp8_rowwise")
+    return out, scales
 
 
 def quant_fp8_dynamic(x, out=None):
