@@ -761,6 +761,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
+      float fp8_sa = 1.f, fp8_sw = 1.f;
+      if (FP8) {
+        fp8_sa = p.scale_a_per_token ? (row < p.M ? __ldg(p.scale_a + row) : 0.f) : __ldg(p.scale_a);
+        if (!p.scale_w_per_channel) fp8_sw = __ldg(p.scale_w);
+      }
       // accumulator columns [c * 32, c * 32 + 32) of this thread's row, stream-K partials added
       auto load_chunk = [&](int c, float (&v)[32]) {
         uint32_t r[32];
@@ -778,12 +783,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int i = 0; i < 32; ++i) v[i] += f[i];
         }
         if (FP8) {
-          const float sa = p.scale_a_per_token ? (row < p.M ? p.scale_a[row] : 0.f) : *p.scale_a;
+          // scales fetched as vectors ahead of their use: scalar loads between the stores of the
+          // previous chunk would each wait out their own latency (one warp per scheduler here)
+          const int col = tn * BN + c * 32;
+          if (p.scale_w_per_channel) {
+            float4 sw[8];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = tn * BN + c * 32 + i;
-            const float sw = p.scale_w_per_channel ? (col < p.N ? p.scale_w[col] : 0.f) : *p.scale_w;
-            v[i] *= sa * sw;
+            for (int i = 0; i < 8; ++i)
+              sw[i] = col + i * 4 < p.N ? __ldg(reinterpret_cast<const float4*>(p.scale_w + col) + i)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i * 4 + 0] *= fp8_sa * sw[i].x; v[i * 4 + 1] *= fp8_sa * sw[i].y;
+              v[i * 4 + 2] *= fp8_sa * sw[i].z; v[i * 4 + 3] *= fp8_sa * sw[i].w;
+            }
+          } else {
+            const float s1 = fp8_sa * fp8_sw;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= s1;
           }
         }
       };

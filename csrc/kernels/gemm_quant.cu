@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(kQThreads, 1)
     const int quarter = warp & 3;
     uint32_t tc = 0;
     bool ok = true;
+    const float sw0 = p.w_scale_per_channel ? 0.f : __ldg(p.w_scale);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
       const int buf = tc & 1;
@@ -142,14 +143,21 @@ __global__ void __launch_bounds__(kQThreads, 1)
         const int col0 = tn * kQN + c * 32;
         if (row < p.M && col0 < p.N) {
           bf16* o = p.out + (size_t)row * p.ldo + col0;
+          // the chunk's channel scales as vectors, fetched before the first store
+          float4 swv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            swv[i] = !p.w_scale_per_channel ? make_float4(sw0, sw0, sw0, sw0)
+                     : col0 + i * 4 < p.N   ? __ldg(reinterpret_cast<const float4*>(p.w_scale + col0) + i)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* swf = reinterpret_cast<const float*>(swv);
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             if (col0 + i < p.N) {
               float v[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
-                const float sw = p.w_scale_per_channel ? p.w_scale[col0 + i + e] : p.w_scale[0];
-                v[e] = __uint_as_float(r[i + e]) * sa * sw;
+                v[e] = __uint_as_float(r[i + e]) * sa * swf[i + e];
                 if (p.bias) v[e] += __bfloat162float(p.bias[col0 + i + e]);
               }
               uint4 w;

@@ -139,8 +139,14 @@ def cmd_quant_gemm_bench(a) -> int:
             sf_chunks = quant.nvfp4_sf_chunks(sf, 256)
             g_a = (448.0 * 6.0 / x.float().abs().max()).reshape(1)
             xq, xsf = quant.quant_nvfp4(x, g_a, swizzle=True)
+            w_ch = torch.ones(N, device=dev)
+            x8r, xs = quant.quant_fp8_rowwise(x)
             arms = {"bf16": lambda: ops.gemm(x, wb),
-                    "fp8": lambda: quant.gemm_fp8(x8, w8, one, one)}
+                    "fp8": lambda: quant.gemm_fp8(x8, w8, one, one),
+                    # W8A8 as the models run it: one scale per token and per output channel, the
+                    # row-wise quantiser in front
+                    "fp8+quant": lambda: (quant.quant_fp8_rowwise(x, out=x8r, scales=xs),
+                                          quant.gemm_fp8(x8r, w8, xs, w_ch))}
             if M <= 128:
                 arms["w4a16"] = lambda: quant.gemm_w4a16(x, packed, sf, g)
             if K % 256 == 0:
@@ -161,7 +167,7 @@ def cmd_quant_gemm_bench(a) -> int:
                     e1.record()
                     torch.cuda.synchronize()
                     best = min(best, e0.elapsed_time(e1))
-                wbytes = {"bf16": 2.0, "fp8": 1.0}.get(arm, 0.5 + 1 / 16) * N * K
+                wbytes = {"bf16": 2.0, "fp8": 1.0, "fp8+quant": 1.0}.get(arm, 0.5 + 1 / 16) * N * K
                 rows.append({"proj": name, "M": M, "N": N, "K": K, "arm": arm, "ms": round(best, 4),
                              "tflops": round(2.0 * M * N * K / best / 1e9, 1),
                              "weight_gbs": round(wbytes / best / 1e6, 1)})
