@@ -126,8 +126,8 @@ def small_case(name: str):
         from . import quant as Q
         a8 = torch.randn(4096, 4096, device=dev).to(torch.float8_e4m3fn)
         w8 = (torch.randn(6144, 4096, device=dev) * 0.05).to(torch.float8_e4m3fn)
-        sa = torch.ones(1, device=dev)
-        sw = torch.ones(1, device=dev)
+        sa = torch.ones(4096, device=dev)      # one scale per token and per output channel, as the
+        sw = torch.ones(6144, device=dev)      # W8A8 linear layers run it
         fn = lambda: Q.gemm_fp8(a8, w8, sa, sw)
     elif name == "gemm_w4a16_small":
         from . import quant as Q
