@@ -221,6 +221,7 @@ int b200_gemm_bf16_batched(const void* A, int lda, int a_batch_cols, const void*
 // ---- gemm_quant.cu
 int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int ldo, const float* a_scale, const float* w_scale, int w_scale_per_channel, const void* bias, int M, int N, int K, cudaStream_t stream);
 int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, void* out, long N, int K, cudaStream_t stream);
+int b200_fp8_init_device();
 int b200_quant_fp8_dynamic(const void* x, long ldx, void* scratch, void* out, long ldo, long T, int H, cudaStream_t stream);
 int b200_quant_fp8(const void* x, long ldx, const void* norm_w, float eps, int gemma, const float* scale, void* out, long ldo, long T, int H, cudaStream_t stream);
 int b200_quant_nvfp4_gated(const void* x, long ldx, const void* gate, long ldg, const float* gscale, void* out, void* sf, long T, int K, int swizzle, cudaStream_t stream);

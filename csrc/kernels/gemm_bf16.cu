@@ -1795,8 +1795,10 @@ extern "C" int b200_gemm_bf16_smallm_static(const void* A, int lda, const void* 
 
 // Per-device set-up of everything the launchers would otherwise allocate on first use: the
 // stream-K scratch. Call it once per device before the first capture; 0 on success.
+extern "C" int b200_fp8_init_device();
 extern "C" int b200_init_device() {
   float* p = nullptr;
   uint32_t* f = nullptr;
-  return streamk_scratch(nullptr, &p, &f) ? 0 : -2;
+  if (!streamk_scratch(nullptr, &p, &f)) return -2;
+  return b200_fp8_init_device();
 }

@@ -52,6 +52,8 @@ struct Fp8Params {
   int w_scale_per_channel;
   const bf16* bias;
   int tiles_m, tiles_n, stages;
+  int splits, kb_per_split;  // split-K: work item w = tile * splits + split; partial sums to `partials`
+  float* partials;           // [splits][M][N] fp32 (raw accumulators, scales applied by the reduce)
   int* status;
 };
 
@@ -64,8 +66,8 @@ __global__ void __launch_bounds__(kQThreads, 1)
   const int stages = p.stages;
   QBars* bars = reinterpret_cast<QBars*>(smem + (size_t)stages * kStage);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int kblocks = (p.K + kQKB - 1) / kQKB;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;     // work items: (tile, K split)
+  const int kblocks_total = (p.K + kQKB - 1) / kQKB;
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&bars->acc_full[b], 1); mbar_init(&bars->acc_empty[b], 4); }
@@ -81,9 +83,11 @@ __global__ void __launch_bounds__(kQThreads, 1)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
+        const int t = w / p.splits, sp = w % p.splits;
         const int tm = t % p.tiles_m, tn = t / p.tiles_m;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int kb0 = sp * p.kb_per_split, kb1 = min(kblocks_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % stages;
           if (!mbar_wait(&bars->empty[s], ((it / stages) & 1) ^ 1, p.status)) { ok = false; break; }
           uint8_t* a_dst = smem + (size_t)s * kStage;
@@ -99,12 +103,14 @@ __global__ void __launch_bounds__(kQThreads, 1)
       constexpr uint32_t idesc = umma_idesc_e4m3(kQM, kQN);
       uint32_t it = 0, tc = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tc) {
         const int buf = tc & 1;
         if (!mbar_wait(&bars->acc_empty[buf], ((tc >> 1) & 1) ^ 1, p.status)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * kQN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int sp = w % p.splits;
+        const int kb0 = sp * p.kb_per_split, kb1 = min(kblocks_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % stages;
           if (!mbar_wait(&bars->full[s], (it / stages) & 1, p.status)) { ok = false; break; }
           tc_fence_after_sync();
@@ -113,7 +119,7 @@ __global__ void __launch_bounds__(kQThreads, 1)
           const uint64_t bdesc = umma_desc_k_sw128(a_addr + kABytes, 1024);
 #pragma unroll
           for (int k = 0; k < kQKB / 32; ++k)   // 32 fp8 values = 32 bytes per instruction
-            umma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+            umma_f8f6f4_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, kb != kb0 || k != 0);
           umma_commit(&bars->empty[s]);
         }
         if (ok) umma_commit(&bars->acc_full[buf]);
@@ -125,7 +131,8 @@ __global__ void __launch_bounds__(kQThreads, 1)
     uint32_t tc = 0;
     bool ok = true;
     const float sw0 = p.w_scale_per_channel ? 0.f : __ldg(p.w_scale);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tc) {
+    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tc) {
+      const int t = w / p.splits, sp = w % p.splits;
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
       const int buf = tc & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_full[buf], (tc >> 1) & 1, p.status));
@@ -141,7 +148,17 @@ __global__ void __launch_bounds__(kQThreads, 1)
         tmem_ld_32x32b_x32(t_addr + c * 32, r);
         tmem_ld_wait();
         const int col0 = tn * kQN + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (p.splits > 1) {
+          // raw partial sums; the reduce kernel adds the splits and applies scales and bias
+          if (row < p.M && col0 < p.N) {
+            float* o = p.partials + ((size_t)sp * p.M + row) * p.N + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              if (col0 + i < p.N)
+                *reinterpret_cast<float4*>(o + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                                                __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+          }
+        } else if (row < p.M && col0 < p.N) {
           bf16* o = p.out + (size_t)row * p.ldo + col0;
           // the chunk's channel scales as vectors, fetched before the first store
           float4 swv[8];
@@ -411,6 +428,55 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// out = (sum over splits of partials) * a_scale * w_scale (+ bias), four columns per thread.
+__global__ void __launch_bounds__(256)
+    fp8_splitk_reduce_kernel(const float* __restrict__ partials, int splits, int M, int N,
+                             const float* __restrict__ a_scale, int a_per_token, const float* __restrict__ w_scale,
+                             int w_per_channel, const bf16* __restrict__ bias, bf16* __restrict__ out, int ldo) {
+  const int nq = N >> 2;
+  const size_t total = (size_t)M * nq;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / nq), col = (int)(i % nq) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < splits; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(partials + ((size_t)sp * M + row) * N + col));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const float sa = a_per_token ? a_scale[row] : a_scale[0];
+    float4 sw = w_per_channel ? *reinterpret_cast<const float4*>(w_scale + col)
+                              : make_float4(w_scale[0], w_scale[0], w_scale[0], w_scale[0]);
+    acc.x *= sa * sw.x; acc.y *= sa * sw.y; acc.z *= sa * sw.z; acc.w *= sa * sw.w;
+    if (bias) {
+      const uint2 b = *reinterpret_cast<const uint2*>(bias + col);
+      const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+      acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+    }
+    *reinterpret_cast<uint2*>(out + (size_t)row * ldo + col) =
+        make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+  }
+}
+
+// Split-K scratch of the current device: one 128 x 128 fp32 partial per SM (a split plan never has
+// more work items than SMs). Allocated by b200_init_device() or by a first use outside a capture.
+static float* fp8_splitk_scratch(cudaStream_t stream) {
+  static std::mutex mu;
+  static float* g_part[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!g_part[dev]) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+    float* pp = nullptr;
+    if (cudaMalloc(&pp, (size_t)b200_num_sms() * kQM * kQN * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    g_part[dev] = pp;
+  }
+  return g_part[dev];
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -444,15 +510,48 @@ int b200_gemm_fp8(const void* A, int lda, const void* W, int ldw, void* out, int
   const int kblocks = (K + kQKB - 1) / kQKB;
   p.stages = kblocks + 1 < 6 ? (kblocks + 1 < 2 ? 2 : kblocks + 1) : 6;
   p.status = device_status_word();
+  // few tiles and a long K (decode batches against the down projection): split K over the idle
+  // SMs, at least four k-blocks per split, partial sums through the per-device scratch
+  p.splits = 1;
+  p.kb_per_split = kblocks;
+  {
+    const int tiles0 = p.tiles_m * p.tiles_n, sms = b200_num_sms();
+    int splits = sms / tiles0;
+    if (splits > kblocks / 4) splits = kblocks / 4;
+    if (splits > 16) splits = 16;
+    if (splits >= 2 && !(N & 3) && !(ldo & 3)) {
+      float* scratch = fp8_splitk_scratch(stream);
+      if (scratch) {
+        p.kb_per_split = (kblocks + splits - 1) / splits;
+        p.splits = (kblocks + p.kb_per_split - 1) / p.kb_per_split;
+        p.partials = scratch;
+        p.stages = p.kb_per_split + 1 < 6 ? (p.kb_per_split + 1 < 2 ? 2 : p.kb_per_split + 1) : 6;
+      }
+    }
+  }
   const size_t smem = (size_t)p.stages * (kQM * kQKB + kQN * kQKB) + 1024 + sizeof(QBars);
   static PerDeviceOnce attr_once;
   if (attr_once.first()) {
     cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 6 * 32768 + 2048 + (int)sizeof(QBars));
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.splits;
   const int grid = tiles < b200_num_sms() ? tiles : b200_num_sms();
   gemm_fp8_kernel<<<grid, kQThreads, smem, stream>>>(tmA, tmB, p);
+  if (cudaGetLastError() != cudaSuccess) return -2;
+  if (p.splits > 1) {
+    const size_t total = (size_t)M * (N / 4);
+    long blocks = (long)((total + 255) / 256);
+    if (blocks > (long)b200_num_sms() * 8) blocks = (long)b200_num_sms() * 8;
+    fp8_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p.partials, p.splits, M, N, a_scale,
+                                                                   p.a_scale_per_token, w_scale, p.w_scale_per_channel,
+                                                                   (const bf16*)bias, (bf16*)out, ldo);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int b200_fp8_init_device() {
+  if (b200_num_sms() <= 0) return -2;
+  return fp8_splitk_scratch(nullptr) ? 0 : -2;
 }
 
 int b200_nvfp4_dequant(const void* packed, const void* sf, const float* gscale, void* out, long N, int K,

@@ -33,6 +33,28 @@ def test_gemm_fp8(M, N, K, per_channel):
     assert _rel(out, exp) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (200, 1024, 2048), (256, 6144, 4096), (1280, 1024, 1024),
+                                   (9, 520, 1040)])
+def test_gemm_fp8_per_token_scales_and_split_k(M, N, K):
+    """One activation scale per row and one weight scale per channel; the small-batch shapes take
+    the split-K plan (partial sums through the per-device scratch, scales applied by the reduce)."""
+    torch.manual_seed(5)
+    a = torch.randn(M, K, device=DEV) * (torch.rand(M, 1, device=DEV) * 4 + 0.1)
+    w = torch.randn(N, K, device=DEV) * 0.1
+    sa = (a.abs().amax(1) / 448).float().contiguous()
+    sw = (w.abs().amax(1) / 448).float().contiguous()
+    a8 = (a / sa[:, None]).to(torch.float8_e4m3fn)
+    w8 = (w / sw[:, None]).to(torch.float8_e4m3fn)
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    exp = (a8.float() @ w8.float().t()) * sa[:, None] * sw[None, :] + bias.float()
+    for _ in range(2):                               # the scratch is reused by the next call
+        out = Q.gemm_fp8(a8, w8, sa, sw, bias=bias)
+        assert ops.read_status() == 0
+        assert _rel(out, exp) < 1e-2
+    out2 = Q.gemm_fp8(a8, w8, sa, sw)
+    assert _rel(out2, exp - bias.float()) < 1e-2
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 256, 128), (64, 4096, 4096), (256, 1024, 14336), (33, 520, 512),
                                    (700, 1024, 1024)])
 def test_nvfp4_weights(M, N, K):
