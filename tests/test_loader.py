@@ -86,3 +86,41 @@ def test_native_layer_binding_matches_the_c_structs():
     _lib.lib().b200_dense_layer_abi(out)
     assert list(out) == [ctypes.sizeof(DenseLayerWeights), ctypes.sizeof(DenseStep),
                          DenseLayerWeights.down_scale.offset, DenseStep.fp8_scales.offset]
+
+
+def test_fp8_checkpoint_loads_into_w8a8_layers(tmp_path):
+    """A checkpoint whose projections are e4m3 with per-tensor scales (ModelOpt / compressed-tensors
+    fp8 layout) loads into Fp8Weight layers holding the checkpoint's own codes, and generates."""
+    import json
+    from vllm_cpp_b200.loader.safetensors import SafetensorsFile, save_file
+    from vllm_cpp_b200.models.backend import Fp8Weight
+    cfg = synthetic_config("tiny-dense")
+    d = loader.write_synthetic_checkpoint(str(tmp_path / "ckpt"), cfg, seed=5)
+    f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+    tensors, codes = {}, {}
+    for k in f.keys():
+        t = f.get(k).clone()
+        if k.endswith("_proj.weight"):
+            s = (t.float().abs().max() / 448.0).reshape(1)
+            q = (t.float() / s).to(torch.float8_e4m3fn)
+            tensors[k], tensors[k[:-len(".weight")] + ".weight_scale"] = q, s
+            codes[k] = q
+        else:
+            tensors[k] = t
+    f.close()
+    save_file(tensors, os.path.join(d, "model.safetensors"), {"format": "pt"})
+    with open(os.path.join(d, "config.json")) as fh:
+        hf = json.load(fh)
+    hf["quantization_config"] = {"quant_method": "fp8", "activation_scheme": "dynamic"}
+    with open(os.path.join(d, "config.json"), "w") as fh:
+        json.dump(hf, fh)
+    llm = LLM(EngineArgs(model=d, device="cpu", block_size=16, num_blocks=64, max_model_len=256,
+                         max_num_seqs=4, max_num_batched_tokens=128))
+    down = llm.model.layers[0]["down"]
+    assert isinstance(down, Fp8Weight)
+    c = codes["model.layers.0.mlp.down_proj.weight"].float()
+    ratio = torch.where(c == 0, torch.ones_like(c), down.w8.float() / c)
+    assert torch.equal(ratio, ratio.amax(1, keepdim=True).expand_as(ratio))      # the same codes, row by row
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    outs = llm.generate(["The quick brown fox"], sp)
+    assert len(outs[0].outputs[0].token_ids) == 5

@@ -147,3 +147,27 @@ def test_fp8_gpu_model_matches_fp8_cpu_model():
     assert [a[0] for a in gpu] == [a[0] for a in cpu]
     hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(gpu, cpu))
     assert hit / sum(len(a) for a in gpu) > 0.7
+
+
+def test_fp8_requantisation_recovers_checkpoint_codes():
+    """A per-tensor-scaled e4m3 checkpoint expanded to bf16 (what the loader hands the models) and
+    re-encoded per channel gives back the checkpoint's codes times a power of two per row: no second
+    rounding. Weights of other origin keep the plain max / 448 scale."""
+    from vllm_cpp_b200.loader import dequant_fp8
+    from vllm_cpp_b200.models.backend import Fp8Weight
+    torch.manual_seed(3)
+    w = torch.randn(96, 256) * torch.rand(96, 1)            # rows with different maxima
+    s = w.abs().max() / 448.0
+    codes = (w / s).to(torch.float8_e4m3fn)
+    expanded = dequant_fp8(codes, s.reshape(1))             # bf16
+    q = Fp8Weight.from_dense(expanded)
+    ratio = q.w8.float() / codes.float()
+    ratio = torch.where(codes.float() == 0, torch.ones_like(ratio), ratio)
+    per_row = ratio.amax(1, keepdim=True)
+    assert torch.equal(ratio, per_row.expand_as(ratio))                              # one factor per row
+    assert torch.equal(torch.log2(per_row), torch.log2(per_row).round())             # a power of two
+    assert (q.dequant().float() - expanded.float()).abs().max() <= expanded.float().abs().max() * 2 ** -7
+    # not from a grid: the plain scale
+    dense = torch.randn(32, 256).to(torch.bfloat16)
+    q2 = Fp8Weight.from_dense(dense)
+    assert torch.allclose(q2.w_scale, dense.float().abs().amax(1) / 448.0)

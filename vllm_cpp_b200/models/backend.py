@@ -86,10 +86,34 @@ class Fp8Weight:
         return (self.w8.float() * s).to(torch.bfloat16)
 
     @staticmethod
+    def _grid_scales(wf: torch.Tensor, amax: torch.Tensor, scale: torch.Tensor):
+        """Rows that were decoded from e4m3 (value = code x scale, rounded to bf16) get a scale that
+        puts every element back on the e4m3 grid, so re-encoding returns the checkpoint's codes (times
+        a power of two) instead of rounding a second time. The row maximum is some code m x 2^e with
+        m in 8..15 times the unknown scale: each m is tried, and the one under which the whole row
+        lands on the grid is kept. Rows of other origin (bf16 checkpoints) match no m and keep
+        max / 448."""
+        found = torch.zeros_like(amax, dtype=torch.bool)
+        for m in (14, 15, 13, 12, 11, 10, 9, 8):         # 14 x 2^5 = 448: the plain choice comes first
+            cand = (amax / (m * (32.0 if m <= 14 else 16.0))).clamp_min(1e-30)
+            q = wf / cand[:, None]
+            r = q.clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float()
+            ok = ((q - r).abs() <= q.abs() * 2.0 ** -6 + 2.0 ** -12).all(1) & ~found & (amax > 0)
+            scale = torch.where(ok, cand, scale)
+            found |= ok
+        return scale, found
+
+    @staticmethod
     def from_dense(w: torch.Tensor, per_channel: bool = True) -> "Fp8Weight":
         wf = w.float()
         amax = wf.abs().amax(1) if per_channel else wf.abs().max().reshape(1)
         scale = (amax / 448.0).clamp_min(1e-12)
+        if per_channel and wf.shape[1] >= 64:
+            # weights expanded from an fp8 checkpoint: recover its grid (a sample of rows tells
+            # whether the search is worth running over the whole matrix)
+            n = min(16, wf.shape[0])
+            if bool(Fp8Weight._grid_scales(wf[:n], amax[:n], scale[:n])[1].any()):
+                scale = Fp8Weight._grid_scales(wf, amax, scale)[0]
         w8 = (wf / (scale[:, None] if per_channel else scale)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
         return Fp8Weight(w8.contiguous(), scale)
 
