@@ -61,3 +61,30 @@ def test_validation_layer_names_the_broken_rule():
     except OpArgumentError as ex:
         e = ex
     assert e is not None and e.op == "rmsnorm" and "weight" in e.rule and "(3, 8)" in str(e)
+
+
+def test_nvfp4_plan_file_round_trip(tmp_path, monkeypatch):
+    """The W4A4 tile plans survive a restart through B200_NVFP4_PLAN_FILE; a damaged file is ignored."""
+    from vllm_cpp_b200.ops import quant as Q
+    path = str(tmp_path / "plans.json")
+    monkeypatch.setenv("B200_NVFP4_PLAN_FILE", path)
+    saved = dict(Q._NVFP4_PLANS)
+    try:
+        Q._NVFP4_PLANS.clear()
+        Q._NVFP4_PLANS[(64, 34816, 5120)] = 256
+        Q._NVFP4_PLANS[(64, 5120, 17408)] = 128
+        Q.save_nvfp4_plans()
+        Q._NVFP4_PLANS.clear()
+        Q._NVFP4_PLANS[(64, 5120, 17408)] = 256              # already in memory: kept
+        assert Q.load_nvfp4_plans() == 1
+        assert Q._NVFP4_PLANS == {(64, 34816, 5120): 256, (64, 5120, 17408): 256}
+        with open(path, "w") as f:
+            f.write("{not json")
+        Q._NVFP4_PLANS.clear()
+        assert Q.load_nvfp4_plans() == 0 and not Q._NVFP4_PLANS
+        with open(path, "w") as f:
+            f.write('{"1,2": 256, "a,b,c": 128, "64,8,256": 64, "16,512,256": 128}')
+        assert Q.load_nvfp4_plans() == 1 and Q._NVFP4_PLANS == {(16, 512, 256): 128}
+    finally:
+        Q._NVFP4_PLANS.clear()
+        Q._NVFP4_PLANS.update(saved)

@@ -171,3 +171,33 @@ def test_fp8_requantisation_recovers_checkpoint_codes():
     dense = torch.randn(32, 256).to(torch.bfloat16)
     q2 = Fp8Weight.from_dense(dense)
     assert torch.allclose(q2.w_scale, dense.float().abs().amax(1) / 448.0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,quant", [("tiny-gdn", "nvfp4"), ("tiny-dense", "nvfp4"), ("tiny-dense", "fp8"),
+                                        ("tiny-gdn", "fp8")])
+def test_fused_producers_give_the_tokens_of_the_two_kernel_form(name, quant, monkeypatch):
+    """Quantised activations written by the producer kernel (RMSNorm -> fp4 / fp8, act-mul -> fp4 / fp8,
+    sigmoid gate -> fp4) against the same model with norm / activation and quantiser as separate
+    launches: the producers round where the separate kernels round, so greedy tokens agree."""
+    from vllm_cpp_b200 import ops
+    monkeypatch.setenv("B200_NVFP4_ACTIVATIONS", "nvfp4")
+    monkeypatch.setenv("B200_NATIVE_LAYERS", "0")         # the per-op path is the one with the entry points
+    cfg = synthetic_config(name)
+    cfg.quant = quant
+    if name == "tiny-dense":
+        cfg.head_dim = 128
+    prompts = _prompts(cfg)
+    monkeypatch.setenv("B200_FUSED_PRODUCERS", "1")
+    n0 = ops._lib.LAUNCHES[0]
+    _, fused = _run("cuda", cfg, prompts)
+    n_fused = ops._lib.LAUNCHES[0] - n0
+    monkeypatch.setenv("B200_FUSED_PRODUCERS", "0")
+    n0 = ops._lib.LAUNCHES[0]
+    _, plain = _run("cuda", cfg, prompts)
+    n_plain = ops._lib.LAUNCHES[0] - n0
+    assert ops.read_status() == 0
+    assert n_fused < n_plain                               # fewer launches, not just other ones
+    assert [a[0] for a in fused] == [a[0] for a in plain]
+    hit = sum(sum(1 for p, q in zip(a, b) if p == q) for a, b in zip(fused, plain))
+    assert hit / sum(len(a) for a in plain) > 0.8

@@ -166,7 +166,32 @@ class BlockQuantWeight:
 _SHARED_SCRATCH: dict = {}
 
 
-class CpuBackend:
+class FusedLinearMixin:
+    """Producer + linear pairs the model code asks for by meaning. The default runs the two ops one
+    after the other; the GPU back end overrides them where the linear layer takes quantised
+    activations, so that the producer writes them directly (no bf16 round trip through HBM and one
+    launch less). Reference: the quantise-once producers of the NVFP4 dense dispatch
+    (src/vllm/model_executor/models/qwen3_5.cpp:1752-2055)."""
+
+    def norm_gemm(self, hidden, ln_w, eps, w, out, *, residual=None, gemma=False, normed=None,
+                  need_normed=False, bias=None):
+        """out = RMSNorm(hidden (+ residual, updated in place)) @ w^T. ``normed``: a buffer for the
+        normalised rows; they are only guaranteed to be written when ``need_normed`` (a fused
+        path skips them otherwise). Returns (out, normalised rows or None)."""
+        x = self.rmsnorm(hidden, ln_w, eps, residual=residual, out=normed, gemma=gemma)
+        return self.gemm(x, w, bias=bias, out=out), x
+
+    def act_gemm(self, gate_up, kind, w, out, *, act=None, interleaved=False):
+        """out = (act(gate) * up) @ w^T for ``gate_up`` rows ``[gate | up]``."""
+        a = self.act_and_mul(gate_up, kind, out=act, interleaved=interleaved)
+        return self.gemm(a, w, out=out)
+
+    def sigmoid_gate_gemm(self, x, gate, w, out):
+        """out = (x * sigmoid(gate)) @ w^T (the output gate of gated attention)."""
+        return self.gemm(self.sigmoid_mul(x, gate), w, out=out)
+
+
+class CpuBackend(FusedLinearMixin):
     name = "cpu"
 
     def __init__(self, device="cpu"):
@@ -330,7 +355,7 @@ class CpuNativeBackend(CpuBackend):
                                       out=out)
 
 
-class GpuBackend:
+class GpuBackend(FusedLinearMixin):
     name = "cuda"
 
     def __init__(self, device="cuda"):
@@ -341,6 +366,58 @@ class GpuBackend:
         # NVFP4 weights: "bf16" keeps activations in bf16 (W4A16), "nvfp4" quantises them per call
         # and runs W4A4 on kind::mxf4nvf4 (what NVFP4 checkpoints are calibrated for)
         self.w4a4 = os.environ.get("B200_NVFP4_ACTIVATIONS", "bf16") == "nvfp4"
+
+    # ---- producers that write quantised activations directly -----------------------------------
+    def _w4a4_ok(self, w, K):
+        return isinstance(w, QuantWeight) and self.w4a4 and K % 256 == 0 and w.shape[0] % 8 == 0
+
+    def norm_gemm(self, hidden, ln_w, eps, w, out, *, residual=None, gemma=False, normed=None,
+                  need_normed=False, bias=None):
+        from ..ops import quant as Q
+        T, K = hidden.shape
+        if T > 0 and hidden.stride(-1) == 1 and os.environ.get("B200_FUSED_PRODUCERS", "1") == "1":
+            if self._w4a4_ok(w, K):
+                g_a = w.act_gscale()
+                keep = normed if need_normed else None
+                ap, sfa = Q.rmsnorm_quant_nvfp4(hidden, ln_w, eps, g_a, residual=residual, gemma=gemma, swizzle=True,
+                                                out=self._w4a4_buffers(T, K), normed=keep)
+                y = Q.gemm_nvfp4(ap, sfa, g_a, w.packed, w.sf_chunks(), w.gscale, out=out, bias=bias)
+                return y, keep
+            if isinstance(w, Fp8Weight) and w.input_scale is None and not need_normed:
+                a8, scales = self._fp8_buffer(T, K), self._fp8_row_scales(T)
+                Q.quant_fp8_rowwise(hidden, out=a8, scales=scales, norm_weight=ln_w, eps=eps, gemma=gemma,
+                                    residual=residual)
+                return Q.gemm_fp8(a8, w.w8, scales, w.w_scale, out=out, bias=bias), None
+        return super().norm_gemm(hidden, ln_w, eps, w, out, residual=residual, gemma=gemma, normed=normed,
+                                 need_normed=need_normed, bias=bias)
+
+    def act_gemm(self, gate_up, kind, w, out, *, act=None, interleaved=False):
+        from ..ops import quant as Q
+        T, K = gate_up.shape[0], gate_up.shape[1] // 2
+        if T > 0 and gate_up.stride(-1) == 1 and os.environ.get("B200_FUSED_PRODUCERS", "1") == "1":
+            if self._w4a4_ok(w, K) and kind == 0 and not interleaved:
+                g_a = w.act_gscale()
+                ap, sfa = Q.quant_nvfp4(gate_up, g_a, silu_mul=True, swizzle=True, out=self._w4a4_buffers(T, K))
+                return Q.gemm_nvfp4(ap, sfa, g_a, w.packed, w.sf_chunks(), w.gscale, out=out)
+            if isinstance(w, Fp8Weight) and w.input_scale is None and (not interleaved or K % 128 == 0):
+                a8, scales = self._fp8_buffer(T, K), self._fp8_row_scales(T)
+                Q.quant_fp8_rowwise(gate_up, out=a8, scales=scales, act_kind=kind, interleaved=interleaved)
+                return Q.gemm_fp8(a8, w.w8, scales, w.w_scale, out=out)
+        return super().act_gemm(gate_up, kind, w, out, act=act, interleaved=interleaved)
+
+    def sigmoid_gate_gemm(self, x, gate, w, out):
+        from ..ops import quant as Q
+        T, K = x.shape
+        if T > 0 and self._w4a4_ok(w, K) and x.stride(-1) == 1 and gate.stride(-1) == 1 \
+                and os.environ.get("B200_FUSED_PRODUCERS", "1") == "1":
+            g_a = w.act_gscale()
+            ap, sfa = Q.quant_nvfp4_gated(x, gate, g_a, swizzle=True, out=self._w4a4_buffers(T, K))
+            return Q.gemm_nvfp4(ap, sfa, g_a, w.packed, w.sf_chunks(), w.gscale, out=out)
+        return super().sigmoid_gate_gemm(x, gate, w, out)
+
+    def _fp8_row_scales(self, T: int):
+        from .. import ops
+        return ops.workspace(self.device, T * 4, "fp8_row_scales").view(torch.float32)[:T]
 
     def _fp8_buffer(self, T: int, K: int):
         """Persistent scratch of the fp8 activation quantiser."""
@@ -368,8 +445,7 @@ class GpuBackend:
                 Q.quant_fp8(a, w.input_scale, out=a8)
                 a_scale = w.input_scale
             else:
-                from .. import ops
-                scales = ops.workspace(self.device, a.shape[0] * 4, "fp8_row_scales").view(torch.float32)[: a.shape[0]]
+                scales = self._fp8_row_scales(a.shape[0])
                 Q.quant_fp8_rowwise(a, out=a8, scales=scales)
                 a_scale = scales
             y = Q.gemm_fp8(a8, w.w8, a_scale, w.w_scale, out=out, bias=bias)

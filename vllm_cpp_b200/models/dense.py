@@ -634,15 +634,15 @@ class DenseModel:
             if c.post_norm:
                 if first:
                     resid.copy_(hidden)
-                x_in = resid
-            elif first:
-                resid.copy_(hidden)
-                x_in = be.rmsnorm(hidden, L["ln1"], eps, out=normed, gemma=c.gemma_norm)
+                be.gemm(resid, L["qkv"], bias=L.get("qkv_bias"), out=qkv)
             else:
-                x_in = be.rmsnorm(hidden, L["ln1"], eps, residual=resid, out=normed,
-                                  gemma=c.gemma_norm)
+                if first:
+                    resid.copy_(hidden)
+                # the norm hands its rows to the projection (as quantised activations when the
+                # weights take them)
+                be.norm_gemm(hidden, L["ln1"], eps, L["qkv"], qkv, residual=None if first else resid,
+                             gemma=c.gemma_norm, normed=normed, bias=L.get("qkv_bias"))
             first = False
-            be.gemm(x_in, L["qkv"], bias=L.get("qkv_bias"), out=qkv)
             be.rope_kv(qkv, pos, self.rope_table, num_q_heads=self.hq, num_kv_heads=self.hkv,
                        head_dim=self.D, rot_dim=self.rot, neox=c.rope.neox,
                        q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=eps,
@@ -667,16 +667,24 @@ class DenseModel:
                 else:
                     if c.residual_multiplier != 1.0:
                         hidden = be.mul_scalar(hidden, c.residual_multiplier)
-                    x_mlp = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed,
-                                       gemma=c.gemma_norm)
+                    x_mlp = None           # ln2 runs with the gate / up projection below
             # ---- MLP block
-            if self.gate_up_il:
-                a = be.gemm_gated(x_mlp, L["gate_up"], act_kind, out=act, scratch=gate_up)
+            plain_w = isinstance(L["gate_up"], torch.Tensor)
+            if x_mlp is None and (plain_w and self.gate_up_il):
+                x_mlp = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed, gemma=c.gemma_norm)
+            if x_mlp is None:
+                be.norm_gemm(hidden, L["ln2"], eps, L["gate_up"], gate_up, residual=resid, gemma=c.gemma_norm,
+                             normed=normed)
+                hidden = self.bufs.get("hidden", T, H)
+                be.act_gemm(gate_up, act_kind, L["down"], hidden, act=act, interleaved=self.gate_up_il)
             else:
-                be.gemm(x_mlp, L["gate_up"], out=gate_up)
-                a = be.act_and_mul(gate_up, act_kind, out=act)
-            hidden = self.bufs.get("hidden", T, H)
-            be.gemm(a, L["down"], out=hidden)
+                if self.gate_up_il:
+                    a = be.gemm_gated(x_mlp, L["gate_up"], act_kind, out=act, scratch=gate_up)
+                else:
+                    be.gemm(x_mlp, L["gate_up"], out=gate_up)
+                    a = be.act_and_mul(gate_up, act_kind, out=act)
+                hidden = self.bufs.get("hidden", T, H)
+                be.gemm(a, L["down"], out=hidden)
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
             if c.post_norm:

@@ -365,16 +365,19 @@ class Qwen35Model(DenseModel):
         return hidden
 
     # ------------------------------------------------------------------ GDN layer
-    def _gdn_layer(self, l: int, L: dict, x: torch.Tensor | None, ctx: StepContext, T: int, meta: dict):
+    def _gdn_layer(self, l: int, L: dict, x: torch.Tensor | None, ctx: StepContext, T: int, meta: dict,
+                   proj: torch.Tensor | None = None):
         """x: normed hidden [T, H] -> core attention output after the gated norm [T, gv*128].
-        ``x`` None: the input is the gathered activation buffer of the fused tensor-parallel path
-        (the in_proj GEMM waits for its rows tile by tile)."""
+        ``proj``: the in_proj output when the caller already ran it (fused with the norm). ``x``
+        None without ``proj``: the input is the gathered activation buffer of the fused
+        tensor-parallel path (the in_proj GEMM waits for its rows tile by tile)."""
         be = self.be
-        proj = self.bufs.get("gdn_in", T, self.in_w_pad)
-        if x is None:
-            self.tpf.gemm_gather(T, L["in_proj"], proj)
-        else:
-            be.gemm(x, L["in_proj"], out=proj)
+        if proj is None:
+            proj = self.bufs.get("gdn_in", T, self.in_w_pad)
+            if x is None:
+                self.tpf.gemm_gather(T, L["in_proj"], proj)
+            else:
+                be.gemm(x, L["in_proj"], out=proj)
         core = self.bufs.get("gdn_core", T, self.gv * 128)
         nd = ctx.num_decodes
         mixed = proj[:, : self.conv_dim]
@@ -567,14 +570,15 @@ class Qwen35Model(DenseModel):
         for l, L in enumerate(self.layers):
             if l == 0:
                 resid.copy_(hidden)
-                x = be.rmsnorm(hidden, L["ln1"], eps, out=normed, gemma=True)
-            else:
-                x = be.rmsnorm(hidden, L["ln1"], eps, residual=resid, out=normed, gemma=True)
+            res_in = None if l == 0 else resid
             if self.is_gdn[l]:
-                core = self._gdn_layer(l, L, x, ctx, T, meta)
+                # the norm hands its rows to in_proj (as quantised activations when the weights take them)
+                proj = self.bufs.get("gdn_in", T, self.in_w_pad)
+                be.norm_gemm(hidden, L["ln1"], eps, L["in_proj"], proj, residual=res_in, gemma=True, normed=normed)
+                core = self._gdn_layer(l, L, None, ctx, T, meta, proj=proj)
                 be.gemm(core, L["out"], out=hidden)
             else:
-                be.gemm(x, L["qkv"], out=qkv)
+                be.norm_gemm(hidden, L["ln1"], eps, L["qkv"], qkv, residual=res_in, gemma=True, normed=normed)
                 # q rows are [q | gate] per head (head stride 2D): the fused norm + RoPE kernel
                 # reads them strided and writes the rotated q compactly
                 qv = qkv[:, :k_off].view(T, self.hq, 2 * D)
@@ -598,17 +602,15 @@ class Qwen35Model(DenseModel):
                              head_dim=D, block_size=self.block_size, scale=self.scale, out=attn)
                 gate = self.bufs.get("gate_compact", T, self.hq * D)
                 gate.view(T, self.hq, D).copy_(qv[:, :, D:])
-                gated = be.sigmoid_mul(attn, gate)
-                be.gemm(gated, L["o"], out=hidden)
+                be.sigmoid_gate_gemm(attn, gate, L["o"], hidden)
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
-            x = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed, gemma=True)
             if self.has_moe:
+                x = be.rmsnorm(hidden, L["ln2"], eps, residual=resid, out=normed, gemma=True)
                 hidden = self._expert_block(x, L, T, act_kind)
             else:
-                be.gemm(x, L["gate_up"], out=gate_up)
-                a_ = be.act_and_mul(gate_up, act_kind, out=act)
-                be.gemm(a_, L["down"], out=hidden)
+                be.norm_gemm(hidden, L["ln2"], eps, L["gate_up"], gate_up, residual=resid, gemma=True, normed=normed)
+                be.act_gemm(gate_up, act_kind, L["down"], hidden, act=act)
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
         full = be.rmsnorm(hidden, self.w["final_norm"], eps, residual=resid, out=normed, gemma=True)

@@ -195,6 +195,52 @@ def nvfp4_sf_chunks(sf: torch.Tensor, pad_rows: int = 256) -> torch.Tensor:
 # (rows bucket, N, K) -> weight rows per CTA; filled by the heuristic or, with B200_NVFP4_AUTOTUNE=1, by
 # timing both tile widths once per shape (outside stream capture)
 _NVFP4_PLANS: dict[tuple[int, int, int], int] = {}
+_PLAN_FILE_READ = [False]
+
+
+def _plan_file() -> str:
+    import os
+    return os.environ.get("B200_NVFP4_PLAN_FILE", "")
+
+
+def load_nvfp4_plans(path: str | None = None) -> int:
+    """Reads plans saved by an earlier process (JSON ``{"M,N,K": tile}``); plans already in memory
+    win. Returns the number read. A missing or unreadable file is no plans, not an error: the cache
+    is an optimisation (reference: ``nvfp4_persistent_cache.cpp``, the tactic cache that survives
+    restarts so that serving does not re-tune)."""
+    import json
+    import os
+    path = path or _plan_file()
+    if not path or not os.path.exists(path):
+        return 0
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+    except (OSError, ValueError):
+        return 0
+    n = 0
+    for k, v in raw.items():
+        try:
+            key = tuple(int(x) for x in k.split(","))
+        except ValueError:
+            continue
+        if len(key) == 3 and v in (128, 256) and key not in _NVFP4_PLANS:
+            _NVFP4_PLANS[key] = int(v)
+            n += 1
+    return n
+
+
+def save_nvfp4_plans(path: str | None = None) -> None:
+    """Writes the plan table (atomically: a temporary file, then a rename)."""
+    import json
+    import os
+    path = path or _plan_file()
+    if not path:
+        return
+    tmp = f"{path}.{os.getpid()}.tmp"
+    with open(tmp, "w") as f:
+        json.dump({",".join(map(str, k)): v for k, v in sorted(_NVFP4_PLANS.items())}, f, indent=0)
+    os.replace(tmp, path)
 
 
 def _m_bucket(M: int) -> int:
@@ -213,6 +259,9 @@ def nvfp4_plan(M: int, N: int, K: int, run=None) -> int:
     events and the faster one is kept (reference: the per-shape tactic cache of
     ``src/vt/cuda/nvfp4_cutlass_tactic_impl.cuh``)."""
     import os
+    if not _PLAN_FILE_READ[0]:
+        _PLAN_FILE_READ[0] = True
+        load_nvfp4_plans()
     key = (_m_bucket(M), N, K)
     plan = _NVFP4_PLANS.get(key)
     if plan is not None:
@@ -236,6 +285,8 @@ def nvfp4_plan(M: int, N: int, K: int, run=None) -> int:
             if best is None or t < best[0]:
                 best = (t, nt)
         plan = best[1]
+        _NVFP4_PLANS[key] = plan
+        save_nvfp4_plans()            # timed plans are worth keeping across restarts (B200_NVFP4_PLAN_FILE)
     _NVFP4_PLANS[key] = plan
     return plan
 
