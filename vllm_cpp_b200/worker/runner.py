@@ -248,6 +248,16 @@ class ModelRunner(E.ModelRunnerBase):
         """Capture forward + greedy argmax for a decode-only batch padded to ``size`` rows."""
         info_stub = type("S", (), {"max_seq_len": 0, "max_query_len": 1})()
         ctx = self._context(info_stub, padded=size)
+        # The warm-up runs below execute the model for real, so they must not see a live step's
+        # inputs: KV writes would be harmless repeats, but a recurrent layer would advance the
+        # state of live requests once per warm-up run. Every row becomes a pad row first (no KV
+        # slot, no state slot, empty context); the caller copies the step's inputs in afterwards.
+        v = self.views
+        for k in ("input_ids", "positions", "seq_lens"):
+            v[k].zero_()
+        v["state_slots"].fill_(-1)
+        for g_ in range(self.num_groups):
+            v["slot_mapping"][g_].fill_(-1)
         # warm-up run on a side stream (allocations, tensor maps, lazy module state)
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream())
@@ -277,6 +287,7 @@ class ModelRunner(E.ModelRunnerBase):
         hv = self.host_views
         for k in ("input_ids", "positions", "seq_lens"):
             hv[k].zero_()
+        hv["state_slots"].fill_(-1)
         for g in range(self.num_groups):
             hv["slot_mapping"][g].fill_(-1)
             hv["block_table"][g].zero_()
@@ -314,6 +325,7 @@ class ModelRunner(E.ModelRunnerBase):
             hv["input_ids"][R:pad].zero_()
             hv["positions"][R:pad].zero_()
             hv["seq_lens"][R:pad].zero_()
+            hv["state_slots"][R:pad].fill_(-1)     # a stale slot here would update a live request's state
             for g in range(self.num_groups):
                 hv["slot_mapping"][g][R:pad].fill_(-1)
         if self.step_channel is not None:
@@ -335,6 +347,8 @@ class ModelRunner(E.ModelRunnerBase):
             e0.record()
             self.step_events.append([e0, None])
         nbytes = self.layout.total_bytes
+        if pad is not None and pad not in self.graphs:
+            self._capture(pad)                 # before this step's inputs reach the device buffer
         if self.is_cuda:
             self.dev_buf.copy_(self.host_buf, non_blocking=True)
         else:
@@ -347,7 +361,7 @@ class ModelRunner(E.ModelRunnerBase):
                 v["input_ids"].data_ptr(), v["splice_dst"].data_ptr(), v["splice_src"].data_ptr(),
                 self.last_sampled.data_ptr(), info.num_splice, _lib.stream_ptr()), "splice")
         if pad is not None:
-            g = self.graphs.get(pad) or self._capture(pad)
+            g = self.graphs[pad]
             g[0].replay()
             from ..ops import _lib as _l
             if _l.SYNC_CHECK:
