@@ -367,45 +367,87 @@ __global__ void __launch_bounds__(128)
   }
 }
 
-// (residual +) RMSNorm -> NVFP4 in one pass over the row: one block per token keeps the row in
-// shared memory between the sum of squares and the quantisation; the updated residual (bf16) is
-// written back when given, the normalised row itself only when `normed` is given. The normalised
-// values are rounded to bf16 before quantisation, as a separate norm kernel would hand them over.
+// (residual +) RMSNorm -> NVFP4 in one pass over the row: one block per token keeps the row (bf16,
+// 16-byte vectors) in shared memory between the sum of squares and the quantisation; the updated
+// residual is written back when given, the normalised row itself only when `normed` is given.
+// The norm is rmsnorm_kernel's arithmetic (same vector striding, same two-level sum, launched with
+// the same thread count) and the quantisation is quant_nvfp4_kernel's, so the fused kernel gives
+// the bytes of the two run one after the other.
+__device__ __forceinline__ float q_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float q_block_sum(float v, float* red) {
+  v = q_warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = q_warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
 __global__ void __launch_bounds__(256)
     rmsnorm_quant_nvfp4_kernel(const bf16* __restrict__ x, long ldx, bf16* residual, const bf16* __restrict__ w,
                                float eps, int gemma, const float* __restrict__ gscale, uint8_t* __restrict__ out,
                                uint8_t* __restrict__ sf, bf16* normed, long T, int K, int swizzle) {
-  extern __shared__ float rowf[];          // K floats
-  __shared__ float red[8];
+  extern __shared__ uint4 row_cache[];     // K / 8 vectors
+  __shared__ float red[32];
   const long t = blockIdx.x;
+  const int nv = K >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + t * ldx);
+  uint4* rr = residual ? reinterpret_cast<uint4*>(residual + t * (long)K) : nullptr;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < K; i += blockDim.x) {
-    float v = __bfloat162float(x[t * ldx + i]);
-    if (residual) {
-      v = __bfloat162float(__float2bfloat16(v + __bfloat162float(residual[t * K + i])));
-      residual[t * K + i] = __float2bfloat16(v);
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    uint4 v = xr[i];
+    if (rr) {
+      uint4 r = rr[i];
+      float2 a, b;
+      a = unpack_bf16x2(v.x); b = unpack_bf16x2(r.x); v.x = pack_bf16x2(a.x + b.x, a.y + b.y);
+      a = unpack_bf16x2(v.y); b = unpack_bf16x2(r.y); v.y = pack_bf16x2(a.x + b.x, a.y + b.y);
+      a = unpack_bf16x2(v.z); b = unpack_bf16x2(r.z); v.z = pack_bf16x2(a.x + b.x, a.y + b.y);
+      a = unpack_bf16x2(v.w); b = unpack_bf16x2(r.w); v.w = pack_bf16x2(a.x + b.x, a.y + b.y);
+      rr[i] = v;
     }
-    rowf[i] = v;
-    ss += v * v;
+    row_cache[i] = v;
+    float2 f;
+    f = unpack_bf16x2(v.x); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(v.y); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(v.z); ss += f.x * f.x + f.y * f.y;
+    f = unpack_bf16x2(v.w); ss += f.x * f.x + f.y * f.y;
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
-  __syncthreads();
-  float tot = 0.f;
-  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
-  const float inv = rsqrtf(tot / (float)K + eps);
-  const float gs = *gscale, gadd = gemma ? 1.f : 0.f;
-  for (int gidx = threadIdx.x; gidx < K / 16; gidx += blockDim.x) {
+  ss = q_block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)K + eps);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* nrow = normed ? reinterpret_cast<uint4*>(normed + t * (long)K) : nullptr;
+  const float g = gemma ? 1.f : 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = row_cache[i];
+    const uint4 wv = wr[i];
+    uint4 o;
+    float2 a, b;
+    a = unpack_bf16x2(v.x); b = unpack_bf16x2(wv.x); o.x = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+    a = unpack_bf16x2(v.y); b = unpack_bf16x2(wv.y); o.y = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+    a = unpack_bf16x2(v.z); b = unpack_bf16x2(wv.z); o.z = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+    a = unpack_bf16x2(v.w); b = unpack_bf16x2(wv.w); o.w = pack_bf16x2(a.x * inv * (b.x + g), a.y * inv * (b.y + g));
+    row_cache[i] = o;
+    if (nrow) nrow[i] = o;
+  }
+  __syncthreads();               // groups below span vectors written by other threads
+  const float gs = *gscale;
+  for (int gidx = threadIdx.x; gidx < (K >> 4); gidx += blockDim.x) {
+    const uint4 v0 = row_cache[2 * gidx], v1 = row_cache[2 * gidx + 1];
+    const uint32_t wds[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
     float v[16];
     float amax = 0.f;
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const int c = gidx * 16 + e;
-      const float n = __bfloat162float(__float2bfloat16(rowf[c] * inv * (__bfloat162float(w[c]) + gadd)));
-      if (normed) normed[t * K + c] = __float2bfloat16(n);
-      v[e] = n;
-      amax = fmaxf(amax, fabsf(n));
+    for (int j = 0; j < 8; ++j) {
+      const float2 f = unpack_bf16x2(wds[j]);
+      v[2 * j] = f.x; v[2 * j + 1] = f.y;
+      amax = fmaxf(amax, fabsf(f.x));
+      amax = fmaxf(amax, fabsf(f.y));
     }
     const uint8_t sb = float_to_e4m3(amax * gs / 6.f);
     const float sdec = e4m3_to_float(sb);
@@ -417,14 +459,7 @@ __global__ void __launch_bounds__(256)
       w1 |= float_to_e2m1(v[8 + e] * mul) << (e * 4);
     }
     reinterpret_cast<uint2*>(out)[t * (K / 16) + gidx] = make_uint2(w0, w1);
-    size_t so;
-    if (swizzle) {
-      const long rb = t / 128, r = t % 128;
-      so = ((size_t)rb * (K / 64) + gidx / 4) * 512 + (size_t)(r % 32) * 16 + (size_t)(r / 32) * 4 + gidx % 4;
-    } else {
-      so = (size_t)t * (K / 16) + gidx;
-    }
-    sf[so] = sb;
+    sf[swizzle ? nvfp4_sf_chunk_offset(t, gidx, K) : (size_t)t * (K / 16) + gidx] = sb;
   }
 }
 
@@ -623,7 +658,12 @@ int b200_rmsnorm_quant_nvfp4(const void* x, long ldx, void* residual, const void
   static PerDeviceOnce attr_once;
   if (attr_once.first())
     cudaFuncSetAttribute(rmsnorm_quant_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4);
-  rmsnorm_quant_nvfp4_kernel<<<(unsigned)T, 256, (size_t)K * 4, stream>>>(
+  if ((ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)weight & 15) || ((uintptr_t)residual & 15) ||
+      ((uintptr_t)normed & 15))
+    return -1;
+  int threads = K / 8 >= 256 ? 256 : ((K / 8 + 31) / 32) * 32;      // as b200_rmsnorm launches its kernel
+  if (threads < 32) threads = 32;
+  rmsnorm_quant_nvfp4_kernel<<<(unsigned)T, threads, (size_t)K * 2, stream>>>(
       (const bf16*)x, ldx, (bf16*)residual, (const bf16*)weight, eps, gemma, gscale, (uint8_t*)out, (uint8_t*)sf,
       (bf16*)normed, T, K, swizzle);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
