@@ -10,6 +10,7 @@ void bind_structured(py::module_& m) __attribute__((weak));
 void bind_offload(py::module_& m) __attribute__((weak));
 void bind_cpu_backend(py::module_& m) __attribute__((weak));
 void bind_frontend(py::module_& m) __attribute__((weak));
+void bind_parallel(py::module_& m) __attribute__((weak));
 
 void bind_extras(py::module_& m) {
   if (bind_tokenizer) bind_tokenizer(m);
@@ -18,4 +19,5 @@ void bind_extras(py::module_& m) {
   if (bind_offload) bind_offload(m);
   if (bind_cpu_backend) bind_cpu_backend(m);
   if (bind_frontend) bind_frontend(m);
+  if (bind_parallel) bind_parallel(m);
 }

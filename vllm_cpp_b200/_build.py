@@ -98,7 +98,8 @@ def build_engine(verbose: bool = False) -> Path:
     return out
 
 
-BINDING_STEMS = ("bindings", "tokenizer_bindings", "structured_bindings", "offload_bindings", "extras_bindings")
+BINDING_STEMS = ("bindings", "tokenizer_bindings", "structured_bindings", "offload_bindings", "extras_bindings",
+                 "parallel_bindings")
 
 
 def build_capi(verbose: bool = False) -> Path:

@@ -374,6 +374,21 @@ class ParallelConfig:
     # ``LLM.serve_as_worker()`` and never see a request (serving). False: every rank runs its own
     # scheduler and must be fed identical requests (offline batches driven by one script per rank).
     driver_worker: bool = False
+    # Expert-parallel load balancing (parallel/eplb.py): redundant physical expert slots (the
+    # total must divide over the ranks), steps between rebalances, steps of load history used.
+    enable_eplb: bool = False
+    eplb_redundant_experts: int = 0
+    eplb_interval: int = 3000
+    eplb_window: int = 1000
+    # Decode context parallelism (KV of one sequence split over ranks). Only 1 is implemented:
+    # long prompts are handled by chunked prefill over the paged cache. The field exists so that
+    # KV-cache specs and attention metadata carry the degree (reference: dcp_world_size = 1 fixed
+    # in src/vllm/v1/core/sched/scheduler.cpp:78-79).
+    dcp_world_size: int = 1
+
+    def __post_init__(self):
+        if self.dcp_world_size != 1:
+            raise ValueError("decode context parallelism is not implemented: dcp_world_size must be 1")
 
     @property
     def world_size(self) -> int:

@@ -94,6 +94,11 @@ class LLM:
         if args.cpu_weight_quant and torch.device(device).type == "cpu" \
                 and hasattr(self.model, "quantize_weights"):
             self.model.quantize_weights(args.cpu_weight_quant)
+        if par.enable_eplb and hasattr(self.model, "enable_eplb") and getattr(cfg, "num_experts", 0):
+            from ..parallel.eplb import EplbConfig
+            self.model.enable_eplb(EplbConfig(
+                num_redundant_experts=par.eplb_redundant_experts, interval=par.eplb_interval,
+                window=par.eplb_window, num_groups=max(1, getattr(cfg, "n_group", 1) or 1)))
         budget = args.resolve_max_num_batched_tokens(cfg)
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
         if par.tensor_parallel_size > 1:

@@ -344,6 +344,9 @@ class Qwen35Model(DenseModel):
     # ------------------------------------------------------------------ expert block
     _moe_block = MoeModel._moe_block
     _moe_block_cpu = MoeModel._moe_block_cpu
+    eplb = None
+    enable_eplb = MoeModel.enable_eplb
+    eplb_end_step = MoeModel.eplb_end_step
 
     def _expert_block(self, x: torch.Tensor, L: dict, T: int, act_kind: int) -> torch.Tensor:
         """routed(x) + sigmoid(x . w_g) * shared(x); each rank returns its partial sum (its

@@ -37,6 +37,45 @@ class MoeModel(DenseModel):
         self.e_local = self.E // self.ep
         self.e0 = self.rank * self.e_local if self.ep > 1 else 0
         self.moe_ws = None
+        self.eplb = None
+
+    # ------------------------------------------------------------------ expert load balancing
+    def enable_eplb(self, eplb_cfg) -> None:
+        """Switches the MoE layers from the contiguous expert split to balanced physical slots
+        (``parallel/eplb.py``): the expert tensors are rearranged (redundant slots filled with
+        replicas), the router's ids go through the placement table from now on, and
+        ``eplb_end_step`` rebalances on schedule. Collective over the expert-parallel ranks."""
+        from ..parallel.comm import SingleComm
+        from ..parallel.eplb import EplbState
+        moe_layers = [l for l, L in enumerate(self.layers) if "w_gate_up" in L]
+        comm = self.comm if self.ep > 1 else SingleComm()
+        st = EplbState(eplb_cfg, comm, len(moe_layers), self.E, self.device)
+        new = st.initial([[self.layers[l]["w_gate_up"], self.layers[l]["w_down"]] for l in moe_layers])
+        for i, l in enumerate(moe_layers):
+            self.layers[l]["w_gate_up"], self.layers[l]["w_down"] = new[i]
+            self.layers[l]["_eplb_idx"] = i
+        self._eplb_layers = moe_layers
+        self.eplb = st
+        self.e_local = st.S
+        self.e0 = self.rank * st.S if self.ep > 1 else 0
+        if self.moe_ws is not None:
+            from ..ops.moe import MoeWorkspace
+            self.moe_ws = MoeWorkspace(self.device, self.moe_ws.max_pairs // self.k, self.k, self.e_local,
+                                       self.cfg.hidden_size, self.moe_inter)
+
+    def eplb_end_step(self) -> bool:
+        """Called once per engine step; True when the experts were rebalanced in this call. The
+        rearranged tensors replace the old ones in place (same shapes, same storage), so captured
+        graphs stay valid."""
+        st = self.eplb
+        if st is None or not st.end_step():
+            return False
+        layers = self._eplb_layers
+        new = st.rebalance_now([[self.layers[l]["w_gate_up"], self.layers[l]["w_down"]] for l in layers])
+        for i, l in enumerate(layers):
+            self.layers[l]["w_gate_up"].copy_(new[i][0])
+            self.layers[l]["w_down"].copy_(new[i][1])
+        return True
 
     # ------------------------------------------------------------------ weights
     def init_random(self, seed: int = 0, std: float = 0.02) -> None:
@@ -195,6 +234,8 @@ class MoeModel(DenseModel):
         self.be.gemm(x, L["router"], out=logits, out_dtype=torch.float32)
         ids, w = M.router_topk(logits, self.k, renorm=c.norm_topk_prob,
                                routed_scale=c.routed_scaling_factor)
+        if self.eplb is not None:
+            ids = self.eplb.remap(L["_eplb_idx"], ids)       # logical expert -> physical slot
         M.moe_sort(ids, self.e0, self.e0 + self.e_local, ws)
         P = T * self.k
         chunks = min(ws.max_chunks, self.e_local + (P + 255) // 256)
@@ -219,11 +260,15 @@ class MoeModel(DenseModel):
             logits = N.gemm(x.contiguous(), L["router"], out_dtype=torch.float32)
             ids, w = N.moe_router_topk(logits, self.k, renorm=c.norm_topk_prob,
                                        routed_scale=c.routed_scaling_factor)
+            if self.eplb is not None:
+                ids = self.eplb.remap(L["_eplb_idx"], ids)
             return N.moe_experts(x.contiguous(), ids, w, L["w_gate_up"], L["w_down"], e0=self.e0,
                                  act_kind=ACT_KIND.get(c.hidden_act, 0))
         logits = (x.float() @ L["router"].float().t())
         ids, w = M.ref_router_topk(logits, self.k, renorm=c.norm_topk_prob,
                                    routed_scale=c.routed_scaling_factor)
+        if self.eplb is not None:
+            ids = self.eplb.remap(L["_eplb_idx"], ids)
         return M.ref_moe_block(x, ids, w, L["w_gate_up"], L["w_down"], e0=self.e0)
 
     # ------------------------------------------------------------------ forward

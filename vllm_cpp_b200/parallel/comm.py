@@ -39,6 +39,11 @@ class SingleComm:
     def all_gather_object(self, obj) -> list:
         return [obj]
 
+    def exchange(self, sends, recvs) -> None:
+        """Point-to-point batch: ``sends`` [(dst rank, tensor)], ``recvs`` [(src rank, buffer)];
+        between a pair of ranks tensors arrive in the order they were listed."""
+        assert not sends and not recvs
+
     def barrier(self) -> None:
         pass
 
@@ -74,6 +79,16 @@ class TorchComm:
     def all_to_all_single(self, out, inp, out_splits=None, in_splits=None):
         self.dist.all_to_all_single(out, inp, out_splits, in_splits, group=self.group)
         return out
+
+    def exchange(self, sends, recvs) -> None:
+        ops = [self.dist.P2POp(self.dist.isend, t, self._global(dst), self.group) for dst, t in sends]
+        ops += [self.dist.P2POp(self.dist.irecv, buf, self._global(src), self.group) for src, buf in recvs]
+        if ops:
+            for w in self.dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def _global(self, r: int) -> int:
+        return self.dist.get_global_rank(self.group, r) if self.group is not None else r
 
     def broadcast_object(self, obj, src=0):
         box = [obj]
@@ -144,6 +159,13 @@ class FakeComm:
             acc += v.float()
         n = t.shape[0] // self.world
         return acc[self.rank * n:(self.rank + 1) * n].to(t.dtype)
+
+    def exchange(self, sends, recvs) -> None:
+        vals = self._exchange([(dst, t.clone()) for dst, t in sends])
+        pending = {src: [t for dst, t in vals[src] if dst == self.rank] for src in range(self.world)}
+        for src, buf in recvs:
+            buf.copy_(pending[src].pop(0))
+        assert not any(pending.values()), "FakeComm.exchange: sends without a matching receive"
 
     def broadcast_object(self, obj, src=0):
         vals = self._exchange(obj)

@@ -379,6 +379,8 @@ class ModelRunner(E.ModelRunnerBase):
                 self._logits = self.model.forward(ctx)
             self._graph_sampled = self._logits is None
         self.num_kernel_steps += 1
+        if getattr(self.model, "eplb", None) is not None:
+            self.model.eplb_end_step()         # closes the load window of the step; rebalances on schedule
 
     def _sample_device(self, info, grammar) -> torch.Tensor:
         """Runs the sampler pipeline on the logits of this step; returns int64 ids [num_logits]."""
