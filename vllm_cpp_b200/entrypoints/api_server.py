@@ -557,6 +557,12 @@ def build_arg_parser() -> argparse.ArgumentParser:
                     help="engine replicas (one per GPU) behind this server; a request goes to the least loaded one")
     ap.add_argument("--enable-expert-parallel", action="store_true",
                     help="MoE models: experts are split over the ranks instead of sharded")
+    ap.add_argument("--enable-eplb", action="store_true",
+                    help="expert parallel: rebalance the expert placement from observed loads")
+    ap.add_argument("--eplb-redundant-experts", type=int, default=0,
+                    help="physical expert slots beyond one per expert (hot experts get replicas)")
+    ap.add_argument("--eplb-interval", type=int, default=3000, help="engine steps between rebalances")
+    ap.add_argument("--eplb-window", type=int, default=1000, help="engine steps of load history used")
     return ap
 
 
@@ -570,7 +576,9 @@ def main(argv=None) -> int:
               gpu_memory_utilization=a.gpu_memory_utilization, async_scheduling=a.async_scheduling,
               enable_prefix_caching=a.enable_prefix_caching)
     kw["parallel"] = ParallelConfig(tensor_parallel_size=max(1, a.tensor_parallel_size),
-                                    enable_expert_parallel=a.enable_expert_parallel)
+                                    enable_expert_parallel=a.enable_expert_parallel,
+                                    enable_eplb=a.enable_eplb, eplb_redundant_experts=a.eplb_redundant_experts,
+                                    eplb_interval=a.eplb_interval, eplb_window=a.eplb_window)
     llm, _workers = launch_engine(EngineArgs(**{k: v for k, v in kw.items() if v is not None}))
     replicas = []
     if a.data_parallel_size > 1:
