@@ -232,7 +232,8 @@ PYBIND11_MODULE(_engine, m) {
       .def_readwrite("logprobs", &ModelRunnerOutput::logprobs)
       .def_readwrite("num_nans_in_logits", &ModelRunnerOutput::num_nans_in_logits)
       .def_readwrite("finished_sending", &ModelRunnerOutput::finished_sending)
-      .def_readwrite("finished_recving", &ModelRunnerOutput::finished_recving);
+      .def_readwrite("finished_recving", &ModelRunnerOutput::finished_recving)
+      .def_readwrite("num_recompute", &ModelRunnerOutput::num_recompute);
   py::class_<DraftTokenIds>(m, "DraftTokenIds")
       .def(py::init<>())
       .def_readwrite("req_ids", &DraftTokenIds::req_ids)

@@ -370,6 +370,13 @@ EngineCoreOutputs Scheduler::update_from_output(const SchedulerOutput& so,
         if (so_ && req->use_structured_output) so_->rollback(*req, 0);
       }
     }
+    {
+      auto rc = mro.num_recompute.find(p.first);
+      if (rc != mro.num_recompute.end() && rc->second > 0) {
+        // kept tokens whose recurrent state was rolled back: they run again with the next step
+        req->num_computed_tokens -= std::min(rc->second, req->num_computed_tokens);
+      }
+    }
     bool stopped = false;
     if (!generated.empty()) update_request_with_output(*req, generated, stopped);
 

@@ -228,6 +228,10 @@ struct ModelRunnerOutput {
   std::vector<std::vector<LogprobsRow>> logprobs;       // optional, per request per token
   std::vector<int> num_nans_in_logits;
   std::set<std::string> finished_sending, finished_recving;
+  // Speculative decoding on models with recurrent state: a rejected draft has advanced the state
+  // past the tokens that were kept, so the runner restores the state it saved before the step and
+  // asks for the kept tokens of the step (this many) to be computed again with the next one.
+  std::map<std::string, int> num_recompute;
   bool empty() const { return req_ids.empty(); }
 };
 

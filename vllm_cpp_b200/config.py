@@ -78,6 +78,7 @@ class ModelConfig:
     scoring_func: str = "softmax"
     topk_method: str = "greedy"
     n_group: int = 1
+    mtp_num_hidden_layers: int = 0            # decoder blocks of the multi-token-prediction head (0: none in the checkpoint)
     topk_group: int = 1
     # MLA
     kv_lora_rank: int = 0
@@ -194,6 +195,7 @@ def model_config_from_hf(cfg: dict) -> ModelConfig:
         m.scoring_func = t.get("scoring_func", "softmax")
         m.topk_method = t.get("topk_method", "greedy")
         m.n_group = int(t.get("n_group") or 1)
+        m.mtp_num_hidden_layers = int(t.get("mtp_num_hidden_layers") or 0)
         m.topk_group = int(t.get("topk_group") or 1)
         m.rope.neox = False
         if m.rope.scaling_type == "yarn":

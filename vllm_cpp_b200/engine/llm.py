@@ -80,8 +80,19 @@ class LLM:
         if torch.device(device).type == "cpu" and args.cpu_backend == "native":
             from ..models.backend import CpuNativeBackend
             self.model.be = CpuNativeBackend(device)
+        mtp_tensors: dict = {}
         if tensors is not None:
-            self.model.load_weights(tensors)
+            want_mtp = args.speculative_config is not None and args.speculative_config.method == "mtp"
+
+            def trunk_only(it):
+                # the draft head's tensors ride in the same checkpoint; they are set aside here
+                for name, t in it:
+                    if name.startswith(("mtp.", "model.mtp.")):
+                        if want_mtp:
+                            mtp_tensors[name] = t
+                        continue
+                    yield name, t
+            self.model.load_weights(trunk_only(tensors))
         else:
             self.model.init_random(args.seed)
         if getattr(cfg, "quant", None) == "nvfp4" and getattr(args, "quantize", True) \
@@ -108,12 +119,24 @@ class LLM:
         channel = self._make_step_channel(par) if (par.driver_worker and par.tensor_parallel_size > 1) else None
         use_async = args.async_scheduling if args.async_scheduling is not None else False
         spec = args.speculative_config
-        if spec is not None and spec.method == "ngram":
+        if spec is not None and spec.method in ("ngram", "mtp"):
             use_async = False       # drafts are verified on the host between steps
+        if spec is not None and spec.method == "mtp":
+            if not hasattr(self.model, "is_gdn") or par.tensor_parallel_size > 1:
+                raise ValueError("method 'mtp' needs a model with a multi-token-prediction head "
+                                 "(the Qwen3.5 / 3.6 / Qwen3-Next hybrids) on one rank")
         self.runner = ModelRunner(self.model, block_size=args.block_size, num_blocks=num_blocks,
                                   max_num_seqs=args.max_num_seqs, max_num_batched_tokens=budget,
                                   max_model_len=max_len, enable_cuda_graphs=args.enable_cuda_graphs,
                                   async_mode=use_async, speculative_config=spec, step_channel=channel)
+        if spec is not None and spec.method == "mtp":
+            from ..models.gdn_mtp import Qwen35MTP
+            mtp = Qwen35MTP(self.model, getattr(cfg, "mtp_num_hidden_layers", 1) or 1)
+            if mtp_tensors:
+                mtp.load_weights(iter(mtp_tensors.items()))
+            else:
+                mtp.init_random(args.seed)
+            self.runner.attach_mtp(mtp)
         sc = E.SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=args.max_num_seqs,
                                max_model_len=max_len, policy=args.scheduling_policy,
                                async_scheduling=use_async,

@@ -299,6 +299,31 @@ class Qwen35Model(DenseModel):
     def kv_bytes_per_block(self, block_size: int) -> int:
         return len(self.attn_layers) * 2 * block_size * self.hkv * self.D * 2
 
+    # ---- recurrent state across a speculative step
+    def snapshot_state(self, slots: list) -> None:
+        """Saves the convolution and recurrent state of the given request slots. A step that
+        verifies draft tokens advances the state over all of them; when some are rejected there is
+        nothing to subtract, so the runner restores this copy and has the kept tokens run again."""
+        if not slots or not self.gdn_layers:
+            return
+        if not getattr(self, "_snap", None):
+            self._snap = {l: (torch.empty_like(self.conv_state[l]), torch.empty_like(self.ssm_state[l]))
+                          for l in self.gdn_layers}
+        idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+        for l in self.gdn_layers:
+            c, s = self._snap[l]
+            c.index_copy_(0, idx, self.conv_state[l].index_select(0, idx))
+            s.index_copy_(0, idx, self.ssm_state[l].index_select(0, idx))
+
+    def restore_state(self, slots: list) -> None:
+        if not slots or not self.gdn_layers:
+            return
+        idx = torch.tensor(slots, dtype=torch.long, device=self.device)
+        for l in self.gdn_layers:
+            c, s = self._snap[l]
+            self.conv_state[l].index_copy_(0, idx, c.index_select(0, idx))
+            self.ssm_state[l].index_copy_(0, idx, s.index_select(0, idx))
+
     def state_bytes_per_request(self) -> int:
         return len(self.gdn_layers) * (self.conv_dim * 3 * 2 + self.gv * 128 * 128 * 4)
 
@@ -561,12 +586,17 @@ class Qwen35Model(DenseModel):
         attn = self.bufs.get("attn", T, self.hq * D)
         gate_up = self.bufs.get("gate_up", T, 2 * self.inter)
         act = self.bufs.get("act", T, self.inter)
-        e = be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
-                         vocab_total=c.vocab_size)
-        if e is not hidden:
-            hidden.copy_(e)
-        if self.tp > 1:
-            self.comm.all_reduce(hidden)
+        given = ctx.extra.get("inputs_embeds")
+        if given is not None:
+            # a draft head runs this stack on its own input rows instead of token embeddings
+            hidden.copy_(given[:T])
+        else:
+            e = be.embedding(ctx.input_ids[:T], self.w["embed"], out=hidden, vocab_start=self.vocab_start,
+                             vocab_total=c.vocab_size)
+            if e is not hidden:
+                hidden.copy_(e)
+            if self.tp > 1:
+                self.comm.all_reduce(hidden)
         pos = ctx.positions[:T]
         meta = self._step_meta(ctx, T)
         k_off = 2 * self.hq * D
@@ -617,6 +647,7 @@ class Qwen35Model(DenseModel):
             if self.tp > 1:
                 self.comm.all_reduce(hidden)
         full = be.rmsnorm(hidden, self.w["final_norm"], eps, residual=resid, out=normed, gemma=True)
+        self.last_full = full          # every row after the final norm: what a draft head continues from
         if ctx.decode_only_full_logits:
             n, last = T, full
         else:

@@ -67,9 +67,16 @@ class ModelRunner(E.ModelRunnerBase):
         # Speculative decoding, n-gram (prompt lookup) drafts verified by argmax comparison:
         # a request scheduled with k drafts runs k + 1 query tokens, gets k + 1 logits rows and
         # keeps the longest prefix of drafts that the target agrees with plus one more token.
+        # "mtp": the drafts come from the model's multi-token-prediction head instead (one per
+        # step, models/gdn_mtp.py), verified the same way.
         self.spec = speculative_config if (speculative_config is not None and
-                                           speculative_config.method == "ngram") else None
+                                           speculative_config.method in ("ngram", "mtp")) else None
         self.max_spec = self.spec.num_speculative_tokens if self.spec else 0
+        if self.spec is not None and self.spec.method == "mtp":
+            self.max_spec = 1            # the head predicts one token past the trunk's
+        self.mtp = None
+        self.mtp_proposed: dict[str, list[int]] = {}     # every draft the head proposed, per request
+        self._last_ctx = None
         self._drafts: dict[str, list[int]] = {}
         self._scheduled_spec: dict[str, list[int]] = {}
         self.spec_stats = {"drafted": 0, "accepted": 0}
@@ -334,6 +341,10 @@ class ModelRunner(E.ModelRunnerBase):
                 {"kind": "step", "pad": pad, "plain": plain_greedy,
                  "info": {f: _plain(getattr(info, f)) for f in STEP_INFO_FIELDS},
                  "buf": self.host_buf.numpy().tobytes()})
+        if self.spec is not None and hasattr(self.model, "snapshot_state"):
+            # requests that verify drafts in this step: their recurrent state is saved first
+            slots = [int(self.host_views["state_slots"][r]) for r in range(R) if info.num_draft[r] > 0]
+            self.model.snapshot_state(slots)
         self._launch_step(info, pad, plain_greedy)
 
     def _launch_step(self, info, pad, plain_greedy) -> None:
@@ -371,6 +382,7 @@ class ModelRunner(E.ModelRunnerBase):
             self._graph_sampled = True
         else:
             ctx = self._context(info)
+            self._last_ctx = ctx
             if plain_greedy and self._model_samples_greedy:
                 # the model writes the argmax ids itself (tensor parallel: candidates per vocabulary
                 # shard are exchanged instead of the logits)
@@ -569,6 +581,8 @@ class ModelRunner(E.ModelRunnerBase):
         out = E.ModelRunnerOutput()
         out.req_ids = list(info.req_ids)
         toks = []
+        rollback: list = []
+        recompute: dict = {}
         row = 0
         for r, p in enumerate(info.produces_token):
             if p:
@@ -583,6 +597,11 @@ class ModelRunner(E.ModelRunnerBase):
                     new = [int(ids_host[row + i]) for i in range(acc + 1)]
                     self.spec_stats["drafted"] += k
                     self.spec_stats["accepted"] += acc
+                    if acc < k and hasattr(self.model, "restore_state"):
+                        # the recurrent state has run past the kept tokens: back to the saved
+                        # state, and the kept tokens of this step run again with the next one
+                        rollback.append(int(self.host_views["state_slots"][r]))
+                        recompute[rid] = acc + 1
                 else:
                     new = [int(ids_host[row])]
                 toks.append(new)
@@ -591,7 +610,12 @@ class ModelRunner(E.ModelRunnerBase):
             else:
                 toks.append([])
         out.sampled_token_ids = toks
-        if self.spec is not None:
+        if rollback:
+            self.model.restore_state(rollback)
+            out.num_recompute = recompute          # (assigned whole: the binding copies containers)
+        if self.mtp is not None:
+            self._propose_mtp(info, toks)
+        elif self.spec is not None:
             for r, p in enumerate(info.produces_token):
                 rid = info.req_ids[r]
                 if p:
@@ -600,6 +624,57 @@ class ModelRunner(E.ModelRunnerBase):
                         rid, self.spec.prompt_lookup_min, self.spec.prompt_lookup_max,
                         self.max_spec) if self.batch.plain_greedy(rid) else []
         return out
+
+    def attach_mtp(self, mtp) -> None:
+        """The multi-token-prediction drafter of the model (its blocks get a KV cache over the same
+        block numbers as the trunk's, and activation buffers of the step's size)."""
+        mtp.alloc(self.num_blocks, self.block_size, self.max_tokens, self.max_num_seqs)
+        self.mtp = mtp
+
+    def _propose_mtp(self, info, toks) -> None:
+        """Runs the draft head over the rows of the step that just finished. ``toks``: per request
+        the tokens it kept in this step (accepted drafts plus the trunk's own choice), empty for a
+        request that only prefilled. Every row's "next token" is the following query token, and
+        for the last row a request keeps, the token the trunk chose; rows past it are rejected
+        drafts whose cache entries the next pass over those positions rewrites."""
+        T, R = info.num_tokens, info.num_reqs
+        hv = self.host_views
+        ids = hv["input_ids"][:T]
+        qs = hv["query_start"][: R + 1].tolist()
+        nxt = torch.zeros(T, dtype=torch.int64)
+        if T > 1:
+            nxt[: T - 1] = ids[1:T]
+        rows, rids = [], []
+        for r in range(R):
+            e = qs[r + 1]
+            rid = info.req_ids[r]
+            new = toks[r]
+            if not new:
+                # a prompt chunk that stops short of the prompt's end: the next prompt token is known
+                pos = int(hv["positions"][e - 1])
+                known = self.batch.token_ids(rid)
+                nxt[e - 1] = known[pos + 1] if pos + 1 < len(known) else 0
+                continue
+            base = e - 1 - info.num_draft[r]         # row of the last token the request had
+            for j, t in enumerate(new):
+                nxt[base + j] = t
+            if self.batch.plain_greedy(rid):
+                rows.append(base + len(new) - 1)
+                rids.append(rid)
+            else:
+                self._drafts[rid] = []
+        m = self.mtp
+        m.next_ids[:T].copy_(nxt)
+        n = len(rows)
+        if n:
+            m.rows[:n].copy_(torch.tensor(rows, dtype=torch.int32))
+        # the head runs even when no request wants a draft: its cache must cover every position
+        logits = m.forward(self._last_ctx, m.next_ids, self.model.last_full, m.rows[:max(n, 1)])
+        if n:
+            draft = logits[:n].argmax(-1).tolist()
+            for rid, d in zip(rids, draft):
+                self._drafts[rid] = [int(d)]
+                self.mtp_proposed.setdefault(rid, []).append(int(d))
 
     def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
         info = self._info
