@@ -32,6 +32,7 @@ class RopeConfig:
     long_factor: Optional[list] = None
     mrope_section: Optional[list] = None
     alpha: Optional[float] = None             # dynamic NTK alpha
+    config_max_position: int = 0              # the checkpoint's max_position_embeddings (longrope magnitude scale)
 
 
 @dataclass
@@ -132,8 +133,11 @@ def _rope_from_hf(cfg: dict, head_dim: int) -> RopeConfig:
         r.factor = float(rs.get("factor", 1.0))
         r.low_freq_factor = float(rs.get("low_freq_factor", 1.0))
         r.high_freq_factor = float(rs.get("high_freq_factor", 4.0))
+        # Phi-3 keeps the original window beside rope_scaling, not inside it
         r.original_max_position = int(rs.get("original_max_position_embeddings",
-                                             cfg.get("max_position_embeddings", 8192)))
+                                             cfg.get("original_max_position_embeddings",
+                                                     cfg.get("max_position_embeddings", 8192))))
+        r.config_max_position = int(cfg.get("max_position_embeddings", 0) or 0)
         r.beta_fast = float(rs.get("beta_fast", 32.0))
         r.beta_slow = float(rs.get("beta_slow", 1.0))
         r.mscale = float(rs.get("mscale", 1.0))

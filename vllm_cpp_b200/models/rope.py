@@ -69,8 +69,10 @@ def rope_parameters(cfg: RopeConfig, head_dim: int, max_position: int):
     elif t in ("yarn", "deepseek_yarn"):
         extrap = inv
         interp = inv / cfg.factor
-        lo, hi = _yarn_correction_range(cfg.beta_fast, cfg.beta_slow, rot, cfg.theta,
-                                        cfg.original_max_position)
+        # upstream's multimodal (sectioned) rotary class takes the correction range over the whole
+        # head width, its plain YaRN class over the rotated width; they only differ with partial rotation
+        lo, hi = _yarn_correction_range(cfg.beta_fast, cfg.beta_slow, head_dim if cfg.mrope_section else rot,
+                                        cfg.theta, cfg.original_max_position)
         mask = (1 - _yarn_linear_ramp(lo, hi, rot // 2))
         inv = interp * (1 - mask) + extrap * mask
         if t == "deepseek_yarn":
@@ -94,7 +96,9 @@ def rope_parameters(cfg: RopeConfig, head_dim: int, max_position: int):
         f = cfg.long_factor if use_long else cfg.short_factor
         if f is not None:
             inv = inv / torch.tensor(f, dtype=torch.float64)
-        scale = max_position / cfg.original_max_position
+        # the magnitude correction follows the checkpoint's declared window, whatever length this
+        # engine was sized for (and applies to the short factors too)
+        scale = (cfg.config_max_position or max_position) / cfg.original_max_position
         mscale = 1.0 if scale <= 1.0 else math.sqrt(
             1 + math.log(scale) / math.log(cfg.original_max_position))
     else:

@@ -175,16 +175,16 @@ def ref_post_conv(xc, Hk, Hv, a, b, A_log, dt_bias, eps=1e-6):
 
 
 def ref_recurrent(q, k, v, g, beta, state0):
-    """Sequential gated delta rule for ONE sequence. q, k: [L, Hk, 128]; v: [L, Hv, 128];
-    g, beta: [L, Hv]; state0 fp32 [Hv, Dv, Dk]. Returns (o fp32 [L, Hv, 128], state)."""
+    """Sequential gated delta rule for ONE sequence. q, k: [L, Hk, Dk]; v: [L, Hv, Dv];
+    g, beta: [L, Hv]; state0 fp32 [Hv, Dv, Dk]. Returns (o fp32 [L, Hv, Dv], state)."""
     L, Hk, D = q.shape
-    Hv = v.shape[1]
+    Hv, Dv = v.shape[1], v.shape[2]
     rep = Hv // Hk
     S = state0.clone().float()
     qf = q.float().repeat_interleave(rep, 1) * (D ** -0.5)
     kf = k.float().repeat_interleave(rep, 1)
     vf = v.float()
-    o = torch.empty(L, Hv, D, dtype=torch.float32, device=q.device)
+    o = torch.empty(L, Hv, Dv, dtype=torch.float32, device=q.device)
     for t in range(L):
         S = S * torch.exp(g[t]).view(Hv, 1, 1)
         kv = torch.einsum("hvk,hk->hv", S, kf[t])
