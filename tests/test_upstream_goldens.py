@@ -313,3 +313,73 @@ def test_gated_attention(case):
     attn = torch.einsum("hts,shd->thd", torch.softmax(s, -1), vf)
     close(attn, t["attn"], m["tol"])
     close((attn * torch.sigmoid(t["gate"])).reshape(T, -1), t["out"], m["tol"])
+
+
+def test_gdn_prefill_bf16_against_the_chunked_oracle():
+    """bf16 inputs, upstream's chunked kernel as the oracle, one sequence with and one without an
+    initial state: the sequential restatement at the recorded bf16 tolerance, and the CPU backend's
+    native recurrence on the same vectors."""
+    from vllm_cpp_b200.ops.gdn import ref_recurrent
+    m, t = load("gdn_prefill_bf16_realdims")
+    a = m["args"]
+    qsl = t["query_start_loc"].tolist()
+    init = a["with_initial_state"]
+    outs, states = [], []
+    for i in range(len(qsl) - 1):
+        b, e = qsl[i], qsl[i + 1]
+        s0 = t["state_in"][i].float() if init[i] else torch.zeros_like(t["state_out"][i])
+        o, s1 = ref_recurrent(t["q"][b:e], t["k"][b:e], t["v"][b:e], t["g"][b:e].float(), t["beta"][b:e].float(), s0)
+        outs.append(o)
+        states.append(s1)
+    close(torch.cat(outs, 0), t["out"], m["tol"])
+    close(torch.stack(states, 0), t["state_out"], m["tol"])
+    from vllm_cpp_b200.ops import cpu_native as N
+    ssm = torch.stack([t["state_in"][i].float() if init[i] else torch.zeros_like(t["state_out"][i])
+                       for i in range(len(init))], 0).contiguous()
+    out = N.gdn_recurrent(t["q"].to(torch.bfloat16).contiguous(), t["k"].to(torch.bfloat16).contiguous(),
+                          t["v"].to(torch.bfloat16).contiguous(), t["g"].float().contiguous(),
+                          t["beta"].float().contiguous(), ssm, qsl, list(range(len(init))), [1] * len(init))
+    close(out.float(), t["out"], {"atol": 1e-2, "rtol": 1e-2})
+    close(ssm, t["state_out"], {"atol": 1e-2, "rtol": 1e-2})
+
+
+def test_gdn_packed_decode_gating_and_step():
+    """One decode step of the packed kernel's contract: g = -exp(A_log) * softplus(a + dt_bias),
+    beta = sigmoid(b), q / k L2-normalised in the kernel, bf16 state in and out."""
+    from vllm_cpp_b200.ops.gdn import ref_post_conv, ref_recurrent
+    m, t = load("gdn-packed-decode-oracle")
+    a = m["args"]
+    Hk, Hv, B = a["Hk"], a["Hv"], a["batch"]
+    qn, kn, g, beta = ref_post_conv(t["mixed_qkv"], Hk, Hv, t["a"], t["b"], t["A_log"], t["dt_bias"])
+    close(g, t["g"], {"atol": 2e-3, "rtol": 2e-3})
+    close(beta, t["beta_full_f32"], {"atol": 2e-3, "rtol": 2e-3})
+    v = t["mixed_qkv"][:, 2 * Hk * 128:].reshape(B, Hv, 128)
+    assert torch.equal(v, t["v"])
+    idx = t["state_indices"].tolist()
+    for i in range(B):
+        o, s1 = ref_recurrent(qn[i: i + 1], kn[i: i + 1], v[i: i + 1], g[i: i + 1], beta[i: i + 1],
+                              t["state_in"][idx[i]].float())
+        close(o[0], t["out"][i], {"atol": 2e-2, "rtol": 2e-2})
+        close(s1, t["state_out"][idx[i]], {"atol": 2e-2, "rtol": 2e-2})
+
+
+def test_moe_block_bf16_layer_contract():
+    """The sparse-MoE block of the hybrid MoE models in bf16 (router, routed experts, gated shared
+    expert): this engine's restatement and its CPU kernels against upstream's layer output."""
+    from vllm_cpp_b200.ops import cpu_native as N
+    from vllm_cpp_b200.ops.moe import ref_moe_block, ref_router_topk
+    m, t = load("moe_block_bf16_small")
+    a = m["args"]
+    x = t["x"]
+    logits = x.float() @ t["gate_w"].float().t()
+    ids, w = ref_router_topk(logits, a["top_k"], renorm=a["renormalize"], scoring=a["scoring_func"])
+    assert torch.equal(ids.to(torch.int32), t["topk_ids"])
+    routed = ref_moe_block(x, ids, w, t["w13"], t["w2"])
+    S = a["shared_intermediate"]
+    sgu = (x.float() @ t["w_shared_gate_up"].float().t()).to(torch.bfloat16).float()
+    act = (torch.nn.functional.silu(sgu[:, :S]) * sgu[:, S:]).to(torch.bfloat16).float()
+    shared = (act @ t["w_shared_down"].float().t()) * torch.sigmoid(x.float() @ t["w_shared_gate"].float().t())
+    close(routed.float() + shared, t["out"], m["tol"])
+    native = N.moe_experts(x.contiguous(), ids.to(torch.int32), w.float(), t["w13"].contiguous(), t["w2"].contiguous(),
+                           e0=0, act_kind=0)
+    close(native.float() + shared, t["out"], m["tol"])
