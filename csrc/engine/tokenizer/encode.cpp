@@ -145,7 +145,9 @@ void Tokenizer::encode_segment(const std::string& text, bool first_segment, std:
     return;
   }
   const std::string norm = normalize(text, first_segment);
-  if (sp_metaspace_) {
+  if (sp_metaspace_ && !sp_metaspace_split_) {
+    bpe_word(norm, out);        // one piece: runs of markers merge ("▁▁", "▁▁▁" are vocabulary entries)
+  } else if (sp_metaspace_) {
     // split before every marker; the marker stays with the piece that follows it
     size_t start = 0;
     for (size_t pos = norm.find(kMeta, 1); pos != std::string::npos; pos = norm.find(kMeta, pos + 3)) {

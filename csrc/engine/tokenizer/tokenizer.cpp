@@ -152,6 +152,7 @@ std::unique_ptr<Tokenizer> Tokenizer::from_hf_json(const std::string& tokenizer_
     const std::string& scheme = pt["prepend_scheme"].as_string();
     t->sp_prepend_ = scheme.empty() ? pt["add_prefix_space"].as_bool(true) : (scheme != "never");
     t->sp_prepend_first_only_ = (scheme == "first");
+    t->sp_metaspace_split_ = pt["split"].as_bool(true);
   }
 
   // normalizer

@@ -128,6 +128,7 @@ class Tokenizer {
   bool sp_prepend_ = false;           // normalizer prepends U+2581 to the text
   bool sp_replace_space_ = false;     // normalizer maps ' ' to U+2581
   bool sp_metaspace_ = false;         // Metaspace pre-tokenizer (split on U+2581)
+  bool sp_metaspace_split_ = true;    // "split": false keeps the text whole, so merges may span markers
   bool sp_prepend_first_only_ = false;  // marker only before the first segment of the text
   bool dec_strip_leading_space_ = false;
   bool nfc_ = false;

@@ -383,3 +383,21 @@ def test_moe_block_bf16_layer_contract():
     native = N.moe_experts(x.contiguous(), ids.to(torch.int32), w.float(), t["w13"].contiguous(), t["w2"].contiguous(),
                            e0=0, act_kind=0)
     close(native.float() + shared, t["out"], m["tol"])
+
+
+# ------------------------------------------------------------------ tokenizer
+def test_tokenizer_against_recorded_encodings():
+    """A SentencePiece-style BPE tokenizer file with byte fallback (Metaspace pre-tokenizer that
+    does not split, so runs of spaces merge) and the ids / decoded text the HF tokenizers library
+    produced for a corpus of edge cases: byte-exact both ways."""
+    from vllm_cpp_b200 import _engine as E
+    d = G / "tokenizer_mistral"
+    if not (d / "tokenizer.json").exists():
+        pytest.skip("this set of goldens has no tokenizer file")
+    tok = E.Tokenizer.from_hf_json((d / "tokenizer.json").read_text(encoding="utf-8"), "")
+    rec = json.loads((d / "encodings.json").read_text(encoding="utf-8"))
+    assert tok.bos_id == rec["bos_id"]
+    for ent in rec["entries"]:
+        assert list(tok.encode(ent["text"], False)) == ent["ids"], ent["text"]
+        assert list(tok.encode(ent["text"], True)) == ent["ids_special"], ent["text"]
+        assert tok.decode(ent["ids"], False) == ent["decode"], ent["text"]
