@@ -14,6 +14,7 @@
 #include "core/scheduler.h"
 #include "offload/lmcache.h"
 #include "offload/offload.h"
+#include "parallel/eplb.h"
 #include "worker/input_batch.h"
 
 using namespace b200;
@@ -41,6 +42,8 @@ class FakeRunner : public ModelRunnerBase {
         const int n = 1 + (info_.num_draft[r] ? (int)(rng_() % (info_.num_draft[r] + 1)) : 0);
         for (int i = 0; i < n; ++i) toks.push_back((int32_t)(rng_() % 1000));
         batch_.append_sampled(info_.req_ids[r], toks);
+        // a runner with recurrent state: every rejection has the kept tokens of the step run again
+        if (recompute_ && info_.num_draft[r] && n <= info_.num_draft[r]) out.num_recompute[info_.req_ids[r]] = n;
         drafts_.req_ids.push_back(info_.req_ids[r]);
         drafts_.draft_token_ids.push_back(batch_.propose_ngram(info_.req_ids[r], 1, 3, 2));
       }
@@ -63,6 +66,9 @@ class FakeRunner : public ModelRunnerBase {
   bool has_ = false;
   DraftTokenIds drafts_;
   std::mt19937 rng_{7};
+
+ public:
+  bool recompute_ = false;
 };
 
 static int run_engine(bool priority, int num_blocks) {
@@ -79,6 +85,7 @@ static int run_engine(bool priority, int num_blocks) {
   spec.block_size = block;
   kv.groups.push_back(KVCacheGroupSpec{{"layer0"}, spec});
   FakeRunner runner(max_reqs, max_len, budget, block);
+  runner.recompute_ = priority;        // one of the two runs rolls state back on rejected drafts
   Executor exec(&runner, 1);
   EngineCore core(std::make_unique<Scheduler>(sc, kv), &exec);
   std::mt19937 rng(3);
@@ -148,8 +155,37 @@ static int run_offload_and_lmcache() {
   return (k2 == k && v2 == v) ? 0 : 1;
 }
 
+static int run_eplb() {
+  std::mt19937 rng(11);
+  const int cfgs[][6] = {{3, 64, 72, 8, 1, 8}, {2, 12, 16, 4, 2, 8}, {1, 8, 8, 1, 1, 2}, {4, 60, 64, 3, 1, 4},
+                         {2, 128, 160, 8, 2, 8}};
+  for (auto& c : cfgs) {
+    const int L = c[0], E = c[1], P = c[2];
+    std::vector<double> loads((size_t)L * E);
+    for (double& v : loads) v = (double)(rng() % 1000);
+    EplbPlacement p = eplb_rebalance(loads, L, E, P, c[3], c[4], c[5]);
+    for (int l = 0; l < L; ++l) {
+      std::vector<int> seen(E, 0);
+      for (int s = 0; s < P; ++s) {
+        const int e = p.phy2log[(size_t)l * P + s];
+        if (e < 0 || e >= E) return 1;
+        seen[e]++;
+      }
+      for (int e = 0; e < E; ++e)
+        if (seen[e] != p.logcnt[(size_t)l * E + e] || seen[e] < 1) return 1;
+    }
+  }
+  try {
+    eplb_rebalance(std::vector<double>(8, 1.0), 1, 8, 9, 1, 1, 2);
+    return 1;
+  } catch (const std::invalid_argument&) {
+  }
+  return 0;
+}
+
 int main() {
   int rc = 0;
+  rc |= run_eplb();
   rc |= run_engine(false, 64);
   rc |= run_engine(true, 24);      // few blocks: preemption and recompute
   rc |= run_offload_and_lmcache();
