@@ -557,6 +557,9 @@ def build_arg_parser() -> argparse.ArgumentParser:
                     help="engine replicas (one per GPU) behind this server; a request goes to the least loaded one")
     ap.add_argument("--enable-expert-parallel", action="store_true",
                     help="MoE models: experts are split over the ranks instead of sharded")
+    ap.add_argument("--speculative-config", default=None,
+                    help='JSON, e.g. {"method": "ngram", "num_speculative_tokens": 3, "prompt_lookup_max": 4} '
+                         'or {"method": "mtp", "num_speculative_tokens": 1}')
     ap.add_argument("--enable-eplb", action="store_true",
                     help="expert parallel: rebalance the expert placement from observed loads")
     ap.add_argument("--eplb-redundant-experts", type=int, default=0,
@@ -575,6 +578,13 @@ def main(argv=None) -> int:
               max_num_batched_tokens=a.max_num_batched_tokens,
               gpu_memory_utilization=a.gpu_memory_utilization, async_scheduling=a.async_scheduling,
               enable_prefix_caching=a.enable_prefix_caching)
+    if a.speculative_config:
+        import json as _json
+        from ..spec_decode import SpeculativeConfig
+        try:
+            kw["speculative_config"] = SpeculativeConfig(**_json.loads(a.speculative_config))
+        except (TypeError, ValueError) as e:
+            raise SystemExit(f"--speculative-config: {e}")
     kw["parallel"] = ParallelConfig(tensor_parallel_size=max(1, a.tensor_parallel_size),
                                     enable_expert_parallel=a.enable_expert_parallel,
                                     enable_eplb=a.enable_eplb, eplb_redundant_experts=a.eplb_redundant_experts,
