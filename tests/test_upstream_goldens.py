@@ -19,7 +19,8 @@ def _goldens_dir():
     env = os.environ.get("B200_GOLDENS_DIR")
     cands = [Path(env)] if env else []
     here = Path(__file__).resolve()
-    cands += [here.parents[2] / "reference" / "tests" / "parity" / "goldens"]
+    if len(here.parents) > 2:
+        cands += [here.parents[2] / "reference" / "tests" / "parity" / "goldens"]
     for c in cands:
         if c.is_dir():
             return c
