@@ -402,3 +402,27 @@ def test_tokenizer_against_recorded_encodings():
         assert list(tok.encode(ent["text"], False)) == ent["ids"], ent["text"]
         assert list(tok.encode(ent["text"], True)) == ent["ids_special"], ent["text"]
         assert tok.decode(ent["ids"], False) == ent["decode"], ent["text"]
+
+
+@pytest.mark.parametrize("case", ["long_rope_yarn_mrope_bf16_interleaved", "long_rope_yarn_mrope_f32_contiguous"])
+def test_sectioned_rotary_positions(case):
+    """Three position streams (temporal, height, width) over sections of the frequencies, in the
+    contiguous and the interleaved layout, on a YaRN table."""
+    from vllm_cpp_b200.models.rope import mrope_cos_sin, rope_parameters
+    from vllm_cpp_b200.ops import reference as R
+    m, t = load(case)
+    a = m["args"]
+    p = a["rope_parameters"]
+    cfg = _rope_cfg(p, a["is_neox_style"])
+    D, hq, hkv = a["head_size"], a["num_q_heads"], a["num_kv_heads"]
+    rot = cfg.rotary_dim or D
+    inv, msc, _ = rope_parameters(cfg, D, a["max_position"])
+    want_table = t["cos_sin_cache"].float()
+    table = R.rope_table(inv, want_table.shape[0], msc)[:, :rot]
+    close(table, want_table, m["tol"])
+    cos, sin = mrope_cos_sin(table, t["positions"], p["mrope_section"], bool(p.get("mrope_interleaved")))
+    T = t["positions"].shape[-1]
+    q = R.apply_rope(t["q_in"].float().reshape(T, hq, D), cos, sin, rot, a["is_neox_style"])
+    k = R.apply_rope(t["k_in"].float().reshape(T, hkv, D), cos, sin, rot, a["is_neox_style"])
+    close(q.reshape(T, -1), t["q_out"], m["tol"])
+    close(k.reshape(T, -1), t["k_out"], m["tol"])

@@ -118,3 +118,31 @@ def softmax_scale(cfg: RopeConfig, qk_head_dim: int) -> float:
 def mrope_positions(positions: torch.Tensor) -> torch.Tensor:
     """Text-only MRoPE: the three position streams coincide."""
     return positions.unsqueeze(0).expand(3, -1)
+
+
+def mrope_cos_sin(table: torch.Tensor, positions: torch.Tensor, sections, interleaved: bool = False):
+    """cos / sin rows [T, rot/2] for sectioned rotary positions. ``table`` [max_pos, rot] holds
+    [cos | sin] per position; ``positions`` is [T] (text: one stream) or [3, T] (temporal, height,
+    width); ``sections`` gives how many of the rot/2 frequencies follow each stream. Contiguous
+    layout: the first ``sections[0]`` frequencies take the temporal position, the next the
+    height, the rest the width. Interleaved layout: frequency i takes stream i % 3 while that
+    stream still has frequencies left (i < 3 * sections[stream]), else the temporal one.
+    Reference: src/vllm/model_executor/layers/rotary_embedding/mrope.cpp."""
+    half = table.shape[1] // 2
+    if positions.dim() == 1:
+        rows = table[positions]
+        return rows[:, :half], rows[:, half:]
+    assert positions.shape[0] == 3 and sum(sections) == half
+    per = table[positions]                                   # [3, T, rot]
+    stream = torch.zeros(half, dtype=torch.long)
+    if interleaved:
+        for i in range(half):
+            st = i % 3
+            stream[i] = st if (st > 0 and i < 3 * sections[st]) else 0
+    else:
+        stream = torch.repeat_interleave(torch.arange(3), torch.tensor(list(sections)))
+    idx = stream.to(table.device)
+    f = torch.arange(half, device=table.device)
+    cos = per[idx, :, f].t()                                 # [T, half]
+    sin = per[idx, :, half + f].t()
+    return cos, sin
