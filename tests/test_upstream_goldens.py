@@ -139,7 +139,10 @@ def _rope_cfg(p, neox):
                    original_max_position=p.get("original_max_position_embeddings", 8192),
                    beta_fast=p.get("beta_fast", 32.0), beta_slow=p.get("beta_slow", 1.0),
                    attn_factor=p.get("attn_factor", 1.0), short_factor=p.get("short_factor"),
-                   long_factor=p.get("long_factor"), mrope_section=p.get("mrope_section"), alpha=p.get("alpha"))
+                   long_factor=p.get("long_factor"), mrope_section=p.get("mrope_section"), alpha=p.get("alpha"),
+                   truncate=p.get("truncate", True), extrapolation_factor=p.get("extrapolation_factor", 1.0),
+                   apply_yarn_scaling=p.get("apply_yarn_scaling", True), short_mscale=p.get("short_mscale"),
+                   long_mscale=p.get("long_mscale"))
     return c
 
 
@@ -147,7 +150,8 @@ LONG_ROPE = ["long_rope_llama3_neox_f32_bands", "long_rope_llama3_neox_f32_equal
              "long_rope_llama3_gptj_bf16_bands", "long_rope_yarn_neox_bf16", "long_rope_yarn_neox_f32_truncate",
              "long_rope_dynamic_alpha_neox_f32", "long_rope_dynamic_factor1_neox_f32",
              "long_rope_dynamic_factor_gptj_bf16", "long_rope_phi3_neox_f32_short", "long_rope_phi3_neox_bf16_long",
-             "long_rope_yarn_mrope_f32_text_1d"]
+             "long_rope_yarn_mrope_f32_text_1d", "long_rope_yarn_gptj_f32_untruncated_no_mscale",
+             "long_rope_phi3_neox_f32_mscale_override"]
 
 
 @pytest.mark.parametrize("case", LONG_ROPE)
@@ -159,8 +163,6 @@ def test_long_context_rope(case):
     m, t = load(case)
     a = m["args"]
     p = a["rope_parameters"]
-    if p.get("truncate") is False or "mscale_override" in case:
-        pytest.skip("variant outside the configurations the engine's models use")
     cfg = _rope_cfg(p, a["is_neox_style"])
     D, hq, hkv = a["head_size"], a["num_q_heads"], a["num_kv_heads"]
     rot = cfg.rotary_dim or D

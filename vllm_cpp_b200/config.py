@@ -33,6 +33,11 @@ class RopeConfig:
     mrope_section: Optional[list] = None
     alpha: Optional[float] = None             # dynamic NTK alpha
     config_max_position: int = 0              # the checkpoint's max_position_embeddings (longrope magnitude scale)
+    short_mscale: Optional[float] = None      # longrope: explicit magnitude scales, when the checkpoint gives them
+    long_mscale: Optional[float] = None
+    truncate: bool = True                     # YaRN: round the correction range outward to whole dimensions
+    extrapolation_factor: float = 1.0         # YaRN: weight of the unscaled frequencies inside the ramp
+    apply_yarn_scaling: bool = True           # YaRN: False keeps only attn_factor as the magnitude scale
 
 
 @dataclass
@@ -147,6 +152,10 @@ def _rope_from_hf(cfg: dict, head_dim: int) -> RopeConfig:
         r.long_factor = rs.get("long_factor")
         r.mrope_section = rs.get("mrope_section")
         r.alpha = rs.get("alpha")
+        r.short_mscale, r.long_mscale = rs.get("short_mscale"), rs.get("long_mscale")
+        r.truncate = bool(rs.get("truncate", True))
+        r.extrapolation_factor = float(rs.get("extrapolation_factor", 1.0))
+        r.apply_yarn_scaling = bool(rs.get("apply_yarn_scaling", True))
     return r
 
 

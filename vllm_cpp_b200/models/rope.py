@@ -32,9 +32,11 @@ def _yarn_find_correction_dim(num_rot, dim, base, max_pos):
     return (dim * math.log(max_pos / (num_rot * 2 * math.pi))) / (2 * math.log(base))
 
 
-def _yarn_correction_range(low_rot, high_rot, dim, base, max_pos):
-    low = math.floor(_yarn_find_correction_dim(low_rot, dim, base, max_pos))
-    high = math.ceil(_yarn_find_correction_dim(high_rot, dim, base, max_pos))
+def _yarn_correction_range(low_rot, high_rot, dim, base, max_pos, truncate=True):
+    low = _yarn_find_correction_dim(low_rot, dim, base, max_pos)
+    high = _yarn_find_correction_dim(high_rot, dim, base, max_pos)
+    if truncate:
+        low, high = math.floor(low), math.ceil(high)
     return max(low, 0), min(high, dim - 1)
 
 
@@ -72,10 +74,12 @@ def rope_parameters(cfg: RopeConfig, head_dim: int, max_position: int):
         # upstream's multimodal (sectioned) rotary class takes the correction range over the whole
         # head width, its plain YaRN class over the rotated width; they only differ with partial rotation
         lo, hi = _yarn_correction_range(cfg.beta_fast, cfg.beta_slow, head_dim if cfg.mrope_section else rot,
-                                        cfg.theta, cfg.original_max_position)
-        mask = (1 - _yarn_linear_ramp(lo, hi, rot // 2))
+                                        cfg.theta, cfg.original_max_position, cfg.truncate)
+        mask = (1 - _yarn_linear_ramp(lo, hi, rot // 2)) * cfg.extrapolation_factor
         inv = interp * (1 - mask) + extrap * mask
-        if t == "deepseek_yarn":
+        if not cfg.apply_yarn_scaling:
+            mscale = cfg.attn_factor
+        elif t == "deepseek_yarn":
             mscale = (yarn_get_mscale(cfg.factor, cfg.mscale) /
                       yarn_get_mscale(cfg.factor, cfg.mscale_all_dim)) * cfg.attn_factor
         else:
@@ -101,6 +105,9 @@ def rope_parameters(cfg: RopeConfig, head_dim: int, max_position: int):
         scale = (cfg.config_max_position or max_position) / cfg.original_max_position
         mscale = 1.0 if scale <= 1.0 else math.sqrt(
             1 + math.log(scale) / math.log(cfg.original_max_position))
+        given = cfg.long_mscale if use_long else cfg.short_mscale
+        if given is not None:
+            mscale = float(given)
     else:
         raise ValueError(f"unknown rope scaling type {t}")
     return inv, float(mscale), int(table_len)
