@@ -674,6 +674,8 @@ class ModelRunner(E.ModelRunnerBase):
             draft = logits[:n].argmax(-1).tolist()
             for rid, d in zip(rids, draft):
                 self._drafts[rid] = [int(d)]
+                if len(self.mtp_proposed) > 256:          # a debugging aid, not a log: keep it small
+                    self.mtp_proposed.clear()
                 self.mtp_proposed.setdefault(rid, []).append(int(d))
 
     def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
