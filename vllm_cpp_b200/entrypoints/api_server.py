@@ -557,6 +557,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
                     help="engine replicas (one per GPU) behind this server; a request goes to the least loaded one")
     ap.add_argument("--enable-expert-parallel", action="store_true",
                     help="MoE models: experts are split over the ranks instead of sharded")
+    ap.add_argument("--no-warmup", action="store_true",
+                    help="skip the pre-serve warm-up (decode graphs are then captured by the first steps that need them)")
     ap.add_argument("--speculative-config", default=None,
                     help='JSON, e.g. {"method": "ngram", "num_speculative_tokens": 3, "prompt_lookup_max": 4} '
                          'or {"method": "mtp", "num_speculative_tokens": 1}')
@@ -590,6 +592,10 @@ def main(argv=None) -> int:
                                     enable_eplb=a.enable_eplb, eplb_redundant_experts=a.eplb_redundant_experts,
                                     eplb_interval=a.eplb_interval, eplb_window=a.eplb_window)
     llm, _workers = launch_engine(EngineArgs(**{k: v for k, v in kw.items() if v is not None}))
+    if not a.no_warmup and llm.runner.is_cuda and a.tensor_parallel_size <= 1:
+        # capture the decode graphs of every padded batch size before the first request arrives
+        # (tensor-parallel engines capture in lockstep inside their first steps instead)
+        llm.runner.warmup_graphs()
     replicas = []
     if a.data_parallel_size > 1:
         if a.tensor_parallel_size > 1:
