@@ -93,10 +93,12 @@ def test_mtp_head_drafts_keep_the_greedy_tokens():
     cfg = synthetic_config("tiny-gdn")
     prompts = _prompts(cfg, 5)
     base, lb = _run(cfg, prompts, None)
-    for budget in (256, 32):
-        got, llm = _run(cfg, prompts, SpeculativeConfig(method="mtp", num_speculative_tokens=1), budget)
+    for k, budget in ((1, 256), (1, 32), (3, 48)):
+        got, llm = _run(cfg, prompts, SpeculativeConfig(method="mtp", num_speculative_tokens=k), budget)
         _same(got, llm, base, lb)
         assert llm.runner.spec_stats["drafted"] > 0 and llm.runner.mtp is not None
+        # chains of k drafts: the head continues from its own hidden state for drafts two to k
+        assert all(len(d) % k == 0 for d in llm.runner.mtp_proposed.values())
     # the head's cache does not depend on how the prompt was chunked: the same drafts either way
     def drafts(budget):
         _, llm = _run(cfg, prompts[:1], SpeculativeConfig(method="mtp", num_speculative_tokens=1), budget, n=3)
@@ -133,3 +135,32 @@ def test_mtp_head_weights_load_from_a_checkpoint_stream():
     assert head.inner.layers[0]["qkv"].shape[1] == H and "final_norm" in head.inner.w
     with pytest.raises(ValueError):
         Qwen35MTP(llm.model).load_weights(iter({"model.embed_tokens.weight": torch.zeros(4, H)}.items()))
+
+
+def test_mtp_chains_are_accepted_when_the_head_agrees_with_the_trunk():
+    """A head rigged to repeat the trunk's own choice (fc passes the trunk's hidden state through,
+    its block adds nothing): on a model that repeats tokens its chains are accepted, which runs the
+    accepting path with several drafts per step; tokens and logit gaps stay those of plain decoding."""
+    cfg = synthetic_config("tiny-gdn")
+    prompts = _prompts(cfg, 1)
+    base, lb = _run(cfg, prompts, None)
+    H = cfg.hidden_size
+
+    def rig(llm):
+        m = llm.runner.mtp
+        m.w["fc"] = torch.cat([torch.zeros(H, H), torch.eye(H)], 1).to(torch.bfloat16)
+        m.inner.layers[0]["o"].zero_()
+        m.inner.layers[0]["down"].zero_()
+
+    for k in (1, 3):
+        llm = LLM(EngineArgs(model_config=cfg, device="cpu", block_size=16, num_blocks=160, max_model_len=512,
+                             max_num_seqs=4, max_num_batched_tokens=64,
+                             speculative_config=SpeculativeConfig(method="mtp", num_speculative_tokens=k)))
+        rig(llm)
+        sp = SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True)
+        got = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+        assert got == base
+        st = llm.runner.spec_stats
+        assert st["accepted"] > 0.5 * st["drafted"] > 0, st
+        # fewer trunk steps than tokens: accepted drafts really shorten the loop
+        assert llm.runner.num_kernel_steps < 14 + 4

@@ -10,12 +10,13 @@ The decoder blocks are an instance of the trunk's own model class over a configu
 only those layers, so every kernel, the paged KV cache and chunked prefill behave as in the trunk;
 the head only replaces the input rows (``inputs_embeds``) and owns the three extra tensors.
 
-As a drafter (``SpeculativeConfig(method="mtp", num_speculative_tokens=1)``): after the trunk's
+As a drafter (``SpeculativeConfig(method="mtp", num_speculative_tokens=k)``): after the trunk's
 step the head runs over the same rows with the token ids shifted by one (the last accepted row of a
 request gets the token the trunk just chose), which both fills the head's KV cache for every
-position the trunk has passed and yields one draft per request for the next step. Rows past the
-accepted prefix of a verification write cache entries that the next pass over those positions
-overwrites.
+position the trunk has passed and yields one draft per request for the next step. Drafts two to k
+come from decode-only passes of the head over its own hidden state (one row per request, at the
+look-ahead positions the scheduler reserved). Rows past the accepted prefix of a verification, and
+those look-ahead rows, write cache entries that the next pass over those positions overwrites.
 
 Reference: src/vllm/model_executor/models/qwen3_5_mtp.cpp (weights and forward of the head; the
 reference does not connect it to its engine loop).
@@ -86,8 +87,20 @@ class Qwen35MTP:
     def alloc(self, num_blocks: int, block_size: int, max_tokens: int, max_reqs: int) -> None:
         self.inner.alloc_kv_cache(num_blocks, block_size)
         self.inner.reserve_buffers(max_tokens, max_reqs)
-        self.next_ids = torch.zeros(max_tokens, dtype=torch.int64, device=self.target.device)
-        self.rows = torch.zeros(max_reqs, dtype=torch.int32, device=self.target.device)
+        dev = self.target.device
+        self.next_ids = torch.zeros(max_tokens, dtype=torch.int64, device=dev)
+        self.rows = torch.zeros(max_reqs, dtype=torch.int32, device=dev)
+        # step inputs of the decode-only passes that extend a draft chain (one row per request)
+        max_blocks = (self.inner.max_position + block_size - 1) // block_size + 1
+        self.d_pos = torch.zeros(max_reqs, dtype=torch.int64, device=dev)
+        self.d_slots = torch.zeros(max_reqs, dtype=torch.int64, device=dev)
+        self.d_seq = torch.zeros(max_reqs, dtype=torch.int32, device=dev)
+        self.d_qs = torch.zeros(max_reqs + 1, dtype=torch.int32, device=dev)
+        self.d_bt = None
+        self._max_reqs = max_reqs
+
+    def bind_block_table(self, max_blocks: int) -> None:
+        self.d_bt = torch.zeros((self._max_reqs, max_blocks), dtype=torch.int32, device=self.target.device)
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx, next_ids: torch.Tensor, hidden: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

@@ -72,8 +72,6 @@ class ModelRunner(E.ModelRunnerBase):
         self.spec = speculative_config if (speculative_config is not None and
                                            speculative_config.method in ("ngram", "mtp")) else None
         self.max_spec = self.spec.num_speculative_tokens if self.spec else 0
-        if self.spec is not None and self.spec.method == "mtp":
-            self.max_spec = 1            # the head predicts one token past the trunk's
         self.mtp = None
         self.mtp_proposed: dict[str, list[int]] = {}     # every draft the head proposed, per request
         self._last_ctx = None
@@ -629,6 +627,7 @@ class ModelRunner(E.ModelRunnerBase):
         """The multi-token-prediction drafter of the model (its blocks get a KV cache over the same
         block numbers as the trunk's, and activation buffers of the step's size)."""
         mtp.alloc(self.num_blocks, self.block_size, self.max_tokens, self.max_num_seqs)
+        mtp.bind_block_table(self.max_blocks)
         self.mtp = mtp
 
     def _propose_mtp(self, info, toks) -> None:
@@ -670,13 +669,66 @@ class ModelRunner(E.ModelRunnerBase):
             m.rows[:n].copy_(torch.tensor(rows, dtype=torch.int32))
         # the head runs even when no request wants a draft: its cache must cover every position
         logits = m.forward(self._last_ctx, m.next_ids, self.model.last_full, m.rows[:max(n, 1)])
-        if n:
-            draft = logits[:n].argmax(-1).tolist()
-            for rid, d in zip(rids, draft):
-                self._drafts[rid] = [int(d)]
-                if len(self.mtp_proposed) > 256:          # a debugging aid, not a log: keep it small
-                    self.mtp_proposed.clear()
-                self.mtp_proposed.setdefault(rid, []).append(int(d))
+        if not n:
+            return
+        draft = logits[:n].argmax(-1)
+        chains = [[int(d)] for d in draft.tolist()]
+        if self.max_spec > 1:
+            self._extend_mtp_drafts(info, rows, rids, draft, chains)
+        for rid, ch in zip(rids, chains):
+            self._drafts[rid] = ch
+            if len(self.mtp_proposed) > 256:          # a debugging aid, not a log: keep it small
+                self.mtp_proposed.clear()
+            self.mtp_proposed.setdefault(rid, []).extend(ch)
+
+    def _extend_mtp_drafts(self, info, rows, rids, draft, chains) -> None:
+        """Drafts two to k: the head continues from its own output. Step i feeds (the head's hidden
+        state of step i - 1, draft i) at position p + i, one row per request, as a decode-only
+        batch over the same block tables (the scheduler reserved those slots as look-ahead); the
+        cache entries it writes there are replaced when the trunk reaches those positions."""
+        from ..models.base import StepContext
+        m, hv, n = self.mtp, self.host_views, len(rows)
+        R = info.num_reqs
+        qs = hv["query_start"][: R + 1].tolist()
+        req_of_row = {}
+        for r in range(R):
+            for row in range(qs[r], qs[r + 1]):
+                req_of_row[row] = r
+        reqs = [req_of_row[row] for row in rows]
+        pos0 = torch.tensor([int(hv["positions"][row]) for row in rows], dtype=torch.int64)
+        bt_host = torch.stack([hv["block_table"][0][r] for r in reqs], 0)          # [n, max_blocks]
+        bs = self.block_size
+        hidden = m.inner.last_full[torch.tensor(rows, dtype=torch.long, device=self.device)].clone()
+        ids = draft.to(torch.int64)
+        dev = self.device
+        m.d_bt[:n].copy_(bt_host)
+        m.d_qs[: n + 1].copy_(torch.arange(n + 1, dtype=torch.int32))
+        m.rows[:n].copy_(torch.arange(n, dtype=torch.int32))
+        for i in range(1, self.max_spec):
+            pos = pos0 + i
+            if int(pos.max()) + 1 >= self.max_model_len:
+                break
+            blk = torch.gather(bt_host.long(), 1, (pos // bs).unsqueeze(1)).squeeze(1)
+            m.d_pos[:n].copy_(pos)
+            m.d_slots[:n].copy_(blk * bs + pos % bs)
+            m.d_seq[:n].copy_((pos + 1).to(torch.int32))
+            m.next_ids[:n].copy_(ids)
+            splits, tmp = self._decode_splits(n) if self.is_cuda else (1, None)
+            ctx = StepContext(
+                num_tokens=n, num_reqs=n, num_decodes=n, num_prefills=0, num_prefill_tokens=0, num_tiles=0,
+                num_logits=n, input_ids=m.next_ids, positions=m.d_pos, slot_mapping=[m.d_slots],
+                query_start=m.d_qs if self.is_cuda else m.d_qs[: n + 1],
+                seq_lens=m.d_seq if self.is_cuda else m.d_seq[:n],
+                block_table=[m.d_bt if self.is_cuda else m.d_bt[:n]], logits_indices=m.rows,
+                tile_req=self.views["tile_req"], tile_q0=self.views["tile_q0"],
+                prefill_q_start=self.views["prefill_q_start"], state_slots=self.views["state_slots"],
+                decode_splits=splits, max_seq_len=int(pos.max()) + 1, max_query_len=1)
+            ctx.extra["decode_tmp"] = tmp
+            logits = m.forward(ctx, m.next_ids, hidden, m.rows[:n])
+            ids = logits[:n].argmax(-1).to(torch.int64)
+            for ch, d in zip(chains, ids.tolist()):
+                ch.append(int(d))
+            hidden = m.inner.last_full[:n].clone()
 
     def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
         info = self._info
