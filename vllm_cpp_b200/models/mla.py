@@ -222,7 +222,7 @@ class DeepseekV2Model(MoeModel):
 
     def fused_tp_supported(self) -> bool:
         return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
-                and self.cfg.hidden_size % 8 == 0)
+                and self.cfg.hidden_size % 8 == 0 and not getattr(self, "quantized", None))
 
     # ------------------------------------------------------------------ attention
     def _decode_plan(self, B: int, max_seq_len: int):

@@ -327,7 +327,9 @@ class MoeModel(DenseModel):
         return logits[:, : c.vocab_size] if logits.shape[1] != c.vocab_size else logits
 
     def fused_tp_supported(self) -> bool:
-        return self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+        # the fused GEMMs take bf16 weights; quantised checkpoints run tensor parallel over NCCL
+        return (self.tp > 1 and self.par.fused_collectives and self.device.type == "cuda"
+                and not getattr(self, "quantized", None))
 
     def _forward_tp_fused_moe(self, ctx: StepContext) -> torch.Tensor:
         """TP attention + EP experts with every collective fused into a kernel."""
