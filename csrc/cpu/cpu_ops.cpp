@@ -7,11 +7,16 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
 #if defined(__x86_64__)
 #include <immintrin.h>
+#if defined(__linux__)
+#include <sys/syscall.h>
+#include <unistd.h>
+#endif
 #endif
 
 #include "cpu_common.h"
@@ -86,6 +91,162 @@ __attribute__((target("avx2,fma"))) static void axpy_bf16_avx2(float p, const bf
 }
 #endif
 
+#if defined(__x86_64__)
+// ------------------------------------------------------------------ AVX-512 BF16 tier (GEMM)
+// vdpbf16ps multiplies 32 bf16 pairs and adds them into 16 fp32 lanes, so neither operand is
+// widened first and one instruction does the work of four AVX2 FMAs. B200CPU_SIMD=avx2 (or
+// scalar) in the environment keeps the narrower tiers, for comparing them.
+static int simd_cap() {
+  static const int cap = [] {
+    const char* e = std::getenv("B200CPU_SIMD");
+    if (e && !std::strcmp(e, "scalar")) return 0;
+    if (e && !std::strcmp(e, "avx2")) return 2;
+    if (e && !std::strcmp(e, "avx512")) return 3;
+    return 4;
+  }();
+  return cap;
+}
+static bool has_avx512bf16() {
+  static const bool ok = __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") &&
+                         __builtin_cpu_supports("avx512vl") && __builtin_cpu_supports("avx512bf16");
+  return ok && simd_cap() >= 3;
+}
+#define B200_T512 __attribute__((target("avx512f,avx512bw,avx512vl,avx512bf16,avx2,fma")))
+B200_T512 static inline float hsum16(__m512 v) {
+  // lanes i and i + 8 first, then the 8-lane order of the other tiers
+  const __m256 s = _mm256_add_ps(_mm512_castps512_ps256(v),
+                                 _mm256_castpd_ps(_mm512_extractf64x4_pd(_mm512_castps_pd(v), 1)));
+  return hsum8(s);
+}
+// MB activation rows x NB weight rows: MB * NB accumulators stay in registers over the whole K
+// loop (6 x 4 = 24 of the 32 vector registers), every 64-byte load of A is used NB times and
+// every load of W MB times. Each output's sum runs over K in the same order whatever the block
+// it falls in, so results do not depend on the batch size or the thread partition.
+template <int MB, int NB>
+B200_T512 static void gemm_block_512(const bf16_t* a, int64_t lda, const bf16_t* w, int64_t ldw, int K, float* out) {
+  __m512 acc[MB][NB];
+  for (int m = 0; m < MB; ++m)
+    for (int n = 0; n < NB; ++n) acc[m][n] = _mm512_setzero_ps();
+  int k = 0;
+  for (; k + 32 <= K; k += 32) {
+    __m512bh wv[NB];
+    for (int n = 0; n < NB; ++n) wv[n] = (__m512bh)_mm512_loadu_si512(w + n * ldw + k);
+    for (int m = 0; m < MB; ++m) {
+      const __m512bh av = (__m512bh)_mm512_loadu_si512(a + m * lda + k);
+      for (int n = 0; n < NB; ++n) acc[m][n] = _mm512_dpbf16_ps(acc[m][n], av, wv[n]);
+    }
+  }
+  for (int m = 0; m < MB; ++m) {
+    if (NB == 4) {
+      // four horizontal sums at once, each in hsum16's order: lanes i + (i + 8), then
+      // ((0+4)+(2+6)) + ((1+5)+(3+7)) through a 4 x 4 transpose
+      __m128 t[4];
+      for (int n = 0; n < 4; ++n) {
+        const __m256 h = _mm256_add_ps(_mm512_castps512_ps256(acc[m][n]),
+                                       _mm256_castpd_ps(_mm512_extractf64x4_pd(_mm512_castps_pd(acc[m][n]), 1)));
+        t[n] = _mm_add_ps(_mm256_castps256_ps128(h), _mm256_extractf128_ps(h, 1));
+      }
+      _MM_TRANSPOSE4_PS(t[0], t[1], t[2], t[3]);
+      _mm_storeu_ps(out + m * 4, _mm_add_ps(_mm_add_ps(t[0], t[2]), _mm_add_ps(t[1], t[3])));
+      if (k < K)
+        for (int n = 0; n < 4; ++n) {
+          float s = out[m * 4 + n];
+          for (int kk = k; kk < K; ++kk) s = std::fmaf(bf16_to_f32(w[n * ldw + kk]), bf16_to_f32(a[m * lda + kk]), s);
+          out[m * 4 + n] = s;
+        }
+      continue;
+    }
+    for (int n = 0; n < NB; ++n) {
+      float s = hsum16(acc[m][n]);
+      for (int kk = k; kk < K; ++kk) s = std::fmaf(bf16_to_f32(w[n * ldw + kk]), bf16_to_f32(a[m * lda + kk]), s);
+      out[m * NB + n] = s;
+    }
+  }
+}
+template <int NB>
+B200_T512 static void gemm_rows_512(int mb, const bf16_t* a, int64_t lda, const bf16_t* w, int64_t ldw, int K,
+                                    float* out) {
+  switch (mb) {
+    case 6: gemm_block_512<6, NB>(a, lda, w, ldw, K, out); break;
+    case 5: gemm_block_512<5, NB>(a, lda, w, ldw, K, out); break;
+    case 4: gemm_block_512<4, NB>(a, lda, w, ldw, K, out); break;
+    case 3: gemm_block_512<3, NB>(a, lda, w, ldw, K, out); break;
+    case 2: gemm_block_512<2, NB>(a, lda, w, ldw, K, out); break;
+    default: gemm_block_512<1, NB>(a, lda, w, ldw, K, out); break;
+  }
+}
+#endif
+
+#if defined(__x86_64__) && defined(__linux__)
+// ------------------------------------------------------------------ AMX tier (GEMM)
+// Tile matrix multiply: one TDPBF16PS does a 16 x 16 x 32 bf16 block (fp32 accumulate). The
+// weight matrix [N, K] is the row-major operand as it lies in memory; the activations are packed
+// once per call into the pair-interleaved layout the second operand needs ([k / 2][m][2]), so the
+// product comes out transposed (C^T[n][m]) and the epilogue writes it back row by row. The kernel
+// must ask the kernel for permission to use tile state once per process; each worker thread loads
+// its own tile configuration.
+struct AmxTileCfg {
+  uint8_t palette, start_row;
+  uint8_t rsv[14];
+  uint16_t colsb[16];
+  uint8_t rows[16];
+} __attribute__((packed));
+
+static bool has_amx() {
+  static const bool ok = [] {
+    if (simd_cap() < 4) return false;
+    if (!__builtin_cpu_supports("amx-tile") || !__builtin_cpu_supports("amx-bf16") || !has_avx2()) return false;
+    return syscall(SYS_arch_prctl, 0x1023 /* ARCH_REQ_XCOMP_PERM */, 18 /* XFEATURE_XTILEDATA */) == 0;
+  }();
+  return ok;
+}
+
+#define B200_TAMX __attribute__((target("amx-tile,amx-bf16,avx2,fma")))
+// rows [n0, n0 + 32) of W against all of M. wblk: the 32 weight rows (row stride ldw elements);
+// ap: packed activations [mblocks][kblocks][16][32]; ct: scratch [32][32] fp32.
+B200_TAMX static void amx_block(const bf16_t* w0, const bf16_t* w1, int64_t ldw, const bf16_t* ap, int mblocks,
+                                int kblocks, int mb0, float* ct) {
+  // tiles 0..3: C (n-half x m-half), 4 / 5: weight rows, 6 / 7: packed activations
+  _tile_zero(0); _tile_zero(1); _tile_zero(2); _tile_zero(3);
+  const bf16_t* b0 = ap + (size_t)mb0 * kblocks * 512;
+  const bool two_m = mb0 + 1 < mblocks;
+  const bf16_t* b1 = two_m ? b0 + (size_t)kblocks * 512 : b0;
+  // a decode-sized batch streams each weight row once, 64 bytes per k-step from 32 rows that are
+  // kilobytes apart: too many streams for the hardware prefetcher, so the lines are asked for ahead
+  const bool stream = mblocks <= 2;
+  for (int kb = 0; kb < kblocks; ++kb) {
+    if (stream && kb + 8 < kblocks) {
+      for (int r = 0; r < 16; ++r) {
+        _mm_prefetch(reinterpret_cast<const char*>(w0 + r * ldw + (kb + 8) * 32), _MM_HINT_T0);
+        _mm_prefetch(reinterpret_cast<const char*>(w1 + r * ldw + (kb + 8) * 32), _MM_HINT_T0);
+      }
+    }
+    _tile_loadd(4, w0 + kb * 32, ldw * 2);
+    _tile_loadd(5, w1 + kb * 32, ldw * 2);
+    _tile_loadd(6, b0 + (size_t)kb * 512, 64);
+    _tile_dpbf16ps(0, 4, 6);
+    _tile_dpbf16ps(2, 5, 6);
+    if (two_m) {
+      _tile_loadd(7, b1 + (size_t)kb * 512, 64);
+      _tile_dpbf16ps(1, 4, 7);
+      _tile_dpbf16ps(3, 5, 7);
+    }
+  }
+  _tile_stored(0, ct, 128);                 // rows 0..15 (n), columns 0..15 (m)
+  _tile_stored(1, ct + 16, 128);            //               columns 16..31
+  _tile_stored(2, ct + 16 * 32, 128);       // rows 16..31
+  _tile_stored(3, ct + 16 * 32 + 16, 128);
+}
+B200_TAMX static void amx_load_cfg() {
+  AmxTileCfg cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.palette = 1;
+  for (int i = 0; i < 8; ++i) { cfg.colsb[i] = 64; cfg.rows[i] = 16; }
+  _tile_loadconfig(&cfg);
+}
+B200_TAMX static void amx_release() { _tile_release(); }
+#endif
+
 static float dot_bf16_bf16(const bf16_t* a, const bf16_t* b, int D) {
 #if defined(__x86_64__)
   if (has_avx2()) return dot_bf16_bf16_avx2(a, b, D);
@@ -113,7 +274,15 @@ extern "C" {
 
 void b200cpu_set_threads(int n) { ThreadPool::set_num_threads(n); }
 int b200cpu_num_threads() { return ThreadPool::instance().size(); }
-int b200cpu_simd_tier() { return has_avx2() ? 2 : 0; }
+int b200cpu_simd_tier() {
+#if defined(__x86_64__) && defined(__linux__)
+  if (has_amx()) return 4;
+#endif
+#if defined(__x86_64__)
+  if (has_avx512bf16()) return 3;
+#endif
+  return has_avx2() ? 2 : 0;
+}
 
 // out[M, N] = A[M, K] W[N, K]^T (+ bias[N]) (+ residual[M, N]); bf16 in, fp32 accumulate, one
 // rounding at the end (bf16 or fp32 output). Threads own ranges of output columns; a weight row
@@ -122,8 +291,96 @@ void b200cpu_matmul_bt(const uint16_t* A, int64_t lda, const uint16_t* W, int64_
                        int out_f32, const uint16_t* bias, const uint16_t* residual, int64_t ldr, int M,
                        int N, int K) {
   if (M <= 0 || N <= 0) return;
-  std::vector<float> af((size_t)M * K);
   ThreadPool& tp = ThreadPool::instance();
+#if defined(__x86_64__) && defined(__linux__)
+  if (has_amx() && K % 32 == 0 && K >= 32) {
+    // every batch size takes this path (rows are padded to 16), so a row's result does not depend
+    // on what it is batched with
+    const int mblocks = (M + 15) / 16, kblocks = K / 32;
+    std::vector<bf16_t> ap((size_t)mblocks * kblocks * 512);
+    auto pack = [&](int64_t b0, int64_t b1) {
+      for (int64_t mb = b0; mb < b1; ++mb)
+        for (int kb = 0; kb < kblocks; ++kb) {
+          bf16_t* dst = ap.data() + ((size_t)mb * kblocks + kb) * 512;
+          for (int j = 0; j < 16; ++j)
+            for (int m = 0; m < 16; ++m) {
+              const int64_t row = mb * 16 + m;
+              uint32_t pair = 0;
+              if (row < M) std::memcpy(&pair, A + row * lda + kb * 32 + 2 * j, 4);
+              std::memcpy(dst + j * 32 + m * 2, &pair, 4);
+            }
+        }
+    };
+    if (mblocks <= 2) pack(0, mblocks);          // a few kilobytes: not worth waking the pool
+    else tp.parallel_for(mblocks, 1, pack);
+    const int nblocks = (N + 31) / 32;
+    tp.parallel_for(nblocks, 1, [&](int64_t nb0, int64_t nb1) {
+      amx_load_cfg();
+      alignas(64) float ct[32 * 32];
+      std::vector<bf16_t> edge;
+      for (int64_t nb = nb0; nb < nb1; ++nb) {
+        const int64_t n0 = nb * 32;
+        const int nrows = (int)std::min<int64_t>(32, N - n0);
+        const bf16_t* w0 = W + n0 * ldw;
+        int64_t ld = ldw;
+        if (nrows < 32) {                       // last block: its missing rows read as zeros
+          edge.assign((size_t)32 * K, 0);
+          for (int r = 0; r < nrows; ++r) std::memcpy(edge.data() + (size_t)r * K, W + (n0 + r) * ldw, (size_t)K * 2);
+          w0 = edge.data();
+          ld = K;
+        }
+        for (int mb = 0; mb < mblocks; mb += 2) {
+          amx_block(w0, w0 + 16 * ld, ld, ap.data(), mblocks, kblocks, mb, ct);
+          const int mrows = std::min(32, M - mb * 16);
+          for (int i = 0; i < mrows; ++i) {
+            const int64_t m = (int64_t)mb * 16 + i;
+            for (int j = 0; j < nrows; ++j) {
+              const int64_t n = n0 + j;
+              float v = ct[j * 32 + i];
+              if (bias) v = v + bf16_to_f32(bias[n]);
+              if (residual) v = v + bf16_to_f32(residual[m * ldr + n]);
+              if (out_f32) reinterpret_cast<float*>(out)[m * ldo + n] = v;
+              else reinterpret_cast<uint16_t*>(out)[m * ldo + n] = f32_to_bf16(v);
+            }
+          }
+        }
+      }
+      amx_release();
+    });
+    return;
+  }
+#endif
+#if defined(__x86_64__)
+  if (has_avx512bf16()) {
+    auto store = [&](int64_t m, int64_t n, float v) {
+      if (bias) v = v + bf16_to_f32(bias[n]);
+      if (residual) v = v + bf16_to_f32(residual[m * ldr + n]);
+      if (out_f32) reinterpret_cast<float*>(out)[m * ldo + n] = v;
+      else reinterpret_cast<uint16_t*>(out)[m * ldo + n] = f32_to_bf16(v);
+    };
+    tp.parallel_for(N, 16, [&](int64_t n0, int64_t n1) {
+      float tmp[6 * 4];
+      for (int64_t n = n0; n < n1; n += 4) {
+        const int nb = (int)std::min<int64_t>(4, n1 - n);
+        for (int m = 0; m < M; m += 6) {
+          const int mb = std::min(6, M - m);
+          const bf16_t* a = A + (int64_t)m * lda;
+          const bf16_t* w = W + n * ldw;
+          switch (nb) {
+            case 4: gemm_rows_512<4>(mb, a, lda, w, ldw, K, tmp); break;
+            case 3: gemm_rows_512<3>(mb, a, lda, w, ldw, K, tmp); break;
+            case 2: gemm_rows_512<2>(mb, a, lda, w, ldw, K, tmp); break;
+            default: gemm_rows_512<1>(mb, a, lda, w, ldw, K, tmp); break;
+          }
+          for (int i = 0; i < mb; ++i)
+            for (int j = 0; j < nb; ++j) store(m + i, n + j, tmp[i * nb + j]);
+        }
+      }
+    });
+    return;
+  }
+#endif
+  std::vector<float> af((size_t)M * K);
   tp.parallel_for(M, 1, [&](int64_t m0, int64_t m1) {
     for (int64_t m = m0; m < m1; ++m)
       for (int k = 0; k < K; ++k) af[(size_t)m * K + k] = bf16_to_f32(A[m * lda + k]);
@@ -169,7 +426,8 @@ void b200cpu_matmul_bt(const uint16_t* A, int64_t lda, const uint16_t* W, int64_
 // residual (optional, in place): r = bf16(x + residual); out = bf16(r * rsqrt(mean(r^2) + eps) * (w [+ 1])).
 void b200cpu_rmsnorm(const uint16_t* x, int64_t ldx, const uint16_t* w, float eps, uint16_t* residual,
                      int64_t ldr, uint16_t* out, int64_t ldo, int T, int H, int gemma) {
-  ThreadPool::instance().parallel_for(T, 1, [&](int64_t t0, int64_t t1) {
+  // a part is worth a thread from about 32 K elements on; decode-sized calls run inline
+  ThreadPool::instance().parallel_for(T, std::max(1, 32768 / std::max(1, H)), [&](int64_t t0, int64_t t1) {
     std::vector<float> row(H);
     for (int64_t t = t0; t < t1; ++t) {
       double ss = 0.0;
@@ -194,7 +452,7 @@ void b200cpu_rmsnorm(const uint16_t* x, int64_t ldx, const uint16_t* w, float ep
 
 // x = [gate | up]; out = bf16(act(gate) * up). kind: 0 SiLU, 1 GELU-tanh, 2 GELU-erf.
 void b200cpu_act_and_mul(const uint16_t* x, int64_t ldx, uint16_t* out, int64_t ldo, int T, int I, int kind) {
-  ThreadPool::instance().parallel_for(T, 1, [&](int64_t t0, int64_t t1) {
+  ThreadPool::instance().parallel_for(T, std::max(1, 16384 / std::max(1, I)), [&](int64_t t0, int64_t t1) {
     for (int64_t t = t0; t < t1; ++t)
       for (int i = 0; i < I; ++i) {
         const float g = bf16_to_f32(x[t * ldx + i]), u = bf16_to_f32(x[t * ldx + I + i]);
@@ -230,7 +488,7 @@ void b200cpu_rope_kv(uint16_t* qkv, int64_t ld, const int64_t* positions, const 
                      int Hkv, int D, int rot, int neox, const uint16_t* q_norm, const uint16_t* k_norm,
                      float eps, int gemma, const int64_t* slot_mapping, uint16_t* kv_cache, int block_size) {
   const int half = rot / 2;
-  ThreadPool::instance().parallel_for(T, 1, [&](int64_t t0, int64_t t1) {
+  ThreadPool::instance().parallel_for(T, std::max(1, 32768 / std::max(1, (Hq + Hkv) * D)), [&](int64_t t0, int64_t t1) {
     std::vector<float> buf(D);
     std::vector<uint16_t> krow((size_t)Hkv * D);
     for (int64_t t = t0; t < t1; ++t) {

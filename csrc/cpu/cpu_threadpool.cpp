@@ -47,9 +47,10 @@ ThreadPool::~ThreadPool() {
 void ThreadPool::worker_loop(int id) {
   uint64_t seen = 0;
   while (true) {
-    // spin a little (back-to-back ops of one forward pass), then park
+    // spin for about a millisecond (the ops of one forward pass follow each other within tens of
+    // microseconds; waking a parked thread costs more than the small ops themselves), then park
     uint64_t e = epoch_.load(std::memory_order_acquire);
-    for (int spin = 0; e == seen && spin < 2000; ++spin) {
+    for (int spin = 0; e == seen && spin < 30000; ++spin) {
 #if defined(__x86_64__)
       __builtin_ia32_pause();
 #endif
