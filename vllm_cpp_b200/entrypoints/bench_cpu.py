@@ -105,6 +105,9 @@ def main(argv=None) -> int:
         "backend": llm.model.be.name, "layers": cfg.num_layers,
         "threads": (__import__("vllm_cpp_b200.ops.cpu_native", fromlist=["x"]).num_threads()
                     if args.backend == "native" else torch.get_num_threads()),
+        "gemm_tier": ({0: "scalar", 2: "avx2", 3: "avx512-bf16", 4: "amx-bf16"}.get(
+            __import__("vllm_cpp_b200.ops.cpu_native", fromlist=["x"]).lib().b200cpu_simd_tier(), "?")
+            if args.backend == "native" else "torch"),
         "prefill_tok_s": round(n_in / t_prefill, 1), "decode_tok_s": round(n_out / t_decode, 1),
         "decode_steps": steps, "wall_s": round(t_prefill + t_decode, 2),
         "output_tok_s": round(args.prompts * args.output_len / (t_prefill + t_decode), 2),
