@@ -24,9 +24,19 @@
 
 namespace b200cpu {
 
+static int simd_cap() {
+  static const int cap = [] {
+    const char* e = std::getenv("B200CPU_SIMD");
+    if (e && !std::strcmp(e, "scalar")) return 0;
+    if (e && !std::strcmp(e, "avx2")) return 2;
+    if (e && !std::strcmp(e, "avx512")) return 3;
+    return 4;
+  }();
+  return cap;
+}
 static bool has_avx2() {
 #if defined(__x86_64__)
-  static const bool ok = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma");
+  static const bool ok = __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma") && simd_cap() >= 2;
   return ok;
 #else
   return false;
@@ -96,16 +106,6 @@ __attribute__((target("avx2,fma"))) static void axpy_bf16_avx2(float p, const bf
 // vdpbf16ps multiplies 32 bf16 pairs and adds them into 16 fp32 lanes, so neither operand is
 // widened first and one instruction does the work of four AVX2 FMAs. B200CPU_SIMD=avx2 (or
 // scalar) in the environment keeps the narrower tiers, for comparing them.
-static int simd_cap() {
-  static const int cap = [] {
-    const char* e = std::getenv("B200CPU_SIMD");
-    if (e && !std::strcmp(e, "scalar")) return 0;
-    if (e && !std::strcmp(e, "avx2")) return 2;
-    if (e && !std::strcmp(e, "avx512")) return 3;
-    return 4;
-  }();
-  return cap;
-}
 static bool has_avx512bf16() {
   static const bool ok = __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") &&
                          __builtin_cpu_supports("avx512vl") && __builtin_cpu_supports("avx512bf16");

@@ -118,3 +118,39 @@ def test_engine_on_native_backend_matches_oracle():
     same = sum(a == b for x, y in zip(outs["torch"], outs["native"]) for a, b in zip(x, y))
     assert [x[0] for x in outs["torch"]] == [x[0] for x in outs["native"]]
     assert same >= 0.75 * 24
+
+
+def test_gemm_tiers_agree():
+    """The GEMM tiers this machine offers (scalar, AVX2, AVX-512 BF16, AMX tiles; the cap is read
+    once per process, so each runs in a child) give the same product up to fp32 summation order."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch, sys\n"
+        "from vllm_cpp_b200.ops import cpu_native as CN\n"
+        "g = torch.Generator().manual_seed(3)\n"
+        "a = torch.randn(37, 1056, generator=g).to(torch.bfloat16)\n"
+        "w = (torch.randn(203, 1056, generator=g) * 0.05).to(torch.bfloat16)\n"
+        "b = torch.randn(203, generator=g).to(torch.bfloat16)\n"
+        "out = CN.gemm(a, w, b, out_dtype=torch.float32)\n"
+        "torch.save((CN.lib().b200cpu_simd_tier(), out), sys.argv[1])\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    outs = {}
+    for cap in ("scalar", "avx2", "avx512", ""):
+        path = os.path.join(os.environ.get("TMPDIR", "/tmp"), f"b200_tier_{os.getpid()}_{cap or 'best'}.pt")
+        env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        if cap:
+            env["B200CPU_SIMD"] = cap
+        else:
+            env.pop("B200CPU_SIMD", None)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+        tier, out = torch.load(path)
+        os.remove(path)
+        outs[tier] = out
+    assert 0 in outs                                   # the scalar tier always exists
+    base = outs[0]
+    for tier, out in outs.items():
+        assert ((out - base).abs().max() / base.abs().max()).item() < 2e-6, tier
+    if 2 in outs:
+        assert torch.equal(outs[2], outs[0])           # AVX2 sums in the scalar tier's order
