@@ -63,6 +63,9 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=4)
     ap.add_argument("--input-len", type=int, default=128)
     ap.add_argument("--output-len", type=int, default=64)
+    ap.add_argument("--weight-quant", default=None, choices=["q8_0", "q4_0"],
+                    help="keep the linear weights in GGUF blocks and multiply on the packed form (not the "
+                         "bf16 configuration the reference numbers are quoted on)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--reference-bin", default="baseline/_ref/cpu/bin/vllm-bench")
     args = ap.parse_args(argv)
@@ -82,7 +85,7 @@ def main(argv=None) -> int:
     llm = LLM(EngineArgs(model_config=cfg, device="cpu", block_size=16, max_model_len=max_len,
                          max_num_seqs=args.prompts, max_num_batched_tokens=args.prompts * args.input_len,
                          num_blocks=args.prompts * ((max_len + 15) // 16 + 1) + 8, cpu_backend=args.backend,
-                         seed=0))
+                         cpu_weight_quant=args.weight_quant, seed=0))
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (args.input_len,), generator=g).tolist()
                for _ in range(args.prompts)]
@@ -100,8 +103,8 @@ def main(argv=None) -> int:
     n_in = args.prompts * args.input_len
     n_out = args.prompts * (args.output_len - 1)
     print(json.dumps({
-        "config": "Qwen3-0.6B-shaped bf16, CPU, %d x %d -> %d, block 16" % (args.prompts, args.input_len,
-                                                                        args.output_len),
+        "config": "Qwen3-0.6B-shaped %s, CPU, %d x %d -> %d, block 16" % (args.weight_quant or "bf16", args.prompts,
+                                                                      args.input_len, args.output_len),
         "backend": llm.model.be.name, "layers": cfg.num_layers,
         "threads": (__import__("vllm_cpp_b200.ops.cpu_native", fromlist=["x"]).num_threads()
                     if args.backend == "native" else torch.get_num_threads()),
