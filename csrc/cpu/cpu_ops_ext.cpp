@@ -17,6 +17,11 @@
 #include <limits>
 #include <vector>
 
+#if defined(__x86_64__)
+#include <immintrin.h>
+#endif
+#include <cstdlib>
+
 #include "cpu_common.h"
 #include "cpu_threadpool.h"
 
@@ -336,6 +341,51 @@ void b200cpu_mla_attention(const uint16_t* q, int64_t ldq, const uint16_t* cache
   }
 }
 
+#if defined(__x86_64__)
+static bool quant_has_avx2() {
+  static const bool ok = [] {
+    const char* e = std::getenv("B200CPU_SIMD");
+    if (e && !std::strcmp(e, "scalar")) return false;
+    return (bool)__builtin_cpu_supports("avx2");
+  }();
+  return ok;
+}
+// 32 int8 weights (one block) against 32 int8 activations: |w| as unsigned bytes times a * sign(w),
+// pairs summed to 16-bit (at most 2 * 128 * 127, no saturation), then to 32-bit lanes.
+__attribute__((target("avx2"))) static inline int32_t dot32_i8(__m256i w, const int8_t* a) {
+  const __m256i av = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(a));
+  const __m256i p16 = _mm256_maddubs_epi16(_mm256_abs_epi8(w), _mm256_sign_epi8(av, w));
+  const __m256i p32 = _mm256_madd_epi16(p16, _mm256_set1_epi16(1));
+  const __m128i s = _mm_add_epi32(_mm256_castsi256_si128(p32), _mm256_extracti128_si256(p32, 1));
+  const __m128i t = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4e));
+  return _mm_cvtsi128_si32(_mm_add_epi32(t, _mm_shuffle_epi32(t, 0xb1)));
+}
+__attribute__((target("avx2"))) static void quant_row_avx2(const uint8_t* wrow, int kind, int nb, const int8_t* qa,
+                                                           const float* da, int M, int K, float* acc) {
+  const size_t bb = kind == 8 ? 34 : 18;
+  for (int m = 0; m < M; ++m) acc[m] = 0.f;
+  for (int blk = 0; blk < nb; ++blk) {
+    const uint8_t* wb = wrow + (size_t)blk * bb;
+    uint16_t dh;
+    std::memcpy(&dh, wb, 2);
+    const float dw = b200cpu::f16_to_f32(dh);
+    __m256i wv;
+    if (kind == 8) {
+      wv = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(wb + 2));
+    } else {
+      const __m128i raw = _mm_loadu_si128(reinterpret_cast<const __m128i*>(wb + 2));
+      const __m128i lo = _mm_and_si128(raw, _mm_set1_epi8(15));
+      const __m128i hi = _mm_and_si128(_mm_srli_epi16(raw, 4), _mm_set1_epi8(15));
+      wv = _mm256_sub_epi8(_mm256_set_m128i(hi, lo), _mm256_set1_epi8(8));
+    }
+    for (int m = 0; m < M; ++m) {
+      const int32_t isum = dot32_i8(wv, qa + (size_t)m * K + blk * 32);
+      acc[m] += dw * da[(size_t)m * nb + blk] * (float)isum;
+    }
+  }
+}
+#endif
+
 // ------------------------------------------------------------------------------- block-quant GEMM
 // GGUF blocks of 32 weights: Q8_0 = fp16 scale d + 32 int8 (34 bytes), value d * q; Q4_0 = fp16 d +
 // 16 bytes of nibbles (18 bytes), element j in the low nibble of byte j, element j + 16 in the
@@ -360,6 +410,24 @@ void b200cpu_matmul_bt_quant(const uint16_t* A, int64_t lda, const uint8_t* Wq, 
         for (int i = 0; i < 32; ++i) qa[m * K + blk * 32 + i] = (int8_t)std::lrintf(bf16_to_f32(src[i]) * id);
       }
   });
+#if defined(__x86_64__)
+  if (quant_has_avx2()) {
+    // one weight block is decoded once and meets every activation row; the integer block dot is
+    // exact, and each output still sums its blocks in ascending order, so the result has the bits
+    // of the scalar loop below
+    ThreadPool::instance().parallel_for(N, 4, [&](int64_t n0, int64_t n1) {
+      std::vector<float> acc(M);
+      for (int64_t n = n0; n < n1; ++n) {
+        quant_row_avx2(Wq + (size_t)n * nb * bb, kind, nb, qa.data(), da.data(), M, K, acc.data());
+        for (int m = 0; m < M; ++m) {
+          if (out_f32) ((float*)out)[(size_t)m * ldo + n] = acc[m];
+          else ((uint16_t*)out)[(size_t)m * ldo + n] = f32_to_bf16(acc[m]);
+        }
+      }
+    });
+    return;
+  }
+#endif
   ThreadPool::instance().parallel_for(N, 4, [&](int64_t n0, int64_t n1) {
     int8_t wq[32];
     for (int64_t n = n0; n < n1; ++n) {
