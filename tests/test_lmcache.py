@@ -218,7 +218,12 @@ def test_engine_reuses_kv_from_lmcache_server():
     plain = engine(False).generate([prompt], sp)[0].outputs[0].token_ids
     a = engine(True)
     assert a.generate([prompt], sp)[0].outputs[0].token_ids == plain
-    assert a.offload.stored_chunks == 2 and len(srv.store) == 2          # 64 of the 75 computed tokens
+    assert a.offload.stored_chunks == 2                                  # 64 of the 75 computed tokens
+    import time
+    deadline = time.monotonic() + 5.0                                    # the server thread files them on its own time
+    while len(srv.store) < 2 and time.monotonic() < deadline:
+        time.sleep(0.01)
+    assert len(srv.store) == 2
     b = engine(True)
     out = b.generate([prompt], sp)[0]
     assert out.outputs[0].token_ids == plain
