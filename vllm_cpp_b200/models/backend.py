@@ -295,6 +295,13 @@ class CpuNativeBackend(CpuBackend):
         from ..ops import cpu_native
         self.n = cpu_native
         cpu_native.lib()
+        # The heavy ops run on the native pool; what is left to PyTorch here is small (index ops,
+        # the sampler). Its OpenMP workers keep spinning for a while after every op and take cores
+        # from the pool (a 0.6B decode step: 71 ms with them, 49 ms without), so PyTorch gets one
+        # thread once a native back end exists. B200_TORCH_THREADS=n keeps n (0: leave it alone).
+        n = os.environ.get("B200_TORCH_THREADS", "1")
+        if n.isdigit() and int(n) > 0:
+            torch.set_num_threads(int(n))
 
     def gemm(self, a, w, bias=None, residual=None, out=None, out_dtype=torch.bfloat16):
         if isinstance(w, BlockQuantWeight) and a.dtype == torch.bfloat16 and a.stride(-1) == 1 \
