@@ -111,6 +111,12 @@ class LLM:
                 num_redundant_experts=par.eplb_redundant_experts, interval=par.eplb_interval,
                 window=par.eplb_window, num_groups=max(1, getattr(cfg, "n_group", 1) or 1)))
         budget = args.resolve_max_num_batched_tokens(cfg)
+        spec = args.speculative_config
+        # a draft model is loaded before the cache is sized: its weights and its share of every
+        # KV block come out of the same memory
+        drafter = self._load_draft_model(spec, args, par, max_len) \
+            if spec is not None and spec.method == "draft_model" else None
+        self._draft_kv_bytes = drafter.model.kv_bytes_per_block(args.block_size) if drafter else 0
         num_blocks = args.num_blocks or self._size_kv_cache(args, budget, max_len)
         if par.tensor_parallel_size > 1:
             # every rank must size its cache alike: the scheduler counts one set of blocks
@@ -118,8 +124,7 @@ class LLM:
         self.is_driver = par.rank == 0 or not par.driver_worker
         channel = self._make_step_channel(par) if (par.driver_worker and par.tensor_parallel_size > 1) else None
         use_async = args.async_scheduling if args.async_scheduling is not None else False
-        spec = args.speculative_config
-        if spec is not None and spec.method in ("ngram", "mtp"):
+        if spec is not None and spec.method in ("ngram", "mtp", "draft_model"):
             use_async = False       # drafts are verified on the host between steps
         if spec is not None and spec.method == "mtp":
             if not hasattr(self.model, "is_gdn") or par.tensor_parallel_size > 1:
@@ -137,6 +142,8 @@ class LLM:
             else:
                 mtp.init_random(args.seed)
             self.runner.attach_mtp(mtp)
+        if drafter is not None:
+            self.runner.attach_draft_model(drafter)
         sc = E.SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=args.max_num_seqs,
                                max_model_len=max_len, policy=args.scheduling_policy,
                                async_scheduling=use_async,
@@ -179,6 +186,28 @@ class LLM:
         self.step_times: list = []
 
     # ------------------------------------------------------------------ set-up helpers
+    def _load_draft_model(self, spec, args, par, max_len):
+        """The second model of ``method="draft_model"``: same device, backend and max length as the
+        target; its weights come from ``spec.draft_model`` (a directory or .gguf file) or, for a
+        ``draft_model_config``, from a seeded random init."""
+        from ..models.draft import DraftModel
+        if par.tensor_parallel_size > 1:
+            raise ValueError("method 'draft_model' runs on one rank")
+        tensors = None
+        dcfg = spec.draft_model_config
+        if dcfg is None:
+            from ..loader import load_model_dir
+            dcfg, tensors, _ = load_model_dir(spec.draft_model, args.tokenizer or args.model)
+        _, cls = registry.resolve(dcfg.architecture)
+        draft = cls(dcfg, device=self.device, parallel=par, comm=self.comm, max_position=max_len)
+        if type(draft.be) is not type(self.model.be):
+            draft.be = type(self.model.be)(self.device)
+        if tensors is not None:
+            draft.load_weights(tensors)
+        else:
+            draft.init_random(args.seed if spec.draft_seed is None else spec.draft_seed)
+        return DraftModel(draft, self.model)
+
     @staticmethod
     def _make_comm(par: ParallelConfig):
         from ..parallel.comm import SingleComm, TorchComm
@@ -215,7 +244,7 @@ class LLM:
             self.workers = None
 
     def _size_kv_cache(self, args: EngineArgs, budget: int, max_len: int) -> int:
-        per_block = self.model.kv_bytes_per_block(args.block_size)
+        per_block = self.model.kv_bytes_per_block(args.block_size) + getattr(self, "_draft_kv_bytes", 0)
         if self.device.type != "cuda":
             want = args.max_num_seqs * ((max_len + args.block_size - 1) // args.block_size) + 1
             return max(16, min(want, 4096))

@@ -561,7 +561,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
                     help="skip the pre-serve warm-up (decode graphs are then captured by the first steps that need them)")
     ap.add_argument("--speculative-config", default=None,
                     help='JSON, e.g. {"method": "ngram", "num_speculative_tokens": 3, "prompt_lookup_max": 4} '
-                         'or {"method": "mtp", "num_speculative_tokens": 1}')
+                         'or {"method": "mtp", "num_speculative_tokens": 1} '
+                         'or {"method": "draft_model", "draft_model": "<directory>", "num_speculative_tokens": 3}')
     ap.add_argument("--enable-eplb", action="store_true",
                     help="expert parallel: rebalance the expert placement from observed loads")
     ap.add_argument("--eplb-redundant-experts", type=int, default=0,

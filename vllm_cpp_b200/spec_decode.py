@@ -1,9 +1,10 @@
 """Speculative decoding building blocks: configuration (look-ahead arithmetic per method), the
 greedy rejection sampler (accept a draft token iff it equals the target's argmax, stop at the
-first mismatch, always emit one more token: the replacement or the bonus), an n-gram proposer
-and the Qwen3.5/3.6 multi-token-prediction draft head. The scheduler already reserves
-look-ahead slots and rolls rejected tokens back; as in the reference there is no user-facing
-switch that turns the whole loop on.
+first mismatch, always emit one more token: the replacement or the bonus), an n-gram proposer,
+the Qwen3.5/3.6 multi-token-prediction draft head and a separate draft model (models/draft.py).
+The scheduler reserves look-ahead slots and rolls rejected tokens back; the loop is switched on
+with ``EngineArgs(speculative_config=...)`` or the server's ``--speculative-config`` (methods
+ngram, mtp and draft_model; the reference stops short of a user-facing switch).
 
 Reference: ``include/vllm/config/speculative.h``, ``include/vllm/v1/spec_decode/
 rejection_sampler.h:1-128``, ``src/vllm/model_executor/models/qwen3_5_mtp.cpp``.
@@ -20,7 +21,9 @@ import torch
 class SpeculativeConfig:
     method: str = "mtp"                  # mtp | eagle | eagle3 | draft_model | ngram | dflash
     num_speculative_tokens: int = 1
-    draft_model: Optional[str] = None
+    draft_model: Optional[str] = None    # checkpoint directory (or .gguf file) of the draft model
+    draft_model_config: Optional[object] = None   # a ModelConfig instead: random weights from draft_seed
+    draft_seed: Optional[int] = None
     prompt_lookup_min: int = 2
     prompt_lookup_max: int = 4
     parallel_drafting: bool = False      # dflash: all draft positions from one forward
@@ -30,7 +33,7 @@ class SpeculativeConfig:
             raise ValueError(f"unknown speculative method {self.method!r}")
         if self.num_speculative_tokens < 1:
             raise ValueError("num_speculative_tokens must be at least 1")
-        if self.method == "draft_model" and not self.draft_model:
+        if self.method == "draft_model" and not self.draft_model and self.draft_model_config is None:
             raise ValueError("draft_model speculation needs a draft model")
 
     @property

@@ -67,12 +67,14 @@ class ModelRunner(E.ModelRunnerBase):
         # Speculative decoding, n-gram (prompt lookup) drafts verified by argmax comparison:
         # a request scheduled with k drafts runs k + 1 query tokens, gets k + 1 logits rows and
         # keeps the longest prefix of drafts that the target agrees with plus one more token.
-        # "mtp": the drafts come from the model's multi-token-prediction head instead (one per
-        # step, models/gdn_mtp.py), verified the same way.
+        # "mtp": the drafts come from the model's multi-token-prediction head instead
+        # (models/gdn_mtp.py); "draft_model": from a second, smaller model (models/draft.py). Both
+        # are verified the same way.
         self.spec = speculative_config if (speculative_config is not None and
-                                           speculative_config.method in ("ngram", "mtp")) else None
+                                           speculative_config.method in ("ngram", "mtp", "draft_model")) else None
         self.max_spec = self.spec.num_speculative_tokens if self.spec else 0
         self.mtp = None
+        self.drafter = None                              # a separate draft model (models/draft.py)
         self.mtp_proposed: dict[str, list[int]] = {}     # every draft the head proposed, per request
         self._last_ctx = None
         self._drafts: dict[str, list[int]] = {}
@@ -613,6 +615,8 @@ class ModelRunner(E.ModelRunnerBase):
             out.num_recompute = recompute          # (assigned whole: the binding copies containers)
         if self.mtp is not None:
             self._propose_mtp(info, toks)
+        elif self.drafter is not None:
+            self._propose_draft_model(info, toks)
         elif self.spec is not None:
             for r, p in enumerate(info.produces_token):
                 rid = info.req_ids[r]
@@ -686,7 +690,6 @@ class ModelRunner(E.ModelRunnerBase):
         state of step i - 1, draft i) at position p + i, one row per request, as a decode-only
         batch over the same block tables (the scheduler reserved those slots as look-ahead); the
         cache entries it writes there are replaced when the trunk reaches those positions."""
-        from ..models.base import StepContext
         m, hv, n = self.mtp, self.host_views, len(rows)
         R = info.num_reqs
         qs = hv["query_start"][: R + 1].tolist()
@@ -697,38 +700,92 @@ class ModelRunner(E.ModelRunnerBase):
         reqs = [req_of_row[row] for row in rows]
         pos0 = torch.tensor([int(hv["positions"][row]) for row in rows], dtype=torch.int64)
         bt_host = torch.stack([hv["block_table"][0][r] for r in reqs], 0)          # [n, max_blocks]
-        bs = self.block_size
         hidden = m.inner.last_full[torch.tensor(rows, dtype=torch.long, device=self.device)].clone()
         ids = draft.to(torch.int64)
-        dev = self.device
-        m.d_bt[:n].copy_(bt_host)
-        m.d_qs[: n + 1].copy_(torch.arange(n + 1, dtype=torch.int32))
-        m.rows[:n].copy_(torch.arange(n, dtype=torch.int32))
         for i in range(1, self.max_spec):
             pos = pos0 + i
             if int(pos.max()) + 1 >= self.max_model_len:
                 break
-            blk = torch.gather(bt_host.long(), 1, (pos // bs).unsqueeze(1)).squeeze(1)
-            m.d_pos[:n].copy_(pos)
-            m.d_slots[:n].copy_(blk * bs + pos % bs)
-            m.d_seq[:n].copy_((pos + 1).to(torch.int32))
             m.next_ids[:n].copy_(ids)
-            splits, tmp = self._decode_splits(n) if self.is_cuda else (1, None)
-            ctx = StepContext(
-                num_tokens=n, num_reqs=n, num_decodes=n, num_prefills=0, num_prefill_tokens=0, num_tiles=0,
-                num_logits=n, input_ids=m.next_ids, positions=m.d_pos, slot_mapping=[m.d_slots],
-                query_start=m.d_qs if self.is_cuda else m.d_qs[: n + 1],
-                seq_lens=m.d_seq if self.is_cuda else m.d_seq[:n],
-                block_table=[m.d_bt if self.is_cuda else m.d_bt[:n]], logits_indices=m.rows,
-                tile_req=self.views["tile_req"], tile_q0=self.views["tile_q0"],
-                prefill_q_start=self.views["prefill_q_start"], state_slots=self.views["state_slots"],
-                decode_splits=splits, max_seq_len=int(pos.max()) + 1, max_query_len=1)
-            ctx.extra["decode_tmp"] = tmp
+            ctx = self._draft_decode_ctx(m, n, pos, bt_host)
             logits = m.forward(ctx, m.next_ids, hidden, m.rows[:n])
             ids = logits[:n].argmax(-1).to(torch.int64)
             for ch, d in zip(chains, ids.tolist()):
                 ch.append(int(d))
             hidden = m.inner.last_full[:n].clone()
+
+    def _draft_decode_ctx(self, m, n: int, pos: torch.Tensor, bt_host: torch.Tensor):
+        """A decode-only step of ``n`` rows (one per request) at positions ``pos`` over the block
+        tables ``bt_host`` [n, max_blocks], written into the drafter's own input buffers
+        (``m.d_*``, ``m.next_ids`` already holds the token ids)."""
+        from ..models.base import StepContext
+        bs = self.block_size
+        blk = torch.gather(bt_host.long(), 1, (pos // bs).unsqueeze(1)).squeeze(1)
+        m.d_bt[:n].copy_(bt_host)
+        m.d_qs[: n + 1].copy_(torch.arange(n + 1, dtype=torch.int32))
+        m.rows[:n].copy_(torch.arange(n, dtype=torch.int32))
+        m.d_pos[:n].copy_(pos)
+        m.d_slots[:n].copy_(blk * bs + pos % bs)
+        m.d_seq[:n].copy_((pos + 1).to(torch.int32))
+        splits, tmp = self._decode_splits(n) if self.is_cuda else (1, None)
+        ctx = StepContext(
+            num_tokens=n, num_reqs=n, num_decodes=n, num_prefills=0, num_prefill_tokens=0, num_tiles=0,
+            num_logits=n, input_ids=m.next_ids, positions=m.d_pos, slot_mapping=[m.d_slots],
+            query_start=m.d_qs if self.is_cuda else m.d_qs[: n + 1],
+            seq_lens=m.d_seq if self.is_cuda else m.d_seq[:n],
+            block_table=[m.d_bt if self.is_cuda else m.d_bt[:n]], logits_indices=m.rows,
+            tile_req=self.views["tile_req"], tile_q0=self.views["tile_q0"],
+            prefill_q_start=self.views["prefill_q_start"], state_slots=self.views["state_slots"],
+            decode_splits=splits, max_seq_len=int(pos.max()) + 1, max_query_len=1)
+        ctx.extra["decode_tmp"] = tmp
+        return ctx
+
+    # ---- a separate draft model
+    def attach_draft_model(self, drafter) -> None:
+        """``drafter``: models/draft.py DraftModel. Its KV cache uses the target's block numbers."""
+        if self.num_groups != 1:
+            raise ValueError("draft-model speculation needs a target with one KV cache group")
+        drafter.alloc(self.num_blocks, self.block_size, self.max_tokens, self.max_num_seqs, self.max_blocks)
+        self.drafter = drafter
+
+    def _propose_draft_model(self, info, toks) -> None:
+        """After the target's step: the draft model runs the same rows (cache fill), then k
+        decode-only passes from the token each request just got. ``toks`` as in _propose_mtp."""
+        d, hv = self.drafter, self.host_views
+        R = info.num_reqs
+        d.fill(self._last_ctx)
+        qs = hv["query_start"][: R + 1].tolist()
+        reqs, rids, first, pos_last = [], [], [], []
+        for r in range(R):
+            new, rid = toks[r], info.req_ids[r]
+            if not new:
+                continue
+            if not self.batch.plain_greedy(rid):
+                self._drafts[rid] = []
+                continue
+            base = qs[r + 1] - 1 - info.num_draft[r]          # row of the last token the request had
+            reqs.append(r)
+            rids.append(rid)
+            first.append(new[-1])
+            pos_last.append(int(hv["positions"][base + len(new) - 1]))
+        n = len(reqs)
+        if not n:
+            return
+        bt_host = torch.stack([hv["block_table"][0][r] for r in reqs], 0)
+        ids = torch.tensor(first, dtype=torch.int64)
+        pos0 = torch.tensor(pos_last, dtype=torch.int64) + 1       # where the new token sits
+        chains = [[] for _ in range(n)]
+        for i in range(self.max_spec):
+            pos = pos0 + i
+            if int(pos.max()) + 1 >= self.max_model_len:
+                break
+            d.next_ids[:n].copy_(ids)
+            logits = d.decode(self._draft_decode_ctx(d, n, pos, bt_host))
+            ids = logits[:n].argmax(-1).to(torch.int64).cpu()
+            for ch, t in zip(chains, ids.tolist()):
+                ch.append(int(t))
+        for rid, ch in zip(rids, chains):
+            self._drafts[rid] = ch
 
     def sample_tokens(self, grammar) -> "E.ModelRunnerOutput":
         info = self._info
