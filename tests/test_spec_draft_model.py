@@ -22,7 +22,7 @@ def _run(cfg, prompts, spec, budget=256, n=14, seed=0):
     sp = SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True)
     # Besides the tokens: the draft model's logits of every chain step, and the target's logits of the
     # rows that verify those drafts one step later (row i of a verifying step predicts the same
-    # position as chain step i of the round before).
+    # position as chain step i of the drafting pass before).
     llm.draft_rounds, llm.target_rounds = {}, {}
     if llm.runner.drafter is not None:
         propose, decode, build = llm.runner._propose_draft_model, llm.runner.drafter.decode, llm.runner._build_output
